@@ -1,0 +1,253 @@
+"""TEST INFRASTRUCTURE ONLY: ctypes bindings for the parity oracle.
+
+`Oracle` wraps oracle/_build/libscn_oracle.so (the CPU restatement, scn_oracle.cpp) and
+`Reference` wraps oracle/_ref/libscn_ref.so (the reference's own Regions.cu compiled
+unchanged, see the Makefile).  Only tests/, the smoke check and the benchmark's CPU-baseline
+legs import this module; the product package never does.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "_build", "libscn_oracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libscn_ref.so")
+
+c_int, c_ll, c_f, c_p, c_d = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_double
+
+# ActivationFunction (types.h:20-29)
+NOSIGMOID, RELU, VLEAKYRELU, LEAKYRELU, TANH, SOFTMAX, PRELU, SIGMOID = range(8)
+# layer types of scn_oracle.cpp
+L_CONV, L_CONV_TRI, L_NIN, L_MAXPOOL, L_MAXPOOL_TRI, L_TERMINAL = range(6)
+
+
+def build(force=False):
+    """Compile the oracle (and oracle/_ref when the reference checkout is present)."""
+    if force or not os.path.exists(ORACLE_SO) or os.path.getmtime(ORACLE_SO) < os.path.getmtime(
+            os.path.join(HERE, "scn_oracle.cpp")):
+        subprocess.check_call(["make", "-C", HERE, "oracle"], stdout=subprocess.DEVNULL)
+    if os.path.isdir("/root/reference/SparseConvNet") and (force or not os.path.exists(REF_SO)):
+        subprocess.check_call(["make", "-C", HERE, "_ref"], stdout=subprocess.DEVNULL)
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(c_p)
+
+
+class _RulesLib:
+    """Shared flat protocol of orc_grid_rules / ref_grid_rules."""
+
+    def __init__(self, path, prefix):
+        self.lib = ctypes.CDLL(path)
+        L, self.pre = self.lib, prefix
+        f = getattr(L, prefix + "_grid_rules")
+        f.restype, f.argtypes = c_p, [c_int] * 8 + [c_p] * 4
+        for n in ("n_rules", "n_out"):
+            g = getattr(L, prefix + "_result_" + n)
+            g.restype, g.argtypes = c_ll, [c_p]
+        g = getattr(L, prefix + "_result_n_sites")
+        g.restype, g.argtypes = c_int, [c_p]
+        getattr(L, prefix + "_result_fetch").argtypes = [c_p] * 6
+        getattr(L, prefix + "_result_free").argtypes = [c_p]
+
+    def grid_rules(self, kind, dim, nIn, nOut, size, stride, minActive, keys, rows, off, bg):
+        """-> dict(rules, out_keys, out_rows, out_off, out_bg, n_sites); one call = one layer's
+        preprocess over a batch (row ids run on across samples)."""
+        keys = np.ascontiguousarray(keys, np.int64)
+        rows = np.ascontiguousarray(rows, np.int32)
+        off = np.ascontiguousarray(off, np.int32)
+        bg = np.ascontiguousarray(bg, np.int32)
+        B = len(bg)
+        L, pre = self.lib, self.pre
+        h = getattr(L, pre + "_grid_rules")(kind, dim, nIn, nOut, size, stride, minActive, B,
+                                            _p(keys), _p(rows), _p(off), _p(bg))
+        nr = getattr(L, pre + "_result_n_rules")(h)
+        no = getattr(L, pre + "_result_n_out")(h)
+        ns = getattr(L, pre + "_result_n_sites")(h)
+        rules = np.zeros(nr, np.int32)
+        ok, orow = np.zeros(no, np.int64), np.zeros(no, np.int32)
+        ooff, obg = np.zeros(B + 1, np.int32), np.zeros(B, np.int32)
+        getattr(L, pre + "_result_fetch")(h, _p(rules), _p(ok), _p(orow), _p(ooff), _p(obg))
+        getattr(L, pre + "_result_free")(h)
+        return dict(rules=rules, out_keys=ok, out_rows=orow, out_off=ooff, out_bg=obg, n_sites=ns)
+
+
+class Reference(_RulesLib):
+    """The reference's own rule construction (vectorHash order)."""
+
+    def __init__(self):
+        super().__init__(REF_SO, "ref")
+        L = self.lib
+        for n in ("ref_ipow", "ref_triangleSize", "ref_intRound"):
+            getattr(L, n).restype, getattr(L, n).argtypes = c_int, [c_int, c_int]
+        L.ref_vectorTopIndices.argtypes = [c_p, c_int, c_int, c_p]
+
+    @staticmethod
+    def available():
+        return os.path.exists(REF_SO)
+
+    def top_indices(self, v, k):
+        v = np.ascontiguousarray(v, np.float32)
+        out = np.zeros(k, np.int32)
+        self.lib.ref_vectorTopIndices(_p(v), len(v), k, _p(out))
+        return out
+
+
+class Oracle(_RulesLib):
+    def __init__(self):
+        build()
+        super().__init__(ORACLE_SO, "orc")
+        L = self.lib
+        for n in ("orc_ipow", "orc_triangleSize", "orc_intRound"):
+            getattr(L, n).restype, getattr(L, n).argtypes = c_int, [c_int, c_int]
+        L.orc_gather.argtypes = [c_p, c_p, c_ll, c_int, c_p]
+        L.orc_nin_forward.argtypes = [c_p, c_ll, c_int, c_p, c_p, c_p, c_int, c_f, c_int, c_int, c_p]
+        L.orc_maxpool.argtypes = [c_p, c_p, c_ll, c_int, c_int, c_p, c_p]
+        L.orc_terminal_pool.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p]
+        L.orc_top_indices.argtypes = [c_p, c_int, c_int, c_p]
+        L.orc_net_create.restype, L.orc_net_create.argtypes = c_p, [c_int] * 4
+        L.orc_net_free.argtypes = [c_p]
+        for n in ("orc_net_addLeNetLayerMP", "orc_net_addTriangularLeNetLayerMP"):
+            getattr(L, n).argtypes = [c_p] + [c_int] * 6 + [c_f, c_int]
+        L.orc_net_addTerminalPoolingLayer.argtypes = [c_p, c_int, c_int]
+        L.orc_net_addSoftmaxLayer.argtypes = [c_p]
+        L.orc_net_DeepCNet.restype = c_p
+        L.orc_net_DeepCNet.argtypes = [c_int] * 6 + [c_f, c_int]
+        L.orc_net_n_layers.restype, L.orc_net_n_layers.argtypes = c_int, [c_p]
+        L.orc_net_input_spatial_size.restype, L.orc_net_input_spatial_size.argtypes = c_int, [c_p]
+        L.orc_net_layer_info.argtypes = [c_p, c_int, c_p, c_p]
+        L.orc_net_set_weights.argtypes = [c_p, c_int, c_p, c_p, c_p]
+        L.orc_net_load_weights.restype, L.orc_net_load_weights.argtypes = c_int, [c_p, ctypes.c_char_p]
+        L.orc_net_forward.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p]
+        L.orc_net_iface_sizes.argtypes = [c_p, c_int, c_p]
+        L.orc_net_iface_fetch.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p]
+
+    # ---- layers
+    def gather(self, feat, rules, nIn):
+        feat = np.ascontiguousarray(feat, np.float32)
+        rules = np.ascontiguousarray(rules, np.int32).ravel()
+        out = np.zeros((rules.size, nIn), np.float32)
+        self.lib.orc_gather(_p(feat), _p(rules), rules.size, nIn, _p(out))
+        return out
+
+    def nin_forward(self, X, W, B, prelu=None, p=1.0, act=NOSIGMOID, accum64=False):
+        X = np.ascontiguousarray(X, np.float32)
+        W = np.ascontiguousarray(W, np.float32)
+        B = np.ascontiguousarray(B, np.float32)
+        prelu = None if prelu is None else np.ascontiguousarray(prelu, np.float32)
+        rows, K = X.shape
+        N = W.shape[1]
+        out = np.zeros((rows, N), np.float32)
+        self.lib.orc_nin_forward(_p(X), rows, K, _p(W), _p(B), _p(prelu), N, p, act, int(accum64), _p(out))
+        return out
+
+    def maxpool(self, feat, rules, sd):
+        feat = np.ascontiguousarray(feat, np.float32)
+        rules = np.ascontiguousarray(rules, np.int32).reshape(-1, sd)
+        C = feat.shape[1]
+        out = np.zeros((rules.shape[0], C), np.float32)
+        ch = np.zeros((rules.shape[0], C), np.int32)
+        self.lib.orc_maxpool(_p(feat), _p(rules), rules.shape[0], sd, C, _p(out), _p(ch))
+        return out, ch
+
+    def terminal_pool(self, feat, rules, S):
+        feat = np.ascontiguousarray(feat, np.float32)
+        rules = np.ascontiguousarray(rules, np.int32).reshape(-1, S)
+        C = feat.shape[1]
+        out = np.zeros((rules.shape[0], C), np.float32)
+        self.lib.orc_terminal_pool(_p(feat), _p(rules), rules.shape[0], S, C, _p(out))
+        return out
+
+    def top_indices(self, v, k):
+        v = np.ascontiguousarray(v, np.float32)
+        out = np.zeros(k, np.int32)
+        self.lib.orc_top_indices(_p(v), len(v), k, _p(out))
+        return out
+
+
+class OracleNet:
+    """Mirror of SparseConvNetCUDA's builder calls plus a CPU forward."""
+
+    def __init__(self, oracle, dim, nInputFeatures, nClasses, nTop=1, handle=None):
+        self.o, self.L = oracle, oracle.lib
+        self.dim, self.nIn, self.nClasses, self.nTop = dim, nInputFeatures, nClasses, nTop
+        self.h = handle if handle is not None else self.L.orc_net_create(dim, nInputFeatures, nClasses, nTop)
+
+    @classmethod
+    def DeepCNet(cls, oracle, dim, l, k, fn, nInputFeatures, nClasses, p=0.0, nTop=1):
+        h = oracle.lib.orc_net_DeepCNet(dim, l, k, fn, nInputFeatures, nClasses, p, nTop)
+        return cls(oracle, dim, nInputFeatures, nClasses, nTop, handle=h)
+
+    def __del__(self):
+        try:
+            self.L.orc_net_free(self.h)
+        except Exception:
+            pass
+
+    def addLeNetLayerMP(self, nFeatures, fs, fstride, ps, pstride, act=RELU, dropout=0.0, minActive=1):
+        self.L.orc_net_addLeNetLayerMP(self.h, nFeatures, fs, fstride, ps, pstride, act, dropout, minActive)
+
+    def addTriangularLeNetLayerMP(self, nFeatures, fs, fstride, ps, pstride, act=RELU, dropout=0.0, minActive=1):
+        self.L.orc_net_addTriangularLeNetLayerMP(self.h, nFeatures, fs, fstride, ps, pstride, act, dropout, minActive)
+
+    def addTerminalPoolingLayer(self, poolSize, S):
+        self.L.orc_net_addTerminalPoolingLayer(self.h, poolSize, S)
+
+    def addSoftmaxLayer(self):
+        self.L.orc_net_addSoftmaxLayer(self.h)
+
+    @property
+    def inputSpatialSize(self):
+        return self.L.orc_net_input_spatial_size(self.h)
+
+    def layers(self):
+        out = []
+        for i in range(self.L.orc_net_n_layers(self.h)):
+            info = np.zeros(10, np.int32)
+            d = c_f()
+            self.L.orc_net_layer_info(self.h, i, _p(info), ctypes.byref(d))
+            keys = ("type", "size", "stride", "minActive", "nIn", "nOut", "fs", "act", "inSpatial", "outSpatial")
+            rec = dict(zip(keys, (int(v) for v in info)))
+            rec["dropout"] = float(d.value)
+            out.append(rec)
+        return out
+
+    def set_weights(self, i, W, B, prelu=None):
+        W = np.ascontiguousarray(W, np.float32)
+        B = np.ascontiguousarray(B, np.float32)
+        prelu = None if prelu is None else np.ascontiguousarray(prelu, np.float32)
+        self.L.orc_net_set_weights(self.h, i, _p(W), _p(B), _p(prelu))
+
+    def load_weights(self, path):
+        rc = self.L.orc_net_load_weights(self.h, path.encode())
+        if rc != 0:
+            raise IOError("cannot read %s (%d)" % (path, rc))
+
+    def forward(self, keys, off, features, threads=1, accum64=False, keep=False):
+        """keys[row] (int64, -1 = background row), off[batch+1], features [rows x nIn]."""
+        keys = np.ascontiguousarray(keys, np.int64)
+        off = np.ascontiguousarray(off, np.int32)
+        features = np.ascontiguousarray(features, np.float32)
+        B = len(off) - 1
+        probs = np.zeros((B, self.nClasses), np.float32)
+        pred = np.zeros((B, self.nTop), np.int32)
+        times = np.zeros(2, np.float64)
+        self.L.orc_net_forward(self.h, B, _p(keys), _p(off), _p(features), threads, int(accum64), int(keep),
+                               _p(probs), _p(pred), _p(times))
+        self.times = times
+        return probs, pred
+
+    def iface(self, i):
+        """Interface i of the last forward(keep=True): 0 is the input, i+1 layer i's output."""
+        s = np.zeros(5, np.int64)
+        self.L.orc_net_iface_sizes(self.h, i, _p(s))
+        rows, nF, sp, nr, nc = (int(v) for v in s)
+        feat = np.zeros((rows, nF), np.float32)
+        rules = np.zeros(nr, np.int32)
+        ch = np.zeros(nc, np.int32)
+        rk = np.zeros(rows, np.int64)
+        self.L.orc_net_iface_fetch(self.h, i, _p(feat), _p(rules), _p(ch), _p(rk))
+        return dict(nSpatialSites=rows, nFeatures=nF, spatialSize=sp, features=feat, rules=rules,
+                    choices=ch, row_keys=rk)
