@@ -1,0 +1,165 @@
+/* scn_b200 -- C ABI of the B200 (sm_100a) forward path for spatially-sparse CNNs.
+ *
+ * Every entry point is the device-side replacement of one piece of the forward
+ * (inference) path of btgraham/SparseConvNet-archived; the comment above each declaration
+ * names the reference interface it replaces (paths inside the reference project,
+ * SparseConvNet/...).  The C++ classes that keep the reference's names
+ * (sparseconvnet-archived_b200/csrc/host/) call nothing but these functions.
+ *
+ * Conventions
+ *   - all pointers named d_* are DEVICE pointers owned by the caller; nothing here
+ *     allocates or frees device memory unless its comment says so;
+ *   - `stream` is a cudaStream_t passed as an opaque pointer; calls enqueue work and
+ *     return without synchronising unless stated;
+ *   - every function returns an scn_status; nothing prints or exits (the reference
+ *     prints and calls exit(), utilities.h:32-67);
+ *   - rows ("spatial sites") are numbered across the whole batch; sample b owns the
+ *     contiguous rows [off[b], off[b+1]) (BatchProducer.cu:54-58);
+ *   - a grid is carried as `keys[row]`: the row-major site index inside the sample's
+ *     S^dim cube (Regions.cu:195-200), or -1 for the sample's background ("null vector")
+ *     row; `bg[b]` is that row's id (SparseGrid::backgroundCol, SparseGrid.h:68-77) or -1.
+ */
+#ifndef SCN_B200_H
+#define SCN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *scn_stream_t; /* cudaStream_t */
+
+enum scn_status {
+  SCN_OK = 0,
+  SCN_ERR_INVALID = 1,     /* bad argument (sizes, null pointers, unsupported geometry)   */
+  SCN_ERR_CUDA = 2,        /* a CUDA runtime call or launch failed; see scn_last_error()   */
+  SCN_ERR_WORKSPACE = 3,   /* workspace too small                                          */
+  SCN_ERR_UNSUPPORTED = 4  /* valid in the reference, not built here                       */
+};
+
+/* Bits a rule-build kernel may set in d_result[2] (read them after the stream has run). */
+#define SCN_DEV_ERR_CAPACITY 1  /* more output rows than rows_out_capacity: outputs truncated */
+#define SCN_DEV_ERR_KEY 2       /* a key outside [0, nIn^dim) was skipped                      */
+#define SCN_DEV_ERR_DUPLICATE 4 /* the same key twice in one sample                            */
+
+/* ActivationFunction, types.h:20-29 (same numeric values). */
+enum scn_activation {
+  SCN_NOSIGMOID = 0, SCN_RELU = 1, SCN_VLEAKYRELU = 2, SCN_LEAKYRELU = 3,
+  SCN_TANH = 4, SCN_SOFTMAX = 5, SCN_PRELU = 6, SCN_SIGMOID = 7
+};
+
+/* Arithmetic of the fused conv/NiN kernel. */
+enum scn_precision {
+  SCN_PREC_AUTO = -1,  /* tensor cores when the shape allows, else SIMT                    */
+  SCN_PREC_FP32 = 0,   /* fp32 FMA on CUDA cores                                           */
+  SCN_PREC_3XTF32 = 1, /* tcgen05 kind::tf32, hi/lo split of both operands (fp32-grade)    */
+  SCN_PREC_BF16 = 2    /* tcgen05 kind::f16 with bf16 operands, fp32 accumulation          */
+};
+
+#define SCN_LATTICE_SQUARE 0     /* RegularSquareRegions, Regions.cu:13-29      */
+#define SCN_LATTICE_TRIANGULAR 1 /* RegularTriangularRegions, Regions.cu:804-832 */
+
+/* The arguments of the reference's region constructors plus gridRules' minActiveInputs:
+ * 1 = every touched output site, >1 = keep sites with at least that many active inputs,
+ * -1 = 'valid' 3^dim convolution (square lattice). */
+typedef struct {
+  int lattice, dim, nIn, nOut, size, stride, minActive;
+} scn_regions_t;
+
+const char *scn_status_string(int status);
+/* Message of the last failing call on this thread ("" if none). */
+const char *scn_last_error(void);
+/* 1 when the library was built for, and the current device is, compute capability 10.x. */
+int scn_device_supported(void);
+
+/* Cells per rule row: size^dim, or triangleSize(size, dim) (utilities.cu:14-32). */
+int scn_regions_cells(const scn_regions_t *r);
+
+/* Replaces gridRules() looped over a batch, i.e. the body of
+ * ConvolutionalLayer::preprocess (ConvolutionalLayer.cu:101-123),
+ * MaxPoolingLayer::preprocess (MaxPoolingLayer.cu:104-119),
+ * ConvolutionalTriangularLayer::preprocess (ConvolutionalTriangularLayer.cu:23-45) and
+ * MaxPoolingTriangularLayer::preprocess, with the builders of Regions.cu:338-526
+ * (square Min), 528-653 (square NoMin), 658-780 (Valid), 834-970 and 972-1164
+ * (triangular), and the SparseGrid/vectorHash maps they use (SparseGrid.h, vectorHash.cpp).
+ * Output rows are numbered exactly as the reference's ascending-key (vectorHash) backend
+ * numbers them; rule cells without an active input hold d_in_bg[b].
+ *
+ *   d_in_keys[rows_in], d_in_off[batch+1], d_in_bg[batch]   the input grids
+ *   rows_in_bound   >= d_in_off[batch]; sizes the launches and the workspace
+ *   d_out_keys[rows_out_capacity], d_out_off[batch+1], d_out_bg[batch]  the output grids
+ *   d_rules[rows_out_capacity * scn_regions_cells(r)]
+ *   d_result[4]     {output rows incl. background rows, output sites, SCN_DEV_ERR_* bits,
+ *                    largest number of sites in one output sample}
+ * No host synchronisation: the caller reads d_result when it needs the counts. */
+size_t scn_rules_workspace_bytes(const scn_regions_t *r, int batch, int rows_in_bound);
+int scn_rules_build(const scn_regions_t *r, int batch, const int *d_in_keys, const int *d_in_off,
+                    const int *d_in_bg, int rows_in_bound, int *d_out_keys, int *d_out_off,
+                    int *d_out_bg, int *d_rules, int rows_out_capacity, int *d_result,
+                    void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
+
+/* Replaces terminalGridPoolingRules() looped over a batch (TerminalPoolingLayer.cu:8-20,
+ * 81-99): row b lists sample b's rows in ascending key order (its background row if it has
+ * no site), padded with -1 to S columns; the output grid is one site (key 0) per sample.
+ * S must be >= the largest site count of a sample (the reference uses max(1, that)).
+ * `spatial_size`^dim bounds the keys.  d_result as above. */
+size_t scn_terminal_rules_workspace_bytes(int dim, int spatial_size, int batch, int rows_in_bound);
+int scn_terminal_rules_build(int dim, int spatial_size, int batch, const int *d_in_keys,
+                             const int *d_in_off, const int *d_in_bg, int rows_in_bound, int S,
+                             int *d_out_keys, int *d_out_off, int *d_out_bg, int *d_rules,
+                             int *d_result, void *d_workspace, size_t workspace_bytes,
+                             scn_stream_t stream);
+
+/* Replaces ConvolutionalLayer::forwards + NetworkInNetworkLayer::forwards (test branch) as
+ * ONE kernel: propForwardToMatrixMultiply (ConvolutionalLayer.cu:12-41, 124-133), then
+ * replicateArray + cublasSgemm(alpha=p, beta=p) + applySigmoid
+ * (NetworkInNetworkLayer.cu:187-201; SigmoidLayer.cu:187-222), or dPReLU
+ * (NetworkInNetworkPReLULayer.cu:8-23, 159-170):
+ *     out[r][n] = act( p * sum_{f,c} in[rules[r*fs+f]][c] * W[(f*nIn+c)*N + n] + p * B[n] )
+ * d_rules == NULL (then fs must be 1) is a plain NetworkInNetworkLayer.  A negative rule
+ * contributes a zero row.  d_prelu (per-channel slopes) is required iff act == SCN_PRELU.
+ * act == SCN_SOFTMAX applies the row softmax of SigmoidLayer.cu:160-177 (N <= 1024).
+ * `precision` is an scn_precision; shapes a tensor-core path cannot take return
+ * SCN_ERR_UNSUPPORTED unless SCN_PREC_AUTO.  d_W_packed is the result of
+ * scn_conv_pack_weights for that precision, or NULL for SCN_PREC_FP32. */
+int scn_conv_nin_forward(const float *d_in, const int *d_rules, int rows_out, int fs, int nIn,
+                         const float *d_W, const void *d_W_packed, const float *d_B,
+                         const float *d_prelu, int N, float p, int act, int precision,
+                         float *d_out, scn_stream_t stream);
+/* One-time repack of W[K x N] (K = fs*nIn) for a tensor-core precision: bytes needed, then
+ * the packing kernel.  No reference counterpart (the reference hands W to cuBLAS as is). */
+size_t scn_conv_packed_weight_bytes(int K, int N, int precision);
+int scn_conv_pack_weights(const float *d_W, int K, int N, int precision, void *d_W_packed,
+                          scn_stream_t stream);
+
+/* Replaces propForwardToMatrixMultiply alone (ConvolutionalLayer.cu:12-41): the
+ * materialised gather, for callers that read ConvolutionalLayer's output themselves.
+ * out[c*nIn + j] = in[rules[c]*nIn + j], zero where rules[c] < 0; count = rows_out*fs. */
+int scn_gather_forward(const float *d_in, const int *d_rules, long long count, int nIn,
+                       float *d_out, scn_stream_t stream);
+
+/* Replaces maxPool / dMaxPool (MaxPoolingLayer.cu:9-72): per output row and channel the
+ * maximum over the row's non-negative rules, first maximum wins, and the flat input index
+ * rule*C + channel of the winner in d_choices (SpatiallySparseBatchSubInterface::
+ * poolingChoices).  Rows without a usable rule give 0 and -1. */
+int scn_maxpool_forward(const float *d_in, const int *d_rules, int rows_out, int sd, int C,
+                        float *d_out, int *d_choices, scn_stream_t stream);
+
+/* Replaces terminalPool / dTerminalPool (TerminalPoolingLayer.cu:22-46): mean over each
+ * row's rules up to the first negative one. */
+int scn_terminal_pool_forward(const float *d_in, const int *d_rules, int batch, int S, int C,
+                              float *d_out, scn_stream_t stream);
+
+/* Replaces the device half of SoftmaxClassifier plus vectorTopIndices
+ * (SoftmaxClassifier.cu:16-41; utilities.cu:35-56): per row of d_probs[rows x nClasses]
+ * the nTop largest classes in descending order (ties: lowest index first) into
+ * d_top[rows x nTop]. */
+int scn_top_indices(const float *d_probs, int rows, int nClasses, int nTop, int *d_top,
+                    scn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SCN_B200_H */

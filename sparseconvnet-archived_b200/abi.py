@@ -1,0 +1,193 @@
+"""ctypes bindings of the C ABI in include/scn_b200.h, taking torch CUDA tensors.
+
+torch is used only for device memory and streams: every function passes raw device pointers
+and torch's current stream to libscn_b200.so.
+"""
+import ctypes
+
+import torch
+
+from . import KERNEL_LIB
+
+c_int, c_ll, c_f, c_p, c_sz = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
+
+SCN_OK = 0
+LATTICE_SQUARE, LATTICE_TRIANGULAR = 0, 1
+NOSIGMOID, RELU, VLEAKYRELU, LEAKYRELU, TANH, SOFTMAX, PRELU, SIGMOID = range(8)
+PREC_AUTO, PREC_FP32, PREC_3XTF32, PREC_BF16 = -1, 0, 1, 2
+DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
+
+EXPORTS = [
+    "scn_status_string", "scn_last_error", "scn_device_supported", "scn_regions_cells",
+    "scn_rules_workspace_bytes", "scn_rules_build", "scn_terminal_rules_workspace_bytes",
+    "scn_terminal_rules_build", "scn_conv_nin_forward", "scn_conv_packed_weight_bytes",
+    "scn_conv_pack_weights", "scn_gather_forward", "scn_maxpool_forward",
+    "scn_terminal_pool_forward", "scn_top_indices",
+]
+
+
+class Regions(ctypes.Structure):
+    _fields_ = [(n, c_int) for n in ("lattice", "dim", "nIn", "nOut", "size", "stride", "minActive")]
+
+
+class ScnError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    """The kernel library; raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        try:
+            L = ctypes.CDLL(KERNEL_LIB)
+        except OSError as e:
+            raise ScnError("libscn_b200.so is missing or unloadable (%s): run __graft_entry__.build()" % e)
+        L.scn_status_string.restype = ctypes.c_char_p
+        L.scn_status_string.argtypes = [c_int]
+        L.scn_last_error.restype = ctypes.c_char_p
+        L.scn_device_supported.restype = c_int
+        L.scn_regions_cells.restype, L.scn_regions_cells.argtypes = c_int, [c_p]
+        L.scn_rules_workspace_bytes.restype = c_sz
+        L.scn_rules_workspace_bytes.argtypes = [c_p, c_int, c_int]
+        L.scn_rules_build.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_p, c_p, c_sz, c_p]
+        L.scn_terminal_rules_workspace_bytes.restype = c_sz
+        L.scn_terminal_rules_workspace_bytes.argtypes = [c_int] * 4
+        L.scn_terminal_rules_build.argtypes = [c_int, c_int, c_int, c_p, c_p, c_p, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]
+        L.scn_conv_nin_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_int, c_f, c_int, c_int, c_p, c_p]
+        L.scn_conv_packed_weight_bytes.restype = c_sz
+        L.scn_conv_packed_weight_bytes.argtypes = [c_int, c_int, c_int]
+        L.scn_conv_pack_weights.argtypes = [c_p, c_int, c_int, c_int, c_p, c_p]
+        L.scn_gather_forward.argtypes = [c_p, c_p, c_ll, c_int, c_p, c_p]
+        L.scn_maxpool_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p]
+        L.scn_terminal_pool_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p]
+        L.scn_top_indices.argtypes = [c_p, c_int, c_int, c_int, c_p, c_p]
+        _lib = L
+    return _lib
+
+
+def check(status):
+    if status != SCN_OK:
+        L = lib()
+        raise ScnError("%s: %s" % (L.scn_status_string(status).decode(), L.scn_last_error().decode()))
+
+
+def _ptr(t):
+    return None if t is None else c_p(t.data_ptr())
+
+
+def _stream():
+    return c_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _i32(t):
+    assert t.is_cuda and t.dtype == torch.int32 and t.is_contiguous()
+    return t
+
+
+def _f32(t):
+    assert t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()
+    return t
+
+
+def regions(lattice, dim, nIn, nOut, size, stride, minActive=1):
+    return Regions(lattice, dim, nIn, nOut, size, stride, minActive)
+
+
+def rules_build(R, keys, off, bg, rows_out_capacity, rows_in_bound=None):
+    """scn_rules_build over torch int32 CUDA tensors.  Returns the raw outputs at capacity
+    size plus d_result; nothing is synchronised."""
+    L = lib()
+    batch = bg.numel()
+    rows_in_bound = keys.numel() if rows_in_bound is None else rows_in_bound
+    sd = L.scn_regions_cells(ctypes.byref(R))
+    if sd < 0:
+        raise ScnError("invalid argument: %s" % L.scn_last_error().decode())
+    dev = keys.device
+    ws_bytes = L.scn_rules_workspace_bytes(ctypes.byref(R), batch, rows_in_bound)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    out_keys = torch.empty(max(rows_out_capacity, 1), dtype=torch.int32, device=dev)
+    out_off = torch.empty(batch + 1, dtype=torch.int32, device=dev)
+    out_bg = torch.empty(batch, dtype=torch.int32, device=dev)
+    rules = torch.empty(max(rows_out_capacity, 1) * sd, dtype=torch.int32, device=dev)
+    result = torch.empty(4, dtype=torch.int32, device=dev)
+    check(L.scn_rules_build(ctypes.byref(R), batch, _ptr(_i32(keys)), _ptr(_i32(off)), _ptr(_i32(bg)), rows_in_bound,
+                            _ptr(out_keys), _ptr(out_off), _ptr(out_bg), _ptr(rules), rows_out_capacity, _ptr(result),
+                            _ptr(ws), ws_bytes, _stream()))
+    return dict(out_keys=out_keys, out_off=out_off, out_bg=out_bg, rules=rules, result=result, sd=sd, workspace=ws)
+
+
+def terminal_rules_build(dim, spatial_size, keys, off, bg, S):
+    L = lib()
+    batch = bg.numel()
+    dev = keys.device
+    ws_bytes = L.scn_terminal_rules_workspace_bytes(dim, spatial_size, batch, keys.numel())
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    out_keys = torch.empty(batch, dtype=torch.int32, device=dev)
+    out_off = torch.empty(batch + 1, dtype=torch.int32, device=dev)
+    out_bg = torch.empty(batch, dtype=torch.int32, device=dev)
+    rules = torch.empty(batch * S, dtype=torch.int32, device=dev)
+    result = torch.empty(4, dtype=torch.int32, device=dev)
+    check(L.scn_terminal_rules_build(dim, spatial_size, batch, _ptr(_i32(keys)), _ptr(_i32(off)), _ptr(_i32(bg)),
+                                     keys.numel(), S, _ptr(out_keys), _ptr(out_off), _ptr(out_bg), _ptr(rules),
+                                     _ptr(result), _ptr(ws), ws_bytes, _stream()))
+    return dict(out_keys=out_keys, out_off=out_off, out_bg=out_bg, rules=rules, result=result, workspace=ws)
+
+
+def pack_weights(W, precision):
+    L = lib()
+    K, N = W.shape
+    nbytes = L.scn_conv_packed_weight_bytes(K, N, precision)
+    if nbytes == 0:
+        raise ScnError("unsupported configuration: no packed layout for K=%d N=%d precision=%d" % (K, N, precision))
+    packed = torch.empty(nbytes, dtype=torch.uint8, device=W.device)
+    check(L.scn_conv_pack_weights(_ptr(_f32(W)), K, N, precision, _ptr(packed), _stream()))
+    return packed
+
+
+def conv_nin_forward(feat, rules, fs, W, B, prelu=None, p=1.0, act=NOSIGMOID, precision=PREC_FP32, packed=None,
+                     rows_out=None):
+    """rules: int32 [rows_out*fs] or None (plain NiN, fs == 1)."""
+    L = lib()
+    nIn = feat.shape[1]
+    K, N = W.shape
+    assert K == fs * nIn
+    if rows_out is None:
+        rows_out = feat.shape[0] if rules is None else rules.numel() // fs
+    out = torch.empty((rows_out, N), dtype=torch.float32, device=feat.device)
+    check(L.scn_conv_nin_forward(_ptr(_f32(feat)), _ptr(rules), rows_out, fs, nIn, _ptr(_f32(W)), _ptr(packed),
+                                 _ptr(_f32(B)), _ptr(prelu), N, p, act, precision, _ptr(out), _stream()))
+    return out
+
+
+def gather_forward(feat, rules):
+    nIn = feat.shape[1]
+    out = torch.empty((rules.numel(), nIn), dtype=torch.float32, device=feat.device)
+    check(lib().scn_gather_forward(_ptr(_f32(feat)), _ptr(_i32(rules)), rules.numel(), nIn, _ptr(out), _stream()))
+    return out
+
+
+def maxpool_forward(feat, rules, sd):
+    C = feat.shape[1]
+    rows_out = rules.numel() // sd
+    out = torch.empty((rows_out, C), dtype=torch.float32, device=feat.device)
+    ch = torch.empty((rows_out, C), dtype=torch.int32, device=feat.device)
+    check(lib().scn_maxpool_forward(_ptr(_f32(feat)), _ptr(_i32(rules)), rows_out, sd, C, _ptr(out), _ptr(ch), _stream()))
+    return out, ch
+
+
+def terminal_pool_forward(feat, rules, S):
+    C = feat.shape[1]
+    batch = rules.numel() // S
+    out = torch.empty((batch, C), dtype=torch.float32, device=feat.device)
+    check(lib().scn_terminal_pool_forward(_ptr(_f32(feat)), _ptr(_i32(rules)), batch, S, C, _ptr(out), _stream()))
+    return out
+
+
+def top_indices(probs, nTop):
+    rows, nClasses = probs.shape
+    top = torch.empty((rows, nTop), dtype=torch.int32, device=probs.device)
+    check(lib().scn_top_indices(_ptr(_f32(probs)), rows, nClasses, nTop, _ptr(top), _stream()))
+    return top

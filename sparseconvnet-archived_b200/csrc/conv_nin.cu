@@ -1,0 +1,139 @@
+// Fused rule-gather + NetworkInNetwork forward: dispatcher, the fp32 CUDA-core kernel used
+// for small contractions (K = fs*nIn of a few dozen, which are HBM-bound) and as the
+// arithmetic reference for the tensor-core kernel, and the row softmax of the classifier.
+#include "scn_common.cuh"
+#include "conv_nin_tc.cuh"
+
+namespace scn {
+namespace {
+
+// out[r][n] = act(p * sum_k A[r][k] W[k][n] + p * B[n]),  A[r][f*nIn + c] = in[rules[r*fs+f]][c].
+// CTA tile BM x BN, K slabs of BK, each thread a TM x TN register tile.  The gathered A tile
+// only ever lives in shared memory: the [rows x K] matrix the reference materialises
+// (ConvolutionalLayer.cu:124-133) is never written to HBM.
+template <int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+k_conv_nin_simt(const float *__restrict__ in, const int *__restrict__ rules, int rows, int fs, int nIn,
+                const float *__restrict__ W, const float *__restrict__ B, const float *__restrict__ prelu,
+                int N, float p, int act, float *__restrict__ out) {
+  constexpr int THREADS = (BM / TM) * (BN / TN);
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN];
+  const int K = fs * nIn;
+  const int row0 = blockIdx.x * BM, col0 = blockIdx.y * BN;
+  const int tx = threadIdx.x % (BN / TN), ty = threadIdx.x / (BN / TN);
+  float acc[TM][TN];
+#pragma unroll
+  for (int a = 0; a < TM; ++a)
+#pragma unroll
+    for (int b = 0; b < TN; ++b) acc[a][b] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int e = threadIdx.x; e < BM * BK; e += THREADS) {
+      const int m = e / BK, kk = e % BK;
+      const int k = k0 + kk, r = row0 + m;
+      float v = 0.f;
+      if (r < rows && k < K) {
+        const int f = k / nIn, c = k - f * nIn;
+        const int src = rules ? __ldg(rules + (long long)r * fs + f) : r;
+        if (src >= 0) v = __ldg(in + (long long)src * nIn + c);
+      }
+      As[kk][m] = v;
+    }
+    for (int e = threadIdx.x; e < BK * BN; e += THREADS) {
+      const int kk = e / BN, n = e % BN;
+      const int k = k0 + kk, col = col0 + n;
+      Bs[kk][n] = (k < K && col < N) ? __ldg(W + (long long)k * N + col) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) b[j] = Bs[kk][tx * TN + j];
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int r = row0 + ty * TM + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int col = col0 + tx * TN + j;
+      if (col >= N) continue;
+      // NetworkInNetworkLayer.cu:187-195: SGEMM with alpha = beta = p over a bias-filled C
+      float v = p * acc[i][j] + p * __ldg(B + col);
+      out[(long long)r * N + col] = activate(v, act, prelu ? __ldg(prelu + col) : 0.f);
+    }
+  }
+}
+
+// Row softmax of SigmoidLayer.cu:160-177 (running max starts at -10000), in place, one
+// thread per row (N is the class count).
+__global__ void k_softmax_rows(float *x, int rows, int N) {
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
+    float *a = x + (long long)r * N;
+    float mx = -10000.0f, acc = 0.0f;
+    for (int k = 0; k < N; ++k) if (a[k] > mx) mx = a[k];
+    for (int k = 0; k < N; ++k) { a[k] = expf(a[k] - mx); acc += a[k]; }
+    for (int k = 0; k < N; ++k) a[k] /= acc;
+  }
+}
+
+} // namespace
+} // namespace scn
+
+using namespace scn;
+
+extern "C" int scn_conv_nin_forward(const float *d_in, const int *d_rules, int rows_out, int fs, int nIn,
+                                    const float *d_W, const void *d_W_packed, const float *d_B,
+                                    const float *d_prelu, int N, float p, int act, int precision, float *d_out,
+                                    scn_stream_t stream) {
+  clear_error();
+  if (rows_out < 0 || fs < 1 || nIn < 1 || N < 1) return fail(SCN_ERR_INVALID, "bad conv/NiN sizes");
+  if (!d_rules && fs != 1) return fail(SCN_ERR_INVALID, "fs must be 1 without rules");
+  if (act < SCN_NOSIGMOID || act > SCN_SIGMOID) return fail(SCN_ERR_INVALID, "unknown activation");
+  if (act == SCN_PRELU && !d_prelu) return fail(SCN_ERR_INVALID, "PReLU slopes missing");
+  if (act == SCN_SOFTMAX && N > 1024) return fail(SCN_ERR_INVALID, "softmax over more than 1024 classes");
+  if (precision < SCN_PREC_AUTO || precision > SCN_PREC_BF16) return fail(SCN_ERR_INVALID, "unknown precision");
+  if (rows_out == 0) return SCN_OK;
+  if (!d_in || !d_W || !d_B || !d_out) return fail(SCN_ERR_INVALID, "null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int inner = (act == SCN_SOFTMAX) ? SCN_NOSIGMOID : act;
+
+  int use = precision;
+  if (precision == SCN_PREC_AUTO) use = (d_W_packed && tc_shape_ok(fs, nIn, N, SCN_PREC_3XTF32)) ? SCN_PREC_3XTF32 : SCN_PREC_FP32;
+  if (use != SCN_PREC_FP32) {
+    if (!tc_shape_ok(fs, nIn, N, use)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel (need nIn % 8 == 0, N % 16 == 0)");
+    if (!d_W_packed) return fail(SCN_ERR_INVALID, "tensor-core precision needs packed weights");
+    int st = tc_launch(d_in, d_rules, rows_out, fs, nIn, d_W_packed, d_B, d_prelu, N, p, inner, use, d_out, s);
+    if (st != SCN_OK) return st;
+  } else {
+    constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+    dim3 grid((rows_out + BM - 1) / BM, (N + BN - 1) / BN);
+    k_conv_nin_simt<BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B,
+                                                                           d_prelu, N, p, inner, d_out);
+    SCN_LAUNCH_CHECK("k_conv_nin_simt");
+  }
+  if (act == SCN_SOFTMAX) {
+    k_softmax_rows<<<grid_for(rows_out, 128), 128, 0, s>>>(d_out, rows_out, N);
+    SCN_LAUNCH_CHECK("k_softmax_rows");
+  }
+  return SCN_OK;
+}
+
+extern "C" size_t scn_conv_packed_weight_bytes(int K, int N, int precision) { return tc_packed_bytes(K, N, precision); }
+
+extern "C" int scn_conv_pack_weights(const float *d_W, int K, int N, int precision, void *d_W_packed,
+                                     scn_stream_t stream) {
+  clear_error();
+  if (K < 1 || N < 1 || !d_W || !d_W_packed) return fail(SCN_ERR_INVALID, "bad pack arguments");
+  return tc_pack(d_W, K, N, precision, d_W_packed, (cudaStream_t)stream);
+}

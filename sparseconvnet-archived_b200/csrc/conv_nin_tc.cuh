@@ -1,0 +1,14 @@
+// Interface of the tcgen05/TMEM fused conv/NiN kernel (conv_nin_tc.cu).
+#pragma once
+#include "scn_common.cuh"
+
+namespace scn {
+// Can the tensor-core kernel take this layer shape at this precision?
+bool tc_shape_ok(int fs, int nIn, int N, int precision);
+// Bytes of the packed copy of W[K x N] the kernel reads (0 if unsupported).
+size_t tc_packed_bytes(int K, int N, int precision);
+int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaStream_t s);
+int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed,
+              const float *d_B, const float *d_prelu, int N, float p, int act, int precision, float *d_out,
+              cudaStream_t s);
+} // namespace scn

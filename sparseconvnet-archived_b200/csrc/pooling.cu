@@ -1,0 +1,141 @@
+// Rule-driven pooling and the small row-wise kernels of the forward path.  All of them are
+// HBM-bound: each input element is read once per rule that names it, every output element
+// is written once, accesses are coalesced along the channel axis (float4 where C % 4 == 0).
+#include "scn_common.cuh"
+
+namespace scn {
+namespace {
+
+// Max pooling with argmax (MaxPoolingLayer.cu:9-35): negative rules are skipped, the first
+// maximum wins (strict '<'), the choice is the flat input index rule*C + channel.
+template <int VEC>
+__global__ void k_maxpool(const float *__restrict__ in, const int *__restrict__ rules, int rowsOut, int sd, int C,
+                          float *__restrict__ out, int *__restrict__ choice) {
+  const int cv = C / VEC;
+  const long long n = (long long)rowsOut * cv;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n; q += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(q / cv), j = (int)(q % cv) * VEC;
+    float best[VEC];
+    int idx[VEC];
+    bool none = true;
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) { best[v] = 0.f; idx[v] = -1; }
+    for (int p = 0; p < sd; ++p) {
+      const int rp = __ldg(rules + (long long)r * sd + p);
+      if (rp < 0) continue;
+      float s[VEC];
+      const long long base = (long long)rp * C + j;
+      if (VEC == 4) { float4 t = *reinterpret_cast<const float4 *>(in + base); s[0] = t.x; s[1 % VEC] = t.y; s[2 % VEC] = t.z; s[3 % VEC] = t.w; }
+      else { s[0] = in[base]; }
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+        if (none || best[v] < s[v]) { best[v] = s[v]; idx[v] = (int)(base + v); }
+      none = false;
+    }
+    const long long o = (long long)r * C + j;
+    if (VEC == 4) {
+      *reinterpret_cast<float4 *>(out + o) = make_float4(best[0], best[1 % VEC], best[2 % VEC], best[3 % VEC]);
+      *reinterpret_cast<int4 *>(choice + o) = make_int4(idx[0], idx[1 % VEC], idx[2 % VEC], idx[3 % VEC]);
+    } else { out[o] = best[0]; choice[o] = idx[0]; }
+  }
+}
+
+// Mean over each row's rules up to the first negative one (TerminalPoolingLayer.cu:22-34).
+__global__ void k_terminal_pool(const float *__restrict__ in, const int *__restrict__ rules, int batch, int S, int C,
+                                float *__restrict__ out) {
+  const long long n = (long long)batch * C;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n; q += (long long)gridDim.x * blockDim.x) {
+    const int b = (int)(q / C), j = (int)(q % C);
+    float t = 0.f;
+    int p = 0;
+    for (; p < S; ++p) {
+      const int rp = __ldg(rules + (long long)b * S + p);
+      if (rp < 0) break;
+      t += in[(long long)rp * C + j];
+    }
+    out[q] = t / p;
+  }
+}
+
+// propForwardToMatrixMultiply (ConvolutionalLayer.cu:12-31), a negative rule giving zeros.
+__global__ void k_gather(const float *__restrict__ in, const int *__restrict__ rules, long long count, int nIn,
+                         float *__restrict__ out) {
+  const long long n = count * nIn;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n; q += (long long)gridDim.x * blockDim.x) {
+    const long long c = q / nIn;
+    const int j = (int)(q % nIn);
+    const int r = __ldg(rules + c);
+    out[q] = r >= 0 ? in[(long long)r * nIn + j] : 0.f;
+  }
+}
+
+// vectorTopIndices (utilities.cu:35-56): descending values, equal values in index order.
+__global__ void k_top_indices(const float *__restrict__ probs, int rows, int nClasses, int nTop, int *__restrict__ top) {
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
+    const float *v = probs + (long long)r * nClasses;
+    float lastVal = 0.f;
+    int lastIdx = -1;
+    for (int t = 0; t < nTop; ++t) {
+      int best = -1;
+      float bv = 0.f;
+      for (int i = 0; i < nClasses; ++i) {
+        const float x = v[i];
+        const bool eligible = (lastIdx < 0) || x < lastVal || (x == lastVal && i > lastIdx);
+        if (eligible && (best < 0 || x > bv)) { best = i; bv = x; }
+      }
+      top[(long long)r * nTop + t] = best < 0 ? 0 : best;
+      lastVal = bv; lastIdx = best;
+    }
+  }
+}
+
+} // namespace
+} // namespace scn
+
+using namespace scn;
+
+extern "C" int scn_maxpool_forward(const float *d_in, const int *d_rules, int rows_out, int sd, int C, float *d_out,
+                                   int *d_choices, scn_stream_t stream) {
+  clear_error();
+  if (rows_out < 0 || sd < 1 || C < 1) return fail(SCN_ERR_INVALID, "bad max-pooling sizes");
+  if (rows_out == 0) return SCN_OK;
+  if (!d_in || !d_rules || !d_out || !d_choices) return fail(SCN_ERR_INVALID, "null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool vec = (C % 4 == 0) && ((uintptr_t)d_in % 16 == 0) && ((uintptr_t)d_out % 16 == 0) && ((uintptr_t)d_choices % 16 == 0);
+  if (vec) k_maxpool<4><<<grid_for((long long)rows_out * (C / 4), 256), 256, 0, s>>>(d_in, d_rules, rows_out, sd, C, d_out, d_choices);
+  else k_maxpool<1><<<grid_for((long long)rows_out * C, 256), 256, 0, s>>>(d_in, d_rules, rows_out, sd, C, d_out, d_choices);
+  SCN_LAUNCH_CHECK("k_maxpool");
+  return SCN_OK;
+}
+
+extern "C" int scn_terminal_pool_forward(const float *d_in, const int *d_rules, int batch, int S, int C, float *d_out,
+                                         scn_stream_t stream) {
+  clear_error();
+  if (batch < 0 || S < 1 || C < 1) return fail(SCN_ERR_INVALID, "bad terminal-pooling sizes");
+  if (batch == 0) return SCN_OK;
+  if (!d_in || !d_rules || !d_out) return fail(SCN_ERR_INVALID, "null pointer");
+  k_terminal_pool<<<grid_for((long long)batch * C, 128), 128, 0, (cudaStream_t)stream>>>(d_in, d_rules, batch, S, C, d_out);
+  SCN_LAUNCH_CHECK("k_terminal_pool");
+  return SCN_OK;
+}
+
+extern "C" int scn_gather_forward(const float *d_in, const int *d_rules, long long count, int nIn, float *d_out,
+                                  scn_stream_t stream) {
+  clear_error();
+  if (count < 0 || nIn < 1) return fail(SCN_ERR_INVALID, "bad gather sizes");
+  if (count == 0) return SCN_OK;
+  if (!d_in || !d_rules || !d_out) return fail(SCN_ERR_INVALID, "null pointer");
+  k_gather<<<grid_for(count * nIn, 256), 256, 0, (cudaStream_t)stream>>>(d_in, d_rules, count, nIn, d_out);
+  SCN_LAUNCH_CHECK("k_gather");
+  return SCN_OK;
+}
+
+extern "C" int scn_top_indices(const float *d_probs, int rows, int nClasses, int nTop, int *d_top, scn_stream_t stream) {
+  clear_error();
+  if (rows < 0 || nClasses < 1 || nTop < 1 || nTop > nClasses) return fail(SCN_ERR_INVALID, "need 1 <= nTop <= nClasses");
+  if (rows == 0) return SCN_OK;
+  if (!d_probs || !d_top) return fail(SCN_ERR_INVALID, "null pointer");
+  k_top_indices<<<grid_for(rows, 128), 128, 0, (cudaStream_t)stream>>>(d_probs, rows, nClasses, nTop, d_top);
+  SCN_LAUNCH_CHECK("k_top_indices");
+  return SCN_OK;
+}

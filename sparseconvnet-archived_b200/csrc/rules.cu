@@ -1,0 +1,515 @@
+// Rule construction on the GPU: the device replacement of the reference's per-sample
+// SparseGrid maps (SparseGrid.h, vectorHash.cpp) and gridRules builders (Regions.cu).
+//
+// Data structure.  A sample's grid is an occupancy bitmap over its nIn^dim cells with a rank
+// directory: word w of sample b is {bits, number of active cells in earlier words}.  This is
+// the reference's vectorHash (a dense key-indexed array, vectorHash.h:6-23) at 1/16 of its
+// size, and it answers both questions the builders ask: "is cell k active" (one bit) and
+// "which row is cell k" (rank of k among the active cells -> sortedRow[]).  The rank is also
+// the position of k in ascending-key order, which is the order the reference's vectorHash
+// backend iterates in and therefore the order that fixes output row numbers.
+//
+// Row numbering.  The reference visits input sites in ascending key and, for each, the
+// output sites it touches in ascending output key; an output site gets the next free row id
+// the first time it is touched (Regions.cu:566-573).  So an output site is "created" by the
+// smallest active key in its receptive field, and its id is
+//     (#sites created by smaller input keys) + (its rank among the sites this key creates).
+// Kernels: mark bits -> rank directory -> per input site, flag the outputs it creates ->
+// exclusive scan of the per-site counts -> per sample offsets and background rows -> assign
+// output keys -> fill rule cells.  All pure integer, HBM/L2-bound work; no host
+// synchronisation: every size the kernels need is read from device memory.
+#include "scn_common.cuh"
+
+namespace scn {
+namespace {
+
+constexpr int MAX_CUBE = 256; // size^dim cells of a receptive field
+
+struct Regions {
+  int lattice, dim, nIn, nOut, size, stride, minActive;
+  int sd, cube, Tax, T, W, cells, fullSize;
+  signed char ord[MAX_CUBE];         // cube cell -> rule column, -1 outside a triangular filter
+  unsigned char cellOfCol[MAX_CUBE]; // rule column -> cube cell
+};
+
+__host__ __device__ inline long long ipowll(long long b, int e) {
+  long long r = 1;
+  while (e-- > 0) r *= b;
+  return r;
+}
+
+// Largest b with off[b] <= row (samples own contiguous row blocks).
+__device__ __forceinline__ int find_sample(const int *__restrict__ off, int batch, int row) {
+  int lo = 0, hi = batch;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (__ldg(off + mid) <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ void decode(int key, int n, int dim, int *c) {
+  for (int a = dim - 1; a >= 0; --a) { c[a] = key % n; key /= n; }
+}
+__device__ __forceinline__ int encode(const int *c, int n, int dim) {
+  int k = 0;
+  for (int a = 0; a < dim; ++a) k = k * n + c[a];
+  return k;
+}
+
+__global__ void k_mark(Regions R, int batch, const int *__restrict__ keys, const int *__restrict__ off,
+                       uint2 *dir, int *result) {
+  const int n = off[batch];
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < n; row += gridDim.x * blockDim.x) {
+    int key = keys[row];
+    if (key < 0) continue; // background row
+    if (key >= R.cells) { atomicOr(result + 2, SCN_DEV_ERR_KEY); continue; }
+    int b = find_sample(off, batch, row);
+    unsigned bit = 1u << (key & 31);
+    unsigned old = atomicOr(&dir[(size_t)b * R.W + (key >> 5)].x, bit);
+    if (old & bit) atomicOr(result + 2, SCN_DEV_ERR_DUPLICATE);
+  }
+}
+
+// One CTA per sample: exclusive scan of the word popcounts.
+__global__ void k_rank(Regions R, int batch, uint2 *dir, int *nSites) {
+  __shared__ int warpSum[32];
+  __shared__ int carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nWarps = blockDim.x >> 5;
+  for (int b = blockIdx.x; b < batch; b += gridDim.x) {
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    uint2 *d = dir + (size_t)b * R.W;
+    for (int w0 = 0; w0 < R.W; w0 += blockDim.x) {
+      int w = w0 + threadIdx.x;
+      int c = (w < R.W) ? __popc(d[w].x) : 0;
+      int incl = c;
+      for (int o = 1; o < 32; o <<= 1) { int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+      if (lane == 31) warpSum[warp] = incl;
+      __syncthreads();
+      if (warp == 0) {
+        int v = (lane < nWarps) ? warpSum[lane] : 0;
+        for (int o = 1; o < 32; o <<= 1) { int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+        warpSum[lane] = v; // inclusive over warps
+      }
+      __syncthreads();
+      int base = carry + (warp ? warpSum[warp - 1] : 0);
+      if (w < R.W) d[w].y = base + incl - c;
+      __syncthreads();
+      if (threadIdx.x == 0) carry += warpSum[nWarps - 1];
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) nSites[b] = carry;
+    __syncthreads();
+  }
+}
+
+__device__ __forceinline__ bool cell_active(const uint2 *__restrict__ d, int key) {
+  return (d[key >> 5].x >> (key & 31)) & 1u;
+}
+__device__ __forceinline__ int cell_rank(const uint2 *__restrict__ d, int key) {
+  uint2 e = d[key >> 5];
+  return e.y + __popc(e.x & ((1u << (key & 31)) - 1u));
+}
+
+// Output coordinates of the t-th output site input site i can touch (mixed radix over the
+// axes, so ascending t = ascending output key); false if t names none.
+__device__ __forceinline__ bool touched_output(const Regions &R, const int *i, int t, int *j) {
+  if (R.minActive == -1) { // 'valid': the site centred on i (Regions.cu:691-696)
+    bool ok = true;
+    for (int a = 0; a < R.dim; ++a) { ok = ok && i[a] >= 1 && i[a] <= R.nOut; j[a] = i[a] - 1; }
+    return ok;
+  }
+  int sum = 0;
+  for (int a = R.dim - 1; a >= 0; --a) {
+    int ta = t % R.Tax; t /= R.Tax;
+    int lo = max(0, (i[a] - R.size + R.stride) / R.stride);
+    int hi = min(i[a] / R.stride + 1, R.nOut);
+    j[a] = lo + ta;
+    if (j[a] >= hi) return false;
+    sum += j[a];
+  }
+  if (R.lattice == SCN_LATTICE_TRIANGULAR && sum >= R.nOut) return false;
+  return true;
+}
+
+// Does input site i (active) create output site j: is i the first active cell of j's cube
+// field in lexicographic (= key) order, and does the field hold enough active inputs?
+__device__ bool creates(const Regions &R, const uint2 *__restrict__ d, const int *i, const int *j) {
+  if (R.minActive == -1) return true;
+  int cc[4] = {0, 0, 0, 0}, ii[4];
+  int active = 0;
+  for (int cell = 0; cell < R.cube; ++cell) {
+    bool self = true;
+    for (int a = 0; a < R.dim; ++a) { ii[a] = j[a] * R.stride + cc[a]; self = self && ii[a] == i[a]; }
+    if (self) {
+      if (R.minActive <= 1) return true;
+      active += (R.ord[cell] >= 0);
+      // keep counting the rest of the field
+      for (int c2 = cell + 1; c2 < R.cube; ++c2) {
+        int a = R.dim - 1;
+        while (a >= 0 && ++cc[a] >= R.size) { cc[a] = 0; --a; }
+        if (R.ord[c2] < 0) continue;
+        for (int q = 0; q < R.dim; ++q) ii[q] = j[q] * R.stride + cc[q];
+        active += cell_active(d, encode(ii, R.nIn, R.dim));
+      }
+      return active >= R.minActive;
+    }
+    if (cell_active(d, encode(ii, R.nIn, R.dim))) return false; // an earlier key got there first
+    int a = R.dim - 1;
+    while (a >= 0 && ++cc[a] >= R.size) { cc[a] = 0; --a; }
+  }
+  return false;
+}
+
+// Per input row: its slot in ascending-key order, the outputs it creates, and their count.
+__global__ void k_flags(Regions R, int batch, const int *__restrict__ keys, const int *__restrict__ off,
+                        const uint2 *__restrict__ dir, int *sortedRow, unsigned char *flags, int *cnt,
+                        bool withFlags) {
+  const int n = off[batch];
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < n; row += gridDim.x * blockDim.x) {
+    int key = keys[row];
+    if (key < 0 || key >= R.cells) continue;
+    int b = find_sample(off, batch, row);
+    const uint2 *d = dir + (size_t)b * R.W;
+    int slot = off[b] + cell_rank(d, key);
+    sortedRow[slot] = row;
+    if (!withFlags) continue;
+    int i[4], j[4];
+    decode(key, R.nIn, R.dim, i);
+    int c = 0;
+    for (int t = 0; t < R.T; ++t) {
+      bool f = touched_output(R, i, t, j) && creates(R, d, i, j);
+      flags[(size_t)slot * R.T + t] = f;
+      c += f;
+    }
+    cnt[slot] = c;
+  }
+}
+
+// ---- exclusive scan of cnt[0..n) in place, total at cnt[n]; n read from the device.
+constexpr int SCAN_THREADS = 256, SCAN_ITEMS = 8, SCAN_CHUNK = SCAN_THREADS * SCAN_ITEMS;
+
+__device__ __forceinline__ int block_exclusive_scan(int v, int *total) {
+  __shared__ int ws[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nWarps = blockDim.x >> 5;
+  int incl = v;
+  for (int o = 1; o < 32; o <<= 1) { int u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+  __syncthreads(); // ws may still be read by a previous call
+  if (lane == 31) ws[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int s = (lane < nWarps) ? ws[lane] : 0;
+    for (int o = 1; o < 32; o <<= 1) { int u = __shfl_up_sync(0xffffffffu, s, o); if (lane >= o) s += u; }
+    ws[lane] = s;
+  }
+  __syncthreads();
+  *total = ws[nWarps - 1];
+  return (warp ? ws[warp - 1] : 0) + incl - v;
+}
+
+__global__ void k_scan_reduce(const int *__restrict__ cnt, const int *__restrict__ off, int batch, int *partial) {
+  const int n = off[batch];
+  const int nChunks = (n + SCAN_CHUNK - 1) / SCAN_CHUNK;
+  for (int c = blockIdx.x; c < nChunks; c += gridDim.x) {
+    int s = 0;
+    for (int k = 0; k < SCAN_ITEMS; ++k) {
+      int idx = c * SCAN_CHUNK + k * SCAN_THREADS + threadIdx.x;
+      if (idx < n) s += cnt[idx];
+    }
+    int total;
+    block_exclusive_scan(s, &total);
+    if (threadIdx.x == 0) partial[c] = total;
+  }
+}
+__global__ void k_scan_partials(const int *__restrict__ off, int batch, int *partial) {
+  const int n = off[batch];
+  const int nChunks = (n + SCAN_CHUNK - 1) / SCAN_CHUNK;
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int c0 = 0; c0 < nChunks; c0 += blockDim.x) {
+    int c = c0 + threadIdx.x;
+    int v = (c < nChunks) ? partial[c] : 0;
+    int total;
+    int ex = block_exclusive_scan(v, &total);
+    if (c < nChunks) partial[c] = carry + ex;
+    __syncthreads();
+    if (threadIdx.x == 0) carry += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) partial[nChunks] = carry;
+}
+__global__ void k_scan_apply(int *cnt, const int *__restrict__ off, int batch, const int *__restrict__ partial) {
+  const int n = off[batch];
+  const int nChunks = (n + SCAN_CHUNK - 1) / SCAN_CHUNK;
+  for (int c = blockIdx.x; c < nChunks; c += gridDim.x) {
+    int v[SCAN_ITEMS], s = 0;
+    const int base = c * SCAN_CHUNK + threadIdx.x * SCAN_ITEMS;
+    for (int k = 0; k < SCAN_ITEMS; ++k) { v[k] = (base + k < n) ? cnt[base + k] : 0; s += v[k]; }
+    int total;
+    int ex = block_exclusive_scan(s, &total) + partial[c];
+    for (int k = 0; k < SCAN_ITEMS; ++k) { if (base + k < n) cnt[base + k] = ex; ex += v[k]; }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) cnt[n] = partial[nChunks];
+}
+
+// Per sample: output row offsets, background rows, totals.  One CTA.
+__global__ void k_samples(Regions R, int batch, const int *__restrict__ inOff, const int *__restrict__ P,
+                          int *outOff, int *outBg, int *outKeys, int capacity, int *result) {
+  __shared__ int carry, maxSites;
+  if (threadIdx.x == 0) { carry = 0; maxSites = 0; }
+  __syncthreads();
+  for (int b0 = 0; b0 < batch; b0 += blockDim.x) {
+    int b = b0 + threadIdx.x;
+    int sites = 0, need = 0, before = 0;
+    if (b < batch) {
+      before = P[inOff[b]];
+      sites = P[inOff[b + 1]] - before;
+      need = sites < R.fullSize; // e.g. Regions.cu:647-652
+    }
+    int total;
+    int ex = block_exclusive_scan(need, &total);
+    if (b < batch) {
+      int first = before + carry + ex;
+      outOff[b] = first;
+      int bgRow = need ? first + sites : -1;
+      outBg[b] = bgRow;
+      if (need && bgRow < capacity) outKeys[bgRow] = -1;
+      atomicMax(&maxSites, sites);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) carry += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    int sitesTotal = P[inOff[batch]];
+    int rows = sitesTotal + carry;
+    outOff[batch] = rows;
+    result[0] = rows;
+    result[1] = sitesTotal;
+    result[3] = maxSites;
+    if (rows > capacity) atomicOr(result + 2, SCN_DEV_ERR_CAPACITY);
+  }
+}
+
+// Per (input slot, touched output) pair that creates a site: the site's row id and key.
+__global__ void k_assign(Regions R, int batch, const int *__restrict__ keys, const int *__restrict__ inOff,
+                         const int *__restrict__ sortedRow, const unsigned char *__restrict__ flags,
+                         const int *__restrict__ P, const int *__restrict__ outOff, int *outKeys, int capacity) {
+  const long long n = (long long)inOff[batch] * R.T;
+  for (long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x; p < n; p += (long long)gridDim.x * blockDim.x) {
+    if (!flags[p]) continue;
+    int slot = (int)(p / R.T), t = (int)(p % R.T);
+    int rank = 0;
+    for (int q = 0; q < t; ++q) rank += flags[(size_t)slot * R.T + q];
+    int b = find_sample(inOff, batch, slot);
+    int outRow = outOff[b] + (P[slot] - P[inOff[b]]) + rank;
+    if (outRow >= capacity) continue;
+    int i[4], j[4];
+    decode(keys[sortedRow[slot]], R.nIn, R.dim, i);
+    touched_output(R, i, t, j);
+    outKeys[outRow] = encode(j, R.nOut, R.dim);
+  }
+}
+
+// One thread per rule cell: rules[row*sd + col], coalesced.
+__global__ void k_fill(Regions R, int batch, const int *__restrict__ inOff, const int *__restrict__ inBg,
+                       const uint2 *__restrict__ dir, const int *__restrict__ sortedRow,
+                       const int *__restrict__ outOff, const int *__restrict__ outKeys, int *rules,
+                       int capacity, const int *__restrict__ result) {
+  const long long n = (long long)min(result[0], capacity) * R.sd;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n; q += (long long)gridDim.x * blockDim.x) {
+    int r = (int)(q / R.sd), col = (int)(q % R.sd);
+    int b = find_sample(outOff, batch, r);
+    int key = outKeys[r];
+    int v = inBg[b];
+    if (key >= 0) {
+      int j[4], cc[4], ii[4];
+      decode(key, R.nOut, R.dim, j);
+      decode(R.cellOfCol[col], R.size, R.dim, cc);
+      for (int a = 0; a < R.dim; ++a) ii[a] = j[a] * R.stride + cc[a];
+      int ck = encode(ii, R.nIn, R.dim);
+      const uint2 *d = dir + (size_t)b * R.W;
+      uint2 e = d[ck >> 5];
+      if ((e.x >> (ck & 31)) & 1u) v = sortedRow[inOff[b] + e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
+    }
+    rules[q] = v;
+  }
+}
+
+// TerminalPoolingLayer.cu:8-20: sample b's rows in ascending key order, padded with -1.
+__global__ void k_terminal(int batch, int S, const int *__restrict__ inOff, const int *__restrict__ inBg,
+                           const int *__restrict__ nSites, const int *__restrict__ sortedRow, int *rules,
+                           int *outKeys, int *outOff, int *outBg, int *result) {
+  const long long n = (long long)batch * S;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n; q += (long long)gridDim.x * blockDim.x) {
+    int b = (int)(q / S), p = (int)(q % S);
+    int ns = nSites[b];
+    int v = -1;
+    if (p < ns) v = sortedRow[inOff[b] + p];
+    else if (p == 0) v = inBg[b]; // no site at all: the background row stands in
+    rules[q] = v;
+    if (p == 0) {
+      outKeys[b] = 0; outOff[b] = b; outBg[b] = -1;
+      if (ns > S) atomicOr(result + 2, SCN_DEV_ERR_CAPACITY);
+      if (b == 0) { outOff[batch] = batch; result[0] = batch; result[1] = batch; result[3] = 1; }
+    }
+  }
+}
+
+struct Workspace {
+  uint2 *dir; int *nSites; int *sortedRow; int *cnt; int *partial; unsigned char *flags;
+  size_t bytes;
+};
+
+Workspace carve(void *base, int batch, int W, int rows, int T) {
+  Workspace w;
+  size_t o = 0;
+  auto take = [&](size_t n) { size_t at = o; o = align_up(o + n, 256); return (char *)base + at; };
+  w.dir = (uint2 *)take((size_t)batch * W * sizeof(uint2));
+  w.nSites = (int *)take((size_t)batch * sizeof(int));
+  w.sortedRow = (int *)take((size_t)rows * sizeof(int));
+  w.cnt = (int *)take(((size_t)rows + 1) * sizeof(int));
+  w.partial = (int *)take(((size_t)rows / SCAN_CHUNK + 2) * sizeof(int));
+  w.flags = (unsigned char *)take((size_t)rows * (T > 0 ? T : 0));
+  w.bytes = o;
+  return w;
+}
+
+int make_regions(const scn_regions_t *r, Regions *out) {
+  if (!r) return fail(SCN_ERR_INVALID, "regions is NULL");
+  Regions R;
+  R.lattice = r->lattice; R.dim = r->dim; R.nIn = r->nIn; R.nOut = r->nOut;
+  R.size = r->size; R.stride = r->stride; R.minActive = r->minActive;
+  if (R.lattice != SCN_LATTICE_SQUARE && R.lattice != SCN_LATTICE_TRIANGULAR) return fail(SCN_ERR_INVALID, "unknown lattice");
+  if (R.dim < 1 || R.dim > 4) return fail(SCN_ERR_INVALID, "dimension must be 1..4");
+  if (R.size < 1 || R.stride < 1 || R.nOut < 1) return fail(SCN_ERR_INVALID, "size, stride and nOut must be positive");
+  // the assert of both region constructors (Regions.cu:17, 823)
+  if (R.nIn != R.size + (R.nOut - 1) * R.stride) return fail(SCN_ERR_INVALID, "nIn != size + (nOut-1)*stride");
+  if (R.minActive == 0 || R.minActive < -1) return fail(SCN_ERR_INVALID, "minActive must be -1 or >= 1");
+  if (R.minActive == -1 && (R.size != 3 || R.stride != 1 || R.lattice != SCN_LATTICE_SQUARE))
+    return fail(SCN_ERR_INVALID, "valid mode needs a 3^dim stride-1 square filter (Regions.cu:665)");
+  long long cube = ipowll(R.size, R.dim), cells = ipowll(R.nIn, R.dim);
+  if (cube > MAX_CUBE) return fail(SCN_ERR_UNSUPPORTED, "receptive field larger than 256 cells");
+  if (cells >= (1ll << 31)) return fail(SCN_ERR_UNSUPPORTED, "nIn^dim must be below 2^31");
+  R.cube = (int)cube; R.cells = (int)cells;
+  int S = 0;
+  for (int c = 0; c < R.cube; ++c) {
+    int j = c, J = 0;
+    while (j > 0) { J += j % R.size; j /= R.size; }
+    if (R.lattice == SCN_LATTICE_SQUARE || J < R.size) { R.ord[c] = (signed char)S; R.cellOfCol[S] = (unsigned char)c; ++S; }
+    else R.ord[c] = -1;
+  }
+  R.sd = S;
+  R.Tax = (R.minActive == -1) ? 1 : (R.size + R.stride - 1) / R.stride;
+  long long T = (R.minActive == -1) ? 1 : ipowll(R.Tax, R.dim);
+  if (T > 4096) return fail(SCN_ERR_UNSUPPORTED, "too many touched outputs per input");
+  R.T = (int)T;
+  R.W = (int)((cells + 31) / 32);
+  if (R.lattice == SCN_LATTICE_SQUARE) R.fullSize = (int)ipowll(R.nOut, R.dim);
+  else { long long fs = 1; for (int i = 1; i <= R.dim; ++i) fs = fs * (R.nOut + R.dim - i) / i; R.fullSize = (int)fs; }
+  *out = R;
+  return SCN_OK;
+}
+
+} // namespace
+} // namespace scn
+
+using namespace scn;
+
+extern "C" int scn_regions_cells(const scn_regions_t *r) {
+  Regions R;
+  if (make_regions(r, &R) != SCN_OK) return -1;
+  return R.sd;
+}
+
+extern "C" size_t scn_rules_workspace_bytes(const scn_regions_t *r, int batch, int rows_in_bound) {
+  Regions R;
+  if (make_regions(r, &R) != SCN_OK || batch < 0 || rows_in_bound < 0) return 0;
+  return carve(nullptr, batch, R.W, rows_in_bound, R.T).bytes;
+}
+
+extern "C" int scn_rules_build(const scn_regions_t *r, int batch, const int *d_in_keys, const int *d_in_off,
+                               const int *d_in_bg, int rows_in_bound, int *d_out_keys, int *d_out_off,
+                               int *d_out_bg, int *d_rules, int rows_out_capacity, int *d_result,
+                               void *d_workspace, size_t workspace_bytes, scn_stream_t stream_) {
+  clear_error();
+  Regions R;
+  int st = make_regions(r, &R);
+  if (st != SCN_OK) return st;
+  if (batch < 1 || rows_in_bound < 0 || rows_out_capacity < 0) return fail(SCN_ERR_INVALID, "bad batch/row counts");
+  if ((!d_in_keys && rows_in_bound > 0) || !d_in_off || !d_in_bg || !d_out_keys || !d_out_off || !d_out_bg || !d_rules || !d_result || !d_workspace)
+    return fail(SCN_ERR_INVALID, "null pointer");
+  Workspace w = carve(d_workspace, batch, R.W, rows_in_bound, R.T);
+  if (w.bytes > workspace_bytes) return fail(SCN_ERR_WORKSPACE, "workspace smaller than scn_rules_workspace_bytes()");
+  cudaStream_t s = (cudaStream_t)stream_;
+  const int rows = rows_in_bound > 0 ? rows_in_bound : 1;
+
+  SCN_CUDA_TRY(cudaMemsetAsync(w.dir, 0, (size_t)batch * R.W * sizeof(uint2), s));
+  SCN_CUDA_TRY(cudaMemsetAsync(w.cnt, 0, ((size_t)rows_in_bound + 1) * sizeof(int), s));
+  SCN_CUDA_TRY(cudaMemsetAsync(d_result, 0, 4 * sizeof(int), s));
+  // slots no site maps to (a sample's background row, skipped keys) must read as "creates nothing"
+  if (rows_in_bound > 0) SCN_CUDA_TRY(cudaMemsetAsync(w.flags, 0, (size_t)rows_in_bound * R.T, s));
+  k_mark<<<grid_for(rows, 256), 256, 0, s>>>(R, batch, d_in_keys, d_in_off, w.dir, d_result);
+  SCN_LAUNCH_CHECK("k_mark");
+  k_rank<<<batch < sm_count() * 4 ? batch : sm_count() * 4, 256, 0, s>>>(R, batch, w.dir, w.nSites);
+  SCN_LAUNCH_CHECK("k_rank");
+  k_flags<<<grid_for(rows, 128), 128, 0, s>>>(R, batch, d_in_keys, d_in_off, w.dir, w.sortedRow, w.flags, w.cnt, true);
+  SCN_LAUNCH_CHECK("k_flags");
+  const int chunks = rows / SCAN_CHUNK + 1;
+  k_scan_reduce<<<grid_for(chunks, 1), SCAN_THREADS, 0, s>>>(w.cnt, d_in_off, batch, w.partial);
+  SCN_LAUNCH_CHECK("k_scan_reduce");
+  k_scan_partials<<<1, 1024, 0, s>>>(d_in_off, batch, w.partial);
+  SCN_LAUNCH_CHECK("k_scan_partials");
+  k_scan_apply<<<grid_for(chunks, 1), SCAN_THREADS, 0, s>>>(w.cnt, d_in_off, batch, w.partial);
+  SCN_LAUNCH_CHECK("k_scan_apply");
+  k_samples<<<1, 1024, 0, s>>>(R, batch, d_in_off, w.cnt, d_out_off, d_out_bg, d_out_keys, rows_out_capacity, d_result);
+  SCN_LAUNCH_CHECK("k_samples");
+  k_assign<<<grid_for((long long)rows * R.T, 256), 256, 0, s>>>(R, batch, d_in_keys, d_in_off, w.sortedRow, w.flags, w.cnt,
+                                                                 d_out_off, d_out_keys, rows_out_capacity);
+  SCN_LAUNCH_CHECK("k_assign");
+  k_fill<<<grid_for((long long)(rows_out_capacity > 0 ? rows_out_capacity : 1) * R.sd, 256), 256, 0, s>>>(
+      R, batch, d_in_off, d_in_bg, w.dir, w.sortedRow, d_out_off, d_out_keys, d_rules, rows_out_capacity, d_result);
+  SCN_LAUNCH_CHECK("k_fill");
+  return SCN_OK;
+}
+
+extern "C" size_t scn_terminal_rules_workspace_bytes(int dim, int spatial_size, int batch, int rows_in_bound) {
+  if (dim < 1 || dim > 4 || spatial_size < 1 || batch < 0 || rows_in_bound < 0) return 0;
+  long long cells = ipowll(spatial_size, dim);
+  if (cells >= (1ll << 31)) return 0;
+  return carve(nullptr, batch, (int)((cells + 31) / 32), rows_in_bound, 0).bytes;
+}
+
+extern "C" int scn_terminal_rules_build(int dim, int spatial_size, int batch, const int *d_in_keys,
+                                        const int *d_in_off, const int *d_in_bg, int rows_in_bound, int S,
+                                        int *d_out_keys, int *d_out_off, int *d_out_bg, int *d_rules,
+                                        int *d_result, void *d_workspace, size_t workspace_bytes,
+                                        scn_stream_t stream_) {
+  clear_error();
+  if (dim < 1 || dim > 4 || spatial_size < 1 || batch < 1 || rows_in_bound < 0 || S < 1)
+    return fail(SCN_ERR_INVALID, "bad terminal pooling geometry");
+  if ((!d_in_keys && rows_in_bound > 0) || !d_in_off || !d_in_bg || !d_out_keys || !d_out_off || !d_out_bg || !d_rules || !d_result || !d_workspace)
+    return fail(SCN_ERR_INVALID, "null pointer");
+  long long cells = ipowll(spatial_size, dim);
+  if (cells >= (1ll << 31)) return fail(SCN_ERR_UNSUPPORTED, "spatial_size^dim must be below 2^31");
+  Regions R = {};
+  R.dim = dim; R.nIn = spatial_size; R.cells = (int)cells; R.W = (int)((cells + 31) / 32); R.T = 0;
+  Workspace w = carve(d_workspace, batch, R.W, rows_in_bound, 0);
+  if (w.bytes > workspace_bytes) return fail(SCN_ERR_WORKSPACE, "workspace smaller than scn_terminal_rules_workspace_bytes()");
+  cudaStream_t s = (cudaStream_t)stream_;
+  const int rows = rows_in_bound > 0 ? rows_in_bound : 1;
+  SCN_CUDA_TRY(cudaMemsetAsync(w.dir, 0, (size_t)batch * R.W * sizeof(uint2), s));
+  SCN_CUDA_TRY(cudaMemsetAsync(d_result, 0, 4 * sizeof(int), s));
+  k_mark<<<grid_for(rows, 256), 256, 0, s>>>(R, batch, d_in_keys, d_in_off, w.dir, d_result);
+  SCN_LAUNCH_CHECK("k_mark");
+  k_rank<<<batch < sm_count() * 4 ? batch : sm_count() * 4, 256, 0, s>>>(R, batch, w.dir, w.nSites);
+  SCN_LAUNCH_CHECK("k_rank");
+  k_flags<<<grid_for(rows, 128), 128, 0, s>>>(R, batch, d_in_keys, d_in_off, w.dir, w.sortedRow, nullptr, nullptr, false);
+  SCN_LAUNCH_CHECK("k_flags");
+  k_terminal<<<grid_for((long long)batch * S, 256), 256, 0, s>>>(batch, S, d_in_off, d_in_bg, w.nSites, w.sortedRow, d_rules,
+                                                                d_out_keys, d_out_off, d_out_bg, d_result);
+  SCN_LAUNCH_CHECK("k_terminal");
+  return SCN_OK;
+}

@@ -1,0 +1,65 @@
+// Shared host/device helpers of libscn_b200.so (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <cstdint>
+#include "scn_b200.h"
+
+namespace scn {
+
+// Thread-local message behind scn_last_error().
+void set_error(const char *fmt, ...);
+void clear_error();
+
+// Number of SMs of the current device (cached per device); grids are sized in multiples of it.
+int sm_count();
+
+inline int fail(int status, const char *what) {
+  set_error("%s", what);
+  return status;
+}
+
+#define SCN_CUDA_TRY(expr)                                                                  \
+  do {                                                                                      \
+    cudaError_t e__ = (expr);                                                               \
+    if (e__ != cudaSuccess) {                                                               \
+      scn::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
+      return SCN_ERR_CUDA;                                                                  \
+    }                                                                                       \
+  } while (0)
+
+#define SCN_LAUNCH_CHECK(name)                                                              \
+  do {                                                                                      \
+    cudaError_t e__ = cudaGetLastError();                                                   \
+    if (e__ != cudaSuccess) {                                                               \
+      scn::set_error("launch of %s failed: %s", name, cudaGetErrorString(e__));             \
+      return SCN_ERR_CUDA;                                                                  \
+    }                                                                                       \
+  } while (0)
+
+// Grid size for a grid-stride kernel over n items: enough CTAs to cover n, capped at
+// `waves` CTAs per SM so a launch never exceeds a few resident waves.
+inline int grid_for(long long n, int block, int waves = 8) {
+  long long need = (n + block - 1) / block;
+  long long cap = (long long)sm_count() * waves;
+  if (need < 1) need = 1;
+  return (int)(need < cap ? need : cap);
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ActivationFunction semantics of the reference (SigmoidLayer.cu:9, 46, 83, 121, 204-213;
+// NetworkInNetworkPReLULayer.cu:12-13).  SOFTMAX is handled by the callers.
+__device__ __forceinline__ float activate(float v, int act, float slope) {
+  switch (act) {
+  case SCN_RELU: return v > 0.f ? v : 0.f;
+  case SCN_VLEAKYRELU: return v > 0.f ? v : v * 0.333f;
+  case SCN_LEAKYRELU: return v > 0.f ? v : v * 0.01f;
+  case SCN_TANH: return tanhf(v);
+  case SCN_SIGMOID: return 1.0f / (1.0f + expf(-v));
+  case SCN_PRELU: return v > 0.f ? v : v * slope;
+  default: return v;
+  }
+}
+
+} // namespace scn

@@ -1,0 +1,116 @@
+"""GPU parity of the feature kernels through the C ABI against the oracle's CPU
+restatement: integer results bit-exact, fp32 results within 1e-4 relative (the tolerance
+the target states for the fp32 / 3xTF32 path), measured against the fp64-accumulating
+oracle."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RTOL_FP32 = 1e-4  # max |a-b| / max|b| over a tensor
+
+
+def relerr(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def random_rules(rng, rows_out, fs, rows_in, neg_frac=0.1):
+    r = rng.integers(0, rows_in, size=(rows_out, fs)).astype(np.int32)
+    r[rng.random(r.shape) < neg_frac] = -1
+    return r
+
+
+@pytest.mark.parametrize("C,sd", [(32, 4), (96, 4), (96, 8), (7, 9), (64, 27), (200, 3)])
+def test_maxpool(abi, oracle, C, sd):
+    rng = np.random.default_rng(C * 100 + sd)
+    rows_in, rows_out = 500, 333
+    feat = rng.standard_normal((rows_in, C)).astype(np.float32)
+    feat[rng.random(feat.shape) < 0.2] = 0.5  # ties: the first maximum must win
+    rules = random_rules(rng, rows_out, sd, rows_in, 0.2)
+    rules[5, :] = -1  # a row without any usable rule
+    ref_out, ref_ch = oracle.maxpool(feat, rules, sd)
+    out, ch = abi.maxpool_forward(torch.from_numpy(feat).cuda(), torch.from_numpy(rules).cuda().flatten(), sd)
+    np.testing.assert_array_equal(ch.cpu().numpy(), ref_ch)
+    np.testing.assert_array_equal(out.cpu().numpy(), ref_out)
+
+
+def test_terminal_pool(abi, oracle):
+    rng = np.random.default_rng(4)
+    C, S, batch, rows_in = 96, 9, 17, 200
+    feat = rng.standard_normal((rows_in, C)).astype(np.float32)
+    rules = np.full((batch, S), -1, np.int32)
+    for b in range(batch):
+        n = rng.integers(1, S + 1)
+        rules[b, :n] = rng.integers(0, rows_in, n)
+    ref = oracle.terminal_pool(feat, rules, S)
+    out = abi.terminal_pool_forward(torch.from_numpy(feat).cuda(), torch.from_numpy(rules).cuda().flatten(), S)
+    np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=1e-6, atol=1e-6)
+
+
+def test_gather(abi, oracle):
+    rng = np.random.default_rng(8)
+    feat = rng.standard_normal((100, 5)).astype(np.float32)
+    rules = random_rules(rng, 77, 9, 100)
+    ref = oracle.gather(feat, rules, 5)
+    out = abi.gather_forward(torch.from_numpy(feat).cuda(), torch.from_numpy(rules).cuda().flatten())
+    np.testing.assert_array_equal(out.cpu().numpy(), ref)
+
+
+def test_top_indices(abi, oracle):
+    rng = np.random.default_rng(3)
+    for n, k in ((10, 1), (10, 3), (101, 5), (2, 2), (1, 1)):
+        v = rng.standard_normal((64, n)).astype(np.float32)
+        v[::3] = np.round(v[::3])  # ties
+        ref = np.stack([oracle.top_indices(row, k) for row in v])
+        out = abi.top_indices(torch.from_numpy(v).cuda(), k)
+        np.testing.assert_array_equal(out.cpu().numpy(), ref)
+
+
+CONV = [
+    # rows_in, rows_out, fs, nIn, N, act, p
+    (300, 257, 9, 3, 32, "VLEAKYRELU", 1.0),
+    (300, 100, 4, 32, 64, "VLEAKYRELU", 0.9),
+    (64, 64, 1, 160, 10, "SOFTMAX", 1.0),
+    (200, 513, 27, 1, 32, "RELU", 1.0),
+    (128, 130, 8, 16, 96, "LEAKYRELU", 0.75),
+    (50, 70, 4, 24, 40, "PRELU", 1.0),
+    (50, 70, 4, 8, 33, "TANH", 1.0),
+    (50, 70, 1, 8, 16, "SIGMOID", 1.0),
+    (50, 70, 2, 5, 7, "NOSIGMOID", 0.5),
+]
+
+
+@pytest.mark.parametrize("rows_in,rows_out,fs,nIn,N,act,p", CONV)
+def test_conv_nin_fp32(abi, oracle, rows_in, rows_out, fs, nIn, N, act, p):
+    from oracle import orc
+    rng = np.random.default_rng(rows_out + fs * 7 + N)
+    actc = getattr(orc, act)
+    K = fs * nIn
+    feat = rng.standard_normal((rows_in, nIn)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * np.sqrt(2.0 / K)).astype(np.float32)
+    B = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    prelu = rng.uniform(0.1, 0.4, N).astype(np.float32) if act == "PRELU" else None
+    if fs == 1:
+        rows_out = rows_in
+        rules = None
+        X = feat
+    else:
+        rules = random_rules(rng, rows_out, fs, rows_in)
+        X = oracle.gather(feat, rules, nIn).reshape(rows_out, K)
+    ref = oracle.nin_forward(X, W, B, prelu, p, actc, accum64=True)
+    out = abi.conv_nin_forward(torch.from_numpy(feat).cuda(),
+                               None if rules is None else torch.from_numpy(rules).cuda().flatten(), fs,
+                               torch.from_numpy(W).cuda(), torch.from_numpy(B).cuda(),
+                               None if prelu is None else torch.from_numpy(prelu).cuda(), p, actc, abi.PREC_FP32)
+    assert relerr(out.cpu().numpy(), ref) < RTOL_FP32
+
+
+def test_conv_nin_rejects_bad_arguments(abi):
+    f = torch.zeros((4, 8), device="cuda")
+    W = torch.zeros((16, 16), device="cuda")
+    B = torch.zeros(16, device="cuda")
+    with pytest.raises(abi.ScnError):
+        abi.conv_nin_forward(f, None, 2, W, B)  # fs != 1 without rules
+    with pytest.raises(abi.ScnError):
+        abi.conv_nin_forward(f, None, 1, W[:8].contiguous(), B, act=abi.PRELU)  # PReLU slopes missing

@@ -1,0 +1,194 @@
+"""GPU parity (bit-exact): scn_rules_build / scn_terminal_rules_build through the C ABI
+against the oracle's rule construction on the same seeded grids."""
+import numpy as np
+import pytest
+import torch
+
+from gridgen import random_grids
+
+pytestmark = pytest.mark.gpu
+
+
+def to_dev_grid(keys, rows, off, bg):
+    """Flat (keys, rows) protocol -> device keys[row] / off / bg (rows are contiguous per
+    sample, background row included)."""
+    first = int(min([r for r in rows.tolist()] + [b for b in bg.tolist() if b >= 0] + [10 ** 9]))
+    if first == 10 ** 9:
+        first = 0
+    n_rows = len(rows) + int((bg >= 0).sum())
+    dk = np.full(n_rows, -1, np.int32)
+    doff = np.zeros(len(bg) + 1, np.int32)
+    row_lo = first
+    for b in range(len(bg)):
+        doff[b] = row_lo - first
+        cnt = off[b + 1] - off[b] + (1 if bg[b] >= 0 else 0)
+        row_lo += cnt
+    doff[len(bg)] = row_lo - first
+    dk[rows - first] = keys
+    dbg = np.where(bg >= 0, bg - first, -1).astype(np.int32)
+    return (torch.from_numpy(dk).cuda(), torch.from_numpy(doff).cuda(), torch.from_numpy(dbg).cuda(), first)
+
+
+def run_gpu(abi, lattice, dim, nIn, nOut, size, stride, minActive, g, capacity=None):
+    dk, doff, dbg, first = to_dev_grid(*g)
+    assert first == 0
+    R = abi.regions(lattice, dim, nIn, nOut, size, stride, minActive)
+    T = ((size + stride - 1) // stride) ** dim
+    cap = capacity if capacity is not None else dk.numel() * max(T, 1) + len(g[3]) + 8
+    out = abi.rules_build(R, dk, doff, dbg, cap)
+    torch.cuda.synchronize()
+    res = out["result"].cpu().numpy()
+    return out, res
+
+
+def compare(out, res, ref):
+    rows, sites, err, _ = (int(v) for v in res)
+    assert err == 0
+    assert rows == ref["n_sites"]
+    sd = out["sd"]
+    np.testing.assert_array_equal(out["rules"].cpu().numpy()[: rows * sd], ref["rules"])
+    np.testing.assert_array_equal(out["out_bg"].cpu().numpy(), ref["out_bg"])
+    gk = out["out_keys"].cpu().numpy()[:rows]
+    goff = out["out_off"].cpu().numpy()
+    # rebuild the (key, row) listing per sample in ascending key order
+    keys, rws = [], []
+    for b in range(len(ref["out_bg"])):
+        lo, hi = goff[b], goff[b + 1]
+        k = gk[lo:hi]
+        r = np.arange(lo, hi)
+        m = k >= 0
+        order = np.argsort(k[m], kind="stable")
+        keys.append(k[m][order]); rws.append(r[m][order])
+        assert (~m).sum() == (1 if ref["out_bg"][b] >= 0 else 0)
+        if ref["out_bg"][b] >= 0:
+            assert r[~m][0] == ref["out_bg"][b]
+        assert len(k[m]) == ref["out_off"][b + 1] - ref["out_off"][b]
+    np.testing.assert_array_equal(np.concatenate(keys) if keys else np.zeros(0), ref["out_keys"])
+    np.testing.assert_array_equal(np.concatenate(rws) if rws else np.zeros(0), ref["out_rows"])
+    assert sites == len(ref["out_keys"])
+
+
+SQUARE = [
+    (1, 9, 3, 1, 1), (1, 5, 2, 2, 1), (1, 6, 3, 2, 1),
+    (2, 6, 3, 1, 1), (2, 7, 2, 1, 1), (2, 5, 2, 2, 1), (2, 4, 3, 2, 1), (2, 3, 3, 3, 1), (2, 1, 2, 1, 1),
+    (3, 5, 3, 1, 1), (3, 6, 2, 1, 1), (3, 4, 2, 2, 1), (3, 3, 3, 2, 1), (4, 3, 2, 1, 1), (4, 2, 3, 1, 1),
+    (1, 6, 3, 1, 2), (2, 6, 3, 1, 2), (2, 6, 2, 1, 3), (2, 5, 2, 2, 2), (3, 5, 2, 1, 2), (3, 4, 3, 1, 4),
+    (4, 3, 2, 1, 2), (4, 2, 2, 2, 3),
+    (2, 7, 3, 1, -1), (3, 4, 3, 1, -1),
+]
+
+
+@pytest.mark.parametrize("dim,nOut,size,stride,minActive", SQUARE)
+def test_square_rules(abi, oracle, dim, nOut, size, stride, minActive):
+    nIn = size + (nOut - 1) * stride
+    rng = np.random.default_rng(1000 * dim + 10 * nOut + size + stride)
+    for density in (0.0, 0.03, 0.3, 0.8, 1.0):
+        for with_bg in (True, False):
+            g = random_grids(rng, 5, dim, nIn, density, with_bg=with_bg)
+            ref = oracle.grid_rules(0, dim, nIn, nOut, size, stride, minActive, *g)
+            out, res = run_gpu(abi, 0, dim, nIn, nOut, size, stride, minActive, g)
+            compare(out, res, ref)
+
+
+TRI = [
+    (2, 6, 2, 1, 1), (2, 5, 3, 1, 1), (2, 4, 2, 2, 1), (2, 3, 3, 2, 1),
+    (3, 5, 2, 1, 1), (3, 4, 3, 1, 1), (3, 4, 2, 2, 1), (4, 3, 2, 1, 1), (4, 2, 2, 2, 1),
+    (1, 5, 2, 1, 2), (2, 6, 2, 1, 2), (2, 5, 3, 1, 3), (3, 5, 2, 1, 2), (3, 4, 3, 1, 2), (3, 3, 2, 2, 2), (4, 3, 2, 1, 2),
+]
+
+
+@pytest.mark.parametrize("dim,nOut,size,stride,minActive", TRI)
+def test_triangular_rules(abi, oracle, dim, nOut, size, stride, minActive):
+    nIn = size + (nOut - 1) * stride
+    rng = np.random.default_rng(77 + 1000 * dim + 10 * nOut + size + stride)
+    for density in (0.0, 0.05, 0.3, 0.8, 1.0):
+        for with_bg in (True, False):
+            g = random_grids(rng, 5, dim, nIn, density, triangular=True, with_bg=with_bg)
+            ref = oracle.grid_rules(1, dim, nIn, nOut, size, stride, minActive, *g)
+            out, res = run_gpu(abi, 1, dim, nIn, nOut, size, stride, minActive, g)
+            compare(out, res, ref)
+
+
+def test_larger_batches_and_ragged(abi, oracle):
+    """Config-shaped geometry: ragged site counts, empty samples, many samples."""
+    rng = np.random.default_rng(11)
+    cases = [(2, 96, 3, 1, 64, [0.0, 0.11, 0.5]), (2, 94, 2, 2, 64, [0.02, 0.3]),
+             (3, 48, 3, 1, 6, [0.0, 0.01, 0.05]), (3, 46, 2, 2, 6, [0.03, 0.2]), (3, 23, 2, 1, 9, [0.1, 0.6, 1.0])]
+    for dim, nIn, size, stride, batch, dens in cases:
+        nOut = (nIn - size) // stride + 1
+        g = random_grids(rng, batch, dim, nIn, dens)
+        ref = oracle.grid_rules(0, dim, nIn, nOut, size, stride, 1, *g)
+        out, res = run_gpu(abi, 0, dim, nIn, nOut, size, stride, 1, g)
+        compare(out, res, ref)
+
+
+def test_chain_on_device(abi, oracle):
+    """Feed each layer's device outputs straight into the next build (no host round trip of
+    the grids), as the network driver does."""
+    rng = np.random.default_rng(5)
+    for dim, S in ((2, 24), (3, 12)):
+        g = random_grids(rng, 7, dim, S, [0.02, 0.2, 0.6, 1.0, 0.0])
+        cur = g
+        dk, doff, dbg, _ = to_dev_grid(*g)
+        n = S
+        for size, stride in ((3, 1), (2, 2), (2, 1), (2, 2)):
+            nOut = (n - size) // stride + 1
+            ref = oracle.grid_rules(0, dim, n, nOut, size, stride, 1, *cur)
+            R = abi.regions(0, dim, n, nOut, size, stride, 1)
+            cap = dk.numel() * ((size + stride - 1) // stride) ** dim + 16
+            out = abi.rules_build(R, dk, doff, dbg, cap)
+            torch.cuda.synchronize()
+            res = out["result"].cpu().numpy()
+            compare(out, res, ref)
+            rows = int(res[0])
+            dk, doff, dbg = out["out_keys"][:rows].contiguous(), out["out_off"], out["out_bg"]
+            cur = (ref["out_keys"], ref["out_rows"], ref["out_off"], ref["out_bg"])
+            n = nOut
+
+
+def test_capacity_and_bad_keys_are_reported(abi):
+    rng = np.random.default_rng(2)
+    g = random_grids(rng, 2, 2, 8, 0.5)
+    out, res = run_gpu(abi, 0, 2, 8, 6, 3, 1, 1, g, capacity=3)
+    assert res[2] & abi.DEV_ERR_CAPACITY
+    dk, doff, dbg, _ = to_dev_grid(*g)
+    dk2 = dk.clone()
+    site = int((dk2 >= 0).nonzero()[0])
+    dk2[site] = 8 * 8 + 5  # outside the grid
+    out = abi.rules_build(abi.regions(0, 2, 8, 6, 3, 1, 1), dk2, doff, dbg, 200)
+    torch.cuda.synchronize()
+    assert int(out["result"][2]) & abi.DEV_ERR_KEY
+    dk3 = dk.clone()
+    sites = (dk3 >= 0).nonzero().flatten()
+    same = [int(s) for s in sites if int(s) < int(doff[1])][:2]
+    dk3[same[1]] = dk3[same[0]]
+    out = abi.rules_build(abi.regions(0, 2, 8, 6, 3, 1, 1), dk3, doff, dbg, 200)
+    torch.cuda.synchronize()
+    assert int(out["result"][2]) & abi.DEV_ERR_DUPLICATE
+
+
+def test_invalid_geometry_is_rejected(abi):
+    z = torch.zeros(4, dtype=torch.int32, device="cuda")
+    with pytest.raises(abi.ScnError):
+        abi.rules_build(abi.regions(0, 2, 9, 6, 3, 1, 1), z, z[:2], z[:1], 10)  # nIn != size+(nOut-1)*stride
+    with pytest.raises(abi.ScnError):
+        abi.rules_build(abi.regions(0, 5, 8, 6, 3, 1, 1), z, z[:2], z[:1], 10)  # dim 5
+    with pytest.raises(abi.ScnError):
+        abi.rules_build(abi.regions(1, 2, 8, 6, 3, 1, -1), z, z[:2], z[:1], 10)  # valid on a triangular lattice
+
+
+def test_terminal_rules(abi, oracle):
+    rng = np.random.default_rng(9)
+    for dim, S in ((2, 3), (3, 2), (3, 3)):
+        for dens in ([0.0, 0.5, 1.0], [0.0], [0.3]):
+            g = random_grids(rng, 6, dim, S, dens)
+            ref = oracle.grid_rules(2, dim, S, 1, 1, 1, 1, *g)
+            dk, doff, dbg, _ = to_dev_grid(*g)
+            width = len(ref["rules"]) // 6
+            out = abi.terminal_rules_build(dim, S, dk, doff, dbg, width)
+            torch.cuda.synchronize()
+            assert int(out["result"][2]) == 0 and int(out["result"][0]) == 6
+            np.testing.assert_array_equal(out["rules"].cpu().numpy(), ref["rules"])
+            np.testing.assert_array_equal(out["out_off"].cpu().numpy(), np.arange(7))
+            np.testing.assert_array_equal(out["out_bg"].cpu().numpy(), ref["out_bg"])
+            np.testing.assert_array_equal(out["out_keys"].cpu().numpy(), np.zeros(6))
