@@ -140,6 +140,12 @@ int scn_conv_pack_weights(const float *d_W, int K, int N, int precision, void *d
 int scn_gather_forward(const float *d_in, const int *d_rules, long long count, int nIn,
                        float *d_out, scn_stream_t stream);
 
+/* Replaces applySigmoid and PreLU as stand-alone passes (SigmoidLayer.cu:187-222;
+ * NetworkInNetworkPReLULayer.cu:8-23): d_out = act(d_in) over [rows x N], in place allowed.
+ * The layer kernels fuse their activation; this is for callers that apply one themselves. */
+int scn_activation_forward(const float *d_in, float *d_out, int rows, int N, int act,
+                           const float *d_prelu, scn_stream_t stream);
+
 /* Replaces maxPool / dMaxPool (MaxPoolingLayer.cu:9-72): per output row and channel the
  * maximum over the row's non-negative rules, first maximum wins, and the flat input index
  * rule*C + channel of the winner in d_choices (SpatiallySparseBatchSubInterface::

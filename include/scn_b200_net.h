@@ -1,0 +1,102 @@
+/* scn_b200_net -- C entry points of libscn_b200_host.so, the C++ host library whose classes
+ * keep the reference's names (SparseConvNetCUDA, the layer classes, vectorCUDA,
+ * SpatiallySparseBatchInterface, NetworkArchitectures; headers under
+ * sparseconvnet-archived_b200/csrc/host/).  C++ callers use those classes directly; this
+ * header exists for hosts that cannot (the Python test and benchmark harness binds it with
+ * ctypes).  Each function wraps the reference-named method given in its comment (paths
+ * inside the reference project, SparseConvNet/...).
+ *
+ * All functions return 0 on success, non-zero on failure with scn_net_last_error() set;
+ * nothing prints an error or exits.  Buffers named h_* are host memory, d_* device memory.
+ */
+#ifndef SCN_B200_NET_H
+#define SCN_B200_NET_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct scn_net scn_net_t;
+
+const char *scn_net_last_error(void);
+
+/* SparseConvNetCUDA::SparseConvNetCUDA (SparseConvNetCUDA.cu:24-42).  `stream` is a
+ * cudaStream_t to enqueue on, or NULL for a stream of the network's own; the current CUDA
+ * device is used.  lattice: 0 square/cubic (SparseConvNet), 1 triangular/tetrahedral
+ * (SparseConvTriangLeNet). */
+scn_net_t *scn_net_create(int dimension, int nInputFeatures, int nClasses, int nTop, int lattice, void *stream);
+void scn_net_destroy(scn_net_t *net);
+
+/* SparseConvNet::addLeNetLayerMP / SparseConvTriangLeNet::addLeNetLayerMP (SparseConvNet.h:29-32, 80-83). */
+int scn_net_addLeNetLayerMP(scn_net_t *net, int nFeatures, int filterSize, int filterStride, int poolSize, int poolStride,
+                            int activationFn, float dropout, int minActiveInputs);
+/* SparseConvNet::addTerminalPoolingLayer (SparseConvNet.cu:56-58, 123-126). */
+int scn_net_addTerminalPoolingLayer(scn_net_t *net, int poolSize);
+/* SparseConvNetCUDA::addSoftmaxLayer (SparseConvNetCUDA.cu:200-213). */
+int scn_net_addSoftmaxLayer(scn_net_t *net);
+/* DeepCNet::DeepCNet (NetworkArchitectures.cpp:3-11), on the given stream. */
+scn_net_t *scn_net_DeepCNet(int dimension, int l, int k, int fn, int nInputFeatures, int nClasses, float p, int nTop, void *stream);
+
+int scn_net_n_layers(scn_net_t *net);
+int scn_net_input_spatial_size(scn_net_t *net);
+/* info[10] = type (0 conv, 1 triangular conv, 2 NiN, 3 max pool, 4 triangular max pool,
+ * 5 terminal pool), size, stride, minActiveInputs, nFeaturesIn, nFeaturesOut, cells,
+ * activation, inSpatialSize, outSpatialSize. */
+int scn_net_layer_info(scn_net_t *net, int layer, int *info, float *dropout);
+/* Set NetworkInNetworkLayer::W, B (and PReLU) of layer `layer` from host arrays
+ * (NetworkInNetworkLayer.h:12-19). */
+int scn_net_set_weights(scn_net_t *net, int layer, const float *h_W, const float *h_B, const float *h_prelu);
+/* SparseConvNetCUDA::loadWeights / saveWeights (SparseConvNetCUDA.cu:406-442), momentum = false. */
+int scn_net_load_weights(scn_net_t *net, const char *baseName, int epoch);
+int scn_net_save_weights(scn_net_t *net, const char *baseName, int epoch);
+/* scn_precision for every NetworkInNetwork layer (default SCN_PREC_AUTO). */
+int scn_net_set_precision(scn_net_t *net, int precision);
+
+/* One batch end to end from HOST buffers, as BatchProducer::nextBatch + processBatch do
+ * (BatchProducer.cu:108-142; SparseConvNetCUDA.cu:227-271): upload, rule chain on the
+ * device, all layers, classifier read-back.
+ *   h_keys[rows]  site key per row, -1 for a sample's background row
+ *   h_off[batch+1] first row of each sample;  h_features[rows x nInputFeatures]
+ *   h_probs[batch x nClasses], h_predictions[batch x nTop] (either may be NULL) */
+int scn_net_forward_host(scn_net_t *net, int batch, const int *h_keys, const int *h_off, const float *h_features,
+                         float *h_probs, int *h_predictions);
+/* The same with inputs already resident in device memory (they are copied device-to-device
+ * into the batch's interface).  d_bg[batch] is each sample's background row or -1;
+ * maxSitesPerSample the largest site count of a sample.  Results are left on the device:
+ * d_probs[batch x nClasses], d_top[batch x nTop] (either may be NULL).  Does not wait for
+ * the stream beyond the rule chain's one read-back. */
+int scn_net_forward_device(scn_net_t *net, int batch, int rows, int maxSitesPerSample, const int *d_keys, const int *d_off,
+                           const int *d_bg, const float *d_features, float *d_probs, int *d_top);
+
+/* SpatiallySparseBatchInterface i of the last forward (0 = input, i+1 = output of layer i;
+ * SpatiallySparseBatchInterface.h:19-46).  sizes[5] = nSpatialSites, nFeatures, spatialSize,
+ * rules.size(), poolingChoices.size() (0 unless layer i-1 pools).  A ConvolutionalLayer
+ * fused into the next layer has no materialised features: its nFeatures is reported but
+ * fetching its features fails unless h_features is NULL. */
+int scn_net_iface_sizes(scn_net_t *net, int i, long long *sizes);
+int scn_net_iface_fetch(scn_net_t *net, int i, float *h_features, int *h_rules, int *h_choices, int *h_rowKeys);
+
+/* multiplyAddCount since the last call (types.h:46-52; NetworkInNetworkLayer.cu:197-199). */
+double scn_net_take_multiply_adds(void);
+
+/* CUDA-event timing of each layer's forwards() and of the rule chain, for roofline reports.
+ * After a forward and a stream synchronisation, h_ms[0..n_layers) holds the milliseconds of
+ * each layer's forward kernels and h_ms[n_layers] the rule chain (uploads excluded). */
+int scn_net_enable_timing(scn_net_t *net, int on);
+int scn_net_layer_times(scn_net_t *net, float *h_ms);
+
+/* Run a small synthetic dataset of SitesPicture objects through
+ * SparseConvNetCUDA::processDataset with its BatchProducer threads
+ * (SparseConvNetCUDA.cu:272-326; BatchProducer.cu): same flat input as
+ * scn_net_forward_host plus labels; returns the error rate through *errorRate and the
+ * per-sample probabilities of the pass in h_probs. */
+int scn_net_process_dataset(scn_net_t *net, int nSamples, const int *h_keys, const int *h_off, const float *h_features,
+                            const int *h_labels, int batchSize, float *errorRate, float *h_probs);
+
+/* utilities.cu:35-56, host version, for pinning against the oracle. */
+int scn_host_vectorTopIndices(const float *h_v, int n, int k, int *h_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

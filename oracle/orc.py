@@ -170,9 +170,10 @@ class Oracle(_RulesLib):
 class OracleNet:
     """Mirror of SparseConvNetCUDA's builder calls plus a CPU forward."""
 
-    def __init__(self, oracle, dim, nInputFeatures, nClasses, nTop=1, handle=None):
+    def __init__(self, oracle, dim, nInputFeatures, nClasses, nTop=1, handle=None, lattice=0):
+        """lattice 0 mirrors SparseConvNet, 1 SparseConvTriangLeNet (SparseConvNet.h:20-99)."""
         self.o, self.L = oracle, oracle.lib
-        self.dim, self.nIn, self.nClasses, self.nTop = dim, nInputFeatures, nClasses, nTop
+        self.dim, self.nIn, self.nClasses, self.nTop, self.lattice = dim, nInputFeatures, nClasses, nTop, lattice
         self.h = handle if handle is not None else self.L.orc_net_create(dim, nInputFeatures, nClasses, nTop)
 
     @classmethod
@@ -187,12 +188,15 @@ class OracleNet:
             pass
 
     def addLeNetLayerMP(self, nFeatures, fs, fstride, ps, pstride, act=RELU, dropout=0.0, minActive=1):
-        self.L.orc_net_addLeNetLayerMP(self.h, nFeatures, fs, fstride, ps, pstride, act, dropout, minActive)
+        f = self.L.orc_net_addTriangularLeNetLayerMP if self.lattice == 1 else self.L.orc_net_addLeNetLayerMP
+        f(self.h, nFeatures, fs, fstride, ps, pstride, act, dropout, minActive)
 
     def addTriangularLeNetLayerMP(self, nFeatures, fs, fstride, ps, pstride, act=RELU, dropout=0.0, minActive=1):
         self.L.orc_net_addTriangularLeNetLayerMP(self.h, nFeatures, fs, fstride, ps, pstride, act, dropout, minActive)
 
-    def addTerminalPoolingLayer(self, poolSize, S):
+    def addTerminalPoolingLayer(self, poolSize, S=None):
+        if S is None:  # the facades pass ipow / triangleSize (SparseConvNet.cu:56-58, 123-126)
+            S = self.L.orc_triangleSize(poolSize, self.dim) if self.lattice == 1 else self.L.orc_ipow(poolSize, self.dim)
         self.L.orc_net_addTerminalPoolingLayer(self.h, poolSize, S)
 
     def addSoftmaxLayer(self):

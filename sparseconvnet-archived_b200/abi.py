@@ -22,7 +22,7 @@ EXPORTS = [
     "scn_rules_workspace_bytes", "scn_rules_build", "scn_terminal_rules_workspace_bytes",
     "scn_terminal_rules_build", "scn_conv_nin_forward", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_gather_forward", "scn_maxpool_forward",
-    "scn_terminal_pool_forward", "scn_top_indices",
+    "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward",
 ]
 
 
@@ -64,6 +64,7 @@ def lib():
         L.scn_maxpool_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p]
         L.scn_terminal_pool_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p]
         L.scn_top_indices.argtypes = [c_p, c_int, c_int, c_int, c_p, c_p]
+        L.scn_activation_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p]
         _lib = L
     return _lib
 
@@ -191,3 +192,10 @@ def top_indices(probs, nTop):
     top = torch.empty((rows, nTop), dtype=torch.int32, device=probs.device)
     check(lib().scn_top_indices(_ptr(_f32(probs)), rows, nClasses, nTop, _ptr(top), _stream()))
     return top
+
+
+def activation_forward(x, act, prelu=None):
+    rows, N = x.shape
+    out = torch.empty_like(x)
+    check(lib().scn_activation_forward(_ptr(_f32(x)), _ptr(out), rows, N, act, _ptr(prelu), _stream()))
+    return out

@@ -1,0 +1,464 @@
+// Geometry layers and the learnt layers: host-side bookkeeping around the C ABI calls.
+#include <cmath>
+#include <cstring>
+#include <random>
+#include "ConvolutionalLayer.h"
+#include "ConvolutionalTriangularLayer.h"
+#include "MaxPoolingLayer.h"
+#include "MaxPoolingTriangularLayer.h"
+#include "NetworkInNetworkLayer.h"
+#include "NetworkInNetworkPReLULayer.h"
+#include "RuleChain.h"
+#include "SigmoidLayer.h"
+#include "SoftmaxClassifier.h"
+#include "TerminalPoolingLayer.h"
+
+using rulechain::preprocessNow;
+
+namespace {
+void requireInference(const SpatiallySparseBatch &batch) {
+  if (batch.type == TRAINBATCH) throw ScnException("TRAINBATCH: this is an inference library (TESTBATCH, UNLABELEDBATCH, RESCALEBATCH only)");
+}
+// Shared body of the four region layers' finishRules().
+void finishGeometry(const scn_regions_t &R, SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                    SpatiallySparseBatchInterface &output, int nFeaturesOut, int copies, const int *h) {
+  output.nFeatures = nFeaturesOut;
+  output.spatialSize = R.nOut;
+  output.backpropErrors = input.backpropErrors;
+  rulechain::finishRegions(R, output, h);
+  if (copies > 1) {
+    output.featuresPresent.copyToCPU();
+    rulechain::convolutionFeaturesPresent(input.featuresPresent.hVector(), output.featuresPresent.hVector(), input.nFeatures,
+                                          (int)input.featuresPresent.size(), copies);
+  } else {
+    output.featuresPresent.hVector() = input.featuresPresent.hVector();
+  }
+  (void)batch;
+}
+void checkSpatial(const SpatiallySparseBatchInterface &input, int inSpatialSize, const char *who) {
+  if (input.spatialSize != inSpatialSize)
+    throw ScnException(std::string(who) + ": input spatial size " + std::to_string(input.spatialSize) + " but the layer expects " +
+                       std::to_string(inSpatialSize) + " (call addSoftmaxLayer / calculateInputSpatialSize first)");
+}
+} // namespace
+
+// ------------------------------------------------------------------ ConvolutionalLayer
+ConvolutionalLayer::ConvolutionalLayer(cudaMemStream &memStream, int filterSize, int filterStride, int dimension, int nFeaturesIn,
+                                       int minActiveInputs)
+    : SpatiallySparseLayer(memStream), inSpatialSize(0), outSpatialSize(0), filterSize(filterSize), filterStride(filterStride),
+      dimension(dimension), nFeaturesIn(nFeaturesIn), minActiveInputs(minActiveInputs), fuseWithNext(false) {
+  changesGeometry = true;
+  fs = ipow(filterSize, dimension);
+  nFeaturesOut = fs * nFeaturesIn;
+  std::cout << "Convolution " << filterSize << "^" << dimension << "x" << nFeaturesIn << "->" << nFeaturesOut;
+  if (filterStride != 1) std::cout << " stride:" << filterStride;
+  if (minActiveInputs != 1) std::cout << " minActiveInputs:" << minActiveInputs;
+  std::cout << std::endl;
+}
+long long ConvolutionalLayer::enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                           SpatiallySparseBatchInterface &output, long long rowsInBound, int *d_result) {
+  requireInference(batch);
+  if (input.nFeatures != nFeaturesIn) throw ScnException("ConvolutionalLayer: wrong number of input features");
+  checkSpatial(input, inSpatialSize, "ConvolutionalLayer");
+  scn_regions_t R = {SCN_LATTICE_SQUARE, dimension, inSpatialSize, outSpatialSize, filterSize, filterStride, minActiveInputs};
+  output.nFeatures = nFeaturesOut; output.spatialSize = outSpatialSize; // known before any count is
+  return rulechain::enqueueRegions(R, batch, input, output, rowsInBound, d_result, memStream);
+}
+void ConvolutionalLayer::finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                     SpatiallySparseBatchInterface &output, const int *h) {
+  scn_regions_t R = {SCN_LATTICE_SQUARE, dimension, inSpatialSize, outSpatialSize, filterSize, filterStride, minActiveInputs};
+  finishGeometry(R, batch, input, output, nFeaturesOut, fs, h);
+}
+void ConvolutionalLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  preprocessNow(*this, batch, input, output);
+}
+void ConvolutionalLayer::forwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  if (fuseWithNext) { // the NetworkInNetwork layer behind this one gathers inside its kernel
+    output.deferredFrom = &input;
+    output.deferredCells = fs;
+    return;
+  }
+  output.sub->features.resize(output.nSpatialSites * output.featuresPresent.size());
+  propForwardToMatrixMultiply(input.sub->features.dPtr(), output.sub->features.dPtr(), output.rules.dPtr(), output.nSpatialSites * fs,
+                              input.featuresPresent.size(), memStream);
+}
+int ConvolutionalLayer::calculateInputSpatialSize(int outputSpatialSize) {
+  outSpatialSize = outputSpatialSize;
+  inSpatialSize = filterSize + (outputSpatialSize - 1) * filterStride;
+  std::cout << "-(C" << filterSize;
+  if (filterStride != 1) std::cout << "/" << filterStride;
+  std::cout << ")-" << inSpatialSize;
+  return inSpatialSize;
+}
+void propForwardToMatrixMultiply(float *inFeatures, float *outFeatures, int *rules, int count, int nIn, cudaMemStream &memStream) {
+  scnSafeCall(scn_gather_forward(inFeatures, rules, count, nIn, outFeatures, memStream.stream));
+}
+
+// ------------------------------------------------------------------ ConvolutionalTriangularLayer
+ConvolutionalTriangularLayer::ConvolutionalTriangularLayer(cudaMemStream &memStream, int filterSize, int filterStride, int dimension,
+                                                           int nFeaturesIn, int minActiveInputs)
+    : SpatiallySparseLayer(memStream), inSpatialSize(0), outSpatialSize(0), filterSize(filterSize), filterStride(filterStride),
+      dimension(dimension), nFeaturesIn(nFeaturesIn), minActiveInputs(minActiveInputs), fuseWithNext(false) {
+  changesGeometry = true;
+  fs = triangleSize(filterSize, dimension);
+  nFeaturesOut = fs * nFeaturesIn;
+  std::cout << dimension << "D ConvolutionalTriangularLayer side-length=" << filterSize << " " << nFeaturesIn << "x" << fs << "->" << nFeaturesOut;
+  if (filterStride > 1) std::cout << ", stride " << filterStride;
+  if (minActiveInputs != 1) std::cout << " minActiveInputs:" << minActiveInputs;
+  std::cout << std::endl;
+}
+long long ConvolutionalTriangularLayer::enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                                     SpatiallySparseBatchInterface &output, long long rowsInBound, int *d_result) {
+  requireInference(batch);
+  if (input.nFeatures != nFeaturesIn) throw ScnException("ConvolutionalTriangularLayer: wrong number of input features");
+  checkSpatial(input, inSpatialSize, "ConvolutionalTriangularLayer");
+  scn_regions_t R = {SCN_LATTICE_TRIANGULAR, dimension, inSpatialSize, outSpatialSize, filterSize, filterStride, minActiveInputs};
+  output.nFeatures = nFeaturesOut; output.spatialSize = outSpatialSize;
+  return rulechain::enqueueRegions(R, batch, input, output, rowsInBound, d_result, memStream);
+}
+void ConvolutionalTriangularLayer::finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                               SpatiallySparseBatchInterface &output, const int *h) {
+  scn_regions_t R = {SCN_LATTICE_TRIANGULAR, dimension, inSpatialSize, outSpatialSize, filterSize, filterStride, minActiveInputs};
+  finishGeometry(R, batch, input, output, nFeaturesOut, fs, h);
+}
+void ConvolutionalTriangularLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  preprocessNow(*this, batch, input, output);
+}
+void ConvolutionalTriangularLayer::forwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  if (fuseWithNext) { output.deferredFrom = &input; output.deferredCells = fs; return; }
+  output.sub->features.resize(output.nSpatialSites * output.featuresPresent.size());
+  propForwardToMatrixMultiply(input.sub->features.dPtr(), output.sub->features.dPtr(), output.rules.dPtr(), output.nSpatialSites * fs,
+                              input.featuresPresent.size(), memStream);
+}
+int ConvolutionalTriangularLayer::calculateInputSpatialSize(int outputSpatialSize) {
+  outSpatialSize = outputSpatialSize;
+  inSpatialSize = filterSize + (outputSpatialSize - 1) * filterStride;
+  std::cout << "-(C" << filterSize;
+  if (filterStride != 1) std::cout << "/" << filterStride;
+  std::cout << ")-" << inSpatialSize;
+  return inSpatialSize;
+}
+
+// ------------------------------------------------------------------ MaxPoolingLayer
+void maxPool(float *g1, float *g2, int *rules, int count, int sd, int nOut, int *d_choice, cudaMemStream &memStream) {
+  scnSafeCall(scn_maxpool_forward(g1, rules, count, sd, nOut, g2, d_choice, memStream.stream));
+}
+MaxPoolingLayer::MaxPoolingLayer(cudaMemStream &memStream, int poolSize, int poolStride, int dimension)
+    : SpatiallySparseLayer(memStream), inSpatialSize(0), outSpatialSize(0), poolSize(poolSize), poolStride(poolStride), dimension(dimension) {
+  changesGeometry = true;
+  sd = ipow(poolSize, dimension);
+  std::cout << "MaxPooling " << poolSize << " " << poolStride << std::endl;
+}
+long long MaxPoolingLayer::enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                        SpatiallySparseBatchInterface &output, long long rowsInBound, int *d_result) {
+  requireInference(batch);
+  checkSpatial(input, inSpatialSize, "MaxPoolingLayer");
+  scn_regions_t R = {SCN_LATTICE_SQUARE, dimension, inSpatialSize, outSpatialSize, poolSize, poolStride, 1};
+  output.nFeatures = input.nFeatures; output.spatialSize = outSpatialSize;
+  return rulechain::enqueueRegions(R, batch, input, output, rowsInBound, d_result, memStream);
+}
+void MaxPoolingLayer::finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                                  const int *h) {
+  scn_regions_t R = {SCN_LATTICE_SQUARE, dimension, inSpatialSize, outSpatialSize, poolSize, poolStride, 1};
+  finishGeometry(R, batch, input, output, input.nFeatures, 1, h);
+}
+void MaxPoolingLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  preprocessNow(*this, batch, input, output);
+}
+void MaxPoolingLayer::forwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  const int n = output.nSpatialSites * output.featuresPresent.size();
+  output.sub->poolingChoices.resize(n);
+  output.sub->features.resize(n);
+  maxPool(input.sub->features.dPtr(), output.sub->features.dPtr(), output.rules.dPtr(), output.nSpatialSites, sd,
+          output.featuresPresent.size(), output.sub->poolingChoices.dPtr(), memStream);
+}
+int MaxPoolingLayer::calculateInputSpatialSize(int outputSpatialSize) {
+  outSpatialSize = outputSpatialSize;
+  inSpatialSize = poolSize + (outputSpatialSize - 1) * poolStride;
+  std::cout << "-(MP" << poolSize;
+  if (poolStride != poolSize) std::cout << "/" << poolStride;
+  std::cout << ")-" << inSpatialSize;
+  return inSpatialSize;
+}
+
+// ------------------------------------------------------------------ MaxPoolingTriangularLayer
+MaxPoolingTriangularLayer::MaxPoolingTriangularLayer(cudaMemStream &memStream, int poolSize, int poolStride, int dimension)
+    : SpatiallySparseLayer(memStream), inSpatialSize(0), outSpatialSize(0), poolSize(poolSize), poolStride(poolStride), dimension(dimension) {
+  changesGeometry = true;
+  S = triangleSize(poolSize, dimension);
+  std::cout << dimension << "D MaxPoolingTriangularLayer side-length=" << poolSize << " volume=" << S << " stride " << poolStride << std::endl;
+}
+long long MaxPoolingTriangularLayer::enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                                  SpatiallySparseBatchInterface &output, long long rowsInBound, int *d_result) {
+  requireInference(batch);
+  checkSpatial(input, inSpatialSize, "MaxPoolingTriangularLayer");
+  scn_regions_t R = {SCN_LATTICE_TRIANGULAR, dimension, inSpatialSize, outSpatialSize, poolSize, poolStride, 1};
+  output.nFeatures = input.nFeatures; output.spatialSize = outSpatialSize;
+  return rulechain::enqueueRegions(R, batch, input, output, rowsInBound, d_result, memStream);
+}
+void MaxPoolingTriangularLayer::finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                            SpatiallySparseBatchInterface &output, const int *h) {
+  scn_regions_t R = {SCN_LATTICE_TRIANGULAR, dimension, inSpatialSize, outSpatialSize, poolSize, poolStride, 1};
+  finishGeometry(R, batch, input, output, input.nFeatures, 1, h);
+}
+void MaxPoolingTriangularLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  preprocessNow(*this, batch, input, output);
+}
+void MaxPoolingTriangularLayer::forwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  const int n = output.nSpatialSites * output.featuresPresent.size();
+  output.sub->poolingChoices.resize(n);
+  output.sub->features.resize(n);
+  maxPool(input.sub->features.dPtr(), output.sub->features.dPtr(), output.rules.dPtr(), output.nSpatialSites, S,
+          output.featuresPresent.size(), output.sub->poolingChoices.dPtr(), memStream);
+}
+int MaxPoolingTriangularLayer::calculateInputSpatialSize(int outputSpatialSize) {
+  outSpatialSize = outputSpatialSize;
+  inSpatialSize = poolSize + (outputSpatialSize - 1) * poolStride;
+  std::cout << "-(MP" << poolSize;
+  if (poolStride != poolSize) std::cout << "/" << poolStride;
+  std::cout << ")-" << inSpatialSize;
+  return inSpatialSize;
+}
+
+// ------------------------------------------------------------------ TerminalPoolingLayer
+TerminalPoolingLayer::TerminalPoolingLayer(cudaMemStream &memStream, int poolSize, int S)
+    : SpatiallySparseLayer(memStream), inSpatialSize(poolSize), outSpatialSize(1), poolSize(poolSize), S(S), dimension(2), widthBuilt(0) {
+  changesGeometry = true;
+  std::cout << "TerminalPooling " << poolSize << " " << S << std::endl;
+}
+// The rule width is max(1, largest site count of a sample) (TerminalPoolingLayer.cu:89-92),
+// which the host may not know yet: build with a safe width now (the forward kernel stops at
+// the first -1, so any width >= the true one gives the same means) and, if the exact width
+// turns out smaller, rebuild to it in finishRules so `rules` has the reference's shape.
+long long TerminalPoolingLayer::enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                             SpatiallySparseBatchInterface &output, long long rowsInBound, int *d_result) {
+  requireInference(batch);
+  checkSpatial(input, inSpatialSize, "TerminalPoolingLayer");
+  output.nFeatures = input.nFeatures; output.spatialSize = outSpatialSize;
+  long long cells = 1;
+  for (int a = 0; a < dimension; ++a) cells *= inSpatialSize;
+  long long width = std::max<long long>(1, std::min(cells, rowsInBound));
+  if (width * batch.batchSize > 0x7fffffffll) throw ScnException("TerminalPoolingLayer: rules too large");
+  SpatiallySparseBatchInterface *g = input.gridOwner;
+  output.gridOwner = &output;
+  output.siteKeys.resize(batch.batchSize);
+  output.sampleOffsets.resize(batch.batchSize + 1);
+  output.backgroundRows.resize(batch.batchSize);
+  output.rules.resize((int)(width * batch.batchSize));
+  size_t wsBytes = scn_terminal_rules_workspace_bytes(dimension, inSpatialSize, batch.batchSize, (int)rowsInBound);
+  void *ws = rulechain::workspace(wsBytes);
+  scnSafeCall(scn_terminal_rules_build(dimension, inSpatialSize, batch.batchSize, g->siteKeys.dPtr(), g->sampleOffsets.dPtr(),
+                                       g->backgroundRows.dPtr(), (int)rowsInBound, (int)width, output.siteKeys.dPtr(),
+                                       output.sampleOffsets.dPtr(), output.backgroundRows.dPtr(), output.rules.dPtr(), d_result, ws,
+                                       wsBytes, memStream.stream));
+  widthBuilt = (int)width;
+  return batch.batchSize;
+}
+void TerminalPoolingLayer::finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                                       const int *h) {
+  if (h[2]) throw ScnException("terminal pooling rule build reported device error bits " + std::to_string(h[2]));
+  output.nFeatures = input.nFeatures;
+  output.featuresPresent.hVector() = input.featuresPresent.hVector();
+  output.spatialSize = outSpatialSize;
+  output.nSpatialSites = batch.batchSize;
+  output.maxSitesPerSample = 1;
+  output.backpropErrors = input.backpropErrors;
+  const int exact = std::max(1, input.gridOwner->maxSitesPerSample);
+  if (exact != widthBuilt) {
+    SpatiallySparseBatchInterface *g = input.gridOwner;
+    output.rules.resize(exact * batch.batchSize);
+    size_t wsBytes = scn_terminal_rules_workspace_bytes(dimension, inSpatialSize, batch.batchSize, input.nSpatialSites);
+    void *ws = rulechain::workspace(wsBytes);
+    scnSafeCall(scn_terminal_rules_build(dimension, inSpatialSize, batch.batchSize, g->siteKeys.dPtr(), g->sampleOffsets.dPtr(),
+                                         g->backgroundRows.dPtr(), input.nSpatialSites, exact, output.siteKeys.dPtr(),
+                                         output.sampleOffsets.dPtr(), output.backgroundRows.dPtr(), output.rules.dPtr(),
+                                         rulechain::scratchResult(), ws, wsBytes, memStream.stream));
+    widthBuilt = exact;
+  }
+}
+void TerminalPoolingLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  preprocessNow(*this, batch, input, output);
+}
+void TerminalPoolingLayer::forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  const int n = output.nSpatialSites * output.featuresPresent.size();
+  output.sub->poolingChoices.resize(n);
+  output.sub->features.resize(n);
+  scnSafeCall(scn_terminal_pool_forward(input.sub->features.dPtr(), output.rules.dPtr(), output.nSpatialSites,
+                                        output.rules.size() / batch.batchSize, output.featuresPresent.size(),
+                                        output.sub->features.dPtr(), memStream.stream));
+}
+int TerminalPoolingLayer::calculateInputSpatialSize(int outputSpatialSize) {
+  if (outputSpatialSize != 1) throw ScnException("TerminalPoolingLayer must produce a 1x1 grid");
+  std::cout << "-(TP)-" << inSpatialSize;
+  return inSpatialSize;
+}
+
+// ------------------------------------------------------------------ NetworkInNetworkLayer
+NetworkInNetworkLayer::NetworkInNetworkLayer(cudaMemStream &memStream, cublasHandle_t &, int nFeaturesIn, int nFeaturesOut, float dropout,
+                                             ActivationFunction fn, float alpha)
+    : SpatiallySparseLayer(memStream), W(false, nFeaturesIn * nFeaturesOut), MW(false, 0), B(false, nFeaturesOut), MB(false, 0), fn(fn),
+      nFeaturesIn(nFeaturesIn), nFeaturesOut(nFeaturesOut), dropout(dropout), precision(SCN_PREC_AUTO), packed(nullptr), packedBytes(0),
+      packedPrecision(-100), packedFs(0) {
+  // uniform(+-sqrt(6/(nIn + nOut*alpha))) as NetworkInNetworkLayer.cu:135-137, from a fixed
+  // seed (the reference seeds from the clock); real runs load weights.
+  const float scale = std::pow(6.0f / (nFeaturesIn + nFeaturesOut * alpha), 0.5f);
+  std::mt19937 gen(1234567u + 31u * nFeaturesIn + nFeaturesOut);
+  std::uniform_real_distribution<float> u(-scale, scale);
+  for (auto &w : W.hVector()) w = u(gen);
+  B.setZero();
+  std::cout << "Learn " << nFeaturesIn << "->" << nFeaturesOut << " dropout=" << dropout << " " << sigmoidNames[fn] << std::endl;
+}
+NetworkInNetworkLayer::~NetworkInNetworkLayer() { if (packed) cudaFree(packed); }
+float *NetworkInNetworkLayer::slopes() { return nullptr; }
+void NetworkInNetworkLayer::weightsChanged() { packedPrecision = -100; }
+const void *NetworkInNetworkLayer::packedWeights(int fs, int nIn, int prec) {
+  if (prec == SCN_PREC_FP32) return nullptr;
+  size_t need = scn_conv_packed_weight_bytes(nFeaturesIn, nFeaturesOut, prec);
+  if (need == 0) return nullptr;
+  if (packed && packedPrecision == prec && packedFs == fs) return packed;
+  if (need > packedBytes) {
+    if (packed) cudaSafeCall(cudaFree(packed));
+    packed = nullptr;
+    cudaSafeCall(cudaMalloc(&packed, need));
+    packedBytes = need;
+  }
+  scnSafeCall(scn_conv_pack_weights(W.dPtr(), nFeaturesIn, nFeaturesOut, prec, packed, memStream.stream));
+  packedPrecision = prec; packedFs = fs;
+  (void)nIn;
+  return packed;
+}
+long long NetworkInNetworkLayer::enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                              SpatiallySparseBatchInterface &output, long long rowsInBound, int *) {
+  requireInference(batch);
+  if (input.nFeatures != nFeaturesIn) throw ScnException("NetworkInNetworkLayer: wrong number of input features");
+  output.nFeatures = nFeaturesOut;
+  output.spatialSize = input.spatialSize;
+  output.gridOwner = input.gridOwner; // same geometry: the grids are shared, not copied
+  return rowsInBound;
+}
+void NetworkInNetworkLayer::finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                                        const int *) {
+  requireInference(batch);
+  if (input.nFeatures != nFeaturesIn) throw ScnException("NetworkInNetworkLayer: wrong number of input features");
+  output.nFeatures = nFeaturesOut;
+  output.spatialSize = input.spatialSize;
+  output.nSpatialSites = input.nSpatialSites;
+  output.maxSitesPerSample = input.maxSitesPerSample;
+  output.gridOwner = input.gridOwner; // same geometry: the grids are shared, not copied
+  output.featuresPresent.hVector() = range(nFeaturesOut); // all features at test time
+  output.backpropErrors = true;
+}
+void NetworkInNetworkLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  enqueueRules(batch, input, output, input.nSpatialSites, nullptr);
+  finishRules(batch, input, output, nullptr);
+}
+void NetworkInNetworkLayer::forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  requireInference(batch);
+  output.sub->features.resize(output.nSpatialSites * output.featuresPresent.size());
+  const float p = 1.0f - (batch.type != RESCALEBATCH ? dropout : 0.0f); // NetworkInNetworkLayer.cu:188
+  const float *src;
+  const int *rules = nullptr;
+  int fs = 1, nIn = nFeaturesIn;
+  if (input.deferredFrom) { // fused gather
+    src = input.deferredFrom->sub->features.dPtr();
+    rules = input.rules.dPtr();
+    fs = input.deferredCells;
+    nIn = nFeaturesIn / fs;
+  } else {
+    src = input.sub->features.dPtr();
+  }
+  int prec = precision;
+  const void *pk = nullptr;
+  if (prec != SCN_PREC_FP32) {
+    pk = packedWeights(fs, nIn, prec == SCN_PREC_AUTO ? SCN_PREC_3XTF32 : prec);
+    if (!pk && prec != SCN_PREC_AUTO) throw ScnException("NetworkInNetworkLayer: layer shape has no tensor-core path; use SCN_PREC_AUTO or SCN_PREC_FP32");
+  }
+  scnSafeCall(scn_conv_nin_forward(src, rules, output.nSpatialSites, fs, nIn, W.dPtr(), pk, B.dPtr(), slopes(), nFeaturesOut, p,
+                                   (int)fn, prec, output.sub->features.dPtr(), memStream.stream));
+  multiplyAddCount += (__int128_t)output.nSpatialSites * input.featuresPresent.size() * output.featuresPresent.size();
+}
+// Weight files: raw fp32 W then B (then momentum copies) per layer (NetworkInNetworkLayer.cu:290-328).
+void NetworkInNetworkLayer::loadWeightsFromStream(std::ifstream &f, bool momentum) {
+  std::vector<float> &w = W.hVector(), &b = B.hVector();
+  f.read((char *)w.data(), sizeof(float) * w.size());
+  f.read((char *)b.data(), sizeof(float) * b.size());
+  if (momentum) f.seekg((std::streamoff)(sizeof(float) * (w.size() + b.size())), std::ios::cur);
+  if (!f) throw ScnException("weight file ends early");
+  weightsChanged();
+}
+void NetworkInNetworkLayer::putWeightsToStream(std::ofstream &f, bool momentum) {
+  const bool wOn = W.onGPU, bOn = B.onGPU;
+  std::vector<float> &w = W.hVector(), &b = B.hVector();
+  f.write((char *)w.data(), sizeof(float) * w.size());
+  f.write((char *)b.data(), sizeof(float) * b.size());
+  if (momentum) { std::vector<float> z(w.size() + b.size(), 0.f); f.write((char *)z.data(), sizeof(float) * z.size()); }
+  if (wOn) W.copyToGPU();
+  if (bOn) B.copyToGPU();
+}
+int NetworkInNetworkLayer::calculateInputSpatialSize(int outputSpatialSize) { return outputSpatialSize; }
+void replicateArray(float *src, float *dst, int nRows, int nColumns, cudaMemStream &memStream) {
+  for (int r = 0; r < nRows; ++r)
+    cudaSafeCall(cudaMemcpyAsync(dst + (size_t)r * nColumns, src, sizeof(float) * nColumns, cudaMemcpyDeviceToDevice, memStream.stream));
+}
+
+// ------------------------------------------------------------------ NetworkInNetworkPReLULayer
+NetworkInNetworkPReLULayer::NetworkInNetworkPReLULayer(cudaMemStream &memStream, cublasHandle_t &h, int nFeaturesIn, int nFeaturesOut,
+                                                       float dropout, float alpha)
+    : NetworkInNetworkLayer(memStream, h, nFeaturesIn, nFeaturesOut, dropout, PRELU, alpha), PReLU(false, nFeaturesOut), MPReLU(false, 0) {
+  PReLU.setConstant(0.25f);
+}
+float *NetworkInNetworkPReLULayer::slopes() { return PReLU.dPtr(); }
+void NetworkInNetworkPReLULayer::loadWeightsFromStream(std::ifstream &f, bool momentum) {
+  std::vector<float> &w = W.hVector(), &b = B.hVector(), &s = PReLU.hVector();
+  f.read((char *)w.data(), sizeof(float) * w.size());
+  f.read((char *)b.data(), sizeof(float) * b.size());
+  f.read((char *)s.data(), sizeof(float) * s.size());
+  if (momentum) f.seekg((std::streamoff)(sizeof(float) * (w.size() + b.size() + s.size())), std::ios::cur);
+  if (!f) throw ScnException("weight file ends early");
+  weightsChanged();
+}
+void NetworkInNetworkPReLULayer::putWeightsToStream(std::ofstream &f, bool momentum) {
+  std::vector<float> &w = W.hVector(), &b = B.hVector(), &s = PReLU.hVector();
+  f.write((char *)w.data(), sizeof(float) * w.size());
+  f.write((char *)b.data(), sizeof(float) * b.size());
+  f.write((char *)s.data(), sizeof(float) * s.size());
+  if (momentum) { std::vector<float> z(w.size() + b.size() + s.size(), 0.f); f.write((char *)z.data(), sizeof(float) * z.size()); }
+}
+
+// ------------------------------------------------------------------ applySigmoid / SoftmaxClassifier
+void applySigmoid(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, ActivationFunction fn, cudaMemStream &memStream) {
+  if (fn == PRELU) throw ScnException("applySigmoid: PReLU needs its layer's slopes");
+  scnSafeCall(scn_activation_forward(input.sub->features.dPtr(), output.sub->features.dPtr(), output.nSpatialSites,
+                                     output.featuresPresent.size(), (int)fn, nullptr, memStream.stream));
+}
+
+// SoftmaxClassifier.cu:16-58 without the training branch: probabilities and the nTop
+// predictions come back in one staged copy; NLL and mistakes are scored on the host.
+void SoftmaxClassifier(SpatiallySparseBatchInterface &input, SpatiallySparseBatch &batch, int nTop, cudaMemStream &memStream) {
+  requireInference(batch);
+  if (batch.batchSize != input.nSpatialSites) throw ScnException("SoftmaxClassifier: the top layer must hold one row per sample");
+  const int n = batch.batchSize, C = input.nFeatures;
+  static thread_local vectorCUDA<int> top;
+  top.resize(n * nTop);
+  scnSafeCall(scn_top_indices(input.sub->features.dPtr(), n, C, nTop, top.dPtr(), memStream.stream));
+  const size_t pb = sizeof(float) * (size_t)n * C, tb = sizeof(int) * (size_t)n * nTop;
+  char *stage = (char *)memStream.staging(pb + tb);
+  cudaSafeCall(cudaMemcpyAsync(stage, input.sub->features.dPtr(), pb, cudaMemcpyDeviceToHost, memStream.stream));
+  cudaSafeCall(cudaMemcpyAsync(stage + pb, top.dPtr(), tb, cudaMemcpyDeviceToHost, memStream.stream));
+  cudaSafeCall(cudaStreamSynchronize(memStream.stream));
+  const float *probs = (const float *)stage;
+  const int *pred = (const int *)(stage + pb);
+  for (int i = 0; i < n; ++i) {
+    batch.probabilities.emplace_back(probs + (size_t)i * C, probs + (size_t)(i + 1) * C);
+    batch.predictions.emplace_back(pred + (size_t)i * nTop, pred + (size_t)(i + 1) * nTop);
+  }
+  if (batch.type != UNLABELEDBATCH && batch.labels.size() == (unsigned)n) {
+    std::vector<int> &labels = batch.labels.hVector();
+    batch.mistakes += n;
+    for (int i = 0; i < n; ++i) {
+      batch.negativeLogLikelihood -= std::log(std::max(batch.probabilities[i][labels[i]], 1.0e-15f));
+      for (int j = 0; j < nTop; ++j)
+        if (batch.predictions[i][j] == labels[i]) batch.mistakes--;
+    }
+  }
+}

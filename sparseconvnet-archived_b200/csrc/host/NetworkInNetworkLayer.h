@@ -1,0 +1,42 @@
+// 1x1 convolution: out = act(p * X W + p * B) at test time (NetworkInNetworkLayer.h:6-45).
+// Behind a fused ConvolutionalLayer it is the whole convolution: one kernel gathers the rows
+// named by the rules, contracts them with W and applies bias, dropout scaling and activation.
+#pragma once
+#include <fstream>
+#include "SpatiallySparseLayer.h"
+
+class NetworkInNetworkLayer : public SpatiallySparseLayer {
+public:
+  vectorCUDA<float> W;  // [nFeaturesIn x nFeaturesOut], row-major
+  vectorCUDA<float> MW; // momentum (kept for weight-file compatibility; unused)
+  vectorCUDA<float> B;  // [nFeaturesOut]
+  vectorCUDA<float> MB;
+  ActivationFunction fn;
+  int nFeaturesIn, nFeaturesOut;
+  float dropout;
+  int precision; // scn_precision used by forwards(); SCN_PREC_AUTO by default
+  NetworkInNetworkLayer(cudaMemStream &memStream, cublasHandle_t &cublasHandle, int nFeaturesIn, int nFeaturesOut,
+                        float dropout = 0, ActivationFunction fn = NOSIGMOID, float alpha = 1);
+  ~NetworkInNetworkLayer();
+  void preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
+  void forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
+  void loadWeightsFromStream(std::ifstream &f, bool momentum);
+  void putWeightsToStream(std::ofstream &f, bool momentum);
+  int calculateInputSpatialSize(int outputSpatialSize);
+  long long enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                         long long rowsInBound, int *d_result);
+  void finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                   const int *h_result);
+  // Call after writing W directly (e.g. W.hVector()[i] = ...): drops the packed copy the
+  // tensor-core kernel reads.
+  void weightsChanged();
+
+protected:
+  virtual float *slopes(); // per-channel PReLU slopes, or nullptr
+  void *packed;            // W repacked for `packedPrecision`
+  size_t packedBytes;
+  int packedPrecision;
+  int packedFs;
+  const void *packedWeights(int fs, int nIn, int prec);
+};
+void replicateArray(float *src, float *dst, int nRows, int nColumns, cudaMemStream &memStream);

@@ -1,0 +1,86 @@
+#include "RuleChain.h"
+#include <climits>
+#include <mutex>
+
+namespace rulechain {
+namespace {
+struct PerDevice { void *ws = nullptr; size_t bytes = 0; int *res = nullptr; };
+PerDevice g_dev[64];
+std::mutex g_mu;
+PerDevice &cur() {
+  int d = 0;
+  cudaSafeCall(cudaGetDevice(&d));
+  return g_dev[d & 63];
+}
+} // namespace
+
+void *workspace(size_t bytes) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  PerDevice &p = cur();
+  if (bytes > p.bytes) {
+    if (p.ws) { cudaSafeCall(cudaDeviceSynchronize()); cudaSafeCall(cudaFree(p.ws)); p.ws = nullptr; p.bytes = 0; }
+    size_t want = bytes + bytes / 4;
+    cudaSafeCall(cudaMalloc(&p.ws, want));
+    p.bytes = want;
+  }
+  return p.ws;
+}
+int *scratchResult() {
+  std::lock_guard<std::mutex> lk(g_mu);
+  PerDevice &p = cur();
+  if (!p.res) cudaSafeCall(cudaMalloc((void **)&p.res, 4 * sizeof(int)));
+  return p.res;
+}
+
+long long enqueueRegions(const scn_regions_t &R, SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                         SpatiallySparseBatchInterface &output, long long rowsInBound, int *d_result, cudaMemStream &ms) {
+  const int sd = scn_regions_cells(&R);
+  if (sd < 0) throw ScnException(std::string("rule build: ") + scn_last_error());
+  long long T = 1, full = 1;
+  if (R.minActive != -1) for (int a = 0; a < R.dim; ++a) T *= (R.size + R.stride - 1) / R.stride;
+  if (R.lattice == SCN_LATTICE_SQUARE) for (int a = 0; a < R.dim; ++a) full *= R.nOut;
+  else full = triangleSize(R.nOut, R.dim);
+  long long bound = std::min(rowsInBound * T, (long long)batch.batchSize * full) + batch.batchSize;
+  if (bound * sd > INT_MAX || rowsInBound > INT_MAX) throw ScnException("rule build: more than 2^31 rule cells in one batch; use smaller batches");
+  SpatiallySparseBatchInterface *g = input.gridOwner;
+  output.gridOwner = &output;
+  output.siteKeys.resize((int)bound);
+  output.sampleOffsets.resize(batch.batchSize + 1);
+  output.backgroundRows.resize(batch.batchSize);
+  output.rules.resize((int)(bound * sd));
+  size_t wsBytes = scn_rules_workspace_bytes(&R, batch.batchSize, (int)rowsInBound);
+  void *ws = workspace(wsBytes);
+  scnSafeCall(scn_rules_build(&R, batch.batchSize, g->siteKeys.dPtr(), g->sampleOffsets.dPtr(), g->backgroundRows.dPtr(),
+                              (int)rowsInBound, output.siteKeys.dPtr(), output.sampleOffsets.dPtr(), output.backgroundRows.dPtr(),
+                              output.rules.dPtr(), (int)bound, d_result, ws, wsBytes, ms.stream));
+  return bound;
+}
+
+void finishRegions(const scn_regions_t &R, SpatiallySparseBatchInterface &output, const int *h) {
+  if (h[2]) throw ScnException("rule build reported device error bits " + std::to_string(h[2]) +
+                               " (1 capacity, 2 key outside the grid, 4 duplicate key)");
+  const int sd = scn_regions_cells(&R);
+  output.nSpatialSites = h[0];
+  output.maxSitesPerSample = h[3];
+  output.siteKeys.resize(h[0]);
+  output.rules.resize(h[0] * sd);
+}
+
+void preprocessNow(SpatiallySparseLayer &layer, SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                   SpatiallySparseBatchInterface &output) {
+  int *d_res = scratchResult();
+  layer.enqueueRules(batch, input, output, input.nSpatialSites, d_res);
+  int h[4] = {0, 0, 0, 0};
+  if (layer.changesGeometry) {
+    cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(h), cudaMemcpyDeviceToHost, layer.memStream.stream));
+    cudaSafeCall(cudaStreamSynchronize(layer.memStream.stream));
+  }
+  layer.finishRules(batch, input, output, h);
+}
+
+void convolutionFeaturesPresent(std::vector<int> &src, std::vector<int> &dst, int nf, int nfp, int nCopies) {
+  dst.resize((size_t)nfp * nCopies);
+  for (int c = 0; c < nCopies; ++c)
+    for (int i = 0; i < nfp; ++i) dst[(size_t)c * nfp + i] = src[i] + nf * c;
+}
+} // namespace rulechain

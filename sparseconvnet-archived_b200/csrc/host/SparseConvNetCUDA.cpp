@@ -1,0 +1,278 @@
+#include "SparseConvNetCUDA.h"
+#include <chrono>
+#include <cmath>
+#include "BatchProducer.h"
+#include "ConvolutionalLayer.h"
+#include "ConvolutionalTriangularLayer.h"
+#include "MaxPoolingLayer.h"
+#include "MaxPoolingTriangularLayer.h"
+#include "NetworkInNetworkLayer.h"
+#include "NetworkInNetworkPReLULayer.h"
+#include "SoftmaxClassifier.h"
+#include "TerminalPoolingLayer.h"
+
+void SparseConvNetCUDA::init(int nInputFeatures_, int nClasses_) {
+  if (nBatchProducerThreads < 1 || nBatchProducerThreads > N_MAX_BATCH_PRODUCER_THREADS) throw ScnException("nBatchProducerThreads must be 1..20");
+  std::cout << "Sparse CNN - dimension=" << dimension << " nInputFeatures=" << nInputFeatures_ << " nClasses=" << nClasses_ << std::endl;
+  nOutputFeatures = nInputFeatures_;
+  timing = false;
+  inputSpatialSize = 0;
+  cublasHandle = nullptr;
+  batchPool.reserve(nBatchProducerThreads); // interfaces hold pointers into each other: no reallocation later
+  for (int c = 0; c < nBatchProducerThreads; ++c) {
+    initialSubInterfaces.push_back(new SpatiallySparseBatchSubInterface());
+    batchPool.emplace_back(initialSubInterfaces.back());
+  }
+}
+SparseConvNetCUDA::SparseConvNetCUDA(int dimension, int nInputFeatures, int nClasses, int pciBusID, int nTop, int nBatchProducerThreads)
+    : dimension(dimension), nClasses(nClasses), nTop(nTop), nInputFeatures(nInputFeatures), deviceID(initializeGPU(pciBusID)),
+      nBatchProducerThreads(nBatchProducerThreads), memStream() {
+  init(nInputFeatures, nClasses);
+}
+SparseConvNetCUDA::SparseConvNetCUDA(int dimension, int nInputFeatures, int nClasses, cudaStream_t stream, int nTop, int nBatchProducerThreads)
+    : dimension(dimension), nClasses(nClasses), nTop(nTop), nInputFeatures(nInputFeatures), deviceID(0),
+      nBatchProducerThreads(nBatchProducerThreads), memStream(stream) {
+  cudaSafeCall(cudaGetDevice(&deviceID));
+  if (!scn_device_supported()) throw ScnException("this library runs on compute capability 10.x (B200) devices only");
+  init(nInputFeatures, nClasses);
+}
+SparseConvNetCUDA::~SparseConvNetCUDA() {
+  cudaStreamSynchronize(memStream.stream);
+  for (auto e : events) cudaEventDestroy(e);
+  for (auto p : layers) delete p;
+  batchPool.clear();
+  for (auto p : initialSubInterfaces) delete p;
+  for (auto p : sharedSubInterfaces) delete p;
+}
+
+// Widths are rounded to multiples of 32 and dropout is re-quantised the same way
+// (SparseConvNetCUDA.cu:50-70): existing weight files assume these sizes.
+void SparseConvNetCUDA::addLearntLayer(int nFeatures, ActivationFunction activationFn, float dropout, float alpha) {
+  if (activationFn != SOFTMAX) nFeatures = std::max(KERNELBLOCKSIZE, intRound(nFeatures, KERNELBLOCKSIZE));
+  if (dropout > 0) dropout = 1 - (intRound(nFeatures * (1 - dropout), KERNELBLOCKSIZE) + 0.01f) * 1.0f / nFeatures;
+  if (dropout < 0) dropout = 0;
+  std::cout << layers.size() << ":";
+  if (activationFn == PRELU)
+    layers.push_back(new NetworkInNetworkPReLULayer(memStream, cublasHandle, nOutputFeatures, nFeatures, dropout, alpha));
+  else
+    layers.push_back(new NetworkInNetworkLayer(memStream, cublasHandle, nOutputFeatures, nFeatures, dropout, activationFn, alpha));
+  nOutputFeatures = nFeatures;
+}
+void SparseConvNetCUDA::addNetworkInNetworkLayer(int nFeatures, ActivationFunction activationFn, float dropout) {
+  addLearntLayer(nFeatures, activationFn, dropout, 1.0f);
+}
+void SparseConvNetCUDA::addConvolutionalLayer(int nFeatures, int filterSize, int filterStride, ActivationFunction activationFn, float dropout,
+                                              int minActiveInputs, float poolingToFollow) {
+  if (filterSize > 1) {
+    std::cout << layers.size() << ":";
+    ConvolutionalLayer *c = new ConvolutionalLayer(memStream, filterSize, filterStride, dimension, nOutputFeatures, minActiveInputs);
+    c->fuseWithNext = true; // the learnt layer added next runs gather + GEMM + epilogue as one kernel
+    layers.push_back(c);
+    nOutputFeatures *= ipow(filterSize, dimension);
+  }
+  addLearntLayer(nFeatures, activationFn, dropout, std::pow(filterSize * 1.0f / filterStride / poolingToFollow, 2.0f));
+}
+void SparseConvNetCUDA::addLeNetLayerMP(int nFeatures, int filterSize, int filterStride, int poolSize, int poolStride,
+                                        ActivationFunction activationFn, float dropout, int minActiveInputs) {
+  addConvolutionalLayer(nFeatures, filterSize, filterStride, activationFn, dropout, minActiveInputs, poolSize);
+  if (poolSize > 1) {
+    std::cout << layers.size() << ":";
+    layers.push_back(new MaxPoolingLayer(memStream, poolSize, poolStride, dimension));
+  }
+}
+void SparseConvNetCUDA::addTriangularConvolutionalLayer(int nFeatures, int filterSize, int filterStride, ActivationFunction activationFn,
+                                                        float dropout, int minActiveInputs, float poolingToFollow) {
+  if (filterSize > 1) {
+    std::cout << layers.size() << ":";
+    ConvolutionalTriangularLayer *c =
+        new ConvolutionalTriangularLayer(memStream, filterSize, filterStride, dimension, nOutputFeatures, minActiveInputs);
+    c->fuseWithNext = true;
+    layers.push_back(c);
+    nOutputFeatures *= triangleSize(filterSize, dimension);
+  }
+  addLearntLayer(nFeatures, activationFn, dropout, std::pow(filterSize * 1.0f / filterStride / poolingToFollow, 2.0f));
+}
+// The reference passes poolSize where the callee expects minActiveInputs and
+// minActiveInputs where it expects poolingToFollow (SparseConvNetCUDA.cu:183-185 against
+// 165-168).  Networks trained with it depend on that, so the call is reproduced as is: with
+// poolSize 2 the convolution keeps only sites with at least two active inputs.
+void SparseConvNetCUDA::addTriangularLeNetLayerMP(int nFeatures, int filterSize, int filterStride, int poolSize, int poolStride,
+                                                  ActivationFunction activationFn, float dropout, int minActiveInputs) {
+  addTriangularConvolutionalLayer(nFeatures, filterSize, filterStride, activationFn, dropout, poolSize, (float)minActiveInputs);
+  if (poolSize > 1) {
+    std::cout << layers.size() << ":";
+    layers.push_back(new MaxPoolingTriangularLayer(memStream, poolSize, poolStride, dimension));
+  }
+}
+void SparseConvNetCUDA::addTerminalPoolingLayer(int poolSize, int S) {
+  std::cout << layers.size() << ":";
+  TerminalPoolingLayer *t = new TerminalPoolingLayer(memStream, poolSize, S);
+  t->dimension = dimension;
+  layers.push_back(t);
+}
+void SparseConvNetCUDA::addSoftmaxLayer() {
+  addLearntLayer(nClasses, SOFTMAX, 0.0f, 1);
+  inputSpatialSize = 1;
+  std::cout << "Spatially sparse CNN with layer sizes: " << inputSpatialSize;
+  for (int i = (int)layers.size() - 1; i >= 0; --i) inputSpatialSize = layers[i]->calculateInputSpatialSize(inputSpatialSize);
+  std::cout << std::endl << "Input-field dimensions = " << inputSpatialSize;
+  for (int i = 1; i < dimension; ++i) std::cout << "x" << inputSpatialSize;
+  std::cout << std::endl;
+}
+
+void SparseConvNetCUDA::prepareBatch(SpatiallySparseBatch &batch) {
+  if (batch.interfaces.size() == layers.size() + 1) return;
+  batch.interfaces.reserve(layers.size() + 1); // before any pointer into the vector exists
+  while (sharedSubInterfaces.size() < layers.size()) sharedSubInterfaces.push_back(new SpatiallySparseBatchSubInterface());
+  // interfaces behind layer i share one sub-interface across the pool: one batch in flight
+  // on the device at a time (BatchProducer.cu:28-33)
+  while (batch.interfaces.size() < layers.size() + 1) batch.interfaces.emplace_back(sharedSubInterfaces[batch.interfaces.size() - 1]);
+}
+
+void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
+  prepareBatch(batch);
+  const int nL = (int)layers.size();
+  chainResults.resize(4 * nL + 4);
+  int *d_res = chainResults.dPtr();
+  long long bound = batch.interfaces[0].nSpatialSites;
+  if (timing) cudaSafeCall(cudaEventRecord(events[nL + 1], memStream.stream));
+  for (int i = 0; i < nL; ++i)
+    bound = layers[i]->enqueueRules(batch, batch.interfaces[i], batch.interfaces[i + 1], bound, d_res + 4 * i);
+  if (timing) cudaSafeCall(cudaEventRecord(events[nL + 2], memStream.stream));
+  int *h = (int *)memStream.staging(sizeof(int) * 4 * nL);
+  cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, memStream.stream));
+  cudaSafeCall(cudaStreamSynchronize(memStream.stream)); // the one host wait of the rule chain
+  std::vector<int> counts(h, h + 4 * nL); // staging is reused below
+  for (int i = 0; i < nL; ++i) layers[i]->finishRules(batch, batch.interfaces[i], batch.interfaces[i + 1], counts.data() + 4 * i);
+}
+
+void SparseConvNetCUDA::forwardLayers(SpatiallySparseBatch &batch) {
+  for (size_t i = 0; i < layers.size(); ++i) {
+    if (timing) cudaSafeCall(cudaEventRecord(events[i], memStream.stream));
+    batch.interfaces[i + 1].sub->reset();
+    batch.interfaces[i + 1].deferredFrom = nullptr;
+    layers[i]->forwards(batch, batch.interfaces[i], batch.interfaces[i + 1]);
+  }
+  if (timing) cudaSafeCall(cudaEventRecord(events[layers.size()], memStream.stream));
+}
+void SparseConvNetCUDA::enableTiming(bool on) {
+  timing = on;
+  while (on && events.size() < layers.size() + 3) {
+    cudaEvent_t e;
+    cudaSafeCall(cudaEventCreate(&e));
+    events.push_back(e);
+  }
+}
+std::vector<float> SparseConvNetCUDA::layerTimes() {
+  std::vector<float> ms(layers.size() + 1, 0.f);
+  if (!timing) return ms;
+  cudaSafeCall(cudaStreamSynchronize(memStream.stream));
+  const size_t nL = layers.size();
+  for (size_t i = 0; i < nL; ++i) cudaSafeCall(cudaEventElapsedTime(&ms[i], events[i], events[i + 1]));
+  cudaSafeCall(cudaEventElapsedTime(&ms[nL], events[nL + 1], events[nL + 2]));
+  return ms;
+}
+
+// SparseConvNetCUDA.cu:227-271 without the training and rescaling branches.
+void SparseConvNetCUDA::processBatch(SpatiallySparseBatch &batch, float, float, std::ofstream &f, std::ofstream &g) {
+  if (batch.type == TRAINBATCH) throw ScnException("processBatch: TRAINBATCH is not supported by this inference library");
+  forwardLayers(batch);
+  SoftmaxClassifier(batch.interfaces.back(), batch, nTop, memStream);
+  if (f)
+    for (auto &p : batch.predictions) {
+      for (size_t k = 0; k < p.size(); ++k) f << (k ? " " : "") << p[k];
+      f << std::endl;
+    }
+  if (g)
+    for (auto &p : batch.probabilities) {
+      for (size_t k = 0; k < p.size(); ++k) g << (k ? " " : "") << p[k];
+      g << std::endl;
+    }
+}
+
+// One pass over a dataset (SparseConvNetCUDA.cu:272-326): returns the error rate and prints
+// the reference's summary line.
+float SparseConvNetCUDA::processDataset(SpatiallySparseDataset &dataset, int batchSize, float learningRate, float momentum) {
+  if (dataset.pictures.empty()) throw ScnException("processDataset: empty dataset");
+  if (dataset.type == TRAINBATCH) throw ScnException("processDataset: TRAINBATCH is not supported by this inference library");
+  float errorRate = 0, nll = 0;
+  multiplyAddCount = 0;
+  auto start = std::chrono::system_clock::now();
+  std::ofstream f, g;
+  BatchProducer bp(*this, dataset, inputSpatialSize, batchSize);
+  if (dataset.type == UNLABELEDBATCH) {
+    f.open("unlabelledData.predictions");
+    g.open("unlabelledData.probabilities");
+  }
+  while (SpatiallySparseBatch *batch = bp.nextBatch()) {
+    processBatch(*batch, learningRate, momentum, f, g);
+    errorRate += batch->mistakes * 1.0 / dataset.pictures.size();
+    nll += batch->negativeLogLikelihood * 1.0 / dataset.pictures.size();
+  }
+  auto end = std::chrono::system_clock::now();
+  double diff = std::chrono::duration_cast<std::chrono::nanoseconds>(end - start).count();
+  if (dataset.type != UNLABELEDBATCH)
+    std::cout << dataset.name << " Mistakes:" << 100.0 * errorRate << "% NLL:" << nll
+              << " MegaMultiplyAdds/sample:" << std::round((double)multiplyAddCount / dataset.pictures.size() / 1000000)
+              << " time:" << diff / 1000000000L << "s GigaMultiplyAdds/s:" << std::round((double)multiplyAddCount / diff)
+              << " rate:" << std::round(dataset.pictures.size() * 1000000000.0f / diff) << "/s" << std::endl;
+  return errorRate;
+}
+
+// Repeated test passes with averaged probabilities (SparseConvNetCUDA.cu:327-405): prints the
+// cumulative error after each repetition and optionally writes predictions / a confusion matrix.
+void SparseConvNetCUDA::processDatasetRepeatTest(SpatiallySparseDataset &dataset, int batchSize, int nReps, std::string predictionsFilename,
+                                                 std::string confusionMatrixFilename) {
+  const size_t n = dataset.pictures.size();
+  std::vector<std::vector<float>> probs(n, std::vector<float>(dataset.nClasses, 0.f));
+  std::ofstream nof, nog;
+  for (int rep = 1; rep <= nReps; ++rep) {
+    BatchProducer bp(*this, dataset, inputSpatialSize, batchSize);
+    size_t at = 0;
+    while (SpatiallySparseBatch *batch = bp.nextBatch()) {
+      processBatch(*batch, 0, 0, nof, nog);
+      for (int i = 0; i < batch->batchSize; ++i, ++at)
+        for (int k = 0; k < dataset.nClasses; ++k) probs[at][k] += batch->probabilities[i][k];
+    }
+    int mistakes = 0;
+    double nll = 0;
+    std::vector<std::vector<int>> confusion(dataset.nClasses, std::vector<int>(dataset.nClasses, 0));
+    std::ofstream pf;
+    if (!predictionsFilename.empty()) pf.open(predictionsFilename.c_str());
+    for (size_t i = 0; i < n; ++i) {
+      std::vector<int> pred = vectorTopIndices(probs[i], nTop);
+      const int label = dataset.pictures[i]->label;
+      bool hit = false;
+      for (int j = 0; j < nTop; ++j) hit = hit || pred[j] == label;
+      if (label >= 0) {
+        mistakes += !hit;
+        nll -= std::log(std::max(probs[i][label] / rep, 1.0e-15f));
+        confusion[label][pred[0]]++;
+      }
+      if (pf) { for (int j = 0; j < nTop; ++j) pf << (j ? " " : "") << pred[j]; pf << std::endl; }
+    }
+    std::cout << dataset.name << " rep " << rep << "/" << nReps << " Mistakes: " << 100.0 * mistakes / n << "% NLL " << nll / n << std::endl;
+    if (!confusionMatrixFilename.empty()) {
+      std::ofstream cm(confusionMatrixFilename.c_str());
+      for (auto &row : confusion) { for (size_t k = 0; k < row.size(); ++k) cm << (k ? " " : "") << row[k]; cm << std::endl; }
+    }
+  }
+}
+
+// <base>_epoch-<n>.cnn: every layer's weights in order, then the input normalising constants
+// (SparseConvNetCUDA.cu:406-442).
+void SparseConvNetCUDA::loadWeights(std::string baseName, int epoch, bool momentum, int firstNlayers) {
+  std::string filename = baseName + "_epoch-" + std::to_string(epoch) + ".cnn";
+  std::ifstream f(filename.c_str(), std::ios::in | std::ios::binary);
+  if (!f) throw ScnException("Cannot find " + filename);
+  std::cout << "Loading network parameters from " << filename << std::endl;
+  for (int i = 0; i < std::min((int)layers.size(), firstNlayers); ++i) layers[i]->loadWeightsFromStream(f, momentum);
+  if (!inputNormalizingConstants.empty()) f.read((char *)inputNormalizingConstants.data(), sizeof(float) * inputNormalizingConstants.size());
+}
+void SparseConvNetCUDA::saveWeights(std::string baseName, int epoch, bool momentum) {
+  std::string filename = baseName + "_epoch-" + std::to_string(epoch) + ".cnn";
+  std::ofstream f(filename.c_str(), std::ios::binary);
+  if (!f) throw ScnException("Cannot write " + filename);
+  for (auto l : layers) l->putWeightsToStream(f, momentum);
+  if (!inputNormalizingConstants.empty()) f.write((char *)inputNormalizingConstants.data(), sizeof(float) * inputNormalizingConstants.size());
+}

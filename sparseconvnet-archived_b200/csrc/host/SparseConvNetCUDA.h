@@ -1,0 +1,66 @@
+// The network runtime (SparseConvNetCUDA.h:25-114): the layer list, the builder methods with
+// the reference's rounding rules, the per-batch forward, dataset loops and weight files.
+#pragma once
+#include <fstream>
+#include <iostream>
+#include <mutex>
+#include <string>
+#include <vector>
+#include "SpatiallySparseBatch.h"
+#include "SpatiallySparseDataset.h"
+#include "SpatiallySparseLayer.h"
+#define N_MAX_BATCH_PRODUCER_THREADS 20
+
+class SparseConvNetCUDA {
+public:
+  std::vector<SpatiallySparseLayer *> layers; // owned
+  std::vector<float> inputNormalizingConstants;
+  int dimension, nClasses, nTop, inputSpatialSize, nInputFeatures, nOutputFeatures, deviceID, nBatchProducerThreads;
+  cudaMemStream memStream;
+  std::vector<SpatiallySparseBatch> batchPool;
+  std::vector<SpatiallySparseBatchSubInterface *> initialSubInterfaces;
+  std::vector<SpatiallySparseBatchSubInterface *> sharedSubInterfaces;
+  cublasHandle_t cublasHandle; // unused, kept for the layer constructors' signatures
+
+  SparseConvNetCUDA(int dimension, int nInputFeatures, int nClasses, int pciBusID = -1, int nTop = 1, int nBatchProducerThreads = 10);
+  // Same, enqueueing on a stream the caller owns (no reference counterpart).
+  SparseConvNetCUDA(int dimension, int nInputFeatures, int nClasses, cudaStream_t stream, int nTop, int nBatchProducerThreads);
+  ~SparseConvNetCUDA();
+  void processBatch(SpatiallySparseBatch &batch, float learningRate, float momentum, std::ofstream &f, std::ofstream &g);
+  void addLearntLayer(int nFeatures, ActivationFunction activationFn = RELU, float dropout = 0.0f, float alpha = 1.0f);
+  void addNetworkInNetworkLayer(int nFeatures, ActivationFunction activationFn = RELU, float dropout = 0.0f);
+  void addConvolutionalLayer(int nFeatures, int filterSize, int filterStride, ActivationFunction activationFn = RELU, float dropout = 0.0f,
+                             int minActiveInputs = 1, float poolingToFollow = 1.0f);
+  void addLeNetLayerMP(int nFeatures, int filterSize, int filterStride, int poolSize, int poolStride, ActivationFunction activationFn = RELU,
+                       float dropout = 0.0f, int minActiveInputs = 1);
+  void addTriangularConvolutionalLayer(int nFeatures, int filterSize, int filterStride, ActivationFunction activationFn = RELU,
+                                       float dropout = 0.0f, int minActiveInputs = 1, float poolingToFollow = 1.0f);
+  void addTriangularLeNetLayerMP(int nFeatures, int filterSize, int filterStride, int poolSize, int poolStride,
+                                 ActivationFunction activationFn = RELU, float dropout = 0.0f, int minActiveInputs = 1);
+  void addSoftmaxLayer();
+  void addTerminalPoolingLayer(int poolSize, int S);
+  float processDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0, float momentum = 0.99);
+  void processDatasetRepeatTest(SpatiallySparseDataset &dataset, int batchSize = 100, int nReps = 12,
+                                std::string predictionsFilename = "", std::string confusionMatrixFilename = "");
+  void loadWeights(std::string baseName, int epoch, bool momentum, int firstNlayers = 1000000);
+  void saveWeights(std::string baseName, int epoch, bool momentum);
+
+  // ---- additions (no reference counterpart)
+  // Run every layer's rule construction on the device for a batch whose interface 0 holds
+  // the input grids in device form, with a single read-back of all per-layer counts.
+  void preprocessBatchOnDevice(SpatiallySparseBatch &batch);
+  // Grow batch.interfaces to layers.size()+1.
+  void prepareBatch(SpatiallySparseBatch &batch);
+  // Forward of all layers without the classifier read-back.
+  void forwardLayers(SpatiallySparseBatch &batch);
+  // CUDA-event timing per layer (off by default).  layerTimes() waits for the stream and
+  // returns layers.size()+1 values in ms: each layer's forwards(), then the rule chain.
+  void enableTiming(bool on);
+  std::vector<float> layerTimes();
+
+private:
+  void init(int nInputFeatures, int nClasses);
+  vectorCUDA<int> chainResults; // 4 ints per layer
+  bool timing;
+  std::vector<cudaEvent_t> events; // layers.size()+1 layer boundaries, then rule chain begin/end
+};

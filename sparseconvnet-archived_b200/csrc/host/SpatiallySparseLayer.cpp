@@ -1,0 +1,15 @@
+#include "SpatiallySparseLayer.h"
+
+SpatiallySparseLayer::SpatiallySparseLayer(cudaMemStream &memStream) : memStream(memStream), changesGeometry(false) {}
+SpatiallySparseLayer::~SpatiallySparseLayer() {}
+void SpatiallySparseLayer::scaleWeights(SpatiallySparseBatchInterface &, SpatiallySparseBatchInterface &, float &, bool) {
+  throw ScnException("scaleWeights: weight rescaling belongs to training and is not part of this inference library");
+}
+void SpatiallySparseLayer::backwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &, SpatiallySparseBatchInterface &, float, float) {
+  throw ScnException("backwards: this is an inference library");
+}
+void SpatiallySparseLayer::loadWeightsFromStream(std::ifstream &, bool) {}
+void SpatiallySparseLayer::putWeightsToStream(std::ofstream &, bool) {}
+long long SpatiallySparseLayer::enqueueRules(SpatiallySparseBatch &, SpatiallySparseBatchInterface &, SpatiallySparseBatchInterface &,
+                                             long long rowsInBound, int *) { return rowsInBound; }
+void SpatiallySparseLayer::finishRules(SpatiallySparseBatch &, SpatiallySparseBatchInterface &, SpatiallySparseBatchInterface &, const int *) {}

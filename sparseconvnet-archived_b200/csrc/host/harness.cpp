@@ -1,0 +1,325 @@
+// extern "C" entry points over the C++ classes (include/scn_b200_net.h).
+#include <cstring>
+#include <memory>
+#include <sstream>
+#include "BatchProducer.h"
+#include "ConvolutionalLayer.h"
+#include "ConvolutionalTriangularLayer.h"
+#include "MaxPoolingLayer.h"
+#include "MaxPoolingTriangularLayer.h"
+#include "NetworkInNetworkLayer.h"
+#include "NetworkInNetworkPReLULayer.h"
+#include "SoftmaxClassifier.h"
+#include "SparseConvNetCUDA.h"
+#include "TerminalPoolingLayer.h"
+#include "scn_b200_net.h"
+
+struct scn_net {
+  std::unique_ptr<SparseConvNetCUDA> cnn;
+  int lattice;
+  SpatiallySparseBatch *last; // batch of the last forward
+  vectorCUDA<int> top;
+};
+
+namespace {
+thread_local std::string g_err;
+struct Quiet { // the builders print the reference's architecture banner; keep harness runs silent
+  std::streambuf *old;
+  std::ostringstream sink;
+  Quiet() : old(std::cout.rdbuf(sink.rdbuf())) {}
+  ~Quiet() { std::cout.rdbuf(old); }
+};
+template <class F> int guarded(F f) {
+  try { g_err.clear(); f(); return 0; }
+  catch (const std::exception &e) { g_err = e.what(); return 1; }
+  catch (...) { g_err = "unknown exception"; return 1; }
+}
+void describe(SpatiallySparseLayer *L, int *info, float *dropout) {
+  int v[10] = {-1, 1, 1, 1, 0, 0, 1, 0, 0, 0};
+  *dropout = 0;
+  if (auto c = dynamic_cast<ConvolutionalLayer *>(L)) {
+    int w[10] = {0, c->filterSize, c->filterStride, c->minActiveInputs, c->nFeaturesIn, c->nFeaturesOut, c->nFeaturesOut / c->nFeaturesIn, 0, c->inSpatialSize, c->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto c = dynamic_cast<ConvolutionalTriangularLayer *>(L)) {
+    int w[10] = {1, c->filterSize, c->filterStride, c->minActiveInputs, c->nFeaturesIn, c->nFeaturesOut, c->nFeaturesOut / c->nFeaturesIn, 0, c->inSpatialSize, c->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto n = dynamic_cast<NetworkInNetworkLayer *>(L)) {
+    int w[10] = {2, 1, 1, 1, n->nFeaturesIn, n->nFeaturesOut, 1, (int)n->fn, 0, 0};
+    std::memcpy(v, w, sizeof(v));
+    *dropout = n->dropout;
+  } else if (auto m = dynamic_cast<MaxPoolingLayer *>(L)) {
+    int w[10] = {3, m->poolSize, m->poolStride, 1, 0, 0, m->sd, 0, m->inSpatialSize, m->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto m = dynamic_cast<MaxPoolingTriangularLayer *>(L)) {
+    int w[10] = {4, m->poolSize, m->poolStride, 1, 0, 0, m->S, 0, m->inSpatialSize, m->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto t = dynamic_cast<TerminalPoolingLayer *>(L)) {
+    int w[10] = {5, t->poolSize, 1, 1, 0, 0, 1, 0, t->inSpatialSize, t->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  }
+  std::memcpy(info, v, sizeof(v));
+}
+// Fill interface 0 of a batch from device arrays.
+void adoptDeviceInput(SparseConvNetCUDA &cnn, SpatiallySparseBatch &b, int batch, int rows, int maxSites, const int *d_keys,
+                      const int *d_off, const int *d_bg, const float *d_features) {
+  cnn.prepareBatch(b);
+  b.reset();
+  b.type = UNLABELEDBATCH;
+  b.batchSize = batch;
+  SpatiallySparseBatchInterface &in = b.interfaces[0];
+  in.nFeatures = cnn.nInputFeatures;
+  in.spatialSize = cnn.inputSpatialSize;
+  in.featuresPresent.hVector() = range(cnn.nInputFeatures);
+  in.nSpatialSites = rows;
+  in.maxSitesPerSample = maxSites;
+  in.gridOwner = &in;
+  cudaStream_t s = cnn.memStream.stream;
+  in.siteKeys.copyToGPU(); in.sampleOffsets.copyToGPU(); in.backgroundRows.copyToGPU();
+  in.siteKeys.resize(rows); in.sampleOffsets.resize(batch + 1); in.backgroundRows.resize(batch);
+  in.sub->features.copyToGPU();
+  in.sub->features.resize(rows * cnn.nInputFeatures);
+  if (rows) {
+    cudaSafeCall(cudaMemcpyAsync(in.siteKeys.dPtr(), d_keys, sizeof(int) * rows, cudaMemcpyDeviceToDevice, s));
+    cudaSafeCall(cudaMemcpyAsync(in.sub->features.dPtr(), d_features, sizeof(float) * (size_t)rows * cnn.nInputFeatures, cudaMemcpyDeviceToDevice, s));
+  }
+  cudaSafeCall(cudaMemcpyAsync(in.sampleOffsets.dPtr(), d_off, sizeof(int) * (batch + 1), cudaMemcpyDeviceToDevice, s));
+  cudaSafeCall(cudaMemcpyAsync(in.backgroundRows.dPtr(), d_bg, sizeof(int) * batch, cudaMemcpyDeviceToDevice, s));
+}
+} // namespace
+
+extern "C" {
+
+const char *scn_net_last_error(void) { return g_err.c_str(); }
+
+scn_net_t *scn_net_create(int dimension, int nInputFeatures, int nClasses, int nTop, int lattice, void *stream) {
+  scn_net *n = nullptr;
+  int rc = guarded([&] {
+    Quiet q;
+    n = new scn_net();
+    n->lattice = lattice;
+    n->last = nullptr;
+    if (stream) n->cnn.reset(new SparseConvNetCUDA(dimension, nInputFeatures, nClasses, (cudaStream_t)stream, nTop, 2));
+    else n->cnn.reset(new SparseConvNetCUDA(dimension, nInputFeatures, nClasses, -1, nTop, 2));
+  });
+  if (rc) { delete n; return nullptr; }
+  return n;
+}
+void scn_net_destroy(scn_net_t *net) { delete net; }
+
+int scn_net_addLeNetLayerMP(scn_net_t *net, int nFeatures, int fs, int fstride, int ps, int pstride, int act, float dropout, int minActive) {
+  return guarded([&] {
+    Quiet q;
+    if (net->lattice == 0) net->cnn->addLeNetLayerMP(nFeatures, fs, fstride, ps, pstride, (ActivationFunction)act, dropout, minActive);
+    else net->cnn->addTriangularLeNetLayerMP(nFeatures, fs, fstride, ps, pstride, (ActivationFunction)act, dropout, minActive);
+  });
+}
+int scn_net_addTerminalPoolingLayer(scn_net_t *net, int poolSize) {
+  return guarded([&] {
+    Quiet q;
+    int S = net->lattice == 0 ? ipow(poolSize, net->cnn->dimension) : triangleSize(poolSize, net->cnn->dimension);
+    net->cnn->addTerminalPoolingLayer(poolSize, S);
+  });
+}
+int scn_net_addSoftmaxLayer(scn_net_t *net) { return guarded([&] { Quiet q; net->cnn->addSoftmaxLayer(); }); }
+
+scn_net_t *scn_net_DeepCNet(int dimension, int l, int k, int fn, int nInputFeatures, int nClasses, float p, int nTop, void *stream) {
+  scn_net_t *n = scn_net_create(dimension, nInputFeatures, nClasses, nTop, 0, stream);
+  if (!n) return nullptr;
+  int rc = guarded([&] {
+    Quiet q; // the call sequence of DeepCNet::DeepCNet
+    for (int i = 0; i <= l; ++i)
+      n->cnn->addLeNetLayerMP((i + 1) * k, i == 0 ? 3 : 2, 1, i < l ? 3 : 1, i < l ? 2 : 1, (ActivationFunction)fn, p * i * 1.0f / l);
+    n->cnn->addSoftmaxLayer();
+  });
+  if (rc) { scn_net_destroy(n); return nullptr; }
+  return n;
+}
+
+int scn_net_n_layers(scn_net_t *net) { return (int)net->cnn->layers.size(); }
+int scn_net_input_spatial_size(scn_net_t *net) { return net->cnn->inputSpatialSize; }
+int scn_net_layer_info(scn_net_t *net, int layer, int *info, float *dropout) {
+  return guarded([&] {
+    if (layer < 0 || layer >= (int)net->cnn->layers.size()) throw ScnException("layer index out of range");
+    describe(net->cnn->layers[layer], info, dropout);
+  });
+}
+int scn_net_set_weights(scn_net_t *net, int layer, const float *W, const float *B, const float *prelu) {
+  return guarded([&] {
+    auto n = dynamic_cast<NetworkInNetworkLayer *>(net->cnn->layers.at(layer));
+    if (!n) throw ScnException("layer has no weights");
+    std::vector<float> &w = n->W.hVector(), &b = n->B.hVector();
+    std::memcpy(w.data(), W, sizeof(float) * w.size());
+    std::memcpy(b.data(), B, sizeof(float) * b.size());
+    if (auto pr = dynamic_cast<NetworkInNetworkPReLULayer *>(n)) {
+      if (prelu) { std::vector<float> &s = pr->PReLU.hVector(); std::memcpy(s.data(), prelu, sizeof(float) * s.size()); }
+    }
+    n->weightsChanged();
+  });
+}
+int scn_net_load_weights(scn_net_t *net, const char *base, int epoch) { return guarded([&] { Quiet q; net->cnn->loadWeights(base, epoch, false); }); }
+int scn_net_save_weights(scn_net_t *net, const char *base, int epoch) { return guarded([&] { net->cnn->saveWeights(base, epoch, false); }); }
+int scn_net_set_precision(scn_net_t *net, int precision) {
+  return guarded([&] {
+    if (precision < SCN_PREC_AUTO || precision > SCN_PREC_BF16) throw ScnException("unknown precision");
+    for (auto L : net->cnn->layers)
+      if (auto n = dynamic_cast<NetworkInNetworkLayer *>(L)) n->precision = precision;
+  });
+}
+
+int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *off, const float *features, float *probs, int *predictions) {
+  return guarded([&] {
+    SparseConvNetCUDA &cnn = *net->cnn;
+    if (batch < 1) throw ScnException("batch must be positive");
+    SpatiallySparseBatch &b = cnn.batchPool[0];
+    cnn.prepareBatch(b);
+    b.reset();
+    b.type = UNLABELEDBATCH;
+    b.batchSize = batch;
+    SpatiallySparseBatchInterface &in = b.interfaces[0];
+    const int rows = off[batch];
+    const int nF = cnn.nInputFeatures;
+    in.nFeatures = nF;
+    in.spatialSize = cnn.inputSpatialSize;
+    in.featuresPresent.hVector() = range(nF);
+    in.nSpatialSites = rows;
+    in.gridOwner = &in;
+    // one pinned staging block: keys | offsets | background rows | features, one wait
+    const size_t kb = sizeof(int) * rows, ob = sizeof(int) * (batch + 1), bb = sizeof(int) * batch, fb = sizeof(float) * (size_t)rows * nF;
+    char *stage = (char *)cnn.memStream.staging(kb + ob + bb + fb);
+    int *sk = (int *)stage, *so = (int *)(stage + kb), *sb = (int *)(stage + kb + ob);
+    std::memcpy(sk, keys, kb);
+    std::memcpy(so, off, ob);
+    std::memcpy(stage + kb + ob + bb, features, fb);
+    int maxSites = 0;
+    for (int s = 0; s < batch; ++s) {
+      sb[s] = -1;
+      int sites = 0;
+      for (int r = off[s]; r < off[s + 1]; ++r) { if (keys[r] < 0) sb[s] = r; else ++sites; }
+      maxSites = std::max(maxSites, sites);
+    }
+    in.maxSitesPerSample = maxSites;
+    in.siteKeys.copyToGPU(); in.sampleOffsets.copyToGPU(); in.backgroundRows.copyToGPU(); in.sub->features.copyToGPU();
+    in.siteKeys.resize(rows); in.sampleOffsets.resize(batch + 1); in.backgroundRows.resize(batch); in.sub->features.resize(rows * nF);
+    cudaStream_t s = cnn.memStream.stream;
+    if (rows) cudaSafeCall(cudaMemcpyAsync(in.siteKeys.dPtr(), sk, kb, cudaMemcpyHostToDevice, s));
+    cudaSafeCall(cudaMemcpyAsync(in.sampleOffsets.dPtr(), so, ob, cudaMemcpyHostToDevice, s));
+    cudaSafeCall(cudaMemcpyAsync(in.backgroundRows.dPtr(), sb, bb, cudaMemcpyHostToDevice, s));
+    if (rows) cudaSafeCall(cudaMemcpyAsync(in.sub->features.dPtr(), stage + kb + ob + bb, fb, cudaMemcpyHostToDevice, s));
+    cnn.preprocessBatchOnDevice(b); // waits once, after the uploads and the rule chain
+    std::ofstream nof, nog;
+    cnn.processBatch(b, 0, 0, nof, nog);
+    net->last = &b;
+    for (int i = 0; i < batch; ++i) {
+      if (probs) std::memcpy(probs + (size_t)i * cnn.nClasses, b.probabilities[i].data(), sizeof(float) * cnn.nClasses);
+      if (predictions) std::memcpy(predictions + (size_t)i * cnn.nTop, b.predictions[i].data(), sizeof(int) * cnn.nTop);
+    }
+  });
+}
+
+int scn_net_forward_device(scn_net_t *net, int batch, int rows, int maxSites, const int *d_keys, const int *d_off, const int *d_bg,
+                           const float *d_features, float *d_probs, int *d_top) {
+  return guarded([&] {
+    SparseConvNetCUDA &cnn = *net->cnn;
+    SpatiallySparseBatch &b = cnn.batchPool[0];
+    adoptDeviceInput(cnn, b, batch, rows, maxSites, d_keys, d_off, d_bg, d_features);
+    cnn.preprocessBatchOnDevice(b);
+    cnn.forwardLayers(b);
+    net->last = &b;
+    SpatiallySparseBatchInterface &topI = b.interfaces.back();
+    cudaStream_t s = cnn.memStream.stream;
+    if (d_probs) cudaSafeCall(cudaMemcpyAsync(d_probs, topI.sub->features.dPtr(), sizeof(float) * (size_t)batch * cnn.nClasses, cudaMemcpyDeviceToDevice, s));
+    if (d_top) scnSafeCall(scn_top_indices(topI.sub->features.dPtr(), batch, cnn.nClasses, cnn.nTop, d_top, s));
+  });
+}
+
+int scn_net_iface_sizes(scn_net_t *net, int i, long long *sizes) {
+  return guarded([&] {
+    if (!net->last) throw ScnException("no forward has run");
+    SpatiallySparseBatchInterface &I = net->last->interfaces.at(i);
+    sizes[0] = I.nSpatialSites; sizes[1] = I.nFeatures; sizes[2] = I.spatialSize; sizes[3] = I.rules.size();
+    bool pools = i > 0 && (dynamic_cast<MaxPoolingLayer *>(net->cnn->layers[i - 1]) || dynamic_cast<MaxPoolingTriangularLayer *>(net->cnn->layers[i - 1]));
+    sizes[4] = pools ? (long long)I.nSpatialSites * I.nFeatures : 0;
+  });
+}
+// Interfaces behind layer i share sub-interface i across batches, so this is only valid
+// until the next forward.
+int scn_net_iface_fetch(scn_net_t *net, int i, float *features, int *rules, int *choices, int *rowKeys) {
+  return guarded([&] {
+    if (!net->last) throw ScnException("no forward has run");
+    SpatiallySparseBatchInterface &I = net->last->interfaces.at(i);
+    cudaSafeCall(cudaStreamSynchronize(net->cnn->memStream.stream));
+    if (features) {
+      if (I.deferredFrom) throw ScnException("this interface's gather is fused into the next layer and was never materialised");
+      size_t n = (size_t)I.nSpatialSites * I.nFeatures;
+      if (I.sub->features.size() != n) throw ScnException("interface features are no longer resident");
+      if (n) cudaSafeCall(cudaMemcpy(features, I.sub->features.dPtr(), sizeof(float) * n, cudaMemcpyDeviceToHost));
+    }
+    if (rules && I.rules.size()) cudaSafeCall(cudaMemcpy(rules, I.rules.dPtr(), sizeof(int) * I.rules.size(), cudaMemcpyDeviceToHost));
+    if (choices) {
+      size_t n = (size_t)I.nSpatialSites * I.nFeatures;
+      if (I.sub->poolingChoices.size() != n) throw ScnException("interface has no pooling choices");
+      if (n) cudaSafeCall(cudaMemcpy(choices, I.sub->poolingChoices.dPtr(), sizeof(int) * n, cudaMemcpyDeviceToHost));
+    }
+    if (rowKeys && I.nSpatialSites) {
+      SpatiallySparseBatchInterface *g = I.gridOwner;
+      cudaSafeCall(cudaMemcpy(rowKeys, g->siteKeys.dPtr(), sizeof(int) * I.nSpatialSites, cudaMemcpyDeviceToHost));
+    }
+  });
+}
+
+double scn_net_take_multiply_adds(void) {
+  double v = (double)multiplyAddCount;
+  multiplyAddCount = 0;
+  return v;
+}
+int scn_net_enable_timing(scn_net_t *net, int on) { return guarded([&] { net->cnn->enableTiming(on != 0); }); }
+int scn_net_layer_times(scn_net_t *net, float *ms) {
+  return guarded([&] {
+    std::vector<float> t = net->cnn->layerTimes();
+    std::memcpy(ms, t.data(), sizeof(float) * t.size());
+  });
+}
+
+int scn_net_process_dataset(scn_net_t *net, int nSamples, const int *keys, const int *off, const float *features, const int *labels,
+                            int batchSize, float *errorRate, float *probs) {
+  return guarded([&] {
+    Quiet q;
+    SparseConvNetCUDA &cnn = *net->cnn;
+    const int nF = cnn.nInputFeatures;
+    std::vector<std::unique_ptr<SitesPicture>> pics;
+    SpatiallySparseDataset ds;
+    ds.name = "synthetic"; ds.nFeatures = nF; ds.nClasses = cnn.nClasses; ds.type = labels ? TESTBATCH : UNLABELEDBATCH;
+    for (int s = 0; s < nSamples; ++s) {
+      bool bg = false;
+      for (int r = off[s]; r < off[s + 1]; ++r) bg = bg || keys[r] < 0;
+      pics.emplace_back(new SitesPicture(nF, labels ? labels[s] : -1, bg));
+      for (int r = off[s]; r < off[s + 1]; ++r) {
+        if (keys[r] < 0) continue;
+        pics.back()->keys.push_back(keys[r]);
+        pics.back()->features.insert(pics.back()->features.end(), features + (size_t)r * nF, features + (size_t)(r + 1) * nF);
+      }
+      ds.pictures.push_back(pics.back().get());
+    }
+    // the loop of SparseConvNetCUDA::processDataset, keeping each batch's probabilities
+    BatchProducer bp(cnn, ds, cnn.inputSpatialSize, batchSize);
+    std::ofstream nof, nog;
+    float err = 0;
+    size_t at = 0;
+    while (SpatiallySparseBatch *b = bp.nextBatch()) {
+      cnn.processBatch(*b, 0, 0, nof, nog);
+      err += b->mistakes * 1.0f / nSamples;
+      for (int i = 0; i < b->batchSize; ++i, ++at)
+        if (probs) std::memcpy(probs + at * cnn.nClasses, b->probabilities[i].data(), sizeof(float) * cnn.nClasses);
+    }
+    if (errorRate) *errorRate = err;
+  });
+}
+
+int scn_host_vectorTopIndices(const float *v, int n, int k, int *out) {
+  return guarded([&] {
+    std::vector<float> t(v, v + n);
+    std::vector<int> r = vectorTopIndices(t, k);
+    std::memcpy(out, r.data(), sizeof(int) * k);
+  });
+}
+}

@@ -1,0 +1,57 @@
+// Host helpers with the reference's names (utilities.h): integer arithmetic used by the
+// builders, the pinned-staging stream object, top-k selection, error handling.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdexcept>
+#include <string>
+#include <vector>
+#include "scn_b200.h"
+
+// The reference's constructors take a cuBLAS handle (NetworkInNetworkLayer.h:24-28).  No
+// cuBLAS is used here; the type is declared (identically to cublas_api.h) so the same
+// signatures compile, and the handle is ignored.
+struct cublasContext;
+typedef struct cublasContext *cublasHandle_t;
+
+#define NTHREADS 512
+#define KERNELBLOCKSIZE 32
+
+std::vector<int> range(int n);                    // 0,1,...,n-1
+int ipow(int base, int exp);                      // utilities.cu:14-26
+int triangleSize(int linearSize, int dimension);  // utilities.cu:27-32
+int intRound(int a, int d);                       // utilities.cu:103
+int intRoundUp(int a, int d);                     // utilities.cu:102
+template <typename t> std::vector<int> vectorTopIndices(std::vector<t> &test, int k); // utilities.cu:35-56
+
+// Errors are C++ exceptions here; the reference prints and calls exit() (utilities.h:32-67).
+struct ScnException : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+void scnCheckCuda(cudaError_t err, const char *file, int line);
+void scnCheckStatus(int status, const char *file, int line);
+#define cudaSafeCall(err) scnCheckCuda((err), __FILE__, __LINE__)
+#define cudaCheckError() scnCheckCuda(cudaGetLastError(), __FILE__, __LINE__)
+#define scnSafeCall(st) scnCheckStatus((st), __FILE__, __LINE__)
+
+// Selects the device with this PCI bus id (-1: device 0) and returns its ordinal
+// (utilities.cu:105-130).  Refuses devices that are not compute capability 10.x.
+int initializeGPU(int pciBusID);
+
+// A stream plus a pinned staging buffer (utilities.h:105-112).  The buffer grows on demand.
+// With an external stream (the benchmark passes torch's current stream) the object does
+// not own it.
+class cudaMemStream {
+public:
+  int pinnedMemorySize;
+  void *pinnedMemory;
+  cudaStream_t stream;
+  cudaMemStream();
+  explicit cudaMemStream(cudaStream_t external);
+  ~cudaMemStream();
+  void *staging(size_t bytes); // pinned buffer of at least `bytes`
+  cudaMemStream(const cudaMemStream &) = delete;
+  cudaMemStream &operator=(const cudaMemStream &) = delete;
+
+private:
+  bool ownsStream;
+};

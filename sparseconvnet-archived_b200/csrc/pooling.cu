@@ -89,10 +89,42 @@ __global__ void k_top_indices(const float *__restrict__ probs, int rows, int nCl
   }
 }
 
+// applySigmoid as a stand-alone elementwise pass (SigmoidLayer.cu:187-222).
+__global__ void k_activation(const float *__restrict__ in, float *__restrict__ out, long long n, int N, int act,
+                             const float *__restrict__ prelu) {
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n; q += (long long)gridDim.x * blockDim.x)
+    out[q] = activate(in[q], act, prelu ? prelu[q % N] : 0.f);
+}
+// Row softmax (SigmoidLayer.cu:160-177), one thread per row.
+__global__ void k_softmax(const float *__restrict__ in, float *__restrict__ out, int rows, int N) {
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
+    const float *a = in + (long long)r * N;
+    float *b = out + (long long)r * N;
+    float mx = -10000.0f, acc = 0.0f;
+    for (int k = 0; k < N; ++k) if (a[k] > mx) mx = a[k];
+    for (int k = 0; k < N; ++k) { b[k] = expf(a[k] - mx); acc += b[k]; }
+    for (int k = 0; k < N; ++k) b[k] /= acc;
+  }
+}
+
 } // namespace
 } // namespace scn
 
 using namespace scn;
+
+extern "C" int scn_activation_forward(const float *d_in, float *d_out, int rows, int N, int act, const float *d_prelu,
+                                      scn_stream_t stream) {
+  clear_error();
+  if (rows < 0 || N < 1 || act < SCN_NOSIGMOID || act > SCN_SIGMOID) return fail(SCN_ERR_INVALID, "bad activation arguments");
+  if (act == SCN_PRELU && !d_prelu) return fail(SCN_ERR_INVALID, "PReLU slopes missing");
+  if (rows == 0) return SCN_OK;
+  if (!d_in || !d_out) return fail(SCN_ERR_INVALID, "null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (act == SCN_SOFTMAX) k_softmax<<<grid_for(rows, 128), 128, 0, s>>>(d_in, d_out, rows, N);
+  else k_activation<<<grid_for((long long)rows * N, 256), 256, 0, s>>>(d_in, d_out, (long long)rows * N, N, act, d_prelu);
+  SCN_LAUNCH_CHECK("k_activation");
+  return SCN_OK;
+}
 
 extern "C" int scn_maxpool_forward(const float *d_in, const int *d_rules, int rows_out, int sd, int C, float *d_out,
                                    int *d_choices, scn_stream_t stream) {
