@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the forward hot path: samples/sec of a DeepCNet(5,100)-style network
+(addLeNetLayerMP levels with conv + 2/2 max pooling, builder-rounded widths 96..608) on the
+CIFAR-10-shaped dense-in-sparse 2-D workload, batch 256 per GPU.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One "step" = one full forward of one batch: rule construction for every layer on the
+device, all fused conv/NiN, pooling and softmax kernels, top-1, and (N > 1) the all-gather
+of the class probabilities.  Rank r of N processes its own 256 samples (weak scaling).
+
+  value     device-timed throughput with the inputs already resident in HBM
+  e2e       the same through the host-buffer entry point (scn_net_forward_host): pinned
+            staging + H2D of keys/offsets/features inside the timed region, D2H of
+            probabilities and predictions at the end of every step
+  roofline  the kernel with the largest share of the step, CUDA-event timed in the same run
+  cpu_baseline  the CPU oracle (port of the reference's host rule construction and layer
+            semantics) on a bounded sample of the same workload, all host cores
+
+--impl reference times that CPU path alone (the reference has no CPU-only executable and
+its CUDA kernels are what this library replaces), rank 0 only.
+"""
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = 2
+BATCH_PER_GPU = 256
+METRIC = "samples/sec DeepCNet(5,100) fwd"
+WORKLOAD = ("config 2: CIFAR-10-shaped dense 32x32x3 N(0,1) patch in a 96x96 grid, DeepCNet(5,100)-style "
+            "(conv3 + 5 x conv2, MP2/2, widths 96/192/288/416/512/608 as the reference builder rounds them, "
+            "VLeakyReLU, test-time dropout scaling p=0.5 ramp, softmax 10), batch 256 per GPU")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], tflops=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def build_pair(scn, want_oracle):
+    """The benchmark network in the product and (optionally) in the CPU oracle, same weights."""
+    c = scn.synth.CONFIGS[CFG]
+    gnet = None
+    import torch
+    if torch.cuda.is_available():
+        gnet = scn.net.Net(c["dim"], c["nIn"], c["nClasses"], 1, c["lattice"])
+        scn.synth.build_network(gnet, CFG)
+    onet = None
+    if want_oracle:
+        from oracle import orc
+        onet = orc.OracleNet(orc.Oracle(), c["dim"], c["nIn"], c["nClasses"], 1, lattice=c["lattice"])
+        scn.synth.build_network(onet, CFG)
+    layers = (gnet or onet).layers()
+    for i, (W, B, pr) in scn.synth.init_weights(layers).items():
+        if gnet:
+            gnet.set_weights(i, W, B, pr)
+        if onet:
+            onet.set_weights(i, W, B, pr)
+    return gnet, onet
+
+
+def cpu_leg(scn, onet, budget_s, threads):
+    """Oracle forward on a bounded sample sized for about budget_s seconds of wall time."""
+    gen = scn.synth.CONFIGS[CFG]["gen"]
+    keys, off, feats = gen(threads)  # one sample per thread to estimate the rate
+    t0 = time.time()
+    onet.forward(keys.astype(np.int64), off, feats, threads=threads)
+    per_sample = (time.time() - t0) / threads * threads  # wall seconds per `threads` samples
+    n = int(max(threads, min(BATCH_PER_GPU, threads * max(1, round(budget_s / max(per_sample, 1e-3))))))
+    keys, off, feats = gen(n)
+    t0 = time.time()
+    onet.forward(keys.astype(np.int64), off, feats, threads=threads)
+    wall = time.time() - t0
+    return dict(value=n / wall, unit="samples/s", cores=threads, kind="port",
+                sample="%d samples of the workload, oracle fp32 forward incl. rule construction, %.1f s wall "
+                       "(rule construction alone %.0f samples/s)" % (n, wall, n / max(onet.times[0], 1e-9)),
+                rules_only_samples_per_s=n / max(float(onet.times[0]), 1e-9))
+
+
+def run_reference(args, scn):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    _, onet = build_pair_cpu_only(scn)
+    gen = scn.synth.CONFIGS[CFG]["gen"]
+    n = BATCH_PER_GPU  # one whole batch per step
+    keys, off, feats = gen(n)
+    keys = keys.astype(np.int64)
+    for _ in range(args.warmup):
+        onet.forward(keys[: off[threads]], off[: threads + 1], feats[: off[threads]], threads=threads)
+    t0 = time.time()
+    rules_s = 0.0
+    for _ in range(args.steps):
+        onet.forward(keys, off, feats, threads=threads)
+        rules_s += float(onet.times[0])
+    wall = time.time() - t0
+    v = n * args.steps / wall
+    line = dict(impl="reference", metric=METRIC, value=v, unit="samples/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=1000.0 * wall / args.steps, higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload=WORKLOAD, step="one CPU forward of a bounded sample of %d samples" % n),
+                cpu_baseline=dict(value=v, unit="samples/s", cores=threads, kind="port",
+                                  sample="%d samples per step, %d steps; the reference's host rule construction and "
+                                         "layer semantics restated in C++ (oracle), std::thread over samples" % (n, args.steps)),
+                e2e=dict(value=v, unit="samples/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0)
+    print(json.dumps(line))
+
+
+def build_pair_cpu_only(scn):
+    from oracle import orc
+    c = scn.synth.CONFIGS[CFG]
+    onet = orc.OracleNet(orc.Oracle(), c["dim"], c["nIn"], c["nClasses"], 1, lattice=c["lattice"])
+    scn.synth.build_network(onet, CFG)
+    for i, (W, B, pr) in scn.synth.init_weights(onet.layers()).items():
+        onet.set_weights(i, W, B, pr)
+    return None, onet
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--precision", default="auto", choices=["auto", "fp32", "3xtf32", "bf16"])
+    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="wall budget of the cpu_baseline leg (0 = skip)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+
+    scn = importlib.import_module("sparseconvnet-archived_b200")
+    if args.impl == "reference":
+        run_reference(args, scn)
+        return
+
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    abi = scn.abi
+    stream = torch.cuda.Stream(device=dev)
+    c = scn.synth.CONFIGS[CFG]
+    nC = c["nClasses"]
+    peaks = measured_peaks()
+
+    with torch.cuda.stream(stream):
+        gnet, _ = build_pair(scn, False)
+        gnet.set_precision(dict(auto=abi.PREC_AUTO, fp32=abi.PREC_FP32, **{"3xtf32": abi.PREC_3XTF32}, bf16=abi.PREC_BF16)[args.precision])
+        # this rank's shard of the global batch, several distinct batches rotated between steps
+        n_rot = 2
+        host_batches = [c["gen"](BATCH_PER_GPU, first=(rank * n_rot + j) * BATCH_PER_GPU) for j in range(n_rot)]
+        dev_batches = []
+        for keys, off, feats in host_batches:
+            bg = off[:-1].copy()  # the background row is each sample's first row
+            dev_batches.append(tuple(torch.from_numpy(x).to(dev) for x in (keys, off, bg, feats)) + (int(np.diff(off).max() - 1),))
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
+        d_probs = torch.empty((BATCH_PER_GPU, nC), dtype=torch.float32, device=dev)
+        d_top = torch.empty((BATCH_PER_GPU, 1), dtype=torch.int32, device=dev)
+        gathered = torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32, device=dev)
+        h_gathered = torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32).pin_memory()
+
+        def step_device(j):
+            dk, do, db, df, ms = dev_batches[j % n_rot]
+            gnet.forward_device(dk, do, db, df, ms, d_probs, d_top)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, d_probs)
+
+        def step_host(j):
+            keys, off, feats = host_batches[j % n_rot]
+            probs, pred = gnet.forward_host(keys, off, feats)
+            if world > 1:
+                gnet.copy_probs_device(d_probs)
+                dist.all_gather_into_tensor(gathered, d_probs)
+                h_gathered.copy_(gathered, non_blocking=True)
+                stream.synchronize()
+            return probs
+
+        def timed(step, steps, with_layer_times):
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+            layer_ms = None
+            for j in range(steps):
+                flush.fill_(j & 0xff)
+                ev[j][0].record(stream)
+                step(j)
+                ev[j][1].record(stream)
+                if with_layer_times:
+                    t = gnet.layer_times()  # waits for the stream
+                    layer_ms = t if layer_ms is None else layer_ms + t
+            stream.synchronize()
+            ms = sum(a.elapsed_time(b) for a, b in ev)
+            return ms, (layer_ms / steps if layer_ms is not None else None)
+
+        def barrier():
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        # ---- device-resident leg
+        for j in range(args.warmup):
+            step_device(j)
+        gnet.enable_timing(True)
+        barrier()
+        sampler = ClockSampler(local)
+        launches0 = abi.kernel_launch_count()
+        t_wall = time.time()
+        ms_dev, layer_ms = timed(step_device, args.steps, True)
+        barrier()
+        t_wall = time.time() - t_wall
+        launches = abi.kernel_launch_count() - launches0
+        gnet.enable_timing(False)
+        # ---- host-buffer leg
+        for j in range(args.warmup):
+            step_host(j)
+        barrier()
+        ms_e2e, _ = timed(step_host, args.steps, False)
+        barrier()
+        clocks = sampler.stop()
+
+        # shapes of the last forward for the roofline arithmetic
+        layers = gnet.layers()
+        sizes = [gnet.iface(i, features=False) for i in range(len(layers) + 1)]
+
+    t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_dev, ms_e2e = (float(x) for x in t.cpu())
+    total = world * BATCH_PER_GPU * args.steps
+
+    # ---- roofline of the kernel with the largest share of the step
+    per_layer = []
+    for i, L in enumerate(layers):
+        rows_in, rows_out = sizes[i]["nSpatialSites"], sizes[i + 1]["nSpatialSites"]
+        ms = float(layer_ms[i])
+        if L["type"] == 2:
+            fused = i > 0 and layers[i - 1]["type"] in (0, 1)
+            fs = layers[i - 1]["fs"] if fused else 1
+            src_rows = sizes[i - 1]["nSpatialSites"] if fused else rows_in
+            K, N = L["nIn"], L["nOut"]
+            flops = 2.0 * rows_out * K * N
+            byts = 4.0 * (src_rows * (K // fs) + (rows_out * fs if fused else 0) + K * N + N + rows_out * N)
+            per_layer.append(dict(layer=i, kernel="conv_nin_fused" if fused else "nin", rows=rows_out, K=K, N=N, ms=ms,
+                                  flops=flops, bytes=byts))
+        elif L["type"] in (3, 4):
+            C = sizes[i + 1]["nFeatures"]
+            byts = 4.0 * (rows_out * L["fs"] + rows_in * C + 2 * rows_out * C)
+            per_layer.append(dict(layer=i, kernel="maxpool_rules", rows=rows_out, C=C, ms=ms, flops=0.0, bytes=byts))
+    rules_ms = float(layer_ms[len(layers)])
+    top = max(per_layer, key=lambda d: d["ms"])
+    if top["kernel"] != "maxpool_rules" and top["K"] >= 128:
+        ach = top["flops"] / (top["ms"] * 1e-3) / 1e12
+        roof = dict(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"], traffic=None)
+    else:
+        ach = top["bytes"] / (top["ms"] * 1e-3) / 1e9
+        roof = dict(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"], traffic=None)
+    roof.update(kernel="layer %d %s" % (top["layer"], top["kernel"]), ms_per_launch=top["ms"], peak_source=peaks["source"],
+                share_of_step=top["ms"] / (ms_dev / args.steps))
+    all_flops = sum(d["flops"] for d in per_layer)
+    conv_ms = sum(d["ms"] for d in per_layer if d["kernel"] != "maxpool_rules")
+
+    if rank == 0:
+        cpu = None
+        if args.cpu_seconds > 0:
+            try:
+                _, onet = build_pair_cpu_only(scn)
+                cpu = cpu_leg(scn, onet, args.cpu_seconds, os.cpu_count() or 1)
+            except Exception as e:  # the oracle is a checker, its absence must not hide the GPU numbers
+                cpu = dict(value=None, unit="samples/s", cores=0, kind="port", sample="unavailable: %s" % e)
+        h2d = int(sum(x.nbytes for x in host_batches[0]) + host_batches[0][1][:-1].nbytes)
+        d2h = int(BATCH_PER_GPU * nC * 4 + BATCH_PER_GPU * 4 + (world * BATCH_PER_GPU * nC * 4 if world > 1 else 0))
+        line = dict(
+            metric=METRIC, value=total / (ms_dev * 1e-3), unit="samples/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+            ms_per_step=ms_dev / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
+            dtype="f32" if args.precision == "fp32" else ("bf16" if args.precision == "bf16" else "tf32x3/f32"), data="synthetic",
+            config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample, all-gather of probabilities" % world,
+                        l2="256 MiB written between timed steps; 2 distinct batches rotated", precision=args.precision,
+                        timing="CUDA events per step on the launching stream, max over ranks; wall %.3f s for the device leg" % t_wall),
+            e2e=dict(value=total / (ms_e2e * 1e-3), unit="samples/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                     ms_per_step=ms_e2e / args.steps),
+            gpu_launches=int(launches), roofline=roof, cpu_baseline=cpu, clocks=clocks,
+            breakdown=dict(rule_chain_ms=rules_ms, conv_nin_ms=conv_ms, conv_algorithmic_tflops=all_flops / (conv_ms * 1e-3) / 1e12,
+                           multiply_adds_per_sample=all_flops / 2 / BATCH_PER_GPU,
+                           layers=[dict(layer=d["layer"], kernel=d["kernel"], ms=round(d["ms"], 4), rows=d["rows"],
+                                        gflop=round(d["flops"] / 1e9, 3), mbytes=round(d["bytes"] / 1e6, 2)) for d in per_layer]),
+        )
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -71,6 +71,9 @@ typedef struct {
 const char *scn_status_string(int status);
 /* Message of the last failing call on this thread ("" if none). */
 const char *scn_last_error(void);
+/* Kernels this library has launched in this process so far (memsets and copies are not
+ * counted).  No reference counterpart: the benchmark reports it. */
+long long scn_kernel_launch_count(void);
 /* 1 when the library was built for, and the current device is, compute capability 10.x. */
 int scn_device_supported(void);
 

@@ -68,6 +68,10 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *h_keys, const int
 int scn_net_forward_device(scn_net_t *net, int batch, int rows, int maxSitesPerSample, const int *d_keys, const int *d_off,
                            const int *d_bg, const float *d_features, float *d_probs, int *d_top);
 
+/* Copy the class probabilities of the last forward (the top interface's features,
+ * [batch x nClasses]) to d_probs on the network's stream, e.g. into an all-gather buffer. */
+int scn_net_copy_probs_device(scn_net_t *net, float *d_probs);
+
 /* SpatiallySparseBatchInterface i of the last forward (0 = input, i+1 = output of layer i;
  * SpatiallySparseBatchInterface.h:19-46).  sizes[5] = nSpatialSites, nFeatures, spatialSize,
  * rules.size(), poolingChoices.size() (0 unless layer i-1 pools).  A ConvolutionalLayer

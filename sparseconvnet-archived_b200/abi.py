@@ -18,7 +18,7 @@ PREC_AUTO, PREC_FP32, PREC_3XTF32, PREC_BF16 = -1, 0, 1, 2
 DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
 
 EXPORTS = [
-    "scn_status_string", "scn_last_error", "scn_device_supported", "scn_regions_cells",
+    "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
     "scn_rules_workspace_bytes", "scn_rules_build", "scn_terminal_rules_workspace_bytes",
     "scn_terminal_rules_build", "scn_conv_nin_forward", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_gather_forward", "scn_maxpool_forward",
@@ -49,6 +49,7 @@ def lib():
         L.scn_status_string.argtypes = [c_int]
         L.scn_last_error.restype = ctypes.c_char_p
         L.scn_device_supported.restype = c_int
+        L.scn_kernel_launch_count.restype = c_ll
         L.scn_regions_cells.restype, L.scn_regions_cells.argtypes = c_int, [c_p]
         L.scn_rules_workspace_bytes.restype = c_sz
         L.scn_rules_workspace_bytes.argtypes = [c_p, c_int, c_int]
@@ -199,3 +200,7 @@ def activation_forward(x, act, prelu=None):
     out = torch.empty_like(x)
     check(lib().scn_activation_forward(_ptr(_f32(x)), _ptr(out), rows, N, act, _ptr(prelu), _stream()))
     return out
+
+
+def kernel_launch_count():
+    return int(lib().scn_kernel_launch_count())

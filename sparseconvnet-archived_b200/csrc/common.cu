@@ -1,5 +1,6 @@
 // Error reporting, device queries and status strings of libscn_b200.so.
 #include "scn_common.cuh"
+#include <atomic>
 #include <cstdarg>
 #include <cstring>
 
@@ -14,6 +15,9 @@ void set_error(const char *fmt, ...) {
   va_end(ap);
 }
 void clear_error() { g_err[0] = 0; }
+
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int sm_count() {
   static int cached[64];
@@ -41,6 +45,7 @@ extern "C" const char *scn_status_string(int status) {
 }
 
 extern "C" const char *scn_last_error(void) { return scn::g_err; }
+extern "C" long long scn_kernel_launch_count(void) { return scn::g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int scn_device_supported(void) {
   int dev = 0, major = 0;

@@ -232,6 +232,16 @@ int scn_net_forward_device(scn_net_t *net, int batch, int rows, int maxSites, co
   });
 }
 
+int scn_net_copy_probs_device(scn_net_t *net, float *d_probs) {
+  return guarded([&] {
+    if (!net->last) throw ScnException("no forward has run");
+    SpatiallySparseBatchInterface &topI = net->last->interfaces.back();
+    const size_t n = (size_t)topI.nSpatialSites * topI.nFeatures;
+    if (topI.sub->features.size() != n) throw ScnException("probabilities are no longer resident");
+    cudaSafeCall(cudaMemcpyAsync(d_probs, topI.sub->features.dPtr(), sizeof(float) * n, cudaMemcpyDeviceToDevice, net->cnn->memStream.stream));
+  });
+}
+
 int scn_net_iface_sizes(scn_net_t *net, int i, long long *sizes) {
   return guarded([&] {
     if (!net->last) throw ScnException("no forward has run");

@@ -11,6 +11,9 @@ namespace scn {
 void set_error(const char *fmt, ...);
 void clear_error();
 
+// Kernels launched by this library in this process (every SCN_LAUNCH_CHECK counts one).
+void count_launch();
+
 // Number of SMs of the current device (cached per device); grids are sized in multiples of it.
 int sm_count();
 
@@ -30,6 +33,7 @@ inline int fail(int status, const char *what) {
 
 #define SCN_LAUNCH_CHECK(name)                                                              \
   do {                                                                                      \
+    scn::count_launch();                                                                    \
     cudaError_t e__ = cudaGetLastError();                                                   \
     if (e__ != cudaSuccess) {                                                               \
       scn::set_error("launch of %s failed: %s", name, cudaGetErrorString(e__));             \

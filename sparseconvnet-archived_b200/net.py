@@ -17,7 +17,7 @@ EXPORTS = [
     "scn_net_addTerminalPoolingLayer", "scn_net_addSoftmaxLayer", "scn_net_DeepCNet", "scn_net_n_layers",
     "scn_net_input_spatial_size", "scn_net_layer_info", "scn_net_set_weights", "scn_net_load_weights",
     "scn_net_save_weights", "scn_net_set_precision", "scn_net_forward_host", "scn_net_forward_device",
-    "scn_net_iface_sizes", "scn_net_iface_fetch", "scn_net_take_multiply_adds", "scn_net_enable_timing",
+    "scn_net_copy_probs_device", "scn_net_iface_sizes", "scn_net_iface_fetch", "scn_net_take_multiply_adds", "scn_net_enable_timing",
     "scn_net_layer_times", "scn_net_process_dataset", "scn_host_vectorTopIndices",
 ]
 
@@ -59,6 +59,7 @@ def lib():
         L.scn_net_set_precision.argtypes = [c_p, c_int]
         L.scn_net_forward_host.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p, c_p]
         L.scn_net_forward_device.argtypes = [c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p]
+        L.scn_net_copy_probs_device.argtypes = [c_p, c_p]
         L.scn_net_iface_sizes.argtypes = [c_p, c_int, c_p]
         L.scn_net_iface_fetch.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p]
         L.scn_net_take_multiply_adds.restype = c_d
@@ -175,6 +176,10 @@ class Net:
                                              c_p(d_bg.data_ptr()), c_p(d_features.data_ptr()), c_p(d_probs.data_ptr()),
                                              c_p(d_top.data_ptr())))
         return d_probs, d_top
+
+    def copy_probs_device(self, d_probs):
+        _check(self.L.scn_net_copy_probs_device(self.h, c_p(d_probs.data_ptr())))
+        return d_probs
 
     def iface(self, i, features=True):
         s = np.zeros(5, np.int64)
