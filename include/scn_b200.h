@@ -137,6 +137,12 @@ size_t scn_conv_packed_weight_bytes(int K, int N, int precision);
 int scn_conv_pack_weights(const float *d_W, int K, int N, int precision, void *d_W_packed,
                           scn_stream_t stream);
 
+/* Every wait inside the tensor-core kernel has a time limit (2 s); a wait that runs out
+ * records a code and the kernel proceeds to its normal exit.  Returns that code (0 = none)
+ * and clears it; copies from the device, so it waits for running work.  No reference
+ * counterpart. */
+int scn_conv_tc_take_error(void);
+
 /* Replaces propForwardToMatrixMultiply alone (ConvolutionalLayer.cu:12-41): the
  * materialised gather, for callers that read ConvolutionalLayer's output themselves.
  * out[c*nIn + j] = in[rules[c]*nIn + j], zero where rules[c] < 0; count = rows_out*fs. */

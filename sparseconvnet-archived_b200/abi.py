@@ -21,7 +21,7 @@ EXPORTS = [
     "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
     "scn_rules_workspace_bytes", "scn_rules_build", "scn_terminal_rules_workspace_bytes",
     "scn_terminal_rules_build", "scn_conv_nin_forward", "scn_conv_packed_weight_bytes",
-    "scn_conv_pack_weights", "scn_gather_forward", "scn_maxpool_forward",
+    "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward",
 ]
 
@@ -204,3 +204,7 @@ def activation_forward(x, act, prelu=None):
 
 def kernel_launch_count():
     return int(lib().scn_kernel_launch_count())
+
+
+def conv_tc_take_error():
+    return int(lib().scn_conv_tc_take_error())

@@ -137,3 +137,5 @@ extern "C" int scn_conv_pack_weights(const float *d_W, int K, int N, int precisi
   if (K < 1 || N < 1 || !d_W || !d_W_packed) return fail(SCN_ERR_INVALID, "bad pack arguments");
   return tc_pack(d_W, K, N, precision, d_W_packed, (cudaStream_t)stream);
 }
+
+extern "C" int scn_conv_tc_take_error(void) { return tc_take_error(); }

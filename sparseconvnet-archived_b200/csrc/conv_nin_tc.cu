@@ -1,9 +1,356 @@
-// tcgen05/TMEM fused conv/NiN kernel -- placeholder until the kernel lands.
+// Fused rule-gather + NetworkInNetwork forward on the 5th-generation tensor cores
+// (tcgen05.mma with the accumulator in tensor memory), sm_100a only.
+//
+//   out[r][n] = act( p * sum_k A[r][k] * W[k][n] + p * B[n] ),   A[r][f*nIn + c] = in[rules[r*fs+f]][c]
+//
+// One CTA computes a 128-row x BN-column output tile.  The K axis is walked in slabs of 32
+// fp32 values (128 bytes, one 128B-swizzle row); nIn is a multiple of 32, so a slab never
+// straddles two filter cells and every A row of a slab is 128 contiguous bytes of one input
+// row named by the rulebook.
+//
+//   warps 0-3  gather: 16-byte loads of the rows the rules name (zeros for a negative rule or
+//              a row past the end), split each fp32 into tf32 hi + tf32 lo, store both into
+//              shared memory in the canonical K-major SWIZZLE_128B layout, fence to the async
+//              proxy, arrive on the stage's "full" barrier.  Afterwards the same warps run
+//              the epilogue: tcgen05.ld of their 32 accumulator lanes, p*acc + p*bias,
+//              activation, 16-byte stores.
+//   warp 4     one thread issues a cp.async.bulk per slab for the weight tile (hi and lo
+//              images, pre-split, pre-transposed and pre-swizzled once by tc_pack, so the
+//              copy is a plain contiguous block into this CTA's own shared memory; no
+//              tensor map is needed).
+//   warp 5     allocates tensor memory; one thread issues, per slab, 3 x 4 tcgen05.mma
+//              (kind::tf32, M=128, N=BN, K=8): A_lo*B_hi + A_hi*B_lo + A_hi*B_hi, which
+//              restores fp32-grade accuracy from tf32 products ("3xTF32"), then
+//              tcgen05.commit onto the stage's "empty" barrier.
+//
+// The gathered matrix never exists in global memory (the reference writes and re-reads it,
+// ConvolutionalLayer.cu:124-133).  Every mbarrier wait has an iteration limit: on expiry the
+// kernel records an error code in g_tc_error and carries on to its normal exit, so tensor
+// memory is always released and the context stays usable.
 #include "conv_nin_tc.cuh"
+
 namespace scn {
-bool tc_shape_ok(int, int, int, int) { return false; }
-size_t tc_packed_bytes(int, int, int) { return 0; }
-int tc_pack(const float *, int, int, int, void *, cudaStream_t) { return fail(SCN_ERR_UNSUPPORTED, "tensor-core path not built"); }
-int tc_launch(const float *, const int *, int, int, int, const void *, const float *, const float *, int, float, int, int,
-              float *, cudaStream_t) { return fail(SCN_ERR_UNSUPPORTED, "tensor-core path not built"); }
+
+__device__ int g_tc_error = 0;
+
+namespace {
+
+constexpr int BM = 128;          // rows per CTA tile (UMMA M)
+constexpr int SLAB = 32;         // fp32 values of K per pipeline stage
+constexpr int ROW_BYTES = 128;   // bytes of one smem row (SLAB * 4)
+constexpr int A_HALF = BM * ROW_BYTES; // 16 KB: one of A_hi / A_lo
+constexpr int NUM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: false (and an error code) if the phase did not complete in time.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+  unsigned long long start = 0;
+  for (uint32_t i = 0;; ++i) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 63) == 63) {
+      if (*(volatile int *)&g_tc_error != 0) return false; // another wait already gave up: do not wait again
+      const unsigned long long now = global_ns();
+      if (start == 0) start = now;
+      else if (now - start > WAIT_LIMIT_NS) break;
+    }
+  }
+  atomicCAS(&g_tc_error, 0, code);
+  return false;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, SWIZZLE_128B: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fff);
+  d |= (uint64_t)1 << 16;             // leading byte offset (unused for swizzled K-major): 1
+  d |= (uint64_t)(1024 >> 4) << 32;   // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;             // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;             // SWIZZLE_128B
+  return d;
+}
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+struct Params {
+  const float *in; const int *rules; int rows, fs, nIn;
+  const unsigned char *packed; const float *bias; const float *prelu;
+  int N, BN, nTiles, nSlabs, stages, tmemCols; float p; int act; float *out; uint32_t idesc;
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) {
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment: the swizzle pattern is a function of absolute shared-memory address bits
+  unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int bHalf = P.BN * ROW_BYTES;            // one of B_hi / B_lo
+  const int stageBytes = 2 * A_HALF + 2 * bHalf; // A_hi, A_lo, B_hi, B_lo
+  __shared__ __align__(8) uint64_t bars[2 * 8 + 1];
+  __shared__ uint32_t tmemBase;
+  const uint32_t fullBar = smem_u32(&bars[0]), emptyBar = smem_u32(&bars[8]), accumBar = smem_u32(&bars[16]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tileN = blockIdx.x % P.nTiles, tileM = blockIdx.x / P.nTiles;
+  const int row0 = tileM * BM;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P.stages; ++s) { mbar_init(fullBar + 8 * s, 128 + 1); mbar_init(emptyBar + 8 * s, 1); }
+    mbar_init(accumBar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) { // tensor memory for the 128 x BN fp32 accumulator
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmemBase)), "r"((uint32_t)P.tmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmemBase;
+
+  if (warp < 4) {
+    // ------------------------------------------------------------ gather producers
+    const int t = threadIdx.x, chunk = t & 7, rbase = t >> 3;
+    const int sw = (chunk ^ (rbase & 7)) << 4;
+    int src[8];
+    int curF = -1;
+    for (int s = 0; s < P.nSlabs; ++s) {
+      const int st = s % P.stages, it = s / P.stages;
+      const int k0 = s * SLAB, f = k0 / P.nIn, c0 = k0 - f * P.nIn;
+      if (f != curF) { // the rule column changes: refresh the 8 source rows of this thread
+        curF = f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int r = row0 + rbase + 16 * i;
+          src[i] = (r < P.rows) ? (P.rules ? __ldg(P.rules + (long long)r * P.fs + f) : r) : -1;
+        }
+      }
+      float4 v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        v[i] = src[i] >= 0 ? __ldg(reinterpret_cast<const float4 *>(P.in + (long long)src[i] * P.nIn + c0) + chunk) : make_float4(0.f, 0.f, 0.f, 0.f);
+      mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 1);
+      unsigned char *aHi = smem + (size_t)st * stageBytes, *aLo = aHi + A_HALF;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = rbase + 16 * i;
+        const int off = (r >> 3) * 1024 + (r & 7) * ROW_BYTES + sw;
+        float4 hi, lo;
+        hi.x = to_tf32(v[i].x); hi.y = to_tf32(v[i].y); hi.z = to_tf32(v[i].z); hi.w = to_tf32(v[i].w);
+        lo.x = to_tf32(v[i].x - hi.x); lo.y = to_tf32(v[i].y - hi.y); lo.z = to_tf32(v[i].z - hi.z); lo.w = to_tf32(v[i].w - hi.w);
+        *reinterpret_cast<float4 *>(aHi + off) = hi;
+        *reinterpret_cast<float4 *>(aLo + off) = lo;
+      }
+      fence_async_smem(); // make the generic-proxy stores visible to the tensor core's reads
+      mbar_arrive(fullBar + 8 * st);
+    }
+    // ------------------------------------------------------------ epilogue
+    mbar_wait(accumBar, 0, 2);
+    tc_fence_after();
+    const int r = row0 + warp * 32 + lane;
+    const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
+    const int col0 = tileN * P.BN;
+    for (int c = 0; c < P.BN; c += 16) {
+      uint32_t a[16];
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                   : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]),
+                     "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15])
+                   : "r"(laneAddr + (uint32_t)c));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (r < P.rows) {
+        float *o = P.out + (long long)r * P.N + col0 + c;
+#pragma unroll
+        for (int q = 0; q < 16; q += 4) {
+          const int col = col0 + c + q;
+          if (col + 3 < P.N) {
+            float4 w;
+            float *wv = reinterpret_cast<float *>(&w);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
+              float x = P.p * __uint_as_float(a[q + e]) + P.p * __ldg(P.bias + col + e);
+              wv[e] = activate(x, P.act, P.prelu ? __ldg(P.prelu + col + e) : 0.f);
+            }
+            *reinterpret_cast<float4 *>(o + q) = w;
+          } else {
+            for (int e = 0; e < 4; ++e)
+              if (col + e < P.N) {
+                float x = P.p * __uint_as_float(a[q + e]) + P.p * __ldg(P.bias + col + e);
+                o[q + e] = activate(x, P.act, P.prelu ? __ldg(P.prelu + col + e) : 0.f);
+              }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  } else if (warp == 4) {
+    // ------------------------------------------------------------ weight tiles by bulk copy
+    if (lane == 0) {
+      const uint32_t bytes = 2 * bHalf;
+      const unsigned char *srcBase = P.packed + (size_t)tileN * P.nSlabs * bytes;
+      for (int s = 0; s < P.nSlabs; ++s) {
+        const int st = s % P.stages, it = s / P.stages;
+        mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 3);
+        mbar_arrive_expect_tx(fullBar + 8 * st, bytes);
+        bulk_g2s(smem_u32(smem + (size_t)st * stageBytes + 2 * A_HALF), srcBase + (size_t)s * bytes, bytes, fullBar + 8 * st);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      for (int s = 0; s < P.nSlabs; ++s) {
+        const int st = s % P.stages, it = s / P.stages;
+        mbar_wait(fullBar + 8 * st, it & 1, 4);
+        tc_fence_after();
+        const uint32_t aHi = smem_u32(smem + (size_t)st * stageBytes), aLo = aHi + A_HALF;
+        const uint32_t bHi = aHi + 2 * A_HALF, bLo = bHi + bHalf;
+        const uint64_t dAhi = smem_desc(aHi), dAlo = smem_desc(aLo), dBhi = smem_desc(bHi), dBlo = smem_desc(bLo);
+        // small cross terms first, the dominant hi*hi product last
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_tf32(tmem, dAlo + 2 * k, dBhi + 2 * k, P.idesc, (s | k) != 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_tf32(tmem, dAhi + 2 * k, dBlo + 2 * k, P.idesc, 1);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_tf32(tmem, dAhi + 2 * k, dBhi + 2 * k, P.idesc, 1);
+        mma_commit(emptyBar + 8 * st); // frees the stage once these MMAs have read it
+      }
+      mma_commit(accumBar);
+    }
+  }
+  __syncwarp(); // the single-thread roles rejoin their warps before the block-wide barrier
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)P.tmemCols) : "memory");
+  }
+}
+
+// W[K x N] row-major -> per (column tile, K slab) one contiguous block: the hi image then the lo
+// image of the [BN x 32] K-major tile, already in the SWIZZLE_128B shared-memory order.
+__global__ void k_pack_tf32(const float *__restrict__ W, int K, int N, int BN, int nTiles, int nSlabs, float *__restrict__ packed) {
+  const long long total = (long long)nTiles * nSlabs * BN * SLAB;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < total; q += (long long)gridDim.x * blockDim.x) {
+    const int kl = (int)(q % SLAB);
+    const int nl = (int)((q / SLAB) % BN);
+    const long long blk = q / ((long long)SLAB * BN);
+    const int slab = (int)(blk % nSlabs), tile = (int)(blk / nSlabs);
+    const int k = slab * SLAB + kl, n = tile * BN + nl;
+    const float w = (k < K && n < N) ? W[(long long)k * N + n] : 0.f;
+    const float hi = to_tf32(w), lo = to_tf32(w - hi);
+    const int off = (nl >> 3) * 1024 + (nl & 7) * ROW_BYTES + ((((kl >> 2) ^ (nl & 7))) << 4) + (kl & 3) * 4;
+    float *base = packed + blk * (2LL * BN * SLAB);
+    base[off >> 2] = hi;
+    base[BN * SLAB + (off >> 2)] = lo;
+  }
+}
+
+struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols; size_t smemBytes; };
+
+bool make_tiling(int K, int N, Tiling *t) {
+  if (K % SLAB != 0 || N < 16) return false;
+  t->nTiles = (N + 255) / 256;
+  t->BN = ((N + t->nTiles - 1) / t->nTiles + 15) / 16 * 16;
+  t->nSlabs = K / SLAB;
+  const int stageBytes = 2 * A_HALF + 2 * t->BN * ROW_BYTES;
+  int stages = (int)((220 * 1024 - 1024) / stageBytes);
+  if (stages > 4) stages = 4;
+  if (stages < 2) return false;
+  t->stages = stages;
+  int cols = 32;
+  while (cols < t->BN) cols *= 2;
+  t->tmemCols = cols;
+  t->smemBytes = (size_t)stages * stageBytes + 1024;
+  return true;
+}
+
+} // namespace
+
+bool tc_shape_ok(int fs, int nIn, int N, int precision) {
+  if (precision != SCN_PREC_3XTF32) return false;
+  Tiling t;
+  return nIn % SLAB == 0 && N % 4 == 0 && make_tiling(fs * nIn, N, &t);
+}
+
+size_t tc_packed_bytes(int K, int N, int precision) {
+  if (precision != SCN_PREC_3XTF32) return 0;
+  Tiling t;
+  if (!make_tiling(K, N, &t)) return 0;
+  return (size_t)t.nTiles * t.nSlabs * 2 * t.BN * ROW_BYTES;
+}
+
+int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaStream_t s) {
+  Tiling t;
+  if (precision != SCN_PREC_3XTF32 || !make_tiling(K, N, &t)) return fail(SCN_ERR_UNSUPPORTED, "no tensor-core layout for this shape/precision");
+  const long long total = (long long)t.nTiles * t.nSlabs * t.BN * SLAB;
+  k_pack_tf32<<<grid_for(total, 256), 256, 0, s>>>(d_W, K, N, t.BN, t.nTiles, t.nSlabs, (float *)d_packed);
+  SCN_LAUNCH_CHECK("k_pack_tf32");
+  return SCN_OK;
+}
+
+int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed, const float *d_B,
+              const float *d_prelu, int N, float p, int act, int precision, float *d_out, cudaStream_t s) {
+  Tiling t;
+  if (precision != SCN_PREC_3XTF32 || nIn % SLAB != 0 || N % 4 != 0 || !make_tiling(fs * nIn, N, &t))
+    return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
+  if (((uintptr_t)d_in | (uintptr_t)d_out | (uintptr_t)d_packed) & 15) return fail(SCN_ERR_INVALID, "tensor-core path needs 16-byte aligned buffers");
+  static bool attrSet[64] = {false};
+  int dev = 0;
+  SCN_CUDA_TRY(cudaGetDevice(&dev));
+  if (!attrSet[dev & 63]) {
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 256));
+    attrSet[dev & 63] = true;
+  }
+  Params P;
+  P.in = d_in; P.rules = d_rules; P.rows = rows; P.fs = fs; P.nIn = nIn;
+  P.packed = (const unsigned char *)d_packed; P.bias = d_B; P.prelu = d_prelu;
+  P.N = N; P.BN = t.BN; P.nTiles = t.nTiles; P.nSlabs = t.nSlabs; P.stages = t.stages; P.tmemCols = t.tmemCols;
+  P.p = p; P.act = act; P.out = d_out;
+  // instruction descriptor: D = fp32, A = B = tf32, both K-major, N = BN, M = 128
+  P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(t.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  const int mTiles = (rows + BM - 1) / BM;
+  k_conv_nin_tc<<<mTiles * t.nTiles, NUM_THREADS, t.smemBytes, s>>>(P);
+  SCN_LAUNCH_CHECK("k_conv_nin_tc");
+  return SCN_OK;
+}
+
+int tc_take_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+  return v;
+}
+
 } // namespace scn

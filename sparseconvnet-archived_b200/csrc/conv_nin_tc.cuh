@@ -11,4 +11,7 @@ int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaS
 int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed,
               const float *d_B, const float *d_prelu, int N, float p, int act, int precision, float *d_out,
               cudaStream_t s);
+// Error code a bounded wait of the kernel recorded since the last call (0 = none); waits for
+// the device and clears it.  1 gather/empty, 2 epilogue/accumulator, 3 weight copy/empty, 4 MMA/full.
+int tc_take_error();
 } // namespace scn

@@ -106,6 +106,62 @@ def test_conv_nin_fp32(abi, oracle, rows_in, rows_out, fs, nIn, N, act, p):
     assert relerr(out.cpu().numpy(), ref) < RTOL_FP32
 
 
+CONV_TC = [
+    # rows_in, rows_out, fs, nIn, N, act, p
+    (200, 300, 4, 32, 64, "VLEAKYRELU", 1.0),     # one column tile, 4 slabs
+    (500, 1000, 4, 96, 192, "VLEAKYRELU", 0.9),   # the shape of the benchmark's second convolution
+    (300, 257, 9, 32, 288, "RELU", 1.0),          # two column tiles of 144, ragged last row tile
+    (300, 129, 8, 64, 608, "LEAKYRELU", 0.75),    # three column tiles of 208 (624 > 608: masked edge)
+    (256, 256, 1, 608, 32, "NOSIGMOID", 1.0),     # plain NiN, 19 slabs
+    (100, 90, 4, 128, 416, "PRELU", 1.0),
+    (64, 50, 27, 32, 96, "TANH", 1.0),
+]
+
+
+@pytest.mark.parametrize("rows_in,rows_out,fs,nIn,N,act,p", CONV_TC)
+def test_conv_nin_tensor_core_3xtf32(abi, oracle, rows_in, rows_out, fs, nIn, N, act, p):
+    """tcgen05 kind::tf32 with hi/lo split of both operands: fp32-grade, same 1e-4 bound."""
+    from oracle import orc
+    rng = np.random.default_rng(rows_out + fs * 7 + N)
+    actc = getattr(orc, act)
+    K = fs * nIn
+    feat = rng.standard_normal((rows_in, nIn)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * np.sqrt(2.0 / K)).astype(np.float32)
+    B = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    prelu = rng.uniform(0.1, 0.4, N).astype(np.float32) if act == "PRELU" else None
+    if fs == 1:
+        rows_out, rules, X = rows_in, None, feat
+    else:
+        rules = random_rules(rng, rows_out, fs, rows_in)
+        X = oracle.gather(feat, rules, nIn).reshape(rows_out, K)
+    ref = oracle.nin_forward(X, W, B, prelu, p, actc, accum64=True)
+    dW = torch.from_numpy(W).cuda()
+    packed = abi.pack_weights(dW, abi.PREC_3XTF32)
+    out = abi.conv_nin_forward(torch.from_numpy(feat).cuda(),
+                               None if rules is None else torch.from_numpy(rules).cuda().flatten(), fs, dW,
+                               torch.from_numpy(B).cuda(), None if prelu is None else torch.from_numpy(prelu).cuda(),
+                               p, actc, abi.PREC_3XTF32, packed=packed)
+    torch.cuda.synchronize()
+    assert abi.conv_tc_take_error() == 0
+    err = relerr(out.cpu().numpy(), ref)
+    assert err < RTOL_FP32, err
+    # and it is much closer to fp32 than a single tf32 product would be (about 1e-3)
+    assert err < 2e-5
+
+
+def test_tensor_core_path_rejects_unsupported_shapes(abi):
+    f = torch.zeros((4, 24), device="cuda")
+    W = torch.zeros((24, 16), device="cuda")
+    B = torch.zeros(16, device="cuda")
+    with pytest.raises(abi.ScnError):
+        abi.pack_weights(W, abi.PREC_3XTF32)  # K not a multiple of 32
+    with pytest.raises(abi.ScnError):
+        abi.conv_nin_forward(f, None, 1, W, B, precision=abi.PREC_3XTF32, packed=torch.zeros(16, dtype=torch.uint8, device="cuda"))
+    # AUTO falls back to the CUDA-core kernel for such shapes
+    out = abi.conv_nin_forward(f, None, 1, W, B, precision=abi.PREC_AUTO)
+    assert out.shape == (4, 16)
+
+
 def test_conv_nin_rejects_bad_arguments(abi):
     f = torch.zeros((4, 8), device="cuda")
     W = torch.zeros((16, 16), device="cuda")
