@@ -28,6 +28,6 @@ def build(verbose=False):
 
 
 def __getattr__(name):
-    if name in ("abi", "net", "synth"):
+    if name in ("abi", "net", "synth", "shard"):
         return importlib.import_module(__name__ + "." + name)
     raise AttributeError(name)

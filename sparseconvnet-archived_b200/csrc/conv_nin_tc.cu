@@ -8,17 +8,20 @@
 // straddles two filter cells and every A row of a slab is 128 contiguous bytes of one input
 // row named by the rulebook.
 //
-//   warps 0-3  gather: 16-byte loads of the rows the rules name (zeros for a negative rule or
-//              a row past the end), split each fp32 into tf32 hi + tf32 lo, store both into
-//              shared memory in the canonical K-major SWIZZLE_128B layout, fence to the async
-//              proxy, arrive on the stage's "full" barrier.  Afterwards the same warps run
-//              the epilogue: tcgen05.ld of their 32 accumulator lanes, p*acc + p*bias,
-//              activation, 16-byte stores.
-//   warp 4     one thread issues a cp.async.bulk per slab for the weight tile (hi and lo
+//   warps 0-3  gather: asynchronous 16-byte copies (cp.async) of the rows the rules name (zero
+//              fill for a negative rule or a row past the end) straight into the canonical
+//              K-major SWIZZLE_128B tile; their completion arrives on the stage's "raw"
+//              barrier, so several slabs are in flight.  Afterwards the same warps run the
+//              epilogue: tcgen05.ld of their 32 accumulator lanes, p*acc + p*bias, activation,
+//              16-byte stores.
+//   warps 4-7  split: once a raw tile has landed, rewrite each fp32 as tf32 hi (in place) and
+//              write tf32 lo = x - hi into the second image, fence to the async proxy, arrive
+//              on the stage's "full" barrier.
+//   warp 8     one thread issues a cp.async.bulk per slab for the weight tile (hi and lo
 //              images, pre-split, pre-transposed and pre-swizzled once by tc_pack, so the
 //              copy is a plain contiguous block into this CTA's own shared memory; no
 //              tensor map is needed).
-//   warp 5     allocates tensor memory; one thread issues, per slab, 3 x 4 tcgen05.mma
+//   warp 9     allocates tensor memory; one thread issues, per slab, 3 x 4 tcgen05.mma
 //              (kind::tf32, M=128, N=BN, K=8): A_lo*B_hi + A_hi*B_lo + A_hi*B_hi, which
 //              restores fp32-grade accuracy from tf32 products ("3xTF32"), then
 //              tcgen05.commit onto the stage's "empty" barrier.
@@ -39,7 +42,7 @@ constexpr int BM = 128;          // rows per CTA tile (UMMA M)
 constexpr int SLAB = 32;         // fp32 values of K per pipeline stage
 constexpr int ROW_BYTES = 128;   // bytes of one smem row (SLAB * 4)
 constexpr int A_HALF = BM * ROW_BYTES; // 16 KB: one of A_hi / A_lo
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // 2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -111,30 +114,53 @@ __device__ __forceinline__ float to_tf32(float x) {
 struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
-  int N, BN, nTiles, nSlabs, stages, tmemCols; float p; int act; float *out; uint32_t idesc;
+  int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
 };
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(srcBytes) : "memory");
+}
+// The barrier receives one arrival once all cp.async issued so far by this thread have landed.
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+constexpr int MAX_STAGES = 6;
 
 __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) {
   extern __shared__ unsigned char smem_raw[];
+  int *rulesS = reinterpret_cast<int *>(smem_raw); // [128 x fs] rule tile (when it fits)
   // 1024-byte alignment: the swizzle pattern is a function of absolute shared-memory address bits
-  unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + P.rulesBytes + 1023) & ~(uintptr_t)1023);
   const int bHalf = P.BN * ROW_BYTES;            // one of B_hi / B_lo
   const int stageBytes = 2 * A_HALF + 2 * bHalf; // A_hi, A_lo, B_hi, B_lo
-  __shared__ __align__(8) uint64_t bars[2 * 8 + 1];
+  __shared__ __align__(8) uint64_t bars[3 * MAX_STAGES + 1];
   __shared__ uint32_t tmemBase;
-  const uint32_t fullBar = smem_u32(&bars[0]), emptyBar = smem_u32(&bars[8]), accumBar = smem_u32(&bars[16]);
+  const uint32_t rawBar = smem_u32(&bars[0]), fullBar = smem_u32(&bars[MAX_STAGES]), emptyBar = smem_u32(&bars[2 * MAX_STAGES]),
+                 accumBar = smem_u32(&bars[3 * MAX_STAGES]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tileN = blockIdx.x % P.nTiles, tileM = blockIdx.x / P.nTiles;
   const int row0 = tileM * BM;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < P.stages; ++s) { mbar_init(fullBar + 8 * s, 128 + 1); mbar_init(emptyBar + 8 * s, 1); }
+    for (int s = 0; s < P.stages; ++s) {
+      mbar_init(rawBar + 8 * s, 128);      // the gather threads' cp.async completions
+      mbar_init(fullBar + 8 * s, 128 + 1); // the split threads + the weight copy
+      mbar_init(emptyBar + 8 * s, 1);      // tcgen05.commit
+    }
     mbar_init(accumBar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) { // tensor memory for the 128 x BN fp32 accumulator
+  if (warp == 9) { // tensor memory for the 128 x BN fp32 accumulator
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmemBase)), "r"((uint32_t)P.tmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (P.rulesBytes > 0) { // this tile's rules, so the gather does not chain two global loads per slab
+    const int n = BM * P.fs;
+    for (int e = threadIdx.x; e < n; e += NUM_THREADS) {
+      const int r = row0 + e / P.fs;
+      rulesS[e] = (r < P.rows) ? __ldg(P.rules + (long long)row0 * P.fs + e) : -1;
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -142,40 +168,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   const uint32_t tmem = tmemBase;
 
   if (warp < 4) {
-    // ------------------------------------------------------------ gather producers
+    // ------------------------------------------------------------ gather: asynchronous 16-byte copies
     const int t = threadIdx.x, chunk = t & 7, rbase = t >> 3;
     const int sw = (chunk ^ (rbase & 7)) << 4;
-    int src[8];
-    int curF = -1;
     for (int s = 0; s < P.nSlabs; ++s) {
       const int st = s % P.stages, it = s / P.stages;
       const int k0 = s * SLAB, f = k0 / P.nIn, c0 = k0 - f * P.nIn;
-      if (f != curF) { // the rule column changes: refresh the 8 source rows of this thread
-        curF = f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int r = row0 + rbase + 16 * i;
-          src[i] = (r < P.rows) ? (P.rules ? __ldg(P.rules + (long long)r * P.fs + f) : r) : -1;
-        }
-      }
-      float4 v[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        v[i] = src[i] >= 0 ? __ldg(reinterpret_cast<const float4 *>(P.in + (long long)src[i] * P.nIn + c0) + chunk) : make_float4(0.f, 0.f, 0.f, 0.f);
       mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 1);
-      unsigned char *aHi = smem + (size_t)st * stageBytes, *aLo = aHi + A_HALF;
+      const uint32_t aRaw = smem_u32(smem + (size_t)st * stageBytes);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int r = rbase + 16 * i;
-        const int off = (r >> 3) * 1024 + (r & 7) * ROW_BYTES + sw;
-        float4 hi, lo;
-        hi.x = to_tf32(v[i].x); hi.y = to_tf32(v[i].y); hi.z = to_tf32(v[i].z); hi.w = to_tf32(v[i].w);
-        lo.x = to_tf32(v[i].x - hi.x); lo.y = to_tf32(v[i].y - hi.y); lo.z = to_tf32(v[i].z - hi.z); lo.w = to_tf32(v[i].w - hi.w);
-        *reinterpret_cast<float4 *>(aHi + off) = hi;
-        *reinterpret_cast<float4 *>(aLo + off) = lo;
+        const int rl = rbase + 16 * i, r = row0 + rl;
+        int src;
+        if (P.rulesBytes > 0) src = rulesS[rl * P.fs + f];
+        else if (P.rules) src = (r < P.rows) ? __ldg(P.rules + (long long)r * P.fs + f) : -1;
+        else src = (r < P.rows) ? r : -1;
+        const uint32_t dst = aRaw + (rl >> 3) * 1024 + (rl & 7) * ROW_BYTES + sw;
+        // a negative rule (or a row past the end) copies 0 source bytes: the 16 bytes are zero-filled
+        const float *g = src >= 0 ? P.in + (long long)src * P.nIn + c0 + chunk * 4 : P.in;
+        cp_async16(dst, g, src >= 0 ? 16u : 0u);
       }
-      fence_async_smem(); // make the generic-proxy stores visible to the tensor core's reads
-      mbar_arrive(fullBar + 8 * st);
+      cp_async_arrive(rawBar + 8 * st);
     }
     // ------------------------------------------------------------ epilogue
     mbar_wait(accumBar, 0, 2);
@@ -216,7 +229,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
       }
     }
     tc_fence_before();
-  } else if (warp == 4) {
+  } else if (warp < 8) {
+    // ------------------------------------------------------------ split: fp32 -> tf32 hi (in place) + tf32 lo
+    const int t = threadIdx.x - 128;
+    for (int s = 0; s < P.nSlabs; ++s) {
+      const int st = s % P.stages, it = s / P.stages;
+      mbar_wait(rawBar + 8 * st, it & 1, 5);
+      unsigned char *aHi = smem + (size_t)st * stageBytes, *aLo = aHi + A_HALF;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int off = t * 16 + i * 2048; // the swizzle is the same in both images: work on raw offsets
+        const float4 v = *reinterpret_cast<const float4 *>(aHi + off);
+        float4 hi, lo;
+        hi.x = to_tf32(v.x); hi.y = to_tf32(v.y); hi.z = to_tf32(v.z); hi.w = to_tf32(v.w);
+        lo.x = to_tf32(v.x - hi.x); lo.y = to_tf32(v.y - hi.y); lo.z = to_tf32(v.z - hi.z); lo.w = to_tf32(v.w - hi.w);
+        *reinterpret_cast<float4 *>(aHi + off) = hi;
+        *reinterpret_cast<float4 *>(aLo + off) = lo;
+      }
+      fence_async_smem(); // make the generic-proxy stores visible to the tensor core's reads
+      mbar_arrive(fullBar + 8 * st);
+    }
+  } else if (warp == 8) {
     // ------------------------------------------------------------ weight tiles by bulk copy
     if (lane == 0) {
       const uint32_t bytes = 2 * bHalf;
@@ -252,7 +285,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   }
   __syncwarp(); // the single-thread roles rejoin their warps before the block-wide barrier
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)P.tmemCols) : "memory");
   }
@@ -277,22 +310,23 @@ __global__ void k_pack_tf32(const float *__restrict__ W, int K, int N, int BN, i
   }
 }
 
-struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols; size_t smemBytes; };
+struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; size_t smemBytes; };
 
-bool make_tiling(int K, int N, Tiling *t) {
+bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
   if (K % SLAB != 0 || N < 16) return false;
+  t->rulesBytes = (haveRules && fs <= 32) ? BM * fs * 4 : 0;
   t->nTiles = (N + 255) / 256;
   t->BN = ((N + t->nTiles - 1) / t->nTiles + 15) / 16 * 16;
   t->nSlabs = K / SLAB;
   const int stageBytes = 2 * A_HALF + 2 * t->BN * ROW_BYTES;
-  int stages = (int)((220 * 1024 - 1024) / stageBytes);
-  if (stages > 4) stages = 4;
+  int stages = (int)((226 * 1024 - 1024 - t->rulesBytes) / stageBytes);
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) return false;
   t->stages = stages;
   int cols = 32;
   while (cols < t->BN) cols *= 2;
   t->tmemCols = cols;
-  t->smemBytes = (size_t)stages * stageBytes + 1024;
+  t->smemBytes = (size_t)stages * stageBytes + 1024 + t->rulesBytes;
   return true;
 }
 
@@ -301,19 +335,19 @@ bool make_tiling(int K, int N, Tiling *t) {
 bool tc_shape_ok(int fs, int nIn, int N, int precision) {
   if (precision != SCN_PREC_3XTF32) return false;
   Tiling t;
-  return nIn % SLAB == 0 && N % 4 == 0 && make_tiling(fs * nIn, N, &t);
+  return nIn % SLAB == 0 && N % 4 == 0 && make_tiling(fs * nIn, N, fs, true, &t);
 }
 
 size_t tc_packed_bytes(int K, int N, int precision) {
   if (precision != SCN_PREC_3XTF32) return 0;
   Tiling t;
-  if (!make_tiling(K, N, &t)) return 0;
+  if (!make_tiling(K, N, 1, false, &t)) return 0;
   return (size_t)t.nTiles * t.nSlabs * 2 * t.BN * ROW_BYTES;
 }
 
 int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaStream_t s) {
   Tiling t;
-  if (precision != SCN_PREC_3XTF32 || !make_tiling(K, N, &t)) return fail(SCN_ERR_UNSUPPORTED, "no tensor-core layout for this shape/precision");
+  if (precision != SCN_PREC_3XTF32 || !make_tiling(K, N, 1, false, &t)) return fail(SCN_ERR_UNSUPPORTED, "no tensor-core layout for this shape/precision");
   const long long total = (long long)t.nTiles * t.nSlabs * t.BN * SLAB;
   k_pack_tf32<<<grid_for(total, 256), 256, 0, s>>>(d_W, K, N, t.BN, t.nTiles, t.nSlabs, (float *)d_packed);
   SCN_LAUNCH_CHECK("k_pack_tf32");
@@ -323,20 +357,20 @@ int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaS
 int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed, const float *d_B,
               const float *d_prelu, int N, float p, int act, int precision, float *d_out, cudaStream_t s) {
   Tiling t;
-  if (precision != SCN_PREC_3XTF32 || nIn % SLAB != 0 || N % 4 != 0 || !make_tiling(fs * nIn, N, &t))
+  if (precision != SCN_PREC_3XTF32 || nIn % SLAB != 0 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t))
     return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
   if (((uintptr_t)d_in | (uintptr_t)d_out | (uintptr_t)d_packed) & 15) return fail(SCN_ERR_INVALID, "tensor-core path needs 16-byte aligned buffers");
   static bool attrSet[64] = {false};
   int dev = 0;
   SCN_CUDA_TRY(cudaGetDevice(&dev));
   if (!attrSet[dev & 63]) {
-    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 256));
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attrSet[dev & 63] = true;
   }
   Params P;
   P.in = d_in; P.rules = d_rules; P.rows = rows; P.fs = fs; P.nIn = nIn;
   P.packed = (const unsigned char *)d_packed; P.bias = d_B; P.prelu = d_prelu;
-  P.N = N; P.BN = t.BN; P.nTiles = t.nTiles; P.nSlabs = t.nSlabs; P.stages = t.stages; P.tmemCols = t.tmemCols;
+  P.N = N; P.BN = t.BN; P.nTiles = t.nTiles; P.nSlabs = t.nSlabs; P.stages = t.stages; P.tmemCols = t.tmemCols; P.rulesBytes = t.rulesBytes;
   P.p = p; P.act = act; P.out = d_out;
   // instruction descriptor: D = fp32, A = B = tf32, both K-major, N = BN, M = 128
   P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(t.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);

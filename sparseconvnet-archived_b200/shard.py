@@ -1,0 +1,60 @@
+"""Sharding of a batch over ranks: samples are independent through every layer (rules, gather
+and pooling are per sample, the GEMM is row-wise), so rank r simply takes a contiguous block
+of samples, builds its own rulebooks and runs its own forward; the single exchange step is an
+all-gather of the final class probabilities.  Works with any torch.distributed backend (NCCL
+on GPUs, gloo in the CPU tests)."""
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n_samples, rank, world):
+    """Contiguous block [lo, hi) of samples for `rank`, sizes differing by at most one."""
+    base, extra = divmod(n_samples, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def balanced_ranges(site_counts, world):
+    """Contiguous blocks with nearly equal numbers of ACTIVE SITES (the cost driver when samples
+    differ in size).  Returns world+1 boundaries."""
+    c = np.concatenate([[0], np.cumsum(np.asarray(site_counts, np.int64))])
+    total = c[-1]
+    bounds = [0]
+    for r in range(1, world):
+        target = total * r / world
+        i = int(np.searchsorted(c, target, side="left"))
+        i = min(max(i, bounds[-1]), len(site_counts))
+        # pick the nearer of the two candidate cuts
+        if i > bounds[-1] and abs(c[i - 1] - target) <= abs(c[i] - target):
+            i -= 1
+        bounds.append(max(i, bounds[-1]))
+    bounds.append(len(site_counts))
+    return bounds
+
+
+def take_samples(keys, off, feats, lo, hi):
+    """Slice a flat batch (keys, off, feats) to samples [lo, hi), renumbering rows from 0."""
+    r0, r1 = int(off[lo]), int(off[hi])
+    return keys[r0:r1], (off[lo:hi + 1] - r0).astype(np.int32), feats[r0:r1]
+
+
+def gather_probabilities(local, group=None):
+    """All-gather equal-sized [n x C] blocks into [world*n x C] in rank order."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return local
+    out = torch.empty((dist.get_world_size(group) * local.shape[0],) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+    return out
+
+
+def gather_ragged(local, counts, group=None):
+    """All-gather [n_r x C] blocks of different sizes (counts[r] rows from rank r): pad to the
+    largest, gather, cut."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return local
+    m = int(max(counts))
+    pad = torch.zeros((m,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    pad[: local.shape[0]] = local
+    g = gather_probabilities(pad, group)
+    return torch.cat([g[r * m: r * m + int(counts[r])] for r in range(len(counts))])
