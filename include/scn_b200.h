@@ -103,6 +103,29 @@ int scn_rules_build(const scn_regions_t *r, int batch, const int *d_in_keys, con
                     int *d_out_bg, int *d_rules, int rows_out_capacity, int *d_result,
                     void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
 
+/* scn_rules_build for callers that cannot allocate device memory (no counterpart in the
+ * reference, whose rule construction runs on the host).  Hosts embedded in a framework that
+ * owns the GPU's memory, code on a latency-critical path that must stay clear of cudaMalloc
+ * (it can lock and synchronise the whole device), or a plugin loaded after a pool has taken
+ * all free memory still pass their own input and output buffers, but the scratch comes from a
+ * fixed array of SCN_RULES_STATIC_SCRATCH_BYTES compiled into the library; each GPU that loads
+ * the library keeps that much memory reserved until the process exits.  The call allocates and
+ * frees nothing.  Arguments and results are those of scn_rules_build without the workspace.
+ *   - A build whose scn_rules_workspace_bytes() exceeds the array is refused with
+ *     SCN_ERR_WORKSPACE and a message naming both sizes.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress): make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  It keeps the last call's contents and the
+ *     kernels clear what they need cleared, so back-to-back calls on one stream are fine;
+ *     calls that can overlap on the GPU (different streams, different threads) race and
+ *     corrupt each other's rules. */
+#define SCN_RULES_STATIC_SCRATCH_BYTES (16u << 20)
+size_t scn_rules_static_scratch_bytes(void);
+int scn_rules_build_static(const scn_regions_t *r, int batch, const int *d_in_keys, const int *d_in_off,
+                           const int *d_in_bg, int rows_in_bound, int *d_out_keys, int *d_out_off,
+                           int *d_out_bg, int *d_rules, int rows_out_capacity, int *d_result,
+                           scn_stream_t stream);
+
 /* Replaces terminalGridPoolingRules() looped over a batch (TerminalPoolingLayer.cu:8-20,
  * 81-99): row b lists sample b's rows in ascending key order (its background row if it has
  * no site), padded with -1 to S columns; the output grid is one site (key 0) per sample.

@@ -19,7 +19,7 @@ DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
 
 EXPORTS = [
     "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
-    "scn_rules_workspace_bytes", "scn_rules_build", "scn_terminal_rules_workspace_bytes",
+    "scn_rules_workspace_bytes", "scn_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_terminal_rules_workspace_bytes",
     "scn_terminal_rules_build", "scn_conv_nin_forward", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward",
@@ -54,6 +54,8 @@ def lib():
         L.scn_rules_workspace_bytes.restype = c_sz
         L.scn_rules_workspace_bytes.argtypes = [c_p, c_int, c_int]
         L.scn_rules_build.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_p, c_p, c_sz, c_p]
+        L.scn_rules_static_scratch_bytes.restype = c_sz
+        L.scn_rules_build_static.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_p, c_p]
         L.scn_terminal_rules_workspace_bytes.restype = c_sz
         L.scn_terminal_rules_workspace_bytes.argtypes = [c_int] * 4
         L.scn_terminal_rules_build.argtypes = [c_int, c_int, c_int, c_p, c_p, c_p, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]
@@ -208,3 +210,25 @@ def kernel_launch_count():
 
 def conv_tc_take_error():
     return int(lib().scn_conv_tc_take_error())
+
+
+def rules_build_static(R, keys, off, bg, rows_out_capacity, out=None):
+    """scn_rules_build_static: the rule build whose scratch is the library's fixed device array,
+    for callers that must not allocate.  Pass `out` (a dict from an earlier call) to reuse its
+    output tensors, so that the call itself creates no tensor at all."""
+    L = lib()
+    batch = bg.numel()
+    sd = L.scn_regions_cells(ctypes.byref(R))
+    if sd < 0:
+        raise ScnError("invalid argument: %s" % L.scn_last_error().decode())
+    if out is None:
+        dev = keys.device
+        out = dict(out_keys=torch.empty(max(rows_out_capacity, 1), dtype=torch.int32, device=dev),
+                   out_off=torch.empty(batch + 1, dtype=torch.int32, device=dev),
+                   out_bg=torch.empty(batch, dtype=torch.int32, device=dev),
+                   rules=torch.empty(max(rows_out_capacity, 1) * sd, dtype=torch.int32, device=dev),
+                   result=torch.empty(4, dtype=torch.int32, device=dev), sd=sd)
+    check(L.scn_rules_build_static(ctypes.byref(R), batch, _ptr(_i32(keys)), _ptr(_i32(off)), _ptr(_i32(bg)), keys.numel(),
+                                   _ptr(out["out_keys"]), _ptr(out["out_off"]), _ptr(out["out_bg"]), _ptr(out["rules"]),
+                                   rows_out_capacity, _ptr(out["result"]), _stream()))
+    return out

@@ -19,6 +19,7 @@
 // output keys -> fill rule cells.  All pure integer, HBM/L2-bound work; no host
 // synchronisation: every size the kernels need is read from device memory.
 #include "scn_common.cuh"
+#include <mutex>
 
 namespace scn {
 namespace {
@@ -512,4 +513,58 @@ extern "C" int scn_terminal_rules_build(int dim, int spatial_size, int batch, co
                                                                 d_out_keys, d_out_off, d_out_bg, d_result);
   SCN_LAUNCH_CHECK("k_terminal");
   return SCN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rule construction for callers that may not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need rules: code
+// running inside a framework that owns all device memory and forbids foreign allocations, a
+// real-time loop that must not take the allocator's lock or risk a device synchronisation,
+// a plugin loaded after the process has handed every free byte to a memory pool.  For them the
+// scratch that scn_rules_build takes from its caller lives here, in a fixed array inside the
+// library image: every device that loads the library holds these bytes from load until exit.
+namespace {
+constexpr size_t STATIC_SCRATCH_BYTES = (size_t)SCN_RULES_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+// In host code `g_static_scratch` is only a stand-in for the symbol, not a device address; the
+// address is asked from the runtime once per device, with that device current.
+void *g_static_scratch_ptr[64] = {nullptr};
+std::mutex g_static_scratch_mu;
+} // namespace
+
+extern "C" size_t scn_rules_static_scratch_bytes(void) { return STATIC_SCRATCH_BYTES; }
+
+extern "C" int scn_rules_build_static(const scn_regions_t *r, int batch, const int *d_in_keys, const int *d_in_off,
+                                      const int *d_in_bg, int rows_in_bound, int *d_out_keys, int *d_out_off,
+                                      int *d_out_bg, int *d_rules, int rows_out_capacity, int *d_result,
+                                      scn_stream_t stream) {
+  clear_error();
+  Regions R;
+  int st = make_regions(r, &R);
+  if (st != SCN_OK) return st;
+  if (batch < 1 || rows_in_bound < 0) return fail(SCN_ERR_INVALID, "bad batch/row counts");
+  const size_t need = carve(nullptr, batch, R.W, rows_in_bound, R.T).bytes;
+  if (need > STATIC_SCRATCH_BYTES) {
+    set_error("this build needs %zu bytes of scratch but the library's fixed scratch array holds %zu: "
+              "use smaller batches or scn_rules_build with a caller-owned workspace", need, STATIC_SCRATCH_BYTES);
+    return SCN_ERR_WORKSPACE;
+  }
+  int dev = 0;
+  SCN_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SCN_ERR_UNSUPPORTED, "device ordinal beyond 63");
+  void *scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_static_scratch_mu);
+    if (!g_static_scratch_ptr[dev]) { // first call on this device: resolve the array's device address
+      void *p = nullptr;
+      SCN_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+      g_static_scratch_ptr[dev] = p;
+    }
+    scratch = g_static_scratch_ptr[dev];
+  }
+  // Same kernels as the allocating caller's path; they zero every part of the scratch that must
+  // start at zero (bitmap, counts, flags), so what the previous call left behind does not matter.
+  return scn_rules_build(r, batch, d_in_keys, d_in_off, d_in_bg, rows_in_bound, d_out_keys, d_out_off, d_out_bg, d_rules,
+                         rows_out_capacity, d_result, scratch, STATIC_SCRATCH_BYTES, stream);
 }
