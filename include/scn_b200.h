@@ -103,6 +103,32 @@ int scn_rules_build(const scn_regions_t *r, int batch, const int *d_in_keys, con
                     int *d_out_bg, int *d_rules, int rows_out_capacity, int *d_result,
                     void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
 
+/* Replaces the loop "for every layer: layer->preprocess(batch, in, out)" of
+ * BatchProducer::preprocessBatch (BatchProducer.cu:72-75) for the geometry layers
+ * (convolutions and poolings, in network order) with ONE kernel: each sample's whole chain
+ * of grids is built by one CTA in shared memory.  Only for small samples
+ * (scn_rules_chain_supported says whether these layers and this per-sample row bound fit);
+ * larger ones are built layer by layer with scn_rules_build.  Outputs per layer are exactly
+ * those of scn_rules_build; layer l+1 reads layer l's output grid.
+ *   max_rows_per_sample   upper bound on the rows (sites + background row) of one input sample
+ *   rows_hint             0, or the largest number of rows one sample is expected to have in
+ *                         any layer (e.g. 1.25 x what d_result[3] reported for earlier
+ *                         batches): shared memory is sized for it instead of the worst case,
+ *                         more samples run per SM, and a sample that exceeds it sets
+ *                         SCN_DEV_ERR_CAPACITY (rebuild with rows_hint = 0). */
+typedef struct {
+  scn_regions_t regions;
+  int *d_out_keys, *d_out_off, *d_out_bg, *d_rules; /* as in scn_rules_build */
+  int rows_out_capacity;
+  int *d_result; /* [4] as in scn_rules_build */
+} scn_chain_layer_t;
+size_t scn_rules_chain_workspace_bytes(int n_layers, int batch);
+int scn_rules_chain_supported(const scn_chain_layer_t *layers, int n_layers, int batch, int max_rows_per_sample,
+                              int rows_hint);
+int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_layers, int batch, const int *d_in_keys,
+                          const int *d_in_off, const int *d_in_bg, int max_rows_per_sample, int rows_hint,
+                          void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
+
 /* scn_rules_build for callers that cannot allocate device memory (no counterpart in the
  * reference, whose rule construction runs on the host).  Hosts embedded in a framework that
  * owns the GPU's memory, code on a latency-critical path that must stay clear of cudaMalloc

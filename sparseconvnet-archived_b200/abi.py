@@ -19,7 +19,7 @@ DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
 
 EXPORTS = [
     "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
-    "scn_rules_workspace_bytes", "scn_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_terminal_rules_workspace_bytes",
+    "scn_rules_workspace_bytes", "scn_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_terminal_rules_workspace_bytes",
     "scn_terminal_rules_build", "scn_conv_nin_forward", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward",
@@ -28,6 +28,11 @@ EXPORTS = [
 
 class Regions(ctypes.Structure):
     _fields_ = [(n, c_int) for n in ("lattice", "dim", "nIn", "nOut", "size", "stride", "minActive")]
+
+
+class ChainLayer(ctypes.Structure):
+    _fields_ = [("regions", Regions), ("d_out_keys", c_p), ("d_out_off", c_p), ("d_out_bg", c_p), ("d_rules", c_p),
+                ("rows_out_capacity", c_int), ("d_result", c_p)]
 
 
 class ScnError(RuntimeError):
@@ -56,6 +61,10 @@ def lib():
         L.scn_rules_build.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_p, c_p, c_sz, c_p]
         L.scn_rules_static_scratch_bytes.restype = c_sz
         L.scn_rules_build_static.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_p, c_p]
+        L.scn_rules_chain_workspace_bytes.restype = c_sz
+        L.scn_rules_chain_workspace_bytes.argtypes = [c_int, c_int]
+        L.scn_rules_chain_supported.argtypes = [c_p, c_int, c_int, c_int, c_int]
+        L.scn_rules_chain_build.argtypes = [c_p, c_int, c_int, c_p, c_p, c_p, c_int, c_int, c_p, c_sz, c_p]
         L.scn_terminal_rules_workspace_bytes.restype = c_sz
         L.scn_terminal_rules_workspace_bytes.argtypes = [c_int] * 4
         L.scn_terminal_rules_build.argtypes = [c_int, c_int, c_int, c_p, c_p, c_p, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]
@@ -232,3 +241,36 @@ def rules_build_static(R, keys, off, bg, rows_out_capacity, out=None):
                                    _ptr(out["out_keys"]), _ptr(out["out_off"]), _ptr(out["out_bg"]), _ptr(out["rules"]),
                                    rows_out_capacity, _ptr(out["result"]), _stream()))
     return out
+
+
+def rules_chain_build(regions_list, keys, off, bg, max_rows_per_sample, capacities, rows_hint=0):
+    """scn_rules_chain_build: all geometry layers of a network in one kernel.  Returns one
+    output dict per layer (as rules_build), or None if the samples are too large for it."""
+    L = lib()
+    batch = bg.numel()
+    dev = keys.device
+    n = len(regions_list)
+    arr = (ChainLayer * n)()
+    outs = []
+    for i, (R, cap) in enumerate(zip(regions_list, capacities)):
+        sd = L.scn_regions_cells(ctypes.byref(R))
+        if sd < 0:
+            raise ScnError("invalid argument: %s" % L.scn_last_error().decode())
+        o = dict(out_keys=torch.empty(max(cap, 1), dtype=torch.int32, device=dev),
+                 out_off=torch.empty(batch + 1, dtype=torch.int32, device=dev),
+                 out_bg=torch.empty(batch, dtype=torch.int32, device=dev),
+                 rules=torch.empty(max(cap, 1) * sd, dtype=torch.int32, device=dev),
+                 result=torch.empty(4, dtype=torch.int32, device=dev), sd=sd)
+        outs.append(o)
+        arr[i].regions = R
+        arr[i].d_out_keys, arr[i].d_out_off, arr[i].d_out_bg = o["out_keys"].data_ptr(), o["out_off"].data_ptr(), o["out_bg"].data_ptr()
+        arr[i].d_rules, arr[i].rows_out_capacity, arr[i].d_result = o["rules"].data_ptr(), cap, o["result"].data_ptr()
+    if not L.scn_rules_chain_supported(arr, n, batch, max_rows_per_sample, rows_hint):
+        return None
+    nbytes = L.scn_rules_chain_workspace_bytes(n, batch)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    check(L.scn_rules_chain_build(arr, n, batch, _ptr(_i32(keys)), _ptr(_i32(off)), _ptr(_i32(bg)), max_rows_per_sample,
+                                  rows_hint, _ptr(ws), nbytes, _stream()))
+    for o in outs:
+        o["workspace"] = ws
+    return outs

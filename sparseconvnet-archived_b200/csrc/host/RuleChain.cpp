@@ -32,6 +32,32 @@ int *scratchResult() {
   return p.res;
 }
 
+namespace { thread_local std::vector<DeferredBuild> *g_deferred = nullptr; }
+void beginDeferred(std::vector<DeferredBuild> *list) { g_deferred = list; }
+void endDeferred() { g_deferred = nullptr; }
+
+bool runDeferred(std::vector<DeferredBuild> &list, int batch, int maxRowsPerSample, int rowsHint, cudaMemStream &ms) {
+  if (list.empty()) return false;
+  std::vector<scn_chain_layer_t> layers;
+  for (auto &d : list) layers.push_back(d.out);
+  const int n = (int)layers.size();
+  if (rowsHint > 0 && !scn_rules_chain_supported(layers.data(), n, batch, maxRowsPerSample, rowsHint)) rowsHint = 0;
+  if (scn_rules_chain_supported(layers.data(), n, batch, maxRowsPerSample, rowsHint)) {
+    size_t bytes = scn_rules_chain_workspace_bytes(n, batch);
+    void *ws = workspace(bytes);
+    scnSafeCall(scn_rules_chain_build(layers.data(), n, batch, list[0].inKeys, list[0].inOff, list[0].inBg, maxRowsPerSample,
+                                      rowsHint, ws, bytes, ms.stream));
+    return rowsHint > 0;
+  }
+  for (auto &d : list) {
+    size_t bytes = scn_rules_workspace_bytes(&d.R, batch, d.rowsInBound);
+    void *ws = workspace(bytes);
+    scnSafeCall(scn_rules_build(&d.R, batch, d.inKeys, d.inOff, d.inBg, d.rowsInBound, d.out.d_out_keys, d.out.d_out_off,
+                                d.out.d_out_bg, d.out.d_rules, d.out.rows_out_capacity, d.out.d_result, ws, bytes, ms.stream));
+  }
+  return false;
+}
+
 long long enqueueRegions(const scn_regions_t &R, SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
                          SpatiallySparseBatchInterface &output, long long rowsInBound, int *d_result, cudaMemStream &ms) {
   const int sd = scn_regions_cells(&R);
@@ -48,6 +74,18 @@ long long enqueueRegions(const scn_regions_t &R, SpatiallySparseBatch &batch, Sp
   output.sampleOffsets.resize(batch.batchSize + 1);
   output.backgroundRows.resize(batch.batchSize);
   output.rules.resize((int)(bound * sd));
+  if (g_deferred) {
+    DeferredBuild d;
+    d.R = R;
+    d.inKeys = g->siteKeys.dPtr(); d.inOff = g->sampleOffsets.dPtr(); d.inBg = g->backgroundRows.dPtr();
+    d.rowsInBound = (int)rowsInBound;
+    d.out.regions = R;
+    d.out.d_out_keys = output.siteKeys.dPtr(); d.out.d_out_off = output.sampleOffsets.dPtr();
+    d.out.d_out_bg = output.backgroundRows.dPtr(); d.out.d_rules = output.rules.dPtr();
+    d.out.rows_out_capacity = (int)bound; d.out.d_result = d_result;
+    g_deferred->push_back(d);
+    return bound;
+  }
   size_t wsBytes = scn_rules_workspace_bytes(&R, batch.batchSize, (int)rowsInBound);
   void *ws = workspace(wsBytes);
   scnSafeCall(scn_rules_build(&R, batch.batchSize, g->siteKeys.dPtr(), g->sampleOffsets.dPtr(), g->backgroundRows.dPtr(),

@@ -9,6 +9,21 @@ void *workspace(size_t bytes);
 // A small device record array for callers that build one layer at a time.
 int *scratchResult();
 
+// While a list is installed (this thread), enqueueRegions() sizes the output buffers but records
+// the build instead of launching it, so that the caller can hand the whole chain to one kernel.
+struct DeferredBuild {
+  scn_regions_t R;
+  const int *inKeys, *inOff, *inBg;
+  int rowsInBound;
+  scn_chain_layer_t out;
+};
+void beginDeferred(std::vector<DeferredBuild> *list);
+void endDeferred();
+// Run recorded builds: one fused kernel when the samples are small enough, else one
+// scn_rules_build per layer.  rowsHint as in scn_rules_chain_build; returns true if the fused
+// kernel ran with a hint (so a capacity error means "retry with rowsHint = 0").
+bool runDeferred(std::vector<DeferredBuild> &list, int batch, int maxRowsPerSample, int rowsHint, cudaMemStream &ms);
+
 long long enqueueRegions(const scn_regions_t &R, SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
                          SpatiallySparseBatchInterface &output, long long rowsInBound, int *d_result, cudaMemStream &ms);
 void finishRegions(const scn_regions_t &R, SpatiallySparseBatchInterface &output, const int *h_result);

@@ -8,6 +8,7 @@
 #include "MaxPoolingTriangularLayer.h"
 #include "NetworkInNetworkLayer.h"
 #include "NetworkInNetworkPReLULayer.h"
+#include "RuleChain.h"
 #include "SoftmaxClassifier.h"
 #include "TerminalPoolingLayer.h"
 
@@ -16,6 +17,7 @@ void SparseConvNetCUDA::init(int nInputFeatures_, int nClasses_) {
   std::cout << "Sparse CNN - dimension=" << dimension << " nInputFeatures=" << nInputFeatures_ << " nClasses=" << nClasses_ << std::endl;
   nOutputFeatures = nInputFeatures_;
   timing = false;
+  chainRowsHint = 0;
   inputSpatialSize = 0;
   cublasHandle = nullptr;
   batchPool.reserve(nBatchProducerThreads); // interfaces hold pointers into each other: no reallocation later
@@ -136,13 +138,45 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
   int *d_res = chainResults.dPtr();
   long long bound = batch.interfaces[0].nSpatialSites;
   if (timing) cudaSafeCall(cudaEventRecord(events[nL + 1], memStream.stream));
-  for (int i = 0; i < nL; ++i)
-    bound = layers[i]->enqueueRules(batch, batch.interfaces[i], batch.interfaces[i + 1], bound, d_res + 4 * i);
+  // Without terminal pooling (whose build reads its input grid at once) the region builds are
+  // only recorded here and then run together: one fused kernel when the samples are small.
+  bool defer = true;
+  for (auto L : layers) defer = defer && dynamic_cast<TerminalPoolingLayer *>(L) == nullptr;
+  std::vector<rulechain::DeferredBuild> builds;
+  if (defer) rulechain::beginDeferred(&builds);
+  try {
+    for (int i = 0; i < nL; ++i)
+      bound = layers[i]->enqueueRules(batch, batch.interfaces[i], batch.interfaces[i + 1], bound, d_res + 4 * i);
+  } catch (...) {
+    rulechain::endDeferred();
+    throw;
+  }
+  bool hinted = false;
+  if (defer) {
+    rulechain::endDeferred();
+    hinted = rulechain::runDeferred(builds, batch.batchSize, batch.interfaces[0].maxSitesPerSample + 1, chainRowsHint, memStream);
+  }
   if (timing) cudaSafeCall(cudaEventRecord(events[nL + 2], memStream.stream));
   int *h = (int *)memStream.staging(sizeof(int) * 4 * nL);
   cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, memStream.stream));
   cudaSafeCall(cudaStreamSynchronize(memStream.stream)); // the one host wait of the rule chain
   std::vector<int> counts(h, h + 4 * nL); // staging is reused below
+  if (hinted) { // a sample outgrew the shared-memory hint learnt from earlier batches: rebuild for the worst case
+    bool overflow = false;
+    for (int i = 0; i < nL; ++i) overflow = overflow || (layers[i]->changesGeometry && (counts[4 * i + 2] & SCN_DEV_ERR_CAPACITY));
+    if (overflow) {
+      chainRowsHint = 0;
+      rulechain::runDeferred(builds, batch.batchSize, batch.interfaces[0].maxSitesPerSample + 1, 0, memStream);
+      cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, memStream.stream));
+      cudaSafeCall(cudaStreamSynchronize(memStream.stream));
+      counts.assign(h, h + 4 * nL);
+    }
+  }
+  if (defer) { // remember how large samples get, with head-room, for the next batch's shared-memory plan
+    int most = batch.interfaces[0].maxSitesPerSample + 1;
+    for (int i = 0; i < nL; ++i) if (layers[i]->changesGeometry) most = std::max(most, counts[4 * i + 3] + 1);
+    chainRowsHint = std::max(chainRowsHint, most + most / 4 + 32);
+  }
   for (int i = 0; i < nL; ++i) layers[i]->finishRules(batch, batch.interfaces[i], batch.interfaces[i + 1], counts.data() + 4 * i);
 }
 

@@ -62,5 +62,6 @@ private:
   void init(int nInputFeatures, int nClasses);
   vectorCUDA<int> chainResults; // 4 ints per layer
   bool timing;
+  int chainRowsHint; // rows per sample seen so far (+25 %): sizes the fused rule chain's shared memory
   std::vector<cudaEvent_t> events; // layers.size()+1 layer boundaries, then rule chain begin/end
 };

@@ -19,7 +19,9 @@
 // output keys -> fill rule cells.  All pure integer, HBM/L2-bound work; no host
 // synchronisation: every size the kernels need is read from device memory.
 #include "scn_common.cuh"
+#include <algorithm>
 #include <mutex>
+#include <vector>
 
 namespace scn {
 namespace {
@@ -415,6 +417,249 @@ int make_regions(const scn_regions_t *r, Regions *out) {
 }
 
 } // namespace
+
+// ---------------------------------------------------------------------------------------------
+// Fused rule chain for small samples: ONE kernel builds the rulebooks of every geometry layer
+// of a network.  CTA = one sample, all of that sample's per-layer state (bitmap + rank
+// directory, key lists, creation flags, prefix sums) lives in shared memory, and the layers
+// are walked in order.  The only thing a sample needs from the others is, per layer, how many
+// output rows the samples before it produced (row ids run on across the batch): each CTA
+// publishes its count and sums its predecessors' counts (bounded spin on a device array).
+// Samples are handed out by an atomic ticket, so every predecessor of a CTA has already
+// started and never waits on a later one.  Same arithmetic as the kernels above, same outputs.
+namespace {
+
+struct ChainLayer {
+  Regions R;
+  int *outKeys, *outOff, *outBg, *rules, *result;
+  int capacity;
+};
+struct ChainParams {
+  const ChainLayer *layers; int nLayers, batch;
+  const int *inKeys, *inOff, *inBg;
+  int *counts;  // [nLayers x batch], -1 until published; value = rows | needBg << 30
+  int *ticket;
+  int rowsMax, wMax, tMax, flagBytes;
+};
+constexpr int CHAIN_THREADS = 256;
+constexpr unsigned long long CHAIN_WAIT_NS = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long chain_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams P) {
+  extern __shared__ __align__(16) unsigned char chain_smem[];
+  __shared__ Regions R;
+  __shared__ int sTicket, sTotal, sBase, sSitesBase;
+  uint2 *dir = reinterpret_cast<uint2 *>(chain_smem);
+  int *keysA = reinterpret_cast<int *>(dir + P.wMax);
+  int *keysB = keysA + P.rowsMax;
+  int *sorted = keysB + P.rowsMax;
+  int *cnt = sorted + P.rowsMax; // rowsMax + 1
+  unsigned char *flags = reinterpret_cast<unsigned char *>(cnt + P.rowsMax + 1);
+  const int tid = threadIdx.x;
+
+  if (tid == 0) sTicket = atomicAdd(P.ticket, 1);
+  __syncthreads();
+  const int b = sTicket;
+  if (b >= P.batch) return;
+
+  int *inKeys = keysA, *outKeysS = keysB;
+  int inBase = P.inOff[b];
+  int nRows = P.inOff[b + 1] - inBase;
+  int inBgGlobal = P.inBg[b];
+  if (nRows > P.rowsMax) { // the caller's bound was wrong: report on every layer and stop
+    if (tid == 0) for (int l = 0; l < P.nLayers; ++l) { atomicOr(P.layers[l].result + 2, SCN_DEV_ERR_CAPACITY); P.counts[l * P.batch + b] = 0; }
+    return;
+  }
+  for (int j = tid; j < nRows; j += CHAIN_THREADS) inKeys[j] = P.inKeys[inBase + j];
+
+  for (int l = 0; l < P.nLayers; ++l) {
+    const ChainLayer &L = P.layers[l];
+    __syncthreads();
+    for (int i = tid; i < (int)(sizeof(Regions) / 4); i += CHAIN_THREADS) reinterpret_cast<int *>(&R)[i] = reinterpret_cast<const int *>(&L.R)[i];
+    for (int w = tid; w < P.wMax; w += CHAIN_THREADS) dir[w] = make_uint2(0u, 0u);
+    __syncthreads();
+    // 1. occupancy bits
+    for (int j = tid; j < nRows; j += CHAIN_THREADS) {
+      const int key = inKeys[j];
+      if (key < 0) continue;
+      if (key >= R.cells) { atomicOr(L.result + 2, SCN_DEV_ERR_KEY); continue; }
+      const unsigned bit = 1u << (key & 31);
+      if (atomicOr(&dir[key >> 5].x, bit) & bit) atomicOr(L.result + 2, SCN_DEV_ERR_DUPLICATE);
+    }
+    __syncthreads();
+    // 2. rank directory
+    int nSites = 0;
+    {
+      int carry = 0;
+      for (int w0 = 0; w0 < R.W; w0 += CHAIN_THREADS) {
+        const int w = w0 + tid;
+        const int c = (w < R.W) ? __popc(dir[w].x) : 0;
+        int total;
+        const int ex = block_exclusive_scan(c, &total);
+        if (w < R.W) dir[w].y = carry + ex;
+        carry += total;
+      }
+      nSites = carry;
+    }
+    __syncthreads();
+    if ((long long)nSites * R.T > P.flagBytes) { // more sites than the caller's hint allowed for
+      if (tid == 0) { atomicOr(L.result + 2, SCN_DEV_ERR_CAPACITY); for (int l2 = l; l2 < P.nLayers; ++l2) P.counts[l2 * P.batch + b] = 0; }
+      return;
+    }
+    // 3. ascending-key order, 4. which outputs each site creates
+    for (int j = tid; j < nRows; j += CHAIN_THREADS) {
+      const int key = inKeys[j];
+      if (key >= 0 && key < R.cells) sorted[cell_rank(dir, key)] = j;
+    }
+    __syncthreads();
+    for (int slot = tid; slot < nSites; slot += CHAIN_THREADS) {
+      int i[4], j[4];
+      decode(inKeys[sorted[slot]], R.nIn, R.dim, i);
+      int c = 0;
+      for (int t = 0; t < R.T; ++t) {
+        const bool f = touched_output(R, i, t, j) && creates(R, dir, i, j);
+        flags[slot * R.T + t] = f;
+        c += f;
+      }
+      cnt[slot] = c;
+    }
+    __syncthreads();
+    // 5. prefix sums of the counts
+    {
+      int carry = 0;
+      for (int s0 = 0; s0 < nSites; s0 += CHAIN_THREADS) {
+        const int s = s0 + tid;
+        const int c = (s < nSites) ? cnt[s] : 0;
+        int total;
+        const int ex = block_exclusive_scan(c, &total);
+        __syncthreads();
+        if (s < nSites) cnt[s] = carry + ex;
+        carry += total;
+      }
+      if (tid == 0) sTotal = carry;
+    }
+    __syncthreads();
+    const int sitesOut = sTotal;
+    const int needBg = sitesOut < R.fullSize;
+    const int rowsOut = sitesOut + needBg;
+    // 6. publish this sample's count, sum the earlier samples' counts
+    if (tid == 0) {
+      __threadfence();
+      atomicExch(P.counts + l * P.batch + b, rowsOut | (needBg << 30));
+      atomicMax(L.result + 3, sitesOut);
+      sBase = 0; sSitesBase = 0;
+    }
+    __syncthreads();
+    {
+      int rowsBefore = 0, bgBefore = 0;
+      for (int p = tid; p < b; p += CHAIN_THREADS) {
+        volatile int *slotp = P.counts + l * P.batch + p;
+        int v = *slotp;
+        if (v < 0) {
+          const unsigned long long t0 = chain_ns();
+          while ((v = *slotp) < 0) {
+            if (chain_ns() - t0 > CHAIN_WAIT_NS) { atomicOr(L.result + 2, SCN_DEV_ERR_CAPACITY); v = 0; break; }
+          }
+        }
+        rowsBefore += v & 0x3fffffff;
+        bgBefore += (v >> 30) & 1;
+      }
+      if (rowsBefore) atomicAdd(&sBase, rowsBefore);
+      if (bgBefore) atomicAdd(&sSitesBase, bgBefore);
+    }
+    __syncthreads();
+    const int base = sBase;
+    const bool fits = base + rowsOut <= L.capacity && rowsOut <= P.rowsMax;
+    if (tid == 0) {
+      L.outOff[b] = base;
+      L.outBg[b] = needBg ? base + sitesOut : -1;
+      if (!fits) atomicOr(L.result + 2, SCN_DEV_ERR_CAPACITY);
+      if (b == P.batch - 1) {
+        L.outOff[P.batch] = base + rowsOut;
+        L.result[0] = base + rowsOut;
+        L.result[1] = base + rowsOut - (sSitesBase + needBg);
+      }
+    }
+    if (!fits) { // keep publishing zero-sized results so nobody behind this sample waits
+      if (tid == 0) for (int l2 = l + 1; l2 < P.nLayers; ++l2) P.counts[l2 * P.batch + b] = 0;
+      return;
+    }
+    // 7. output keys (shared copy for the next layer + the interface's array)
+    for (int p = tid; p < nSites * R.T; p += CHAIN_THREADS) {
+      if (!flags[p]) continue;
+      const int slot = p / R.T, t = p % R.T;
+      int rank = 0;
+      for (int q = 0; q < t; ++q) rank += flags[slot * R.T + q];
+      int i[4], j[4];
+      decode(inKeys[sorted[slot]], R.nIn, R.dim, i);
+      touched_output(R, i, t, j);
+      const int key = encode(j, R.nOut, R.dim);
+      const int lo = cnt[slot] + rank;
+      outKeysS[lo] = key;
+      L.outKeys[base + lo] = key;
+    }
+    if (needBg && tid == 0) { outKeysS[sitesOut] = -1; L.outKeys[base + sitesOut] = -1; }
+    __syncthreads();
+    // 8. rule cells, coalesced over this sample's block of rows
+    for (int q = tid; q < rowsOut * R.sd; q += CHAIN_THREADS) {
+      const int r = q / R.sd, col = q % R.sd;
+      const int key = outKeysS[r];
+      int v = inBgGlobal;
+      if (key >= 0) {
+        int j[4], cc[4], ii[4];
+        decode(key, R.nOut, R.dim, j);
+        decode(R.cellOfCol[col], R.size, R.dim, cc);
+        for (int a = 0; a < R.dim; ++a) ii[a] = j[a] * R.stride + cc[a];
+        const int ck = encode(ii, R.nIn, R.dim);
+        const uint2 e = dir[ck >> 5];
+        if ((e.x >> (ck & 31)) & 1u) v = inBase + sorted[e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
+      }
+      L.rules[(long long)base * R.sd + q] = v;
+    }
+    // the output is the next layer's input
+    int *tmp = inKeys; inKeys = outKeysS; outKeysS = tmp;
+    nRows = rowsOut;
+    inBase = base;
+    inBgGlobal = needBg ? base + sitesOut : -1;
+  }
+}
+
+struct ChainPlan { int rowsMax, wMax, tMax; size_t smemBytes; bool ok; size_t flagBytes; };
+
+// Shared-memory plan.  Without a hint the row bound is the worst case over the layers for a
+// sample with at most `rowsIn` input rows; with a hint (rows per sample the caller expects at
+// most, in any layer) the arrays are sized for the hint and the kernel reports
+// SCN_DEV_ERR_CAPACITY if a sample exceeds it.
+ChainPlan plan_chain(const Regions *Rs, int n, int rowsIn, int rowsHint) {
+  ChainPlan p = {rowsIn, 1, 1, 0, true, 0};
+  long long rows = rowsIn;
+  size_t flagBytes = 0;
+  for (int l = 0; l < n; ++l) {
+    const Regions &R = Rs[l];
+    if (R.W > p.wMax) p.wMax = R.W;
+    if (R.T > p.tMax) p.tMax = R.T;
+    flagBytes = std::max(flagBytes, (size_t)rows * R.T);
+    long long out = std::min(rows * (long long)R.T, (long long)R.fullSize) + 1;
+    rows = out;
+    if (rows > p.rowsMax) p.rowsMax = (int)std::min<long long>(rows, 1 << 28);
+  }
+  if (rowsHint > 0 && rowsHint < p.rowsMax) {
+    p.rowsMax = std::max(rowsHint, rowsIn);
+    flagBytes = (size_t)p.rowsMax * p.tMax;
+  }
+  p.flagBytes = flagBytes;
+  p.smemBytes = (size_t)p.wMax * 8 + (size_t)p.rowsMax * 12 + ((size_t)p.rowsMax + 1) * 4 + flagBytes + 64;
+  p.ok = p.smemBytes <= 200 * 1024;
+  return p;
+}
+
+} // namespace
+
 } // namespace scn
 
 using namespace scn;
@@ -567,4 +812,67 @@ extern "C" int scn_rules_build_static(const scn_regions_t *r, int batch, const i
   // start at zero (bitmap, counts, flags), so what the previous call left behind does not matter.
   return scn_rules_build(r, batch, d_in_keys, d_in_off, d_in_bg, rows_in_bound, d_out_keys, d_out_off, d_out_bg, d_rules,
                          rows_out_capacity, d_result, scratch, STATIC_SCRATCH_BYTES, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+extern "C" size_t scn_rules_chain_workspace_bytes(int n_layers, int batch) {
+  if (n_layers < 1 || batch < 1) return 0;
+  return align_up(sizeof(ChainLayer) * (size_t)n_layers, 256) + align_up(sizeof(int) * ((size_t)n_layers * batch + 1), 256);
+}
+
+extern "C" int scn_rules_chain_supported(const scn_chain_layer_t *layers, int n_layers, int batch, int max_rows_per_sample,
+                                         int rows_hint) {
+  if (!layers || n_layers < 1 || n_layers > 64 || batch < 1 || max_rows_per_sample < 0) return 0;
+  std::vector<Regions> Rs(n_layers);
+  for (int l = 0; l < n_layers; ++l)
+    if (make_regions(&layers[l].regions, &Rs[l]) != SCN_OK) return 0;
+  clear_error();
+  return plan_chain(Rs.data(), n_layers, max_rows_per_sample, rows_hint).ok ? 1 : 0;
+}
+
+extern "C" int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_layers, int batch, const int *d_in_keys,
+                                     const int *d_in_off, const int *d_in_bg, int max_rows_per_sample, int rows_hint,
+                                     void *d_workspace, size_t workspace_bytes, scn_stream_t stream_) {
+  clear_error();
+  if (!layers || n_layers < 1 || n_layers > 64 || batch < 1 || max_rows_per_sample < 0) return fail(SCN_ERR_INVALID, "bad chain arguments");
+  if (!d_in_off || !d_in_bg || !d_workspace) return fail(SCN_ERR_INVALID, "null pointer");
+  std::vector<ChainLayer> h(n_layers);
+  std::vector<Regions> Rs(n_layers);
+  for (int l = 0; l < n_layers; ++l) {
+    int st = make_regions(&layers[l].regions, &Rs[l]);
+    if (st != SCN_OK) return st;
+    if (!layers[l].d_out_keys || !layers[l].d_out_off || !layers[l].d_out_bg || !layers[l].d_rules || !layers[l].d_result)
+      return fail(SCN_ERR_INVALID, "null pointer in a chain layer");
+    if (l > 0 && (Rs[l].nIn != Rs[l - 1].nOut || Rs[l].dim != Rs[l - 1].dim)) return fail(SCN_ERR_INVALID, "chain layers do not fit together");
+    h[l].R = Rs[l];
+    h[l].outKeys = layers[l].d_out_keys; h[l].outOff = layers[l].d_out_off; h[l].outBg = layers[l].d_out_bg;
+    h[l].rules = layers[l].d_rules; h[l].result = layers[l].d_result; h[l].capacity = layers[l].rows_out_capacity;
+  }
+  ChainPlan plan = plan_chain(Rs.data(), n_layers, max_rows_per_sample, rows_hint);
+  if (!plan.ok) return fail(SCN_ERR_UNSUPPORTED, "samples too large for the fused rule chain: build layer by layer with scn_rules_build");
+  if (scn_rules_chain_workspace_bytes(n_layers, batch) > workspace_bytes) return fail(SCN_ERR_WORKSPACE, "workspace smaller than scn_rules_chain_workspace_bytes()");
+  cudaStream_t s = (cudaStream_t)stream_;
+  ChainLayer *dLayers = (ChainLayer *)d_workspace;
+  int *counts = (int *)((char *)d_workspace + align_up(sizeof(ChainLayer) * (size_t)n_layers, 256));
+  int *ticket = counts + (size_t)n_layers * batch;
+  // the descriptors travel through a pinned-free path: a small synchronous-to-stream copy from pageable memory
+  SCN_CUDA_TRY(cudaMemcpyAsync(dLayers, h.data(), sizeof(ChainLayer) * n_layers, cudaMemcpyHostToDevice, s));
+  SCN_CUDA_TRY(cudaMemsetAsync(counts, 0xff, sizeof(int) * (size_t)n_layers * batch, s));
+  SCN_CUDA_TRY(cudaMemsetAsync(ticket, 0, sizeof(int), s));
+  for (int l = 0; l < n_layers; ++l) SCN_CUDA_TRY(cudaMemsetAsync(layers[l].d_result, 0, 4 * sizeof(int), s));
+  static bool attrSet[64] = {false};
+  int dev = 0;
+  SCN_CUDA_TRY(cudaGetDevice(&dev));
+  if (!attrSet[dev & 63]) {
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attrSet[dev & 63] = true;
+  }
+  ChainParams P;
+  P.layers = dLayers; P.nLayers = n_layers; P.batch = batch;
+  P.inKeys = d_in_keys; P.inOff = d_in_off; P.inBg = d_in_bg;
+  P.counts = counts; P.ticket = ticket;
+  P.rowsMax = plan.rowsMax; P.wMax = plan.wMax; P.tMax = plan.tMax; P.flagBytes = (int)std::min<size_t>(plan.flagBytes, 0x7fffffff);
+  k_rule_chain<<<batch, CHAIN_THREADS, plan.smemBytes, s>>>(P);
+  SCN_LAUNCH_CHECK("k_rule_chain");
+  return SCN_OK;
 }

@@ -192,3 +192,69 @@ def test_terminal_rules(abi, oracle):
             np.testing.assert_array_equal(out["out_off"].cpu().numpy(), np.arange(7))
             np.testing.assert_array_equal(out["out_bg"].cpu().numpy(), ref["out_bg"])
             np.testing.assert_array_equal(out["out_keys"].cpu().numpy(), np.zeros(6))
+
+
+CHAINS = [
+    # (lattice, dim, S, [(size, stride, minActive), ...])
+    (0, 2, 24, [(3, 1, 1), (2, 2, 1), (2, 1, 1), (2, 2, 1), (2, 1, 1)]),
+    (0, 2, 26, [(3, 1, -1), (3, 1, 2), (2, 2, 1), (3, 2, 1)]),
+    (0, 3, 12, [(3, 1, 1), (2, 2, 1), (2, 1, 2), (2, 2, 1)]),
+    (1, 3, 11, [(2, 1, 2), (2, 2, 1), (2, 1, 1), (2, 2, 1)]),
+    (1, 2, 14, [(3, 1, 1), (2, 2, 1), (2, 1, 3)]),
+    (0, 1, 21, [(3, 1, 1), (3, 2, 1), (2, 1, 2)]),
+]
+
+
+@pytest.mark.parametrize("lattice,dim,S,steps", CHAINS)
+def test_fused_chain_matches_oracle(abi, oracle, lattice, dim, S, steps):
+    """scn_rules_chain_build (all layers in one kernel) against the oracle layer by layer."""
+    rng = np.random.default_rng(S * 10 + dim)
+    for dens, batch in (([0.02, 0.2, 0.6, 1.0, 0.0], 9), ([0.3], 300)):
+        g = random_grids(rng, batch, dim, S, dens, triangular=(lattice == 1))
+        dk, doff, dbg, _ = to_dev_grid(*g)
+        regs, caps, n, bound = [], [], S, dk.numel()
+        for size, stride, mn in steps:
+            nOut = (n - size) // stride + 1
+            regs.append(abi.regions(lattice, dim, n, nOut, size, stride, mn))
+            T = 1 if mn == -1 else ((size + stride - 1) // stride) ** dim
+            bound = min(bound * T, batch * nOut ** dim) + batch
+            caps.append(bound)
+            n = nOut
+        max_rows = int(np.diff(g[2]).max() + 1)
+        outs = abi.rules_chain_build(regs, dk, doff, dbg, max_rows, caps)
+        assert outs is not None
+        torch.cuda.synchronize()
+        cur, n = g, S
+        for (size, stride, mn), out in zip(steps, outs):
+            nOut = (n - size) // stride + 1
+            ref = oracle.grid_rules(lattice, dim, n, nOut, size, stride, mn, *cur)
+            compare(out, out["result"].cpu().numpy(), ref)
+            assert int(out["result"][3]) == int(np.diff(ref["out_off"]).max())
+            cur = (ref["out_keys"], ref["out_rows"], ref["out_off"], ref["out_bg"])
+            n = nOut
+
+
+def test_fused_chain_declines_large_samples(abi):
+    regs = [abi.regions(0, 3, 48, 46, 3, 1, 1)]
+    z = torch.zeros(4, dtype=torch.int32, device="cuda")
+    assert abi.rules_chain_build(regs, z, z[:2], z[:1], 6000, [200000]) is None
+
+
+def test_fused_chain_row_hint(abi, oracle):
+    """A hint sizes shared memory below the worst case: results are unchanged when it holds and
+    SCN_DEV_ERR_CAPACITY is reported when a sample outgrows it."""
+    rng = np.random.default_rng(77)
+    dim, S, batch = 2, 20, 40
+    g = random_grids(rng, batch, dim, S, [0.1, 0.5])
+    dk, doff, dbg, _ = to_dev_grid(*g)
+    regs = [abi.regions(0, dim, 20, 18, 3, 1, 1), abi.regions(0, dim, 18, 9, 2, 2, 1)]
+    caps = [batch * (18 * 18 + 1), batch * (9 * 9 + 1)]
+    max_rows = int(np.diff(g[2]).max() + 1)
+    ref1 = oracle.grid_rules(0, dim, 20, 18, 3, 1, 1, *g)
+    need = int(np.diff(ref1["out_off"]).max() + 1)
+    good = abi.rules_chain_build(regs, dk, doff, dbg, max_rows, caps, rows_hint=need + 8)
+    torch.cuda.synchronize()
+    compare(good[0], good[0]["result"].cpu().numpy(), ref1)
+    small = abi.rules_chain_build(regs, dk, doff, dbg, max_rows, caps, rows_hint=max_rows + 1)
+    torch.cuda.synchronize()
+    assert int(small[0]["result"][2]) & abi.DEV_ERR_CAPACITY
