@@ -31,6 +31,7 @@ constexpr int MAX_CUBE = 256; // size^dim cells of a receptive field
 struct Regions {
   int lattice, dim, nIn, nOut, size, stride, minActive;
   int sd, cube, Tax, T, W, cells, fullSize;
+  float rNIn, rNOut, rSize, rSd, rT, rTax, rStride; // reciprocals for the float-assisted divisions below
   signed char ord[MAX_CUBE];         // cube cell -> rule column, -1 outside a triangular filter
   unsigned char cellOfCol[MAX_CUBE]; // rule column -> cube cell
 };
@@ -410,6 +411,7 @@ int make_regions(const scn_regions_t *r, Regions *out) {
   if (T > 4096) return fail(SCN_ERR_UNSUPPORTED, "too many touched outputs per input");
   R.T = (int)T;
   R.W = (int)((cells + 31) / 32);
+  R.rNIn = 1.0f / R.nIn; R.rNOut = 1.0f / R.nOut; R.rSize = 1.0f / R.size; R.rSd = 1.0f / R.sd; R.rT = 1.0f / R.T; R.rTax = 1.0f / R.Tax; R.rStride = 1.0f / R.stride;
   if (R.lattice == SCN_LATTICE_SQUARE) R.fullSize = (int)ipowll(R.nOut, R.dim);
   else { long long fs = 1; for (int i = 1; i <= R.dim; ++i) fs = fs * (R.nOut + R.dim - i) / i; R.fullSize = (int)fs; }
   *out = R;
@@ -441,6 +443,76 @@ struct ChainParams {
   int *ticket;
   int rowsMax, wMax, tMax, flagBytes;
 };
+
+// Division of 0 <= x < 2^24 by n with a float reciprocal (quotient off by at most one, then fixed).
+__device__ __forceinline__ int fdiv(int x, int n, float rn, int *rem) {
+  int q = __float2int_rz(__int2float_rn(x) * rn);
+  int r = x - q * n;
+  if (r < 0) { --q; r += n; } else if (r >= n) { ++q; r -= n; }
+  *rem = r;
+  return q;
+}
+template <int DIM> __device__ __forceinline__ void decode_f(int key, int n, float rn, int *c) {
+#pragma unroll
+  for (int a = DIM - 1; a > 0; --a) key = fdiv(key, n, rn, &c[a]);
+  c[0] = key;
+}
+template <int DIM> __device__ __forceinline__ int encode_f(const int *c, int n) {
+  int k = c[0];
+#pragma unroll
+  for (int a = 1; a < DIM; ++a) k = k * n + c[a];
+  return k;
+}
+template <int DIM> __device__ __forceinline__ bool touched_output_f(const Regions &R, const int *i, int t, int *j) {
+  if (R.minActive == -1) {
+    bool ok = true;
+#pragma unroll
+    for (int a = 0; a < DIM; ++a) { ok = ok && i[a] >= 1 && i[a] <= R.nOut; j[a] = i[a] - 1; }
+    return ok;
+  }
+  int sum = 0;
+  bool ok = true;
+#pragma unroll
+  for (int a = DIM - 1; a >= 0; --a) {
+    int ta;
+    t = fdiv(t, R.Tax, R.rTax, &ta);
+    int rem;
+    const int num = i[a] - R.size + R.stride; // outputL = max(0, num / stride): a non-positive num gives 0
+    const int lo = num <= 0 ? 0 : fdiv(num, R.stride, R.rStride, &rem);
+    const int hi = min(fdiv(i[a], R.stride, R.rStride, &rem) + 1, R.nOut);
+    j[a] = lo + ta;
+    ok = ok && j[a] < hi;
+    sum += j[a];
+  }
+  if (R.lattice == SCN_LATTICE_TRIANGULAR && sum >= R.nOut) return false;
+  return ok;
+}
+template <int DIM> __device__ bool creates_f(const Regions &R, const uint2 *d, const int *i, const int *j) {
+  if (R.minActive == -1) return true;
+  int cc[DIM], ii[DIM];
+#pragma unroll
+  for (int a = 0; a < DIM; ++a) cc[a] = 0;
+  int active = 0;
+  bool seenSelf = false;
+  for (int cell = 0; cell < R.cube; ++cell) {
+    bool self = true;
+#pragma unroll
+    for (int a = 0; a < DIM; ++a) { ii[a] = j[a] * R.stride + cc[a]; self = self && ii[a] == i[a]; }
+    if (self) {
+      if (R.minActive <= 1) return true;
+      seenSelf = true;
+      active += (R.ord[cell] >= 0);
+    } else {
+      const bool on = cell_active(d, encode_f<DIM>(ii, R.nIn));
+      if (!seenSelf) { if (on) return false; } // an earlier key got there first
+      else if (R.ord[cell] >= 0) active += on;
+    }
+#pragma unroll
+    for (int a = DIM - 1; a >= 0; --a) { if (++cc[a] < R.size) break; cc[a] = 0; }
+  }
+  return seenSelf && active >= R.minActive;
+}
+
 constexpr int CHAIN_THREADS = 256;
 constexpr unsigned long long CHAIN_WAIT_NS = 2000000000ull;
 
@@ -450,6 +522,7 @@ __device__ __forceinline__ unsigned long long chain_ns() {
   return t;
 }
 
+template <int DIM>
 __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams P) {
   extern __shared__ __align__(16) unsigned char chain_smem[];
   __shared__ Regions R;
@@ -518,11 +591,11 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
     }
     __syncthreads();
     for (int slot = tid; slot < nSites; slot += CHAIN_THREADS) {
-      int i[4], j[4];
-      decode(inKeys[sorted[slot]], R.nIn, R.dim, i);
+      int i[DIM], j[DIM];
+      decode_f<DIM>(inKeys[sorted[slot]], R.nIn, R.rNIn, i);
       int c = 0;
       for (int t = 0; t < R.T; ++t) {
-        const bool f = touched_output(R, i, t, j) && creates(R, dir, i, j);
+        const bool f = touched_output_f<DIM>(R, i, t, j) && creates_f<DIM>(R, dir, i, j);
         flags[slot * R.T + t] = f;
         c += f;
       }
@@ -592,13 +665,14 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
     // 7. output keys (shared copy for the next layer + the interface's array)
     for (int p = tid; p < nSites * R.T; p += CHAIN_THREADS) {
       if (!flags[p]) continue;
-      const int slot = p / R.T, t = p % R.T;
+      int t;
+      const int slot = fdiv(p, R.T, R.rT, &t);
       int rank = 0;
       for (int q = 0; q < t; ++q) rank += flags[slot * R.T + q];
-      int i[4], j[4];
-      decode(inKeys[sorted[slot]], R.nIn, R.dim, i);
-      touched_output(R, i, t, j);
-      const int key = encode(j, R.nOut, R.dim);
+      int i[DIM], j[DIM];
+      decode_f<DIM>(inKeys[sorted[slot]], R.nIn, R.rNIn, i);
+      touched_output_f<DIM>(R, i, t, j);
+      const int key = encode_f<DIM>(j, R.nOut);
       const int lo = cnt[slot] + rank;
       outKeysS[lo] = key;
       L.outKeys[base + lo] = key;
@@ -607,15 +681,17 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
     __syncthreads();
     // 8. rule cells, coalesced over this sample's block of rows
     for (int q = tid; q < rowsOut * R.sd; q += CHAIN_THREADS) {
-      const int r = q / R.sd, col = q % R.sd;
+      int col;
+      const int r = fdiv(q, R.sd, R.rSd, &col);
       const int key = outKeysS[r];
       int v = inBgGlobal;
       if (key >= 0) {
-        int j[4], cc[4], ii[4];
-        decode(key, R.nOut, R.dim, j);
-        decode(R.cellOfCol[col], R.size, R.dim, cc);
-        for (int a = 0; a < R.dim; ++a) ii[a] = j[a] * R.stride + cc[a];
-        const int ck = encode(ii, R.nIn, R.dim);
+        int j[DIM], cc[DIM], ii[DIM];
+        decode_f<DIM>(key, R.nOut, R.rNOut, j);
+        decode_f<DIM>(R.cellOfCol[col], R.size, R.rSize, cc);
+#pragma unroll
+        for (int a = 0; a < DIM; ++a) ii[a] = j[a] * R.stride + cc[a];
+        const int ck = encode_f<DIM>(ii, R.nIn);
         const uint2 e = dir[ck >> 5];
         if ((e.x >> (ck & 31)) & 1u) v = inBase + sorted[e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
       }
@@ -864,7 +940,10 @@ extern "C" int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_laye
   int dev = 0;
   SCN_CUDA_TRY(cudaGetDevice(&dev));
   if (!attrSet[dev & 63]) {
-    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attrSet[dev & 63] = true;
   }
   ChainParams P;
@@ -872,7 +951,12 @@ extern "C" int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_laye
   P.inKeys = d_in_keys; P.inOff = d_in_off; P.inBg = d_in_bg;
   P.counts = counts; P.ticket = ticket;
   P.rowsMax = plan.rowsMax; P.wMax = plan.wMax; P.tMax = plan.tMax; P.flagBytes = (int)std::min<size_t>(plan.flagBytes, 0x7fffffff);
-  k_rule_chain<<<batch, CHAIN_THREADS, plan.smemBytes, s>>>(P);
+  switch (Rs[0].dim) {
+  case 1: k_rule_chain<1><<<batch, CHAIN_THREADS, plan.smemBytes, s>>>(P); break;
+  case 2: k_rule_chain<2><<<batch, CHAIN_THREADS, plan.smemBytes, s>>>(P); break;
+  case 3: k_rule_chain<3><<<batch, CHAIN_THREADS, plan.smemBytes, s>>>(P); break;
+  default: k_rule_chain<4><<<batch, CHAIN_THREADS, plan.smemBytes, s>>>(P); break;
+  }
   SCN_LAUNCH_CHECK("k_rule_chain");
   return SCN_OK;
 }
