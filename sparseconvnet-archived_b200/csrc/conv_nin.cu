@@ -75,6 +75,121 @@ k_conv_nin_simt(const float *__restrict__ in, const int *__restrict__ rules, int
   }
 }
 
+
+// Small contraction (K = fs*nIn <= 64, e.g. the first 3x3 convolution over 3 channels,
+// K = 27): the layer is HBM-bound (it writes rows x N and reads almost nothing), so the
+// kernel is organised around the output write.  The whole W lives in shared memory; a CTA
+// walks row tiles, gathers each tile's A rows into shared memory (transposed, so that four
+// rows' values at one k are one 16-byte read), and each thread owns 4 rows x 4 consecutive
+// columns: per k two 16-byte shared loads feed 16 FMAs, and the epilogue stores float4s that
+// are contiguous across the threads of a row.
+__global__ void __launch_bounds__(256)
+k_conv_nin_smallk(const float *__restrict__ in, const int *__restrict__ rules, int rows, int fs, int nIn,
+                  const float *__restrict__ W, const float *__restrict__ B, const float *__restrict__ prelu, int N,
+                  float p, int act, float *__restrict__ out) {
+  extern __shared__ __align__(16) float sk_smem[];
+  const int K = fs * nIn, NV = N >> 2;
+  const int TY = blockDim.x / NV, TR = TY * 4;
+  float *Ws = sk_smem;           // [K][N]
+  float *As = sk_smem + K * N;   // [K][TR]
+  const int tx = threadIdx.x % NV, ty = threadIdx.x / NV;
+  const bool active = ty < TY;
+  for (int e = threadIdx.x; e < K * N; e += blockDim.x) Ws[e] = __ldg(W + e);
+  float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = b4;
+  if (active) {
+    b4 = __ldg(reinterpret_cast<const float4 *>(B) + tx);
+    if (prelu) s4 = __ldg(reinterpret_cast<const float4 *>(prelu) + tx);
+  }
+  const int nTiles = (rows + TR - 1) / TR;
+  for (int tile = blockIdx.x; tile < nTiles; tile += gridDim.x) {
+    const int row0 = tile * TR;
+    __syncthreads();
+    for (int e = threadIdx.x; e < TR * K; e += blockDim.x) {
+      const int r = e / K, k = e - r * K;
+      const int row = row0 + r;
+      float v = 0.f;
+      if (row < rows) {
+        const int f = k / nIn, c = k - f * nIn;
+        const int src = rules ? __ldg(rules + (long long)row * fs + f) : row;
+        if (src >= 0) v = __ldg(in + (long long)src * nIn + c);
+      }
+      As[k * TR + r] = v;
+    }
+    __syncthreads();
+    if (!active) continue;
+    float4 acc[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < K; ++k) {
+      const float4 w = *reinterpret_cast<const float4 *>(Ws + k * N + tx * 4);
+      const float4 a = *reinterpret_cast<const float4 *>(As + k * TR + ty * 4);
+      const float av[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[i].x = fmaf(av[i], w.x, acc[i].x); acc[i].y = fmaf(av[i], w.y, acc[i].y);
+        acc[i].z = fmaf(av[i], w.z, acc[i].z); acc[i].w = fmaf(av[i], w.w, acc[i].w);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = row0 + ty * 4 + i;
+      if (row >= rows) continue;
+      float4 o;
+      o.x = activate(p * acc[i].x + p * b4.x, act, s4.x); o.y = activate(p * acc[i].y + p * b4.y, act, s4.y);
+      o.z = activate(p * acc[i].z + p * b4.z, act, s4.z); o.w = activate(p * acc[i].w + p * b4.w, act, s4.w);
+      reinterpret_cast<float4 *>(out + (long long)row * N)[tx] = o;
+    }
+  }
+}
+
+// Few outputs (N <= 32, the classifier): one warp per row.  Lanes stride over K, keep N partial
+// sums each, the sums are combined with shuffles, lane n finishes output n; SOFTMAX is the row
+// softmax of SigmoidLayer.cu:160-177 done across the lanes (running max starts at -10000).
+template <int NMAX>
+__global__ void __launch_bounds__(256)
+k_nin_smalln(const float *__restrict__ in, const int *__restrict__ rules, int rows, int fs, int nIn,
+             const float *__restrict__ W, const float *__restrict__ B, const float *__restrict__ prelu, int N,
+             float p, int act, float *__restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int K = fs * nIn;
+  for (int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += gridDim.x * (blockDim.x >> 5)) {
+    float acc[NMAX];
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) acc[n] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const int f = k / nIn, c = k - f * nIn;
+      const int src = rules ? __ldg(rules + (long long)row * fs + f) : row;
+      const float x = src >= 0 ? __ldg(in + (long long)src * nIn + c) : 0.f;
+      const float *w = W + (long long)k * N;
+#pragma unroll
+      for (int n = 0; n < NMAX; ++n)
+        if (n < N) acc[n] = fmaf(x, __ldg(w + n), acc[n]);
+    }
+    float mine = 0.f;
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      float v = acc[n];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == n) mine = v;
+    }
+    const bool valid = lane < N;
+    float v = valid ? p * mine + p * __ldg(B + lane) : -10000.0f;
+    if (act == SCN_SOFTMAX) {
+      float mx = fmaxf(v, -10000.0f);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float e = valid ? expf(v - mx) : 0.f, sum = e;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      v = e / sum;
+    } else if (valid) {
+      v = activate(v, act, prelu ? __ldg(prelu + lane) : 0.f);
+    }
+    if (valid) out[(long long)row * N + lane] = v;
+  }
+}
+
 // Row softmax of SigmoidLayer.cu:160-177 (running max starts at -10000), in place, one
 // thread per row (N is the class count).
 __global__ void k_softmax_rows(float *x, int rows, int N) {
@@ -115,6 +230,27 @@ extern "C" int scn_conv_nin_forward(const float *d_in, const int *d_rules, int r
     if (!d_W_packed) return fail(SCN_ERR_INVALID, "tensor-core precision needs packed weights");
     int st = tc_launch(d_in, d_rules, rows_out, fs, nIn, d_W_packed, d_B, d_prelu, N, p, inner, use, d_out, s);
     if (st != SCN_OK) return st;
+  } else if (N <= 32) {
+    // the classifier shape: warp per row, softmax fused
+    const int blocks = grid_for((long long)rows_out * 32, 256);
+    if (N <= 16) k_nin_smalln<16><<<blocks, 256, 0, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B, d_prelu, N, p, act, d_out);
+    else k_nin_smalln<32><<<blocks, 256, 0, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B, d_prelu, N, p, act, d_out);
+    SCN_LAUNCH_CHECK("k_nin_smalln");
+    return SCN_OK;
+  } else if (fs * nIn <= 64 && N % 4 == 0 && N <= 256 && (((uintptr_t)d_out | (uintptr_t)d_B | (uintptr_t)d_prelu) & 15) == 0) {
+    const int K = fs * nIn, NV = N / 4, TR = (256 / NV) * 4;
+    const size_t smem = (size_t)(K * N + K * TR) * sizeof(float);
+    static bool attrSet[64] = {false};
+    int dev = 0;
+    SCN_CUDA_TRY(cudaGetDevice(&dev));
+    if (!attrSet[dev & 63]) {
+      SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_smallk, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+      attrSet[dev & 63] = true;
+    }
+    const int tiles = (rows_out + TR - 1) / TR;
+    const int blocks = tiles < sm_count() * 4 ? tiles : sm_count() * 4;
+    k_conv_nin_smallk<<<blocks, 256, smem, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B, d_prelu, N, p, inner, d_out);
+    SCN_LAUNCH_CHECK("k_conv_nin_smallk");
   } else {
     constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
     dim3 grid((rows_out + BM - 1) / BM, (N + BN - 1) / BN);

@@ -78,6 +78,15 @@ CONV = [
     (50, 70, 4, 8, 33, "TANH", 1.0),
     (50, 70, 1, 8, 16, "SIGMOID", 1.0),
     (50, 70, 2, 5, 7, "NOSIGMOID", 0.5),
+    # small-K kernel (K <= 64, N % 4 == 0, N > 32)
+    (1000, 1357, 9, 3, 96, "VLEAKYRELU", 0.9),
+    (100, 100, 1, 64, 128, "PRELU", 1.0),
+    (500, 333, 27, 1, 64, "RELU", 1.0),
+    (40, 41, 4, 4, 256, "LEAKYRELU", 1.0),
+    # warp-per-row kernel (N <= 32)
+    (256, 256, 1, 608, 10, "SOFTMAX", 1.0),
+    (90, 77, 4, 16, 20, "SOFTMAX", 0.8),
+    (90, 77, 4, 16, 32, "PRELU", 0.8),
 ]
 
 
