@@ -170,65 +170,86 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   if (warp < 4) {
     // ------------------------------------------------------------ gather: asynchronous 16-byte copies
     const int t = threadIdx.x, chunk = t & 7, rbase = t >> 3;
-    const int sw = (chunk ^ (rbase & 7)) << 4;
+    // this thread's 16-byte chunk sits at the same offset in each of its 8 rows (16 rows apart)
+    const uint32_t rowOff = (rbase >> 3) * 1024 + (rbase & 7) * ROW_BYTES + ((chunk ^ (rbase & 7)) << 4);
+    const float *rowPtr[8]; // start of the current filter cell's source row (nullptr: no row -> zero fill)
+    int curF = -1;
     for (int s = 0; s < P.nSlabs; ++s) {
       const int st = s % P.stages, it = s / P.stages;
       const int k0 = s * SLAB, f = k0 / P.nIn, c0 = k0 - f * P.nIn;
+      if (f != curF) { // the rule column changes every nIn/32 slabs
+        curF = f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rl = rbase + 16 * i, r = row0 + rl;
+          int src;
+          if (P.rulesBytes > 0) src = rulesS[rl * P.fs + f];
+          else if (P.rules) src = (r < P.rows) ? __ldg(P.rules + (long long)r * P.fs + f) : -1;
+          else src = (r < P.rows) ? r : -1;
+          rowPtr[i] = src >= 0 ? P.in + (long long)src * P.nIn + chunk * 4 : nullptr;
+        }
+      }
       mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 1);
-      const uint32_t aRaw = smem_u32(smem + (size_t)st * stageBytes);
+      const uint32_t dst = smem_u32(smem + (size_t)st * stageBytes) + rowOff;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int rl = rbase + 16 * i, r = row0 + rl;
-        int src;
-        if (P.rulesBytes > 0) src = rulesS[rl * P.fs + f];
-        else if (P.rules) src = (r < P.rows) ? __ldg(P.rules + (long long)r * P.fs + f) : -1;
-        else src = (r < P.rows) ? r : -1;
-        const uint32_t dst = aRaw + (rl >> 3) * 1024 + (rl & 7) * ROW_BYTES + sw;
         // a negative rule (or a row past the end) copies 0 source bytes: the 16 bytes are zero-filled
-        const float *g = src >= 0 ? P.in + (long long)src * P.nIn + c0 + chunk * 4 : P.in;
-        cp_async16(dst, g, src >= 0 ? 16u : 0u);
+        const bool have = rowPtr[i] != nullptr;
+        cp_async16(dst + i * 2048, have ? (const void *)(rowPtr[i] + c0) : (const void *)P.in, have ? 16u : 0u);
       }
       cp_async_arrive(rawBar + 8 * st);
     }
     // ------------------------------------------------------------ epilogue
+    // TMEM holds one output row per lane, so a direct store would scatter 32 rows per
+    // instruction.  The accumulators go through shared memory instead (the pipeline stages are
+    // idle by now): lanes write their rows with a padded stride, then every warp stores whole
+    // rows, 512 contiguous bytes per instruction, applying p*acc + p*bias and the activation.
     mbar_wait(accumBar, 0, 2);
     tc_fence_after();
-    const int r = row0 + warp * 32 + lane;
-    const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
-    const int col0 = tileN * P.BN;
-    for (int c = 0; c < P.BN; c += 16) {
-      uint32_t a[16];
-      asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                   : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]),
-                     "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15])
-                   : "r"(laneAddr + (uint32_t)c));
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (r < P.rows) {
-        float *o = P.out + (long long)r * P.N + col0 + c;
+    float *tile = reinterpret_cast<float *>(smem);
+    const int ld = P.BN + 4; // floats; keeps 16-byte alignment and spreads rows over the banks
+    {
+      const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
+      float *myRow = tile + (size_t)(warp * 32 + lane) * ld;
+      for (int c = 0; c < P.BN; c += 16) {
+        uint32_t a[16];
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                     : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]),
+                       "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15])
+                     : "r"(laneAddr + (uint32_t)c));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int q = 0; q < 16; q += 4) {
-          const int col = col0 + c + q;
-          if (col + 3 < P.N) {
-            float4 w;
-            float *wv = reinterpret_cast<float *>(&w);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
-              float x = P.p * __uint_as_float(a[q + e]) + P.p * __ldg(P.bias + col + e);
-              wv[e] = activate(x, P.act, P.prelu ? __ldg(P.prelu + col + e) : 0.f);
-            }
-            *reinterpret_cast<float4 *>(o + q) = w;
-          } else {
-            for (int e = 0; e < 4; ++e)
-              if (col + e < P.N) {
-                float x = P.p * __uint_as_float(a[q + e]) + P.p * __ldg(P.bias + col + e);
-                o[q + e] = activate(x, P.act, P.prelu ? __ldg(P.prelu + col + e) : 0.f);
-              }
-          }
-        }
+        for (int q = 0; q < 16; q += 4)
+          *reinterpret_cast<float4 *>(myRow + c + q) = make_float4(__uint_as_float(a[q]), __uint_as_float(a[q + 1]), __uint_as_float(a[q + 2]), __uint_as_float(a[q + 3]));
       }
     }
     tc_fence_before();
+    asm volatile("bar.sync 1, 128;" ::: "memory"); // the four epilogue warps only
+    {
+      const int col0 = tileN * P.BN;
+      const int nv = P.BN >> 2; // float4 columns of the tile
+      for (int v0 = 0; v0 < nv; v0 += 32) {
+        const int v = v0 + lane;
+        const int col = col0 + v * 4;
+        const bool colOk = v < nv && col < P.N; // N % 4 == 0: a float4 is in or out as a whole
+        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = b4;
+        if (colOk) {
+          b4 = __ldg(reinterpret_cast<const float4 *>(P.bias + col));
+          if (P.prelu) s4 = __ldg(reinterpret_cast<const float4 *>(P.prelu + col));
+        }
+        for (int rl = warp; rl < BM; rl += 4) {
+          const int r = row0 + rl;
+          if (r >= P.rows) break;
+          if (!colOk) continue;
+          const float4 a = *reinterpret_cast<const float4 *>(tile + (size_t)rl * ld + v * 4);
+          float4 o;
+          // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
+          o.x = activate(P.p * a.x + P.p * b4.x, P.act, s4.x); o.y = activate(P.p * a.y + P.p * b4.y, P.act, s4.y);
+          o.z = activate(P.p * a.z + P.p * b4.z, P.act, s4.z); o.w = activate(P.p * a.w + P.p * b4.w, P.act, s4.w);
+          *reinterpret_cast<float4 *>(P.out + (long long)r * P.N + col) = o;
+        }
+      }
+    }
   } else if (warp < 8) {
     // ------------------------------------------------------------ split: fp32 -> tf32 hi (in place) + tf32 lo
     const int t = threadIdx.x - 128;
