@@ -14,9 +14,10 @@
 //              barrier, so several slabs are in flight.  Afterwards the same warps run the
 //              epilogue: tcgen05.ld of their 32 accumulator lanes, p*acc + p*bias, activation,
 //              16-byte stores.
-//   warps 4-7  split: once a raw tile has landed, rewrite each fp32 as tf32 hi (in place) and
-//              write tf32 lo = x - hi into the second image, fence to the async proxy, arrive
-//              on the stage's "full" barrier.
+//   warps 4-7  split: once a raw tile has landed it already serves as the tf32 "hi" operand
+//              (the tensor core reads the upper 19 bits of each fp32); these warps write
+//              lo = x - hi into the second image, fence to the async proxy and arrive on the
+//              stage's "full" barrier.
 //   warp 8     one thread issues a cp.async.bulk per slab for the weight tile (hi and lo
 //              images, pre-split, pre-transposed and pre-swizzled once by tc_pack, so the
 //              copy is a plain contiguous block into this CTA's own shared memory; no
@@ -261,10 +262,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
       for (int i = 0; i < 8; ++i) {
         const int off = t * 16 + i * 2048; // the swizzle is the same in both images: work on raw offsets
         const float4 v = *reinterpret_cast<const float4 *>(aHi + off);
-        float4 hi, lo;
-        hi.x = to_tf32(v.x); hi.y = to_tf32(v.y); hi.z = to_tf32(v.z); hi.w = to_tf32(v.w);
-        lo.x = to_tf32(v.x - hi.x); lo.y = to_tf32(v.y - hi.y); lo.z = to_tf32(v.z - hi.z); lo.w = to_tf32(v.w - hi.w);
-        *reinterpret_cast<float4 *>(aHi + off) = hi;
+        // kind::tf32 reads the upper 19 bits of each fp32 (sign, exponent, 10 mantissa bits), so
+        // the raw tile already is the "hi" operand; lo = x - hi is exact in fp32 and is cut to
+        // tf32 the same way when it is read.
+        float4 lo;
+        lo.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+        lo.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+        lo.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+        lo.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
         *reinterpret_cast<float4 *>(aLo + off) = lo;
       }
       fence_async_smem(); // make the generic-proxy stores visible to the tensor core's reads
