@@ -51,7 +51,7 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms."""
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 20 ms."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -59,7 +59,7 @@ class ClockSampler:
         self.rows, self.proc = [], None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -211,6 +211,9 @@ def main():
         # this rank's shard of the global batch, several distinct batches rotated between steps
         n_rot = 2
         host_batches = [c["gen"](BATCH_PER_GPU, first=(rank * n_rot + j) * BATCH_PER_GPU) for j in range(n_rot)]
+        # the host-buffer leg reads its inputs from pinned (page-locked) host memory
+        pinned_keep = [[torch.from_numpy(np.ascontiguousarray(x)).pin_memory() for x in hb] for hb in host_batches]
+        host_batches = [tuple(t.numpy() for t in hb) for hb in pinned_keep]
         dev_batches = []
         for keys, off, feats in host_batches:
             bg = off[:-1].copy()  # the background row is each sample's first row

@@ -198,6 +198,11 @@ int scn_conv_tc_take_error(void);
 int scn_gather_forward(const float *d_in, const int *d_rules, long long count, int nIn,
                        float *d_out, scn_stream_t stream);
 
+/* d_bg[b] = the row of sample b whose key is negative (its background row, the value every
+ * Picture::codifyInputData stores in SparseGrid::backgroundCol, e.g. OpenCVPicture.cpp:373-375),
+ * or -1: lets a caller upload keys and offsets only. */
+int scn_background_rows(const int *d_keys, const int *d_off, int batch, int *d_bg, scn_stream_t stream);
+
 /* Replaces applySigmoid and PreLU as stand-alone passes (SigmoidLayer.cu:187-222;
  * NetworkInNetworkPReLULayer.cu:8-23): d_out = act(d_in) over [rows x N], in place allowed.
  * The layer kernels fuse their activation; this is for callers that apply one themselves. */

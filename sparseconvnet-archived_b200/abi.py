@@ -22,7 +22,7 @@ EXPORTS = [
     "scn_rules_workspace_bytes", "scn_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_terminal_rules_workspace_bytes",
     "scn_terminal_rules_build", "scn_conv_nin_forward", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_gather_forward", "scn_maxpool_forward",
-    "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward",
+    "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
 ]
 
 
@@ -77,6 +77,7 @@ def lib():
         L.scn_terminal_pool_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p]
         L.scn_top_indices.argtypes = [c_p, c_int, c_int, c_int, c_p, c_p]
         L.scn_activation_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p]
+        L.scn_background_rows.argtypes = [c_p, c_p, c_int, c_p, c_p]
         _lib = L
     return _lib
 
@@ -274,3 +275,10 @@ def rules_chain_build(regions_list, keys, off, bg, max_rows_per_sample, capaciti
     for o in outs:
         o["workspace"] = ws
     return outs
+
+
+def background_rows(keys, off):
+    batch = off.numel() - 1
+    bg = torch.empty(batch, dtype=torch.int32, device=keys.device)
+    check(lib().scn_background_rows(_ptr(_i32(keys)), _ptr(_i32(off)), batch, _ptr(bg), _stream()))
+    return bg

@@ -183,28 +183,37 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *
     in.featuresPresent.hVector() = range(nF);
     in.nSpatialSites = rows;
     in.gridOwner = &in;
-    // one pinned staging block: keys | offsets | background rows | features, one wait
-    const size_t kb = sizeof(int) * rows, ob = sizeof(int) * (batch + 1), bb = sizeof(int) * batch, fb = sizeof(float) * (size_t)rows * nF;
-    char *stage = (char *)cnn.memStream.staging(kb + ob + bb + fb);
-    int *sk = (int *)stage, *so = (int *)(stage + kb), *sb = (int *)(stage + kb + ob);
-    std::memcpy(sk, keys, kb);
-    std::memcpy(so, off, ob);
-    std::memcpy(stage + kb + ob + bb, features, fb);
-    int maxSites = 0;
-    for (int s = 0; s < batch; ++s) {
-      sb[s] = -1;
-      int sites = 0;
-      for (int r = off[s]; r < off[s + 1]; ++r) { if (keys[r] < 0) sb[s] = r; else ++sites; }
-      maxSites = std::max(maxSites, sites);
+    // Buffers in pinned (page-locked) host memory are copied straight from where they lie; pageable
+    // ones go through the stream's pinned staging block first.  Background rows are found on the device.
+    const size_t kb = sizeof(int) * rows, ob = sizeof(int) * (batch + 1), fb = sizeof(float) * (size_t)rows * nF;
+    auto pinned = [](const void *p) {
+      cudaPointerAttributes a;
+      if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+      return a.type == cudaMemoryTypeHost;
+    };
+    const void *sk = keys, *so = off, *sf = features;
+    if (!(pinned(keys) && pinned(off) && pinned(features))) {
+      char *stage = (char *)cnn.memStream.staging(kb + ob + fb);
+      std::memcpy(stage, keys, kb);
+      std::memcpy(stage + kb, off, ob);
+      std::memcpy(stage + kb + ob, features, fb);
+      sk = stage; so = stage + kb; sf = stage + kb + ob;
     }
-    in.maxSitesPerSample = maxSites;
+    int maxRows = 0;
+    for (int s = 0; s < batch; ++s) maxRows = std::max(maxRows, off[s + 1] - off[s]);
+    in.maxSitesPerSample = maxRows; // an upper bound (exact when a sample has no background row)
+    if (!cnn.layers.empty() && dynamic_cast<TerminalPoolingLayer *>(cnn.layers[0])) { // its rule width needs the exact count
+      int most = 0;
+      for (int s = 0; s < batch; ++s) { int n = 0; for (int r = off[s]; r < off[s + 1]; ++r) n += keys[r] >= 0; most = std::max(most, n); }
+      in.maxSitesPerSample = most;
+    }
     in.siteKeys.copyToGPU(); in.sampleOffsets.copyToGPU(); in.backgroundRows.copyToGPU(); in.sub->features.copyToGPU();
     in.siteKeys.resize(rows); in.sampleOffsets.resize(batch + 1); in.backgroundRows.resize(batch); in.sub->features.resize(rows * nF);
     cudaStream_t s = cnn.memStream.stream;
     if (rows) cudaSafeCall(cudaMemcpyAsync(in.siteKeys.dPtr(), sk, kb, cudaMemcpyHostToDevice, s));
     cudaSafeCall(cudaMemcpyAsync(in.sampleOffsets.dPtr(), so, ob, cudaMemcpyHostToDevice, s));
-    cudaSafeCall(cudaMemcpyAsync(in.backgroundRows.dPtr(), sb, bb, cudaMemcpyHostToDevice, s));
-    if (rows) cudaSafeCall(cudaMemcpyAsync(in.sub->features.dPtr(), stage + kb + ob + bb, fb, cudaMemcpyHostToDevice, s));
+    if (rows) cudaSafeCall(cudaMemcpyAsync(in.sub->features.dPtr(), sf, fb, cudaMemcpyHostToDevice, s));
+    scnSafeCall(scn_background_rows(in.siteKeys.dPtr(), in.sampleOffsets.dPtr(), batch, in.backgroundRows.dPtr(), s));
     cnn.preprocessBatchOnDevice(b); // waits once, after the uploads and the rule chain
     std::ofstream nof, nog;
     cnn.processBatch(b, 0, 0, nof, nog);

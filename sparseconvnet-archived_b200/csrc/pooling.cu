@@ -89,6 +89,20 @@ __global__ void k_top_indices(const float *__restrict__ probs, int rows, int nCl
   }
 }
 
+// Background row of each sample: the row whose key is negative (at most one per sample), -1 if
+// none.  One warp per sample.
+__global__ void k_background_rows(const int *__restrict__ keys, const int *__restrict__ off, int batch, int *__restrict__ bg) {
+  const int lane = threadIdx.x & 31;
+  for (int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); b < batch; b += gridDim.x * (blockDim.x >> 5)) {
+    int found = -1;
+    for (int r = off[b] + lane; r < off[b + 1]; r += 32)
+      if (keys[r] < 0) found = r;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) found = max(found, __shfl_xor_sync(0xffffffffu, found, o));
+    if (lane == 0) bg[b] = found;
+  }
+}
+
 // applySigmoid as a stand-alone elementwise pass (SigmoidLayer.cu:187-222).
 __global__ void k_activation(const float *__restrict__ in, float *__restrict__ out, long long n, int N, int act,
                              const float *__restrict__ prelu) {
@@ -111,6 +125,14 @@ __global__ void k_softmax(const float *__restrict__ in, float *__restrict__ out,
 } // namespace scn
 
 using namespace scn;
+
+extern "C" int scn_background_rows(const int *d_keys, const int *d_off, int batch, int *d_bg, scn_stream_t stream) {
+  clear_error();
+  if (batch < 1 || !d_off || !d_bg) return fail(SCN_ERR_INVALID, "bad arguments");
+  k_background_rows<<<grid_for((long long)batch * 32, 256), 256, 0, (cudaStream_t)stream>>>(d_keys, d_off, batch, d_bg);
+  SCN_LAUNCH_CHECK("k_background_rows");
+  return SCN_OK;
+}
 
 extern "C" int scn_activation_forward(const float *d_in, float *d_out, int rows, int N, int act, const float *d_prelu,
                                       scn_stream_t stream) {
