@@ -180,6 +180,16 @@ int scn_conv_nin_forward(const float *d_in, const int *d_rules, int rows_out, in
                          const float *d_W, const void *d_W_packed, const float *d_B,
                          const float *d_prelu, int N, float p, int act, int precision,
                          float *d_out, scn_stream_t stream);
+/* The same with optional scratch: layers with few output tiles (small rows_out, large K) then
+ * split K over several CTAs per tile, write partial sums to the scratch and finish with a
+ * second small kernel (summed in a fixed order: results stay deterministic).
+ * scn_conv_nin_workspace_bytes() is the size worth passing (0: the layer does not benefit). */
+size_t scn_conv_nin_workspace_bytes(int rows_out, int fs, int nIn, int N, int precision);
+int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, int rows_out, int fs, int nIn,
+                            const float *d_W, const void *d_W_packed, const float *d_B,
+                            const float *d_prelu, int N, float p, int act, int precision,
+                            float *d_out, void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
+
 /* One-time repack of W[K x N] (K = fs*nIn) for a tensor-core precision: bytes needed, then
  * the packing kernel.  No reference counterpart (the reference hands W to cuBLAS as is). */
 size_t scn_conv_packed_weight_bytes(int K, int N, int precision);

@@ -20,7 +20,7 @@ DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
 EXPORTS = [
     "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
     "scn_rules_workspace_bytes", "scn_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_terminal_rules_workspace_bytes",
-    "scn_terminal_rules_build", "scn_conv_nin_forward", "scn_conv_packed_weight_bytes",
+    "scn_terminal_rules_build", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
 ]
@@ -69,6 +69,9 @@ def lib():
         L.scn_terminal_rules_workspace_bytes.argtypes = [c_int] * 4
         L.scn_terminal_rules_build.argtypes = [c_int, c_int, c_int, c_p, c_p, c_p, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]
         L.scn_conv_nin_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_int, c_f, c_int, c_int, c_p, c_p]
+        L.scn_conv_nin_forward_ws.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_int, c_f, c_int, c_int, c_p, c_p, c_sz, c_p]
+        L.scn_conv_nin_workspace_bytes.restype = c_sz
+        L.scn_conv_nin_workspace_bytes.argtypes = [c_int] * 5
         L.scn_conv_packed_weight_bytes.restype = c_sz
         L.scn_conv_packed_weight_bytes.argtypes = [c_int, c_int, c_int]
         L.scn_conv_pack_weights.argtypes = [c_p, c_int, c_int, c_int, c_p, c_p]
@@ -162,7 +165,7 @@ def pack_weights(W, precision):
 
 
 def conv_nin_forward(feat, rules, fs, W, B, prelu=None, p=1.0, act=NOSIGMOID, precision=PREC_FP32, packed=None,
-                     rows_out=None):
+                     rows_out=None, split_k=True):
     """rules: int32 [rows_out*fs] or None (plain NiN, fs == 1)."""
     L = lib()
     nIn = feat.shape[1]
@@ -171,8 +174,10 @@ def conv_nin_forward(feat, rules, fs, W, B, prelu=None, p=1.0, act=NOSIGMOID, pr
     if rows_out is None:
         rows_out = feat.shape[0] if rules is None else rules.numel() // fs
     out = torch.empty((rows_out, N), dtype=torch.float32, device=feat.device)
-    check(L.scn_conv_nin_forward(_ptr(_f32(feat)), _ptr(rules), rows_out, fs, nIn, _ptr(_f32(W)), _ptr(packed),
-                                 _ptr(_f32(B)), _ptr(prelu), N, p, act, precision, _ptr(out), _stream()))
+    ws_bytes = L.scn_conv_nin_workspace_bytes(rows_out, fs, nIn, N, precision) if (split_k and packed is not None) else 0
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=feat.device) if ws_bytes else None
+    check(L.scn_conv_nin_forward_ws(_ptr(_f32(feat)), _ptr(rules), rows_out, fs, nIn, _ptr(_f32(W)), _ptr(packed),
+                                    _ptr(_f32(B)), _ptr(prelu), N, p, act, precision, _ptr(out), _ptr(ws), ws_bytes, _stream()))
     return out
 
 

@@ -207,10 +207,23 @@ __global__ void k_softmax_rows(float *x, int rows, int N) {
 
 using namespace scn;
 
+extern "C" size_t scn_conv_nin_workspace_bytes(int rows_out, int fs, int nIn, int N, int precision) {
+  if (rows_out < 1 || fs < 1 || nIn < 1 || N < 1) return 0;
+  return tc_workspace_bytes(rows_out, fs, nIn, N, precision == SCN_PREC_AUTO ? SCN_PREC_3XTF32 : precision);
+}
+
 extern "C" int scn_conv_nin_forward(const float *d_in, const int *d_rules, int rows_out, int fs, int nIn,
                                     const float *d_W, const void *d_W_packed, const float *d_B,
                                     const float *d_prelu, int N, float p, int act, int precision, float *d_out,
                                     scn_stream_t stream) {
+  return scn_conv_nin_forward_ws(d_in, d_rules, rows_out, fs, nIn, d_W, d_W_packed, d_B, d_prelu, N, p, act, precision, d_out,
+                                 nullptr, 0, stream);
+}
+
+extern "C" int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, int rows_out, int fs, int nIn,
+                                       const float *d_W, const void *d_W_packed, const float *d_B,
+                                       const float *d_prelu, int N, float p, int act, int precision, float *d_out,
+                                       void *d_workspace, size_t workspace_bytes, scn_stream_t stream) {
   clear_error();
   if (rows_out < 0 || fs < 1 || nIn < 1 || N < 1) return fail(SCN_ERR_INVALID, "bad conv/NiN sizes");
   if (!d_rules && fs != 1) return fail(SCN_ERR_INVALID, "fs must be 1 without rules");
@@ -228,7 +241,7 @@ extern "C" int scn_conv_nin_forward(const float *d_in, const int *d_rules, int r
   if (use != SCN_PREC_FP32) {
     if (!tc_shape_ok(fs, nIn, N, use)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel (need nIn % 8 == 0, N % 16 == 0)");
     if (!d_W_packed) return fail(SCN_ERR_INVALID, "tensor-core precision needs packed weights");
-    int st = tc_launch(d_in, d_rules, rows_out, fs, nIn, d_W_packed, d_B, d_prelu, N, p, inner, use, d_out, s);
+    int st = tc_launch(d_in, d_rules, rows_out, fs, nIn, d_W_packed, d_B, d_prelu, N, p, inner, use, d_out, d_workspace, workspace_bytes, s);
     if (st != SCN_OK) return st;
   } else if (N <= 32) {
     // the classifier shape: warp per row, softmax fused

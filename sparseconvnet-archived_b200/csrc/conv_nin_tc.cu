@@ -116,6 +116,7 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
+  int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
@@ -128,6 +129,7 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
 
 constexpr int MAX_STAGES = 6;
 
+template <bool SPLIT>
 __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) {
   extern __shared__ unsigned char smem_raw[];
   int *rulesS = reinterpret_cast<int *>(smem_raw); // [128 x fs] rule tile (when it fits)
@@ -140,7 +142,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   const uint32_t rawBar = smem_u32(&bars[0]), fullBar = smem_u32(&bars[MAX_STAGES]), emptyBar = smem_u32(&bars[2 * MAX_STAGES]),
                  accumBar = smem_u32(&bars[3 * MAX_STAGES]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tileN = blockIdx.x % P.nTiles, tileM = blockIdx.x / P.nTiles;
+  const int kSplit = SPLIT ? P.kSplit : 1;
+  const int tileId = SPLIT ? blockIdx.x / kSplit : blockIdx.x, split = SPLIT ? blockIdx.x - tileId * kSplit : 0;
+  const int tileN = tileId % P.nTiles, tileM = tileId / P.nTiles;
+  const int slab0 = SPLIT ? split * P.nSlabs / kSplit : 0;
+  const int nLoc = SPLIT ? (split + 1) * P.nSlabs / kSplit - slab0 : P.nSlabs; // this CTA's share of the K slabs
   const int row0 = tileM * BM;
 
   if (threadIdx.x == 0) {
@@ -175,8 +181,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
     const uint32_t rowOff = (rbase >> 3) * 1024 + (rbase & 7) * ROW_BYTES + ((chunk ^ (rbase & 7)) << 4);
     const float *rowPtr[8]; // start of the current filter cell's source row (nullptr: no row -> zero fill)
     int curF = -1;
-    for (int s = 0; s < P.nSlabs; ++s) {
-      const int st = s % P.stages, it = s / P.stages;
+    for (int q = 0; q < nLoc; ++q) {
+      const int s = slab0 + q, st = q % P.stages, it = q / P.stages;
       const int k0 = s * SLAB, f = k0 / P.nIn, c0 = k0 - f * P.nIn;
       if (f != curF) { // the rule column changes every nIn/32 slabs
         curF = f;
@@ -247,15 +253,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
           // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
           o.x = activate(P.p * a.x + P.p * b4.x, P.act, s4.x); o.y = activate(P.p * a.y + P.p * b4.y, P.act, s4.y);
           o.z = activate(P.p * a.z + P.p * b4.z, P.act, s4.z); o.w = activate(P.p * a.w + P.p * b4.w, P.act, s4.w);
-          *reinterpret_cast<float4 *>(P.out + (long long)r * P.N + col) = o;
+          if (SPLIT) *reinterpret_cast<float4 *>(P.partial + ((long long)split * P.rows + r) * P.N + col) = a;
+          else *reinterpret_cast<float4 *>(P.out + (long long)r * P.N + col) = o;
         }
       }
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------ split: fp32 -> tf32 hi (in place) + tf32 lo
     const int t = threadIdx.x - 128;
-    for (int s = 0; s < P.nSlabs; ++s) {
-      const int st = s % P.stages, it = s / P.stages;
+    for (int q = 0; q < nLoc; ++q) {
+      const int s = slab0 + q, st = q % P.stages, it = q / P.stages;
       mbar_wait(rawBar + 8 * st, it & 1, 5);
       unsigned char *aHi = smem + (size_t)st * stageBytes, *aLo = aHi + A_HALF;
 #pragma unroll
@@ -280,8 +287,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
     if (lane == 0) {
       const uint32_t bytes = 2 * bHalf;
       const unsigned char *srcBase = P.packed + (size_t)tileN * P.nSlabs * bytes;
-      for (int s = 0; s < P.nSlabs; ++s) {
-        const int st = s % P.stages, it = s / P.stages;
+      for (int q = 0; q < nLoc; ++q) {
+        const int s = slab0 + q, st = q % P.stages, it = q / P.stages;
         mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 3);
         mbar_arrive_expect_tx(fullBar + 8 * st, bytes);
         bulk_g2s(smem_u32(smem + (size_t)st * stageBytes + 2 * A_HALF), srcBase + (size_t)s * bytes, bytes, fullBar + 8 * st);
@@ -290,8 +297,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   } else {
     // ------------------------------------------------------------ MMA issue
     if (lane == 0) {
-      for (int s = 0; s < P.nSlabs; ++s) {
-        const int st = s % P.stages, it = s / P.stages;
+      for (int q = 0; q < nLoc; ++q) {
+        const int s = slab0 + q, st = q % P.stages, it = q / P.stages;
         mbar_wait(fullBar + 8 * st, it & 1, 4);
         tc_fence_after();
         const uint32_t aHi = smem_u32(smem + (size_t)st * stageBytes), aLo = aHi + A_HALF;
@@ -299,7 +306,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
         const uint64_t dAhi = smem_desc(aHi), dAlo = smem_desc(aLo), dBhi = smem_desc(bHi), dBlo = smem_desc(bLo);
         // small cross terms first, the dominant hi*hi product last
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_tf32(tmem, dAlo + 2 * k, dBhi + 2 * k, P.idesc, (s | k) != 0);
+        for (int k = 0; k < 4; ++k) mma_tf32(tmem, dAlo + 2 * k, dBhi + 2 * k, P.idesc, (q | k) != 0);
 #pragma unroll
         for (int k = 0; k < 4; ++k) mma_tf32(tmem, dAhi + 2 * k, dBlo + 2 * k, P.idesc, 1);
 #pragma unroll
@@ -334,6 +341,39 @@ __global__ void k_pack_tf32(const float *__restrict__ W, int K, int N, int BN, i
     base[off >> 2] = hi;
     base[BN * SLAB + (off >> 2)] = lo;
   }
+}
+
+// Sum the K-split partials in split order (deterministic), then bias, dropout scale, activation.
+__global__ void k_splitk_finish(const float *__restrict__ partial, int kSplit, long long rows, int N, const float *__restrict__ bias,
+                                const float *__restrict__ prelu, float p, int act, float *__restrict__ out) {
+  const long long n4 = rows * N / 4;
+  const int nv = N >> 2;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n4; q += (long long)gridDim.x * blockDim.x) {
+    float4 a = reinterpret_cast<const float4 *>(partial)[q];
+    for (int s = 1; s < kSplit; ++s) {
+      const float4 b = reinterpret_cast<const float4 *>(partial)[(long long)s * n4 + q];
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    const int v = (int)(q % nv);
+    const float4 b4 = __ldg(reinterpret_cast<const float4 *>(bias) + v);
+    float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (prelu) s4 = __ldg(reinterpret_cast<const float4 *>(prelu) + v);
+    float4 o;
+    o.x = activate(p * a.x + p * b4.x, act, s4.x); o.y = activate(p * a.y + p * b4.y, act, s4.y);
+    o.z = activate(p * a.z + p * b4.z, act, s4.z); o.w = activate(p * a.w + p * b4.w, act, s4.w);
+    reinterpret_cast<float4 *>(out)[q] = o;
+  }
+}
+
+// How many CTAs share one output tile's K range: only when the tiles alone leave most SMs idle.
+int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) {
+  const int sms = sm_count();
+  if (tiles * 2 > sms || nSlabs < 8) return 1;
+  int k = sms / tiles;
+  if (k > nSlabs / 4) k = nSlabs / 4;
+  if (k > 32) k = 32;
+  while (k > 1 && (size_t)k * rows * N * sizeof(float) > wsBytes) --k;
+  return k < 2 ? 1 : k;
 }
 
 struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; size_t smemBytes; };
@@ -380,8 +420,17 @@ int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaS
   return SCN_OK;
 }
 
+size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision) {
+  Tiling t;
+  if (precision != SCN_PREC_3XTF32 || nIn % SLAB != 0 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, true, &t)) return 0;
+  const int tiles = ((rows + BM - 1) / BM) * t.nTiles;
+  const int k = choose_ksplit(tiles, t.nSlabs, rows, N, (size_t)-1);
+  return k > 1 ? (size_t)k * rows * N * sizeof(float) : 0;
+}
+
 int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed, const float *d_B,
-              const float *d_prelu, int N, float p, int act, int precision, float *d_out, cudaStream_t s) {
+              const float *d_prelu, int N, float p, int act, int precision, float *d_out, void *d_ws, size_t wsBytes,
+              cudaStream_t s) {
   Tiling t;
   if (precision != SCN_PREC_3XTF32 || nIn % SLAB != 0 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t))
     return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
@@ -390,7 +439,8 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   int dev = 0;
   SCN_CUDA_TRY(cudaGetDevice(&dev));
   if (!attrSet[dev & 63]) {
-    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     attrSet[dev & 63] = true;
   }
   Params P;
@@ -401,8 +451,15 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   // instruction descriptor: D = fp32, A = B = tf32, both K-major, N = BN, M = 128
   P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(t.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   const int mTiles = (rows + BM - 1) / BM;
-  k_conv_nin_tc<<<mTiles * t.nTiles, NUM_THREADS, t.smemBytes, s>>>(P);
+  P.kSplit = (d_ws && ((uintptr_t)d_ws & 15) == 0) ? choose_ksplit(mTiles * t.nTiles, t.nSlabs, rows, N, wsBytes) : 1;
+  P.partial = (float *)d_ws;
+  if (P.kSplit > 1) k_conv_nin_tc<true><<<mTiles * t.nTiles * P.kSplit, NUM_THREADS, t.smemBytes, s>>>(P);
+  else k_conv_nin_tc<false><<<mTiles * t.nTiles, NUM_THREADS, t.smemBytes, s>>>(P);
   SCN_LAUNCH_CHECK("k_conv_nin_tc");
+  if (P.kSplit > 1) {
+    k_splitk_finish<<<grid_for((long long)rows * N / 4, 256), 256, 0, s>>>(P.partial, P.kSplit, rows, N, d_B, d_prelu, p, act, d_out);
+    SCN_LAUNCH_CHECK("k_splitk_finish");
+  }
   return SCN_OK;
 }
 

@@ -8,9 +8,11 @@ bool tc_shape_ok(int fs, int nIn, int N, int precision);
 // Bytes of the packed copy of W[K x N] the kernel reads (0 if unsupported).
 size_t tc_packed_bytes(int K, int N, int precision);
 int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaStream_t s);
+// Scratch for splitting K over several CTAs when a layer has few output tiles (0: not useful).
+size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision);
 int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed,
               const float *d_B, const float *d_prelu, int N, float p, int act, int precision, float *d_out,
-              cudaStream_t s);
+              void *d_ws, size_t wsBytes, cudaStream_t s);
 // Error code a bounded wait of the kernel recorded since the last call (0 = none); waits for
 // the device and clears it.  1 gather/empty, 2 epilogue/accumulator, 3 weight copy/empty, 4 MMA/full.
 int tc_take_error();

@@ -373,8 +373,14 @@ void NetworkInNetworkLayer::forwards(SpatiallySparseBatch &batch, SpatiallySpars
     pk = packedWeights(fs, nIn, prec == SCN_PREC_AUTO ? SCN_PREC_3XTF32 : prec);
     if (!pk && prec != SCN_PREC_AUTO) throw ScnException("NetworkInNetworkLayer: layer shape has no tensor-core path; use SCN_PREC_AUTO or SCN_PREC_FP32");
   }
-  scnSafeCall(scn_conv_nin_forward(src, rules, output.nSpatialSites, fs, nIn, W.dPtr(), pk, B.dPtr(), slopes(), nFeaturesOut, p,
-                                   (int)fn, prec, output.sub->features.dPtr(), memStream.stream));
+  void *ws = nullptr;
+  size_t wsBytes = pk ? scn_conv_nin_workspace_bytes(output.nSpatialSites, fs, nIn, nFeaturesOut, prec) : 0;
+  if (wsBytes) { // few output tiles: split K over more CTAs, partial sums in a per-layer scratch vector
+    splitScratch.resize((int)((wsBytes + sizeof(float) - 1) / sizeof(float)));
+    ws = splitScratch.dPtr();
+  }
+  scnSafeCall(scn_conv_nin_forward_ws(src, rules, output.nSpatialSites, fs, nIn, W.dPtr(), pk, B.dPtr(), slopes(), nFeaturesOut, p,
+                                      (int)fn, prec, output.sub->features.dPtr(), ws, wsBytes, memStream.stream));
   multiplyAddCount += (__int128_t)output.nSpatialSites * input.featuresPresent.size() * output.featuresPresent.size();
 }
 // Weight files: raw fp32 W then B (then momentum copies) per layer (NetworkInNetworkLayer.cu:290-328).

@@ -11,6 +11,7 @@ public:
   vectorCUDA<float> MW; // momentum (kept for weight-file compatibility; unused)
   vectorCUDA<float> B;  // [nFeaturesOut]
   vectorCUDA<float> MB;
+  vectorCUDA<float> splitScratch; // partial sums when the kernel splits K (layers with few rows)
   ActivationFunction fn;
   int nFeaturesIn, nFeaturesOut;
   float dropout;
