@@ -11,11 +11,11 @@ namespace {
 // CTA tile BM x BN, K slabs of BK, each thread a TM x TN register tile.  The gathered A tile
 // only ever lives in shared memory: the [rows x K] matrix the reference materialises
 // (ConvolutionalLayer.cu:124-133) is never written to HBM.
-template <int BM, int BN, int BK, int TM, int TN>
+template <int BM, int BN, int BK, int TM, int TN, int ACT>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 k_conv_nin_simt(const float *__restrict__ in, const int *__restrict__ rules, int rows, int fs, int nIn,
                 const float *__restrict__ W, const float *__restrict__ B, const float *__restrict__ prelu,
-                int N, float p, int act, float *__restrict__ out) {
+                int N, float p, float *__restrict__ out) {
   constexpr int THREADS = (BM / TM) * (BN / TN);
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN];
@@ -70,7 +70,7 @@ k_conv_nin_simt(const float *__restrict__ in, const int *__restrict__ rules, int
       if (col >= N) continue;
       // NetworkInNetworkLayer.cu:187-195: SGEMM with alpha = beta = p over a bias-filled C
       float v = p * acc[i][j] + p * __ldg(B + col);
-      out[(long long)r * N + col] = activate(v, act, prelu ? __ldg(prelu + col) : 0.f);
+      out[(long long)r * N + col] = activate_t<ACT>(v, ACT == SCN_PRELU ? __ldg(prelu + col) : 0.f);
     }
   }
 }
@@ -83,10 +83,11 @@ k_conv_nin_simt(const float *__restrict__ in, const int *__restrict__ rules, int
 // rows' values at one k are one 16-byte read), and each thread owns 4 rows x 4 consecutive
 // columns: per k two 16-byte shared loads feed 16 FMAs, and the epilogue stores float4s that
 // are contiguous across the threads of a row.
+template <int ACT>
 __global__ void __launch_bounds__(256)
 k_conv_nin_smallk(const float *__restrict__ in, const int *__restrict__ rules, int rows, int fs, int nIn,
                   const float *__restrict__ W, const float *__restrict__ B, const float *__restrict__ prelu, int N,
-                  float p, int act, float *__restrict__ out) {
+                  float p, float *__restrict__ out) {
   extern __shared__ __align__(16) float sk_smem[];
   const int K = fs * nIn, NV = N >> 2;
   const int TY = blockDim.x / NV, TR = TY * 4;
@@ -98,7 +99,7 @@ k_conv_nin_smallk(const float *__restrict__ in, const int *__restrict__ rules, i
   float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = b4;
   if (active) {
     b4 = __ldg(reinterpret_cast<const float4 *>(B) + tx);
-    if (prelu) s4 = __ldg(reinterpret_cast<const float4 *>(prelu) + tx);
+    if (ACT == SCN_PRELU) s4 = __ldg(reinterpret_cast<const float4 *>(prelu) + tx);
   }
   const int nTiles = (rows + TR - 1) / TR;
   for (int tile = blockIdx.x; tile < nTiles; tile += gridDim.x) {
@@ -135,8 +136,8 @@ k_conv_nin_smallk(const float *__restrict__ in, const int *__restrict__ rules, i
       const int row = row0 + ty * 4 + i;
       if (row >= rows) continue;
       float4 o;
-      o.x = activate(p * acc[i].x + p * b4.x, act, s4.x); o.y = activate(p * acc[i].y + p * b4.y, act, s4.y);
-      o.z = activate(p * acc[i].z + p * b4.z, act, s4.z); o.w = activate(p * acc[i].w + p * b4.w, act, s4.w);
+      o.x = activate_t<ACT>(p * acc[i].x + p * b4.x, s4.x); o.y = activate_t<ACT>(p * acc[i].y + p * b4.y, s4.y);
+      o.z = activate_t<ACT>(p * acc[i].z + p * b4.z, s4.z); o.w = activate_t<ACT>(p * acc[i].w + p * b4.w, s4.w);
       reinterpret_cast<float4 *>(out + (long long)row * N)[tx] = o;
     }
   }
@@ -253,22 +254,18 @@ extern "C" int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, in
   } else if (fs * nIn <= 64 && N % 4 == 0 && N <= 256 && (((uintptr_t)d_out | (uintptr_t)d_B | (uintptr_t)d_prelu) & 15) == 0) {
     const int K = fs * nIn, NV = N / 4, TR = (256 / NV) * 4;
     const size_t smem = (size_t)(K * N + K * TR) * sizeof(float);
-    static bool attrSet[64] = {false};
-    int dev = 0;
-    SCN_CUDA_TRY(cudaGetDevice(&dev));
-    if (!attrSet[dev & 63]) {
-      SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_smallk, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-      attrSet[dev & 63] = true;
+    if (smem > 48 * 1024) {
+      SCN_DISPATCH_ACT(inner, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_smallk<ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)));
     }
     const int tiles = (rows_out + TR - 1) / TR;
     const int blocks = tiles < sm_count() * 4 ? tiles : sm_count() * 4;
-    k_conv_nin_smallk<<<blocks, 256, smem, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B, d_prelu, N, p, inner, d_out);
+    SCN_DISPATCH_ACT(inner, (k_conv_nin_smallk<ACT><<<blocks, 256, smem, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B, d_prelu, N, p, d_out)));
     SCN_LAUNCH_CHECK("k_conv_nin_smallk");
   } else {
     constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
     dim3 grid((rows_out + BM - 1) / BM, (N + BN - 1) / BN);
-    k_conv_nin_simt<BM, BN, BK, TM, TN><<<grid, (BM / TM) * (BN / TN), 0, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B,
-                                                                           d_prelu, N, p, inner, d_out);
+    SCN_DISPATCH_ACT(inner, (k_conv_nin_simt<BM, BN, BK, TM, TN, ACT><<<grid, (BM / TM) * (BN / TN), 0, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W,
+                                                                                             d_B, d_prelu, N, p, d_out)));
     SCN_LAUNCH_CHECK("k_conv_nin_simt");
   }
   if (act == SCN_SOFTMAX) {

@@ -127,6 +127,40 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// Second half of the epilogue: every warp stores whole rows of the staged tile, 512 contiguous
+// bytes per instruction, applying p*acc + p*bias and the activation (fixed at compile time);
+// with K split over CTAs the raw partial sums go to the scratch instead.
+template <bool SPLIT, int ACT>
+__device__ __forceinline__ void store_tile(const Params &P, const float *tile, int ld, int row0, int tileN, int split, int warp, int lane) {
+  const int col0 = tileN * P.BN;
+  const int nv = P.BN >> 2; // float4 columns of the tile
+  for (int v0 = 0; v0 < nv; v0 += 32) {
+    const int v = v0 + lane;
+    const int col = col0 + v * 4;
+    const bool colOk = v < nv && col < P.N; // N % 4 == 0: a float4 is in or out as a whole
+    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = b4;
+    if (colOk && !SPLIT) {
+      b4 = __ldg(reinterpret_cast<const float4 *>(P.bias + col));
+      if (ACT == SCN_PRELU) s4 = __ldg(reinterpret_cast<const float4 *>(P.prelu + col));
+    }
+    for (int rl = warp; rl < BM; rl += 4) {
+      const int r = row0 + rl;
+      if (r >= P.rows) break;
+      if (!colOk) continue;
+      const float4 a = *reinterpret_cast<const float4 *>(tile + (size_t)rl * ld + v * 4);
+      if (SPLIT) {
+        *reinterpret_cast<float4 *>(P.partial + ((long long)split * P.rows + r) * P.N + col) = a;
+      } else {
+        float4 o;
+        // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
+        o.x = activate_t<ACT>(P.p * a.x + P.p * b4.x, s4.x); o.y = activate_t<ACT>(P.p * a.y + P.p * b4.y, s4.y);
+        o.z = activate_t<ACT>(P.p * a.z + P.p * b4.z, s4.z); o.w = activate_t<ACT>(P.p * a.w + P.p * b4.w, s4.w);
+        *reinterpret_cast<float4 *>(P.out + (long long)r * P.N + col) = o;
+      }
+    }
+  }
+}
+
 constexpr int MAX_STAGES = 6;
 
 template <bool SPLIT>
@@ -232,32 +266,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
     }
     tc_fence_before();
     asm volatile("bar.sync 1, 128;" ::: "memory"); // the four epilogue warps only
-    {
-      const int col0 = tileN * P.BN;
-      const int nv = P.BN >> 2; // float4 columns of the tile
-      for (int v0 = 0; v0 < nv; v0 += 32) {
-        const int v = v0 + lane;
-        const int col = col0 + v * 4;
-        const bool colOk = v < nv && col < P.N; // N % 4 == 0: a float4 is in or out as a whole
-        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = b4;
-        if (colOk) {
-          b4 = __ldg(reinterpret_cast<const float4 *>(P.bias + col));
-          if (P.prelu) s4 = __ldg(reinterpret_cast<const float4 *>(P.prelu + col));
-        }
-        for (int rl = warp; rl < BM; rl += 4) {
-          const int r = row0 + rl;
-          if (r >= P.rows) break;
-          if (!colOk) continue;
-          const float4 a = *reinterpret_cast<const float4 *>(tile + (size_t)rl * ld + v * 4);
-          float4 o;
-          // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
-          o.x = activate(P.p * a.x + P.p * b4.x, P.act, s4.x); o.y = activate(P.p * a.y + P.p * b4.y, P.act, s4.y);
-          o.z = activate(P.p * a.z + P.p * b4.z, P.act, s4.z); o.w = activate(P.p * a.w + P.p * b4.w, P.act, s4.w);
-          if (SPLIT) *reinterpret_cast<float4 *>(P.partial + ((long long)split * P.rows + r) * P.N + col) = a;
-          else *reinterpret_cast<float4 *>(P.out + (long long)r * P.N + col) = o;
-        }
-      }
-    }
+    if (SPLIT) store_tile<true, SCN_NOSIGMOID>(P, tile, ld, row0, tileN, split, warp, lane);
+    else { SCN_DISPATCH_ACT(P.act, (store_tile<false, ACT>(P, tile, ld, row0, tileN, split, warp, lane))); }
   } else if (warp < 8) {
     // ------------------------------------------------------------ split: fp32 -> tf32 hi (in place) + tf32 lo
     const int t = threadIdx.x - 128;
@@ -344,8 +354,9 @@ __global__ void k_pack_tf32(const float *__restrict__ W, int K, int N, int BN, i
 }
 
 // Sum the K-split partials in split order (deterministic), then bias, dropout scale, activation.
+template <int ACT>
 __global__ void k_splitk_finish(const float *__restrict__ partial, int kSplit, long long rows, int N, const float *__restrict__ bias,
-                                const float *__restrict__ prelu, float p, int act, float *__restrict__ out) {
+                                const float *__restrict__ prelu, float p, float *__restrict__ out) {
   const long long n4 = rows * N / 4;
   const int nv = N >> 2;
   for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n4; q += (long long)gridDim.x * blockDim.x) {
@@ -359,8 +370,8 @@ __global__ void k_splitk_finish(const float *__restrict__ partial, int kSplit, l
     float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
     if (prelu) s4 = __ldg(reinterpret_cast<const float4 *>(prelu) + v);
     float4 o;
-    o.x = activate(p * a.x + p * b4.x, act, s4.x); o.y = activate(p * a.y + p * b4.y, act, s4.y);
-    o.z = activate(p * a.z + p * b4.z, act, s4.z); o.w = activate(p * a.w + p * b4.w, act, s4.w);
+    o.x = activate_t<ACT>(p * a.x + p * b4.x, s4.x); o.y = activate_t<ACT>(p * a.y + p * b4.y, s4.y);
+    o.z = activate_t<ACT>(p * a.z + p * b4.z, s4.z); o.w = activate_t<ACT>(p * a.w + p * b4.w, s4.w);
     reinterpret_cast<float4 *>(out)[q] = o;
   }
 }
@@ -457,7 +468,7 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   else k_conv_nin_tc<false><<<mTiles * t.nTiles, NUM_THREADS, t.smemBytes, s>>>(P);
   SCN_LAUNCH_CHECK("k_conv_nin_tc");
   if (P.kSplit > 1) {
-    k_splitk_finish<<<grid_for((long long)rows * N / 4, 256), 256, 0, s>>>(P.partial, P.kSplit, rows, N, d_B, d_prelu, p, act, d_out);
+    SCN_DISPATCH_ACT(act, (k_splitk_finish<ACT><<<grid_for((long long)rows * N / 4, 256), 256, 0, s>>>(P.partial, P.kSplit, rows, N, d_B, d_prelu, p, d_out)));
     SCN_LAUNCH_CHECK("k_splitk_finish");
   }
   return SCN_OK;

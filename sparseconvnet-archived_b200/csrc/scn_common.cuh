@@ -66,4 +66,27 @@ __device__ __forceinline__ float activate(float v, int act, float slope) {
   }
 }
 
+// The same with the activation fixed at compile time: inner loops must not carry the switch
+// (the tanh/exp branches cost hundreds of instructions per element when the compiler keeps
+// them on the path).  SCN_DISPATCH_ACT(act, F) calls F<ACT>() for the run-time value.
+template <int ACT> __device__ __forceinline__ float activate_t(float v, float slope) {
+  if (ACT == SCN_RELU) return v > 0.f ? v : 0.f;
+  if (ACT == SCN_VLEAKYRELU) return v > 0.f ? v : v * 0.333f;
+  if (ACT == SCN_LEAKYRELU) return v > 0.f ? v : v * 0.01f;
+  if (ACT == SCN_TANH) return tanhf(v);
+  if (ACT == SCN_SIGMOID) return 1.0f / (1.0f + expf(-v));
+  if (ACT == SCN_PRELU) return v > 0.f ? v : v * slope;
+  return v;
+}
+#define SCN_DISPATCH_ACT(act, CALL)                                                          \
+  switch (act) {                                                                            \
+  case SCN_RELU: { constexpr int ACT = SCN_RELU; CALL; } break;                             \
+  case SCN_VLEAKYRELU: { constexpr int ACT = SCN_VLEAKYRELU; CALL; } break;                 \
+  case SCN_LEAKYRELU: { constexpr int ACT = SCN_LEAKYRELU; CALL; } break;                   \
+  case SCN_TANH: { constexpr int ACT = SCN_TANH; CALL; } break;                             \
+  case SCN_SIGMOID: { constexpr int ACT = SCN_SIGMOID; CALL; } break;                       \
+  case SCN_PRELU: { constexpr int ACT = SCN_PRELU; CALL; } break;                           \
+  default: { constexpr int ACT = SCN_NOSIGMOID; CALL; } break;                              \
+  }
+
 } // namespace scn
