@@ -43,7 +43,7 @@ constexpr int BM = 128;          // rows per CTA tile (UMMA M)
 constexpr int SLAB = 32;         // fp32 values of K per pipeline stage
 constexpr int ROW_BYTES = 128;   // bytes of one smem row (SLAB * 4)
 constexpr int A_HALF = BM * ROW_BYTES; // 16 KB: one of A_hi / A_lo
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 448;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // 2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -116,7 +116,7 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
-  int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
+  int mTiles, accStride; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
@@ -127,61 +127,34 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// Second half of the epilogue: every warp stores whole rows of the staged tile, 512 contiguous
-// bytes per instruction, applying p*acc + p*bias and the activation (fixed at compile time);
-// with K split over CTAs the raw partial sums go to the scratch instead.
-template <bool SPLIT, int ACT>
-__device__ __forceinline__ void store_tile(const Params &P, const float *tile, int ld, int row0, int tileN, int split, int warp, int lane) {
-  const int col0 = tileN * P.BN;
-  const int nv = P.BN >> 2; // float4 columns of the tile
-  for (int v0 = 0; v0 < nv; v0 += 32) {
-    const int v = v0 + lane;
-    const int col = col0 + v * 4;
-    const bool colOk = v < nv && col < P.N; // N % 4 == 0: a float4 is in or out as a whole
-    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = b4;
-    if (colOk && !SPLIT) {
-      b4 = __ldg(reinterpret_cast<const float4 *>(P.bias + col));
-      if (ACT == SCN_PRELU) s4 = __ldg(reinterpret_cast<const float4 *>(P.prelu + col));
-    }
-    for (int rl = warp; rl < BM; rl += 4) {
-      const int r = row0 + rl;
-      if (r >= P.rows) break;
-      if (!colOk) continue;
-      const float4 a = *reinterpret_cast<const float4 *>(tile + (size_t)rl * ld + v * 4);
-      if (SPLIT) {
-        *reinterpret_cast<float4 *>(P.partial + ((long long)split * P.rows + r) * P.N + col) = a;
-      } else {
-        float4 o;
-        // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
-        o.x = activate_t<ACT>(P.p * a.x + P.p * b4.x, s4.x); o.y = activate_t<ACT>(P.p * a.y + P.p * b4.y, s4.y);
-        o.z = activate_t<ACT>(P.p * a.z + P.p * b4.z, s4.z); o.w = activate_t<ACT>(P.p * a.w + P.p * b4.w, s4.w);
-        *reinterpret_cast<float4 *>(P.out + (long long)r * P.N + col) = o;
-      }
-    }
-  }
-}
-
 constexpr int MAX_STAGES = 6;
+constexpr int EPI_COLS = 32;                      // accumulator columns staged per epilogue step
+constexpr int EPI_LD = EPI_COLS + 4;              // padded row stride (floats) of the staging slice
+constexpr int EPI_BYTES = BM * EPI_LD * 4;        // 18 KB
 
-template <bool SPLIT>
+// Persistent kernel: one CTA per SM walks work items (output tile, or tile x K-split part).
+// Roles (14 warps):
+//   warps 0-3   epilogue of item i while the main loop already runs item i+1 (two accumulators
+//               in tensor memory): tcgen05.ld 32 columns -> padded shared slice -> coalesced
+//               row stores with p*acc + p*bias and the activation
+//   warps 4-7   gather (cp.async) ; warps 8-11 split (lo image) ; warp 12 weight bulk copies ;
+//   warp 13     tensor-memory allocation and MMA issue
+template <bool SPLIT, int ACT>
 __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) {
   extern __shared__ unsigned char smem_raw[];
-  int *rulesS = reinterpret_cast<int *>(smem_raw); // [128 x fs] rule tile (when it fits)
+  int *rulesS = reinterpret_cast<int *>(smem_raw); // [128 x fs] rule tile of the current item (when it fits)
   // 1024-byte alignment: the swizzle pattern is a function of absolute shared-memory address bits
   unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + P.rulesBytes + 1023) & ~(uintptr_t)1023);
   const int bHalf = P.BN * ROW_BYTES;            // one of B_hi / B_lo
-  const int stageBytes = 2 * A_HALF + 2 * bHalf; // A_hi, A_lo, B_hi, B_lo
-  __shared__ __align__(8) uint64_t bars[3 * MAX_STAGES + 1];
+  const int stageBytes = 2 * A_HALF + 2 * bHalf; // A raw(hi), A_lo, B_hi, B_lo
+  float *epi = reinterpret_cast<float *>(smem + (size_t)P.stages * stageBytes);
+  __shared__ __align__(8) uint64_t bars[3 * MAX_STAGES + 4];
   __shared__ uint32_t tmemBase;
   const uint32_t rawBar = smem_u32(&bars[0]), fullBar = smem_u32(&bars[MAX_STAGES]), emptyBar = smem_u32(&bars[2 * MAX_STAGES]),
-                 accumBar = smem_u32(&bars[3 * MAX_STAGES]);
+                 accFullBar = smem_u32(&bars[3 * MAX_STAGES]), accEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 2]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kSplit = SPLIT ? P.kSplit : 1;
-  const int tileId = SPLIT ? blockIdx.x / kSplit : blockIdx.x, split = SPLIT ? blockIdx.x - tileId * kSplit : 0;
-  const int tileN = tileId % P.nTiles, tileM = tileId / P.nTiles;
-  const int slab0 = SPLIT ? split * P.nSlabs / kSplit : 0;
-  const int nLoc = SPLIT ? (split + 1) * P.nSlabs / kSplit - slab0 : P.nSlabs; // this CTA's share of the K slabs
-  const int row0 = tileM * BM;
+  const int nItems = P.mTiles * P.nTiles * kSplit;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P.stages; ++s) {
@@ -189,146 +162,215 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
       mbar_init(fullBar + 8 * s, 128 + 1); // the split threads + the weight copy
       mbar_init(emptyBar + 8 * s, 1);      // tcgen05.commit
     }
-    mbar_init(accumBar, 1);
+    for (int a = 0; a < 2; ++a) { mbar_init(accFullBar + 8 * a, 1); mbar_init(accEmptyBar + 8 * a, 128); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 9) { // tensor memory for the 128 x BN fp32 accumulator
+  if (warp == 13) { // tensor memory: two 128 x BN fp32 accumulators
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmemBase)), "r"((uint32_t)P.tmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  if (P.rulesBytes > 0) { // this tile's rules, so the gather does not chain two global loads per slab
-    const int n = BM * P.fs;
-    for (int e = threadIdx.x; e < n; e += NUM_THREADS) {
-      const int r = row0 + e / P.fs;
-      rulesS[e] = (r < P.rows) ? __ldg(P.rules + (long long)row0 * P.fs + e) : -1;
-    }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmemBase;
 
+  // decode a work item
+  auto itemTile = [&](int item, int &tileM, int &tileN, int &slab0, int &nLoc) {
+    const int tileId = SPLIT ? item / kSplit : item, split = SPLIT ? item - tileId * kSplit : 0;
+    tileN = tileId % P.nTiles; tileM = tileId / P.nTiles;
+    slab0 = SPLIT ? split * P.nSlabs / kSplit : 0;
+    nLoc = SPLIT ? (split + 1) * P.nSlabs / kSplit - slab0 : P.nSlabs;
+    return split;
+  };
+
   if (warp < 4) {
-    // ------------------------------------------------------------ gather: asynchronous 16-byte copies
-    const int t = threadIdx.x, chunk = t & 7, rbase = t >> 3;
-    // this thread's 16-byte chunk sits at the same offset in each of its 8 rows (16 rows apart)
-    const uint32_t rowOff = (rbase >> 3) * 1024 + (rbase & 7) * ROW_BYTES + ((chunk ^ (rbase & 7)) << 4);
-    const float *rowPtr[8]; // start of the current filter cell's source row (nullptr: no row -> zero fill)
-    int curF = -1;
-    for (int q = 0; q < nLoc; ++q) {
-      const int s = slab0 + q, st = q % P.stages, it = q / P.stages;
-      const int k0 = s * SLAB, f = k0 / P.nIn, c0 = k0 - f * P.nIn;
-      if (f != curF) { // the rule column changes every nIn/32 slabs
-        curF = f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int rl = rbase + 16 * i, r = row0 + rl;
-          int src;
-          if (P.rulesBytes > 0) src = rulesS[rl * P.fs + f];
-          else if (P.rules) src = (r < P.rows) ? __ldg(P.rules + (long long)r * P.fs + f) : -1;
-          else src = (r < P.rows) ? r : -1;
-          rowPtr[i] = src >= 0 ? P.in + (long long)src * P.nIn + chunk * 4 : nullptr;
-        }
-      }
-      mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 1);
-      const uint32_t dst = smem_u32(smem + (size_t)st * stageBytes) + rowOff;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        // a negative rule (or a row past the end) copies 0 source bytes: the 16 bytes are zero-filled
-        const bool have = rowPtr[i] != nullptr;
-        cp_async16(dst + i * 2048, have ? (const void *)(rowPtr[i] + c0) : (const void *)P.in, have ? 16u : 0u);
-      }
-      cp_async_arrive(rawBar + 8 * st);
-    }
     // ------------------------------------------------------------ epilogue
-    // TMEM holds one output row per lane, so a direct store would scatter 32 rows per
-    // instruction.  The accumulators go through shared memory instead (the pipeline stages are
-    // idle by now): lanes write their rows with a padded stride, then every warp stores whole
-    // rows, 512 contiguous bytes per instruction, applying p*acc + p*bias and the activation.
-    mbar_wait(accumBar, 0, 2);
-    tc_fence_after();
-    float *tile = reinterpret_cast<float *>(smem);
-    const int ld = P.BN + 4; // floats; keeps 16-byte alignment and spreads rows over the banks
-    {
-      const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
-      float *myRow = tile + (size_t)(warp * 32 + lane) * ld;
-      for (int c = 0; c < P.BN; c += 16) {
-        uint32_t a[16];
+    const int t = threadIdx.x;
+    const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
+    float *myRow = epi + (size_t)t * EPI_LD;
+    const int c4 = t & 7, rsub = t >> 3; // store phase: 8 threads per row, 16 rows per pass
+    int n = 0;
+    for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++n) {
+      int tileM, tileN, slab0, nLoc;
+      const int split = itemTile(item, tileM, tileN, slab0, nLoc);
+      const int ab = n & 1;
+      mbar_wait(accFullBar + 8 * ab, (n >> 1) & 1, 2);
+      tc_fence_after();
+      const int row0 = tileM * BM, col0 = tileN * P.BN;
+      for (int c = 0; c < P.BN; c += EPI_COLS) {
+        const int width = min(EPI_COLS, P.BN - c); // 32, or 16 for the last slice when BN % 32 == 16
+        uint32_t a[32];
+        const uint32_t addr = laneAddr + (uint32_t)(ab * P.accStride + c);
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]),
                        "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15])
-                     : "r"(laneAddr + (uint32_t)c));
+                     : "r"(addr));
+        if (width > 16)
+          asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                       : "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]),
+                         "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31])
+                       : "r"(addr + 16));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int q = 0; q < 16; q += 4)
-          *reinterpret_cast<float4 *>(myRow + c + q) = make_float4(__uint_as_float(a[q]), __uint_as_float(a[q + 1]), __uint_as_float(a[q + 2]), __uint_as_float(a[q + 3]));
-      }
-    }
-    tc_fence_before();
-    asm volatile("bar.sync 1, 128;" ::: "memory"); // the four epilogue warps only
-    if (SPLIT) store_tile<true, SCN_NOSIGMOID>(P, tile, ld, row0, tileN, split, warp, lane);
-    else { SCN_DISPATCH_ACT(P.act, (store_tile<false, ACT>(P, tile, ld, row0, tileN, split, warp, lane))); }
-  } else if (warp < 8) {
-    // ------------------------------------------------------------ split: fp32 -> tf32 hi (in place) + tf32 lo
-    const int t = threadIdx.x - 128;
-    for (int q = 0; q < nLoc; ++q) {
-      const int s = slab0 + q, st = q % P.stages, it = q / P.stages;
-      mbar_wait(rawBar + 8 * st, it & 1, 5);
-      unsigned char *aHi = smem + (size_t)st * stageBytes, *aLo = aHi + A_HALF;
+        for (int q = 0; q < 32; q += 4)
+          if (q < width)
+            *reinterpret_cast<float4 *>(myRow + q) = make_float4(__uint_as_float(a[q]), __uint_as_float(a[q + 1]), __uint_as_float(a[q + 2]), __uint_as_float(a[q + 3]));
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // coalesced: 8 threads cover one row's 128 bytes, a warp covers 4 rows per instruction
+        const int col = col0 + c + c4 * 4;
+        const bool colOk = c4 * 4 < width && col < P.N; // N % 4 == 0: a float4 is in or out as a whole
+        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = b4;
+        if (colOk && !SPLIT) {
+          b4 = __ldg(reinterpret_cast<const float4 *>(P.bias + col));
+          if (ACT == SCN_PRELU) s4 = __ldg(reinterpret_cast<const float4 *>(P.prelu + col));
+        }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int off = t * 16 + i * 2048; // the swizzle is the same in both images: work on raw offsets
-        const float4 v = *reinterpret_cast<const float4 *>(aHi + off);
-        // kind::tf32 reads the upper 19 bits of each fp32 (sign, exponent, 10 mantissa bits), so
-        // the raw tile already is the "hi" operand; lo = x - hi is exact in fp32 and is cut to
-        // tf32 the same way when it is read.
-        float4 lo;
-        lo.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
-        lo.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
-        lo.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
-        lo.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-        *reinterpret_cast<float4 *>(aLo + off) = lo;
+        for (int pass = 0; pass < BM / 16; ++pass) {
+          const int rl = pass * 16 + rsub, r = row0 + rl;
+          if (!colOk || r >= P.rows) continue;
+          const float4 v = *reinterpret_cast<const float4 *>(epi + (size_t)rl * EPI_LD + c4 * 4);
+          if (SPLIT) {
+            *reinterpret_cast<float4 *>(P.partial + ((long long)split * P.rows + r) * P.N + col) = v;
+          } else {
+            float4 o;
+            // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
+            o.x = activate_t<ACT>(P.p * v.x + P.p * b4.x, s4.x); o.y = activate_t<ACT>(P.p * v.y + P.p * b4.y, s4.y);
+            o.z = activate_t<ACT>(P.p * v.z + P.p * b4.z, s4.z); o.w = activate_t<ACT>(P.p * v.w + P.p * b4.w, s4.w);
+            *reinterpret_cast<float4 *>(P.out + (long long)r * P.N + col) = o;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory"); // the slice is free again
       }
-      fence_async_smem(); // make the generic-proxy stores visible to the tensor core's reads
-      mbar_arrive(fullBar + 8 * st);
+      tc_fence_before();
+      mbar_arrive(accEmptyBar + 8 * ab); // this accumulator may be overwritten
     }
-  } else if (warp == 8) {
+  } else if (warp < 8) {
+    // ------------------------------------------------------------ gather: asynchronous 16-byte copies
+    const int t = threadIdx.x - 128, chunk = t & 7, rbase = t >> 3;
+    // this thread's 16-byte chunk sits at the same offset in each of its 8 rows (16 rows apart)
+    const uint32_t rowOff = (rbase >> 3) * 1024 + (rbase & 7) * ROW_BYTES + ((chunk ^ (rbase & 7)) << 4);
+    int g = 0;
+    for (int item = blockIdx.x; item < nItems; item += gridDim.x) {
+      int tileM, tileN, slab0, nLoc;
+      itemTile(item, tileM, tileN, slab0, nLoc);
+      const int row0 = tileM * BM;
+      if (P.rulesBytes > 0) { // this tile's rules, so the gather does not chain two global loads per slab
+        asm volatile("bar.sync 2, 128;" ::: "memory"); // everyone has issued the previous item's copies
+        const int nr = BM * P.fs;
+        for (int e = t; e < nr; e += 128) {
+          const int r = row0 + e / P.fs;
+          rulesS[e] = (r < P.rows) ? __ldg(P.rules + (long long)row0 * P.fs + e) : -1;
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+      }
+      const float *rowPtr[8]; // start of the current filter cell's source row (nullptr: no row -> zero fill)
+      int curF = -1;
+      for (int q = 0; q < nLoc; ++q, ++g) {
+        const int s = slab0 + q, st = g % P.stages, it = g / P.stages;
+        const int k0 = s * SLAB, f = k0 / P.nIn, c0 = k0 - f * P.nIn;
+        if (f != curF) { // the rule column changes every nIn/32 slabs
+          curF = f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rl = rbase + 16 * i, r = row0 + rl;
+            int src;
+            if (P.rulesBytes > 0) src = rulesS[rl * P.fs + f];
+            else if (P.rules) src = (r < P.rows) ? __ldg(P.rules + (long long)r * P.fs + f) : -1;
+            else src = (r < P.rows) ? r : -1;
+            rowPtr[i] = src >= 0 ? P.in + (long long)src * P.nIn + chunk * 4 : nullptr;
+          }
+        }
+        mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 1);
+        const uint32_t dst = smem_u32(smem + (size_t)st * stageBytes) + rowOff;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          // a negative rule (or a row past the end) copies 0 source bytes: the 16 bytes are zero-filled
+          const bool have = rowPtr[i] != nullptr;
+          cp_async16(dst + i * 2048, have ? (const void *)(rowPtr[i] + c0) : (const void *)P.in, have ? 16u : 0u);
+        }
+        cp_async_arrive(rawBar + 8 * st);
+      }
+    }
+  } else if (warp < 12) {
+    // ------------------------------------------------------------ split: lo = x - tf32(x)
+    const int t = threadIdx.x - 256;
+    int g = 0;
+    for (int item = blockIdx.x; item < nItems; item += gridDim.x) {
+      int tileM, tileN, slab0, nLoc;
+      itemTile(item, tileM, tileN, slab0, nLoc);
+      for (int q = 0; q < nLoc; ++q, ++g) {
+        const int st = g % P.stages, it = g / P.stages;
+        mbar_wait(rawBar + 8 * st, it & 1, 5);
+        unsigned char *aHi = smem + (size_t)st * stageBytes, *aLo = aHi + A_HALF;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int off = t * 16 + i * 2048; // the swizzle is the same in both images: work on raw offsets
+          const float4 v = *reinterpret_cast<const float4 *>(aHi + off);
+          // kind::tf32 reads the upper 19 bits of each fp32 (sign, exponent, 10 mantissa bits), so
+          // the raw tile already is the "hi" operand; lo = x - hi is exact in fp32 and is cut to
+          // tf32 the same way when it is read.
+          float4 lo;
+          lo.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+          lo.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+          lo.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+          lo.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+          *reinterpret_cast<float4 *>(aLo + off) = lo;
+        }
+        fence_async_smem(); // make the generic-proxy stores visible to the tensor core's reads
+        mbar_arrive(fullBar + 8 * st);
+      }
+    }
+  } else if (warp == 12) {
     // ------------------------------------------------------------ weight tiles by bulk copy
     if (lane == 0) {
       const uint32_t bytes = 2 * bHalf;
-      const unsigned char *srcBase = P.packed + (size_t)tileN * P.nSlabs * bytes;
-      for (int q = 0; q < nLoc; ++q) {
-        const int s = slab0 + q, st = q % P.stages, it = q / P.stages;
-        mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 3);
-        mbar_arrive_expect_tx(fullBar + 8 * st, bytes);
-        bulk_g2s(smem_u32(smem + (size_t)st * stageBytes + 2 * A_HALF), srcBase + (size_t)s * bytes, bytes, fullBar + 8 * st);
+      int g = 0;
+      for (int item = blockIdx.x; item < nItems; item += gridDim.x) {
+        int tileM, tileN, slab0, nLoc;
+        itemTile(item, tileM, tileN, slab0, nLoc);
+        const unsigned char *srcBase = P.packed + ((size_t)tileN * P.nSlabs + slab0) * bytes;
+        for (int q = 0; q < nLoc; ++q, ++g) {
+          const int st = g % P.stages, it = g / P.stages;
+          mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 3);
+          mbar_arrive_expect_tx(fullBar + 8 * st, bytes);
+          bulk_g2s(smem_u32(smem + (size_t)st * stageBytes + 2 * A_HALF), srcBase + (size_t)q * bytes, bytes, fullBar + 8 * st);
+        }
       }
     }
   } else {
     // ------------------------------------------------------------ MMA issue
     if (lane == 0) {
-      for (int q = 0; q < nLoc; ++q) {
-        const int s = slab0 + q, st = q % P.stages, it = q / P.stages;
-        mbar_wait(fullBar + 8 * st, it & 1, 4);
+      int g = 0, n = 0;
+      for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++n) {
+        int tileM, tileN, slab0, nLoc;
+        itemTile(item, tileM, tileN, slab0, nLoc);
+        const int ab = n & 1;
+        mbar_wait(accEmptyBar + 8 * ab, ((n >> 1) & 1) ^ 1, 6); // the epilogue has drained this accumulator
         tc_fence_after();
-        const uint32_t aHi = smem_u32(smem + (size_t)st * stageBytes), aLo = aHi + A_HALF;
-        const uint32_t bHi = aHi + 2 * A_HALF, bLo = bHi + bHalf;
-        const uint64_t dAhi = smem_desc(aHi), dAlo = smem_desc(aLo), dBhi = smem_desc(bHi), dBlo = smem_desc(bLo);
-        // small cross terms first, the dominant hi*hi product last
+        const uint32_t acc = tmem + (uint32_t)(ab * P.accStride);
+        for (int q = 0; q < nLoc; ++q, ++g) {
+          const int st = g % P.stages, it = g / P.stages;
+          mbar_wait(fullBar + 8 * st, it & 1, 4);
+          tc_fence_after();
+          const uint32_t aHi = smem_u32(smem + (size_t)st * stageBytes), aLo = aHi + A_HALF;
+          const uint32_t bHi = aHi + 2 * A_HALF, bLo = bHi + bHalf;
+          const uint64_t dAhi = smem_desc(aHi), dAlo = smem_desc(aLo), dBhi = smem_desc(bHi), dBlo = smem_desc(bLo);
+          // small cross terms first, the dominant hi*hi product last
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_tf32(tmem, dAlo + 2 * k, dBhi + 2 * k, P.idesc, (q | k) != 0);
+          for (int k = 0; k < 4; ++k) mma_tf32(acc, dAlo + 2 * k, dBhi + 2 * k, P.idesc, (q | k) != 0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_tf32(tmem, dAhi + 2 * k, dBlo + 2 * k, P.idesc, 1);
+          for (int k = 0; k < 4; ++k) mma_tf32(acc, dAhi + 2 * k, dBlo + 2 * k, P.idesc, 1);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_tf32(tmem, dAhi + 2 * k, dBhi + 2 * k, P.idesc, 1);
-        mma_commit(emptyBar + 8 * st); // frees the stage once these MMAs have read it
+          for (int k = 0; k < 4; ++k) mma_tf32(acc, dAhi + 2 * k, dBhi + 2 * k, P.idesc, 1);
+          mma_commit(emptyBar + 8 * st); // frees the stage once these MMAs have read it
+        }
+        mma_commit(accFullBar + 8 * ab);
       }
-      mma_commit(accumBar);
     }
   }
   __syncwarp(); // the single-thread roles rejoin their warps before the block-wide barrier
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 13) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)P.tmemCols) : "memory");
   }
@@ -387,7 +429,7 @@ int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) 
   return k < 2 ? 1 : k;
 }
 
-struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; size_t smemBytes; };
+struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, accStride; size_t smemBytes; };
 
 bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
   if (K % SLAB != 0 || N < 16) return false;
@@ -396,14 +438,15 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
   t->BN = ((N + t->nTiles - 1) / t->nTiles + 15) / 16 * 16;
   t->nSlabs = K / SLAB;
   const int stageBytes = 2 * A_HALF + 2 * t->BN * ROW_BYTES;
-  int stages = (int)((226 * 1024 - 1024 - t->rulesBytes) / stageBytes);
+  int stages = (int)((226 * 1024 - 1024 - t->rulesBytes - EPI_BYTES) / stageBytes);
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages < 2) return false;
   t->stages = stages;
+  t->accStride = (t->BN + 31) / 32 * 32;
   int cols = 32;
-  while (cols < t->BN) cols *= 2;
+  while (cols < 2 * t->accStride) cols *= 2; // two accumulators, at most 2 x 256 columns
   t->tmemCols = cols;
-  t->smemBytes = (size_t)stages * stageBytes + 1024 + t->rulesBytes;
+  t->smemBytes = (size_t)stages * stageBytes + 1024 + t->rulesBytes + EPI_BYTES;
   return true;
 }
 
@@ -446,14 +489,6 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   if (precision != SCN_PREC_3XTF32 || nIn % SLAB != 0 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t))
     return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
   if (((uintptr_t)d_in | (uintptr_t)d_out | (uintptr_t)d_packed) & 15) return fail(SCN_ERR_INVALID, "tensor-core path needs 16-byte aligned buffers");
-  static bool attrSet[64] = {false};
-  int dev = 0;
-  SCN_CUDA_TRY(cudaGetDevice(&dev));
-  if (!attrSet[dev & 63]) {
-    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    attrSet[dev & 63] = true;
-  }
   Params P;
   P.in = d_in; P.rules = d_rules; P.rows = rows; P.fs = fs; P.nIn = nIn;
   P.packed = (const unsigned char *)d_packed; P.bias = d_B; P.prelu = d_prelu;
@@ -464,8 +499,16 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   const int mTiles = (rows + BM - 1) / BM;
   P.kSplit = (d_ws && ((uintptr_t)d_ws & 15) == 0) ? choose_ksplit(mTiles * t.nTiles, t.nSlabs, rows, N, wsBytes) : 1;
   P.partial = (float *)d_ws;
-  if (P.kSplit > 1) k_conv_nin_tc<true><<<mTiles * t.nTiles * P.kSplit, NUM_THREADS, t.smemBytes, s>>>(P);
-  else k_conv_nin_tc<false><<<mTiles * t.nTiles, NUM_THREADS, t.smemBytes, s>>>(P);
+  P.mTiles = mTiles; P.accStride = t.accStride;
+  const int items = mTiles * t.nTiles * P.kSplit;
+  const int grid = items < sm_count() ? items : sm_count(); // persistent: one CTA per SM
+  if (P.kSplit > 1) {
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<true, SCN_NOSIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    k_conv_nin_tc<true, SCN_NOSIGMOID><<<grid, NUM_THREADS, t.smemBytes, s>>>(P);
+  } else {
+    SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+                     (k_conv_nin_tc<false, ACT><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
+  }
   SCN_LAUNCH_CHECK("k_conv_nin_tc");
   if (P.kSplit > 1) {
     SCN_DISPATCH_ACT(act, (k_splitk_finish<ACT><<<grid_for((long long)rows * N / 4, 256), 256, 0, s>>>(P.partial, P.kSplit, rows, N, d_B, d_prelu, p, d_out)));
