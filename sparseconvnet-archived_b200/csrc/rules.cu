@@ -513,7 +513,7 @@ template <int DIM> __device__ bool creates_f(const Regions &R, const uint2 *d, c
   return seenSelf && active >= R.minActive;
 }
 
-constexpr int CHAIN_THREADS = 256;
+constexpr int CHAIN_THREADS = 512;
 constexpr unsigned long long CHAIN_WAIT_NS = 2000000000ull;
 
 __device__ __forceinline__ unsigned long long chain_ns() {
@@ -523,7 +523,7 @@ __device__ __forceinline__ unsigned long long chain_ns() {
 }
 
 template <int DIM>
-__global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams P) {
+__global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   extern __shared__ __align__(16) unsigned char chain_smem[];
   __shared__ Regions R;
   __shared__ int sTicket, sTotal, sBase, sSitesBase;
@@ -534,6 +534,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
   int *cnt = sorted + P.rowsMax; // rowsMax + 1
   unsigned char *flags = reinterpret_cast<unsigned char *>(cnt + P.rowsMax + 1);
   const int tid = threadIdx.x;
+  const int NT = blockDim.x;
 
   if (tid == 0) sTicket = atomicAdd(P.ticket, 1);
   __syncthreads();
@@ -548,16 +549,16 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
     if (tid == 0) for (int l = 0; l < P.nLayers; ++l) { atomicOr(P.layers[l].result + 2, SCN_DEV_ERR_CAPACITY); P.counts[l * P.batch + b] = 0; }
     return;
   }
-  for (int j = tid; j < nRows; j += CHAIN_THREADS) inKeys[j] = P.inKeys[inBase + j];
+  for (int j = tid; j < nRows; j += NT) inKeys[j] = P.inKeys[inBase + j];
 
   for (int l = 0; l < P.nLayers; ++l) {
     const ChainLayer &L = P.layers[l];
     __syncthreads();
-    for (int i = tid; i < (int)(sizeof(Regions) / 4); i += CHAIN_THREADS) reinterpret_cast<int *>(&R)[i] = reinterpret_cast<const int *>(&L.R)[i];
-    for (int w = tid; w < P.wMax; w += CHAIN_THREADS) dir[w] = make_uint2(0u, 0u);
+    for (int i = tid; i < (int)(sizeof(Regions) / 4); i += NT) reinterpret_cast<int *>(&R)[i] = reinterpret_cast<const int *>(&L.R)[i];
+    for (int w = tid; w < P.wMax; w += NT) dir[w] = make_uint2(0u, 0u);
     __syncthreads();
     // 1. occupancy bits
-    for (int j = tid; j < nRows; j += CHAIN_THREADS) {
+    for (int j = tid; j < nRows; j += NT) {
       const int key = inKeys[j];
       if (key < 0) continue;
       if (key >= R.cells) { atomicOr(L.result + 2, SCN_DEV_ERR_KEY); continue; }
@@ -569,7 +570,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
     int nSites = 0;
     {
       int carry = 0;
-      for (int w0 = 0; w0 < R.W; w0 += CHAIN_THREADS) {
+      for (int w0 = 0; w0 < R.W; w0 += NT) {
         const int w = w0 + tid;
         const int c = (w < R.W) ? __popc(dir[w].x) : 0;
         int total;
@@ -585,12 +586,12 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
       return;
     }
     // 3. ascending-key order, 4. which outputs each site creates
-    for (int j = tid; j < nRows; j += CHAIN_THREADS) {
+    for (int j = tid; j < nRows; j += NT) {
       const int key = inKeys[j];
       if (key >= 0 && key < R.cells) sorted[cell_rank(dir, key)] = j;
     }
     __syncthreads();
-    for (int slot = tid; slot < nSites; slot += CHAIN_THREADS) {
+    for (int slot = tid; slot < nSites; slot += NT) {
       int i[DIM], j[DIM];
       decode_f<DIM>(inKeys[sorted[slot]], R.nIn, R.rNIn, i);
       int c = 0;
@@ -605,7 +606,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
     // 5. prefix sums of the counts
     {
       int carry = 0;
-      for (int s0 = 0; s0 < nSites; s0 += CHAIN_THREADS) {
+      for (int s0 = 0; s0 < nSites; s0 += NT) {
         const int s = s0 + tid;
         const int c = (s < nSites) ? cnt[s] : 0;
         int total;
@@ -630,7 +631,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
     __syncthreads();
     {
       int rowsBefore = 0, bgBefore = 0;
-      for (int p = tid; p < b; p += CHAIN_THREADS) {
+      for (int p = tid; p < b; p += NT) {
         volatile int *slotp = P.counts + l * P.batch + p;
         int v = *slotp;
         if (v < 0) {
@@ -663,7 +664,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
       return;
     }
     // 7. output keys (shared copy for the next layer + the interface's array)
-    for (int p = tid; p < nSites * R.T; p += CHAIN_THREADS) {
+    for (int p = tid; p < nSites * R.T; p += NT) {
       if (!flags[p]) continue;
       int t;
       const int slot = fdiv(p, R.T, R.rT, &t);
@@ -680,7 +681,7 @@ __global__ void __launch_bounds__(CHAIN_THREADS) k_rule_chain(const ChainParams 
     if (needBg && tid == 0) { outKeysS[sitesOut] = -1; L.outKeys[base + sitesOut] = -1; }
     __syncthreads();
     // 8. rule cells, coalesced over this sample's block of rows
-    for (int q = tid; q < rowsOut * R.sd; q += CHAIN_THREADS) {
+    for (int q = tid; q < rowsOut * R.sd; q += NT) {
       int col;
       const int r = fdiv(q, R.sd, R.rSd, &col);
       const int key = outKeysS[r];
@@ -951,11 +952,12 @@ extern "C" int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_laye
   P.inKeys = d_in_keys; P.inOff = d_in_off; P.inBg = d_in_bg;
   P.counts = counts; P.ticket = ticket;
   P.rowsMax = plan.rowsMax; P.wMax = plan.wMax; P.tMax = plan.tMax; P.flagBytes = (int)std::min<size_t>(plan.flagBytes, 0x7fffffff);
+  const int chainThreads = CHAIN_THREADS;
   switch (Rs[0].dim) {
-  case 1: k_rule_chain<1><<<batch, CHAIN_THREADS, plan.smemBytes, s>>>(P); break;
-  case 2: k_rule_chain<2><<<batch, CHAIN_THREADS, plan.smemBytes, s>>>(P); break;
-  case 3: k_rule_chain<3><<<batch, CHAIN_THREADS, plan.smemBytes, s>>>(P); break;
-  default: k_rule_chain<4><<<batch, CHAIN_THREADS, plan.smemBytes, s>>>(P); break;
+  case 1: k_rule_chain<1><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
+  case 2: k_rule_chain<2><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
+  case 3: k_rule_chain<3><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
+  default: k_rule_chain<4><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
   }
   SCN_LAUNCH_CHECK("k_rule_chain");
   return SCN_OK;
