@@ -240,7 +240,7 @@ extern "C" int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, in
   int use = precision;
   if (precision == SCN_PREC_AUTO) use = (d_W_packed && tc_shape_ok(fs, nIn, N, SCN_PREC_3XTF32)) ? SCN_PREC_3XTF32 : SCN_PREC_FP32;
   if (use != SCN_PREC_FP32) {
-    if (!tc_shape_ok(fs, nIn, N, use)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel (need nIn % 8 == 0, N % 16 == 0)");
+    if (!tc_shape_ok(fs, nIn, N, use)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel (need N >= 16 and N % 4 == 0)");
     if (!d_W_packed) return fail(SCN_ERR_INVALID, "tensor-core precision needs packed weights");
     int st = tc_launch(d_in, d_rules, rows_out, fs, nIn, d_W_packed, d_B, d_prelu, N, p, inner, use, d_out, d_workspace, workspace_bytes, s);
     if (st != SCN_OK) return st;

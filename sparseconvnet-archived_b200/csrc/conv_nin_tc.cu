@@ -116,13 +116,16 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
-  int mTiles, accStride; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
+  int mTiles, accStride, K, generic; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(srcBytes) : "memory");
 }
 // The barrier receives one arrival once all cp.async issued so far by this thread have landed.
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t srcBytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(srcBytes) : "memory");
+}
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -262,6 +265,37 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
           rulesS[e] = (r < P.rows) ? __ldg(P.rules + (long long)row0 * P.fs + e) : -1;
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
+      }
+      if (P.generic) {
+        // nIn is not a multiple of 32 (e.g. 3 input channels): a slab spans several filter cells,
+        // so the tile is gathered element by element with 4-byte copies, one row per thread;
+        // k >= K (the padding up to a multiple of 32) and missing rows are zero-filled.
+        const int rl = t, r = row0 + rl;
+        const uint32_t rowBase = (rl >> 3) * 1024 + (rl & 7) * ROW_BYTES;
+        for (int q = 0; q < nLoc; ++q, ++g) {
+          const int s = slab0 + q, st = g % P.stages, it = g / P.stages;
+          int k = s * SLAB, f = k / P.nIn, c = k - f * P.nIn;
+          mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 1);
+          const uint32_t dst = smem_u32(smem + (size_t)st * stageBytes) + rowBase;
+          const float *rowPtr = nullptr;
+          int haveF = -1;
+#pragma unroll 4
+          for (int kk = 0; kk < SLAB; ++kk, ++k) {
+            if (k < P.K && f != haveF) {
+              haveF = f;
+              int src;
+              if (P.rulesBytes > 0) src = rulesS[rl * P.fs + f];
+              else if (P.rules) src = (r < P.rows) ? __ldg(P.rules + (long long)r * P.fs + f) : -1;
+              else src = (r < P.rows) ? r : -1;
+              rowPtr = src >= 0 ? P.in + (long long)src * P.nIn : nullptr;
+            }
+            const bool have = k < P.K && rowPtr != nullptr;
+            cp_async4(dst + ((((kk >> 2) ^ (rl & 7))) << 4) + (kk & 3) * 4, have ? (const void *)(rowPtr + c) : (const void *)P.in, have ? 4u : 0u);
+            if (++c == P.nIn) { c = 0; ++f; }
+          }
+          cp_async_arrive(rawBar + 8 * st);
+        }
+        continue;
       }
       const float *rowPtr[8]; // start of the current filter cell's source row (nullptr: no row -> zero fill)
       int curF = -1;
@@ -432,11 +466,11 @@ int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) 
 struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, accStride; size_t smemBytes; };
 
 bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
-  if (K % SLAB != 0 || N < 16) return false;
+  if (K < 1 || N < 16) return false;
   t->rulesBytes = (haveRules && fs <= 32) ? BM * fs * 4 : 0;
   t->nTiles = (N + 255) / 256;
   t->BN = ((N + t->nTiles - 1) / t->nTiles + 15) / 16 * 16;
-  t->nSlabs = K / SLAB;
+  t->nSlabs = (K + SLAB - 1) / SLAB; // the last slab is zero-padded
   const int stageBytes = 2 * A_HALF + 2 * t->BN * ROW_BYTES;
   int stages = (int)((226 * 1024 - 1024 - t->rulesBytes - EPI_BYTES) / stageBytes);
   if (stages > MAX_STAGES) stages = MAX_STAGES;
@@ -455,7 +489,7 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
 bool tc_shape_ok(int fs, int nIn, int N, int precision) {
   if (precision != SCN_PREC_3XTF32) return false;
   Tiling t;
-  return nIn % SLAB == 0 && N % 4 == 0 && make_tiling(fs * nIn, N, fs, true, &t);
+  return N % 4 == 0 && make_tiling(fs * nIn, N, fs, true, &t);
 }
 
 size_t tc_packed_bytes(int K, int N, int precision) {
@@ -476,7 +510,7 @@ int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaS
 
 size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision) {
   Tiling t;
-  if (precision != SCN_PREC_3XTF32 || nIn % SLAB != 0 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, true, &t)) return 0;
+  if (precision != SCN_PREC_3XTF32 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, true, &t)) return 0;
   const int tiles = ((rows + BM - 1) / BM) * t.nTiles;
   const int k = choose_ksplit(tiles, t.nSlabs, rows, N, (size_t)-1);
   return k > 1 ? (size_t)k * rows * N * sizeof(float) : 0;
@@ -486,7 +520,7 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
               const float *d_prelu, int N, float p, int act, int precision, float *d_out, void *d_ws, size_t wsBytes,
               cudaStream_t s) {
   Tiling t;
-  if (precision != SCN_PREC_3XTF32 || nIn % SLAB != 0 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t))
+  if (precision != SCN_PREC_3XTF32 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t))
     return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
   if (((uintptr_t)d_in | (uintptr_t)d_out | (uintptr_t)d_packed) & 15) return fail(SCN_ERR_INVALID, "tensor-core path needs 16-byte aligned buffers");
   Params P;
@@ -500,6 +534,7 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   P.kSplit = (d_ws && ((uintptr_t)d_ws & 15) == 0) ? choose_ksplit(mTiles * t.nTiles, t.nSlabs, rows, N, wsBytes) : 1;
   P.partial = (float *)d_ws;
   P.mTiles = mTiles; P.accStride = t.accStride;
+  P.K = fs * nIn; P.generic = (nIn % SLAB != 0) ? 1 : 0;
   const int items = mTiles * t.nTiles * P.kSplit;
   const int grid = items < sm_count() ? items : sm_count(); // persistent: one CTA per SM
   if (P.kSplit > 1) {

@@ -124,6 +124,12 @@ CONV_TC = [
     (256, 256, 1, 608, 32, "NOSIGMOID", 1.0),     # plain NiN, 19 slabs
     (100, 90, 4, 128, 416, "PRELU", 1.0),
     (64, 50, 27, 32, 96, "TANH", 1.0),
+    # element-wise gather (nIn not a multiple of 32; K padded to a multiple of 32)
+    (1000, 1357, 9, 3, 96, "VLEAKYRELU", 0.9),    # the benchmark's first convolution, K = 27
+    (200, 300, 4, 24, 64, "RELU", 1.0),
+    (64, 150, 27, 1, 32, "LEAKYRELU", 1.0),
+    (100, 100, 1, 40, 48, "PRELU", 1.0),
+    (300, 200, 8, 20, 288, "VLEAKYRELU", 1.0),
 ]
 
 
@@ -160,15 +166,15 @@ def test_conv_nin_tensor_core_3xtf32(abi, oracle, rows_in, rows_out, fs, nIn, N,
 
 def test_tensor_core_path_rejects_unsupported_shapes(abi):
     f = torch.zeros((4, 24), device="cuda")
-    W = torch.zeros((24, 16), device="cuda")
-    B = torch.zeros(16, device="cuda")
+    W = torch.zeros((24, 10), device="cuda")
+    B = torch.zeros(10, device="cuda")
     with pytest.raises(abi.ScnError):
-        abi.pack_weights(W, abi.PREC_3XTF32)  # K not a multiple of 32
+        abi.pack_weights(W, abi.PREC_3XTF32)  # fewer than 16 output columns
     with pytest.raises(abi.ScnError):
         abi.conv_nin_forward(f, None, 1, W, B, precision=abi.PREC_3XTF32, packed=torch.zeros(16, dtype=torch.uint8, device="cuda"))
-    # AUTO falls back to the CUDA-core kernel for such shapes
+    # AUTO falls back to the CUDA-core kernels for such shapes
     out = abi.conv_nin_forward(f, None, 1, W, B, precision=abi.PREC_AUTO)
-    assert out.shape == (4, 16)
+    assert out.shape == (4, 10)
 
 
 def test_conv_nin_rejects_bad_arguments(abi):
