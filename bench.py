@@ -115,21 +115,22 @@ def build_pair(scn, want_oracle):
 
 
 def cpu_leg(scn, onet, budget_s, threads):
-    """Oracle forward on a bounded sample sized for about budget_s seconds of wall time."""
-    gen = scn.synth.CONFIGS[CFG]["gen"]
-    keys, off, feats = gen(threads)  # one sample per thread to estimate the rate
-    t0 = time.time()
-    onet.forward(keys.astype(np.int64), off, feats, threads=threads)
-    per_sample = (time.time() - t0) / threads * threads  # wall seconds per `threads` samples
-    n = int(max(threads, min(BATCH_PER_GPU, threads * max(1, round(budget_s / max(per_sample, 1e-3))))))
-    keys, off, feats = gen(n)
-    t0 = time.time()
-    onet.forward(keys.astype(np.int64), off, feats, threads=threads)
+    """Oracle forward over whole batches of the workload until about budget_s seconds of wall time."""
+    keys, off, feats = scn.synth.CONFIGS[CFG]["gen"](BATCH_PER_GPU)
+    keys = keys.astype(np.int64)
+    onet.forward(keys[: off[threads]], off[: threads + 1], feats[: off[threads]], threads=threads)  # warm-up
+    n, rules_s, t0 = 0, 0.0, time.time()
+    while True:
+        onet.forward(keys, off, feats, threads=threads)
+        n += BATCH_PER_GPU
+        rules_s += float(onet.times[0])
+        if time.time() - t0 >= budget_s:
+            break
     wall = time.time() - t0
     return dict(value=n / wall, unit="samples/s", cores=threads, kind="port",
-                sample="%d samples of the workload, oracle fp32 forward incl. rule construction, %.1f s wall "
-                       "(rule construction alone %.0f samples/s)" % (n, wall, n / max(onet.times[0], 1e-9)),
-                rules_only_samples_per_s=n / max(float(onet.times[0]), 1e-9))
+                sample="%d samples (%d batches of %d) of the workload, oracle fp32 forward incl. rule construction, %.1f s wall; "
+                       "rule construction alone %.0f samples/s" % (n, n // BATCH_PER_GPU, BATCH_PER_GPU, wall, n / max(rules_s, 1e-9)),
+                rules_only_samples_per_s=n / max(rules_s, 1e-9))
 
 
 def run_reference(args, scn):
@@ -311,15 +312,28 @@ def main():
             byts = 4.0 * (rows_out * L["fs"] + rows_in * C + 2 * rows_out * C)
             per_layer.append(dict(layer=i, kernel="maxpool_rules", rows=rows_out, C=C, ms=ms, flops=0.0, bytes=byts))
     rules_ms = float(layer_ms[len(layers)])
-    top = max(per_layer, key=lambda d: d["ms"])
-    if top["kernel"] != "maxpool_rules" and top["K"] >= 128:
-        ach = top["flops"] / (top["ms"] * 1e-3) / 1e12
-        roof = dict(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"], traffic=None)
+    # The dominant kernel of the step is the tensor-core fused conv/NiN kernel (k_conv_nin_tc): its
+    # launches with K >= 128 are tensor-bound, so the roofline entry is their algorithmic flops per
+    # launch over their average launch time.  `traffic` is the DRAM bytes per launch that ncu measured
+    # for the same launches (profiles/conv_nin_tc_cfg2_batch256.md).
+    tc = [d for d in per_layer if d["kernel"] != "maxpool_rules" and d.get("K", 0) >= 128 and d["N"] >= 16]
+    step_ms = ms_dev / args.steps
+    if tc and args.precision != "fp32":
+        ach = sum(d["flops"] for d in tc) / (sum(d["ms"] for d in tc) * 1e-3) / 1e12
+        roof = dict(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"],
+                    traffic=18.7e6 if world == 1 else None, kernel="k_conv_nin_tc (%d launches per step with K >= 128)" % len(tc),
+                    ms_per_launch=sum(d["ms"] for d in tc) / len(tc), share_of_step=sum(d["ms"] for d in tc) / step_ms,
+                    issued_tf32_tflops=3 * ach,
+                    note="peak is the measured bf16 cuBLAS figure; kind::tf32 runs at half that rate and 3xTF32 issues 3 MMAs "
+                         "per product, so 1/6 of this peak is the ceiling of a perfect 3xTF32 kernel")
     else:
+        top = max(per_layer, key=lambda d: d["ms"])
         ach = top["bytes"] / (top["ms"] * 1e-3) / 1e9
-        roof = dict(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"], traffic=None)
-    roof.update(kernel="layer %d %s" % (top["layer"], top["kernel"]), ms_per_launch=top["ms"], peak_source=peaks["source"],
-                share_of_step=top["ms"] / (ms_dev / args.steps))
+        roof = dict(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"], traffic=None,
+                    kernel="layer %d %s" % (top["layer"], top["kernel"]), ms_per_launch=top["ms"], share_of_step=top["ms"] / step_ms)
+    roof["peak_source"] = peaks["source"]
+    pool = [d for d in per_layer if d["kernel"] == "maxpool_rules"]
+    pool_top = max(pool, key=lambda d: d["ms"]) if pool else None
     all_flops = sum(d["flops"] for d in per_layer)
     conv_ms = sum(d["ms"] for d in per_layer if d["kernel"] != "maxpool_rules")
 
@@ -343,6 +357,9 @@ def main():
             e2e=dict(value=total / (ms_e2e * 1e-3), unit="samples/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                      ms_per_step=ms_e2e / args.steps),
             gpu_launches=int(launches), roofline=roof, cpu_baseline=cpu, clocks=clocks,
+            pooling_roofline=(dict(bound="hbm", kernel="k_maxpool layer %d" % pool_top["layer"], achieved=pool_top["bytes"] / (pool_top["ms"] * 1e-3) / 1e9,
+                                   peak=peaks["hbm_gbs"], unit="GB/s", frac=pool_top["bytes"] / (pool_top["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"])
+                              if pool_top else None),
             breakdown=dict(rule_chain_ms=rules_ms, conv_nin_ms=conv_ms, conv_algorithmic_tflops=all_flops / (conv_ms * 1e-3) / 1e12,
                            multiply_adds_per_sample=all_flops / 2 / BATCH_PER_GPU,
                            layers=[dict(layer=d["layer"], kernel=d["kernel"], ms=round(d["ms"], 4), rows=d["rows"],
