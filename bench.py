@@ -182,10 +182,19 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--precision", default="auto", choices=["auto", "fp32", "3xtf32", "bf16"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="wall budget of the cpu_baseline leg (0 = skip)")
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
+                    help="synthetic configuration (2 = the headline workload; the others are side measurements)")
+    ap.add_argument("--batch", type=int, default=0, help="samples per GPU (0 = the configuration's own batch size, at most 256)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
     scn = importlib.import_module("sparseconvnet-archived_b200")
+    global CFG, BATCH_PER_GPU, WORKLOAD
+    if args.config != 2 or args.batch:
+        CFG = args.config
+        BATCH_PER_GPU = args.batch or min(256, scn.synth.CONFIGS[CFG]["batch"])
+        if CFG != 2:
+            WORKLOAD = "config %d of the benchmark description (side measurement), batch %d per GPU" % (CFG, BATCH_PER_GPU)
     if args.impl == "reference":
         run_reference(args, scn)
         return
@@ -321,7 +330,7 @@ def main():
     if tc and args.precision != "fp32":
         ach = sum(d["flops"] for d in tc) / (sum(d["ms"] for d in tc) * 1e-3) / 1e12
         roof = dict(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"],
-                    traffic=18.7e6 if world == 1 else None, kernel="k_conv_nin_tc (%d launches per step with K >= 128)" % len(tc),
+                    traffic=18.7e6 if (world == 1 and CFG == 2 and BATCH_PER_GPU == 256) else None, kernel="k_conv_nin_tc (%d launches per step with K >= 128)" % len(tc),
                     ms_per_launch=sum(d["ms"] for d in tc) / len(tc), share_of_step=sum(d["ms"] for d in tc) / step_ms,
                     issued_tf32_tflops=3 * ach,
                     note="peak is the measured bf16 cuBLAS figure; kind::tf32 runs at half that rate and 3xTF32 issues 3 MMAs "

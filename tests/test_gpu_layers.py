@@ -185,3 +185,33 @@ def test_conv_nin_rejects_bad_arguments(abi):
         abi.conv_nin_forward(f, None, 2, W, B)  # fs != 1 without rules
     with pytest.raises(abi.ScnError):
         abi.conv_nin_forward(f, None, 1, W[:8].contiguous(), B, act=abi.PRELU)  # PReLU slopes missing
+
+
+def test_background_rows(abi):
+    keys = torch.tensor([5, -1, 7, 3, 2, -1, 9, 8, 1], dtype=torch.int32, device="cuda")
+    off = torch.tensor([0, 3, 5, 5, 9], dtype=torch.int32, device="cuda")  # sample 1 has no background row, sample 2 is empty
+    bg = abi.background_rows(keys, off)
+    assert bg.cpu().tolist() == [1, -1, -1, 5]
+
+
+def test_split_k_matches_single_pass(abi, oracle):
+    """Layers with few output tiles split K over several CTAs; the partial sums are added in a
+    fixed order, so repeated runs are bit-identical; split and unsplit kernels differ only by
+    the accumulation order (K = 2048 here) and both stay within the 1e-4 bound of the oracle."""
+    rng = np.random.default_rng(12)
+    rows, K, N = 200, 2048, 96
+    feat = torch.from_numpy(rng.standard_normal((rows, K)).astype(np.float32)).cuda()
+    W = torch.from_numpy((rng.standard_normal((K, N)) * 0.02).astype(np.float32)).cuda()
+    B = torch.zeros(N, device="cuda")
+    packed = abi.pack_weights(W, abi.PREC_3XTF32)
+    assert abi.lib().scn_conv_nin_workspace_bytes(rows, 1, K, N, abi.PREC_3XTF32) > 0
+    a = abi.conv_nin_forward(feat, None, 1, W, B, precision=abi.PREC_3XTF32, packed=packed, split_k=True)
+    b = abi.conv_nin_forward(feat, None, 1, W, B, precision=abi.PREC_3XTF32, packed=packed, split_k=True)
+    c = abi.conv_nin_forward(feat, None, 1, W, B, precision=abi.PREC_3XTF32, packed=packed, split_k=False)
+    torch.cuda.synchronize()
+    assert abi.conv_tc_take_error() == 0
+    assert torch.equal(a, b)
+    assert relerr(a.cpu().numpy(), c.cpu().numpy()) < 5e-5
+    ref = oracle.nin_forward(feat.cpu().numpy(), W.cpu().numpy(), B.cpu().numpy(), accum64=True)
+    assert relerr(a.cpu().numpy(), ref) < RTOL_FP32
+    assert relerr(c.cpu().numpy(), ref) < RTOL_FP32
