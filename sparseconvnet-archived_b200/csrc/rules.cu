@@ -166,6 +166,76 @@ __device__ bool creates(const Regions &R, const uint2 *__restrict__ d, const int
   return false;
 }
 
+// Division of 0 <= x < 2^24 by n with a float reciprocal (quotient off by at most one, then fixed).
+__device__ __forceinline__ int fdiv(int x, int n, float rn, int *rem) {
+  int q = __float2int_rz(__int2float_rn(x) * rn);
+  int r = x - q * n;
+  if (r < 0) { --q; r += n; } else if (r >= n) { ++q; r -= n; }
+  *rem = r;
+  return q;
+}
+template <int DIM> __device__ __forceinline__ void decode_f(int key, int n, float rn, int *c) {
+#pragma unroll
+  for (int a = DIM - 1; a > 0; --a) key = fdiv(key, n, rn, &c[a]);
+  c[0] = key;
+}
+template <int DIM> __device__ __forceinline__ int encode_f(const int *c, int n) {
+  int k = c[0];
+#pragma unroll
+  for (int a = 1; a < DIM; ++a) k = k * n + c[a];
+  return k;
+}
+template <int DIM> __device__ __forceinline__ bool touched_output_f(const Regions &R, const int *i, int t, int *j) {
+  if (R.minActive == -1) {
+    bool ok = true;
+#pragma unroll
+    for (int a = 0; a < DIM; ++a) { ok = ok && i[a] >= 1 && i[a] <= R.nOut; j[a] = i[a] - 1; }
+    return ok;
+  }
+  int sum = 0;
+  bool ok = true;
+#pragma unroll
+  for (int a = DIM - 1; a >= 0; --a) {
+    int ta;
+    t = fdiv(t, R.Tax, R.rTax, &ta);
+    int rem;
+    const int num = i[a] - R.size + R.stride; // outputL = max(0, num / stride): a non-positive num gives 0
+    const int lo = num <= 0 ? 0 : fdiv(num, R.stride, R.rStride, &rem);
+    const int hi = min(fdiv(i[a], R.stride, R.rStride, &rem) + 1, R.nOut);
+    j[a] = lo + ta;
+    ok = ok && j[a] < hi;
+    sum += j[a];
+  }
+  if (R.lattice == SCN_LATTICE_TRIANGULAR && sum >= R.nOut) return false;
+  return ok;
+}
+template <int DIM> __device__ bool creates_f(const Regions &R, const uint2 *d, const int *i, const int *j) {
+  if (R.minActive == -1) return true;
+  int cc[DIM], ii[DIM];
+#pragma unroll
+  for (int a = 0; a < DIM; ++a) cc[a] = 0;
+  int active = 0;
+  bool seenSelf = false;
+  for (int cell = 0; cell < R.cube; ++cell) {
+    bool self = true;
+#pragma unroll
+    for (int a = 0; a < DIM; ++a) { ii[a] = j[a] * R.stride + cc[a]; self = self && ii[a] == i[a]; }
+    if (self) {
+      if (R.minActive <= 1) return true;
+      seenSelf = true;
+      active += (R.ord[cell] >= 0);
+    } else {
+      const bool on = cell_active(d, encode_f<DIM>(ii, R.nIn));
+      if (!seenSelf) { if (on) return false; } // an earlier key got there first
+      else if (R.ord[cell] >= 0) active += on;
+    }
+#pragma unroll
+    for (int a = DIM - 1; a >= 0; --a) { if (++cc[a] < R.size) break; cc[a] = 0; }
+  }
+  return seenSelf && active >= R.minActive;
+}
+
+
 // Per input row: its slot in ascending-key order, the outputs it creates, and their count.
 __global__ void k_flags(Regions R, int batch, const int *__restrict__ keys, const int *__restrict__ off,
                         const uint2 *__restrict__ dir, int *sortedRow, unsigned char *flags, int *cnt,
@@ -342,6 +412,75 @@ __global__ void k_fill(Regions R, int batch, const int *__restrict__ inOff, cons
   }
 }
 
+
+// ---- the same three kernels with the dimension fixed at compile time and float-assisted
+// divisions, used whenever every cell index is below 2^24 (all benchmark grids are)
+template <int DIM>
+__global__ void k_flags_t(Regions R, int batch, const int *__restrict__ keys, const int *__restrict__ off,
+                          const uint2 *__restrict__ dir, int *sortedRow, unsigned char *flags, int *cnt) {
+  const int n = off[batch];
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < n; row += gridDim.x * blockDim.x) {
+    const int key = keys[row];
+    if (key < 0 || key >= R.cells) continue;
+    const int b = find_sample(off, batch, row);
+    const uint2 *d = dir + (size_t)b * R.W;
+    const int slot = off[b] + cell_rank(d, key);
+    sortedRow[slot] = row;
+    int i[DIM], j[DIM];
+    decode_f<DIM>(key, R.nIn, R.rNIn, i);
+    int c = 0;
+    for (int t = 0; t < R.T; ++t) {
+      const bool f = touched_output_f<DIM>(R, i, t, j) && creates_f<DIM>(R, d, i, j);
+      flags[(size_t)slot * R.T + t] = f;
+      c += f;
+    }
+    cnt[slot] = c;
+  }
+}
+template <int DIM>
+__global__ void k_assign_t(Regions R, int batch, const int *__restrict__ keys, const int *__restrict__ inOff,
+                           const int *__restrict__ sortedRow, const unsigned char *__restrict__ flags,
+                           const int *__restrict__ P, const int *__restrict__ outOff, int *outKeys, int capacity) {
+  const long long n = (long long)inOff[batch] * R.T;
+  for (long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x; p < n; p += (long long)gridDim.x * blockDim.x) {
+    if (!flags[p]) continue;
+    const int slot = (int)(p / R.T), t = (int)(p - (long long)slot * R.T);
+    int rank = 0;
+    for (int q = 0; q < t; ++q) rank += flags[(size_t)slot * R.T + q];
+    const int b = find_sample(inOff, batch, slot);
+    const int outRow = outOff[b] + (P[slot] - P[inOff[b]]) + rank;
+    if (outRow >= capacity) continue;
+    int i[DIM], j[DIM];
+    decode_f<DIM>(keys[sortedRow[slot]], R.nIn, R.rNIn, i);
+    touched_output_f<DIM>(R, i, t, j);
+    outKeys[outRow] = encode_f<DIM>(j, R.nOut);
+  }
+}
+template <int DIM>
+__global__ void k_fill_t(Regions R, int batch, const int *__restrict__ inOff, const int *__restrict__ inBg,
+                         const uint2 *__restrict__ dir, const int *__restrict__ sortedRow,
+                         const int *__restrict__ outOff, const int *__restrict__ outKeys, int *rules,
+                         int capacity, const int *__restrict__ result) {
+  const long long n = (long long)min(result[0], capacity) * R.sd;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n; q += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(q / R.sd), col = (int)(q - (long long)r * R.sd);
+    const int b = find_sample(outOff, batch, r);
+    const int key = outKeys[r];
+    int v = inBg[b];
+    if (key >= 0) {
+      int j[DIM], cc[DIM], ii[DIM];
+      decode_f<DIM>(key, R.nOut, R.rNOut, j);
+      decode_f<DIM>(R.cellOfCol[col], R.size, R.rSize, cc);
+#pragma unroll
+      for (int a = 0; a < DIM; ++a) ii[a] = j[a] * R.stride + cc[a];
+      const int ck = encode_f<DIM>(ii, R.nIn);
+      const uint2 e = (dir + (size_t)b * R.W)[ck >> 5];
+      if ((e.x >> (ck & 31)) & 1u) v = sortedRow[inOff[b] + e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
+    }
+    rules[q] = v;
+  }
+}
+
 // TerminalPoolingLayer.cu:8-20: sample b's rows in ascending key order, padded with -1.
 __global__ void k_terminal(int batch, int S, const int *__restrict__ inOff, const int *__restrict__ inBg,
                            const int *__restrict__ nSites, const int *__restrict__ sortedRow, int *rules,
@@ -443,75 +582,6 @@ struct ChainParams {
   int *ticket;
   int rowsMax, wMax, tMax, flagBytes;
 };
-
-// Division of 0 <= x < 2^24 by n with a float reciprocal (quotient off by at most one, then fixed).
-__device__ __forceinline__ int fdiv(int x, int n, float rn, int *rem) {
-  int q = __float2int_rz(__int2float_rn(x) * rn);
-  int r = x - q * n;
-  if (r < 0) { --q; r += n; } else if (r >= n) { ++q; r -= n; }
-  *rem = r;
-  return q;
-}
-template <int DIM> __device__ __forceinline__ void decode_f(int key, int n, float rn, int *c) {
-#pragma unroll
-  for (int a = DIM - 1; a > 0; --a) key = fdiv(key, n, rn, &c[a]);
-  c[0] = key;
-}
-template <int DIM> __device__ __forceinline__ int encode_f(const int *c, int n) {
-  int k = c[0];
-#pragma unroll
-  for (int a = 1; a < DIM; ++a) k = k * n + c[a];
-  return k;
-}
-template <int DIM> __device__ __forceinline__ bool touched_output_f(const Regions &R, const int *i, int t, int *j) {
-  if (R.minActive == -1) {
-    bool ok = true;
-#pragma unroll
-    for (int a = 0; a < DIM; ++a) { ok = ok && i[a] >= 1 && i[a] <= R.nOut; j[a] = i[a] - 1; }
-    return ok;
-  }
-  int sum = 0;
-  bool ok = true;
-#pragma unroll
-  for (int a = DIM - 1; a >= 0; --a) {
-    int ta;
-    t = fdiv(t, R.Tax, R.rTax, &ta);
-    int rem;
-    const int num = i[a] - R.size + R.stride; // outputL = max(0, num / stride): a non-positive num gives 0
-    const int lo = num <= 0 ? 0 : fdiv(num, R.stride, R.rStride, &rem);
-    const int hi = min(fdiv(i[a], R.stride, R.rStride, &rem) + 1, R.nOut);
-    j[a] = lo + ta;
-    ok = ok && j[a] < hi;
-    sum += j[a];
-  }
-  if (R.lattice == SCN_LATTICE_TRIANGULAR && sum >= R.nOut) return false;
-  return ok;
-}
-template <int DIM> __device__ bool creates_f(const Regions &R, const uint2 *d, const int *i, const int *j) {
-  if (R.minActive == -1) return true;
-  int cc[DIM], ii[DIM];
-#pragma unroll
-  for (int a = 0; a < DIM; ++a) cc[a] = 0;
-  int active = 0;
-  bool seenSelf = false;
-  for (int cell = 0; cell < R.cube; ++cell) {
-    bool self = true;
-#pragma unroll
-    for (int a = 0; a < DIM; ++a) { ii[a] = j[a] * R.stride + cc[a]; self = self && ii[a] == i[a]; }
-    if (self) {
-      if (R.minActive <= 1) return true;
-      seenSelf = true;
-      active += (R.ord[cell] >= 0);
-    } else {
-      const bool on = cell_active(d, encode_f<DIM>(ii, R.nIn));
-      if (!seenSelf) { if (on) return false; } // an earlier key got there first
-      else if (R.ord[cell] >= 0) active += on;
-    }
-#pragma unroll
-    for (int a = DIM - 1; a >= 0; --a) { if (++cc[a] < R.size) break; cc[a] = 0; }
-  }
-  return seenSelf && active >= R.minActive;
-}
 
 constexpr int CHAIN_THREADS = 512;
 constexpr unsigned long long CHAIN_WAIT_NS = 2000000000ull;
@@ -778,7 +848,16 @@ extern "C" int scn_rules_build(const scn_regions_t *r, int batch, const int *d_i
   SCN_LAUNCH_CHECK("k_mark");
   k_rank<<<batch < sm_count() * 4 ? batch : sm_count() * 4, 256, 0, s>>>(R, batch, w.dir, w.nSites);
   SCN_LAUNCH_CHECK("k_rank");
-  k_flags<<<grid_for(rows, 128), 128, 0, s>>>(R, batch, d_in_keys, d_in_off, w.dir, w.sortedRow, w.flags, w.cnt, true);
+  const bool fast = R.cells < (1 << 24); // float-assisted coordinate arithmetic is exact below 2^24
+#define SCN_DIM_DISPATCH(KERNEL, GRID, BLOCK, ...)                                                       \
+  switch (R.dim) {                                                                                       \
+  case 1: KERNEL<1><<<GRID, BLOCK, 0, s>>>(__VA_ARGS__); break;                                          \
+  case 2: KERNEL<2><<<GRID, BLOCK, 0, s>>>(__VA_ARGS__); break;                                          \
+  case 3: KERNEL<3><<<GRID, BLOCK, 0, s>>>(__VA_ARGS__); break;                                          \
+  default: KERNEL<4><<<GRID, BLOCK, 0, s>>>(__VA_ARGS__); break;                                         \
+  }
+  if (fast) { SCN_DIM_DISPATCH(k_flags_t, grid_for(rows, 128), 128, R, batch, d_in_keys, d_in_off, w.dir, w.sortedRow, w.flags, w.cnt) }
+  else k_flags<<<grid_for(rows, 128), 128, 0, s>>>(R, batch, d_in_keys, d_in_off, w.dir, w.sortedRow, w.flags, w.cnt, true);
   SCN_LAUNCH_CHECK("k_flags");
   const int chunks = rows / SCAN_CHUNK + 1;
   k_scan_reduce<<<grid_for(chunks, 1), SCAN_THREADS, 0, s>>>(w.cnt, d_in_off, batch, w.partial);
@@ -789,12 +868,15 @@ extern "C" int scn_rules_build(const scn_regions_t *r, int batch, const int *d_i
   SCN_LAUNCH_CHECK("k_scan_apply");
   k_samples<<<1, 1024, 0, s>>>(R, batch, d_in_off, w.cnt, d_out_off, d_out_bg, d_out_keys, rows_out_capacity, d_result);
   SCN_LAUNCH_CHECK("k_samples");
-  k_assign<<<grid_for((long long)rows * R.T, 256), 256, 0, s>>>(R, batch, d_in_keys, d_in_off, w.sortedRow, w.flags, w.cnt,
-                                                                 d_out_off, d_out_keys, rows_out_capacity);
+  if (fast) { SCN_DIM_DISPATCH(k_assign_t, grid_for((long long)rows * R.T, 256), 256, R, batch, d_in_keys, d_in_off, w.sortedRow, w.flags, w.cnt, d_out_off, d_out_keys, rows_out_capacity) }
+  else k_assign<<<grid_for((long long)rows * R.T, 256), 256, 0, s>>>(R, batch, d_in_keys, d_in_off, w.sortedRow, w.flags, w.cnt,
+                                                                      d_out_off, d_out_keys, rows_out_capacity);
   SCN_LAUNCH_CHECK("k_assign");
-  k_fill<<<grid_for((long long)(rows_out_capacity > 0 ? rows_out_capacity : 1) * R.sd, 256), 256, 0, s>>>(
-      R, batch, d_in_off, d_in_bg, w.dir, w.sortedRow, d_out_off, d_out_keys, d_rules, rows_out_capacity, d_result);
+  const int fillGrid = grid_for((long long)(rows_out_capacity > 0 ? rows_out_capacity : 1) * R.sd, 256);
+  if (fast) { SCN_DIM_DISPATCH(k_fill_t, fillGrid, 256, R, batch, d_in_off, d_in_bg, w.dir, w.sortedRow, d_out_off, d_out_keys, d_rules, rows_out_capacity, d_result) }
+  else k_fill<<<fillGrid, 256, 0, s>>>(R, batch, d_in_off, d_in_bg, w.dir, w.sortedRow, d_out_off, d_out_keys, d_rules, rows_out_capacity, d_result);
   SCN_LAUNCH_CHECK("k_fill");
+#undef SCN_DIM_DISPATCH
   return SCN_OK;
 }
 
