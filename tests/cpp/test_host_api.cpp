@@ -1,0 +1,187 @@
+// Exercises the C++ classes that keep the reference's names the way a program written against
+// the reference would: builders, per-layer preprocess()/forwards(), processBatch(), the host
+// gridRules() entry point, vectorCUDA migration, fused against unfused convolution.
+// Built and run by tests/test_gpu_cpp_api.py on a B200; prints "OK" lines and exits 0 on success.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <random>
+#include <vector>
+#include "BatchProducer.h"
+#include "ConvolutionalLayer.h"
+#include "NetworkArchitectures.h"
+#include "NetworkInNetworkLayer.h"
+#include "Regions.h"
+#include "SigmoidLayer.h"
+#include "SparseConvNetCUDA.h"
+
+#define CHECK(cond)                                                                   \
+  do {                                                                                \
+    if (!(cond)) { std::printf("FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond); return 1; } \
+  } while (0)
+
+static void fillWeights(SparseConvNetCUDA &cnn, unsigned seed) {
+  std::mt19937 gen(seed);
+  for (auto L : cnn.layers)
+    if (auto n = dynamic_cast<NetworkInNetworkLayer *>(L)) {
+      std::normal_distribution<float> nd(0.f, std::sqrt(2.0f / n->nFeaturesIn));
+      for (auto &w : n->W.hVector()) w = nd(gen);
+      for (auto &b : n->B.hVector()) b = 0.01f * nd(gen);
+      n->weightsChanged();
+    }
+}
+
+static SitesPicture *randomPicture(int S, int nF, int label, std::mt19937 &gen, double density) {
+  SitesPicture *p = new SitesPicture(nF, label);
+  std::uniform_real_distribution<double> u(0, 1);
+  std::normal_distribution<float> nd(0.f, 1.f);
+  for (int x = 0; x < S; ++x)
+    for (int y = 0; y < S; ++y)
+      if (u(gen) < density) {
+        p->keys.push_back((int64_t)x * S + y);
+        for (int f = 0; f < nF; ++f) p->features.push_back(nd(gen));
+      }
+  return p;
+}
+
+int main() {
+  try {
+    // ---- 1. the host gridRules(): the hand-checkable 8x8 example (conv3 then MP2)
+    {
+      SparseGrid in, mid, out;
+      in.backgroundCol = 0;
+      const int pts[5][2] = {{5, 5}, {1, 2}, {2, 2}, {3, 4}, {6, 1}};
+      for (int i = 0; i < 5; ++i) in.mp[pts[i][0] * 8 + pts[i][1]] = i + 1;
+      RegularSquareRegions conv(8, 6, 2, 3, 1), pool(6, 3, 2, 2, 2);
+      int n1 = 0, n2 = 0;
+      std::vector<int> r1, r2;
+      gridRules(in, mid, conv, n1, r1, true, 1);
+      gridRules(mid, out, pool, n2, r2, true, 1);
+      CHECK(n1 == 28 && mid.backgroundCol == 27 && r1.size() == 28 * 9);
+      const int row0[9] = {0, 0, 0, 0, 0, 2, 0, 0, 3}, row5[9] = {2, 0, 0, 3, 0, 0, 0, 0, 4};
+      for (int c = 0; c < 9; ++c) CHECK(r1[c] == row0[c] && r1[5 * 9 + c] == row5[c]);
+      const int p0[4] = {0, 1, 3, 4}, p1[4] = {2, 27, 5, 9};
+      for (int c = 0; c < 4; ++c) CHECK(r2[c] == p0[c] && r2[4 + c] == p1[c]);
+      CHECK(n2 == 9 && out.backgroundCol == -1);
+      RegularTriangularRegions tri(5, 4, 3, 2, 1);
+      CHECK(tri.S == 4 && tri.ord.size() == 8);
+      std::printf("OK gridRules\n");
+    }
+    // ---- 2. builder arithmetic of the named architectures
+    {
+      DeepCNet a(2, 5, 100, VLEAKYRELU, 3, 10, 0.5f);
+      CHECK(a.cnn->inputSpatialSize == 127 && a.cnn->layers.size() == 18);
+    }
+    {
+      DeepC2 b(3, 2, 32, RELU, 1, 20);
+      int s = 1; // walk back: C2 (no pool), then twice MP3/2 + C2
+      s = s + 1;
+      for (int i = 0; i < 2; ++i) { s = 3 + (s - 1) * 2; s = s + 1; }
+      CHECK(b.cnn->inputSpatialSize == s);
+      std::printf("OK builders\n");
+    }
+    // ---- 3. a small network three ways: processDataset (BatchProducer threads + fused rule chain),
+    //         per-layer preprocess()/forwards() with fused convolutions, and with the gather materialised
+    SparseConvNet net(2, 3, 5);
+    net.addLeNetLayerMP(32, 3, 1, 2, 2, VLEAKYRELU, 0.1f);
+    net.addLeNetLayerMP(64, 2, 1, 2, 2, VLEAKYRELU, 0.2f);
+    net.addLeNetLayerMP(96, 2, 1, 1, 1, VLEAKYRELU, 0.0f);
+    net.addSoftmaxLayer();
+    SparseConvNetCUDA &cnn = *net.cnn;
+    const int S = cnn.inputSpatialSize; // 1 <-C2- 2 <-MP2/2- 4 <-C2- 5 <-MP2/2- 10 <-C3- 12
+    CHECK(S == 12);
+    fillWeights(cnn, 5);
+    std::mt19937 gen(11);
+    SpatiallySparseDataset ds;
+    ds.name = "cpp-test"; ds.nFeatures = 3; ds.nClasses = 5; ds.type = TESTBATCH;
+    std::vector<SitesPicture *> pics;
+    for (int i = 0; i < 7; ++i) { pics.push_back(randomPicture(S, 3, i % 5, gen, i == 3 ? 0.0 : 0.4)); ds.pictures.push_back(pics.back()); }
+    std::vector<std::vector<float>> viaDataset;
+    {
+      BatchProducer bp(cnn, ds, S, 3); // batches of 3, 3, 1
+      std::ofstream nof, nog;
+      while (SpatiallySparseBatch *b = bp.nextBatch()) {
+        cnn.processBatch(*b, 0, 0, nof, nog);
+        for (auto &p : b->probabilities) viaDataset.push_back(p);
+      }
+    }
+    CHECK(viaDataset.size() == 7);
+    float err = cnn.processDataset(ds, 4);
+    CHECK(err >= 0.f && err <= 1.f);
+    cnn.processDatasetRepeatTest(ds, 4, 2);
+
+    for (int variant = 0; variant < 2; ++variant) { // 0: fused conv+NiN, 1: ConvolutionalLayer writes the gathered matrix
+      for (auto L : cnn.layers)
+        if (auto c = dynamic_cast<ConvolutionalLayer *>(L)) c->fuseWithNext = (variant == 0);
+      SpatiallySparseBatch &b = cnn.batchPool[0];
+      cnn.prepareBatch(b);
+      b.reset();
+      b.type = TESTBATCH;
+      SpatiallySparseBatchInterface &in = b.interfaces[0];
+      in.nFeatures = 3; in.spatialSize = S; in.featuresPresent.hVector() = range(3);
+      std::vector<float> &feat = in.sub->features.hVector();
+      feat.clear();
+      for (auto p : pics) {
+        b.batchSize++;
+        in.grids.push_back(SparseGrid());
+        b.labels.hVector().push_back(p->label);
+        p->codifyInputData(in.grids.back(), feat, in.nSpatialSites, S);
+      }
+      in.uploadGrids(cnn.memStream);
+      for (size_t i = 0; i < cnn.layers.size(); ++i) cnn.layers[i]->preprocess(b, b.interfaces[i], b.interfaces[i + 1]); // one layer at a time, as BatchProducer.cu:72-75
+      CHECK(b.interfaces.back().nSpatialSites == 7 && b.interfaces.back().nFeatures == 5);
+      b.interfaces[2].materializeGrids(cnn.memStream);
+      CHECK(b.interfaces[2].grids.size() == 7 && b.interfaces[2].grids[3].mp.empty()); // the empty picture stays empty
+      CHECK((int)b.interfaces[1].rules.size() == b.interfaces[1].nSpatialSites * 9);
+      std::ofstream nof, nog;
+      cnn.processBatch(b, 0, 0, nof, nog);
+      CHECK(b.probabilities.size() == 7);
+      for (int i = 0; i < 7; ++i) {
+        float sum = 0;
+        for (int k = 0; k < 5; ++k) {
+          sum += b.probabilities[i][k];
+          CHECK(std::fabs(b.probabilities[i][k] - viaDataset[i][k]) < 2e-5f);
+        }
+        CHECK(std::fabs(sum - 1.f) < 1e-5f);
+      }
+      if (variant == 1) CHECK((int)b.interfaces[1].sub->features.size() == b.interfaces[1].nSpatialSites * 27);
+      CHECK(b.mistakes >= 0 && b.mistakes <= 7);
+    }
+    std::printf("OK network three ways\n");
+    // ---- 4. vectorCUDA migration and applySigmoid
+    {
+      vectorCUDA<float> v(false, 0);
+      v.hVector() = {-3.f, -1.f, 0.f, 2.f};
+      float *d = v.dPtr(); // uploads
+      CHECK(v.onGPU && d != nullptr && v.size() == 4);
+      SpatiallySparseBatchSubInterface sub;
+      SpatiallySparseBatchInterface I(&sub);
+      I.nSpatialSites = 1; I.nFeatures = 4; I.featuresPresent.hVector() = range(4);
+      sub.features.hVector() = v.hVector(); // downloads v again
+      CHECK(!v.onGPU);
+      applySigmoid(I, I, VLEAKYRELU, cnn.memStream);
+      cudaStreamSynchronize(cnn.memStream.stream);
+      std::vector<float> &o = sub.features.hVector();
+      CHECK(std::fabs(o[0] + 0.999f) < 1e-6f && std::fabs(o[1] + 0.333f) < 1e-6f && o[2] == 0.f && o[3] == 2.f);
+      v.resize(0);
+      std::printf("OK vectorCUDA/applySigmoid\n");
+    }
+    // ---- 5. what the inference library refuses
+    {
+      bool threw = false;
+      try { SpatiallySparseBatch &b = cnn.batchPool[0]; cnn.layers[0]->backwards(b, b.interfaces[0], b.interfaces[1], 0.f, 0.f); }
+      catch (const ScnException &) { threw = true; }
+      CHECK(threw);
+      threw = false;
+      try { cnn.loadWeights("/nonexistent/w", 1, false); } catch (const ScnException &) { threw = true; }
+      CHECK(threw);
+      std::printf("OK refusals\n");
+    }
+    for (auto p : pics) delete p;
+  } catch (const std::exception &e) {
+    std::printf("FAILED with exception: %s\n", e.what());
+    return 1;
+  }
+  std::printf("ALL OK\n");
+  return 0;
+}
