@@ -68,9 +68,18 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append([time.time()] + [x.strip() for x in line.split(",")])
 
-    def stop(self):
+    def wait_first(self, timeout=5.0):
+        """Blocks until nvidia-smi has delivered its first sample (its start-up takes a few 100 ms)."""
+        t0 = time.time()
+        while self.proc is not None and not self.rows and time.time() - t0 < timeout:
+            time.sleep(0.01)
+
+    def count_in(self, t0, t1):
+        return sum(1 for r in self.rows if t0 <= r[0] <= t1)
+
+    def stop(self, t0=None, t1=None):
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
         self.proc.terminate()
@@ -81,6 +90,9 @@ class ClockSampler:
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for r in self.rows:
+            if (t0 is not None and r[0] < t0) or (t1 is not None and r[0] > t1):
+                continue
+            r = r[1:]
             try:
                 sm.append(float(r[0])); mx.append(float(r[1]))
             except (ValueError, IndexError):
@@ -272,11 +284,13 @@ def main():
             torch.cuda.synchronize()
 
         # ---- device-resident leg
+        sampler = ClockSampler(local)
+        sampler.wait_first()
         for j in range(args.warmup):
             step_device(j)
         gnet.enable_timing(True)
         barrier()
-        sampler = ClockSampler(local)
+        t_load0 = time.time()
         launches0 = abi.kernel_launch_count()
         t_wall = time.time()
         ms_dev, layer_ms = timed(step_device, args.steps, True)
@@ -290,7 +304,18 @@ def main():
         barrier()
         ms_e2e, _ = timed(step_host, args.steps, False)
         barrier()
-        clocks = sampler.stop()
+        # A short run (few steps) can end between two nvidia-smi samples: keep the same steps going,
+        # untimed, until a handful of samples have been taken under this load.
+        tail_ms, j = 0.0, 0
+        t_tail = time.time()
+        while sampler.proc is not None and sampler.count_in(t_load0, time.time()) < 5 and time.time() - t_tail < 2.0:
+            step_device(j)
+            j += 1
+        if j:
+            stream.synchronize()
+            tail_ms = (time.time() - t_tail) * 1e3
+        clocks = sampler.stop(t_load0, time.time())
+        clocks["window"] = "both timed legs" + (" + %.0f ms of the same steps, untimed" % tail_ms if j else "")
 
         # shapes of the last forward for the roofline arithmetic
         layers = gnet.layers()

@@ -3,34 +3,35 @@
 //
 //   out[r][n] = act( p * sum_k A[r][k] * W[k][n] + p * B[n] ),   A[r][f*nIn + c] = in[rules[r*fs+f]][c]
 //
-// One CTA computes a 128-row x BN-column output tile.  The K axis is walked in slabs of 32
-// fp32 values (128 bytes, one 128B-swizzle row); nIn is a multiple of 32, so a slab never
-// straddles two filter cells and every A row of a slab is 128 contiguous bytes of one input
-// row named by the rulebook.
+// A persistent CTA (one per SM) walks 128-row x BN-column output tiles.  The K axis is walked in
+// slabs of 32 fp32 values (128 bytes, one 128B-swizzle row).  14 warps, by role:
 //
-//   warps 0-3  gather: asynchronous 16-byte copies (cp.async) of the rows the rules name (zero
-//              fill for a negative rule or a row past the end) straight into the canonical
-//              K-major SWIZZLE_128B tile; their completion arrives on the stage's "raw"
-//              barrier, so several slabs are in flight.  Afterwards the same warps run the
-//              epilogue: tcgen05.ld of their 32 accumulator lanes, p*acc + p*bias, activation,
-//              16-byte stores.
-//   warps 4-7  split: once a raw tile has landed it already serves as the tf32 "hi" operand
-//              (the tensor core reads the upper 19 bits of each fp32); these warps write
-//              lo = x - hi into the second image, fence to the async proxy and arrive on the
-//              stage's "full" barrier.
-//   warp 8     one thread issues a cp.async.bulk per slab for the weight tile (hi and lo
-//              images, pre-split, pre-transposed and pre-swizzled once by tc_pack, so the
-//              copy is a plain contiguous block into this CTA's own shared memory; no
-//              tensor map is needed).
-//   warp 9     allocates tensor memory; one thread issues, per slab, 3 x 4 tcgen05.mma
-//              (kind::tf32, M=128, N=BN, K=8): A_lo*B_hi + A_hi*B_lo + A_hi*B_hi, which
-//              restores fp32-grade accuracy from tf32 products ("3xTF32"), then
-//              tcgen05.commit onto the stage's "empty" barrier.
+//   warps 0-3   epilogue of tile i while the main loop already runs tile i+1 (two accumulators in
+//               tensor memory): tcgen05.ld of 32 columns -> padded shared slice -> coalesced row
+//               stores with p*acc + p*bias and the activation.
+//   warps 4-7   gather: asynchronous copies (cp.async, zero fill for a negative rule or a row past
+//               the end) of the rows the rules name, straight into the canonical K-major
+//               SWIZZLE_128B tile; completion arrives on the stage's "raw" barrier, so several
+//               slabs are in flight.  nIn % 32 == 0: a slab lies inside one filter cell and a row of
+//               it is 128 contiguous bytes (16-byte copies).  Any other nIn (3 input channels, say):
+//               4-byte copies, lane = position in the slab, so that the lanes of one instruction
+//               read neighbouring words of the few source rows one output row names.  The tile's rules are staged in shared memory, the next tile's prefetched
+//               meanwhile.
+//   warps 8-11  split: once a raw tile has landed it already serves as the tf32 "hi" operand (the
+//               tensor core reads the upper 19 bits of each fp32); these warps write lo = x - hi
+//               into the second image, fence to the async proxy and arrive on the "full" barrier.
+//   warp 12     one thread issues a cp.async.bulk per slab for the weight tile (hi and lo images,
+//               pre-split, pre-transposed and pre-swizzled once by tc_pack, so the copy is a plain
+//               contiguous block into this CTA's own shared memory; no tensor map is needed).
+//   warp 13     allocates tensor memory; one thread issues, per slab, 3 x 4 tcgen05.mma
+//               (kind::tf32, M=128, N=BN, K=8): A_lo*B_hi + A_hi*B_lo + A_hi*B_hi, which restores
+//               fp32-grade accuracy from tf32 products ("3xTF32"), then tcgen05.commit onto the
+//               stage's "empty" barrier.
 //
 // The gathered matrix never exists in global memory (the reference writes and re-reads it,
-// ConvolutionalLayer.cu:124-133).  Every mbarrier wait has an iteration limit: on expiry the
-// kernel records an error code in g_tc_error and carries on to its normal exit, so tensor
-// memory is always released and the context stays usable.
+// ConvolutionalLayer.cu:124-133).  Every mbarrier wait has a time limit: on expiry the kernel
+// records an error code in g_tc_error and carries on to its normal exit, so tensor memory is
+// always released and the context stays usable.
 #include "conv_nin_tc.cuh"
 
 namespace scn {
@@ -116,16 +117,16 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
-  int mTiles, accStride, K, generic; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
+  int mTiles, accStride, K, generic, rulesDouble; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(srcBytes) : "memory");
 }
-// The barrier receives one arrival once all cp.async issued so far by this thread have landed.
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t srcBytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(srcBytes) : "memory");
 }
+// The barrier receives one arrival once all cp.async issued so far by this thread have landed.
 __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -135,19 +136,13 @@ constexpr int EPI_COLS = 32;                      // accumulator columns staged 
 constexpr int EPI_LD = EPI_COLS + 4;              // padded row stride (floats) of the staging slice
 constexpr int EPI_BYTES = BM * EPI_LD * 4;        // 18 KB
 
-// Persistent kernel: one CTA per SM walks work items (output tile, or tile x K-split part).
-// Roles (14 warps):
-//   warps 0-3   epilogue of item i while the main loop already runs item i+1 (two accumulators
-//               in tensor memory): tcgen05.ld 32 columns -> padded shared slice -> coalesced
-//               row stores with p*acc + p*bias and the activation
-//   warps 4-7   gather (cp.async) ; warps 8-11 split (lo image) ; warp 12 weight bulk copies ;
-//   warp 13     tensor-memory allocation and MMA issue
+// Work items are output tiles, or (tile, K range) pairs when K is split over several CTAs.
 template <bool SPLIT, int ACT>
 __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) {
   extern __shared__ unsigned char smem_raw[];
   int *rulesS = reinterpret_cast<int *>(smem_raw); // [128 x fs] rule tile of the current item (when it fits)
   // 1024-byte alignment: the swizzle pattern is a function of absolute shared-memory address bits
-  unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + P.rulesBytes + 1023) & ~(uintptr_t)1023);
+  unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + (P.rulesDouble ? 2 : 1) * P.rulesBytes + 1023) & ~(uintptr_t)1023);
   const int bHalf = P.BN * ROW_BYTES;            // one of B_hi / B_lo
   const int stageBytes = 2 * A_HALF + 2 * bHalf; // A raw(hi), A_lo, B_hi, B_lo
   float *epi = reinterpret_cast<float *>(smem + (size_t)P.stages * stageBytes);
@@ -252,46 +247,75 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
     const int t = threadIdx.x - 128, chunk = t & 7, rbase = t >> 3;
     // this thread's 16-byte chunk sits at the same offset in each of its 8 rows (16 rows apart)
     const uint32_t rowOff = (rbase >> 3) * 1024 + (rbase & 7) * ROW_BYTES + ((chunk ^ (rbase & 7)) << 4);
-    int g = 0;
-    for (int item = blockIdx.x; item < nItems; item += gridDim.x) {
+    int g = 0, nItem = 0;
+    // 16-byte asynchronous copies of one tile's [128 x fs] rules (the tile starts 512*fs bytes into
+    // the array, so chunks are aligned); bytes past the end of the array are not read.
+    auto stage_rules_async = [&](int item, int buf) {
+      int tileM, tileN, slab0, nLoc;
+      itemTile(item, tileM, tileN, slab0, nLoc);
+      const long long first = (long long)tileM * BM * P.fs, total = (long long)P.rows * P.fs;
+      const uint32_t dst = smem_u32(rulesS) + buf * P.rulesBytes;
+      for (int ch = t; ch < BM * P.fs / 4; ch += 128) {
+        const long long left = total - (first + ch * 4);
+        const uint32_t bytes = left >= 4 ? 16u : left > 0 ? (uint32_t)left * 4u : 0u;
+        cp_async16(dst + ch * 16, bytes ? (const void *)(P.rules + first + ch * 4) : (const void *)P.rules, bytes);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (P.rulesDouble && (int)blockIdx.x < nItems) stage_rules_async(blockIdx.x, 0);
+    for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++nItem) {
       int tileM, tileN, slab0, nLoc;
       itemTile(item, tileM, tileN, slab0, nLoc);
       const int row0 = tileM * BM;
-      if (P.rulesBytes > 0) { // this tile's rules, so the gather does not chain two global loads per slab
+      const int *rulesT = rulesS; // this tile's staged rules
+      if (P.rulesDouble) {
+        // the rules of this tile were prefetched while the previous tile's copies were issued
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("bar.sync 2, 128;" ::: "memory"); // all chunks landed; everyone is done with the other buffer
+        rulesT = rulesS + (nItem & 1) * (P.rulesBytes >> 2);
+        if (item + (int)gridDim.x < nItems) stage_rules_async(item + gridDim.x, (nItem + 1) & 1);
+      } else if (P.rulesBytes > 0) { // synchronous staging (rule pointer not 16-byte aligned, or no room for two buffers)
         asm volatile("bar.sync 2, 128;" ::: "memory"); // everyone has issued the previous item's copies
         const int nr = BM * P.fs;
-        for (int e = t; e < nr; e += 128) {
-          const int r = row0 + e / P.fs;
-          rulesS[e] = (r < P.rows) ? __ldg(P.rules + (long long)row0 * P.fs + e) : -1;
-        }
+        for (int e = t; e < nr; e += 128) rulesS[e] = __ldg(P.rules + min((long long)row0 * P.fs + e, (long long)P.rows * P.fs - 1));
         asm volatile("bar.sync 2, 128;" ::: "memory");
       }
       if (P.generic) {
-        // nIn is not a multiple of 32 (e.g. 3 input channels): a slab spans several filter cells,
-        // so the tile is gathered element by element with 4-byte copies, one row per thread;
-        // k >= K (the padding up to a multiple of 32) and missing rows are zero-filled.
-        const int rl = t, r = row0 + rl;
-        const uint32_t rowBase = (rl >> 3) * 1024 + (rl & 7) * ROW_BYTES;
+        // nIn is not a multiple of 32 (e.g. 3 input channels): a slab spans several filter cells, so
+        // the tile is gathered word by word with 4-byte asynchronous copies.  Lane = position in the
+        // slab: its filter cell f and channel c are fixed per slab, and the 32 lanes of one copy
+        // instruction read neighbouring words of the few source rows that one output row names
+        // (9 sectors instead of 32 for a 3-channel 3x3 filter).  Each warp covers 32 rows; k >= K
+        // (padding up to a multiple of 32) and missing rows are zero-filled.  (Ordinary loads
+        // followed by shared stores were measured slower: they expose the load latency per slab.)
+        const int wq = warp - 4;
         for (int q = 0; q < nLoc; ++q, ++g) {
           const int s = slab0 + q, st = g % P.stages, it = g / P.stages;
-          int k = s * SLAB, f = k / P.nIn, c = k - f * P.nIn;
+          const int k = s * SLAB + lane;
+          const bool kOk = k < P.K;
+          const int f = kOk ? k / P.nIn : 0, c = k - f * P.nIn;
           mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 1);
-          const uint32_t dst = smem_u32(smem + (size_t)st * stageBytes) + rowBase;
-          const float *rowPtr = nullptr;
-          int haveF = -1;
-#pragma unroll 4
-          for (int kk = 0; kk < SLAB; ++kk, ++k) {
-            if (k < P.K && f != haveF) {
-              haveF = f;
-              int src;
-              if (P.rulesBytes > 0) src = rulesS[rl * P.fs + f];
-              else if (P.rules) src = (r < P.rows) ? __ldg(P.rules + (long long)r * P.fs + f) : -1;
-              else src = (r < P.rows) ? r : -1;
-              rowPtr = src >= 0 ? P.in + (long long)src * P.nIn : nullptr;
+          const uint32_t dst0 = smem_u32(smem + (size_t)st * stageBytes) + (uint32_t)wq * 4096 + (lane & 3) * 4;
+          // eight rows at a time: first all rule reads (independent of one another), then the copies,
+          // because the copy instructions keep their program order
+#pragma unroll 1
+          for (int i0 = 0; i0 < 32; i0 += 8) {
+            int src[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int rl = wq * 32 + i0 + j, r = row0 + rl;
+              src[j] = -1;
+              if (kOk && r < P.rows) {
+                if (P.rulesBytes > 0) src[j] = rulesT[rl * P.fs + f];
+                else if (P.rules) src[j] = __ldg(P.rules + (long long)r * P.fs + f);
+                else src[j] = r;
+              }
             }
-            const bool have = k < P.K && rowPtr != nullptr;
-            cp_async4(dst + ((((kk >> 2) ^ (rl & 7))) << 4) + (kk & 3) * 4, have ? (const void *)(rowPtr + c) : (const void *)P.in, have ? 4u : 0u);
-            if (++c == P.nIn) { c = 0; ++f; }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t dst = dst0 + (i0 >> 3) * 1024 + j * ROW_BYTES + (((lane >> 2) ^ j) << 4);
+              cp_async4(dst, src[j] >= 0 ? (const void *)(P.in + (long long)src[j] * P.nIn + c) : (const void *)P.in, src[j] >= 0 ? 4u : 0u);
+            }
           }
           cp_async_arrive(rawBar + 8 * st);
         }
@@ -307,10 +331,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const int rl = rbase + 16 * i, r = row0 + rl;
-            int src;
-            if (P.rulesBytes > 0) src = rulesS[rl * P.fs + f];
-            else if (P.rules) src = (r < P.rows) ? __ldg(P.rules + (long long)r * P.fs + f) : -1;
-            else src = (r < P.rows) ? r : -1;
+            int src = -1;
+            if (r < P.rows) {
+              if (P.rulesBytes > 0) src = rulesT[rl * P.fs + f];
+              else if (P.rules) src = __ldg(P.rules + (long long)r * P.fs + f);
+              else src = r;
+            }
             rowPtr[i] = src >= 0 ? P.in + (long long)src * P.nIn + chunk * 4 : nullptr;
           }
         }
@@ -463,7 +489,7 @@ int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) 
   return k < 2 ? 1 : k;
 }
 
-struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, accStride; size_t smemBytes; };
+struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, rulesDouble, accStride; size_t smemBytes; };
 
 bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
   if (K < 1 || N < 16) return false;
@@ -472,15 +498,19 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
   t->BN = ((N + t->nTiles - 1) / t->nTiles + 15) / 16 * 16;
   t->nSlabs = (K + SLAB - 1) / SLAB; // the last slab is zero-padded
   const int stageBytes = 2 * A_HALF + 2 * t->BN * ROW_BYTES;
-  int stages = (int)((226 * 1024 - 1024 - t->rulesBytes - EPI_BYTES) / stageBytes);
-  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  auto stagesWith = [&](int ruleBufs) {
+    const int n = (int)((226 * 1024 - 1024 - ruleBufs * t->rulesBytes - EPI_BYTES) / stageBytes);
+    return n > MAX_STAGES ? MAX_STAGES : n;
+  };
+  const int stages = stagesWith(1);
   if (stages < 2) return false;
   t->stages = stages;
+  t->rulesDouble = (t->rulesBytes > 0 && stagesWith(2) == stages) ? 1 : 0; // prefetch the next tile's rules if that costs no stage
   t->accStride = (t->BN + 31) / 32 * 32;
   int cols = 32;
   while (cols < 2 * t->accStride) cols *= 2; // two accumulators, at most 2 x 256 columns
   t->tmemCols = cols;
-  t->smemBytes = (size_t)stages * stageBytes + 1024 + t->rulesBytes + EPI_BYTES;
+  t->smemBytes = (size_t)stages * stageBytes + 1024 + (size_t)(1 + t->rulesDouble) * t->rulesBytes + EPI_BYTES;
   return true;
 }
 
@@ -535,6 +565,7 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   P.partial = (float *)d_ws;
   P.mTiles = mTiles; P.accStride = t.accStride;
   P.K = fs * nIn; P.generic = (nIn % SLAB != 0) ? 1 : 0;
+  P.rulesDouble = (t.rulesDouble && ((uintptr_t)d_rules & 15) == 0) ? 1 : 0;
   const int items = mTiles * t.nTiles * P.kSplit;
   const int grid = items < sm_count() ? items : sm_count(); // persistent: one CTA per SM
   if (P.kSplit > 1) {
