@@ -192,7 +192,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--precision", default="auto", choices=["auto", "fp32", "3xtf32", "bf16"])
+    ap.add_argument("--precision", default="auto", choices=["auto", "fp32", "3xtf32", "bf16", "3xbf16"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="wall budget of the cpu_baseline leg (0 = skip)")
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="synthetic configuration (2 = the headline workload; the others are side measurements)")
@@ -229,7 +229,7 @@ def main():
 
     with torch.cuda.stream(stream):
         gnet, _ = build_pair(scn, False)
-        gnet.set_precision(dict(auto=abi.PREC_AUTO, fp32=abi.PREC_FP32, **{"3xtf32": abi.PREC_3XTF32}, bf16=abi.PREC_BF16)[args.precision])
+        gnet.set_precision(dict(auto=abi.PREC_AUTO, fp32=abi.PREC_FP32, **{"3xtf32": abi.PREC_3XTF32, "3xbf16": abi.PREC_3XBF16}, bf16=abi.PREC_BF16)[args.precision])
         # this rank's shard of the global batch, several distinct batches rotated between steps
         n_rot = 2
         host_batches = [c["gen"](BATCH_PER_GPU, first=(rank * n_rot + j) * BATCH_PER_GPU) for j in range(n_rot)]

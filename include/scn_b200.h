@@ -55,8 +55,12 @@ enum scn_precision {
   SCN_PREC_AUTO = -1,  /* tensor cores when the shape allows, else SIMT                    */
   SCN_PREC_FP32 = 0,   /* fp32 FMA on CUDA cores                                           */
   SCN_PREC_3XTF32 = 1, /* tcgen05 kind::tf32, hi/lo split of both operands (fp32-grade)    */
-  SCN_PREC_BF16 = 2    /* tcgen05 kind::f16 with bf16 operands, fp32 accumulation          */
+  SCN_PREC_BF16 = 2,   /* tcgen05 kind::f16 with bf16 operands, fp32 accumulation          */
+  SCN_PREC_3XBF16 = 3  /* kind::f16, bf16 hi/lo split of both operands, three products     */
 };
+/* The tensor-core precision SCN_PREC_AUTO resolves to when the shape has a tensor-core path
+ * (the host classes pack their weights for it).  No reference counterpart. */
+int scn_conv_auto_precision(void);
 
 #define SCN_LATTICE_SQUARE 0     /* RegularSquareRegions, Regions.cu:13-29      */
 #define SCN_LATTICE_TRIANGULAR 1 /* RegularTriangularRegions, Regions.cu:804-832 */

@@ -49,7 +49,9 @@ int scn_net_set_weights(scn_net_t *net, int layer, const float *h_W, const float
 /* SparseConvNetCUDA::loadWeights / saveWeights (SparseConvNetCUDA.cu:406-442), momentum = false. */
 int scn_net_load_weights(scn_net_t *net, const char *baseName, int epoch);
 int scn_net_save_weights(scn_net_t *net, const char *baseName, int epoch);
-/* scn_precision for every NetworkInNetwork layer (default SCN_PREC_AUTO). */
+/* scn_precision for every NetworkInNetwork layer (default SCN_PREC_AUTO).  A tensor-core precision
+ * applies to the layers whose shape has a tensor-core path (N >= 16, N % 4 == 0); the others (the
+ * classifier, say) keep the fp32 CUDA-core kernel. */
 int scn_net_set_precision(scn_net_t *net, int precision);
 
 /* One batch end to end from HOST buffers, as BatchProducer::nextBatch + processBatch do

@@ -14,13 +14,13 @@ c_int, c_ll, c_f, c_p, c_sz = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, c
 SCN_OK = 0
 LATTICE_SQUARE, LATTICE_TRIANGULAR = 0, 1
 NOSIGMOID, RELU, VLEAKYRELU, LEAKYRELU, TANH, SOFTMAX, PRELU, SIGMOID = range(8)
-PREC_AUTO, PREC_FP32, PREC_3XTF32, PREC_BF16 = -1, 0, 1, 2
+PREC_AUTO, PREC_FP32, PREC_3XTF32, PREC_BF16, PREC_3XBF16 = -1, 0, 1, 2, 3
 DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
 
 EXPORTS = [
     "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
     "scn_rules_workspace_bytes", "scn_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_terminal_rules_workspace_bytes",
-    "scn_terminal_rules_build", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
+    "scn_terminal_rules_build", "scn_conv_auto_precision", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
 ]

@@ -1,6 +1,8 @@
 // Fused rule-gather + NetworkInNetwork forward: dispatcher, the fp32 CUDA-core kernel used
 // for small contractions (K = fs*nIn of a few dozen, which are HBM-bound) and as the
 // arithmetic reference for the tensor-core kernel, and the row softmax of the classifier.
+#include <cstdlib>
+#include <cstring>
 #include "scn_common.cuh"
 #include "conv_nin_tc.cuh"
 
@@ -208,9 +210,21 @@ __global__ void k_softmax_rows(float *x, int rows, int N) {
 
 using namespace scn;
 
+extern "C" int scn_conv_auto_precision(void) {
+  // SCN_AUTO_PRECISION=3xtf32|3xbf16|bf16 overrides the default for a process (read once)
+  static const int chosen = [] {
+    const char *e = getenv("SCN_AUTO_PRECISION");
+    if (e && !strcmp(e, "3xbf16")) return (int)SCN_PREC_3XBF16;
+    if (e && !strcmp(e, "bf16")) return (int)SCN_PREC_BF16;
+    if (e && !strcmp(e, "3xtf32")) return (int)SCN_PREC_3XTF32;
+    return (int)SCN_PREC_3XTF32;
+  }();
+  return chosen;
+}
+
 extern "C" size_t scn_conv_nin_workspace_bytes(int rows_out, int fs, int nIn, int N, int precision) {
   if (rows_out < 1 || fs < 1 || nIn < 1 || N < 1) return 0;
-  return tc_workspace_bytes(rows_out, fs, nIn, N, precision == SCN_PREC_AUTO ? SCN_PREC_3XTF32 : precision);
+  return tc_workspace_bytes(rows_out, fs, nIn, N, precision == SCN_PREC_AUTO ? scn_conv_auto_precision() : precision);
 }
 
 extern "C" int scn_conv_nin_forward(const float *d_in, const int *d_rules, int rows_out, int fs, int nIn,
@@ -231,14 +245,14 @@ extern "C" int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, in
   if (act < SCN_NOSIGMOID || act > SCN_SIGMOID) return fail(SCN_ERR_INVALID, "unknown activation");
   if (act == SCN_PRELU && !d_prelu) return fail(SCN_ERR_INVALID, "PReLU slopes missing");
   if (act == SCN_SOFTMAX && N > 1024) return fail(SCN_ERR_INVALID, "softmax over more than 1024 classes");
-  if (precision < SCN_PREC_AUTO || precision > SCN_PREC_BF16) return fail(SCN_ERR_INVALID, "unknown precision");
+  if (precision < SCN_PREC_AUTO || precision > SCN_PREC_3XBF16) return fail(SCN_ERR_INVALID, "unknown precision");
   if (rows_out == 0) return SCN_OK;
   if (!d_in || !d_W || !d_B || !d_out) return fail(SCN_ERR_INVALID, "null pointer");
   cudaStream_t s = (cudaStream_t)stream;
   const int inner = (act == SCN_SOFTMAX) ? SCN_NOSIGMOID : act;
 
   int use = precision;
-  if (precision == SCN_PREC_AUTO) use = (d_W_packed && tc_shape_ok(fs, nIn, N, SCN_PREC_3XTF32)) ? SCN_PREC_3XTF32 : SCN_PREC_FP32;
+  if (precision == SCN_PREC_AUTO) use = (d_W_packed && tc_shape_ok(fs, nIn, N, scn_conv_auto_precision())) ? scn_conv_auto_precision() : SCN_PREC_FP32;
   if (use != SCN_PREC_FP32) {
     if (!tc_shape_ok(fs, nIn, N, use)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel (need N >= 16 and N % 4 == 0)");
     if (!d_W_packed) return fail(SCN_ERR_INVALID, "tensor-core precision needs packed weights");

@@ -33,10 +33,16 @@
 // records an error code in g_tc_error and carries on to its normal exit, so tensor memory is
 // always released and the context stays usable.
 #include "conv_nin_tc.cuh"
+#include <cuda_bf16.h>
 
 namespace scn {
 
 __device__ int g_tc_error = 0;
+
+// Source of the 16-byte gather for a missing row (negative rule, row past the end): zeros.  Copying
+// from here instead of predicating each copy keeps the gather loop at three instructions per copy.
+constexpr int ZERO_ROW_FLOATS = 16384;
+__device__ __align__(128) float g_zero_row[ZERO_ROW_FLOATS];
 
 namespace {
 
@@ -117,11 +123,14 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
-  int mTiles, accStride, K, generic, rulesDouble; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
+  int mTiles, accStride, K, generic, rulesDouble, rawEntries, nStages64; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(srcBytes) : "memory");
+}
+__device__ __forceinline__ void cp_async16_full(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async4(uint32_t dst, const void *src, uint32_t srcBytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(srcBytes) : "memory");
@@ -131,10 +140,84 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// Position in a ring of n buffers and the parity of the current pass over it (no division per step).
+struct Ring {
+  int idx = 0, phase = 0, n;
+  __device__ explicit Ring(int n_) : n(n_) {}
+  __device__ __forceinline__ void next() { if (++idx == n) { idx = 0; phase ^= 1; } }
+};
+
 constexpr int MAX_STAGES = 6;
 constexpr int EPI_COLS = 32;                      // accumulator columns staged per epilogue step
 constexpr int EPI_LD = EPI_COLS + 4;              // padded row stride (floats) of the staging slice
 constexpr int EPI_BYTES = BM * EPI_LD * 4;        // 18 KB
+
+// Epilogue role (warps 0-3 of both tensor-core kernels): drains accumulator n & 1 of work item n
+// while the main loop fills the other one.
+template <bool SPLIT, int ACT>
+__device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint32_t tmem, uint32_t accFullBar, uint32_t accEmptyBar,
+                                              int nItems, int kSplit) {
+  const int warp = threadIdx.x >> 5;
+  const int t = threadIdx.x;
+  const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
+  float *myRow = epi + (size_t)t * EPI_LD;
+  const int c4 = t & 7, rsub = t >> 3; // store phase: 8 threads per row, 16 rows per pass
+  int n = 0;
+  for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++n) {
+    const int tileId = SPLIT ? item / kSplit : item, split = SPLIT ? item - tileId * kSplit : 0;
+    const int tileN = tileId % P.nTiles, tileM = tileId / P.nTiles;
+    const int ab = n & 1;
+    mbar_wait(accFullBar + 8 * ab, (n >> 1) & 1, 2);
+    tc_fence_after();
+    const int row0 = tileM * BM, col0 = tileN * P.BN;
+    for (int c = 0; c < P.BN; c += EPI_COLS) {
+      const int width = min(EPI_COLS, P.BN - c); // 32, or 16 for the last slice when BN % 32 == 16
+      uint32_t a[32];
+      const uint32_t addr = laneAddr + (uint32_t)(ab * P.accStride + c);
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                   : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]),
+                     "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15])
+                   : "r"(addr));
+      if (width > 16)
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                     : "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]),
+                       "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31])
+                     : "r"(addr + 16));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int q = 0; q < 32; q += 4)
+        if (q < width)
+          *reinterpret_cast<float4 *>(myRow + q) = make_float4(__uint_as_float(a[q]), __uint_as_float(a[q + 1]), __uint_as_float(a[q + 2]), __uint_as_float(a[q + 3]));
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // coalesced: 8 threads cover one row's 128 bytes, a warp covers 4 rows per instruction
+      const int col = col0 + c + c4 * 4;
+      const bool colOk = c4 * 4 < width && col < P.N; // N % 4 == 0: a float4 is in or out as a whole
+      float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = b4;
+      if (colOk && !SPLIT) {
+        b4 = __ldg(reinterpret_cast<const float4 *>(P.bias + col));
+        if (ACT == SCN_PRELU) s4 = __ldg(reinterpret_cast<const float4 *>(P.prelu + col));
+      }
+#pragma unroll
+      for (int pass = 0; pass < BM / 16; ++pass) {
+        const int rl = pass * 16 + rsub, r = row0 + rl;
+        if (!colOk || r >= P.rows) continue;
+        const float4 v = *reinterpret_cast<const float4 *>(epi + (size_t)rl * EPI_LD + c4 * 4);
+        if (SPLIT) {
+          *reinterpret_cast<float4 *>(P.partial + ((long long)split * P.rows + r) * P.N + col) = v;
+        } else {
+          float4 o;
+          // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
+          o.x = activate_t<ACT>(P.p * v.x + P.p * b4.x, s4.x); o.y = activate_t<ACT>(P.p * v.y + P.p * b4.y, s4.y);
+          o.z = activate_t<ACT>(P.p * v.z + P.p * b4.z, s4.z); o.w = activate_t<ACT>(P.p * v.w + P.p * b4.w, s4.w);
+          *reinterpret_cast<float4 *>(P.out + (long long)r * P.N + col) = o;
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory"); // the slice is free again
+    }
+    tc_fence_before();
+    mbar_arrive(accEmptyBar + 8 * ab); // this accumulator may be overwritten
+  }
+}
 
 // Work items are output tiles, or (tile, K range) pairs when K is split over several CTAs.
 template <bool SPLIT, int ACT>
@@ -182,72 +265,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   };
 
   if (warp < 4) {
-    // ------------------------------------------------------------ epilogue
-    const int t = threadIdx.x;
-    const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
-    float *myRow = epi + (size_t)t * EPI_LD;
-    const int c4 = t & 7, rsub = t >> 3; // store phase: 8 threads per row, 16 rows per pass
-    int n = 0;
-    for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++n) {
-      int tileM, tileN, slab0, nLoc;
-      const int split = itemTile(item, tileM, tileN, slab0, nLoc);
-      const int ab = n & 1;
-      mbar_wait(accFullBar + 8 * ab, (n >> 1) & 1, 2);
-      tc_fence_after();
-      const int row0 = tileM * BM, col0 = tileN * P.BN;
-      for (int c = 0; c < P.BN; c += EPI_COLS) {
-        const int width = min(EPI_COLS, P.BN - c); // 32, or 16 for the last slice when BN % 32 == 16
-        uint32_t a[32];
-        const uint32_t addr = laneAddr + (uint32_t)(ab * P.accStride + c);
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                     : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]),
-                       "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15])
-                     : "r"(addr));
-        if (width > 16)
-          asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                       : "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]),
-                         "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31])
-                       : "r"(addr + 16));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int q = 0; q < 32; q += 4)
-          if (q < width)
-            *reinterpret_cast<float4 *>(myRow + q) = make_float4(__uint_as_float(a[q]), __uint_as_float(a[q + 1]), __uint_as_float(a[q + 2]), __uint_as_float(a[q + 3]));
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        // coalesced: 8 threads cover one row's 128 bytes, a warp covers 4 rows per instruction
-        const int col = col0 + c + c4 * 4;
-        const bool colOk = c4 * 4 < width && col < P.N; // N % 4 == 0: a float4 is in or out as a whole
-        float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), s4 = b4;
-        if (colOk && !SPLIT) {
-          b4 = __ldg(reinterpret_cast<const float4 *>(P.bias + col));
-          if (ACT == SCN_PRELU) s4 = __ldg(reinterpret_cast<const float4 *>(P.prelu + col));
-        }
-#pragma unroll
-        for (int pass = 0; pass < BM / 16; ++pass) {
-          const int rl = pass * 16 + rsub, r = row0 + rl;
-          if (!colOk || r >= P.rows) continue;
-          const float4 v = *reinterpret_cast<const float4 *>(epi + (size_t)rl * EPI_LD + c4 * 4);
-          if (SPLIT) {
-            *reinterpret_cast<float4 *>(P.partial + ((long long)split * P.rows + r) * P.N + col) = v;
-          } else {
-            float4 o;
-            // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
-            o.x = activate_t<ACT>(P.p * v.x + P.p * b4.x, s4.x); o.y = activate_t<ACT>(P.p * v.y + P.p * b4.y, s4.y);
-            o.z = activate_t<ACT>(P.p * v.z + P.p * b4.z, s4.z); o.w = activate_t<ACT>(P.p * v.w + P.p * b4.w, s4.w);
-            *reinterpret_cast<float4 *>(P.out + (long long)r * P.N + col) = o;
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory"); // the slice is free again
-      }
-      tc_fence_before();
-      mbar_arrive(accEmptyBar + 8 * ab); // this accumulator may be overwritten
-    }
+    epilogue_role<SPLIT, ACT>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit);
   } else if (warp < 8) {
     // ------------------------------------------------------------ gather: asynchronous 16-byte copies
     const int t = threadIdx.x - 128, chunk = t & 7, rbase = t >> 3;
     // this thread's 16-byte chunk sits at the same offset in each of its 8 rows (16 rows apart)
     const uint32_t rowOff = (rbase >> 3) * 1024 + (rbase & 7) * ROW_BYTES + ((chunk ^ (rbase & 7)) << 4);
-    int g = 0, nItem = 0;
+    int nItem = 0;
+    Ring ring(P.stages);
     // 16-byte asynchronous copies of one tile's [128 x fs] rules (the tile starts 512*fs bytes into
     // the array, so chunks are aligned); bytes past the end of the array are not read.
     auto stage_rules_async = [&](int item, int buf) {
@@ -289,12 +314,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
         // (padding up to a multiple of 32) and missing rows are zero-filled.  (Ordinary loads
         // followed by shared stores were measured slower: they expose the load latency per slab.)
         const int wq = warp - 4;
-        for (int q = 0; q < nLoc; ++q, ++g) {
-          const int s = slab0 + q, st = g % P.stages, it = g / P.stages;
+        for (int q = 0; q < nLoc; ++q, ring.next()) {
+          const int s = slab0 + q, st = ring.idx;
           const int k = s * SLAB + lane;
           const bool kOk = k < P.K;
           const int f = kOk ? k / P.nIn : 0, c = k - f * P.nIn;
-          mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 1);
+          mbar_wait(emptyBar + 8 * st, ring.phase ^ 1, 1);
           const uint32_t dst0 = smem_u32(smem + (size_t)st * stageBytes) + (uint32_t)wq * 4096 + (lane & 3) * 4;
           // eight rows at a time: first all rule reads (independent of one another), then the copies,
           // because the copy instructions keep their program order
@@ -323,9 +348,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
       }
       const float *rowPtr[8]; // start of the current filter cell's source row (nullptr: no row -> zero fill)
       int curF = -1;
-      for (int q = 0; q < nLoc; ++q, ++g) {
-        const int s = slab0 + q, st = g % P.stages, it = g / P.stages;
-        const int k0 = s * SLAB, f = k0 / P.nIn, c0 = k0 - f * P.nIn;
+      int f = slab0 * SLAB / P.nIn, c0 = slab0 * SLAB - f * P.nIn; // filter cell and channel offset of the slab, kept incrementally
+      for (int q = 0; q < nLoc; ++q, ring.next(), c0 += SLAB) {
+        const int st = ring.idx;
+        if (c0 == P.nIn) { c0 = 0; ++f; }
         if (f != curF) { // the rule column changes every nIn/32 slabs
           curF = f;
 #pragma unroll
@@ -337,30 +363,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
               else if (P.rules) src = __ldg(P.rules + (long long)r * P.fs + f);
               else src = r;
             }
-            rowPtr[i] = src >= 0 ? P.in + (long long)src * P.nIn + chunk * 4 : nullptr;
+            // a negative rule (or a row past the end) reads zeros
+            rowPtr[i] = (src >= 0 ? P.in + (long long)src * P.nIn : g_zero_row) + chunk * 4;
           }
         }
-        mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 1);
+        mbar_wait(emptyBar + 8 * st, ring.phase ^ 1, 1);
         const uint32_t dst = smem_u32(smem + (size_t)st * stageBytes) + rowOff;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          // a negative rule (or a row past the end) copies 0 source bytes: the 16 bytes are zero-filled
-          const bool have = rowPtr[i] != nullptr;
-          cp_async16(dst + i * 2048, have ? (const void *)(rowPtr[i] + c0) : (const void *)P.in, have ? 16u : 0u);
-        }
+        for (int i = 0; i < 8; ++i) cp_async16_full(dst + i * 2048, rowPtr[i] + c0);
         cp_async_arrive(rawBar + 8 * st);
       }
     }
   } else if (warp < 12) {
     // ------------------------------------------------------------ split: lo = x - tf32(x)
     const int t = threadIdx.x - 256;
-    int g = 0;
+    Ring ring(P.stages);
     for (int item = blockIdx.x; item < nItems; item += gridDim.x) {
       int tileM, tileN, slab0, nLoc;
       itemTile(item, tileM, tileN, slab0, nLoc);
-      for (int q = 0; q < nLoc; ++q, ++g) {
-        const int st = g % P.stages, it = g / P.stages;
-        mbar_wait(rawBar + 8 * st, it & 1, 5);
+      for (int q = 0; q < nLoc; ++q, ring.next()) {
+        const int st = ring.idx;
+        mbar_wait(rawBar + 8 * st, ring.phase, 5);
         unsigned char *aHi = smem + (size_t)st * stageBytes, *aLo = aHi + A_HALF;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -384,14 +407,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
     // ------------------------------------------------------------ weight tiles by bulk copy
     if (lane == 0) {
       const uint32_t bytes = 2 * bHalf;
-      int g = 0;
+      Ring ring(P.stages);
       for (int item = blockIdx.x; item < nItems; item += gridDim.x) {
         int tileM, tileN, slab0, nLoc;
         itemTile(item, tileM, tileN, slab0, nLoc);
         const unsigned char *srcBase = P.packed + ((size_t)tileN * P.nSlabs + slab0) * bytes;
-        for (int q = 0; q < nLoc; ++q, ++g) {
-          const int st = g % P.stages, it = g / P.stages;
-          mbar_wait(emptyBar + 8 * st, (it & 1) ^ 1, 3);
+        for (int q = 0; q < nLoc; ++q, ring.next()) {
+          const int st = ring.idx;
+          mbar_wait(emptyBar + 8 * st, ring.phase ^ 1, 3);
           mbar_arrive_expect_tx(fullBar + 8 * st, bytes);
           bulk_g2s(smem_u32(smem + (size_t)st * stageBytes + 2 * A_HALF), srcBase + (size_t)q * bytes, bytes, fullBar + 8 * st);
         }
@@ -400,7 +423,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   } else {
     // ------------------------------------------------------------ MMA issue
     if (lane == 0) {
-      int g = 0, n = 0;
+      int n = 0;
+      Ring ring(P.stages);
       for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++n) {
         int tileM, tileN, slab0, nLoc;
         itemTile(item, tileM, tileN, slab0, nLoc);
@@ -408,9 +432,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
         mbar_wait(accEmptyBar + 8 * ab, ((n >> 1) & 1) ^ 1, 6); // the epilogue has drained this accumulator
         tc_fence_after();
         const uint32_t acc = tmem + (uint32_t)(ab * P.accStride);
-        for (int q = 0; q < nLoc; ++q, ++g) {
-          const int st = g % P.stages, it = g / P.stages;
-          mbar_wait(fullBar + 8 * st, it & 1, 4);
+        for (int q = 0; q < nLoc; ++q, ring.next()) {
+          const int st = ring.idx;
+          mbar_wait(fullBar + 8 * st, ring.phase, 4);
           tc_fence_after();
           const uint32_t aHi = smem_u32(smem + (size_t)st * stageBytes), aLo = aHi + A_HALF;
           const uint32_t bHi = aHi + 2 * A_HALF, bLo = bHi + bHalf;
@@ -433,6 +457,318 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   if (warp == 13) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)P.tmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// bf16 operands (kind::f16), fp32 accumulation.  PASSES == 3: x = hi + lo with hi = bf16(x),
+// lo = bf16(x - hi) for both operands and A_lo*B_hi + A_hi*B_lo + A_hi*B_hi ("3xBF16": products
+// carry 16 mantissa bits, relative error about 2^-16 per product, half the tensor-pipe time and
+// 5/8 of the operand bytes of 3xTF32).  PASSES == 1: plain bf16 (A_hi*B_hi only).
+//
+// Same roles as k_conv_nin_tc, but the gather lands in a ring of raw fp32 entries (128 rows x 32
+// values) that is separate from the operand stages (128 rows x 64 bf16 = two raw entries), so
+// gathers stay in flight while earlier slabs are converted and multiplied:
+//   warps 4-7   gather into raw entry e: wait rawEmpty[e], cp.async, arrival on rawFull[e]
+//   warps 8-15  convert: wait empty[stage] once, then per half: wait rawFull[e], read fp32,
+//               write the bf16 hi (and lo) 16-byte chunks of the K-major SWIZZLE_128B operand
+//               rows, arrive on rawEmpty[e]; after both halves fence to the async proxy and
+//               arrive on full[stage]
+//   warp 16     weight block of the stage (hi [and lo] image, packed by tc_pack) by bulk copy
+//   warp 17     per stage PASSES x 4 tcgen05.mma (M=128, N=BN, K=16), commit onto empty[stage]
+constexpr int MAX_RAW = 8;
+constexpr int CONVERT_THREADS = 256;                       // warps 8-15
+constexpr int MMA_WARP16 = 8 + CONVERT_THREADS / 32 + 1;   // then the weight warp, then the MMA warp
+constexpr int NUM_THREADS16 = (MMA_WARP16 + 1) * 32;
+
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) { // a at the lower address
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&v);
+}
+__device__ __forceinline__ float bf16_hi(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+template <bool SPLIT, int ACT, int PASSES>
+__global__ void __launch_bounds__(NUM_THREADS16, 1) k_conv_nin_tc16(const Params P) {
+  extern __shared__ unsigned char smem_raw[];
+  int *rulesS = reinterpret_cast<int *>(smem_raw);
+  unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + (P.rulesDouble ? 2 : 1) * P.rulesBytes + 1023) & ~(uintptr_t)1023);
+  const int bImg = P.BN * ROW_BYTES;                       // one weight image: BN rows x 64 bf16
+  const int aBytes = (PASSES == 3 ? 2 : 1) * A_HALF;       // A_hi [, A_lo]
+  const int stageBytes = aBytes + (PASSES == 3 ? 2 : 1) * bImg;
+  unsigned char *rawRing = smem;                           // rawEntries x 16 KB
+  unsigned char *stageRing = smem + (size_t)P.rawEntries * A_HALF;
+  float *epi = reinterpret_cast<float *>(stageRing + (size_t)P.stages * stageBytes);
+  __shared__ __align__(8) uint64_t bars[2 * MAX_RAW + 2 * MAX_STAGES + 4];
+  __shared__ uint32_t tmemBase;
+  const uint32_t rawFullBar = smem_u32(&bars[0]), rawEmptyBar = smem_u32(&bars[MAX_RAW]), fullBar = smem_u32(&bars[2 * MAX_RAW]),
+                 emptyBar = smem_u32(&bars[2 * MAX_RAW + MAX_STAGES]), accFullBar = smem_u32(&bars[2 * MAX_RAW + 2 * MAX_STAGES]),
+                 accEmptyBar = smem_u32(&bars[2 * MAX_RAW + 2 * MAX_STAGES + 2]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kSplit = SPLIT ? P.kSplit : 1;
+  const int nItems = P.mTiles * P.nTiles * kSplit;
+
+  if (threadIdx.x == 0) {
+    for (int e = 0; e < P.rawEntries; ++e) { mbar_init(rawFullBar + 8 * e, 128); mbar_init(rawEmptyBar + 8 * e, CONVERT_THREADS); }
+    for (int st = 0; st < P.stages; ++st) {
+      mbar_init(fullBar + 8 * st, CONVERT_THREADS + 1); // the convert threads + the weight copy
+      mbar_init(emptyBar + 8 * st, 1);      // tcgen05.commit
+    }
+    for (int a = 0; a < 2; ++a) { mbar_init(accFullBar + 8 * a, 1); mbar_init(accEmptyBar + 8 * a, 128); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == MMA_WARP16) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmemBase)), "r"((uint32_t)P.tmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmemBase;
+
+  // work item -> tile and its range of 64-wide K stages
+  auto itemTile = [&](int item, int &tileM, int &tileN, int &stage0, int &nLoc) {
+    const int tileId = SPLIT ? item / kSplit : item, split = SPLIT ? item - tileId * kSplit : 0;
+    tileN = tileId % P.nTiles; tileM = tileId / P.nTiles;
+    stage0 = SPLIT ? split * P.nStages64 / kSplit : 0;
+    nLoc = SPLIT ? (split + 1) * P.nStages64 / kSplit - stage0 : P.nStages64;
+  };
+
+  if (warp < 4) {
+    epilogue_role<SPLIT, ACT>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit);
+  } else if (warp < 8) {
+    // ------------------------------------------------------------ gather into the raw ring
+    const int t = threadIdx.x - 128, chunk = t & 7, rbase = t >> 3;
+    const uint32_t rowOff = (rbase >> 3) * 1024 + (rbase & 7) * ROW_BYTES + ((chunk ^ (rbase & 7)) << 4);
+    int nItem = 0;
+    Ring raw(P.rawEntries); // raw entries: 32 values of K each
+    auto stage_rules_async = [&](int item, int buf) {
+      int tileM, tileN, stage0, nLoc;
+      itemTile(item, tileM, tileN, stage0, nLoc);
+      const long long first = (long long)tileM * BM * P.fs, total = (long long)P.rows * P.fs;
+      const uint32_t dst = smem_u32(rulesS) + buf * P.rulesBytes;
+      for (int ch = t; ch < BM * P.fs / 4; ch += 128) {
+        const long long left = total - (first + ch * 4);
+        const uint32_t bytes = left >= 4 ? 16u : left > 0 ? (uint32_t)left * 4u : 0u;
+        cp_async16(dst + ch * 16, bytes ? (const void *)(P.rules + first + ch * 4) : (const void *)P.rules, bytes);
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (P.rulesDouble && (int)blockIdx.x < nItems) stage_rules_async(blockIdx.x, 0);
+    for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++nItem) {
+      int tileM, tileN, stage0, nLoc;
+      itemTile(item, tileM, tileN, stage0, nLoc);
+      const int row0 = tileM * BM;
+      const int *rulesT = rulesS;
+      if (P.rulesDouble) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        rulesT = rulesS + (nItem & 1) * (P.rulesBytes >> 2);
+        if (item + (int)gridDim.x < nItems) stage_rules_async(item + gridDim.x, (nItem + 1) & 1);
+      } else if (P.rulesBytes > 0) {
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        const int nr = BM * P.fs;
+        for (int e = t; e < nr; e += 128) rulesS[e] = __ldg(P.rules + min((long long)row0 * P.fs + e, (long long)P.rows * P.fs - 1));
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+      }
+      const float *rowPtr[8];
+      int curF = -1;
+      const int wq = warp - 4;
+      int f16 = 2 * stage0 * SLAB / P.nIn, c0 = 2 * stage0 * SLAB - f16 * P.nIn - SLAB; // 16-byte path: cell and channel offset, kept incrementally
+      for (int q = 0; q < 2 * nLoc; ++q) {
+        const int s = 2 * stage0 + q, e = raw.idx; // s: 32-wide slab of K
+        if (s >= P.nSlabs) break; // the second half of the last stage lies past K: the convert warps write zeros
+        c0 += SLAB;
+        if (c0 >= P.nIn) { c0 -= P.nIn; ++f16; }
+        mbar_wait(rawEmptyBar + 8 * e, raw.phase ^ 1, 1);
+        const uint32_t entry = smem_u32(rawRing + (size_t)e * A_HALF);
+        if (P.generic) { // any nIn: 4-byte copies, lane = position in the slab (see k_conv_nin_tc)
+          const int k = s * SLAB + lane;
+          const bool kOk = k < P.K;
+          const int f = kOk ? k / P.nIn : 0, c = k - f * P.nIn;
+          const uint32_t dst0 = entry + (uint32_t)wq * 4096 + (lane & 3) * 4;
+#pragma unroll 1
+          for (int i0 = 0; i0 < 32; i0 += 8) {
+            int src[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int rl = wq * 32 + i0 + j, r = row0 + rl;
+              src[j] = -1;
+              if (kOk && r < P.rows) {
+                if (P.rulesBytes > 0) src[j] = rulesT[rl * P.fs + f];
+                else if (P.rules) src[j] = __ldg(P.rules + (long long)r * P.fs + f);
+                else src[j] = r;
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t dst = dst0 + (i0 >> 3) * 1024 + j * ROW_BYTES + (((lane >> 2) ^ j) << 4);
+              cp_async4(dst, src[j] >= 0 ? (const void *)(P.in + (long long)src[j] * P.nIn + c) : (const void *)P.in, src[j] >= 0 ? 4u : 0u);
+            }
+          }
+        } else {
+          // (one 128-byte bulk copy per row and slab instead of these per-lane copies was measured 1.4-1.8x
+          // slower: the copy engine retires a small bulk copy about every 25 cycles per SM)
+          const int f = f16;
+          if (f != curF) { // the rule column changes every nIn/32 slabs
+            curF = f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rl = rbase + 16 * i, r = row0 + rl;
+              int src = -1;
+              if (r < P.rows) {
+                if (P.rulesBytes > 0) src = rulesT[rl * P.fs + f];
+                else if (P.rules) src = __ldg(P.rules + (long long)r * P.fs + f);
+                else src = r;
+              }
+              rowPtr[i] = (src >= 0 ? P.in + (long long)src * P.nIn : g_zero_row) + chunk * 4;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) cp_async16_full(entry + rowOff + i * 2048, rowPtr[i] + c0);
+        }
+        cp_async_arrive(rawFullBar + 8 * e);
+        raw.next();
+      }
+    }
+  } else if (warp < 8 + CONVERT_THREADS / 32) {
+    // ------------------------------------------------------------ convert fp32 -> bf16 hi [, lo]
+    const int t = threadIdx.x - 256;
+    // 8 consecutive threads take the four 8-value groups of rows r and r + 4: their 16-byte stores
+    // hit eight different chunks (the swizzle term differs in bit 2), and the second row reads its
+    // two fp32 chunks in the opposite order, so loads and stores are free of bank conflicts
+    const int kg = t & 3, hiRow = (t >> 2) & 1, qd = (t >> 3) & 15, part = t >> 7;
+    Ring raw(P.rawEntries), ring(P.stages); // raw entries, operand stages
+    for (int item = blockIdx.x; item < nItems; item += gridDim.x) {
+      int tileM, tileN, stage0, nLoc;
+      itemTile(item, tileM, tileN, stage0, nLoc);
+      for (int q = 0; q < nLoc; ++q, ring.next()) {
+        const int st = ring.idx;
+        mbar_wait(emptyBar + 8 * st, ring.phase ^ 1, 7); // the tensor core has finished with this stage
+        unsigned char *aHi = stageRing + (size_t)st * stageBytes, *aLo = aHi + A_HALF;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          if (2 * (stage0 + q) + h >= P.nSlabs) { // K ends inside this stage: the upper half of the operand rows is zero
+#pragma unroll
+            for (int ii = 0; ii < 512 / CONVERT_THREADS; ++ii) {
+              const int i = part * (512 / CONVERT_THREADS) + ii;
+              const int r = (qd >> 2) * 32 + i * 8 + (qd & 3) + 4 * hiRow;
+              const int off = (r >> 3) * 1024 + (r & 7) * ROW_BYTES + (((h * 4 + kg) ^ (r & 7)) << 4);
+              *reinterpret_cast<uint4 *>(aHi + off) = make_uint4(0u, 0u, 0u, 0u);
+              if (PASSES == 3) *reinterpret_cast<uint4 *>(aLo + off) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            continue;
+          }
+          const int e = raw.idx;
+          mbar_wait(rawFullBar + 8 * e, raw.phase, 5);
+          const unsigned char *rawp = rawRing + (size_t)e * A_HALF;
+#pragma unroll
+          for (int ii = 0; ii < 512 / CONVERT_THREADS; ++ii) {
+            // a group = 8 consecutive values of K of one row: two 16-byte fp32 chunks in, one 16-byte
+            // bf16 chunk out (per image)
+            const int i = part * (512 / CONVERT_THREADS) + ii;
+            const int r = (qd >> 2) * 32 + i * 8 + (qd & 3) + 4 * hiRow;
+            const unsigned char *rowp = rawp + (r >> 3) * 1024 + (r & 7) * ROW_BYTES;
+            const float4 va = *reinterpret_cast<const float4 *>(rowp + (((2 * kg + hiRow) ^ (r & 7)) << 4));
+            const float4 vb = *reinterpret_cast<const float4 *>(rowp + (((2 * kg + 1 - hiRow) ^ (r & 7)) << 4));
+            const float4 v0 = hiRow ? vb : va, v1 = hiRow ? va : vb;
+            const int off = (r >> 3) * 1024 + (r & 7) * ROW_BYTES + (((h * 4 + kg) ^ (r & 7)) << 4);
+            const float h0 = bf16_hi(v0.x), h1 = bf16_hi(v0.y), h2 = bf16_hi(v0.z), h3 = bf16_hi(v0.w);
+            const float h4 = bf16_hi(v1.x), h5 = bf16_hi(v1.y), h6 = bf16_hi(v1.z), h7 = bf16_hi(v1.w);
+            *reinterpret_cast<uint4 *>(aHi + off) = make_uint4(pack_bf16(h0, h1), pack_bf16(h2, h3), pack_bf16(h4, h5), pack_bf16(h6, h7));
+            if (PASSES == 3)
+              *reinterpret_cast<uint4 *>(aLo + off) = make_uint4(pack_bf16(v0.x - h0, v0.y - h1), pack_bf16(v0.z - h2, v0.w - h3),
+                                                                 pack_bf16(v1.x - h4, v1.y - h5), pack_bf16(v1.z - h6, v1.w - h7));
+          }
+          mbar_arrive(rawEmptyBar + 8 * e); // the raw entry may be overwritten
+          raw.next();
+        }
+        fence_async_smem(); // make the generic-proxy stores visible to the tensor core's reads
+        mbar_arrive(fullBar + 8 * st);
+      }
+    }
+  } else if (warp == MMA_WARP16 - 1) {
+    // ------------------------------------------------------------ weight blocks by bulk copy
+    if (lane == 0) {
+      const uint32_t bytes = (PASSES == 3 ? 2 : 1) * bImg;
+      Ring ring(P.stages);
+      for (int item = blockIdx.x; item < nItems; item += gridDim.x) {
+        int tileM, tileN, stage0, nLoc;
+        itemTile(item, tileM, tileN, stage0, nLoc);
+        const unsigned char *srcBase = P.packed + ((size_t)tileN * P.nStages64 + stage0) * bytes;
+        for (int q = 0; q < nLoc; ++q, ring.next()) {
+          const int st = ring.idx;
+          mbar_wait(emptyBar + 8 * st, ring.phase ^ 1, 3);
+          mbar_arrive_expect_tx(fullBar + 8 * st, bytes);
+          bulk_g2s(smem_u32(stageRing + (size_t)st * stageBytes + aBytes), srcBase + (size_t)q * bytes, bytes, fullBar + 8 * st);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      int n = 0;
+      Ring ring(P.stages);
+      for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++n) {
+        int tileM, tileN, stage0, nLoc;
+        itemTile(item, tileM, tileN, stage0, nLoc);
+        const int ab = n & 1;
+        mbar_wait(accEmptyBar + 8 * ab, ((n >> 1) & 1) ^ 1, 6);
+        tc_fence_after();
+        const uint32_t acc = tmem + (uint32_t)(ab * P.accStride);
+        for (int q = 0; q < nLoc; ++q, ring.next()) {
+          const int st = ring.idx;
+          mbar_wait(fullBar + 8 * st, ring.phase, 4);
+          tc_fence_after();
+          const uint32_t aHi = smem_u32(stageRing + (size_t)st * stageBytes), aLo = aHi + A_HALF;
+          const uint32_t bHi = aHi + aBytes, bLo = bHi + bImg;
+          const uint64_t dAhi = smem_desc(aHi), dAlo = smem_desc(aLo), dBhi = smem_desc(bHi), dBlo = smem_desc(bLo);
+          if (PASSES == 3) { // small cross terms first, the dominant hi*hi product last
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_bf16(acc, dAlo + 2 * k, dBhi + 2 * k, P.idesc, (q | k) != 0);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_bf16(acc, dAhi + 2 * k, dBlo + 2 * k, P.idesc, 1);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_bf16(acc, dAhi + 2 * k, dBhi + 2 * k, P.idesc, 1);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_bf16(acc, dAhi + 2 * k, dBhi + 2 * k, P.idesc, (q | k) != 0);
+          }
+          mma_commit(emptyBar + 8 * st);
+        }
+        mma_commit(accFullBar + 8 * ab);
+      }
+    }
+  }
+  __syncwarp();
+  __syncthreads();
+  if (warp == MMA_WARP16) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)P.tmemCols) : "memory");
+  }
+}
+
+// W[K x N] row-major -> per (column tile, 64-wide K stage) one contiguous block: the bf16 hi image
+// [BN x 64] (K-major, SWIZZLE_128B order), then for three passes the lo image.
+__global__ void k_pack_bf16(const float *__restrict__ W, int K, int N, int BN, int nTiles, int nStages64, int passes,
+                            unsigned short *__restrict__ packed) {
+  const long long total = (long long)nTiles * nStages64 * BN * 64;
+  const int images = passes == 3 ? 2 : 1;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < total; q += (long long)gridDim.x * blockDim.x) {
+    const int kl = (int)(q % 64);
+    const int nl = (int)((q / 64) % BN);
+    const long long blk = q / (64LL * BN);
+    const int stage = (int)(blk % nStages64), tile = (int)(blk / nStages64);
+    const int k = stage * 64 + kl, n = tile * BN + nl;
+    const float w = (k < K && n < N) ? W[(long long)k * N + n] : 0.f;
+    const __nv_bfloat16 hi = __float2bfloat16_rn(w), lo = __float2bfloat16_rn(w - __bfloat162float(hi));
+    const int off = (nl >> 3) * 1024 + (nl & 7) * ROW_BYTES + ((((kl >> 3) ^ (nl & 7))) << 4) + (kl & 7) * 2;
+    unsigned short *base = packed + blk * ((long long)images * BN * 64);
+    base[off >> 1] = *reinterpret_cast<const unsigned short *>(&hi);
+    if (images == 2) base[BN * 64 + (off >> 1)] = *reinterpret_cast<const unsigned short *>(&lo);
   }
 }
 
@@ -514,23 +850,78 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
   return true;
 }
 
+// bf16 kernels: operand stage = A images (16 KB each) + weight images (BN x 128 B each) for 64 values
+// of K; the raw ring takes what is left (at least two entries = one stage's worth of gather).
+// The column tiling depends on N and the number of passes only (weights are packed once, before any
+// rulebook is known): the fewest column tiles for which two stages, two raw entries and 4 KB of
+// staged rules (two buffers of a 2^2 filter) fit.  Stages, raw entries and rule buffers are then chosen per launch.
+bool make_tiling16(int K, int N, int fs, bool haveRules, int passes, Tiling *t, int *rawEntries, int *nStages64) {
+  if (K < 1 || N < 16) return false;
+  const int images = passes == 3 ? 2 : 1;
+  const int avail = 226 * 1024 - 1024 - EPI_BYTES;
+  t->nSlabs = (K + SLAB - 1) / SLAB;
+  *nStages64 = (t->nSlabs + 1) / 2;
+  int nTiles = (N + 255) / 256, BN = 0, stageBytes = 0;
+  for (;; ++nTiles) {
+    BN = ((N + nTiles - 1) / nTiles + 15) / 16 * 16;
+    stageBytes = images * (A_HALF + BN * ROW_BYTES);
+    if (2 * stageBytes + 2 * A_HALF + 4 * 1024 <= avail) break;
+    if (BN == 16) return false;
+  }
+  t->nTiles = nTiles; t->BN = BN;
+  const int oneRules = (haveRules && fs <= 32) ? BM * fs * 4 : 0;
+  int ruleBufs = oneRules ? 2 : 0;
+  while (ruleBufs > 0 && 2 * stageBytes + 2 * A_HALF + ruleBufs * oneRules > avail) --ruleBufs;
+  t->rulesBytes = ruleBufs ? oneRules : 0; // 0: the gather reads its rules from global memory
+  t->rulesDouble = ruleBufs == 2 ? 1 : 0;
+  const int budget = avail - ruleBufs * oneRules;
+  int stages = 3, raw = (budget - 3 * stageBytes) / A_HALF; // three stages when two raw entries still fit
+  if (raw < 2) { stages = 2; raw = (budget - 2 * stageBytes) / A_HALF; }
+  if (raw > MAX_RAW) raw = MAX_RAW;
+  t->stages = stages; *rawEntries = raw;
+  t->accStride = (BN + 31) / 32 * 32;
+  int cols = 32;
+  while (cols < 2 * t->accStride) cols *= 2;
+  t->tmemCols = cols;
+  t->smemBytes = (size_t)stages * stageBytes + (size_t)raw * A_HALF + 1024 + (size_t)ruleBufs * oneRules + EPI_BYTES;
+  return true;
+}
+
+int passes_of(int precision) { return precision == SCN_PREC_3XBF16 ? 3 : precision == SCN_PREC_BF16 ? 1 : 0; }
+
 } // namespace
 
 bool tc_shape_ok(int fs, int nIn, int N, int precision) {
-  if (precision != SCN_PREC_3XTF32) return false;
   Tiling t;
+  if (nIn % SLAB == 0 && nIn > ZERO_ROW_FLOATS) return false; // the 16-byte gather reads missing rows from g_zero_row
+  int raw, st64;
+  if (passes_of(precision)) return N % 4 == 0 && make_tiling16(fs * nIn, N, fs, true, passes_of(precision), &t, &raw, &st64);
+  if (precision != SCN_PREC_3XTF32) return false;
   return N % 4 == 0 && make_tiling(fs * nIn, N, fs, true, &t);
 }
 
 size_t tc_packed_bytes(int K, int N, int precision) {
-  if (precision != SCN_PREC_3XTF32) return 0;
   Tiling t;
+  if (const int passes = passes_of(precision)) {
+    int raw, st64;
+    if (!make_tiling16(K, N, 1, false, passes, &t, &raw, &st64)) return 0;
+    return (size_t)t.nTiles * st64 * (passes == 3 ? 2 : 1) * t.BN * ROW_BYTES;
+  }
+  if (precision != SCN_PREC_3XTF32) return 0;
   if (!make_tiling(K, N, 1, false, &t)) return 0;
   return (size_t)t.nTiles * t.nSlabs * 2 * t.BN * ROW_BYTES;
 }
 
 int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaStream_t s) {
   Tiling t;
+  if (const int passes = passes_of(precision)) {
+    int raw, st64;
+    if (!make_tiling16(K, N, 1, false, passes, &t, &raw, &st64)) return fail(SCN_ERR_UNSUPPORTED, "no tensor-core layout for this shape/precision");
+    const long long total = (long long)t.nTiles * st64 * t.BN * 64;
+    k_pack_bf16<<<grid_for(total, 256), 256, 0, s>>>(d_W, K, N, t.BN, t.nTiles, st64, passes, (unsigned short *)d_packed);
+    SCN_LAUNCH_CHECK("k_pack_bf16");
+    return SCN_OK;
+  }
   if (precision != SCN_PREC_3XTF32 || !make_tiling(K, N, 1, false, &t)) return fail(SCN_ERR_UNSUPPORTED, "no tensor-core layout for this shape/precision");
   const long long total = (long long)t.nTiles * t.nSlabs * t.BN * SLAB;
   k_pack_tf32<<<grid_for(total, 256), 256, 0, s>>>(d_W, K, N, t.BN, t.nTiles, t.nSlabs, (float *)d_packed);
@@ -540,6 +931,12 @@ int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaS
 
 size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision) {
   Tiling t;
+  if (const int passes = passes_of(precision)) {
+    int raw, st64;
+    if (N % 4 != 0 || !make_tiling16(fs * nIn, N, fs, true, passes, &t, &raw, &st64)) return 0;
+    const int k = choose_ksplit(((rows + BM - 1) / BM) * t.nTiles, st64 * 2, rows, N, (size_t)-1);
+    return k > 1 ? (size_t)k * rows * N * sizeof(float) : 0;
+  }
   if (precision != SCN_PREC_3XTF32 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, true, &t)) return 0;
   const int tiles = ((rows + BM - 1) / BM) * t.nTiles;
   const int k = choose_ksplit(tiles, t.nSlabs, rows, N, (size_t)-1);
@@ -550,31 +947,49 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
               const float *d_prelu, int N, float p, int act, int precision, float *d_out, void *d_ws, size_t wsBytes,
               cudaStream_t s) {
   Tiling t;
-  if (precision != SCN_PREC_3XTF32 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t))
-    return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
+  const int passes = passes_of(precision);
+  int rawEntries = 0, nStages64 = 0;
+  const bool ok = N % 4 == 0 && (passes ? make_tiling16(fs * nIn, N, fs, d_rules != nullptr, passes, &t, &rawEntries, &nStages64)
+                                        : precision == SCN_PREC_3XTF32 && make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t));
+  if (!ok || (nIn % SLAB == 0 && nIn > ZERO_ROW_FLOATS)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
   if (((uintptr_t)d_in | (uintptr_t)d_out | (uintptr_t)d_packed) & 15) return fail(SCN_ERR_INVALID, "tensor-core path needs 16-byte aligned buffers");
   Params P;
+  P.rawEntries = rawEntries; P.nStages64 = nStages64;
   P.in = d_in; P.rules = d_rules; P.rows = rows; P.fs = fs; P.nIn = nIn;
   P.packed = (const unsigned char *)d_packed; P.bias = d_B; P.prelu = d_prelu;
   P.N = N; P.BN = t.BN; P.nTiles = t.nTiles; P.nSlabs = t.nSlabs; P.stages = t.stages; P.tmemCols = t.tmemCols; P.rulesBytes = t.rulesBytes;
   P.p = p; P.act = act; P.out = d_out;
-  // instruction descriptor: D = fp32, A = B = tf32, both K-major, N = BN, M = 128
-  P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(t.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  // instruction descriptor: D = fp32, A = B = tf32 (2) or bf16 (1), both K-major, N = BN, M = 128
+  const uint32_t fmt = passes ? 1u : 2u;
+  P.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(t.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   const int mTiles = (rows + BM - 1) / BM;
-  P.kSplit = (d_ws && ((uintptr_t)d_ws & 15) == 0) ? choose_ksplit(mTiles * t.nTiles, t.nSlabs, rows, N, wsBytes) : 1;
+  P.kSplit = (d_ws && ((uintptr_t)d_ws & 15) == 0) ? choose_ksplit(mTiles * t.nTiles, passes ? 2 * nStages64 : t.nSlabs, rows, N, wsBytes) : 1;
   P.partial = (float *)d_ws;
   P.mTiles = mTiles; P.accStride = t.accStride;
   P.K = fs * nIn; P.generic = (nIn % SLAB != 0) ? 1 : 0;
   P.rulesDouble = (t.rulesDouble && ((uintptr_t)d_rules & 15) == 0) ? 1 : 0;
   const int items = mTiles * t.nTiles * P.kSplit;
   const int grid = items < sm_count() ? items : sm_count(); // persistent: one CTA per SM
-  if (P.kSplit > 1) {
+#define SCN_TC16_LAUNCH(PASSES)                                                                                                          \
+  do {                                                                                                                                  \
+    if (P.kSplit > 1) {                                                                                                                 \
+      SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc16<true, SCN_NOSIGMOID, PASSES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024)); \
+      k_conv_nin_tc16<true, SCN_NOSIGMOID, PASSES><<<grid, NUM_THREADS16, t.smemBytes, s>>>(P);                                          \
+    } else {                                                                                                                            \
+      SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc16<false, ACT, PASSES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024)); \
+                       (k_conv_nin_tc16<false, ACT, PASSES><<<grid, NUM_THREADS16, t.smemBytes, s>>>(P)));                               \
+    }                                                                                                                                   \
+  } while (0)
+  if (passes == 3) SCN_TC16_LAUNCH(3);
+  else if (passes == 1) SCN_TC16_LAUNCH(1);
+  else if (P.kSplit > 1) {
     SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<true, SCN_NOSIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     k_conv_nin_tc<true, SCN_NOSIGMOID><<<grid, NUM_THREADS, t.smemBytes, s>>>(P);
   } else {
     SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
                      (k_conv_nin_tc<false, ACT><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
   }
+#undef SCN_TC16_LAUNCH
   SCN_LAUNCH_CHECK("k_conv_nin_tc");
   if (P.kSplit > 1) {
     SCN_DISPATCH_ACT(act, (k_splitk_finish<ACT><<<grid_for((long long)rows * N / 4, 256), 256, 0, s>>>(P.partial, P.kSplit, rows, N, d_B, d_prelu, p, d_out)));

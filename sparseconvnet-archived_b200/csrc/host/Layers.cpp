@@ -297,7 +297,7 @@ int TerminalPoolingLayer::calculateInputSpatialSize(int outputSpatialSize) {
 NetworkInNetworkLayer::NetworkInNetworkLayer(cudaMemStream &memStream, cublasHandle_t &, int nFeaturesIn, int nFeaturesOut, float dropout,
                                              ActivationFunction fn, float alpha)
     : SpatiallySparseLayer(memStream), W(false, nFeaturesIn * nFeaturesOut), MW(false, 0), B(false, nFeaturesOut), MB(false, 0), fn(fn),
-      nFeaturesIn(nFeaturesIn), nFeaturesOut(nFeaturesOut), dropout(dropout), precision(SCN_PREC_AUTO), packed(nullptr), packedBytes(0),
+      nFeaturesIn(nFeaturesIn), nFeaturesOut(nFeaturesOut), dropout(dropout), precision(SCN_PREC_AUTO), precisionFallback(false), packed(nullptr), packedBytes(0),
       packedPrecision(-100), packedFs(0) {
   // uniform(+-sqrt(6/(nIn + nOut*alpha))) as NetworkInNetworkLayer.cu:135-137, from a fixed
   // seed (the reference seeds from the clock); real runs load weights.
@@ -370,8 +370,12 @@ void NetworkInNetworkLayer::forwards(SpatiallySparseBatch &batch, SpatiallySpars
   int prec = precision;
   const void *pk = nullptr;
   if (prec != SCN_PREC_FP32) {
-    pk = packedWeights(fs, nIn, prec == SCN_PREC_AUTO ? SCN_PREC_3XTF32 : prec);
-    if (!pk && prec != SCN_PREC_AUTO) throw ScnException("NetworkInNetworkLayer: layer shape has no tensor-core path; use SCN_PREC_AUTO or SCN_PREC_FP32");
+    pk = packedWeights(fs, nIn, prec == SCN_PREC_AUTO ? scn_conv_auto_precision() : prec);
+    if (nFeaturesOut % 4 != 0) pk = nullptr; // the tensor-core kernels store whole float4 columns
+    if (!pk && prec != SCN_PREC_AUTO) {
+      if (!precisionFallback) throw ScnException("NetworkInNetworkLayer: layer shape has no tensor-core path; use SCN_PREC_AUTO or SCN_PREC_FP32");
+      prec = SCN_PREC_FP32;
+    }
   }
   void *ws = nullptr;
   size_t wsBytes = pk ? scn_conv_nin_workspace_bytes(output.nSpatialSites, fs, nIn, nFeaturesOut, prec) : 0;

@@ -16,6 +16,7 @@ public:
   int nFeaturesIn, nFeaturesOut;
   float dropout;
   int precision; // scn_precision used by forwards(); SCN_PREC_AUTO by default
+  bool precisionFallback; // true: a tensor-core precision falls back to the CUDA-core kernel where the shape has no tensor-core path (false: throw)
   NetworkInNetworkLayer(cudaMemStream &memStream, cublasHandle_t &cublasHandle, int nFeaturesIn, int nFeaturesOut,
                         float dropout = 0, ActivationFunction fn = NOSIGMOID, float alpha = 1);
   ~NetworkInNetworkLayer();

@@ -133,10 +133,22 @@ CONV_TC = [
 ]
 
 
+# precision -> (bound against the fp64-accumulating oracle, bound that shows the split is at work)
+TC_PRECISIONS = {
+    "3XTF32": (RTOL_FP32, 2e-5),   # a single tf32 product would be about 1e-3
+    "3XBF16": (RTOL_FP32, 5e-5),   # products carry 16 mantissa bits: about 2^-16 per product; plain bf16 is about 5e-3
+    "BF16": (2e-2, 2e-2),          # the optional reduced-precision path
+}
+
+
+@pytest.mark.parametrize("precision", list(TC_PRECISIONS))
 @pytest.mark.parametrize("rows_in,rows_out,fs,nIn,N,act,p", CONV_TC)
-def test_conv_nin_tensor_core_3xtf32(abi, oracle, rows_in, rows_out, fs, nIn, N, act, p):
-    """tcgen05 kind::tf32 with hi/lo split of both operands: fp32-grade, same 1e-4 bound."""
+def test_conv_nin_tensor_core(abi, oracle, rows_in, rows_out, fs, nIn, N, act, p, precision):
+    """tcgen05 with hi/lo split of both operands (kind::tf32 or bf16 under kind::f16): fp32-grade, same
+    1e-4 bound as the CUDA-core kernels; plain bf16 within 2e-2."""
     from oracle import orc
+    prec = getattr(abi, "PREC_" + precision)
+    bound, tight = TC_PRECISIONS[precision]
     rng = np.random.default_rng(rows_out + fs * 7 + N)
     actc = getattr(orc, act)
     K = fs * nIn
@@ -151,17 +163,16 @@ def test_conv_nin_tensor_core_3xtf32(abi, oracle, rows_in, rows_out, fs, nIn, N,
         X = oracle.gather(feat, rules, nIn).reshape(rows_out, K)
     ref = oracle.nin_forward(X, W, B, prelu, p, actc, accum64=True)
     dW = torch.from_numpy(W).cuda()
-    packed = abi.pack_weights(dW, abi.PREC_3XTF32)
+    packed = abi.pack_weights(dW, prec)
     out = abi.conv_nin_forward(torch.from_numpy(feat).cuda(),
                                None if rules is None else torch.from_numpy(rules).cuda().flatten(), fs, dW,
                                torch.from_numpy(B).cuda(), None if prelu is None else torch.from_numpy(prelu).cuda(),
-                               p, actc, abi.PREC_3XTF32, packed=packed)
+                               p, actc, prec, packed=packed)
     torch.cuda.synchronize()
     assert abi.conv_tc_take_error() == 0
     err = relerr(out.cpu().numpy(), ref)
-    assert err < RTOL_FP32, err
-    # and it is much closer to fp32 than a single tf32 product would be (about 1e-3)
-    assert err < 2e-5
+    assert err < bound, err
+    assert err < tight, err
 
 
 def test_tensor_core_path_rejects_unsupported_shapes(abi):
@@ -194,7 +205,8 @@ def test_background_rows(abi):
     assert bg.cpu().tolist() == [1, -1, -1, 5]
 
 
-def test_split_k_matches_single_pass(abi, oracle):
+@pytest.mark.parametrize("precision", ["3XTF32", "3XBF16"])
+def test_split_k_matches_single_pass(abi, oracle, precision):
     """Layers with few output tiles split K over several CTAs; the partial sums are added in a
     fixed order, so repeated runs are bit-identical; split and unsplit kernels differ only by
     the accumulation order (K = 2048 here) and both stay within the 1e-4 bound of the oracle."""
@@ -203,11 +215,12 @@ def test_split_k_matches_single_pass(abi, oracle):
     feat = torch.from_numpy(rng.standard_normal((rows, K)).astype(np.float32)).cuda()
     W = torch.from_numpy((rng.standard_normal((K, N)) * 0.02).astype(np.float32)).cuda()
     B = torch.zeros(N, device="cuda")
-    packed = abi.pack_weights(W, abi.PREC_3XTF32)
-    assert abi.lib().scn_conv_nin_workspace_bytes(rows, 1, K, N, abi.PREC_3XTF32) > 0
-    a = abi.conv_nin_forward(feat, None, 1, W, B, precision=abi.PREC_3XTF32, packed=packed, split_k=True)
-    b = abi.conv_nin_forward(feat, None, 1, W, B, precision=abi.PREC_3XTF32, packed=packed, split_k=True)
-    c = abi.conv_nin_forward(feat, None, 1, W, B, precision=abi.PREC_3XTF32, packed=packed, split_k=False)
+    prec = getattr(abi, "PREC_" + precision)
+    packed = abi.pack_weights(W, prec)
+    assert abi.lib().scn_conv_nin_workspace_bytes(rows, 1, K, N, prec) > 0
+    a = abi.conv_nin_forward(feat, None, 1, W, B, precision=prec, packed=packed, split_k=True)
+    b = abi.conv_nin_forward(feat, None, 1, W, B, precision=prec, packed=packed, split_k=True)
+    c = abi.conv_nin_forward(feat, None, 1, W, B, precision=prec, packed=packed, split_k=False)
     torch.cuda.synchronize()
     assert abi.conv_tc_take_error() == 0
     assert torch.equal(a, b)

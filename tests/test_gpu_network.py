@@ -57,10 +57,15 @@ def test_deepcnet_builder_rounds_widths(scn, abi, oracle):
 
 
 @pytest.mark.parametrize("cfg", [1, 2, 3, 4, 5])
-@pytest.mark.parametrize("precision", ["fp32", "auto"])
+@pytest.mark.parametrize("precision", ["fp32", "auto", "3xtf32", "3xbf16", "bf16"])
 def test_forward_layer_by_layer(scn, abi, nets, cfg, precision):
+    """Rulebooks and grids bit-exact; features of every interface and the probabilities within 1e-4 of
+    the fp64-accumulating oracle for fp32 and the two split tensor-core precisions, within 2e-2 for the
+    optional plain-bf16 precision; top-1 agrees (bf16: at least 99.9 % over the batch)."""
     gnet, onet = nets(cfg)
-    gnet.set_precision(abi.PREC_FP32 if precision == "fp32" else abi.PREC_AUTO)
+    gnet.set_precision(dict(fp32=abi.PREC_FP32, auto=abi.PREC_AUTO, **{"3xtf32": abi.PREC_3XTF32, "3xbf16": abi.PREC_3XBF16},
+                            bf16=abi.PREC_BF16)[precision])
+    RTOL = 2e-2 if precision == "bf16" else 1e-4
     keys, off, feats = scn.synth.CONFIGS[cfg]["gen"](BATCH[cfg])
     oprobs, opred = onet.forward(keys, off, feats, accum64=True, keep=True)
     gprobs, gpred = gnet.forward_host(keys, off, feats)
@@ -83,7 +88,11 @@ def test_forward_layer_by_layer(scn, abi, nets, cfg, precision):
         o = onet.iface(i)
         assert relerr(g["features"], o["features"]) < RTOL, "features of interface %d" % i
     assert relerr(gprobs, oprobs) < RTOL
-    np.testing.assert_array_equal(gpred, opred)
+    if precision == "bf16":
+        assert (gpred == opred).mean() >= 0.999 or (gpred != opred).sum() <= 1  # small batches: at most one near-tie may flip
+    else:
+        np.testing.assert_array_equal(gpred, opred)
+    gnet.set_precision(abi.PREC_AUTO)
 
 
 @pytest.mark.parametrize("cfg", [1, 3, 4])
