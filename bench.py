@@ -244,13 +244,27 @@ def main():
         d_probs = torch.empty((BATCH_PER_GPU, nC), dtype=torch.float32, device=dev)
         d_top = torch.empty((BATCH_PER_GPU, 1), dtype=torch.int32, device=dev)
         gathered = torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32, device=dev)
+        # device leg at N > 1: the all-gather of step j overlaps the forward of step j + 1 (two buffer
+        # sets); step j + 1 ends only after the gather of step j has completed on its stream
+        d_probs2 = [torch.empty_like(d_probs) for _ in range(2)]
+        gathered2 = [torch.empty_like(gathered) for _ in range(2)]
+        pending = []
         h_gathered = torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32).pin_memory()
 
         def step_device(j):
             dk, do, db, df, ms = dev_batches[j % n_rot]
-            gnet.forward_device(dk, do, db, df, ms, d_probs, d_top)
-            if world > 1:
-                dist.all_gather_into_tensor(gathered, d_probs)
+            if world == 1:
+                gnet.forward_device(dk, do, db, df, ms, d_probs, d_top)
+                return
+            gnet.forward_device(dk, do, db, df, ms, d_probs2[j & 1], d_top)
+            work = dist.all_gather_into_tensor(gathered2[j & 1], d_probs2[j & 1], async_op=True)
+            while pending:
+                pending.pop().wait()  # the launching stream waits for the previous step's gather
+            pending.append(work)
+
+        def drain():
+            while pending:
+                pending.pop().wait()
 
         def step_host(j):
             keys, off, feats = host_batches[j % n_rot]
@@ -273,8 +287,16 @@ def main():
                 if with_layer_times:
                     t = gnet.layer_times()  # waits for the stream
                     layer_ms = t if layer_ms is None else layer_ms + t
+            tail = None
+            if pending:  # the last step's gather: timed after its step
+                tail = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                tail[0].record(stream)
+                drain()
+                tail[1].record(stream)
             stream.synchronize()
             ms = sum(a.elapsed_time(b) for a, b in ev)
+            if tail:
+                ms += tail[0].elapsed_time(tail[1])
             return ms, (layer_ms / steps if layer_ms is not None else None)
 
         def barrier():
@@ -288,6 +310,7 @@ def main():
         sampler.wait_first()
         for j in range(args.warmup):
             step_device(j)
+        drain()
         gnet.enable_timing(True)
         barrier()
         t_load0 = time.time()
@@ -308,8 +331,10 @@ def main():
         # untimed, until a handful of samples have been taken under this load.
         tail_ms, j = 0.0, 0
         t_tail = time.time()
+        # (no collective in here: every rank runs its own number of extra steps)
         while sampler.proc is not None and sampler.count_in(t_load0, time.time()) < 5 and time.time() - t_tail < 2.0:
-            step_device(j)
+            dk, do, db, df, ms = dev_batches[j % n_rot]
+            gnet.forward_device(dk, do, db, df, ms, d_probs, d_top)
             j += 1
         if j:
             stream.synchronize()
@@ -385,7 +410,7 @@ def main():
             metric=METRIC, value=total / (ms_dev * 1e-3), unit="samples/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
             ms_per_step=ms_dev / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
             dtype="f32" if args.precision == "fp32" else ("bf16" if args.precision == "bf16" else "tf32x3/f32"), data="synthetic",
-            config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample, all-gather of probabilities" % world,
+            config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample, all-gather of probabilities%s" % (world, " (step j's gather overlaps step j+1 in the device leg)" if world > 1 else ""),
                         l2="256 MiB written between timed steps; 2 distinct batches rotated", precision=args.precision,
                         timing="CUDA events per step on the launching stream, max over ranks; wall %.3f s for the device leg" % t_wall),
             e2e=dict(value=total / (ms_e2e * 1e-3), unit="samples/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
