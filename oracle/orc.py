@@ -21,6 +21,8 @@ c_int, c_ll, c_f, c_p, c_d = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ct
 NOSIGMOID, RELU, VLEAKYRELU, LEAKYRELU, TANH, SOFTMAX, PRELU, SIGMOID = range(8)
 # layer types of scn_oracle.cpp
 L_CONV, L_CONV_TRI, L_NIN, L_MAXPOOL, L_MAXPOOL_TRI, L_TERMINAL = range(6)
+# fractional max-pooling tick kinds: pseudorandom/random x overlapping/non-overlapping ("disjoint")
+FMP_PO, FMP_PD, FMP_RO, FMP_RD = range(4)
 
 
 def build(force=False):
@@ -28,7 +30,8 @@ def build(force=False):
     if force or not os.path.exists(ORACLE_SO) or os.path.getmtime(ORACLE_SO) < os.path.getmtime(
             os.path.join(HERE, "scn_oracle.cpp")):
         subprocess.check_call(["make", "-C", HERE, "oracle"], stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference/SparseConvNet") and (force or not os.path.exists(REF_SO)):
+    if os.path.isdir("/root/reference/SparseConvNet") and (force or not os.path.exists(REF_SO) or os.path.getmtime(REF_SO) < os.path.getmtime(
+            os.path.join(HERE, "ref_wrap.cpp"))):
         subprocess.check_call(["make", "-C", HERE, "_ref"], stdout=subprocess.DEVNULL)
 
 
@@ -63,6 +66,10 @@ class _RulesLib:
         L, pre = self.lib, self.pre
         h = getattr(L, pre + "_grid_rules")(kind, dim, nIn, nOut, size, stride, minActive, B,
                                             _p(keys), _p(rows), _p(off), _p(bg))
+        return self._fetch(h, B)
+
+    def _fetch(self, h, B):
+        L, pre = self.lib, self.pre
         nr = getattr(L, pre + "_result_n_rules")(h)
         no = getattr(L, pre + "_result_n_out")(h)
         ns = getattr(L, pre + "_result_n_sites")(h)
@@ -94,6 +101,18 @@ class Reference(_RulesLib):
         self.lib.ref_vectorTopIndices(_p(v), len(v), k, _p(out))
         return out
 
+    def fmp_rules(self, kind, dim, nIn, nOut, poolSize, seed, keys, rows, off, bg):
+        """One fractional max-pooling layer's preprocess over a batch with the layer RNG re-seeded
+        (kind: FMP_PO, FMP_PD, FMP_RO, FMP_RD) -> (result dict, ticks[batch, dim, 2*nOut + 2*nIn])."""
+        keys, rows = np.ascontiguousarray(keys, np.int64), np.ascontiguousarray(rows, np.int32)
+        off, bg = np.ascontiguousarray(off, np.int32), np.ascontiguousarray(bg, np.int32)
+        B = len(bg)
+        ticks = np.zeros((B, dim, 2 * nOut + 2 * nIn), np.int32)
+        f = self.lib.ref_fmp_rules
+        f.restype, f.argtypes = c_p, [c_int] * 5 + [ctypes.c_uint, c_int] + [c_p] * 5
+        h = f(kind, dim, nIn, nOut, poolSize, seed, B, _p(keys), _p(rows), _p(off), _p(bg), _p(ticks))
+        return self._fetch(h, B), ticks
+
 
 class Oracle(_RulesLib):
     def __init__(self):
@@ -123,6 +142,25 @@ class Oracle(_RulesLib):
         L.orc_net_forward.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p]
         L.orc_net_iface_sizes.argtypes = [c_p, c_int, c_p]
         L.orc_net_iface_fetch.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p]
+
+    # ---- fractional max-pooling
+    def fmp_ticks(self, kind, dim, nIn, nOut, poolSize, seed, count):
+        """Tick tables of `count` samples drawn from one RNG seeded with `seed`:
+        [count, dim, 2*nOut + 2*nIn] = inputL, inputR, outputL, outputR per sample and axis."""
+        out = np.zeros((count, dim, 2 * nOut + 2 * nIn), np.int32)
+        f = self.lib.orc_fmp_ticks
+        f.argtypes = [c_int] * 5 + [ctypes.c_uint, c_int, c_p]
+        f(kind, dim, nIn, nOut, poolSize, seed, count, _p(out))
+        return out
+
+    def fmp_rules(self, dim, nIn, nOut, poolSize, overlapping, ticks, keys, rows, off, bg):
+        keys, rows = np.ascontiguousarray(keys, np.int64), np.ascontiguousarray(rows, np.int32)
+        off, bg = np.ascontiguousarray(off, np.int32), np.ascontiguousarray(bg, np.int32)
+        ticks = np.ascontiguousarray(ticks, np.int32)
+        f = self.lib.orc_fmp_rules
+        f.restype, f.argtypes = c_p, [c_int] * 6 + [c_p] * 5
+        h = f(dim, nIn, nOut, poolSize, int(overlapping), len(bg), _p(ticks), _p(keys), _p(rows), _p(off), _p(bg))
+        return self._fetch(h, len(bg))
 
     # ---- layers
     def gather(self, feat, rules, nIn):

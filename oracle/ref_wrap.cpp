@@ -23,6 +23,17 @@ struct RefResult {
 };
 } // namespace
 
+template <class T>
+static void fmpSample(RNG &rng, int dim, int nIn, int nOut, int poolSize, bool uniform, SparseGrid &in, SparseGrid &out,
+                      RefResult *res, int *ticksOut) {
+  FractionalPoolingRegions<T> regions(nIn, nOut, dim, poolSize, rng);
+  for (int a = 0; a < dim; ++a) {
+    int *t = ticksOut + a * (2 * nOut + 2 * nIn);
+    for (int j = 0; j < nOut; ++j) { t[j] = regions.inputL(a, j); t[nOut + j] = regions.inputR(a, j); }
+    for (int i = 0; i < nIn; ++i) { t[2 * nOut + i] = regions.outputL(a, i); t[2 * nOut + nIn + i] = regions.outputR(a, i); }
+  }
+  gridRules(in, out, regions, res->nOutSites, res->rules, uniform);
+}
 extern "C" {
 
 // kind: 0 = RegularSquareRegions, 1 = RegularTriangularRegions.
@@ -45,6 +56,40 @@ void *ref_grid_rules(int kind, int dim, int nIn, int nOut, int size, int stride,
       RegularTriangularRegions regions(nIn, nOut, dim, size, stride);
       gridRules(in, out, regions, res->nOutSites, res->rules, minActive);
     }
+    for (auto it = out.mp.begin(); it != out.mp.end(); ++it) {
+      res->outKeys.push_back((int64_t)it->first);
+      res->outRows.push_back(it->second);
+    }
+    res->outOff.push_back((int)res->outKeys.size());
+    res->outBg.push_back(out.backgroundCol);
+  }
+  return res;
+}
+
+// Fractional max-pooling rules as the four FMP layers' preprocess() builds them
+// (MaxPoolingLayer.cu:171-186, 232-247, 293-308, 354-369): one RNG per layer, per sample a fresh
+// FractionalPoolingRegions<ticks> (one ticks object per axis) and gridRules with uniformSizeRegions
+// = true for the overlapping kinds, false for the non-overlapping ones.  The reference seeds the
+// RNG from the clock; here rng.gen is re-seeded so that the draw sequence can be repeated.
+// kind: 0 pseudorandom overlapping, 1 pseudorandom non-overlapping, 2 random overlapping,
+// 3 random non-overlapping.  ticksOut[(b*dim + axis) * (2*nOut + 2*nIn)] receives
+// inputL[nOut], inputR[nOut], outputL[nIn], outputR[nIn] of every sample and axis.
+void *ref_fmp_rules(int kind, int dim, int nIn, int nOut, int poolSize, unsigned seed, int batch, const int64_t *inKeys,
+                    const int *inRows, const int *inOff, const int *inBg, int *ticksOut) {
+  RefResult *res = new RefResult();
+  res->outOff.push_back(0);
+  RNG rng;
+  rng.gen.seed(seed);
+  for (int b = 0; b < batch; ++b) {
+    SparseGrid in, out;
+    in.backgroundCol = inBg[b];
+    for (int i = inOff[b]; i < inOff[b + 1]; ++i)
+      in.mp[inKeys[i]] = inRows[i];
+    int *t = ticksOut + (size_t)b * dim * (2 * nOut + 2 * nIn);
+    if (kind == 0) fmpSample<PseudorandomOverlappingFmpTicks>(rng, dim, nIn, nOut, poolSize, true, in, out, res, t);
+    else if (kind == 1) fmpSample<PseudorandomNonOverlappingFmpTicks>(rng, dim, nIn, nOut, poolSize, false, in, out, res, t);
+    else if (kind == 2) fmpSample<RandomOverlappingFmpTicks>(rng, dim, nIn, nOut, poolSize, true, in, out, res, t);
+    else fmpSample<RandomNonOverlappingFmpTicks>(rng, dim, nIn, nOut, poolSize, false, in, out, res, t);
     for (auto it = out.mp.begin(); it != out.mp.end(); ++it) {
       res->outKeys.push_back((int64_t)it->first);
       res->outRows.push_back(it->second);

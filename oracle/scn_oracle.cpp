@@ -12,6 +12,7 @@
 //     follow the reference source line by line in meaning (citations below).
 //
 // All citations are paths inside the reference project (SparseConvNet/...).
+#include <random>
 #include <algorithm>
 #include <chrono>
 #include <cmath>
@@ -175,6 +176,93 @@ static void gridRules(const Grid &in, Grid &out, const Regions &R, int &nOutSite
   out.bg = -1;
   if ((long long)outSites.size() < R.fullSize()) { // e.g. Regions.cu:647-652
     for (int c = 0; c < R.sd; ++c) rules.push_back(in.bg);
+    out.bg = nOutSites++;
+  }
+}
+
+// ------------------------------------------------------------------ fractional max-pooling
+// The reference's RNG (Rng.h, Rng.cpp:16-21, 59-61): a std::mt19937 behind a double-valued
+// uniform_real_distribution whose result passes through float, and std::shuffle.
+struct FmpRng {
+  std::mt19937 gen;
+  std::uniform_real_distribution<> uniform01{0, 1};
+  float uniform(float a = 0, float b = 1) { return a + (b - a) * uniform01(gen); }
+};
+// FractionalMaxPoolingTicks of one axis (Regions.h:48-54).  kind: 0 pseudorandom overlapping
+// (Regions.cu:31-52), 1 pseudorandom non-overlapping (54-74), 2 random overlapping (76-100),
+// 3 random non-overlapping (102-125).
+struct Ticks { std::vector<int> inputL, inputR, outputL, outputR; };
+static Ticks makeTicks(int kind, int nIn, int nOut, int poolSize, FmpRng &rng) {
+  Ticks t;
+  if (kind == 0 || kind == 1) {
+    const double alpha = kind == 0 ? (nIn - poolSize) * 1.0 / (nOut - 1) : nIn * 1.0 / nOut;
+    const double u = rng.uniform(0, 1);
+    for (int j = 0; j < nOut; ++j) {
+      const int i = (int)((j + u) * alpha) - (int)(u * alpha);
+      t.inputL.push_back(i);
+      t.inputR.push_back(kind == 0 ? i + poolSize : (int)((j + 1 + u) * alpha) - (int)(u * alpha));
+    }
+  } else {
+    const int alpha = (int)(nIn * 1.0 / nOut);
+    std::vector<int> inc;
+    inc.resize(nOut * (alpha + 1) - nIn, alpha);
+    inc.resize(kind == 2 ? nOut - 1 : nOut, alpha + 1);
+    std::shuffle(inc.begin(), inc.end(), rng.gen);
+    t.inputL.push_back(0);
+    t.inputR.push_back(kind == 2 ? poolSize : inc[0]);
+    for (int i = 0; i < nOut - 1; ++i) {
+      t.inputL.push_back(t.inputL.back() + inc[i]);
+      t.inputR.push_back(kind == 2 ? t.inputL.back() + poolSize : t.inputR.back() + inc[i + 1]);
+    }
+  }
+  t.outputL.assign(nIn, nOut);
+  t.outputR.assign(nIn, 0);
+  for (int i = 0; i < nOut; ++i)
+    for (int j = t.inputL[i]; j < t.inputR[i] && j < nIn; ++j) {
+      t.outputL[j] = std::min(t.outputL[j], i);
+      t.outputR[j] = std::max(t.outputR[j], i + 1);
+    }
+  return t;
+}
+// gridRules with tick tables: gridRulesOverlappingNoMin (Regions.cu:528-653) when overlapping,
+// gridRulesNonOverlapping (159-336) otherwise; the two differ in what a new rule row holds outside
+// the (variable-size) pooling region: the background row, or -1.
+static void gridRulesFmp(const Grid &in, Grid &out, const Ticks *pb, int dim, int nIn, int nOut, int s, bool overlapping,
+                         int &nOutSites, std::vector<int> &rules) {
+  const int sd = ipow(s, dim);
+  std::unordered_map<int64_t, int> created;
+  std::vector<std::pair<int64_t, int>> outSites;
+  int i[4], lo[4], hi[4];
+  for (auto &site : in.sites) {
+    decode(site.first, nIn, dim, i);
+    for (int a = 0; a < dim; ++a) { lo[a] = pb[a].outputL[i[a]]; hi[a] = pb[a].outputR[i[a]]; }
+    forBox(dim, lo, hi, [&](const int *j) {
+      const int64_t outKey = encode(j, nOut, dim);
+      auto f = created.find(outKey);
+      if (f == created.end()) {
+        f = created.emplace(outKey, nOutSites++).first;
+        outSites.emplace_back(outKey, f->second);
+        rules.resize((size_t)nOutSites * sd, overlapping ? in.bg : -1);
+        if (!overlapping) { // Regions.cu:206-215: the cells of this site's own region start as background
+          int zero[4] = {0, 0, 0, 0}, ext[4];
+          for (int a = 0; a < dim; ++a) ext[a] = pb[a].inputR[j[a]] - pb[a].inputL[j[a]];
+          forBox(dim, zero, ext, [&](const int *cc) {
+            int k = 0;
+            for (int a = 0; a < dim; ++a) k = k * s + cc[a];
+            rules[(size_t)f->second * sd + k] = in.bg;
+          });
+        }
+      }
+      int off = 0;
+      for (int a = 0; a < dim; ++a) off = off * s + (i[a] - pb[a].inputL[j[a]]);
+      rules[(size_t)f->second * sd + off] = site.second;
+    });
+  }
+  std::sort(outSites.begin(), outSites.end());
+  out.sites = outSites;
+  out.bg = -1;
+  if ((long long)outSites.size() < ipow(nOut, dim)) { // Regions.cu:330-335, 647-652
+    for (int c = 0; c < sd; ++c) rules.push_back(in.bg);
     out.bg = nOutSites++;
   }
 }
@@ -473,6 +561,47 @@ void *orc_grid_rules(int kind, int dim, int nIn, int nOut, int size, int stride,
     Grid out;
     if (kind == 2) terminalRules(in[b], out, (int)S, res->nOutSites, res->rules);
     else { Regions R(kind, dim, nIn, nOut, size, stride); gridRules(in[b], out, R, res->nOutSites, res->rules, minActive); }
+    for (auto &s : out.sites) { res->outKeys.push_back(s.first); res->outRows.push_back(s.second); }
+    res->outOff.push_back((int)res->outKeys.size());
+    res->outBg.push_back(out.bg);
+  }
+  return res;
+}
+// Tick tables of `count` consecutive FractionalPoolingRegions<ticks> objects drawn from one RNG
+// seeded with `seed` (one per sample, one ticks object per axis, in that order):
+// out[(b*dim + axis) * (2*nOut + 2*nIn)] = inputL[nOut], inputR[nOut], outputL[nIn], outputR[nIn].
+void orc_fmp_ticks(int kind, int dim, int nIn, int nOut, int poolSize, unsigned seed, int count, int *out) {
+  FmpRng rng;
+  rng.gen.seed(seed);
+  const int stride = 2 * nOut + 2 * nIn;
+  for (int b = 0; b < count; ++b)
+    for (int a = 0; a < dim; ++a) {
+      Ticks t = makeTicks(kind, nIn, nOut, poolSize, rng);
+      int *o = out + ((size_t)b * dim + a) * stride;
+      std::copy(t.inputL.begin(), t.inputL.end(), o);
+      std::copy(t.inputR.begin(), t.inputR.end(), o + nOut);
+      std::copy(t.outputL.begin(), t.outputL.end(), o + 2 * nOut);
+      std::copy(t.outputR.begin(), t.outputR.end(), o + 2 * nOut + nIn);
+    }
+}
+// Rules of one FMP layer from given tick tables (same flat protocol as orc_grid_rules).
+void *orc_fmp_rules(int dim, int nIn, int nOut, int poolSize, int overlapping, int batch, const int *ticks,
+                    const int64_t *inKeys, const int *inRows, const int *inOff, const int *inBg) {
+  OrcRules *res = new OrcRules();
+  res->outOff.push_back(0);
+  const int stride = 2 * nOut + 2 * nIn;
+  for (int b = 0; b < batch; ++b) {
+    Grid in, out;
+    in.bg = inBg[b];
+    for (int i = inOff[b]; i < inOff[b + 1]; ++i) in.sites.emplace_back(inKeys[i], inRows[i]);
+    std::sort(in.sites.begin(), in.sites.end());
+    Ticks pb[4];
+    for (int a = 0; a < dim; ++a) {
+      const int *o = ticks + ((size_t)b * dim + a) * stride;
+      pb[a].inputL.assign(o, o + nOut); pb[a].inputR.assign(o + nOut, o + 2 * nOut);
+      pb[a].outputL.assign(o + 2 * nOut, o + 2 * nOut + nIn); pb[a].outputR.assign(o + 2 * nOut + nIn, o + stride);
+    }
+    gridRulesFmp(in, out, pb, dim, nIn, nOut, poolSize, overlapping != 0, res->nOutSites, res->rules);
     for (auto &s : out.sites) { res->outKeys.push_back(s.first); res->outRows.push_back(s.second); }
     res->outOff.push_back((int)res->outKeys.size());
     res->outBg.push_back(out.bg);

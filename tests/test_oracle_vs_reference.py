@@ -95,3 +95,30 @@ def test_chain_matches_reference(oracle, reference):
             cur_o = (a["out_keys"], a["out_rows"], a["out_off"], a["out_bg"])
             cur_r = (b["out_keys"], b["out_rows"], b["out_off"], b["out_bg"])
             n = nOut
+
+
+# Fractional max-pooling (MaxPoolingLayer.cu:157-407): (kind, dim, nOut, shrink); poolSize 2 as in the
+# named FMP architectures; nIn as the layers' calculateInputSpatialSize derives it.
+FMP = [(k, d, n, s) for k in range(4) for d, n, s in [(1, 7, 1.414), (2, 5, 1.26), (2, 6, 1.5), (2, 9, 1.7), (3, 4, 1.414), (3, 5, 1.26)]]
+# 4-D only for the non-overlapping kinds: the reference's 4-D gridRulesOverlappingNoMin starts axis 0 at
+# outputL(0, i1) (Regions.cu:613), which indexes outside its rule rows
+FMP += [(1, 4, 3, 1.5), (3, 4, 3, 1.5), (1, 2, 10, 2.0)]
+
+
+def fmp_nin(nOut, shrink):
+    nIn = int(nOut * np.float32(shrink) + 0.5)
+    return nIn + 1 if nIn == nOut else nIn
+
+
+@pytest.mark.parametrize("kind,dim,nOut,shrink", FMP)
+def test_fmp_ticks_and_rules(oracle, reference, kind, dim, nOut, shrink):
+    """The tick tables (the reference's RNG draw by draw) and both FMP rule builders."""
+    nIn = fmp_nin(nOut, shrink)
+    rng = np.random.default_rng(31 * kind + 7 * dim + nOut)
+    for density in (0.0, 0.1, 0.5, 1.0):
+        for with_bg in (True, False):
+            seed = int(rng.integers(1, 2 ** 31))
+            g = random_grids(rng, 4, dim, nIn, density, with_bg=with_bg, first_row=int(rng.integers(0, 5)))
+            ref, ticks = reference.fmp_rules(kind, dim, nIn, nOut, 2, seed, *g)
+            np.testing.assert_array_equal(oracle.fmp_ticks(kind, dim, nIn, nOut, 2, seed, 4), ticks)
+            same(oracle.fmp_rules(dim, nIn, nOut, 2, kind in (0, 2), ticks, *g), ref)
