@@ -107,6 +107,20 @@ int scn_rules_build(const scn_regions_t *r, int batch, const int *d_in_keys, con
                     int *d_out_bg, int *d_rules, int rows_out_capacity, int *d_result,
                     void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
 
+/* Rules of a fractional max-pooling layer: FractionalPoolingRegions<ticks> (Regions.cu:127-157)
+ * with gridRulesOverlappingNoMin (528-653) for the overlapping kinds and gridRulesNonOverlapping
+ * (159-336) for the others, as the four FMP layers' preprocess() call them
+ * (MaxPoolingLayer.cu:171-186, 232-247, 293-308, 354-369).  The tick tables are drawn on the host
+ * (one FractionalPoolingRegions per sample, one ticks object per axis) and passed as
+ * d_ticks[(b*dim + axis) * (2*nOut + 2*nIn)] = inputL[nOut], inputR[nOut], outputL[nIn], outputR[nIn].
+ * Rule rows have poolSize^dim cells; in the non-overlapping case cells beyond a region hold -1.
+ * All other arguments as scn_rules_build. */
+size_t scn_fmp_rules_workspace_bytes(int dim, int nIn, int nOut, int poolSize, int batch, int rows_in_bound);
+int scn_fmp_rules_build(int dim, int nIn, int nOut, int poolSize, int overlapping, int batch, const int *d_ticks,
+                        const int *d_in_keys, const int *d_in_off, const int *d_in_bg, int rows_in_bound,
+                        int *d_out_keys, int *d_out_off, int *d_out_bg, int *d_rules, int rows_out_capacity,
+                        int *d_result, void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
+
 /* Replaces the loop "for every layer: layer->preprocess(batch, in, out)" of
  * BatchProducer::preprocessBatch (BatchProducer.cu:72-75) for the geometry layers
  * (convolutions and poolings, in network order) with ONE kernel: each sample's whole chain

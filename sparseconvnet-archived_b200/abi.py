@@ -19,7 +19,7 @@ DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
 
 EXPORTS = [
     "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
-    "scn_rules_workspace_bytes", "scn_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_terminal_rules_workspace_bytes",
+    "scn_rules_workspace_bytes", "scn_rules_build", "scn_fmp_rules_workspace_bytes", "scn_fmp_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_terminal_rules_workspace_bytes",
     "scn_terminal_rules_build", "scn_conv_auto_precision", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
@@ -59,6 +59,9 @@ def lib():
         L.scn_rules_workspace_bytes.restype = c_sz
         L.scn_rules_workspace_bytes.argtypes = [c_p, c_int, c_int]
         L.scn_rules_build.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_p, c_p, c_sz, c_p]
+        L.scn_fmp_rules_workspace_bytes.restype = c_sz
+        L.scn_fmp_rules_workspace_bytes.argtypes = [c_int] * 6
+        L.scn_fmp_rules_build.argtypes = [c_int] * 6 + [c_p, c_p, c_p, c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_p, c_p, c_sz, c_p]
         L.scn_rules_static_scratch_bytes.restype = c_sz
         L.scn_rules_build_static.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_p, c_p]
         L.scn_rules_chain_workspace_bytes.restype = c_sz
@@ -133,6 +136,25 @@ def rules_build(R, keys, off, bg, rows_out_capacity, rows_in_bound=None):
     check(L.scn_rules_build(ctypes.byref(R), batch, _ptr(_i32(keys)), _ptr(_i32(off)), _ptr(_i32(bg)), rows_in_bound,
                             _ptr(out_keys), _ptr(out_off), _ptr(out_bg), _ptr(rules), rows_out_capacity, _ptr(result),
                             _ptr(ws), ws_bytes, _stream()))
+    return dict(out_keys=out_keys, out_off=out_off, out_bg=out_bg, rules=rules, result=result, sd=sd, workspace=ws)
+
+
+def fmp_rules_build(dim, nIn, nOut, poolSize, overlapping, ticks, keys, off, bg, rows_out_capacity):
+    """scn_fmp_rules_build: ticks is an int32 CUDA tensor [batch, dim, 2*nOut + 2*nIn]."""
+    L = lib()
+    batch = bg.numel()
+    dev = keys.device
+    sd = poolSize ** dim
+    ws_bytes = L.scn_fmp_rules_workspace_bytes(dim, nIn, nOut, poolSize, batch, keys.numel())
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+    out_keys = torch.empty(max(rows_out_capacity, 1), dtype=torch.int32, device=dev)
+    out_off = torch.empty(batch + 1, dtype=torch.int32, device=dev)
+    out_bg = torch.empty(batch, dtype=torch.int32, device=dev)
+    rules = torch.empty(max(rows_out_capacity, 1) * sd, dtype=torch.int32, device=dev)
+    result = torch.empty(4, dtype=torch.int32, device=dev)
+    check(L.scn_fmp_rules_build(dim, nIn, nOut, poolSize, int(overlapping), batch, _ptr(_i32(ticks)), _ptr(_i32(keys)), _ptr(_i32(off)),
+                                _ptr(_i32(bg)), keys.numel(), _ptr(out_keys), _ptr(out_off), _ptr(out_bg), _ptr(rules),
+                                rows_out_capacity, _ptr(result), _ptr(ws), ws_bytes, _stream()))
     return dict(out_keys=out_keys, out_off=out_off, out_bg=out_bg, rules=rules, result=result, sd=sd, workspace=ws)
 
 

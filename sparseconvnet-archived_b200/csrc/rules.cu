@@ -34,7 +34,15 @@ struct Regions {
   float rNIn, rNOut, rSize, rSd, rT, rTax, rStride; // reciprocals for the float-assisted divisions below
   signed char ord[MAX_CUBE];         // cube cell -> rule column, -1 outside a triangular filter
   unsigned char cellOfCol[MAX_CUBE]; // rule column -> cube cell
+  // Fractional max-pooling (FractionalPoolingRegions, Regions.cu:127-157): region bounds come from per
+  // sample, per axis tick tables instead of size/stride.  fmp: 0 regular regions, 1 overlapping
+  // (every region spans `size` cells per axis), 2 non-overlapping (regions of size-1 or size cells;
+  // rule cells outside a region hold -1, Regions.cu:201-215).
+  int fmp, tickStride;
+  const int *ticks; // [(b*dim + axis) * tickStride]: inputL[nOut], inputR[nOut], outputL[nIn], outputR[nIn]
 };
+
+__device__ __forceinline__ const int *tick_axis(const Regions &R, int b, int a) { return R.ticks + ((size_t)b * R.dim + a) * R.tickStride; }
 
 __host__ __device__ inline long long ipowll(long long b, int e) {
   long long r = 1;
@@ -118,7 +126,16 @@ __device__ __forceinline__ int cell_rank(const uint2 *__restrict__ d, int key) {
 
 // Output coordinates of the t-th output site input site i can touch (mixed radix over the
 // axes, so ascending t = ascending output key); false if t names none.
-__device__ __forceinline__ bool touched_output(const Regions &R, const int *i, int t, int *j) {
+__device__ __forceinline__ bool touched_output(const Regions &R, int b, const int *i, int t, int *j) {
+  if (R.fmp) { // outputL/outputR tables (Regions.cu:45-51)
+    for (int a = R.dim - 1; a >= 0; --a) {
+      const int ta = t % R.Tax; t /= R.Tax;
+      const int *tk = tick_axis(R, b, a) + 2 * R.nOut;
+      j[a] = __ldg(tk + i[a]) + ta;
+      if (j[a] >= __ldg(tk + R.nIn + i[a])) return false;
+    }
+    return true;
+  }
   if (R.minActive == -1) { // 'valid': the site centred on i (Regions.cu:691-696)
     bool ok = true;
     for (int a = 0; a < R.dim; ++a) { ok = ok && i[a] >= 1 && i[a] <= R.nOut; j[a] = i[a] - 1; }
@@ -139,10 +156,27 @@ __device__ __forceinline__ bool touched_output(const Regions &R, const int *i, i
 
 // Does input site i (active) create output site j: is i the first active cell of j's cube
 // field in lexicographic (= key) order, and does the field hold enough active inputs?
-__device__ bool creates(const Regions &R, const uint2 *__restrict__ d, const int *i, const int *j) {
+__device__ bool creates(const Regions &R, int b, const uint2 *__restrict__ d, const int *i, const int *j) {
   if (R.minActive == -1) return true;
   int cc[4] = {0, 0, 0, 0}, ii[4];
   int active = 0;
+  if (R.fmp) { // the field of j is [inputL(j), inputR(j)) per axis; first active cell in key order wins
+    int lo[4], ext[4];
+    for (int a = 0; a < R.dim; ++a) {
+      const int *tk = tick_axis(R, b, a);
+      lo[a] = __ldg(tk + j[a]);
+      ext[a] = __ldg(tk + R.nOut + j[a]) - lo[a];
+    }
+    for (;;) {
+      bool self = true;
+      for (int a = 0; a < R.dim; ++a) { ii[a] = lo[a] + cc[a]; self = self && ii[a] == i[a]; }
+      if (self) return true;
+      if (cell_active(d, encode(ii, R.nIn, R.dim))) return false;
+      int a = R.dim - 1;
+      while (a >= 0 && ++cc[a] >= ext[a]) { cc[a] = 0; --a; }
+      if (a < 0) return false;
+    }
+  }
   for (int cell = 0; cell < R.cube; ++cell) {
     bool self = true;
     for (int a = 0; a < R.dim; ++a) { ii[a] = j[a] * R.stride + cc[a]; self = self && ii[a] == i[a]; }
@@ -253,7 +287,7 @@ __global__ void k_flags(Regions R, int batch, const int *__restrict__ keys, cons
     decode(key, R.nIn, R.dim, i);
     int c = 0;
     for (int t = 0; t < R.T; ++t) {
-      bool f = touched_output(R, i, t, j) && creates(R, d, i, j);
+      bool f = touched_output(R, b, i, t, j) && creates(R, b, d, i, j);
       flags[(size_t)slot * R.T + t] = f;
       c += f;
     }
@@ -382,7 +416,7 @@ __global__ void k_assign(Regions R, int batch, const int *__restrict__ keys, con
     if (outRow >= capacity) continue;
     int i[4], j[4];
     decode(keys[sortedRow[slot]], R.nIn, R.dim, i);
-    touched_output(R, i, t, j);
+    touched_output(R, b, i, t, j);
     outKeys[outRow] = encode(j, R.nOut, R.dim);
   }
 }
@@ -402,11 +436,24 @@ __global__ void k_fill(Regions R, int batch, const int *__restrict__ inOff, cons
       int j[4], cc[4], ii[4];
       decode(key, R.nOut, R.dim, j);
       decode(R.cellOfCol[col], R.size, R.dim, cc);
-      for (int a = 0; a < R.dim; ++a) ii[a] = j[a] * R.stride + cc[a];
-      int ck = encode(ii, R.nIn, R.dim);
-      const uint2 *d = dir + (size_t)b * R.W;
-      uint2 e = d[ck >> 5];
-      if ((e.x >> (ck & 31)) & 1u) v = sortedRow[inOff[b] + e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
+      bool inside = true;
+      if (R.fmp) {
+        for (int a = 0; a < R.dim; ++a) {
+          const int *tk = tick_axis(R, b, a);
+          const int lo = __ldg(tk + j[a]);
+          ii[a] = lo + cc[a];
+          inside = inside && ii[a] < __ldg(tk + R.nOut + j[a]);
+        }
+      } else {
+        for (int a = 0; a < R.dim; ++a) ii[a] = j[a] * R.stride + cc[a];
+      }
+      if (!inside) v = -1; // a cell beyond a short non-overlapping region (Regions.cu:201-203)
+      else {
+        int ck = encode(ii, R.nIn, R.dim);
+        const uint2 *d = dir + (size_t)b * R.W;
+        uint2 e = d[ck >> 5];
+        if ((e.x >> (ck & 31)) & 1u) v = sortedRow[inOff[b] + e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
+      }
     }
     rules[q] = v;
   }
@@ -525,6 +572,7 @@ int make_regions(const scn_regions_t *r, Regions *out) {
   Regions R;
   R.lattice = r->lattice; R.dim = r->dim; R.nIn = r->nIn; R.nOut = r->nOut;
   R.size = r->size; R.stride = r->stride; R.minActive = r->minActive;
+  R.fmp = 0; R.tickStride = 0; R.ticks = nullptr;
   if (R.lattice != SCN_LATTICE_SQUARE && R.lattice != SCN_LATTICE_TRIANGULAR) return fail(SCN_ERR_INVALID, "unknown lattice");
   if (R.dim < 1 || R.dim > 4) return fail(SCN_ERR_INVALID, "dimension must be 1..4");
   if (R.size < 1 || R.stride < 1 || R.nOut < 1) return fail(SCN_ERR_INVALID, "size, stride and nOut must be positive");
@@ -823,6 +871,10 @@ extern "C" size_t scn_rules_workspace_bytes(const scn_regions_t *r, int batch, i
   return carve(nullptr, batch, R.W, rows_in_bound, R.T).bytes;
 }
 
+static int run_rules(const Regions &R, int batch, const int *d_in_keys, const int *d_in_off, const int *d_in_bg, int rows_in_bound,
+                     int *d_out_keys, int *d_out_off, int *d_out_bg, int *d_rules, int rows_out_capacity, int *d_result,
+                     void *d_workspace, size_t workspace_bytes, scn_stream_t stream_);
+
 extern "C" int scn_rules_build(const scn_regions_t *r, int batch, const int *d_in_keys, const int *d_in_off,
                                const int *d_in_bg, int rows_in_bound, int *d_out_keys, int *d_out_off,
                                int *d_out_bg, int *d_rules, int rows_out_capacity, int *d_result,
@@ -831,6 +883,52 @@ extern "C" int scn_rules_build(const scn_regions_t *r, int batch, const int *d_i
   Regions R;
   int st = make_regions(r, &R);
   if (st != SCN_OK) return st;
+  return run_rules(R, batch, d_in_keys, d_in_off, d_in_bg, rows_in_bound, d_out_keys, d_out_off, d_out_bg, d_rules, rows_out_capacity,
+                   d_result, d_workspace, workspace_bytes, stream_);
+}
+
+// Regions of one fractional max-pooling layer: a square lattice whose `size` is the pool size; every
+// input coordinate lies in at most `size` regions per axis.
+static int make_fmp_regions(int dim, int nIn, int nOut, int poolSize, int overlapping, const int *d_ticks, Regions *out) {
+  if (dim < 1 || dim > 4 || poolSize < 1 || nOut < 1) return fail(SCN_ERR_INVALID, "bad fractional pooling geometry");
+  // the asserts of the tick constructors (Regions.cu:35, 58, 78, 104)
+  if (nIn < nOut - 1 + poolSize || nIn <= nOut) return fail(SCN_ERR_INVALID, "fractional pooling needs nIn > nOut and nIn >= nOut - 1 + poolSize");
+  scn_regions_t r = {SCN_LATTICE_SQUARE, dim, poolSize, 1, poolSize, 1, 1}; // a one-site stand-in for the shared bookkeeping
+  Regions R;
+  int st = make_regions(&r, &R);
+  if (st != SCN_OK) return st;
+  const long long cells = ipowll(nIn, dim), full = ipowll(nOut, dim);
+  if (cells >= (1ll << 31)) return fail(SCN_ERR_UNSUPPORTED, "nIn^dim must be below 2^31");
+  R.nIn = nIn; R.nOut = nOut; R.cells = (int)cells; R.W = (int)((cells + 31) / 32); R.fullSize = (int)full;
+  R.Tax = poolSize; R.T = R.cube;
+  R.rNIn = 1.0f / nIn; R.rNOut = 1.0f / nOut; R.rT = 1.0f / R.T; R.rTax = 1.0f / R.Tax;
+  R.fmp = overlapping ? 1 : 2; R.tickStride = 2 * nOut + 2 * nIn; R.ticks = d_ticks;
+  *out = R;
+  return SCN_OK;
+}
+
+extern "C" size_t scn_fmp_rules_workspace_bytes(int dim, int nIn, int nOut, int poolSize, int batch, int rows_in_bound) {
+  Regions R;
+  if (batch < 0 || rows_in_bound < 0 || make_fmp_regions(dim, nIn, nOut, poolSize, 1, nullptr, &R) != SCN_OK) return 0;
+  return carve(nullptr, batch, R.W, rows_in_bound, R.T).bytes;
+}
+
+extern "C" int scn_fmp_rules_build(int dim, int nIn, int nOut, int poolSize, int overlapping, int batch, const int *d_ticks,
+                                   const int *d_in_keys, const int *d_in_off, const int *d_in_bg, int rows_in_bound,
+                                   int *d_out_keys, int *d_out_off, int *d_out_bg, int *d_rules, int rows_out_capacity,
+                                   int *d_result, void *d_workspace, size_t workspace_bytes, scn_stream_t stream_) {
+  clear_error();
+  Regions R;
+  int st = make_fmp_regions(dim, nIn, nOut, poolSize, overlapping, d_ticks, &R);
+  if (st != SCN_OK) return st;
+  if (!d_ticks) return fail(SCN_ERR_INVALID, "null pointer");
+  return run_rules(R, batch, d_in_keys, d_in_off, d_in_bg, rows_in_bound, d_out_keys, d_out_off, d_out_bg, d_rules, rows_out_capacity,
+                   d_result, d_workspace, workspace_bytes, stream_);
+}
+
+static int run_rules(const Regions &R, int batch, const int *d_in_keys, const int *d_in_off, const int *d_in_bg, int rows_in_bound,
+                     int *d_out_keys, int *d_out_off, int *d_out_bg, int *d_rules, int rows_out_capacity, int *d_result,
+                     void *d_workspace, size_t workspace_bytes, scn_stream_t stream_) {
   if (batch < 1 || rows_in_bound < 0 || rows_out_capacity < 0) return fail(SCN_ERR_INVALID, "bad batch/row counts");
   if ((!d_in_keys && rows_in_bound > 0) || !d_in_off || !d_in_bg || !d_out_keys || !d_out_off || !d_out_bg || !d_rules || !d_result || !d_workspace)
     return fail(SCN_ERR_INVALID, "null pointer");
@@ -848,7 +946,7 @@ extern "C" int scn_rules_build(const scn_regions_t *r, int batch, const int *d_i
   SCN_LAUNCH_CHECK("k_mark");
   k_rank<<<batch < sm_count() * 4 ? batch : sm_count() * 4, 256, 0, s>>>(R, batch, w.dir, w.nSites);
   SCN_LAUNCH_CHECK("k_rank");
-  const bool fast = R.cells < (1 << 24); // float-assisted coordinate arithmetic is exact below 2^24
+  const bool fast = R.cells < (1 << 24) && !R.fmp; // float-assisted coordinate arithmetic is exact below 2^24
 #define SCN_DIM_DISPATCH(KERNEL, GRID, BLOCK, ...)                                                       \
   switch (R.dim) {                                                                                       \
   case 1: KERNEL<1><<<GRID, BLOCK, 0, s>>>(__VA_ARGS__); break;                                          \

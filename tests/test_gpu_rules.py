@@ -258,3 +258,28 @@ def test_fused_chain_row_hint(abi, oracle):
     small = abi.rules_chain_build(regs, dk, doff, dbg, max_rows, caps, rows_hint=max_rows + 1)
     torch.cuda.synchronize()
     assert int(small[0]["result"][2]) & abi.DEV_ERR_CAPACITY
+
+
+# Fractional max-pooling: (kind, dim, nOut, shrink), pool size 2; kinds 0/2 overlap, 1/3 do not.
+FMP = [(k, d, n, s) for k in range(4) for d, n, s in [(1, 7, 1.414), (2, 5, 1.26), (2, 9, 1.7), (2, 24, 1.414), (3, 5, 1.26), (3, 12, 1.5)]]
+FMP += [(1, 4, 3, 1.5), (3, 4, 3, 1.5), (0, 4, 3, 1.5)]
+
+
+@pytest.mark.parametrize("kind,dim,nOut,shrink", FMP)
+def test_fmp_rules(abi, oracle, kind, dim, nOut, shrink):
+    """scn_fmp_rules_build against the oracle's restatement of the four FMP layers' preprocess, on the
+    same tick tables (drawn by the oracle from a seeded copy of the reference's RNG)."""
+    nIn = int(nOut * np.float32(shrink) + 0.5)
+    nIn = nIn + 1 if nIn == nOut else nIn
+    rng = np.random.default_rng(500 + 31 * kind + 7 * dim + nOut)
+    for density in (0.0, 0.05, 0.4, 1.0):
+        for with_bg in (True, False):
+            g = random_grids(rng, 5, dim, nIn, density, with_bg=with_bg)
+            ticks = oracle.fmp_ticks(kind, dim, nIn, nOut, 2, int(rng.integers(1, 2 ** 31)), 5)
+            ref = oracle.fmp_rules(dim, nIn, nOut, 2, kind in (0, 2), ticks, *g)
+            dk, doff, dbg, first = to_dev_grid(*g)
+            assert first == 0
+            cap = dk.numel() * 2 ** dim + len(g[3]) + 8
+            out = abi.fmp_rules_build(dim, nIn, nOut, 2, kind in (0, 2), torch.from_numpy(ticks).cuda(), dk, doff, dbg, cap)
+            torch.cuda.synchronize()
+            compare(out, out["result"].cpu().numpy(), ref)
