@@ -31,6 +31,13 @@ void scn_net_destroy(scn_net_t *net);
 int scn_net_addLeNetLayerMP(scn_net_t *net, int nFeatures, int filterSize, int filterStride, int poolSize, int poolStride,
                             int activationFn, float dropout, int minActiveInputs);
 /* SparseConvNet::addTerminalPoolingLayer (SparseConvNet.cu:56-58, 123-126). */
+/* SparseConvNet::addLeNetLayer{PO,PD,RO,RD}FMP (SparseConvNet.h:32-47): kind 0 pseudorandom overlapping,
+ * 1 pseudorandom non-overlapping, 2 random overlapping, 3 random non-overlapping. */
+int scn_net_addLeNetLayerFMP(scn_net_t *net, int kind, int nFeatures, int filterSize, int filterStride, int poolSize,
+                             float fmpShrink, int activation, float dropout, int minActiveInputs);
+/* Re-seeds the RNG of every fractional max-pooling layer (layer index l gets seed + l) so that the next
+ * forward draws a known sequence of region bounds.  The reference seeds from the clock (Rng.cpp:8-15). */
+int scn_net_seed_fmp(scn_net_t *net, unsigned seed);
 int scn_net_addTerminalPoolingLayer(scn_net_t *net, int poolSize);
 /* SparseConvNetCUDA::addSoftmaxLayer (SparseConvNetCUDA.cu:200-213). */
 int scn_net_addSoftmaxLayer(scn_net_t *net);

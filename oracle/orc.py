@@ -130,6 +130,8 @@ class Oracle(_RulesLib):
         L.orc_net_free.argtypes = [c_p]
         for n in ("orc_net_addLeNetLayerMP", "orc_net_addTriangularLeNetLayerMP"):
             getattr(L, n).argtypes = [c_p] + [c_int] * 6 + [c_f, c_int]
+        L.orc_net_addLeNetLayerFMP.argtypes = [c_p] + [c_int] * 5 + [c_f, c_int, c_f, c_int]
+        L.orc_net_set_fmp_seed.argtypes = [c_p, ctypes.c_uint]
         L.orc_net_addTerminalPoolingLayer.argtypes = [c_p, c_int, c_int]
         L.orc_net_addSoftmaxLayer.argtypes = [c_p]
         L.orc_net_DeepCNet.restype = c_p
@@ -228,6 +230,13 @@ class OracleNet:
     def addLeNetLayerMP(self, nFeatures, fs, fstride, ps, pstride, act=RELU, dropout=0.0, minActive=1):
         f = self.L.orc_net_addTriangularLeNetLayerMP if self.lattice == 1 else self.L.orc_net_addLeNetLayerMP
         f(self.h, nFeatures, fs, fstride, ps, pstride, act, dropout, minActive)
+
+    def addLeNetLayerFMP(self, kind, nFeatures, fs, fstride, ps, fmpShrink, act=RELU, dropout=0.0, minActive=1):
+        self.L.orc_net_addLeNetLayerFMP(self.h, kind, nFeatures, fs, fstride, ps, fmpShrink, act, dropout, minActive)
+
+    def seed_fmp(self, seed):
+        """Every forward re-seeds FMP layer l's RNG with seed + l."""
+        self.L.orc_net_set_fmp_seed(self.h, seed)
 
     def addTriangularLeNetLayerMP(self, nFeatures, fs, fstride, ps, pstride, act=RELU, dropout=0.0, minActive=1):
         self.L.orc_net_addTriangularLeNetLayerMP(self.h, nFeatures, fs, fstride, ps, pstride, act, dropout, minActive)

@@ -369,7 +369,7 @@ static void topIndices(const float *test, int n, int k, int *indices) {
 }
 
 // ------------------------------------------------------------------ network
-enum LayerType { L_CONV = 0, L_CONV_TRI, L_NIN, L_MAXPOOL, L_MAXPOOL_TRI, L_TERMINAL };
+enum LayerType { L_CONV = 0, L_CONV_TRI, L_NIN, L_MAXPOOL, L_MAXPOOL_TRI, L_TERMINAL, L_FMP };
 
 struct Layer {
   int type;
@@ -378,6 +378,7 @@ struct Layer {
   int fs = 1;                               // cells per rule row
   int act = NOSIGMOID; float dropout = 0;   // NiN
   int S = 0;                                // terminal pooling constructor argument
+  int fmpKind = 0; float fmpShrink = 1;     // fractional max-pooling: tick kind (see makeTicks), shrink factor
   int inSpatial = 0, outSpatial = 0;
   std::vector<float> W, B, prelu;
 };
@@ -396,6 +397,7 @@ struct Net {
   int inputSpatialSize = 0;
   std::vector<Layer> layers;
   std::vector<Iface> kept; // last forward (keep=1): interface i+1 is layer i's output
+  unsigned fmpSeed = 1;    // each forward re-seeds FMP layer l's RNG with fmpSeed + l (the reference seeds from the clock)
 
   // SparseConvNetCUDA.cu:50-70.
   void addLearntLayer(int nFeatures, int act, float dropout) {
@@ -440,6 +442,12 @@ struct Net {
     addTriangularConvolutionalLayer(nFeatures, fsz, fstride, act, dropout, /*minActiveInputs=*/ps);
     if (ps > 1) { Layer L; L.type = L_MAXPOOL_TRI; L.size = ps; L.stride = pstride; L.fs = triangleSize(ps, dim); L.nIn = L.nOut = nOutputFeatures; layers.push_back(L); }
   }
+  // SparseConvNetCUDA.cu:112-163 (addLeNetLayer{PO,PD,RO,RD}FMP): convolution block, then the FMP layer
+  // if it shrinks at all.
+  void addLeNetLayerFMP(int kind, int nFeatures, int fsz, int fstride, int ps, float shrink, int act, float dropout, int minActive) {
+    addConvolutionalLayer(nFeatures, fsz, fstride, act, dropout, minActive);
+    if (shrink > 1) { Layer L; L.type = L_FMP; L.fmpKind = kind; L.fmpShrink = shrink; L.size = ps; L.fs = ipow(ps, dim); L.nIn = L.nOut = nOutputFeatures; layers.push_back(L); }
+  }
   // SparseConvNetCUDA.cu:196-199.
   void addTerminalPoolingLayer(int poolSize, int S) {
     Layer L; L.type = L_TERMINAL; L.size = poolSize; L.S = S; L.nIn = L.nOut = nOutputFeatures; layers.push_back(L);
@@ -454,6 +462,11 @@ struct Net {
       L.outSpatial = s;
       if (L.type == L_NIN) L.inSpatial = s;
       else if (L.type == L_TERMINAL) L.inSpatial = L.size;
+      else if (L.type == L_FMP) { // MaxPoolingLayer.cu:216-223: int * float, + 0.5, truncated
+        const float prod = s * L.fmpShrink;
+        L.inSpatial = (int)(prod + 0.5);
+        if (L.inSpatial == s) L.inSpatial++;
+      }
       else L.inSpatial = L.size + (s - 1) * L.stride;
       s = L.inSpatial;
     }
@@ -465,7 +478,8 @@ struct Net {
 // SparseConvNetCUDA.cu:242-246 run them.  Input rows of sample b are [off[b], off[b+1]);
 // keys[row] is the site key, or -1 for the sample's background ("null vector") row.
 static void forwardChunk(const Net &net, int batch, const int64_t *keys, const int *off, const float *features,
-                         bool accum64, std::vector<Iface> &ifs, double *tRules) {
+                         bool accum64, std::vector<Iface> &ifs, double *tRules,
+                         const std::vector<std::vector<Ticks>> &fmpTicks, int firstSample) {
   auto t0 = std::chrono::steady_clock::now();
   ifs.assign(net.layers.size() + 1, Iface());
   Iface &I0 = ifs[0];
@@ -491,6 +505,11 @@ static void forwardChunk(const Net &net, int batch, const int64_t *keys, const i
       size_t s = 1;
       for (int b = 0; b < batch; ++b) s = std::max(s, in.grids[b].sites.size());
       for (int b = 0; b < batch; ++b) terminalRules(in.grids[b], out.grids[b], (int)s, out.nSpatialSites, out.rules);
+    } else if (L.type == L_FMP) { // MaxPoolingLayer.cu:171-186 and its three siblings
+      out.spatialSize = L.outSpatial; out.grids.resize(batch);
+      for (int b = 0; b < batch; ++b)
+        gridRulesFmp(in.grids[b], out.grids[b], &fmpTicks[l][(size_t)(firstSample + b) * net.dim], net.dim, L.inSpatial, L.outSpatial, L.size,
+                     L.fmpKind == 0 || L.fmpKind == 2, out.nSpatialSites, out.rules);
     } else {
       const bool tri = (L.type == L_CONV_TRI || L.type == L_MAXPOOL_TRI);
       const bool pool = (L.type == L_MAXPOOL || L.type == L_MAXPOOL_TRI);
@@ -517,7 +536,7 @@ static void forwardChunk(const Net &net, int batch, const int64_t *keys, const i
       if (accum64) ninForward<double>(in.features.data(), out.nSpatialSites, L.nIn, L.W.data(), L.B.data(), L.prelu.empty() ? nullptr : L.prelu.data(), L.nOut, 1.0f - L.dropout, L.act, out.features.data());
       else ninForward<float>(in.features.data(), out.nSpatialSites, L.nIn, L.W.data(), L.B.data(), L.prelu.empty() ? nullptr : L.prelu.data(), L.nOut, 1.0f - L.dropout, L.act, out.features.data());
       break;
-    case L_MAXPOOL: case L_MAXPOOL_TRI:
+    case L_MAXPOOL: case L_MAXPOOL_TRI: case L_FMP:
       out.choices.resize(out.features.size());
       maxPool(in.features.data(), out.rules.data(), out.nSpatialSites, L.fs, L.nOut, out.features.data(), out.choices.data());
       break;
@@ -640,6 +659,8 @@ void *orc_net_create(int dim, int nInputFeatures, int nClasses, int nTop) {
 void orc_net_free(void *h) { delete (Net *)h; }
 void orc_net_addLeNetLayerMP(void *h, int nFeatures, int fs, int fstride, int ps, int pstride, int act, float dropout, int minActive) { ((Net *)h)->addLeNetLayerMP(nFeatures, fs, fstride, ps, pstride, act, dropout, minActive); }
 void orc_net_addTriangularLeNetLayerMP(void *h, int nFeatures, int fs, int fstride, int ps, int pstride, int act, float dropout, int minActive) { ((Net *)h)->addTriangularLeNetLayerMP(nFeatures, fs, fstride, ps, pstride, act, dropout, minActive); }
+void orc_net_addLeNetLayerFMP(void *h, int kind, int nFeatures, int fs, int fstride, int ps, float shrink, int act, float dropout, int minActive) { ((Net *)h)->addLeNetLayerFMP(kind, nFeatures, fs, fstride, ps, shrink, act, dropout, minActive); }
+void orc_net_set_fmp_seed(void *h, unsigned seed) { ((Net *)h)->fmpSeed = seed; }
 void orc_net_addTerminalPoolingLayer(void *h, int poolSize, int S) { ((Net *)h)->addTerminalPoolingLayer(poolSize, S); }
 void orc_net_addSoftmaxLayer(void *h) { ((Net *)h)->addSoftmaxLayer(); }
 // NetworkArchitectures.cpp:3-11.
@@ -689,10 +710,20 @@ void orc_net_forward(void *h, int batch, const int64_t *keys, const int *off, co
   nThreads = std::min(nThreads, std::max(1, batch));
   std::vector<double> tr(nThreads, 0.0);
   std::vector<std::vector<Iface>> ifs(nThreads);
+  // fractional max-pooling: every sample's tick tables, drawn in batch order from each layer's RNG
+  std::vector<std::vector<Ticks>> fmpTicks(net->layers.size());
+  for (size_t l = 0; l < net->layers.size(); ++l) {
+    const Layer &L = net->layers[l];
+    if (L.type != L_FMP) continue;
+    FmpRng rng;
+    rng.gen.seed(net->fmpSeed + (unsigned)l);
+    for (int b = 0; b < batch; ++b)
+      for (int a = 0; a < net->dim; ++a) fmpTicks[l].push_back(makeTicks(L.fmpKind, L.inSpatial, L.outSpatial, L.size, rng));
+  }
   auto work = [&](int t) {
     int b0 = (int)((long long)batch * t / nThreads), b1 = (int)((long long)batch * (t + 1) / nThreads);
     if (b1 <= b0) return;
-    forwardChunk(*net, b1 - b0, keys, off + b0, features, accum64 != 0, ifs[t], &tr[t]);
+    forwardChunk(*net, b1 - b0, keys, off + b0, features, accum64 != 0, ifs[t], &tr[t], fmpTicks, b0);
     const Iface &top = ifs[t].back();
     for (int b = b0; b < b1; ++b) {
       const float *pr = top.features.data() + (size_t)(b - b0) * net->nClasses;

@@ -1,4 +1,6 @@
 // Geometry layers and the learnt layers: host-side bookkeeping around the C ABI calls.
+#include <climits>
+#include "Regions.h"
 #include <cmath>
 #include <cstring>
 #include <random>
@@ -180,6 +182,81 @@ int MaxPoolingLayer::calculateInputSpatialSize(int outputSpatialSize) {
   std::cout << ")-" << inSpatialSize;
   return inSpatialSize;
 }
+
+// ------------------------------------------------------------------ fractional max-pooling
+FractionalMaxPoolingLayerBase::FractionalMaxPoolingLayerBase(cudaMemStream &memStream, int poolSize, float fmpShrink, int dimension,
+                                                             const char *label, const char *tag)
+    : SpatiallySparseLayer(memStream), inSpatialSize(0), outSpatialSize(0), poolSize(poolSize), dimension(dimension), fmpShrink(fmpShrink),
+      ticks(false, 0), tag(tag) {
+  changesGeometry = true;
+  sd = ipow(poolSize, dimension);
+  std::cout << label << " Fractional Max Pooling " << fmpShrink << " " << poolSize << std::endl;
+}
+// MaxPoolingLayer.cu:171-186 (and 232-247, 293-308, 354-369): per sample new regions from the layer's
+// rng, then gridRules; here the tables of the whole batch go to the device and one build does all samples.
+long long FractionalMaxPoolingLayerBase::enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                                     SpatiallySparseBatchInterface &output, long long rowsInBound, int *d_result) {
+  requireInference(batch);
+  checkSpatial(input, inSpatialSize, "FractionalMaxPoolingLayer");
+  output.nFeatures = input.nFeatures; output.spatialSize = outSpatialSize;
+  std::vector<int> &t = ticks.hVector();
+  t.clear();
+  for (int item = 0; item < batch.batchSize; ++item) appendSampleTables(t);
+  long long full = 1;
+  for (int a = 0; a < dimension; ++a) full *= outSpatialSize;
+  const long long bound = std::min(rowsInBound * sd, (long long)batch.batchSize * full) + batch.batchSize;
+  if (bound * sd > INT_MAX || rowsInBound > INT_MAX) throw ScnException("rule build: more than 2^31 rule cells in one batch; use smaller batches");
+  SpatiallySparseBatchInterface *g = input.gridOwner;
+  output.gridOwner = &output;
+  output.siteKeys.resize((int)bound);
+  output.sampleOffsets.resize(batch.batchSize + 1);
+  output.backgroundRows.resize(batch.batchSize);
+  output.rules.resize((int)(bound * sd));
+  const size_t wsBytes = scn_fmp_rules_workspace_bytes(dimension, inSpatialSize, outSpatialSize, poolSize, batch.batchSize, (int)rowsInBound);
+  scnSafeCall(scn_fmp_rules_build(dimension, inSpatialSize, outSpatialSize, poolSize, overlapping() ? 1 : 0, batch.batchSize, ticks.dPtr(),
+                                  g->siteKeys.dPtr(), g->sampleOffsets.dPtr(), g->backgroundRows.dPtr(), (int)rowsInBound,
+                                  output.siteKeys.dPtr(), output.sampleOffsets.dPtr(), output.backgroundRows.dPtr(), output.rules.dPtr(),
+                                  (int)bound, d_result, rulechain::workspace(wsBytes), wsBytes, memStream.stream));
+  return bound;
+}
+void FractionalMaxPoolingLayerBase::finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                                SpatiallySparseBatchInterface &output, const int *h) {
+  scn_regions_t R = {SCN_LATTICE_SQUARE, dimension, poolSize, 1, poolSize, 1, 1}; // rule rows of poolSize^dimension cells
+  finishGeometry(R, batch, input, output, input.nFeatures, 1, h);
+  output.spatialSize = outSpatialSize;
+}
+void FractionalMaxPoolingLayerBase::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
+                                               SpatiallySparseBatchInterface &output) {
+  preprocessNow(*this, batch, input, output);
+}
+void FractionalMaxPoolingLayerBase::forwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  const int n = output.nSpatialSites * output.featuresPresent.size();
+  output.sub->poolingChoices.resize(n);
+  output.sub->features.resize(n);
+  maxPool(input.sub->features.dPtr(), output.sub->features.dPtr(), output.rules.dPtr(), output.nSpatialSites, sd,
+          output.featuresPresent.size(), output.sub->poolingChoices.dPtr(), memStream);
+}
+// MaxPoolingLayer.cu:216-223: int * float, + 0.5, truncated; at least one larger than the output
+int FractionalMaxPoolingLayerBase::calculateInputSpatialSize(int outputSpatialSize) {
+  outSpatialSize = outputSpatialSize;
+  inSpatialSize = outputSpatialSize * fmpShrink + 0.5;
+  if (inSpatialSize == outputSpatialSize) inSpatialSize++;
+  std::cout << "-(" << tag << ")-" << inSpatialSize;
+  return inSpatialSize;
+}
+#define SCN_FMP_LAYER(CLASS, TICKS, LABEL, TAG, OVERLAP)                                                             \
+  CLASS::CLASS(cudaMemStream &memStream, int poolSize, float fmpShrink, int dimension)                               \
+      : FractionalMaxPoolingLayerBase(memStream, poolSize, fmpShrink, dimension, LABEL, TAG) {}                      \
+  bool CLASS::overlapping() const { return OVERLAP; }                                                                \
+  void CLASS::appendSampleTables(std::vector<int> &dst) {                                                            \
+    FractionalPoolingRegions<TICKS> regions(inSpatialSize, outSpatialSize, dimension, poolSize, rng);                \
+    regions.appendTables(dst);                                                                                       \
+  }
+SCN_FMP_LAYER(PseudorandomOverlappingFractionalMaxPoolingLayer, PseudorandomOverlappingFmpTicks, "Pseudorandom overlapping", "POFMP", true)
+SCN_FMP_LAYER(PseudorandomNonOverlappingFractionalMaxPoolingLayer, PseudorandomNonOverlappingFmpTicks, "Pseudorandom non-overlapping", "PDFMP", false)
+SCN_FMP_LAYER(RandomOverlappingFractionalMaxPoolingLayer, RandomOverlappingFmpTicks, "Random overlapping", "ROFMP", true)
+SCN_FMP_LAYER(RandomNonOverlappingFractionalMaxPoolingLayer, RandomNonOverlappingFmpTicks, "Random non-overlapping", "RDFMP", false)
+#undef SCN_FMP_LAYER
 
 // ------------------------------------------------------------------ MaxPoolingTriangularLayer
 MaxPoolingTriangularLayer::MaxPoolingTriangularLayer(cudaMemStream &memStream, int poolSize, int poolStride, int dimension)

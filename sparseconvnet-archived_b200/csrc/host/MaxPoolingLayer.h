@@ -1,5 +1,6 @@
 // Max pooling over square/cubic regions (MaxPoolingLayer.h:6-38).
 #pragma once
+#include "Rng.h"
 #include "SpatiallySparseLayer.h"
 
 void maxPool(float *g1, float *g2, int *rules, int count, int sd, int nOut, int *d_choice, cudaMemStream &memStream);
@@ -15,4 +16,56 @@ public:
                          long long rowsInBound, int *d_result);
   void finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
                    const int *h_result);
+};
+
+// Fractional max-pooling (MaxPoolingLayer.h:34-143): per sample a fresh set of random region
+// bounds (one tick object per axis, drawn on the host from the layer's rng), rules built on the
+// device, then the same maxPool kernel.  One base class, four named layers as in the reference.
+class FractionalMaxPoolingLayerBase : public SpatiallySparseLayer {
+public:
+  int inSpatialSize, outSpatialSize, poolSize, dimension, sd;
+  float fmpShrink;
+  RNG rng;
+  vectorCUDA<int> ticks; // this batch's tables, [sample][axis][inputL | inputR | outputL | outputR]
+  FractionalMaxPoolingLayerBase(cudaMemStream &memStream, int poolSize, float fmpShrink, int dimension, const char *label, const char *tag);
+  void preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
+  void forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
+  int calculateInputSpatialSize(int outputSpatialSize);
+  long long enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                         long long rowsInBound, int *d_result);
+  void finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                   const int *h_result);
+
+protected:
+  virtual bool overlapping() const = 0;
+  virtual void appendSampleTables(std::vector<int> &dst) = 0; // one FractionalPoolingRegions<ticks>(..., rng)
+  const char *tag;
+};
+class PseudorandomOverlappingFractionalMaxPoolingLayer : public FractionalMaxPoolingLayerBase {
+public:
+  PseudorandomOverlappingFractionalMaxPoolingLayer(cudaMemStream &memStream, int poolSize, float fmpShrink, int dimension);
+protected:
+  bool overlapping() const;
+  void appendSampleTables(std::vector<int> &dst);
+};
+class PseudorandomNonOverlappingFractionalMaxPoolingLayer : public FractionalMaxPoolingLayerBase {
+public:
+  PseudorandomNonOverlappingFractionalMaxPoolingLayer(cudaMemStream &memStream, int poolSize, float fmpShrink, int dimension);
+protected:
+  bool overlapping() const;
+  void appendSampleTables(std::vector<int> &dst);
+};
+class RandomOverlappingFractionalMaxPoolingLayer : public FractionalMaxPoolingLayerBase {
+public:
+  RandomOverlappingFractionalMaxPoolingLayer(cudaMemStream &memStream, int poolSize, float fmpShrink, int dimension);
+protected:
+  bool overlapping() const;
+  void appendSampleTables(std::vector<int> &dst);
+};
+class RandomNonOverlappingFractionalMaxPoolingLayer : public FractionalMaxPoolingLayerBase {
+public:
+  RandomNonOverlappingFractionalMaxPoolingLayer(cudaMemStream &memStream, int poolSize, float fmpShrink, int dimension);
+protected:
+  bool overlapping() const;
+  void appendSampleTables(std::vector<int> &dst);
 };

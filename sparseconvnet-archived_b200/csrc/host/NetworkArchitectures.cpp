@@ -61,3 +61,19 @@ DeepC3C3::DeepC3C3(int dimension, int l, int k, ActivationFunction fn, int nInpu
   addLeNetLayerMP((l + 1) * k, 1, 1, 1, 1, fn, p);
   addSoftmaxLayer();
 }
+
+// NetworkArchitectures.cpp:72-122.
+#define SCN_FMP_NET(CLASS, ADD)                                                                                               \
+  CLASS::CLASS(int dimension, int l, int k, float fmpShrink, ActivationFunction fn, int nInputFeatures, int nClasses, float p, \
+               int cudaDevice, int nTop)                                                                                      \
+      : SparseConvNet(dimension, nInputFeatures, nClasses, cudaDevice, nTop) {                                                \
+    for (int i = 0; i < l; i++) ADD(k * (i + 1), 2, 1, 2, fmpShrink, fn, p * i / (l + 1));                                    \
+    addLeNetLayerMP(k * (l + 1), 2, 1, 1, 1, fn, p * l / (l + 1));                                                            \
+    addLeNetLayerMP(k * (l + 2), 1, 1, 1, 1, fn, p);                                                                          \
+    addSoftmaxLayer();                                                                                                        \
+  }
+SCN_FMP_NET(POFMPSparseConvNet, addLeNetLayerPOFMP)
+SCN_FMP_NET(ROFMPSparseConvNet, addLeNetLayerROFMP)
+SCN_FMP_NET(PDFMPSparseConvNet, addLeNetLayerPDFMP)
+SCN_FMP_NET(RDFMPSparseConvNet, addLeNetLayerRDFMP)
+#undef SCN_FMP_NET

@@ -1,7 +1,6 @@
 // Named architectures (NetworkArchitectures.h): DeepCNet and its relatives, expressed as
 // sequences of addLeNetLayerMP calls.  l = number of pooling levels, k = width step,
-// p = dropout of the last level (earlier levels scale linearly).  The four fractional
-// max-pooling networks are not built.
+// p = dropout of the last level (earlier levels scale linearly).
 #pragma once
 #include "SparseConvNet.h"
 
@@ -28,4 +27,27 @@ public:
 class DeepC3C3 : public SparseConvNet {
 public:
   DeepC3C3(int dimension, int l, int k, ActivationFunction fn, int nInputFeatures, int nClasses, float p = 0.0f, int cudaDevice = -1, int nTop = 1);
+};
+
+// The four fractional max-pooling networks (NetworkArchitectures.h:43-69): l blocks of a 2^d
+// convolution and an FMP layer of pool size 2, then a 2^d and a 1^d convolution block.
+class POFMPSparseConvNet : public SparseConvNet {
+public:
+  POFMPSparseConvNet(int dimension, int l, int k, float fmpShrink, ActivationFunction fn, int nInputFeatures, int nClasses, float p = 0.0f,
+                     int cudaDevice = -1, int nTop = 1);
+};
+class ROFMPSparseConvNet : public SparseConvNet {
+public:
+  ROFMPSparseConvNet(int dimension, int l, int k, float fmpShrink, ActivationFunction fn, int nInputFeatures, int nClasses, float p = 0.0f,
+                     int cudaDevice = -1, int nTop = 1);
+};
+class PDFMPSparseConvNet : public SparseConvNet {
+public:
+  PDFMPSparseConvNet(int dimension, int l, int k, float fmpShrink, ActivationFunction fn, int nInputFeatures, int nClasses, float p = 0.0f,
+                     int cudaDevice = -1, int nTop = 1);
+};
+class RDFMPSparseConvNet : public SparseConvNet {
+public:
+  RDFMPSparseConvNet(int dimension, int l, int k, float fmpShrink, ActivationFunction fn, int nInputFeatures, int nClasses, float p = 0.0f,
+                     int cudaDevice = -1, int nTop = 1);
 };

@@ -17,6 +17,15 @@ public:
   ~SparseConvNet();
   void addLeNetLayerMP(int nFeatures, int filterSize, int filterStride, int poolSize, int poolStride,
                        ActivationFunction activationFn = RELU, float dropout = 0.0f, int minActiveInputs = 1);
+  // SparseConvNet.h:32-47
+  void addLeNetLayerPOFMP(int nFeatures, int filterSize, int filterStride, int poolSize, float fmpShrink, ActivationFunction activationFn = RELU,
+                          float dropout = 0.0f, int minActiveInputs = 1);
+  void addLeNetLayerROFMP(int nFeatures, int filterSize, int filterStride, int poolSize, float fmpShrink, ActivationFunction activationFn = RELU,
+                          float dropout = 0.0f, int minActiveInputs = 1);
+  void addLeNetLayerPDFMP(int nFeatures, int filterSize, int filterStride, int poolSize, float fmpShrink, ActivationFunction activationFn = RELU,
+                          float dropout = 0.0f, int minActiveInputs = 1);
+  void addLeNetLayerRDFMP(int nFeatures, int filterSize, int filterStride, int poolSize, float fmpShrink, ActivationFunction activationFn = RELU,
+                          float dropout = 0.0f, int minActiveInputs = 1);
   void addTerminalPoolingLayer(int poolSize);
   void addSoftmaxLayer();
   float processDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0, float momentum = 0.99);

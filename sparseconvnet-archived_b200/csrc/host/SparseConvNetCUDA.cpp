@@ -106,6 +106,21 @@ void SparseConvNetCUDA::addTriangularLeNetLayerMP(int nFeatures, int filterSize,
     layers.push_back(new MaxPoolingTriangularLayer(memStream, poolSize, poolStride, dimension));
   }
 }
+// SparseConvNetCUDA.cu:112-163: the shrink factor takes the poolingToFollow slot; no FMP layer if it does not shrink.
+#define SCN_ADD_FMP(NAME, LAYER)                                                                                                      \
+  void SparseConvNetCUDA::NAME(int nFeatures, int filterSize, int filterStride, int poolSize, float fmpShrink,                      \
+                               ActivationFunction activationFn, float dropout, int minActiveInputs) {                               \
+    addConvolutionalLayer(nFeatures, filterSize, filterStride, activationFn, dropout, minActiveInputs, fmpShrink);                  \
+    if (fmpShrink > 1) {                                                                                                            \
+      std::cout << layers.size() << ":";                                                                                            \
+      layers.push_back(new LAYER(memStream, poolSize, fmpShrink, dimension));                                                       \
+    }                                                                                                                               \
+  }
+SCN_ADD_FMP(addLeNetLayerROFMP, RandomOverlappingFractionalMaxPoolingLayer)
+SCN_ADD_FMP(addLeNetLayerPOFMP, PseudorandomOverlappingFractionalMaxPoolingLayer)
+SCN_ADD_FMP(addLeNetLayerRDFMP, RandomNonOverlappingFractionalMaxPoolingLayer)
+SCN_ADD_FMP(addLeNetLayerPDFMP, PseudorandomNonOverlappingFractionalMaxPoolingLayer)
+#undef SCN_ADD_FMP
 void SparseConvNetCUDA::addTerminalPoolingLayer(int poolSize, int S) {
   std::cout << layers.size() << ":";
   TerminalPoolingLayer *t = new TerminalPoolingLayer(memStream, poolSize, S);
@@ -141,7 +156,7 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
   // Without terminal pooling (whose build reads its input grid at once) the region builds are
   // only recorded here and then run together: one fused kernel when the samples are small.
   bool defer = true;
-  for (auto L : layers) defer = defer && dynamic_cast<TerminalPoolingLayer *>(L) == nullptr;
+  for (auto L : layers) defer = defer && dynamic_cast<TerminalPoolingLayer *>(L) == nullptr && dynamic_cast<FractionalMaxPoolingLayerBase *>(L) == nullptr;
   std::vector<rulechain::DeferredBuild> builds;
   if (defer) rulechain::beginDeferred(&builds);
   try {

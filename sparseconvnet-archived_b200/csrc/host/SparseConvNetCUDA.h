@@ -33,6 +33,15 @@ public:
                              int minActiveInputs = 1, float poolingToFollow = 1.0f);
   void addLeNetLayerMP(int nFeatures, int filterSize, int filterStride, int poolSize, int poolStride, ActivationFunction activationFn = RELU,
                        float dropout = 0.0f, int minActiveInputs = 1);
+  // SparseConvNetCUDA.h:67-82: convolution block followed by one of the four fractional max-pooling layers
+  void addLeNetLayerROFMP(int nFeatures, int filterSize, int filterStride, int poolSize, float fmpShrink, ActivationFunction activationFn = RELU,
+                          float dropout = 0.0f, int minActiveInputs = 1);
+  void addLeNetLayerPOFMP(int nFeatures, int filterSize, int filterStride, int poolSize, float fmpShrink, ActivationFunction activationFn = RELU,
+                          float dropout = 0.0f, int minActiveInputs = 1);
+  void addLeNetLayerRDFMP(int nFeatures, int filterSize, int filterStride, int poolSize, float fmpShrink, ActivationFunction activationFn = RELU,
+                          float dropout = 0.0f, int minActiveInputs = 1);
+  void addLeNetLayerPDFMP(int nFeatures, int filterSize, int filterStride, int poolSize, float fmpShrink, ActivationFunction activationFn = RELU,
+                          float dropout = 0.0f, int minActiveInputs = 1);
   void addTriangularConvolutionalLayer(int nFeatures, int filterSize, int filterStride, ActivationFunction activationFn = RELU,
                                        float dropout = 0.0f, int minActiveInputs = 1, float poolingToFollow = 1.0f);
   void addTriangularLeNetLayerMP(int nFeatures, int filterSize, int filterStride, int poolSize, int poolStride,

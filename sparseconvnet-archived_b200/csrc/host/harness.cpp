@@ -53,6 +53,9 @@ void describe(SpatiallySparseLayer *L, int *info, float *dropout) {
   } else if (auto m = dynamic_cast<MaxPoolingTriangularLayer *>(L)) {
     int w[10] = {4, m->poolSize, m->poolStride, 1, 0, 0, m->S, 0, m->inSpatialSize, m->outSpatialSize};
     std::memcpy(v, w, sizeof(v));
+  } else if (auto f = dynamic_cast<FractionalMaxPoolingLayerBase *>(L)) {
+    int w[10] = {6, f->poolSize, 1, 1, 0, 0, f->sd, 0, f->inSpatialSize, f->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
   } else if (auto t = dynamic_cast<TerminalPoolingLayer *>(L)) {
     int w[10] = {5, t->poolSize, 1, 1, 0, 0, 1, 0, t->inSpatialSize, t->outSpatialSize};
     std::memcpy(v, w, sizeof(v));
@@ -111,6 +114,28 @@ int scn_net_addLeNetLayerMP(scn_net_t *net, int nFeatures, int fs, int fstride, 
     Quiet q;
     if (net->lattice == 0) net->cnn->addLeNetLayerMP(nFeatures, fs, fstride, ps, pstride, (ActivationFunction)act, dropout, minActive);
     else net->cnn->addTriangularLeNetLayerMP(nFeatures, fs, fstride, ps, pstride, (ActivationFunction)act, dropout, minActive);
+  });
+}
+int scn_net_addLeNetLayerFMP(scn_net_t *net, int kind, int nFeatures, int fs, int fstride, int ps, float fmpShrink, int act, float dropout,
+                             int minActive) {
+  return guarded([&] {
+    Quiet q;
+    if (net->lattice != 0) throw ScnException("fractional max-pooling exists on the square lattice only");
+    SparseConvNetCUDA &c = *net->cnn;
+    ActivationFunction a = (ActivationFunction)act;
+    switch (kind) {
+    case 0: c.addLeNetLayerPOFMP(nFeatures, fs, fstride, ps, fmpShrink, a, dropout, minActive); break;
+    case 1: c.addLeNetLayerPDFMP(nFeatures, fs, fstride, ps, fmpShrink, a, dropout, minActive); break;
+    case 2: c.addLeNetLayerROFMP(nFeatures, fs, fstride, ps, fmpShrink, a, dropout, minActive); break;
+    case 3: c.addLeNetLayerRDFMP(nFeatures, fs, fstride, ps, fmpShrink, a, dropout, minActive); break;
+    default: throw ScnException("unknown fractional max-pooling kind");
+    }
+  });
+}
+int scn_net_seed_fmp(scn_net_t *net, unsigned seed) {
+  return guarded([&] {
+    for (size_t l = 0; l < net->cnn->layers.size(); ++l)
+      if (auto f = dynamic_cast<FractionalMaxPoolingLayerBase *>(net->cnn->layers[l])) f->rng.gen.seed(seed + (unsigned)l);
   });
 }
 int scn_net_addTerminalPoolingLayer(scn_net_t *net, int poolSize) {
@@ -256,7 +281,8 @@ int scn_net_iface_sizes(scn_net_t *net, int i, long long *sizes) {
     if (!net->last) throw ScnException("no forward has run");
     SpatiallySparseBatchInterface &I = net->last->interfaces.at(i);
     sizes[0] = I.nSpatialSites; sizes[1] = I.nFeatures; sizes[2] = I.spatialSize; sizes[3] = I.rules.size();
-    bool pools = i > 0 && (dynamic_cast<MaxPoolingLayer *>(net->cnn->layers[i - 1]) || dynamic_cast<MaxPoolingTriangularLayer *>(net->cnn->layers[i - 1]));
+    bool pools = i > 0 && (dynamic_cast<MaxPoolingLayer *>(net->cnn->layers[i - 1]) || dynamic_cast<MaxPoolingTriangularLayer *>(net->cnn->layers[i - 1]) ||
+                           dynamic_cast<FractionalMaxPoolingLayerBase *>(net->cnn->layers[i - 1]));
     sizes[4] = pools ? (long long)I.nSpatialSites * I.nFeatures : 0;
   });
 }
