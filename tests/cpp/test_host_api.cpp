@@ -12,6 +12,7 @@
 #include "NetworkArchitectures.h"
 #include "NetworkInNetworkLayer.h"
 #include "Regions.h"
+#include "Rng.h"
 #include "SigmoidLayer.h"
 #include "SparseConvNetCUDA.h"
 
@@ -176,6 +177,37 @@ int main() {
       try { cnn.loadWeights("/nonexistent/w", 1, false); } catch (const ScnException &) { threw = true; }
       CHECK(threw);
       std::printf("OK refusals\n");
+    }
+    // ---- 6. fractional max-pooling: a named FMP network, and the host gridRules over FractionalPoolingRegions
+    {
+      POFMPSparseConvNet fmp(2, 3, 32, 1.414f, VLEAKYRELU, 2, 5);
+      CHECK(fmp.cnn->inputSpatialSize == 11); // 1 <-C2- 2 <-FMP- 3 <-C2- 4 <-FMP- 6 <-C2- 7 <-FMP- 10 <-C2- 11
+      fillWeights(*fmp.cnn, 9);
+      SpatiallySparseDataset fds;
+      fds.name = "cpp-fmp"; fds.nFeatures = 2; fds.nClasses = 5; fds.type = TESTBATCH;
+      std::vector<SitesPicture *> fp;
+      for (int i = 0; i < 5; ++i) { fp.push_back(randomPicture(11, 2, i % 5, gen, 0.4)); fds.pictures.push_back(fp.back()); }
+      float e1 = fmp.processDataset(fds, 2);
+      CHECK(e1 >= 0.f && e1 <= 1.f);
+      for (auto q : fp) delete q;
+
+      RNG rng;
+      rng.gen.seed(42);
+      FractionalPoolingRegions<PseudorandomNonOverlappingFmpTicks> regions(7, 5, 2, 2, rng);
+      int covered = 0;
+      for (int j = 0; j < 5; ++j) { CHECK(regions.inputR(0, j) - regions.inputL(0, j) >= 1 && regions.inputR(0, j) - regions.inputL(0, j) <= 2); covered += regions.inputR(0, j) - regions.inputL(0, j); }
+      CHECK(covered == 7 && regions.inputL(0, 0) == 0 && regions.inputR(0, 4) == 7); // disjoint regions tile the axis
+      SparseGrid gin, gout;
+      gin.backgroundCol = 0;
+      for (int k = 0; k < 49; k += 3) gin.mp[k] = 1 + k / 3;
+      int nSites = 0;
+      std::vector<int> rls;
+      gridRules(gin, gout, regions, nSites, rls, false);
+      CHECK(nSites >= 1 && (int)rls.size() == nSites * 4);
+      int placed = 0;
+      for (int v : rls) placed += v > 0;
+      CHECK(placed == 17); // every input site appears exactly once: the regions do not overlap
+      std::printf("OK fractional max-pooling\n");
     }
     for (auto p : pics) delete p;
   } catch (const std::exception &e) {
