@@ -110,6 +110,11 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a, uint64_t b
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
                ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// A operand in tensor memory (lane = row, one tf32 per column)
+__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -123,7 +128,7 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
-  int mTiles, accStride, K, generic, rulesDouble, rawEntries, nStages64; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
+  int mTiles, accStride, K, generic, rulesDouble, rawEntries, nStages64, atmem; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
@@ -220,19 +225,27 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint3
 }
 
 // Work items are output tiles, or (tile, K range) pairs when K is split over several CTAs.
-template <bool SPLIT, int ACT>
+// ATMEM: the A operand is fed from tensor memory.  The split warps store the hi (raw) and lo images of
+// a slab straight into one of two 64-column tensor-memory slots (tcgen05.st, thread = row) and the MMAs
+// read A from there: the lo image is never written to shared memory and the tensor core reads no A tile
+// from it, which takes about 30 % off the shared-memory data pipe, the resource that bounds this
+// kernel (second convolution of the benchmark 81 -> 66 us, third 72 -> 64 us).  Needs 2 accumulators + 128
+// columns <= 512, i.e. BN <= 192; a shared-memory stage then holds the raw A tile and the weight images only.
+template <bool SPLIT, int ACT, bool ATMEM>
 __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) {
   extern __shared__ unsigned char smem_raw[];
   int *rulesS = reinterpret_cast<int *>(smem_raw); // [128 x fs] rule tile of the current item (when it fits)
   // 1024-byte alignment: the swizzle pattern is a function of absolute shared-memory address bits
   unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + (P.rulesDouble ? 2 : 1) * P.rulesBytes + 1023) & ~(uintptr_t)1023);
   const int bHalf = P.BN * ROW_BYTES;            // one of B_hi / B_lo
-  const int stageBytes = 2 * A_HALF + 2 * bHalf; // A raw(hi), A_lo, B_hi, B_lo
+  const int aBytes = ATMEM ? A_HALF : 2 * A_HALF;  // A raw (= hi) [, A_lo]
+  const int stageBytes = aBytes + 2 * bHalf;       // then B_hi, B_lo
   float *epi = reinterpret_cast<float *>(smem + (size_t)P.stages * stageBytes);
-  __shared__ __align__(8) uint64_t bars[3 * MAX_STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[3 * MAX_STAGES + 8];
   __shared__ uint32_t tmemBase;
   const uint32_t rawBar = smem_u32(&bars[0]), fullBar = smem_u32(&bars[MAX_STAGES]), emptyBar = smem_u32(&bars[2 * MAX_STAGES]),
-                 accFullBar = smem_u32(&bars[3 * MAX_STAGES]), accEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 2]);
+                 accFullBar = smem_u32(&bars[3 * MAX_STAGES]), accEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 2]),
+                 aFullBar = smem_u32(&bars[3 * MAX_STAGES + 4]), aEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 6]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kSplit = SPLIT ? P.kSplit : 1;
   const int nItems = P.mTiles * P.nTiles * kSplit;
@@ -240,10 +253,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P.stages; ++s) {
       mbar_init(rawBar + 8 * s, 128);      // the gather threads' cp.async completions
-      mbar_init(fullBar + 8 * s, 128 + 1); // the split threads + the weight copy
+      mbar_init(fullBar + 8 * s, ATMEM ? 1 : 128 + 1); // [the split threads +] the weight copy
       mbar_init(emptyBar + 8 * s, 1);      // tcgen05.commit
     }
-    for (int a = 0; a < 2; ++a) { mbar_init(accFullBar + 8 * a, 1); mbar_init(accEmptyBar + 8 * a, 128); }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(accFullBar + 8 * a, 1); mbar_init(accEmptyBar + 8 * a, 128);
+      mbar_init(aFullBar + 8 * a, 128); mbar_init(aEmptyBar + 8 * a, 1); // tensor-memory A slots (ATMEM)
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 13) { // tensor memory: two 128 x BN fp32 accumulators
@@ -377,7 +393,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   } else if (warp < 12) {
     // ------------------------------------------------------------ split: lo = x - tf32(x)
     const int t = threadIdx.x - 256;
-    Ring ring(P.stages);
+    Ring ring(P.stages), slot(P.atmem ? P.atmem : 1);
     for (int item = blockIdx.x; item < nItems; item += gridDim.x) {
       int tileM, tileN, slab0, nLoc;
       itemTile(item, tileM, tileN, slab0, nLoc);
@@ -385,6 +401,40 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
         const int st = ring.idx;
         mbar_wait(rawBar + 8 * st, ring.phase, 5);
         unsigned char *aHi = smem + (size_t)st * stageBytes, *aLo = aHi + A_HALF;
+        if (ATMEM) {
+          // thread = row: its 32 values, 8 swizzled 16-byte chunks (rows r..r+7 of a quarter warp read 8
+          // different chunk columns: no bank conflict)
+          const unsigned char *rowp = aHi + (t >> 3) * 1024 + (t & 7) * ROW_BYTES;
+          uint32_t v[32];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 x = *reinterpret_cast<const uint4 *>(rowp + ((c ^ (t & 7)) << 4));
+            v[4 * c] = x.x; v[4 * c + 1] = x.y; v[4 * c + 2] = x.z; v[4 * c + 3] = x.w;
+          }
+          mbar_wait(aEmptyBar + 8 * slot.idx, slot.phase ^ 1, 8); // the MMAs that read this slot have finished
+          tc_fence_after();
+          // lanes 32*(warp % 4)..+31 belong to this warp; hi image at columns +0..31, lo at +32..63
+          const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(2 * P.accStride + slot.idx * 64);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t w[32];
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+              w[k] = h == 0 ? v[k] : __float_as_uint(__uint_as_float(v[k]) - __uint_as_float(v[k] & 0xffffe000u));
+#pragma unroll
+            for (int g16 = 0; g16 < 2; ++g16)
+              asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                           ::"r"(taddr + h * 32 + g16 * 16), "r"(w[16 * g16]), "r"(w[16 * g16 + 1]), "r"(w[16 * g16 + 2]), "r"(w[16 * g16 + 3]),
+                             "r"(w[16 * g16 + 4]), "r"(w[16 * g16 + 5]), "r"(w[16 * g16 + 6]), "r"(w[16 * g16 + 7]), "r"(w[16 * g16 + 8]),
+                             "r"(w[16 * g16 + 9]), "r"(w[16 * g16 + 10]), "r"(w[16 * g16 + 11]), "r"(w[16 * g16 + 12]), "r"(w[16 * g16 + 13]),
+                             "r"(w[16 * g16 + 14]), "r"(w[16 * g16 + 15]) : "memory");
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          tc_fence_before();
+          mbar_arrive(aFullBar + 8 * slot.idx);
+          slot.next();
+          continue;
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int off = t * 16 + i * 2048; // the swizzle is the same in both images: work on raw offsets
@@ -416,7 +466,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
           const int st = ring.idx;
           mbar_wait(emptyBar + 8 * st, ring.phase ^ 1, 3);
           mbar_arrive_expect_tx(fullBar + 8 * st, bytes);
-          bulk_g2s(smem_u32(smem + (size_t)st * stageBytes + 2 * A_HALF), srcBase + (size_t)q * bytes, bytes, fullBar + 8 * st);
+          bulk_g2s(smem_u32(smem + (size_t)st * stageBytes + aBytes), srcBase + (size_t)q * bytes, bytes, fullBar + 8 * st);
         }
       }
     }
@@ -424,7 +474,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
     // ------------------------------------------------------------ MMA issue
     if (lane == 0) {
       int n = 0;
-      Ring ring(P.stages);
+      Ring ring(P.stages), slot(P.atmem ? P.atmem : 1);
       for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++n) {
         int tileM, tileN, slab0, nLoc;
         itemTile(item, tileM, tileN, slab0, nLoc);
@@ -437,8 +487,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
           mbar_wait(fullBar + 8 * st, ring.phase, 4);
           tc_fence_after();
           const uint32_t aHi = smem_u32(smem + (size_t)st * stageBytes), aLo = aHi + A_HALF;
-          const uint32_t bHi = aHi + 2 * A_HALF, bLo = bHi + bHalf;
+          const uint32_t bHi = aHi + aBytes, bLo = bHi + bHalf;
           const uint64_t dAhi = smem_desc(aHi), dAlo = smem_desc(aLo), dBhi = smem_desc(bHi), dBlo = smem_desc(bLo);
+          if (ATMEM) {
+            mbar_wait(aFullBar + 8 * slot.idx, slot.phase, 9);
+            tc_fence_after();
+            const uint32_t tHi = tmem + (uint32_t)(2 * P.accStride + slot.idx * 64), tLo = tHi + 32;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_tf32_ts(acc, tLo + 8 * k, dBhi + 2 * k, P.idesc, (q | k) != 0);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_tf32_ts(acc, tHi + 8 * k, dBlo + 2 * k, P.idesc, 1);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_tf32_ts(acc, tHi + 8 * k, dBhi + 2 * k, P.idesc, 1);
+            mma_commit(emptyBar + 8 * st);
+            mma_commit(aEmptyBar + 8 * slot.idx);
+            slot.next();
+            continue;
+          }
           // small cross terms first, the dominant hi*hi product last
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_tf32(acc, dAlo + 2 * k, dBhi + 2 * k, P.idesc, (q | k) != 0);
@@ -825,15 +890,19 @@ int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) 
   return k < 2 ? 1 : k;
 }
 
-struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, rulesDouble, accStride; size_t smemBytes; };
+struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, rulesDouble, accStride, atmem; size_t smemBytes; };
 
 bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
   if (K < 1 || N < 16) return false;
   t->rulesBytes = (haveRules && fs <= 32) ? BM * fs * 4 : 0;
-  t->nTiles = (N + 255) / 256;
+  t->nTiles = (N + 255) / 256; // narrower tiles (so that every layer could use the tensor-memory A path) were measured slower: A is gathered once per column tile
   t->BN = ((N + t->nTiles - 1) / t->nTiles + 15) / 16 * 16;
   t->nSlabs = (K + SLAB - 1) / SLAB; // the last slab is zero-padded
-  const int stageBytes = 2 * A_HALF + 2 * t->BN * ROW_BYTES;
+  t->accStride = (t->BN + 31) / 32 * 32;
+  // 64-column A slots in tensor memory beside the two accumulators: two (BN <= 192) or none, A then stays in
+  // shared memory (a single slot serialises split and MMA and was measured slower); short K gains nothing
+  t->atmem = (t->nSlabs >= 4 && 2 * t->accStride + 128 <= 512) ? 2 : 0;
+  const int stageBytes = (t->atmem ? 1 : 2) * A_HALF + 2 * t->BN * ROW_BYTES;
   auto stagesWith = [&](int ruleBufs) {
     const int n = (int)((226 * 1024 - 1024 - ruleBufs * t->rulesBytes - EPI_BYTES) / stageBytes);
     return n > MAX_STAGES ? MAX_STAGES : n;
@@ -842,9 +911,8 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
   if (stages < 2) return false;
   t->stages = stages;
   t->rulesDouble = (t->rulesBytes > 0 && stagesWith(2) == stages) ? 1 : 0; // prefetch the next tile's rules if that costs no stage
-  t->accStride = (t->BN + 31) / 32 * 32;
   int cols = 32;
-  while (cols < 2 * t->accStride) cols *= 2; // two accumulators, at most 2 x 256 columns
+  while (cols < 2 * t->accStride + 64 * t->atmem) cols *= 2; // two accumulators [+ the A slots], at most 512 columns
   t->tmemCols = cols;
   t->smemBytes = (size_t)stages * stageBytes + 1024 + (size_t)(1 + t->rulesDouble) * t->rulesBytes + EPI_BYTES;
   return true;
@@ -954,7 +1022,7 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   if (!ok || (nIn % SLAB == 0 && nIn > ZERO_ROW_FLOATS)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
   if (((uintptr_t)d_in | (uintptr_t)d_out | (uintptr_t)d_packed) & 15) return fail(SCN_ERR_INVALID, "tensor-core path needs 16-byte aligned buffers");
   Params P;
-  P.rawEntries = rawEntries; P.nStages64 = nStages64;
+  P.rawEntries = rawEntries; P.nStages64 = nStages64; P.atmem = passes ? 0 : t.atmem;
   P.in = d_in; P.rules = d_rules; P.rows = rows; P.fs = fs; P.nIn = nIn;
   P.packed = (const unsigned char *)d_packed; P.bias = d_B; P.prelu = d_prelu;
   P.N = N; P.BN = t.BN; P.nTiles = t.nTiles; P.nSlabs = t.nSlabs; P.stages = t.stages; P.tmemCols = t.tmemCols; P.rulesBytes = t.rulesBytes;
@@ -982,12 +1050,18 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   } while (0)
   if (passes == 3) SCN_TC16_LAUNCH(3);
   else if (passes == 1) SCN_TC16_LAUNCH(1);
-  else if (P.kSplit > 1) {
-    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<true, SCN_NOSIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    k_conv_nin_tc<true, SCN_NOSIGMOID><<<grid, NUM_THREADS, t.smemBytes, s>>>(P);
+  else if (P.atmem && P.kSplit > 1) {
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<true, SCN_NOSIGMOID, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    k_conv_nin_tc<true, SCN_NOSIGMOID, true><<<grid, NUM_THREADS, t.smemBytes, s>>>(P);
+  } else if (P.atmem) {
+    SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+                     (k_conv_nin_tc<false, ACT, true><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
+  } else if (P.kSplit > 1) {
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<true, SCN_NOSIGMOID, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+    k_conv_nin_tc<true, SCN_NOSIGMOID, false><<<grid, NUM_THREADS, t.smemBytes, s>>>(P);
   } else {
-    SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-                     (k_conv_nin_tc<false, ACT><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
+    SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+                     (k_conv_nin_tc<false, ACT, false><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
   }
 #undef SCN_TC16_LAUNCH
   SCN_LAUNCH_CHECK("k_conv_nin_tc");
