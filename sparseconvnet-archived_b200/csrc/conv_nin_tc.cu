@@ -128,7 +128,7 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
-  int mTiles, accStride, K, generic, rulesDouble, rawEntries, nStages64, atmem; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
+  int mTiles, accStride, K, generic, rulesDouble, rawEntries, nStages64, atmem, aBase; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
@@ -414,7 +414,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
           mbar_wait(aEmptyBar + 8 * slot.idx, slot.phase ^ 1, 8); // the MMAs that read this slot have finished
           tc_fence_after();
           // lanes 32*(warp % 4)..+31 belong to this warp; hi image at columns +0..31, lo at +32..63
-          const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(2 * P.accStride + slot.idx * 64);
+          const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(P.aBase + slot.idx * 64);
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             uint32_t w[32];
@@ -492,7 +492,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
           if (ATMEM) {
             mbar_wait(aFullBar + 8 * slot.idx, slot.phase, 9);
             tc_fence_after();
-            const uint32_t tHi = tmem + (uint32_t)(2 * P.accStride + slot.idx * 64), tLo = tHi + 32;
+            const uint32_t tHi = tmem + (uint32_t)(P.aBase + slot.idx * 64), tLo = tHi + 32;
 #pragma unroll
             for (int k = 0; k < 4; ++k) mma_tf32_ts(acc, tLo + 8 * k, dBhi + 2 * k, P.idesc, (q | k) != 0);
 #pragma unroll
@@ -890,9 +890,11 @@ int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) 
   return k < 2 ? 1 : k;
 }
 
-struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, rulesDouble, accStride, atmem; size_t smemBytes; };
+struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, rulesDouble, accStride, atmem, aBase; size_t smemBytes; };
 
-bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
+// oneItem: no CTA gets more than one work item, so the second accumulator is never used and its columns can
+// hold the A slots: the tensor-memory A path then reaches BN = 256.
+bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool oneItem = false) {
   if (K < 1 || N < 16) return false;
   t->rulesBytes = (haveRules && fs <= 32) ? BM * fs * 4 : 0;
   t->nTiles = (N + 255) / 256; // narrower tiles (so that every layer could use the tensor-memory A path) were measured slower: A is gathered once per column tile
@@ -901,7 +903,8 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
   t->accStride = (t->BN + 31) / 32 * 32;
   // 64-column A slots in tensor memory beside the two accumulators: two (BN <= 192) or none, A then stays in
   // shared memory (a single slot serialises split and MMA and was measured slower); short K gains nothing
-  t->atmem = (t->nSlabs >= 4 && 2 * t->accStride + 128 <= 512) ? 2 : 0;
+  t->aBase = (oneItem ? 1 : 2) * t->accStride;
+  t->atmem = (t->nSlabs >= 4 && t->aBase + 128 <= 512) ? 2 : 0;
   const int stageBytes = (t->atmem ? 1 : 2) * A_HALF + 2 * t->BN * ROW_BYTES;
   auto stagesWith = [&](int ruleBufs) {
     const int n = (int)((226 * 1024 - 1024 - ruleBufs * t->rulesBytes - EPI_BYTES) / stageBytes);
@@ -912,7 +915,7 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t) {
   t->stages = stages;
   t->rulesDouble = (t->rulesBytes > 0 && stagesWith(2) == stages) ? 1 : 0; // prefetch the next tile's rules if that costs no stage
   int cols = 32;
-  while (cols < 2 * t->accStride + 64 * t->atmem) cols *= 2; // two accumulators [+ the A slots], at most 512 columns
+  while (cols < (t->atmem ? t->aBase + 128 : 2 * t->accStride)) cols *= 2; // the accumulators [+ the A slots], at most 512 columns
   t->tmemCols = cols;
   t->smemBytes = (size_t)stages * stageBytes + 1024 + (size_t)(1 + t->rulesDouble) * t->rulesBytes + EPI_BYTES;
   return true;
@@ -1022,7 +1025,10 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   if (!ok || (nIn % SLAB == 0 && nIn > ZERO_ROW_FLOATS)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
   if (((uintptr_t)d_in | (uintptr_t)d_out | (uintptr_t)d_packed) & 15) return fail(SCN_ERR_INVALID, "tensor-core path needs 16-byte aligned buffers");
   Params P;
-  P.rawEntries = rawEntries; P.nStages64 = nStages64; P.atmem = passes ? 0 : t.atmem;
+  const int mTiles = (rows + BM - 1) / BM;
+  int kSplit = (d_ws && ((uintptr_t)d_ws & 15) == 0) ? choose_ksplit(mTiles * t.nTiles, passes ? 2 * nStages64 : t.nSlabs, rows, N, wsBytes) : 1;
+  if (!passes && !t.atmem && mTiles * t.nTiles * kSplit <= sm_count()) make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, true);
+  P.rawEntries = rawEntries; P.nStages64 = nStages64; P.atmem = passes ? 0 : t.atmem; P.aBase = t.aBase;
   P.in = d_in; P.rules = d_rules; P.rows = rows; P.fs = fs; P.nIn = nIn;
   P.packed = (const unsigned char *)d_packed; P.bias = d_B; P.prelu = d_prelu;
   P.N = N; P.BN = t.BN; P.nTiles = t.nTiles; P.nSlabs = t.nSlabs; P.stages = t.stages; P.tmemCols = t.tmemCols; P.rulesBytes = t.rulesBytes;
@@ -1030,8 +1036,7 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   // instruction descriptor: D = fp32, A = B = tf32 (2) or bf16 (1), both K-major, N = BN, M = 128
   const uint32_t fmt = passes ? 1u : 2u;
   P.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(t.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-  const int mTiles = (rows + BM - 1) / BM;
-  P.kSplit = (d_ws && ((uintptr_t)d_ws & 15) == 0) ? choose_ksplit(mTiles * t.nTiles, passes ? 2 * nStages64 : t.nSlabs, rows, N, wsBytes) : 1;
+  P.kSplit = kSplit;
   P.partial = (float *)d_ws;
   P.mTiles = mTiles; P.accStride = t.accStride;
   P.K = fs * nIn; P.generic = (nIn % SLAB != 0) ? 1 : 0;
