@@ -311,15 +311,20 @@ def main():
         for j in range(args.warmup):
             step_device(j)
         drain()
-        gnet.enable_timing(True)
         barrier()
         t_load0 = time.time()
         launches0 = abi.kernel_launch_count()
         t_wall = time.time()
-        ms_dev, layer_ms = timed(step_device, args.steps, True)
+        ms_dev, _ = timed(step_device, args.steps, False)
         barrier()
         t_wall = time.time() - t_wall
         launches = abi.kernel_launch_count() - launches0
+        # Per-kernel durations for the roofline and the breakdown: the same steps once more with a CUDA
+        # event between the layers.  (Those events cost about 0.06 ms of GPU idle per step, which is why
+        # they are kept out of the steps that `value` is computed from.)
+        gnet.enable_timing(True)
+        _, layer_ms = timed(step_device, args.steps, True)
+        barrier()
         gnet.enable_timing(False)
         # ---- host-buffer leg
         for j in range(args.warmup):
@@ -412,7 +417,7 @@ def main():
             dtype="f32" if args.precision == "fp32" else ("bf16" if args.precision == "bf16" else "tf32x3/f32"), data="synthetic",
             config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample, all-gather of probabilities%s" % (world, " (step j's gather overlaps step j+1 in the device leg)" if world > 1 else ""),
                         l2="256 MiB written between timed steps; 2 distinct batches rotated", precision=args.precision,
-                        timing="CUDA events per step on the launching stream, max over ranks; wall %.3f s for the device leg" % t_wall),
+                        timing="CUDA events per step on the launching stream, max over ranks; wall %.3f s for the device leg; per-kernel durations from a second pass of the same steps with events between the layers" % t_wall),
             e2e=dict(value=total / (ms_e2e * 1e-3), unit="samples/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                      ms_per_step=ms_e2e / args.steps),
             gpu_launches=int(launches), roofline=roof, cpu_baseline=cpu, clocks=clocks,

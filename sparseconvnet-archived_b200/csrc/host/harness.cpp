@@ -19,6 +19,14 @@ struct scn_net {
   int lattice;
   SpatiallySparseBatch *last; // batch of the last forward
   vectorCUDA<int> top;
+  // scn_net_forward_host uploads the features on a stream of their own, so that the copy (three
+  // quarters of the input bytes) runs while the rule chain, which needs only keys and offsets, is built
+  cudaStream_t copyStream = nullptr;
+  cudaEvent_t copyDone = nullptr;
+  ~scn_net() {
+    if (copyDone) cudaEventDestroy(copyDone);
+    if (copyStream) cudaStreamDestroy(copyStream);
+  }
 };
 
 namespace {
@@ -237,9 +245,20 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *
     cudaStream_t s = cnn.memStream.stream;
     if (rows) cudaSafeCall(cudaMemcpyAsync(in.siteKeys.dPtr(), sk, kb, cudaMemcpyHostToDevice, s));
     cudaSafeCall(cudaMemcpyAsync(in.sampleOffsets.dPtr(), so, ob, cudaMemcpyHostToDevice, s));
-    if (rows) cudaSafeCall(cudaMemcpyAsync(in.sub->features.dPtr(), sf, fb, cudaMemcpyHostToDevice, s));
+    if (!net->copyStream) {
+      cudaSafeCall(cudaStreamCreateWithFlags(&net->copyStream, cudaStreamNonBlocking));
+      cudaSafeCall(cudaEventCreateWithFlags(&net->copyDone, cudaEventDisableTiming));
+    }
+    if (rows) { // nothing is in flight on the features buffer: the previous forward ended with a host wait
+      float *dst = in.sub->features.dPtr();
+      cudaSafeCall(cudaEventRecord(net->copyDone, s)); // ... but the resize above may have enqueued work on s
+      cudaSafeCall(cudaStreamWaitEvent(net->copyStream, net->copyDone, 0));
+      cudaSafeCall(cudaMemcpyAsync(dst, sf, fb, cudaMemcpyHostToDevice, net->copyStream));
+      cudaSafeCall(cudaEventRecord(net->copyDone, net->copyStream));
+    }
     scnSafeCall(scn_background_rows(in.siteKeys.dPtr(), in.sampleOffsets.dPtr(), batch, in.backgroundRows.dPtr(), s));
-    cnn.preprocessBatchOnDevice(b); // waits once, after the uploads and the rule chain
+    cnn.preprocessBatchOnDevice(b); // waits once, after the key upload and the rule chain
+    if (rows) cudaSafeCall(cudaStreamWaitEvent(s, net->copyDone, 0)); // the layers read the features
     std::ofstream nof, nog;
     cnn.processBatch(b, 0, 0, nof, nog);
     net->last = &b;
