@@ -746,6 +746,22 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
       atomicMax(L.result + 3, sitesOut);
       sBase = 0; sSitesBase = 0;
     }
+    // 7a. output keys into the shared copy (the next layer's input): needs no other sample, so it runs
+    // while the published count travels and the earlier samples' counts arrive
+    if (rowsOut <= P.rowsMax) {
+      for (int p = tid; p < nSites * R.T; p += NT) {
+        if (!flags[p]) continue;
+        int t;
+        const int slot = fdiv(p, R.T, R.rT, &t);
+        int rank = 0;
+        for (int q = 0; q < t; ++q) rank += flags[slot * R.T + q];
+        int i[DIM], j[DIM];
+        decode_f<DIM>(inKeys[sorted[slot]], R.nIn, R.rNIn, i);
+        touched_output_f<DIM>(R, i, t, j);
+        outKeysS[cnt[slot] + rank] = encode_f<DIM>(j, R.nOut);
+      }
+      if (needBg && tid == 0) outKeysS[sitesOut] = -1;
+    }
     __syncthreads();
     {
       int rowsBefore = 0, bgBefore = 0;
@@ -781,23 +797,8 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
       if (tid == 0) for (int l2 = l + 1; l2 < P.nLayers; ++l2) P.counts[l2 * P.batch + b] = 0;
       return;
     }
-    // 7. output keys (shared copy for the next layer + the interface's array)
-    for (int p = tid; p < nSites * R.T; p += NT) {
-      if (!flags[p]) continue;
-      int t;
-      const int slot = fdiv(p, R.T, R.rT, &t);
-      int rank = 0;
-      for (int q = 0; q < t; ++q) rank += flags[slot * R.T + q];
-      int i[DIM], j[DIM];
-      decode_f<DIM>(inKeys[sorted[slot]], R.nIn, R.rNIn, i);
-      touched_output_f<DIM>(R, i, t, j);
-      const int key = encode_f<DIM>(j, R.nOut);
-      const int lo = cnt[slot] + rank;
-      outKeysS[lo] = key;
-      L.outKeys[base + lo] = key;
-    }
-    if (needBg && tid == 0) { outKeysS[sitesOut] = -1; L.outKeys[base + sitesOut] = -1; }
-    __syncthreads();
+    // 7b. the interface's copy of the output keys (coalesced)
+    for (int r = tid; r < rowsOut; r += NT) L.outKeys[base + r] = outKeysS[r];
     // 8. rule cells, coalesced over this sample's block of rows
     for (int q = tid; q < rowsOut * R.sd; q += NT) {
       int col;
