@@ -208,6 +208,16 @@ int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, int rows_out,
                             const float *d_prelu, int N, float p, int act, int precision,
                             float *d_out, void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
 
+/* The same fused layer launched before the host knows the row count: rows_out_bound is an upper
+ * bound (d_out and d_rules are sized for it), the kernel reads the count itself from *d_rows_out,
+ * where an earlier call on the same stream (scn_rules_build's d_result[0], say) leaves it.  3xTF32
+ * tensor-core kernel only (weights packed for SCN_PREC_3XTF32; SCN_ERR_UNSUPPORTED for other shapes),
+ * no softmax.  It lets the first layer of a network start while the rulebooks' counts travel to the host.
+ * No reference counterpart. */
+int scn_conv_nin_forward_dyn(const float *d_in, const int *d_rules, int rows_out_bound, const int *d_rows_out,
+                             int fs, int nIn, const void *d_W_packed, const float *d_B, const float *d_prelu,
+                             int N, float p, int activation, float *d_out, scn_stream_t stream);
+
 /* One-time repack of W[K x N] (K = fs*nIn) for a tensor-core precision: bytes needed, then
  * the packing kernel.  No reference counterpart (the reference hands W to cuBLAS as is). */
 size_t scn_conv_packed_weight_bytes(int K, int N, int precision);

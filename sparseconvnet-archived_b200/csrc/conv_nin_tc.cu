@@ -128,7 +128,7 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
-  int mTiles, accStride, K, generic, rulesDouble, rawEntries, nStages64, atmem, aBase; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
+  int mTiles, accStride, K, generic, rulesDouble, rawEntries, nStages64, atmem, aBase; const int *rowsPtr; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
@@ -161,7 +161,7 @@ constexpr int EPI_BYTES = BM * EPI_LD * 4;        // 18 KB
 // while the main loop fills the other one.
 template <bool SPLIT, int ACT>
 __device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint32_t tmem, uint32_t accFullBar, uint32_t accEmptyBar,
-                                              int nItems, int kSplit) {
+                                              int nItems, int kSplit, int rows) {
   const int warp = threadIdx.x >> 5;
   const int t = threadIdx.x;
   const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
@@ -205,10 +205,10 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint3
 #pragma unroll
       for (int pass = 0; pass < BM / 16; ++pass) {
         const int rl = pass * 16 + rsub, r = row0 + rl;
-        if (!colOk || r >= P.rows) continue;
+        if (!colOk || r >= rows) continue;
         const float4 v = *reinterpret_cast<const float4 *>(epi + (size_t)rl * EPI_LD + c4 * 4);
         if (SPLIT) {
-          *reinterpret_cast<float4 *>(P.partial + ((long long)split * P.rows + r) * P.N + col) = v;
+          *reinterpret_cast<float4 *>(P.partial + ((long long)split * rows + r) * P.N + col) = v;
         } else {
           float4 o;
           // NetworkInNetworkLayer.cu:187-195: alpha = beta = p over a bias-filled output
@@ -247,8 +247,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
                  accFullBar = smem_u32(&bars[3 * MAX_STAGES]), accEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 2]),
                  aFullBar = smem_u32(&bars[3 * MAX_STAGES + 4]), aEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 6]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the row count may still be on its way to the host when this kernel is launched: read it from device memory
+  const int rows = P.rowsPtr ? min(max(__ldg(P.rowsPtr), 0), P.rows) : P.rows;
+  const int mTiles = P.rowsPtr ? (rows + BM - 1) / BM : P.mTiles;
   const int kSplit = SPLIT ? P.kSplit : 1;
-  const int nItems = P.mTiles * P.nTiles * kSplit;
+  const int nItems = mTiles * P.nTiles * kSplit;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P.stages; ++s) {
@@ -281,7 +284,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   };
 
   if (warp < 4) {
-    epilogue_role<SPLIT, ACT>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit);
+    epilogue_role<SPLIT, ACT>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows);
   } else if (warp < 8) {
     // ------------------------------------------------------------ gather: asynchronous 16-byte copies
     const int t = threadIdx.x - 128, chunk = t & 7, rbase = t >> 3;
@@ -294,7 +297,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
     auto stage_rules_async = [&](int item, int buf) {
       int tileM, tileN, slab0, nLoc;
       itemTile(item, tileM, tileN, slab0, nLoc);
-      const long long first = (long long)tileM * BM * P.fs, total = (long long)P.rows * P.fs;
+      const long long first = (long long)tileM * BM * P.fs, total = (long long)rows * P.fs;
       const uint32_t dst = smem_u32(rulesS) + buf * P.rulesBytes;
       for (int ch = t; ch < BM * P.fs / 4; ch += 128) {
         const long long left = total - (first + ch * 4);
@@ -318,7 +321,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
       } else if (P.rulesBytes > 0) { // synchronous staging (rule pointer not 16-byte aligned, or no room for two buffers)
         asm volatile("bar.sync 2, 128;" ::: "memory"); // everyone has issued the previous item's copies
         const int nr = BM * P.fs;
-        for (int e = t; e < nr; e += 128) rulesS[e] = __ldg(P.rules + min((long long)row0 * P.fs + e, (long long)P.rows * P.fs - 1));
+        for (int e = t; e < nr; e += 128) rulesS[e] = __ldg(P.rules + min((long long)row0 * P.fs + e, (long long)rows * P.fs - 1));
         asm volatile("bar.sync 2, 128;" ::: "memory");
       }
       if (P.generic) {
@@ -346,7 +349,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
             for (int j = 0; j < 8; ++j) {
               const int rl = wq * 32 + i0 + j, r = row0 + rl;
               src[j] = -1;
-              if (kOk && r < P.rows) {
+              if (kOk && r < rows) {
                 if (P.rulesBytes > 0) src[j] = rulesT[rl * P.fs + f];
                 else if (P.rules) src[j] = __ldg(P.rules + (long long)r * P.fs + f);
                 else src[j] = r;
@@ -374,7 +377,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
           for (int i = 0; i < 8; ++i) {
             const int rl = rbase + 16 * i, r = row0 + rl;
             int src = -1;
-            if (r < P.rows) {
+            if (r < rows) {
               if (P.rulesBytes > 0) src = rulesT[rl * P.fs + f];
               else if (P.rules) src = __ldg(P.rules + (long long)r * P.fs + f);
               else src = r;
@@ -603,7 +606,7 @@ __global__ void __launch_bounds__(NUM_THREADS16, 1) k_conv_nin_tc16(const Params
   };
 
   if (warp < 4) {
-    epilogue_role<SPLIT, ACT>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit);
+    epilogue_role<SPLIT, ACT>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, P.rows);
   } else if (warp < 8) {
     // ------------------------------------------------------------ gather into the raw ring
     const int t = threadIdx.x - 128, chunk = t & 7, rbase = t >> 3;
@@ -1016,7 +1019,7 @@ size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision) {
 
 int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed, const float *d_B,
               const float *d_prelu, int N, float p, int act, int precision, float *d_out, void *d_ws, size_t wsBytes,
-              cudaStream_t s) {
+              cudaStream_t s, const int *d_rows) {
   Tiling t;
   const int passes = passes_of(precision);
   int rawEntries = 0, nStages64 = 0;
@@ -1029,6 +1032,8 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   int kSplit = (d_ws && ((uintptr_t)d_ws & 15) == 0) ? choose_ksplit(mTiles * t.nTiles, passes ? 2 * nStages64 : t.nSlabs, rows, N, wsBytes) : 1;
   if (!passes && !t.atmem && mTiles * t.nTiles * kSplit <= sm_count()) make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, true);
   P.rawEntries = rawEntries; P.nStages64 = nStages64; P.atmem = passes ? 0 : t.atmem; P.aBase = t.aBase;
+  if (d_rows && (passes || kSplit > 1)) return fail(SCN_ERR_UNSUPPORTED, "a device-side row count needs the 3xTF32 kernel without K split");
+  P.rowsPtr = d_rows;
   P.in = d_in; P.rules = d_rules; P.rows = rows; P.fs = fs; P.nIn = nIn;
   P.packed = (const unsigned char *)d_packed; P.bias = d_B; P.prelu = d_prelu;
   P.N = N; P.BN = t.BN; P.nTiles = t.nTiles; P.nSlabs = t.nSlabs; P.stages = t.stages; P.tmemCols = t.tmemCols; P.rulesBytes = t.rulesBytes;

@@ -12,7 +12,9 @@ int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaS
 size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision);
 int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed,
               const float *d_B, const float *d_prelu, int N, float p, int act, int precision, float *d_out,
-              void *d_ws, size_t wsBytes, cudaStream_t s);
+              void *d_ws, size_t wsBytes, cudaStream_t s, const int *d_rows = nullptr);
+// d_rows: when not null the kernel takes its row count from there (clamped to `rows`, which then is an
+// upper bound); 3xTF32 without K split only.
 // Error code a bounded wait of the kernel recorded since the last call (0 = none); waits for
 // the device and clears it.  1 gather/empty, 2 epilogue/accumulator, 3 weight copy/empty, 4 MMA/full.
 int tc_take_error();

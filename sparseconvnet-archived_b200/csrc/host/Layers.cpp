@@ -429,6 +429,26 @@ void NetworkInNetworkLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySpa
   enqueueRules(batch, input, output, input.nSpatialSites, nullptr);
   finishRules(batch, input, output, nullptr);
 }
+bool NetworkInNetworkLayer::forwardsEarly(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &source, SpatiallySparseBatchInterface &input,
+                                          SpatiallySparseBatchInterface &output, int cells, long long rowsBound, const int *d_rows) {
+  if (batch.type == TRAINBATCH || rowsBound < 1 || rowsBound * (long long)nFeaturesOut > INT_MAX) return false;
+  if ((precision != SCN_PREC_AUTO && precision != SCN_PREC_3XTF32) || scn_conv_auto_precision() != SCN_PREC_3XTF32) return false;
+  if (fn == SOFTMAX || nFeaturesOut % 4 != 0 || nFeaturesIn % cells != 0) return false;
+  const int nIn = nFeaturesIn / cells;
+  const void *pk = packedWeights(cells, nIn, SCN_PREC_3XTF32);
+  if (!pk) return false;
+  output.sub->features.resize((int)(rowsBound * nFeaturesOut));
+  const float p = 1.0f - (batch.type != RESCALEBATCH ? dropout : 0.0f);
+  const int rc = scn_conv_nin_forward_dyn(source.sub->features.dPtr(), input.rules.dPtr(), (int)rowsBound, d_rows, cells, nIn, pk, B.dPtr(), slopes(),
+                                          nFeaturesOut, p, (int)fn, output.sub->features.dPtr(), memStream.stream);
+  if (rc == SCN_ERR_UNSUPPORTED) return false; // e.g. so few rows that K would be split
+  scnSafeCall(rc);
+  return true;
+}
+void NetworkInNetworkLayer::finishEarly(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  output.sub->features.resize(output.nSpatialSites * output.featuresPresent.size());
+  multiplyAddCount += (__int128_t)output.nSpatialSites * input.featuresPresent.size() * output.featuresPresent.size();
+}
 void NetworkInNetworkLayer::forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
   requireInference(batch);
   output.sub->features.resize(output.nSpatialSites * output.featuresPresent.size());

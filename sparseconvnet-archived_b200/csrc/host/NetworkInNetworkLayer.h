@@ -32,6 +32,13 @@ public:
   // Call after writing W directly (e.g. W.hVector()[i] = ...): drops the packed copy the
   // tensor-core kernel reads.
   void weightsChanged();
+  // forwards() of a fused convolution + this layer before the host knows the row count: rowsBound is an
+  // upper bound (rules and output are sized for it), the kernel reads the count from d_rows.  Returns
+  // false (nothing launched) unless the 3xTF32 tensor-core kernel takes the shape without a K split.
+  bool forwardsEarly(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &source, SpatiallySparseBatchInterface &input,
+                     SpatiallySparseBatchInterface &output, int cells, long long rowsBound, const int *d_rows);
+  // The bookkeeping forwards() would have done, once the counts are known.
+  void finishEarly(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
 
 protected:
   virtual float *slopes(); // per-channel PReLU slopes, or nullptr

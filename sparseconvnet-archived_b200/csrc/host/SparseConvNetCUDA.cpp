@@ -17,6 +17,9 @@ void SparseConvNetCUDA::init(int nInputFeatures_, int nClasses_) {
   std::cout << "Sparse CNN - dimension=" << dimension << " nInputFeatures=" << nInputFeatures_ << " nClasses=" << nClasses_ << std::endl;
   nOutputFeatures = nInputFeatures_;
   timing = false;
+  // off by default: with BatchProducer threads the next batch is preprocessed while the current one is
+  // still in its layers, and the features buffers behind the first layers are shared by the batch pool
+  earlyFirstLayer = false; earlyLayers = 0; inputReady = nullptr; countStream = nullptr; chainDone = nullptr;
   chainRowsHint = 0;
   inputSpatialSize = 0;
   cublasHandle = nullptr;
@@ -41,6 +44,8 @@ SparseConvNetCUDA::SparseConvNetCUDA(int dimension, int nInputFeatures, int nCla
 SparseConvNetCUDA::~SparseConvNetCUDA() {
   cudaStreamSynchronize(memStream.stream);
   for (auto e : events) cudaEventDestroy(e);
+  if (chainDone) cudaEventDestroy(chainDone);
+  if (countStream) cudaStreamDestroy(countStream);
   for (auto p : layers) delete p;
   batchPool.clear();
   for (auto p : initialSubInterfaces) delete p;
@@ -151,7 +156,8 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
   const int nL = (int)layers.size();
   chainResults.resize(4 * nL + 4);
   int *d_res = chainResults.dPtr();
-  long long bound = batch.interfaces[0].nSpatialSites;
+  long long bound = batch.interfaces[0].nSpatialSites, bound0 = 0;
+  earlyLayers = 0;
   if (timing) cudaSafeCall(cudaEventRecord(events[nL + 1], memStream.stream));
   // Without terminal pooling (whose build reads its input grid at once) the region builds are
   // only recorded here and then run together: one fused kernel when the samples are small.
@@ -160,8 +166,10 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
   std::vector<rulechain::DeferredBuild> builds;
   if (defer) rulechain::beginDeferred(&builds);
   try {
-    for (int i = 0; i < nL; ++i)
+    for (int i = 0; i < nL; ++i) {
       bound = layers[i]->enqueueRules(batch, batch.interfaces[i], batch.interfaces[i + 1], bound, d_res + 4 * i);
+      if (i == 0) bound0 = bound;
+    }
   } catch (...) {
     rulechain::endDeferred();
     throw;
@@ -172,14 +180,41 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
     hinted = rulechain::runDeferred(builds, batch.batchSize, batch.interfaces[0].maxSitesPerSample + 1, chainRowsHint, memStream);
   }
   if (timing) cudaSafeCall(cudaEventRecord(events[nL + 2], memStream.stream));
+  if (inputReady) { // the features were uploaded on another stream while the rules were built
+    cudaSafeCall(cudaStreamWaitEvent(memStream.stream, inputReady, 0));
+    inputReady = nullptr;
+  }
   int *h = (int *)memStream.staging(sizeof(int) * 4 * nL);
-  cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, memStream.stream));
-  cudaSafeCall(cudaStreamSynchronize(memStream.stream)); // the one host wait of the rule chain
+  bool countsRead = false;
+  if (earlyFirstLayer && !timing && defer && nL >= 2) {
+    ConvolutionalLayer *conv = dynamic_cast<ConvolutionalLayer *>(layers[0]);
+    NetworkInNetworkLayer *nin = dynamic_cast<NetworkInNetworkLayer *>(layers[1]);
+    if (conv && conv->fuseWithNext && nin) {
+      if (!countStream) {
+        cudaSafeCall(cudaStreamCreateWithFlags(&countStream, cudaStreamNonBlocking));
+        cudaSafeCall(cudaEventCreateWithFlags(&chainDone, cudaEventDisableTiming));
+      }
+      cudaSafeCall(cudaEventRecord(chainDone, memStream.stream));
+      if (nin->forwardsEarly(batch, batch.interfaces[0], batch.interfaces[1], batch.interfaces[2], ipow(conv->filterSize, conv->dimension), bound0, d_res)) {
+        earlyLayers = 2;
+        // the counts come back on their own stream, behind the rule chain only, while the first layer runs
+        cudaSafeCall(cudaStreamWaitEvent(countStream, chainDone, 0));
+        cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, countStream));
+        cudaSafeCall(cudaStreamSynchronize(countStream));
+        countsRead = true;
+      }
+    }
+  }
+  if (!countsRead) {
+    cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, memStream.stream));
+    cudaSafeCall(cudaStreamSynchronize(memStream.stream)); // the one host wait of the rule chain
+  }
   std::vector<int> counts(h, h + 4 * nL); // staging is reused below
   if (hinted) { // a sample outgrew the shared-memory hint learnt from earlier batches: rebuild for the worst case
     bool overflow = false;
     for (int i = 0; i < nL; ++i) overflow = overflow || (layers[i]->changesGeometry && (counts[4 * i + 2] & SCN_DEV_ERR_CAPACITY));
     if (overflow) {
+      earlyLayers = 0; // the early kernel ran on truncated rules: the layers run again from the first
       chainRowsHint = 0;
       rulechain::runDeferred(builds, batch.batchSize, batch.interfaces[0].maxSitesPerSample + 1, 0, memStream);
       cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, memStream.stream));
@@ -198,6 +233,10 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
 void SparseConvNetCUDA::forwardLayers(SpatiallySparseBatch &batch) {
   for (size_t i = 0; i < layers.size(); ++i) {
     if (timing) cudaSafeCall(cudaEventRecord(events[i], memStream.stream));
+    if ((int)i == 1 && earlyLayers == 2) { // already running: launched behind the rule chain
+      static_cast<NetworkInNetworkLayer *>(layers[1])->finishEarly(batch.interfaces[1], batch.interfaces[2]);
+      continue;
+    }
     batch.interfaces[i + 1].sub->reset();
     batch.interfaces[i + 1].deferredFrom = nullptr;
     layers[i]->forwards(batch, batch.interfaces[i], batch.interfaces[i + 1]);

@@ -13,6 +13,13 @@
 
 class SparseConvNetCUDA {
 public:
+  // The first convolution + NiN pair is launched right behind the rule chain, before the row counts are
+  // read back (its kernel takes its count from device memory), so the GPU works while the host waits.
+  bool earlyFirstLayer;
+  int earlyLayers;          // layers of the current batch already launched by preprocessBatchOnDevice (0 or 2)
+  cudaStream_t countStream; // the row counts are read back on this stream, so that the early first layer does not delay them
+  cudaEvent_t chainDone;
+  cudaEvent_t inputReady;   // if set: the input features are complete once this event has happened (waited for once, then cleared)
   std::vector<SpatiallySparseLayer *> layers; // owned
   std::vector<float> inputNormalizingConstants;
   int dimension, nClasses, nTop, inputSpatialSize, nInputFeatures, nOutputFeatures, deviceID, nBatchProducerThreads;

@@ -257,8 +257,10 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *
       cudaSafeCall(cudaEventRecord(net->copyDone, net->copyStream));
     }
     scnSafeCall(scn_background_rows(in.siteKeys.dPtr(), in.sampleOffsets.dPtr(), batch, in.backgroundRows.dPtr(), s));
+    if (rows) cnn.inputReady = net->copyDone; // the layers (not the rule chain) wait for the features
+    cnn.earlyFirstLayer = true; // one batch in flight here: the first layer may start behind the rule chain
     cnn.preprocessBatchOnDevice(b); // waits once, after the key upload and the rule chain
-    if (rows) cudaSafeCall(cudaStreamWaitEvent(s, net->copyDone, 0)); // the layers read the features
+    cnn.earlyFirstLayer = false;
     std::ofstream nof, nog;
     cnn.processBatch(b, 0, 0, nof, nog);
     net->last = &b;
@@ -275,7 +277,9 @@ int scn_net_forward_device(scn_net_t *net, int batch, int rows, int maxSites, co
     SparseConvNetCUDA &cnn = *net->cnn;
     SpatiallySparseBatch &b = cnn.batchPool[0];
     adoptDeviceInput(cnn, b, batch, rows, maxSites, d_keys, d_off, d_bg, d_features);
+    cnn.earlyFirstLayer = true; // one batch in flight here: the first layer may start behind the rule chain
     cnn.preprocessBatchOnDevice(b);
+    cnn.earlyFirstLayer = false;
     cnn.forwardLayers(b);
     net->last = &b;
     SpatiallySparseBatchInterface &topI = b.interfaces.back();

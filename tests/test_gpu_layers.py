@@ -228,3 +228,34 @@ def test_split_k_matches_single_pass(abi, oracle, precision):
     ref = oracle.nin_forward(feat.cpu().numpy(), W.cpu().numpy(), B.cpu().numpy(), accum64=True)
     assert relerr(a.cpu().numpy(), ref) < RTOL_FP32
     assert relerr(c.cpu().numpy(), ref) < RTOL_FP32
+
+
+def test_conv_nin_with_row_count_on_the_device(abi, oracle):
+    """scn_conv_nin_forward_dyn: buffers sized for an upper bound, the kernel reads the real row count from
+    device memory (how the first layer starts before the rulebook counts reach the host)."""
+    from oracle import orc
+    rng = np.random.default_rng(21)
+    rows_in, bound, rows, fs, nIn, N = 700, 1000, 777, 9, 3, 96
+    K = fs * nIn
+    feat = rng.standard_normal((rows_in, nIn)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * np.sqrt(2.0 / K)).astype(np.float32)
+    B = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    rules = random_rules(rng, bound, fs, rows_in)
+    X = oracle.gather(feat, rules[:rows], nIn).reshape(rows, K)
+    ref = oracle.nin_forward(X, W, B, None, 0.9, orc.VLEAKYRELU, accum64=True)
+    dW = torch.from_numpy(W).cuda()
+    packed = abi.pack_weights(dW, abi.PREC_3XTF32)
+    d_rows = torch.tensor([rows, 0, 0, 0], dtype=torch.int32, device="cuda")
+    out = abi.conv_nin_forward_dyn(torch.from_numpy(feat).cuda(), torch.from_numpy(rules).cuda().flatten(), fs, dW, torch.from_numpy(B).cuda(),
+                                   d_rows, bound, None, 0.9, abi.VLEAKYRELU, packed)
+    torch.cuda.synchronize()
+    assert abi.conv_tc_take_error() == 0
+    out = out.cpu().numpy()
+    assert relerr(out[:rows], ref) < RTOL_FP32
+    assert not out[rows:].any()  # rows past the count are not written
+    # a count above the bound is clamped
+    d_rows[0] = bound + 500
+    out2 = abi.conv_nin_forward_dyn(torch.from_numpy(feat).cuda(), torch.from_numpy(rules).cuda().flatten(), fs, dW, torch.from_numpy(B).cuda(),
+                                    d_rows, bound, None, 0.9, abi.VLEAKYRELU, packed)
+    torch.cuda.synchronize()
+    assert abi.conv_tc_take_error() == 0 and np.isfinite(out2.cpu().numpy()).all()
