@@ -126,8 +126,8 @@ def build_pair(scn, want_oracle):
     return gnet, onet
 
 
-def cpu_leg(scn, onet, budget_s, threads):
-    """Oracle forward over whole batches of the workload until about budget_s seconds of wall time."""
+def cpu_leg(scn, onet, seconds, threads):
+    """Oracle forward over whole batches of the workload until about seconds seconds of wall time."""
     keys, off, feats = scn.synth.CONFIGS[CFG]["gen"](BATCH_PER_GPU)
     keys = keys.astype(np.int64)
     onet.forward(keys[: off[threads]], off[: threads + 1], feats[: off[threads]], threads=threads)  # warm-up
@@ -136,7 +136,7 @@ def cpu_leg(scn, onet, budget_s, threads):
         onet.forward(keys, off, feats, threads=threads)
         n += BATCH_PER_GPU
         rules_s += float(onet.times[0])
-        if time.time() - t0 >= budget_s:
+        if time.time() - t0 >= seconds:
             break
     wall = time.time() - t0
     return dict(value=n / wall, unit="samples/s", cores=threads, kind="port",
@@ -193,7 +193,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--precision", default="auto", choices=["auto", "fp32", "3xtf32", "bf16", "3xbf16"])
-    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="wall budget of the cpu_baseline leg (0 = skip)")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="wall time of the cpu_baseline leg (0 = skip)")
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="synthetic configuration (2 = the headline workload; the others are side measurements)")
     ap.add_argument("--batch", type=int, default=0, help="samples per GPU (0 = the configuration's own batch size, at most 256)")

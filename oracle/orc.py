@@ -25,14 +25,18 @@ L_CONV, L_CONV_TRI, L_NIN, L_MAXPOOL, L_MAXPOOL_TRI, L_TERMINAL = range(6)
 FMP_PO, FMP_PD, FMP_RO, FMP_RD = range(4)
 
 
+# where the reference checkout lies on the machine that builds oracle/_ref (the Makefile's REF default)
+REF_DIR = os.environ.get("SCN_REFERENCE_DIR", "/root/reference/SparseConvNet")
+
+
 def build(force=False):
     """Compile the oracle (and oracle/_ref when the reference checkout is present)."""
     if force or not os.path.exists(ORACLE_SO) or os.path.getmtime(ORACLE_SO) < os.path.getmtime(
             os.path.join(HERE, "scn_oracle.cpp")):
         subprocess.check_call(["make", "-C", HERE, "oracle"], stdout=subprocess.DEVNULL)
-    if os.path.isdir("/root/reference/SparseConvNet") and (force or not os.path.exists(REF_SO) or os.path.getmtime(REF_SO) < os.path.getmtime(
+    if os.path.isdir(REF_DIR) and (force or not os.path.exists(REF_SO) or os.path.getmtime(REF_SO) < os.path.getmtime(
             os.path.join(HERE, "ref_wrap.cpp"))):
-        subprocess.check_call(["make", "-C", HERE, "_ref"], stdout=subprocess.DEVNULL)
+        subprocess.check_call(["make", "-C", HERE, "_ref", "REF=" + REF_DIR], stdout=subprocess.DEVNULL)
 
 
 def _p(a):

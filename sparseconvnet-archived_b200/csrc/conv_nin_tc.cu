@@ -948,9 +948,9 @@ bool make_tiling16(int K, int N, int fs, bool haveRules, int passes, Tiling *t, 
   while (ruleBufs > 0 && 2 * stageBytes + 2 * A_HALF + ruleBufs * oneRules > avail) --ruleBufs;
   t->rulesBytes = ruleBufs ? oneRules : 0; // 0: the gather reads its rules from global memory
   t->rulesDouble = ruleBufs == 2 ? 1 : 0;
-  const int budget = avail - ruleBufs * oneRules;
-  int stages = 3, raw = (budget - 3 * stageBytes) / A_HALF; // three stages when two raw entries still fit
-  if (raw < 2) { stages = 2; raw = (budget - 2 * stageBytes) / A_HALF; }
+  const int room = avail - ruleBufs * oneRules;
+  int stages = 3, raw = (room - 3 * stageBytes) / A_HALF; // three stages when two raw entries still fit
+  if (raw < 2) { stages = 2; raw = (room - 2 * stageBytes) / A_HALF; }
   if (raw > MAX_RAW) raw = MAX_RAW;
   t->stages = stages; *rawEntries = raw;
   t->accStride = (BN + 31) / 32 * 32;
