@@ -193,15 +193,52 @@ k_nin_smalln(const float *__restrict__ in, const int *__restrict__ rules, int ro
   }
 }
 
+// Few rows (one per sample at the top of a network) and any N: one CTA per row, the (gathered) input row
+// in shared memory, threads over the output columns, so that W is read coalesced and each thread runs
+// K independent FMAs.  The tile kernel would leave all but a couple of SMs idle on such a layer.
+template <int ACT>
+__global__ void __launch_bounds__(256)
+k_nin_fewrows(const float *__restrict__ in, const int *__restrict__ rules, int rows, int fs, int nIn,
+              const float *__restrict__ W, const float *__restrict__ B, const float *__restrict__ prelu, int N,
+              float p, float *__restrict__ out) {
+  extern __shared__ float xS[]; // K floats
+  const int K = fs * nIn;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    __syncthreads();
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+      int src = row, c = k;
+      if (rules) {
+        const int f = k / nIn;
+        c = k - f * nIn;
+        src = __ldg(rules + (long long)row * fs + f);
+      }
+      xS[k] = src >= 0 ? __ldg(in + (long long)src * nIn + c) : 0.f;
+    }
+    __syncthreads();
+    for (int n = threadIdx.x; n < N; n += blockDim.x) {
+      float acc = 0.f;
+#pragma unroll 8
+      for (int k = 0; k < K; ++k) acc = fmaf(xS[k], __ldg(W + (long long)k * N + n), acc);
+      out[(long long)row * N + n] = activate_t<ACT>(p * acc + p * __ldg(B + n), ACT == SCN_PRELU ? __ldg(prelu + n) : 0.f);
+    }
+  }
+}
+
 // Row softmax of SigmoidLayer.cu:160-177 (running max starts at -10000), in place, one
-// thread per row (N is the class count).
+// warp per row (N is the class count).
 __global__ void k_softmax_rows(float *x, int rows, int N) {
-  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
+  const int lane = threadIdx.x & 31;
+  for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += gridDim.x * (blockDim.x >> 5)) {
     float *a = x + (long long)r * N;
-    float mx = -10000.0f, acc = 0.0f;
-    for (int k = 0; k < N; ++k) if (a[k] > mx) mx = a[k];
-    for (int k = 0; k < N; ++k) { a[k] = expf(a[k] - mx); acc += a[k]; }
-    for (int k = 0; k < N; ++k) a[k] /= acc;
+    float mx = -10000.0f;
+    for (int k = lane; k < N; k += 32) mx = fmaxf(mx, a[k]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float acc = 0.0f;
+    for (int k = lane; k < N; k += 32) { const float e = expf(a[k] - mx); a[k] = e; acc += e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    for (int k = lane; k < N; k += 32) a[k] /= acc;
   }
 }
 
@@ -275,6 +312,11 @@ extern "C" int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, in
     const int blocks = tiles < sm_count() * 4 ? tiles : sm_count() * 4;
     SCN_DISPATCH_ACT(inner, (k_conv_nin_smallk<ACT><<<blocks, 256, smem, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B, d_prelu, N, p, d_out)));
     SCN_LAUNCH_CHECK("k_conv_nin_smallk");
+  } else if (rows_out <= 2048 && (size_t)fs * nIn * sizeof(float) <= 48 * 1024) {
+    const int threads = N >= 256 ? 256 : (N + 31) / 32 * 32;
+    SCN_DISPATCH_ACT(inner, (k_nin_fewrows<ACT><<<rows_out, threads, (size_t)fs * nIn * sizeof(float), s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B,
+                                                                                                 d_prelu, N, p, d_out)));
+    SCN_LAUNCH_CHECK("k_nin_fewrows");
   } else {
     constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
     dim3 grid((rows_out + BM - 1) / BM, (N + BN - 1) / BN);
@@ -283,7 +325,7 @@ extern "C" int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, in
     SCN_LAUNCH_CHECK("k_conv_nin_simt");
   }
   if (act == SCN_SOFTMAX) {
-    k_softmax_rows<<<grid_for(rows_out, 128), 128, 0, s>>>(d_out, rows_out, N);
+    k_softmax_rows<<<grid_for((long long)rows_out * 32, 128), 128, 0, s>>>(d_out, rows_out, N);
     SCN_LAUNCH_CHECK("k_softmax_rows");
   }
   return SCN_OK;

@@ -69,21 +69,30 @@ __global__ void k_gather(const float *__restrict__ in, const int *__restrict__ r
   }
 }
 
-// vectorTopIndices (utilities.cu:35-56): descending values, equal values in index order.
+// vectorTopIndices (utilities.cu:35-56): descending values, equal values in index order.  One warp per
+// row: every lane finds the best eligible entry of its stride, a shuffle reduction picks the largest value
+// (the smaller index on a tie).
 __global__ void k_top_indices(const float *__restrict__ probs, int rows, int nClasses, int nTop, int *__restrict__ top) {
-  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += gridDim.x * blockDim.x) {
+  const int lane = threadIdx.x & 31;
+  for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += gridDim.x * (blockDim.x >> 5)) {
     const float *v = probs + (long long)r * nClasses;
     float lastVal = 0.f;
     int lastIdx = -1;
     for (int t = 0; t < nTop; ++t) {
       int best = -1;
       float bv = 0.f;
-      for (int i = 0; i < nClasses; ++i) {
+      for (int i = lane; i < nClasses; i += 32) {
         const float x = v[i];
         const bool eligible = (lastIdx < 0) || x < lastVal || (x == lastVal && i > lastIdx);
         if (eligible && (best < 0 || x > bv)) { best = i; bv = x; }
       }
-      top[(long long)r * nTop + t] = best < 0 ? 0 : best;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best, o);
+        if (oi >= 0 && (best < 0 || ov > bv || (ov == bv && oi < best))) { best = oi; bv = ov; }
+      }
+      if (lane == 0) top[(long long)r * nTop + t] = best < 0 ? 0 : best;
       lastVal = bv; lastIdx = best;
     }
   }
@@ -189,7 +198,7 @@ extern "C" int scn_top_indices(const float *d_probs, int rows, int nClasses, int
   if (rows < 0 || nClasses < 1 || nTop < 1 || nTop > nClasses) return fail(SCN_ERR_INVALID, "need 1 <= nTop <= nClasses");
   if (rows == 0) return SCN_OK;
   if (!d_probs || !d_top) return fail(SCN_ERR_INVALID, "null pointer");
-  k_top_indices<<<grid_for(rows, 128), 128, 0, (cudaStream_t)stream>>>(d_probs, rows, nClasses, nTop, d_top);
+  k_top_indices<<<grid_for((long long)rows * 32, 128), 128, 0, (cudaStream_t)stream>>>(d_probs, rows, nClasses, nTop, d_top);
   SCN_LAUNCH_CHECK("k_top_indices");
   return SCN_OK;
 }

@@ -83,6 +83,10 @@ CONV = [
     (100, 100, 1, 64, 128, "PRELU", 1.0),
     (500, 333, 27, 1, 64, "RELU", 1.0),
     (40, 41, 4, 4, 256, "LEAKYRELU", 1.0),
+    # one-CTA-per-row kernel (few rows, any N) and the tile kernel (more than 2048 rows)
+    (64, 64, 1, 256, 101, "SOFTMAX", 1.0),
+    (90, 77, 4, 50, 101, "PRELU", 0.8),
+    (400, 2500, 4, 24, 40, "VLEAKYRELU", 1.0),
     # warp-per-row kernel (N <= 32)
     (256, 256, 1, 608, 10, "SOFTMAX", 1.0),
     (90, 77, 4, 16, 20, "SOFTMAX", 0.8),
