@@ -503,28 +503,60 @@ __global__ void k_assign_t(Regions R, int batch, const int *__restrict__ keys, c
     outKeys[outRow] = encode_f<DIM>(j, R.nOut);
   }
 }
+// One block takes 64 output rows at a time: 64 threads look up what a row's cells share (its sample, the
+// input coordinates of its field's corner, the sample's bitmap, first input row and background row), then
+// all 256 threads fill the rows' cells in storage order.  Per cell that leaves one bitmap word and, for an
+// active cell, one sortedRow entry to read.
 template <int DIM>
-__global__ void k_fill_t(Regions R, int batch, const int *__restrict__ inOff, const int *__restrict__ inBg,
-                         const uint2 *__restrict__ dir, const int *__restrict__ sortedRow,
-                         const int *__restrict__ outOff, const int *__restrict__ outKeys, int *rules,
-                         int capacity, const int *__restrict__ result) {
-  const long long n = (long long)min(result[0], capacity) * R.sd;
-  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n; q += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(q / R.sd), col = (int)(q - (long long)r * R.sd);
-    const int b = find_sample(outOff, batch, r);
-    const int key = outKeys[r];
-    int v = inBg[b];
-    if (key >= 0) {
-      int j[DIM], cc[DIM], ii[DIM];
-      decode_f<DIM>(key, R.nOut, R.rNOut, j);
-      decode_f<DIM>(R.cellOfCol[col], R.size, R.rSize, cc);
+__global__ void __launch_bounds__(256) k_fill_t(Regions R, int batch, const int *__restrict__ inOff, const int *__restrict__ inBg,
+                                                const uint2 *__restrict__ dir, const int *__restrict__ sortedRow,
+                                                const int *__restrict__ outOff, const int *__restrict__ outKeys, int *rules,
+                                                int capacity, const int *__restrict__ result) {
+  constexpr int RB = 64;
+  __shared__ int sSample[RB], sBg[RB], sFirst[RB], sCorner[RB][DIM];
+  __shared__ unsigned char sCell[MAX_CUBE][DIM];
+  const int tid = threadIdx.x;
+  const int nRows = min(result[0], capacity);
+  for (int col = tid; col < R.sd; col += blockDim.x) {
+    int cc[DIM];
+    decode_f<DIM>(R.cellOfCol[col], R.size, R.rSize, cc);
 #pragma unroll
-      for (int a = 0; a < DIM; ++a) ii[a] = j[a] * R.stride + cc[a];
-      const int ck = encode_f<DIM>(ii, R.nIn);
-      const uint2 e = (dir + (size_t)b * R.W)[ck >> 5];
-      if ((e.x >> (ck & 31)) & 1u) v = sortedRow[inOff[b] + e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
+    for (int a = 0; a < DIM; ++a) sCell[col][a] = (unsigned char)cc[a];
+  }
+  for (long long row0 = (long long)blockIdx.x * RB; row0 < nRows; row0 += (long long)gridDim.x * RB) {
+    __syncthreads();
+    if (tid < RB && row0 + tid < nRows) {
+      const int r = (int)row0 + tid;
+      const int b = find_sample(outOff, batch, r);
+      const int key = outKeys[r];
+      sSample[tid] = key >= 0 ? b : -1; // -1: the sample's background row, every cell holds the input's background row
+      sBg[tid] = inBg[b];
+      sFirst[tid] = inOff[b];
+      if (key >= 0) {
+        int j[DIM];
+        decode_f<DIM>(key, R.nOut, R.rNOut, j);
+#pragma unroll
+        for (int a = 0; a < DIM; ++a) sCorner[tid][a] = j[a] * R.stride;
+      }
     }
-    rules[q] = v;
+    __syncthreads();
+    const int cells = (int)min((long long)RB, nRows - row0) * R.sd;
+    int *dst = rules + row0 * R.sd;
+    for (int c = tid; c < cells; c += blockDim.x) {
+      int col;
+      const int rl = fdiv(c, R.sd, R.rSd, &col);
+      int v = sBg[rl];
+      const int b = sSample[rl];
+      if (b >= 0) {
+        int ii[DIM];
+#pragma unroll
+        for (int a = 0; a < DIM; ++a) ii[a] = sCorner[rl][a] + sCell[col][a];
+        const int ck = encode_f<DIM>(ii, R.nIn);
+        const uint2 e = (dir + (size_t)b * R.W)[ck >> 5];
+        if ((e.x >> (ck & 31)) & 1u) v = sortedRow[sFirst[rl] + e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
+      }
+      dst[c] = v;
+    }
   }
 }
 
@@ -971,7 +1003,8 @@ static int run_rules(const Regions &R, int batch, const int *d_in_keys, const in
   else k_assign<<<grid_for((long long)rows * R.T, 256), 256, 0, s>>>(R, batch, d_in_keys, d_in_off, w.sortedRow, w.flags, w.cnt,
                                                                       d_out_off, d_out_keys, rows_out_capacity);
   SCN_LAUNCH_CHECK("k_assign");
-  const int fillGrid = grid_for((long long)(rows_out_capacity > 0 ? rows_out_capacity : 1) * R.sd, 256);
+  const int fillGrid = fast ? grid_for((long long)(rows_out_capacity > 0 ? rows_out_capacity : 1) * 4, 256)  // 64 rows per block and trip
+                            : grid_for((long long)(rows_out_capacity > 0 ? rows_out_capacity : 1) * R.sd, 256);
   if (fast) { SCN_DIM_DISPATCH(k_fill_t, fillGrid, 256, R, batch, d_in_off, d_in_bg, w.dir, w.sortedRow, d_out_off, d_out_keys, d_rules, rows_out_capacity, d_result) }
   else k_fill<<<fillGrid, 256, 0, s>>>(R, batch, d_in_off, d_in_bg, w.dir, w.sortedRow, d_out_off, d_out_keys, d_rules, rows_out_capacity, d_result);
   SCN_LAUNCH_CHECK("k_fill");
