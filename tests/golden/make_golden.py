@@ -35,6 +35,18 @@ CASES = {
 }
 
 
+# fractional max-pooling, name: (kind, dim, nOut, nIn, batch, density, seed); pool size 2
+FMP_CASES = {
+    "fmp_po2": (0, 2, 7, 10, 3, 0.3, 11),
+    "fmp_pd2": (1, 2, 6, 9, 3, 0.4, 12),
+    "fmp_ro2": (2, 2, 5, 7, 3, 0.5, 13),
+    "fmp_rd2": (3, 2, 8, 11, 2, 0.3, 14),
+    "fmp_po3": (0, 3, 4, 6, 2, 0.2, 15),
+    "fmp_rd3": (3, 3, 5, 7, 2, 0.2, 16),
+    "fmp_pd1": (1, 1, 7, 10, 2, 0.6, 17),
+}
+
+
 def main():
     orc.build()
     ref = orc.Reference()
@@ -53,6 +65,16 @@ def main():
         g = random_grids(rng, batch, dim, nIn, dens, triangular=(lat == 1))
         r = ref.grid_rules(lat, dim, nIn, nOut, size, stride, mn, *g)
         out[name + "/params"] = np.array([lat, dim, nIn, nOut, size, stride, mn], np.int32)
+        for k, v in zip(("in_keys", "in_rows", "in_off", "in_bg"), g):
+            out["%s/%s" % (name, k)] = v
+        for k, v in r.items():
+            out["%s/%s" % (name, k)] = np.asarray(v)
+    for i, (name, (kind, dim, nOut, nIn, batch, dens, seed)) in enumerate(sorted(FMP_CASES.items())):
+        rng = np.random.default_rng(300 + i)
+        g = random_grids(rng, batch, dim, nIn, dens)
+        r, ticks = ref.fmp_rules(kind, dim, nIn, nOut, 2, seed, *g)
+        out[name + "/fmp_params"] = np.array([kind, dim, nIn, nOut, 2, seed], np.int64)
+        out[name + "/ticks"] = ticks
         for k, v in zip(("in_keys", "in_rows", "in_off", "in_bg"), g):
             out["%s/%s" % (name, k)] = v
         for k, v in r.items():

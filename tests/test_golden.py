@@ -8,6 +8,7 @@ import pytest
 G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rules_golden.npz"))
 CASES = sorted({k.split("/")[0] for k in G.files if k.endswith("/params")})
 FIELDS = ("rules", "out_keys", "out_rows", "out_off", "out_bg")
+FMP_CASES = sorted({k.split("/")[0] for k in G.files if k.endswith("/fmp_params")})
 
 
 def test_known_answer_8x8(oracle):
@@ -48,3 +49,33 @@ def test_gpu_matches_golden(abi, name):
     ref["n_sites"] = int(G[name + "/n_sites"])
     compare(out, res, ref)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("name", FMP_CASES)
+def test_oracle_fmp_matches_golden(oracle, name):
+    """Tick tables (the reference's RNG, seeded) and FMP rulebooks as the reference build produced them."""
+    kind, dim, nIn, nOut, ps, seed = (int(v) for v in G[name + "/fmp_params"])
+    ticks = G[name + "/ticks"]
+    np.testing.assert_array_equal(oracle.fmp_ticks(kind, dim, nIn, nOut, ps, seed, ticks.shape[0]), ticks)
+    r = oracle.fmp_rules(dim, nIn, nOut, ps, kind in (0, 2), ticks, G[name + "/in_keys"], G[name + "/in_rows"], G[name + "/in_off"],
+                         G[name + "/in_bg"])
+    assert r["n_sites"] == int(G[name + "/n_sites"])
+    for f in FIELDS:
+        np.testing.assert_array_equal(r[f], G[name + "/" + f], err_msg=f)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", FMP_CASES)
+def test_gpu_fmp_matches_golden(abi, name):
+    import torch
+    from test_gpu_rules import compare, to_dev_grid
+    kind, dim, nIn, nOut, ps, seed = (int(v) for v in G[name + "/fmp_params"])
+    g = (G[name + "/in_keys"], G[name + "/in_rows"], G[name + "/in_off"], G[name + "/in_bg"])
+    dk, doff, dbg, first = to_dev_grid(*g)
+    assert first == 0
+    out = abi.fmp_rules_build(dim, nIn, nOut, ps, kind in (0, 2), torch.from_numpy(G[name + "/ticks"]).cuda(), dk, doff, dbg,
+                              dk.numel() * ps ** dim + len(g[3]) + 8)
+    torch.cuda.synchronize()
+    ref = {f: G[name + "/" + f] for f in FIELDS}
+    ref["n_sites"] = int(G[name + "/n_sites"])
+    compare(out, out["result"].cpu().numpy(), ref)
