@@ -218,6 +218,22 @@ int scn_conv_nin_forward_dyn(const float *d_in, const int *d_rules, int rows_out
                              int fs, int nIn, const void *d_W_packed, const float *d_B, const float *d_prelu,
                              int N, float p, int activation, float *d_out, scn_stream_t stream);
 
+/* ConvolutionalLayer gather + NetworkInNetworkLayer + MaxPoolingLayer in one kernel (ConvolutionalLayer.cu:124-133,
+ * NetworkInNetworkLayer.cu:187-201, MaxPoolingLayer.cu:9-35) for pooling windows that do not overlap
+ * (poolStride == poolSize) and hold 2, 4, 8, 16 or 32 cells: the tile rows of the contraction are ordered
+ * window by window (row d_pool_rules[w*cells + c] of the learnt layer's output), the epilogue takes the
+ * maximum over each window (negative rules skipped, first maximum wins) and writes only
+ * d_out[rows_pool x N] and d_choices (flat index rule*N + column); the learnt layer's own output never
+ * reaches memory.  d_rules are the convolution's rules (fs cells per row).  d_rows_pool: NULL, or the
+ * device-side row count (then rows_pool_bound is an upper bound).  rows_unpooled: rows of the learnt
+ * layer's own output if known, else 0; with it the call also answers SCN_ERR_UNSUPPORTED where fusing would
+ * cost an extra wave of tiles (windows repeat background rows) or where the layer alone would split K.
+ * 3xTF32 tensor-core kernel only; SCN_ERR_UNSUPPORTED for shapes it does not take. */
+int scn_conv_nin_maxpool_forward(const float *d_in, const int *d_rules, int fs, int nIn, const void *d_W_packed,
+                                 const float *d_B, const float *d_prelu, int N, float p, int activation,
+                                 const int *d_pool_rules, int pool_cells, int rows_pool_bound, const int *d_rows_pool,
+                                 int rows_unpooled, float *d_out, int *d_choices, scn_stream_t stream);
+
 /* One-time repack of W[K x N] (K = fs*nIn) for a tensor-core precision: bytes needed, then
  * the packing kernel.  No reference counterpart (the reference hands W to cuBLAS as is). */
 size_t scn_conv_packed_weight_bytes(int K, int N, int precision);

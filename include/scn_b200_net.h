@@ -35,6 +35,9 @@ int scn_net_addLeNetLayerMP(scn_net_t *net, int nFeatures, int filterSize, int f
  * 1 pseudorandom non-overlapping, 2 random overlapping, 3 random non-overlapping. */
 int scn_net_addLeNetLayerFMP(scn_net_t *net, int kind, int nFeatures, int filterSize, int filterStride, int poolSize,
                              float fmpShrink, int activation, float dropout, int minActiveInputs);
+/* Turns the fusion of convolution + learnt layer + non-overlapping max pooling into one kernel on (the
+ * builders' default) or off; off, every learnt layer writes its output, as the reference does. */
+int scn_net_set_pool_fusion(scn_net_t *net, int on);
 /* Re-seeds the RNG of every fractional max-pooling layer (layer index l gets seed + l) so that the next
  * forward draws a known sequence of region bounds.  The reference seeds from the clock (Rng.cpp:8-15). */
 int scn_net_seed_fmp(scn_net_t *net, unsigned seed);

@@ -20,7 +20,7 @@ DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
 EXPORTS = [
     "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
     "scn_rules_workspace_bytes", "scn_rules_build", "scn_fmp_rules_workspace_bytes", "scn_fmp_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_terminal_rules_workspace_bytes",
-    "scn_terminal_rules_build", "scn_conv_auto_precision", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_forward_dyn", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
+    "scn_terminal_rules_build", "scn_conv_auto_precision", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_forward_dyn", "scn_conv_nin_maxpool_forward", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
 ]
@@ -73,6 +73,7 @@ def lib():
         L.scn_terminal_rules_build.argtypes = [c_int, c_int, c_int, c_p, c_p, c_p, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]
         L.scn_conv_nin_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_int, c_f, c_int, c_int, c_p, c_p]
         L.scn_conv_nin_forward_dyn.argtypes = [c_p, c_p, c_int, c_p, c_int, c_int, c_p, c_p, c_p, c_int, c_f, c_int, c_p, c_p]
+        L.scn_conv_nin_maxpool_forward.argtypes = [c_p, c_p, c_int, c_int, c_p, c_p, c_p, c_int, c_f, c_int, c_p, c_int, c_int, c_p, c_int, c_p, c_p, c_p]
         L.scn_conv_nin_forward_ws.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_int, c_f, c_int, c_int, c_p, c_p, c_sz, c_p]
         L.scn_conv_nin_workspace_bytes.restype = c_sz
         L.scn_conv_nin_workspace_bytes.argtypes = [c_int] * 5
@@ -315,6 +316,19 @@ def conv_nin_forward_dyn(feat, rules, fs, W, B, d_rows, rows_bound, prelu=None, 
     check(L.scn_conv_nin_forward_dyn(_ptr(_f32(feat)), None if rules is None else _ptr(_i32(rules)), rows_bound, _ptr(_i32(d_rows)), fs, nIn,
                                      _ptr(packed), _ptr(_f32(B)), None if prelu is None else _ptr(_f32(prelu)), N, p, act, _ptr(out), _stream()))
     return out
+
+
+def conv_nin_maxpool_forward(feat, rules, fs, W, B, pool_rules, cells, prelu=None, p=1.0, act=NOSIGMOID, packed=None, d_rows=None):
+    """scn_conv_nin_maxpool_forward -> (pooled [rows_pool x N], choices)."""
+    L = lib()
+    K, N = W.shape
+    rows_pool = pool_rules.numel() // cells
+    out = torch.zeros((rows_pool, N), dtype=torch.float32, device=feat.device)
+    choices = torch.full((rows_pool, N), -7, dtype=torch.int32, device=feat.device)
+    check(L.scn_conv_nin_maxpool_forward(_ptr(_f32(feat)), _ptr(_i32(rules)), fs, K // fs, _ptr(packed), _ptr(_f32(B)),
+                                         None if prelu is None else _ptr(_f32(prelu)), N, p, act, _ptr(_i32(pool_rules)), cells, rows_pool,
+                                         None if d_rows is None else _ptr(_i32(d_rows)), 0, _ptr(out), _ptr(choices), _stream()))
+    return out, choices
 
 
 def background_rows(keys, off):

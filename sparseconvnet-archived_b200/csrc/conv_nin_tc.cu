@@ -128,7 +128,7 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
-  int mTiles, accStride, K, generic, rulesDouble, rawEntries, nStages64, atmem, aBase; const int *rowsPtr; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
+  int mTiles, accStride, K, generic, rulesDouble, rawEntries, nStages64, atmem, aBase; const int *rowsPtr; const int *poolRules; int *choices; int poolCells; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
@@ -159,9 +159,13 @@ constexpr int EPI_BYTES = BM * EPI_LD * 4;        // 18 KB
 
 // Epilogue role (warps 0-3 of both tensor-core kernels): drains accumulator n & 1 of work item n
 // while the main loop fills the other one.
-template <bool SPLIT, int ACT>
+// POOL: a non-overlapping max-pooling layer behind this layer is applied here (MaxPoolingLayer.cu:9-35).  The
+// tile's 128 rows are 128/cells pooling windows x cells; tile row i is the layer-output row poolRules[row0 + i]
+// (negative: skipped, as maxPool skips it).  Only the pooled rows and their choices are written.
+template <bool SPLIT, int ACT, bool POOL = false>
 __device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint32_t tmem, uint32_t accFullBar, uint32_t accEmptyBar,
                                               int nItems, int kSplit, int rows) {
+  __shared__ int poolRow[BM]; // POOL: this tile's layer-output row per tile row
   const int warp = threadIdx.x >> 5;
   const int t = threadIdx.x;
   const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
@@ -175,6 +179,10 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint3
     mbar_wait(accFullBar + 8 * ab, (n >> 1) & 1, 2);
     tc_fence_after();
     const int row0 = tileM * BM, col0 = tileN * P.BN;
+    if (POOL) { // read before the first slice's barrier, used after it
+      const long long gr = (long long)row0 + t;
+      poolRow[t] = gr < rows ? __ldg(P.poolRules + gr) : -1;
+    }
     for (int c = 0; c < P.BN; c += EPI_COLS) {
       const int width = min(EPI_COLS, P.BN - c); // 32, or 16 for the last slice when BN % 32 == 16
       uint32_t a[32];
@@ -202,6 +210,30 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint3
         b4 = __ldg(reinterpret_cast<const float4 *>(P.bias + col));
         if (ACT == SCN_PRELU) s4 = __ldg(reinterpret_cast<const float4 *>(P.prelu + col));
       }
+      if (POOL) {
+        const int cells = P.poolCells, windows = BM / cells;
+        for (int pr = rsub; pr < windows; pr += 16) {
+          const long long w = (long long)tileM * windows + pr; // pooled row
+          if (!colOk || w * cells >= rows) continue;
+          float best[4] = {0.f, 0.f, 0.f, 0.f};
+          int idx[4] = {-1, -1, -1, -1};
+          bool none = true;
+          for (int cell = 0; cell < cells; ++cell) {
+            const int rl = pr * cells + cell, from = poolRow[rl];
+            if (from < 0) continue;
+            const float4 v = *reinterpret_cast<const float4 *>(epi + (size_t)rl * EPI_LD + c4 * 4);
+            const float o[4] = {activate_t<ACT>(P.p * v.x + P.p * b4.x, s4.x), activate_t<ACT>(P.p * v.y + P.p * b4.y, s4.y),
+                                activate_t<ACT>(P.p * v.z + P.p * b4.z, s4.z), activate_t<ACT>(P.p * v.w + P.p * b4.w, s4.w)};
+            const int base = from * P.N + col;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              if (none || best[k] < o[k]) { best[k] = o[k]; idx[k] = base + k; } // the first maximum wins
+            none = false;
+          }
+          *reinterpret_cast<float4 *>(P.out + w * P.N + col) = make_float4(best[0], best[1], best[2], best[3]);
+          *reinterpret_cast<int4 *>(P.choices + w * P.N + col) = make_int4(idx[0], idx[1], idx[2], idx[3]);
+        }
+      } else
 #pragma unroll
       for (int pass = 0; pass < BM / 16; ++pass) {
         const int rl = pass * 16 + rsub, r = row0 + rl;
@@ -231,7 +263,7 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint3
 // from it, which takes about 30 % off the shared-memory data pipe, the resource that bounds this
 // kernel (second convolution of the benchmark 81 -> 66 us, third 72 -> 64 us).  Needs 2 accumulators + 128
 // columns <= 512, i.e. BN <= 192; a shared-memory stage then holds the raw A tile and the weight images only.
-template <bool SPLIT, int ACT, bool ATMEM>
+template <bool SPLIT, int ACT, bool ATMEM, bool POOL = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) {
   extern __shared__ unsigned char smem_raw[];
   int *rulesS = reinterpret_cast<int *>(smem_raw); // [128 x fs] rule tile of the current item (when it fits)
@@ -248,7 +280,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
                  aFullBar = smem_u32(&bars[3 * MAX_STAGES + 4]), aEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 6]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the row count may still be on its way to the host when this kernel is launched: read it from device memory
-  const int rows = P.rowsPtr ? min(max(__ldg(P.rowsPtr), 0), P.rows) : P.rows;
+  // (POOL: rows counts tile rows = pooled rows x cells, and the device-side count is in pooled rows)
+  const int rows = P.rowsPtr ? min(max(__ldg(P.rowsPtr), 0) * (POOL ? P.poolCells : 1), P.rows) : P.rows;
   const int mTiles = P.rowsPtr ? (rows + BM - 1) / BM : P.mTiles;
   const int kSplit = SPLIT ? P.kSplit : 1;
   const int nItems = mTiles * P.nTiles * kSplit;
@@ -284,7 +317,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   };
 
   if (warp < 4) {
-    epilogue_role<SPLIT, ACT>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows);
+    epilogue_role<SPLIT, ACT, POOL>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows);
   } else if (warp < 8) {
     // ------------------------------------------------------------ gather: asynchronous 16-byte copies
     const int t = threadIdx.x - 128, chunk = t & 7, rbase = t >> 3;
@@ -306,13 +339,43 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    if (P.rulesDouble && (int)blockIdx.x < nItems) stage_rules_async(blockIdx.x, 0);
+    // POOL: tile row t is the layer-output row poolRules[first tile row + t]; its fs rules are copied from there
+    // (4-byte copies), the row id itself goes behind them ([128 x fs] rules, then 128 row ids per buffer)
+    auto pool_row_of = [&](int item) {
+      int tileM, tileN, slab0, nLoc;
+      itemTile(item, tileM, tileN, slab0, nLoc);
+      const long long gr = (long long)tileM * BM + t;
+      return gr < rows ? __ldg(P.poolRules + gr) : -1;
+    };
+    auto stage_rules_pool = [&](int buf, int from) {
+      int *base = rulesS + buf * (P.rulesBytes >> 2);
+      const uint32_t dst = smem_u32(base) + t * P.fs * 4;
+      for (int f = 0; f < P.fs; ++f)
+        cp_async4(dst + 4 * f, from >= 0 ? (const void *)(P.rules + (long long)from * P.fs + f) : (const void *)P.rules, from >= 0 ? 4u : 0u);
+      base[BM * P.fs + t] = from;
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int fromNext = -1; // POOL: this thread's row id of the tile after the next staged one
+    if (POOL) {
+      if ((int)blockIdx.x < nItems) stage_rules_pool(0, pool_row_of(blockIdx.x));
+      if ((int)(blockIdx.x + gridDim.x) < nItems) fromNext = pool_row_of(blockIdx.x + gridDim.x);
+    } else if (P.rulesDouble && (int)blockIdx.x < nItems) stage_rules_async(blockIdx.x, 0);
     for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++nItem) {
       int tileM, tileN, slab0, nLoc;
       itemTile(item, tileM, tileN, slab0, nLoc);
       const int row0 = tileM * BM;
       const int *rulesT = rulesS; // this tile's staged rules
-      if (P.rulesDouble) {
+      const int *fromT = nullptr; // POOL: this tile's layer-output row per tile row
+      if (POOL) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        rulesT = rulesS + (nItem & 1) * (P.rulesBytes >> 2);
+        fromT = rulesT + BM * P.fs;
+        if (item + (int)gridDim.x < nItems) {
+          stage_rules_pool((nItem + 1) & 1, fromNext);
+          fromNext = item + 2 * (int)gridDim.x < nItems ? pool_row_of(item + 2 * gridDim.x) : -1;
+        }
+      } else if (P.rulesDouble) {
         // the rules of this tile were prefetched while the previous tile's copies were issued
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("bar.sync 2, 128;" ::: "memory"); // all chunks landed; everyone is done with the other buffer
@@ -349,7 +412,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
             for (int j = 0; j < 8; ++j) {
               const int rl = wq * 32 + i0 + j, r = row0 + rl;
               src[j] = -1;
-              if (kOk && r < rows) {
+              if (POOL) { if (kOk && fromT[rl] >= 0) src[j] = rulesT[rl * P.fs + f]; }
+              else if (kOk && r < rows) {
                 if (P.rulesBytes > 0) src[j] = rulesT[rl * P.fs + f];
                 else if (P.rules) src[j] = __ldg(P.rules + (long long)r * P.fs + f);
                 else src[j] = r;
@@ -377,7 +441,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
           for (int i = 0; i < 8; ++i) {
             const int rl = rbase + 16 * i, r = row0 + rl;
             int src = -1;
-            if (r < rows) {
+            if (POOL) { if (fromT[rl] >= 0) src = rulesT[rl * P.fs + f]; }
+            else if (r < rows) {
               if (P.rulesBytes > 0) src = rulesT[rl * P.fs + f];
               else if (P.rules) src = __ldg(P.rules + (long long)r * P.fs + f);
               else src = r;
@@ -897,9 +962,13 @@ struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, rulesDoubl
 
 // oneItem: no CTA gets more than one work item, so the second accumulator is never used and its columns can
 // hold the A slots: the tensor-memory A path then reaches BN = 256.
-bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool oneItem = false) {
+bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool oneItem = false, bool pool = false) {
   if (K < 1 || N < 16) return false;
   t->rulesBytes = (haveRules && fs <= 32) ? BM * fs * 4 : 0;
+  if (pool) { // fused max-pooling: staged rules are mandatory, two buffers, each followed by the tile's 128 row ids
+    if (!t->rulesBytes) return false;
+    t->rulesBytes += BM * 4;
+  }
   t->nTiles = (N + 255) / 256; // narrower tiles (so that every layer could use the tensor-memory A path) were measured slower: A is gathered once per column tile
   t->BN = ((N + t->nTiles - 1) / t->nTiles + 15) / 16 * 16;
   t->nSlabs = (K + SLAB - 1) / SLAB; // the last slab is zero-padded
@@ -913,10 +982,10 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool oneItem =
     const int n = (int)((226 * 1024 - 1024 - ruleBufs * t->rulesBytes - EPI_BYTES) / stageBytes);
     return n > MAX_STAGES ? MAX_STAGES : n;
   };
-  const int stages = stagesWith(1);
+  const int stages = stagesWith(pool ? 2 : 1);
   if (stages < 2) return false;
   t->stages = stages;
-  t->rulesDouble = (t->rulesBytes > 0 && stagesWith(2) == stages) ? 1 : 0; // prefetch the next tile's rules if that costs no stage
+  t->rulesDouble = (pool || (t->rulesBytes > 0 && stagesWith(2) == stages)) ? 1 : 0; // prefetch the next tile's rules if that costs no stage
   int cols = 32;
   while (cols < (t->atmem ? t->aBase + 128 : 2 * t->accStride)) cols *= 2; // the accumulators [+ the A slots], at most 512 columns
   t->tmemCols = cols;
@@ -1019,21 +1088,35 @@ size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision) {
 
 int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed, const float *d_B,
               const float *d_prelu, int N, float p, int act, int precision, float *d_out, void *d_ws, size_t wsBytes,
-              cudaStream_t s, const int *d_rows) {
+              cudaStream_t s, const int *d_rows, const int *d_pool_rules, int pool_cells, int *d_choices, int rows_unpooled) {
   Tiling t;
   const int passes = passes_of(precision);
   int rawEntries = 0, nStages64 = 0;
+  const bool pool = d_pool_rules != nullptr;
+  // pooled: `rows` counts pooled rows; the kernel's row space is pooled rows x cells (a tile = 128 / cells windows)
+  if (pool && (passes || !d_rules || !d_choices || pool_cells < 2 || pool_cells > 32 || (pool_cells & (pool_cells - 1)) || (long long)rows * pool_cells > INT_MAX))
+    return fail(SCN_ERR_UNSUPPORTED, "fused max-pooling needs the 3xTF32 kernel, rules, and 2, 4, 8, 16 or 32 cells per window");
+  if (pool) rows *= pool_cells;
   const bool ok = N % 4 == 0 && (passes ? make_tiling16(fs * nIn, N, fs, d_rules != nullptr, passes, &t, &rawEntries, &nStages64)
-                                        : precision == SCN_PREC_3XTF32 && make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t));
+                                        : precision == SCN_PREC_3XTF32 && make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, false, pool));
   if (!ok || (nIn % SLAB == 0 && nIn > ZERO_ROW_FLOATS)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
   if (((uintptr_t)d_in | (uintptr_t)d_out | (uintptr_t)d_packed) & 15) return fail(SCN_ERR_INVALID, "tensor-core path needs 16-byte aligned buffers");
   Params P;
   const int mTiles = (rows + BM - 1) / BM;
   int kSplit = (d_ws && ((uintptr_t)d_ws & 15) == 0) ? choose_ksplit(mTiles * t.nTiles, passes ? 2 * nStages64 : t.nSlabs, rows, N, wsBytes) : 1;
-  if (!passes && !t.atmem && mTiles * t.nTiles * kSplit <= sm_count()) make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, true);
+  if (pool && kSplit > 1) return fail(SCN_ERR_UNSUPPORTED, "fused max-pooling is not combined with a K split");
+  if (pool && rows_unpooled > 0) {
+    // The window-major row space repeats rows that several windows name (background rows) and pads ragged
+    // windows: do not fuse where that costs a wave of tiles, or where the layer alone would split K.
+    const int plainTiles = ((rows_unpooled + BM - 1) / BM) * t.nTiles, sms = sm_count();
+    if (choose_ksplit(plainTiles, t.nSlabs, rows_unpooled, N, (size_t)-1) > 1 ||
+        (mTiles * t.nTiles + sms - 1) / sms > (plainTiles + sms - 1) / sms)
+      return fail(SCN_ERR_UNSUPPORTED, "fused max-pooling would not pay for this shape");
+  }
+  if (!passes && !t.atmem && mTiles * t.nTiles * kSplit <= sm_count()) make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, true, pool);
   P.rawEntries = rawEntries; P.nStages64 = nStages64; P.atmem = passes ? 0 : t.atmem; P.aBase = t.aBase;
   if (d_rows && (passes || kSplit > 1)) return fail(SCN_ERR_UNSUPPORTED, "a device-side row count needs the 3xTF32 kernel without K split");
-  P.rowsPtr = d_rows;
+  P.rowsPtr = d_rows; P.poolRules = d_pool_rules; P.poolCells = pool_cells; P.choices = d_choices;
   P.in = d_in; P.rules = d_rules; P.rows = rows; P.fs = fs; P.nIn = nIn;
   P.packed = (const unsigned char *)d_packed; P.bias = d_B; P.prelu = d_prelu;
   P.N = N; P.BN = t.BN; P.nTiles = t.nTiles; P.nSlabs = t.nSlabs; P.stages = t.stages; P.tmemCols = t.tmemCols; P.rulesBytes = t.rulesBytes;
@@ -1045,7 +1128,7 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   P.partial = (float *)d_ws;
   P.mTiles = mTiles; P.accStride = t.accStride;
   P.K = fs * nIn; P.generic = (nIn % SLAB != 0) ? 1 : 0;
-  P.rulesDouble = (t.rulesDouble && ((uintptr_t)d_rules & 15) == 0) ? 1 : 0;
+  P.rulesDouble = (t.rulesDouble && (pool || ((uintptr_t)d_rules & 15) == 0)) ? 1 : 0;
   const int items = mTiles * t.nTiles * P.kSplit;
   const int grid = items < sm_count() ? items : sm_count(); // persistent: one CTA per SM
 #define SCN_TC16_LAUNCH(PASSES)                                                                                                          \
@@ -1060,7 +1143,13 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   } while (0)
   if (passes == 3) SCN_TC16_LAUNCH(3);
   else if (passes == 1) SCN_TC16_LAUNCH(1);
-  else if (P.atmem && P.kSplit > 1) {
+  else if (pool && P.atmem) {
+    SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+                     (k_conv_nin_tc<false, ACT, true, true><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
+  } else if (pool) {
+    SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+                     (k_conv_nin_tc<false, ACT, false, true><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
+  } else if (P.atmem && P.kSplit > 1) {
     SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<true, SCN_NOSIGMOID, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
     k_conv_nin_tc<true, SCN_NOSIGMOID, true><<<grid, NUM_THREADS, t.smemBytes, s>>>(P);
   } else if (P.atmem) {

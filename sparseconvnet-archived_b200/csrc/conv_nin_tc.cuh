@@ -12,7 +12,12 @@ int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaS
 size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision);
 int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed,
               const float *d_B, const float *d_prelu, int N, float p, int act, int precision, float *d_out,
-              void *d_ws, size_t wsBytes, cudaStream_t s, const int *d_rows = nullptr);
+              void *d_ws, size_t wsBytes, cudaStream_t s, const int *d_rows = nullptr, const int *d_pool_rules = nullptr,
+              int pool_cells = 0, int *d_choices = nullptr, int rows_unpooled = 0);
+// d_pool_rules: a non-overlapping max-pooling layer behind this layer is applied in the epilogue: `rows` then
+// counts pooled rows, d_out / d_choices receive the pooled values and choices ([rows x N]), the layer's own
+// output is never written.  3xTF32 without K split; pool_cells a power of two in 2..32.  rows_unpooled > 0 (rows
+// of the layer's own output): the launch is refused where fusing would cost an extra wave of tiles.
 // d_rows: when not null the kernel takes its row count from there (clamped to `rows`, which then is an
 // upper bound); 3xTF32 without K split only.
 // Error code a bounded wait of the kernel recorded since the last call (0 = none); waits for

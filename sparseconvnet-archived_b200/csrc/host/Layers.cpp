@@ -167,7 +167,18 @@ void MaxPoolingLayer::finishRules(SpatiallySparseBatch &batch, SpatiallySparseBa
 void MaxPoolingLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
   preprocessNow(*this, batch, input, output);
 }
-void MaxPoolingLayer::forwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+void MaxPoolingLayer::forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  if (input.deferredLearnt) { // convolution + learnt layer + this pooling as one kernel, if it takes the case
+    NetworkInNetworkLayer *nin = input.deferredLearnt;
+    SpatiallySparseBatchInterface &ninInput = *input.deferredLearntInput;
+    if (poolSize == poolStride &&
+        nin->forwardsPooled(batch, *ninInput.deferredFrom, ninInput, output, ninInput.deferredCells, sd, output.nSpatialSites, nullptr,
+                            input.nSpatialSites))
+      return;
+    input.deferredLearnt = nullptr; // not taken: materialise the learnt layer's output after all, then pool it
+    input.sub->reset();
+    nin->forwardsNow(batch, ninInput, input);
+  }
   const int n = output.nSpatialSites * output.featuresPresent.size();
   output.sub->poolingChoices.resize(n);
   output.sub->features.resize(n);
@@ -374,7 +385,7 @@ int TerminalPoolingLayer::calculateInputSpatialSize(int outputSpatialSize) {
 NetworkInNetworkLayer::NetworkInNetworkLayer(cudaMemStream &memStream, cublasHandle_t &, int nFeaturesIn, int nFeaturesOut, float dropout,
                                              ActivationFunction fn, float alpha)
     : SpatiallySparseLayer(memStream), W(false, nFeaturesIn * nFeaturesOut), MW(false, 0), B(false, nFeaturesOut), MB(false, 0), fn(fn),
-      nFeaturesIn(nFeaturesIn), nFeaturesOut(nFeaturesOut), dropout(dropout), precision(SCN_PREC_AUTO), precisionFallback(false), packed(nullptr), packedBytes(0),
+      nFeaturesIn(nFeaturesIn), nFeaturesOut(nFeaturesOut), dropout(dropout), precision(SCN_PREC_AUTO), fusePoolNext(false), precisionFallback(false), packed(nullptr), packedBytes(0),
       packedPrecision(-100), packedFs(0) {
   // uniform(+-sqrt(6/(nIn + nOut*alpha))) as NetworkInNetworkLayer.cu:135-137, from a fixed
   // seed (the reference seeds from the clock); real runs load weights.
@@ -445,11 +456,44 @@ bool NetworkInNetworkLayer::forwardsEarly(SpatiallySparseBatch &batch, Spatially
   scnSafeCall(rc);
   return true;
 }
-void NetworkInNetworkLayer::finishEarly(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
-  output.sub->features.resize(output.nSpatialSites * output.featuresPresent.size());
+void NetworkInNetworkLayer::countMultiplyAdds(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
   multiplyAddCount += (__int128_t)output.nSpatialSites * input.featuresPresent.size() * output.featuresPresent.size();
 }
+void NetworkInNetworkLayer::finishEarly(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  output.sub->features.resize(output.nSpatialSites * output.featuresPresent.size());
+  countMultiplyAdds(input, output);
+}
+bool NetworkInNetworkLayer::forwardsPooled(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &source, SpatiallySparseBatchInterface &input,
+                                           SpatiallySparseBatchInterface &poolOutput, int convCells, int poolCells, long long rowsPoolBound,
+                                           const int *d_rowsPool, int rowsUnpooled) {
+  if (batch.type == TRAINBATCH || rowsPoolBound < 1 || rowsPoolBound * (long long)nFeaturesOut > INT_MAX) return false;
+  if ((precision != SCN_PREC_AUTO && precision != SCN_PREC_3XTF32) || scn_conv_auto_precision() != SCN_PREC_3XTF32) return false;
+  if (fn == SOFTMAX || nFeaturesOut % 4 != 0 || nFeaturesIn % convCells != 0) return false;
+  const int nIn = nFeaturesIn / convCells;
+  const void *pk = packedWeights(convCells, nIn, SCN_PREC_3XTF32);
+  if (!pk) return false;
+  const int n = (int)(rowsPoolBound * nFeaturesOut);
+  poolOutput.sub->features.resize(n);
+  poolOutput.sub->poolingChoices.resize(n);
+  const float p = 1.0f - (batch.type != RESCALEBATCH ? dropout : 0.0f);
+  const int rc = scn_conv_nin_maxpool_forward(source.sub->features.dPtr(), input.rules.dPtr(), convCells, nIn, pk, B.dPtr(), slopes(), nFeaturesOut, p,
+                                              (int)fn, poolOutput.rules.dPtr(), poolCells, (int)rowsPoolBound, d_rowsPool, rowsUnpooled,
+                                              poolOutput.sub->features.dPtr(), poolOutput.sub->poolingChoices.dPtr(), memStream.stream);
+  if (rc == SCN_ERR_UNSUPPORTED) return false; // e.g. so few rows that K would be split
+  scnSafeCall(rc);
+  return true;
+}
 void NetworkInNetworkLayer::forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  if (fusePoolNext && input.deferredFrom && batch.type != TRAINBATCH) { // the pooling layer behind this one runs all three steps
+    output.deferredLearnt = this;
+    output.deferredLearntInput = &input;
+    countMultiplyAdds(input, output);
+    return;
+  }
+  forwardsNow(batch, input, output);
+  countMultiplyAdds(input, output);
+}
+void NetworkInNetworkLayer::forwardsNow(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
   requireInference(batch);
   output.sub->features.resize(output.nSpatialSites * output.featuresPresent.size());
   const float p = 1.0f - (batch.type != RESCALEBATCH ? dropout : 0.0f); // NetworkInNetworkLayer.cu:188
@@ -482,7 +526,6 @@ void NetworkInNetworkLayer::forwards(SpatiallySparseBatch &batch, SpatiallySpars
   }
   scnSafeCall(scn_conv_nin_forward_ws(src, rules, output.nSpatialSites, fs, nIn, W.dPtr(), pk, B.dPtr(), slopes(), nFeaturesOut, p,
                                       (int)fn, prec, output.sub->features.dPtr(), ws, wsBytes, memStream.stream));
-  multiplyAddCount += (__int128_t)output.nSpatialSites * input.featuresPresent.size() * output.featuresPresent.size();
 }
 // Weight files: raw fp32 W then B (then momentum copies) per layer (NetworkInNetworkLayer.cu:290-328).
 void NetworkInNetworkLayer::loadWeightsFromStream(std::ifstream &f, bool momentum) {

@@ -16,6 +16,8 @@ public:
   int nFeaturesIn, nFeaturesOut;
   float dropout;
   int precision; // scn_precision used by forwards(); SCN_PREC_AUTO by default
+  bool fusePoolNext; // set by the builders when a non-overlapping max-pooling layer follows: forwards() then leaves the
+                     // output unmaterialised and the pooling layer runs gather + this layer + pooling as one kernel
   bool precisionFallback; // true: a tensor-core precision falls back to the CUDA-core kernel where the shape has no tensor-core path (false: throw)
   NetworkInNetworkLayer(cudaMemStream &memStream, cublasHandle_t &cublasHandle, int nFeaturesIn, int nFeaturesOut,
                         float dropout = 0, ActivationFunction fn = NOSIGMOID, float alpha = 1);
@@ -37,6 +39,15 @@ public:
   // false (nothing launched) unless the 3xTF32 tensor-core kernel takes the shape without a K split.
   bool forwardsEarly(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &source, SpatiallySparseBatchInterface &input,
                      SpatiallySparseBatchInterface &output, int cells, long long rowsBound, const int *d_rows);
+  // Convolution + this layer + the max pooling behind it in one kernel: the pooled features and choices go to
+  // poolOutput, this layer's own output is never written.  d_rowsPool: device-side pooled row count (then
+  // rowsPoolBound is an upper bound) or nullptr.  False (nothing launched) if the kernel does not take the case.
+  bool forwardsPooled(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &source, SpatiallySparseBatchInterface &input,
+                      SpatiallySparseBatchInterface &poolOutput, int convCells, int poolCells, long long rowsPoolBound, const int *d_rowsPool,
+                      int rowsUnpooled = 0);
+  // forwards() without the deferral to a pooling layer.
+  void forwardsNow(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
+  void countMultiplyAdds(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
   // The bookkeeping forwards() would have done, once the counts are known.
   void finishEarly(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
 

@@ -19,6 +19,7 @@ void SparseConvNetCUDA::init(int nInputFeatures_, int nClasses_) {
   timing = false;
   // off by default: with BatchProducer threads the next batch is preprocessed while the current one is
   // still in its layers, and the features buffers behind the first layers are shared by the batch pool
+  fusePooling = true;
   earlyFirstLayer = false; earlyLayers = 0; inputReady = nullptr; countStream = nullptr; chainDone = nullptr;
   chainRowsHint = 0;
   inputSpatialSize = 0;
@@ -84,6 +85,10 @@ void SparseConvNetCUDA::addLeNetLayerMP(int nFeatures, int filterSize, int filte
   addConvolutionalLayer(nFeatures, filterSize, filterStride, activationFn, dropout, minActiveInputs, poolSize);
   if (poolSize > 1) {
     std::cout << layers.size() << ":";
+    // windows that do not overlap and hold 2..32 cells (a power of two): the learnt layer leaves its output to the pooling layer's fused kernel
+    const int cells = ipow(poolSize, dimension);
+    if (poolSize == poolStride && cells >= 2 && cells <= 32 && (cells & (cells - 1)) == 0 && filterSize > 1)
+      if (auto nin = dynamic_cast<NetworkInNetworkLayer *>(layers.back())) nin->fusePoolNext = fusePooling;
     layers.push_back(new MaxPoolingLayer(memStream, poolSize, poolStride, dimension));
   }
 }
@@ -156,7 +161,7 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
   const int nL = (int)layers.size();
   chainResults.resize(4 * nL + 4);
   int *d_res = chainResults.dPtr();
-  long long bound = batch.interfaces[0].nSpatialSites, bound0 = 0;
+  long long bound = batch.interfaces[0].nSpatialSites, bound0 = 0, bound2 = 0;
   earlyLayers = 0;
   if (timing) cudaSafeCall(cudaEventRecord(events[nL + 1], memStream.stream));
   // Without terminal pooling (whose build reads its input grid at once) the region builds are
@@ -169,6 +174,7 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
     for (int i = 0; i < nL; ++i) {
       bound = layers[i]->enqueueRules(batch, batch.interfaces[i], batch.interfaces[i + 1], bound, d_res + 4 * i);
       if (i == 0) bound0 = bound;
+      if (i == 2) bound2 = bound;
     }
   } catch (...) {
     rulechain::endDeferred();
@@ -195,8 +201,14 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
         cudaSafeCall(cudaEventCreateWithFlags(&chainDone, cudaEventDisableTiming));
       }
       cudaSafeCall(cudaEventRecord(chainDone, memStream.stream));
-      if (nin->forwardsEarly(batch, batch.interfaces[0], batch.interfaces[1], batch.interfaces[2], ipow(conv->filterSize, conv->dimension), bound0, d_res)) {
+      const int convCells = ipow(conv->filterSize, conv->dimension);
+      MaxPoolingLayer *pool = nL >= 3 ? dynamic_cast<MaxPoolingLayer *>(layers[2]) : nullptr;
+      if (nin->fusePoolNext && pool && pool->poolSize == pool->poolStride &&
+          nin->forwardsPooled(batch, batch.interfaces[0], batch.interfaces[1], batch.interfaces[3], convCells, pool->sd, bound2, d_res + 8))
+        earlyLayers = 3; // convolution + learnt layer + pooling, the pooled row count read from the pooling layer's record
+      else if (nin->forwardsEarly(batch, batch.interfaces[0], batch.interfaces[1], batch.interfaces[2], convCells, bound0, d_res))
         earlyLayers = 2;
+      if (earlyLayers) {
         // the counts come back on their own stream, behind the rule chain only, while the first layer runs
         cudaSafeCall(cudaStreamWaitEvent(countStream, chainDone, 0));
         cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, countStream));
@@ -237,8 +249,23 @@ void SparseConvNetCUDA::forwardLayers(SpatiallySparseBatch &batch) {
       static_cast<NetworkInNetworkLayer *>(layers[1])->finishEarly(batch.interfaces[1], batch.interfaces[2]);
       continue;
     }
+    if (earlyLayers == 3 && (i == 1 || i == 2)) { // convolution + learnt layer + pooling already running as one kernel
+      SpatiallySparseBatchInterface &out = batch.interfaces[i + 1];
+      if (i == 1) {
+        out.sub->reset();
+        out.deferredLearnt = static_cast<NetworkInNetworkLayer *>(layers[1]);
+        out.deferredLearntInput = &batch.interfaces[1];
+        out.deferredLearnt->countMultiplyAdds(batch.interfaces[1], out);
+      } else {
+        const int n = out.nSpatialSites * out.featuresPresent.size();
+        out.sub->features.resize(n);
+        out.sub->poolingChoices.resize(n);
+      }
+      continue;
+    }
     batch.interfaces[i + 1].sub->reset();
     batch.interfaces[i + 1].deferredFrom = nullptr;
+    batch.interfaces[i + 1].deferredLearnt = nullptr;
     layers[i]->forwards(batch, batch.interfaces[i], batch.interfaces[i + 1]);
   }
   if (timing) cudaSafeCall(cudaEventRecord(events[layers.size()], memStream.stream));

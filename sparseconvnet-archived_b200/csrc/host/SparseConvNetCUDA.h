@@ -15,6 +15,7 @@ class SparseConvNetCUDA {
 public:
   // The first convolution + NiN pair is launched right behind the rule chain, before the row counts are
   // read back (its kernel takes its count from device memory), so the GPU works while the host waits.
+  bool fusePooling;         // builders mark learnt layers that a non-overlapping max pooling follows (see NetworkInNetworkLayer::fusePoolNext)
   bool earlyFirstLayer;
   int earlyLayers;          // layers of the current batch already launched by preprocessBatchOnDevice (0 or 2)
   cudaStream_t countStream; // the row counts are read back on this stream, so that the early first layer does not delay them

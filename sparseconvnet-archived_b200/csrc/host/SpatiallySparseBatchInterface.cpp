@@ -17,7 +17,7 @@ SpatiallySparseBatchInterface::SpatiallySparseBatchInterface(SpatiallySparseBatc
     : sub(o.sub), nFeatures(o.nFeatures), featuresPresent(std::move(o.featuresPresent)), nSpatialSites(o.nSpatialSites),
       spatialSize(o.spatialSize), backpropErrors(o.backpropErrors), grids(std::move(o.grids)), rules(std::move(o.rules)),
       siteKeys(std::move(o.siteKeys)), sampleOffsets(std::move(o.sampleOffsets)), backgroundRows(std::move(o.backgroundRows)),
-      maxSitesPerSample(o.maxSitesPerSample), gridOwner(this), deferredFrom(nullptr), deferredCells(0) {}
+      maxSitesPerSample(o.maxSitesPerSample), gridOwner(this), deferredFrom(nullptr), deferredCells(0), deferredLearnt(nullptr), deferredLearntInput(nullptr) {}
 void SpatiallySparseBatchInterface::summary() {
   std::cout << "nFeatures " << nFeatures << " featuresPresent " << featuresPresent.size() << " spatialSize " << spatialSize
             << " nSpatialSites " << nSpatialSites << " features " << sub->features.size() << " grids " << grids.size() << std::endl;
@@ -33,6 +33,8 @@ void SpatiallySparseBatchInterface::reset() {
   gridOwner = this;
   deferredFrom = nullptr;
   deferredCells = 0;
+  deferredLearnt = nullptr;
+  deferredLearntInput = nullptr;
 }
 
 // Flatten host grids into keys[row] / offsets / background rows.  Rows of a sample must be

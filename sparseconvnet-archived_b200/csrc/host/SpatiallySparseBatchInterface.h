@@ -39,6 +39,11 @@ public:
   // out[r] = concat_f in[rules[r*fs+f]] is implied.
   SpatiallySparseBatchInterface *deferredFrom;
   int deferredCells;
+  // The same one step later: a NetworkInNetworkLayer that is followed by a non-overlapping max-pooling layer
+  // leaves its output unmaterialised (`deferredLearnt` = the layer, `deferredLearntInput` = its input interface)
+  // and the pooling layer runs convolution, learnt layer and pooling as one kernel.
+  class NetworkInNetworkLayer *deferredLearnt;
+  SpatiallySparseBatchInterface *deferredLearntInput;
 
   explicit SpatiallySparseBatchInterface(SpatiallySparseBatchSubInterface *s);
   SpatiallySparseBatchInterface(SpatiallySparseBatchInterface &&o) noexcept; // pointers into a moved-from interface are dropped

@@ -140,6 +140,19 @@ int scn_net_addLeNetLayerFMP(scn_net_t *net, int kind, int nFeatures, int fs, in
     }
   });
 }
+int scn_net_set_pool_fusion(scn_net_t *net, int on) {
+  return guarded([&] {
+    auto &L = net->cnn->layers;
+    for (size_t i = 2; i < L.size(); ++i) {
+      auto conv = dynamic_cast<ConvolutionalLayer *>(L[i - 2]);
+      auto nin = dynamic_cast<NetworkInNetworkLayer *>(L[i - 1]);
+      auto pool = dynamic_cast<MaxPoolingLayer *>(L[i]);
+      if (!conv || !nin || !pool) continue;
+      const int cells = pool->sd;
+      nin->fusePoolNext = on && pool->poolSize == pool->poolStride && cells >= 2 && cells <= 32 && (cells & (cells - 1)) == 0;
+    }
+  });
+}
 int scn_net_seed_fmp(scn_net_t *net, unsigned seed) {
   return guarded([&] {
     for (size_t l = 0; l < net->cnn->layers.size(); ++l)
@@ -318,6 +331,7 @@ int scn_net_iface_fetch(scn_net_t *net, int i, float *features, int *rules, int 
     cudaSafeCall(cudaStreamSynchronize(net->cnn->memStream.stream));
     if (features) {
       if (I.deferredFrom) throw ScnException("this interface's gather is fused into the next layer and was never materialised");
+      if (I.deferredLearnt) throw ScnException("this interface's learnt layer is fused into the pooling layer behind it and was never materialised");
       size_t n = (size_t)I.nSpatialSites * I.nFeatures;
       if (I.sub->features.size() != n) throw ScnException("interface features are no longer resident");
       if (n) cudaSafeCall(cudaMemcpy(features, I.sub->features.dPtr(), sizeof(float) * n, cudaMemcpyDeviceToHost));

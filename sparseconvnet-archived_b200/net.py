@@ -13,7 +13,7 @@ from . import HOST_LIB, abi
 c_int, c_ll, c_f, c_p, c_d = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_double
 
 EXPORTS = [
-    "scn_net_last_error", "scn_net_create", "scn_net_destroy", "scn_net_addLeNetLayerMP", "scn_net_addLeNetLayerFMP", "scn_net_seed_fmp",
+    "scn_net_last_error", "scn_net_create", "scn_net_destroy", "scn_net_addLeNetLayerMP", "scn_net_addLeNetLayerFMP", "scn_net_seed_fmp", "scn_net_set_pool_fusion",
     "scn_net_addTerminalPoolingLayer", "scn_net_addSoftmaxLayer", "scn_net_DeepCNet", "scn_net_n_layers",
     "scn_net_input_spatial_size", "scn_net_layer_info", "scn_net_set_weights", "scn_net_load_weights",
     "scn_net_save_weights", "scn_net_set_precision", "scn_net_forward_host", "scn_net_forward_device",
@@ -48,6 +48,7 @@ def lib():
         L.scn_net_addLeNetLayerMP.argtypes = [c_p] + [c_int] * 6 + [c_f, c_int]
         L.scn_net_addLeNetLayerFMP.argtypes = [c_p] + [c_int] * 5 + [c_f, c_int, c_f, c_int]
         L.scn_net_seed_fmp.argtypes = [c_p, ctypes.c_uint]
+        L.scn_net_set_pool_fusion.argtypes = [c_p, c_int]
         L.scn_net_addTerminalPoolingLayer.argtypes = [c_p, c_int]
         L.scn_net_addSoftmaxLayer.argtypes = [c_p]
         L.scn_net_DeepCNet.restype = c_p
@@ -121,6 +122,10 @@ class Net:
     def addLeNetLayerFMP(self, kind, nFeatures, fs, fstride, ps, fmpShrink, act=abi.RELU, dropout=0.0, minActive=1):
         """Convolution block + fractional max-pooling: kind FMP_PO, FMP_PD, FMP_RO or FMP_RD."""
         _check(self.L.scn_net_addLeNetLayerFMP(self.h, kind, nFeatures, fs, fstride, ps, fmpShrink, act, dropout, minActive))
+
+    def set_pool_fusion(self, on):
+        """Fuse convolution + learnt layer + non-overlapping max pooling into one kernel (default) or not."""
+        _check(self.L.scn_net_set_pool_fusion(self.h, int(bool(on))))
 
     def seed_fmp(self, seed):
         """Re-seed every FMP layer's RNG (layer l gets seed + l) before the next forward."""

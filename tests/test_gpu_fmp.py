@@ -62,15 +62,14 @@ def test_fmp_network_layer_by_layer(scn, abi, oracle, kind, dim, l, k, shrink):
         gprobs, gpred = gnet.forward_host(keys, off, feats)
         layers = gnet.layers()
         for i in range(len(layers) + 1):
-            fused_gather = i > 0 and layers[i - 1]["type"] in (0, 1)
-            g = gnet.iface(i, features=not fused_gather)
+            g = gnet.iface(i, features=False)
             o = onet.iface(i)
             assert g["nSpatialSites"] == o["nSpatialSites"], i
             assert g["spatialSize"] == o["spatialSize"], i
             np.testing.assert_array_equal(g["rules"], o["rules"], err_msg="rules of interface %d" % i)
             np.testing.assert_array_equal(g["row_keys"], o["row_keys"], err_msg="grid of interface %d" % i)
             if i > 0 and layers[i - 1]["type"] not in (0, 1):
-                assert relerr(g["features"], o["features"]) < RTOL, "features of interface %d" % i
+                assert relerr(gnet.iface(i)["features"], o["features"]) < RTOL, "features of interface %d" % i
         assert relerr(gprobs, oprobs) < RTOL
         np.testing.assert_array_equal(gpred, opred)
 

@@ -263,3 +263,50 @@ def test_conv_nin_with_row_count_on_the_device(abi, oracle):
                                     d_rows, bound, None, 0.9, abi.VLEAKYRELU, packed)
     torch.cuda.synchronize()
     assert abi.conv_tc_take_error() == 0 and np.isfinite(out2.cpu().numpy()).all()
+
+
+@pytest.mark.parametrize("rows_in,windows,fs,nIn,N,cells,act", [
+    (600, 333, 4, 32, 64, 4, "VLEAKYRELU"),     # ragged last tile, A from tensor memory
+    (1200, 700, 9, 3, 96, 4, "VLEAKYRELU"),     # the benchmark's first convolution + pooling (element-wise gather)
+    (500, 150, 4, 96, 192, 4, "RELU"),
+    (300, 90, 8, 32, 288, 8, "LEAKYRELU"),      # 2^3 windows, two column tiles
+    (200, 70, 4, 64, 32, 2, "PRELU"),
+])
+def test_conv_nin_maxpool_fused(abi, oracle, rows_in, windows, fs, nIn, N, cells, act):
+    """Gather + NiN + non-overlapping max pooling in one kernel against the oracle's three steps: pooled values
+    within the fp32 tolerance, every choice names an input whose value is the window's maximum."""
+    from oracle import orc
+    rng = np.random.default_rng(windows + N)
+    actc = getattr(orc, act)
+    K = fs * nIn
+    rows_mid = windows * cells + 5  # rows of the learnt layer's output (a few are in no window)
+    feat = rng.standard_normal((rows_in, nIn)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * np.sqrt(2.0 / K)).astype(np.float32)
+    B = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    prelu = rng.uniform(0.1, 0.4, N).astype(np.float32) if act == "PRELU" else None
+    rules = random_rules(rng, rows_mid, fs, rows_in)
+    pool = rng.permutation(rows_mid)[: windows * cells].astype(np.int32).reshape(windows, cells)
+    pool[rng.random(pool.shape) < 0.15] = -1      # cells without an input
+    pool[3] = -1                                   # a window with none at all
+    pool[5, 1:] = pool[5, 0]                       # the same row several times: the first wins
+    X = oracle.gather(feat, rules, nIn).reshape(rows_mid, K)
+    mid = oracle.nin_forward(X, W, B, prelu, 0.9, actc, accum64=True)
+    ref_v, ref_c = oracle.maxpool(mid.astype(np.float32), pool, cells)
+    dW = torch.from_numpy(W).cuda()
+    packed = abi.pack_weights(dW, abi.PREC_3XTF32)
+    out, ch = abi.conv_nin_maxpool_forward(torch.from_numpy(feat).cuda(), torch.from_numpy(rules).cuda().flatten(), fs, dW,
+                                           torch.from_numpy(B).cuda(), torch.from_numpy(pool).cuda().flatten(), cells,
+                                           None if prelu is None else torch.from_numpy(prelu).cuda(), 0.9, actc, packed)
+    torch.cuda.synchronize()
+    assert abi.conv_tc_take_error() == 0
+    out, ch = out.cpu().numpy(), ch.cpu().numpy()
+    assert relerr(out, ref_v) < RTOL_FP32
+    assert (ch[3] == -1).all() and not out[3].any()
+    ok = ch >= 0
+    assert (ok == (ref_c >= 0)).all()
+    picked = mid.reshape(-1)[ch[ok]]
+    assert np.abs(picked - ref_v[ok]).max() <= 1e-4 * np.abs(ref_v).max()  # a choice may differ from the oracle's only between near-equal values
+    rows_of = ch[ok] // N
+    assert (ch[ok] % N == np.broadcast_to(np.arange(N), ch.shape)[ok]).all()
+    assert np.isin(rows_of, pool[pool >= 0]).all()
+    assert (ch[5] == pool[5, 0] * N + np.arange(N)).all()

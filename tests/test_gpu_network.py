@@ -57,8 +57,9 @@ def test_deepcnet_builder_rounds_widths(scn, abi, oracle):
 
 
 @pytest.mark.parametrize("cfg", [1, 2, 3, 4, 5])
+@pytest.mark.parametrize("fusion", [False, True])
 @pytest.mark.parametrize("precision", ["fp32", "auto", "3xtf32", "3xbf16", "bf16"])
-def test_forward_layer_by_layer(scn, abi, nets, cfg, precision):
+def test_forward_layer_by_layer(scn, abi, nets, cfg, precision, fusion):
     """Rulebooks and grids bit-exact; features of every interface and the probabilities within 1e-4 of
     the fp64-accumulating oracle for fp32 and the two split tensor-core precisions, within 2e-2 for the
     optional plain-bf16 precision; top-1 agrees (bf16: at least 99.9 % over the batch)."""
@@ -66,13 +67,15 @@ def test_forward_layer_by_layer(scn, abi, nets, cfg, precision):
     gnet.set_precision(dict(fp32=abi.PREC_FP32, auto=abi.PREC_AUTO, **{"3xtf32": abi.PREC_3XTF32, "3xbf16": abi.PREC_3XBF16},
                             bf16=abi.PREC_BF16)[precision])
     RTOL = 2e-2 if precision == "bf16" else 1e-4
+    # fusion: convolution + learnt layer + non-overlapping pooling as one kernel (the default); the learnt layer's
+    # own output is then never written, so only the run without fusion compares it
+    gnet.set_pool_fusion(fusion)
     keys, off, feats = scn.synth.CONFIGS[cfg]["gen"](BATCH[cfg])
     oprobs, opred = onet.forward(keys, off, feats, accum64=True, keep=True)
     gprobs, gpred = gnet.forward_host(keys, off, feats)
     layers = gnet.layers()
     for i in range(len(layers) + 1):
-        fused_gather = i > 0 and layers[i - 1]["type"] in (0, 1)
-        g = gnet.iface(i, features=not fused_gather)
+        g = gnet.iface(i, features=False)
         o = onet.iface(i)
         assert g["nSpatialSites"] == o["nSpatialSites"], i
         assert g["spatialSize"] == o["spatialSize"], i
@@ -84,7 +87,11 @@ def test_forward_layer_by_layer(scn, abi, nets, cfg, precision):
         t = layers[i - 1]["type"]
         if t in (0, 1):
             continue
-        g = gnet.iface(i)
+        try:
+            g = gnet.iface(i)
+        except abi.ScnError as e:
+            assert fusion and t == 2 and "fused into the pooling layer" in str(e)
+            continue
         o = onet.iface(i)
         assert relerr(g["features"], o["features"]) < RTOL, "features of interface %d" % i
     assert relerr(gprobs, oprobs) < RTOL
@@ -93,6 +100,7 @@ def test_forward_layer_by_layer(scn, abi, nets, cfg, precision):
     else:
         np.testing.assert_array_equal(gpred, opred)
     gnet.set_precision(abi.PREC_AUTO)
+    gnet.set_pool_fusion(True)
 
 
 @pytest.mark.parametrize("cfg", [1, 3, 4])
