@@ -42,6 +42,11 @@ WORKLOAD = ("config 2: CIFAR-10-shaped dense 32x32x3 N(0,1) patch in a 96x96 gri
             "VLeakyReLU, test-time dropout scaling p=0.5 ramp, softmax 10), batch 256 per GPU")
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of k_conv_nin_tc, averaged over the launches with K >= 128 of one
+# forward of config 2, batch 256 (profiles/conv_nin_tc_cfg2_batch256.md)
+TC_TRAFFIC = 18.7e6
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -375,6 +380,20 @@ def main():
             C = sizes[i + 1]["nFeatures"]
             byts = 4.0 * (rows_out * L["fs"] + rows_in * C + 2 * rows_out * C)
             per_layer.append(dict(layer=i, kernel="maxpool_rules", rows=rows_out, C=C, ms=ms, flops=0.0, bytes=byts))
+    # A learnt layer that a non-overlapping max pooling follows leaves its output to the pooling layer; where that
+    # layer ran convolution, learnt layer and pooling as one kernel (layer info `act` = 1) the two are one launch.
+    merged = []
+    for d in per_layer:
+        prev = merged[-1] if merged else None
+        if (d["kernel"] == "maxpool_rules" and layers[d["layer"]]["act"] == 1 and prev is not None
+                and prev["kernel"] == "conv_nin_fused" and prev["layer"] == d["layer"] - 1):
+            prev["kernel"] = "conv_nin_maxpool_fused"
+            prev["ms"] += d["ms"]
+            prev["bytes"] += 4.0 * (d["rows"] * layers[d["layer"]]["fs"] + 2 * d["rows"] * d["C"] - prev["rows"] * prev["N"])
+            prev["pooled_rows"] = d["rows"]
+        else:
+            merged.append(d)
+    per_layer = merged
     rules_ms = float(layer_ms[len(layers)])
     # The dominant kernel of the step is the tensor-core fused conv/NiN kernel (k_conv_nin_tc): its
     # launches with K >= 128 are tensor-bound, so the roofline entry is their algorithmic flops per
@@ -385,7 +404,7 @@ def main():
     if tc and args.precision != "fp32":
         ach = sum(d["flops"] for d in tc) / (sum(d["ms"] for d in tc) * 1e-3) / 1e12
         roof = dict(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"],
-                    traffic=18.7e6 if (world == 1 and CFG == 2 and BATCH_PER_GPU == 256) else None, kernel="k_conv_nin_tc (%d launches per step with K >= 128)" % len(tc),
+                    traffic=TC_TRAFFIC if (world == 1 and CFG == 2 and BATCH_PER_GPU == 256) else None, kernel="k_conv_nin_tc (%d launches per step with K >= 128, %d of them with the max pooling fused in)" % (len(tc), sum(d["kernel"] == "conv_nin_maxpool_fused" for d in tc)),
                     ms_per_launch=sum(d["ms"] for d in tc) / len(tc), share_of_step=sum(d["ms"] for d in tc) / step_ms,
                     issued_tf32_tflops=3 * ach,
                     note="peak is the measured bf16 cuBLAS figure; kind::tf32 runs at half that rate and 3xTF32 issues 3 MMAs "

@@ -51,7 +51,8 @@ int scn_net_n_layers(scn_net_t *net);
 int scn_net_input_spatial_size(scn_net_t *net);
 /* info[10] = type (0 conv, 1 triangular conv, 2 NiN, 3 max pool, 4 triangular max pool,
  * 5 terminal pool), size, stride, minActiveInputs, nFeaturesIn, nFeaturesOut, cells,
- * activation, inSpatialSize, outSpatialSize. */
+ * activation, inSpatialSize, outSpatialSize.  For a max pooling layer `activation` is 1 when its last
+ * forward ran inside the kernel of the convolution + learnt layer in front of it, else 0. */
 int scn_net_layer_info(scn_net_t *net, int layer, int *info, float *dropout);
 /* Set NetworkInNetworkLayer::W, B (and PReLU) of layer `layer` from host arrays
  * (NetworkInNetworkLayer.h:12-19). */

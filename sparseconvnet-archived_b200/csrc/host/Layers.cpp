@@ -148,6 +148,7 @@ void maxPool(float *g1, float *g2, int *rules, int count, int sd, int nOut, int 
 MaxPoolingLayer::MaxPoolingLayer(cudaMemStream &memStream, int poolSize, int poolStride, int dimension)
     : SpatiallySparseLayer(memStream), inSpatialSize(0), outSpatialSize(0), poolSize(poolSize), poolStride(poolStride), dimension(dimension) {
   changesGeometry = true;
+  fusedLast = false; splitEvent = nullptr; splitRecorded = false;
   sd = ipow(poolSize, dimension);
   std::cout << "MaxPooling " << poolSize << " " << poolStride << std::endl;
 }
@@ -168,16 +169,20 @@ void MaxPoolingLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBat
   preprocessNow(*this, batch, input, output);
 }
 void MaxPoolingLayer::forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  fusedLast = false; splitRecorded = false;
   if (input.deferredLearnt) { // convolution + learnt layer + this pooling as one kernel, if it takes the case
     NetworkInNetworkLayer *nin = input.deferredLearnt;
     SpatiallySparseBatchInterface &ninInput = *input.deferredLearntInput;
     if (poolSize == poolStride &&
         nin->forwardsPooled(batch, *ninInput.deferredFrom, ninInput, output, ninInput.deferredCells, sd, output.nSpatialSites, nullptr,
-                            input.nSpatialSites))
+                            input.nSpatialSites)) {
+      fusedLast = true;
       return;
+    }
     input.deferredLearnt = nullptr; // not taken: materialise the learnt layer's output after all, then pool it
     input.sub->reset();
     nin->forwardsNow(batch, ninInput, input);
+    if (splitEvent) { cudaSafeCall(cudaEventRecord(splitEvent, memStream.stream)); splitRecorded = true; }
   }
   const int n = output.nSpatialSites * output.featuresPresent.size();
   output.sub->poolingChoices.resize(n);

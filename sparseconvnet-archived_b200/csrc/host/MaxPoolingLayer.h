@@ -8,6 +8,11 @@ void maxPool(float *g1, float *g2, int *rules, int count, int sd, int nOut, int 
 class MaxPoolingLayer : public SpatiallySparseLayer {
 public:
   int inSpatialSize, outSpatialSize, poolSize, poolStride, dimension, sd;
+  bool fusedLast; // the last forward ran inside the kernel of the convolution + learnt layer in front of it
+  // With layer timing on: recorded between the learnt layer's kernel and the pooling kernel when this layer
+  // ran both (the learnt layer had left its output to it, and the one-kernel form did not take the case).
+  cudaEvent_t splitEvent;
+  bool splitRecorded;
   MaxPoolingLayer(cudaMemStream &memStream, int poolSize, int poolStride, int dimension);
   void preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
   void forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);

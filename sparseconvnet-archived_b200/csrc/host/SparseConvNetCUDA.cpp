@@ -47,6 +47,9 @@ SparseConvNetCUDA::~SparseConvNetCUDA() {
   for (auto e : events) cudaEventDestroy(e);
   if (chainDone) cudaEventDestroy(chainDone);
   if (countStream) cudaStreamDestroy(countStream);
+  for (auto L : layers)
+    if (auto m = dynamic_cast<MaxPoolingLayer *>(L))
+      if (m->splitEvent) cudaEventDestroy(m->splitEvent);
   for (auto p : layers) delete p;
   batchPool.clear();
   for (auto p : initialSubInterfaces) delete p;
@@ -205,7 +208,7 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
       MaxPoolingLayer *pool = nL >= 3 ? dynamic_cast<MaxPoolingLayer *>(layers[2]) : nullptr;
       if (nin->fusePoolNext && pool && pool->poolSize == pool->poolStride &&
           nin->forwardsPooled(batch, batch.interfaces[0], batch.interfaces[1], batch.interfaces[3], convCells, pool->sd, bound2, d_res + 8))
-        earlyLayers = 3; // convolution + learnt layer + pooling, the pooled row count read from the pooling layer's record
+      { earlyLayers = 3; pool->fusedLast = true; } // convolution + learnt layer + pooling, the pooled row count read from the pooling layer's record
       else if (nin->forwardsEarly(batch, batch.interfaces[0], batch.interfaces[1], batch.interfaces[2], convCells, bound0, d_res))
         earlyLayers = 2;
       if (earlyLayers) {
@@ -277,6 +280,11 @@ void SparseConvNetCUDA::enableTiming(bool on) {
     cudaSafeCall(cudaEventCreate(&e));
     events.push_back(e);
   }
+  for (auto L : layers)
+    if (auto m = dynamic_cast<MaxPoolingLayer *>(L)) {
+      if (on && !m->splitEvent) cudaSafeCall(cudaEventCreate(&m->splitEvent));
+      if (!on && m->splitEvent) { cudaSafeCall(cudaEventDestroy(m->splitEvent)); m->splitEvent = nullptr; }
+    }
 }
 std::vector<float> SparseConvNetCUDA::layerTimes() {
   std::vector<float> ms(layers.size() + 1, 0.f);
@@ -285,6 +293,14 @@ std::vector<float> SparseConvNetCUDA::layerTimes() {
   const size_t nL = layers.size();
   for (size_t i = 0; i < nL; ++i) cudaSafeCall(cudaEventElapsedTime(&ms[i], events[i], events[i + 1]));
   cudaSafeCall(cudaEventElapsedTime(&ms[nL], events[nL + 1], events[nL + 2]));
+  for (size_t i = 1; i < nL; ++i) // a pooling layer that ran the learnt layer in front of it as a kernel of its own
+    if (auto m = dynamic_cast<MaxPoolingLayer *>(layers[i]))
+      if (m->splitEvent && m->splitRecorded) {
+        float t = 0;
+        cudaSafeCall(cudaEventElapsedTime(&t, events[i], m->splitEvent));
+        ms[i - 1] += t;
+        ms[i] -= t;
+      }
   return ms;
 }
 

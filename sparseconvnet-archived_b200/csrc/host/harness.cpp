@@ -56,7 +56,7 @@ void describe(SpatiallySparseLayer *L, int *info, float *dropout) {
     std::memcpy(v, w, sizeof(v));
     *dropout = n->dropout;
   } else if (auto m = dynamic_cast<MaxPoolingLayer *>(L)) {
-    int w[10] = {3, m->poolSize, m->poolStride, 1, 0, 0, m->sd, 0, m->inSpatialSize, m->outSpatialSize};
+    int w[10] = {3, m->poolSize, m->poolStride, 1, 0, 0, m->sd, m->fusedLast ? 1 : 0, m->inSpatialSize, m->outSpatialSize};
     std::memcpy(v, w, sizeof(v));
   } else if (auto m = dynamic_cast<MaxPoolingTriangularLayer *>(L)) {
     int w[10] = {4, m->poolSize, m->poolStride, 1, 0, 0, m->S, 0, m->inSpatialSize, m->outSpatialSize};
