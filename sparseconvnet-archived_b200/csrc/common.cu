@@ -1,4 +1,5 @@
 // Error reporting, device queries and status strings of libscn_b200.so.
+#include <cstdlib>
 #include "scn_common.cuh"
 #include <atomic>
 #include <cstdarg>
@@ -17,6 +18,10 @@ void set_error(const char *fmt, ...) {
 void clear_error() { g_err[0] = 0; }
 
 static std::atomic<long long> g_launches{0};
+bool dependent_launch_enabled() {
+  static const bool on = [] { const char *e = std::getenv("SCN_DEPENDENT_LAUNCH"); return !(e && e[0] == '0'); }();
+  return on;
+}
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int sm_count() {

@@ -193,6 +193,107 @@ k_nin_smalln(const float *__restrict__ in, const int *__restrict__ rules, int ro
   }
 }
 
+// The same layer when W fits shared memory (the usual classifier: 608 x 10).  k_nin_smalln waits for L2 in
+// each of its K/32 iterations (17 us on 256 rows).  Here a CTA fetches W (row stride made odd in shared
+// memory, so that the lanes' reads fall in distinct banks) and the (gathered) input rows of its eight warps
+// with batches of independent 16-byte loads held in registers, so that the whole fetch costs two or three
+// round trips to L2, and the sums run out of shared memory.  Needs nIn % 4 == 0, (K * N) % 4 == 0 and
+// 16-byte aligned arrays.
+template <int NMAX>
+__global__ void __launch_bounds__(256)
+k_nin_smalln_staged(const float *__restrict__ in, const int *__restrict__ rules, int rows, int fs, int nIn,
+                    const float *__restrict__ W, const float *__restrict__ B, const float *__restrict__ prelu, int N,
+                    float p, int act, float *__restrict__ out) {
+  extern __shared__ float sm[];
+  constexpr int U = 8, R = 8;
+  const int K = fs * nIn, NP = N | 1, K4 = K >> 2;
+  float *wS = sm;                   // [K][NP]
+  float *xS = sm + (size_t)K * NP;  // [R][K]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  dependents_may_launch();
+  const int nW4 = (K * N) >> 2;
+  for (int base = 0; base < nW4; base += 256 * U) { // the weights do not come from the kernel in front
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u * 256 + threadIdx.x;
+      v[u] = i < nW4 ? __ldg(reinterpret_cast<const float4 *>(W) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = base + u * 256 + threadIdx.x;
+      if (i < nW4) {
+        const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int k = (4 * i + c) / N;
+          wS[k * NP + (4 * i + c - k * N)] = e[c];
+        }
+      }
+    }
+  }
+  wait_for_prior_grids();
+  for (int row0 = blockIdx.x * R; row0 < rows; row0 += gridDim.x * R) {
+    __syncthreads();
+    for (int base = 0; base < R * K4; base += 256 * U) {
+      int src[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) { // rule reads first, then the feature reads that depend on them
+        const int i = base + u * 256 + threadIdx.x, r = i / K4, row = row0 + r;
+        src[u] = -1;
+        if (i < R * K4 && row < rows) src[u] = rules ? __ldg(rules + (long long)row * fs + (4 * (i - r * K4)) / nIn) : row;
+      }
+      float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = base + u * 256 + threadIdx.x, r = i / K4, k = 4 * (i - r * K4);
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src[u] >= 0) v[u] = *reinterpret_cast<const float4 *>(in + (long long)src[u] * nIn + (k % nIn));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = base + u * 256 + threadIdx.x;
+        if (i < R * K4) reinterpret_cast<float4 *>(xS)[i] = v[u];
+      }
+    }
+    __syncthreads();
+    const int row = row0 + warp;
+    if (row >= rows) continue;
+    float acc[NMAX];
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) acc[n] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float x = xS[warp * K + k];
+      const float *w = wS + k * NP;
+#pragma unroll
+      for (int n = 0; n < NMAX; ++n)
+        if (n < N) acc[n] = fmaf(x, w[n], acc[n]);
+    }
+    float mine = 0.f;
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      float v = acc[n];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == n) mine = v;
+    }
+    const bool valid = lane < N;
+    float v = valid ? p * mine + p * __ldg(B + lane) : -10000.0f;
+    if (act == SCN_SOFTMAX) {
+      float mx = fmaxf(v, -10000.0f);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float e = valid ? expf(v - mx) : 0.f, sum = e;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      v = e / sum;
+    } else if (valid) {
+      v = activate(v, act, prelu ? __ldg(prelu + lane) : 0.f);
+    }
+    if (valid) out[(long long)row * N + lane] = v;
+  }
+}
+
 // Few rows (one per sample at the top of a network) and any N: one CTA per row, the (gathered) input row
 // in shared memory, threads over the output columns, so that W is read coalesced and each thread runs
 // K independent FMAs.  The tile kernel would leave all but a couple of SMs idle on such a layer.
@@ -297,6 +398,19 @@ extern "C" int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, in
     if (st != SCN_OK) return st;
   } else if (N <= 32) {
     // the classifier shape: warp per row, softmax fused
+    const size_t staged = ((size_t)fs * nIn * (N | 1) + 8 * (size_t)fs * nIn) * sizeof(float);
+    if (staged <= 96 * 1024 && nIn % 4 == 0 && (fs * nIn * N) % 4 == 0 && (((uintptr_t)d_in | (uintptr_t)d_W) & 15) == 0) {
+      const int tiles = (rows_out + 7) / 8, blocks = tiles < 4 * sm_count() ? tiles : 4 * sm_count();
+      if (N <= 16) {
+        if (staged > 48 * 1024) SCN_CUDA_TRY(cudaFuncSetAttribute(k_nin_smalln_staged<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        (void)launch_dependent(k_nin_smalln_staged<16>, dim3(blocks), dim3(256), staged, s, d_in, d_rules, rows_out, fs, nIn, d_W, d_B, d_prelu, N, p, act, d_out);
+      } else {
+        if (staged > 48 * 1024) SCN_CUDA_TRY(cudaFuncSetAttribute(k_nin_smalln_staged<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        (void)launch_dependent(k_nin_smalln_staged<32>, dim3(blocks), dim3(256), staged, s, d_in, d_rules, rows_out, fs, nIn, d_W, d_B, d_prelu, N, p, act, d_out);
+      }
+      SCN_LAUNCH_CHECK("k_nin_smalln_staged");
+      return SCN_OK;
+    }
     const int blocks = grid_for((long long)rows_out * 32, 256);
     if (N <= 16) k_nin_smalln<16><<<blocks, 256, 0, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B, d_prelu, N, p, act, d_out);
     else k_nin_smalln<32><<<blocks, 256, 0, s>>>(d_in, d_rules, rows_out, fs, nIn, d_W, d_B, d_prelu, N, p, act, d_out);

@@ -279,12 +279,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
                  accFullBar = smem_u32(&bars[3 * MAX_STAGES]), accEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 2]),
                  aFullBar = smem_u32(&bars[3 * MAX_STAGES + 4]), aEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 6]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // the row count may still be on its way to the host when this kernel is launched: read it from device memory
-  // (POOL: rows counts tile rows = pooled rows x cells, and the device-side count is in pooled rows)
-  const int rows = P.rowsPtr ? min(max(__ldg(P.rowsPtr), 0) * (POOL ? P.poolCells : 1), P.rows) : P.rows;
-  const int mTiles = P.rowsPtr ? (rows + BM - 1) / BM : P.mTiles;
-  const int kSplit = SPLIT ? P.kSplit : 1;
-  const int nItems = mTiles * P.nTiles * kSplit;
+  scn::dependents_may_launch(); // the next kernel's CTAs may take over SMs as this grid's CTAs leave them
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P.stages; ++s) {
@@ -306,6 +301,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmemBase;
+  scn::wait_for_prior_grids(); // everything above overlapped the kernel in front; its results are read from here on
+  // the row count may still be on its way to the host when this kernel is launched: read it from device memory
+  // (POOL: rows counts tile rows = pooled rows x cells, and the device-side count is in pooled rows)
+  const int rows = P.rowsPtr ? min(max(*(const volatile int *)P.rowsPtr, 0) * (POOL ? P.poolCells : 1), P.rows) : P.rows;
+  const int mTiles = P.rowsPtr ? (rows + BM - 1) / BM : P.mTiles;
+  const int kSplit = SPLIT ? P.kSplit : 1;
+  const int nItems = mTiles * P.nTiles * kSplit;
 
   // decode a work item
   auto itemTile = [&](int item, int &tileM, int &tileN, int &slab0, int &nLoc) {
@@ -928,6 +930,8 @@ __global__ void k_pack_tf32(const float *__restrict__ W, int K, int N, int BN, i
 template <int ACT>
 __global__ void k_splitk_finish(const float *__restrict__ partial, int kSplit, long long rows, int N, const float *__restrict__ bias,
                                 const float *__restrict__ prelu, float p, float *__restrict__ out) {
+  dependents_may_launch();
+  wait_for_prior_grids(); // the partial sums come from the kernel in front
   const long long n4 = rows * N / 4;
   const int nv = N >> 2;
   for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n4; q += (long long)gridDim.x * blockDim.x) {
@@ -1145,27 +1149,27 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   else if (passes == 1) SCN_TC16_LAUNCH(1);
   else if (pool && P.atmem) {
     SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-                     (k_conv_nin_tc<false, ACT, true, true><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
+                     (void)launch_dependent(k_conv_nin_tc<false, ACT, true, true>, dim3(grid), dim3(NUM_THREADS), (size_t)t.smemBytes, s, P));
   } else if (pool) {
     SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-                     (k_conv_nin_tc<false, ACT, false, true><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
+                     (void)launch_dependent(k_conv_nin_tc<false, ACT, false, true>, dim3(grid), dim3(NUM_THREADS), (size_t)t.smemBytes, s, P));
   } else if (P.atmem && P.kSplit > 1) {
     SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<true, SCN_NOSIGMOID, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    k_conv_nin_tc<true, SCN_NOSIGMOID, true><<<grid, NUM_THREADS, t.smemBytes, s>>>(P);
+    (void)launch_dependent(k_conv_nin_tc<true, SCN_NOSIGMOID, true>, dim3(grid), dim3(NUM_THREADS), (size_t)t.smemBytes, s, P);
   } else if (P.atmem) {
     SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-                     (k_conv_nin_tc<false, ACT, true><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
+                     (void)launch_dependent(k_conv_nin_tc<false, ACT, true>, dim3(grid), dim3(NUM_THREADS), (size_t)t.smemBytes, s, P));
   } else if (P.kSplit > 1) {
     SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<true, SCN_NOSIGMOID, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-    k_conv_nin_tc<true, SCN_NOSIGMOID, false><<<grid, NUM_THREADS, t.smemBytes, s>>>(P);
+    (void)launch_dependent(k_conv_nin_tc<true, SCN_NOSIGMOID, false>, dim3(grid), dim3(NUM_THREADS), (size_t)t.smemBytes, s, P);
   } else {
     SCN_DISPATCH_ACT(act, SCN_CUDA_TRY(cudaFuncSetAttribute(k_conv_nin_tc<false, ACT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
-                     (k_conv_nin_tc<false, ACT, false><<<grid, NUM_THREADS, t.smemBytes, s>>>(P)));
+                     (void)launch_dependent(k_conv_nin_tc<false, ACT, false>, dim3(grid), dim3(NUM_THREADS), (size_t)t.smemBytes, s, P));
   }
 #undef SCN_TC16_LAUNCH
   SCN_LAUNCH_CHECK("k_conv_nin_tc");
   if (P.kSplit > 1) {
-    SCN_DISPATCH_ACT(act, (k_splitk_finish<ACT><<<grid_for((long long)rows * N / 4, 256), 256, 0, s>>>(P.partial, P.kSplit, rows, N, d_B, d_prelu, p, d_out)));
+    SCN_DISPATCH_ACT(act, (void)launch_dependent(k_splitk_finish<ACT>, dim3(grid_for((long long)rows * N / 4, 256)), dim3(256), (size_t)0, s, (const float *)P.partial, P.kSplit, rows, N, d_B, d_prelu, p, d_out));
     SCN_LAUNCH_CHECK("k_splitk_finish");
   }
   return SCN_OK;

@@ -11,6 +11,8 @@ namespace {
 template <int VEC>
 __global__ void k_maxpool(const float *__restrict__ in, const int *__restrict__ rules, int rowsOut, int sd, int C,
                           float *__restrict__ out, int *__restrict__ choice) {
+  dependents_may_launch();
+  wait_for_prior_grids(); // the features come from the kernel in front
   const int cv = C / VEC;
   const long long n = (long long)rowsOut * cv;
   for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < n; q += (long long)gridDim.x * blockDim.x) {
@@ -165,8 +167,8 @@ extern "C" int scn_maxpool_forward(const float *d_in, const int *d_rules, int ro
   if (!d_in || !d_rules || !d_out || !d_choices) return fail(SCN_ERR_INVALID, "null pointer");
   cudaStream_t s = (cudaStream_t)stream;
   const bool vec = (C % 4 == 0) && ((uintptr_t)d_in % 16 == 0) && ((uintptr_t)d_out % 16 == 0) && ((uintptr_t)d_choices % 16 == 0);
-  if (vec) k_maxpool<4><<<grid_for((long long)rows_out * (C / 4), 256), 256, 0, s>>>(d_in, d_rules, rows_out, sd, C, d_out, d_choices);
-  else k_maxpool<1><<<grid_for((long long)rows_out * C, 256), 256, 0, s>>>(d_in, d_rules, rows_out, sd, C, d_out, d_choices);
+  if (vec) (void)launch_dependent(k_maxpool<4>, dim3(grid_for((long long)rows_out * (C / 4), 256)), dim3(256), (size_t)0, s, d_in, d_rules, rows_out, sd, C, d_out, d_choices);
+  else (void)launch_dependent(k_maxpool<1>, dim3(grid_for((long long)rows_out * C, 256)), dim3(256), (size_t)0, s, d_in, d_rules, rows_out, sd, C, d_out, d_choices);
   SCN_LAUNCH_CHECK("k_maxpool");
   return SCN_OK;
 }

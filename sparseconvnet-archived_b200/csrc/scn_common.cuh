@@ -41,6 +41,26 @@ inline int fail(int status, const char *what) {
     }                                                                                       \
   } while (0)
 
+// Programmatic dependent launch.  A kernel launched through launch_dependent() may start while the kernel
+// in front of it in the stream is still running, once all of that kernel's CTAs have called
+// dependents_may_launch() or exited; it must call wait_for_prior_grids() before it reads or writes any global
+// memory that an earlier kernel of the stream touches (the wait returns when the earlier grids have finished
+// and their writes are visible).  What runs before the wait (barrier and tensor-memory set-up, block scheduling)
+// overlaps the earlier kernel's last wave.  SCN_DEPENDENT_LAUNCH=0 in the environment gives plain launches.
+bool dependent_launch_enabled();
+__device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wait_for_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+template <class... KArgs, class... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled() ? 1 : 0;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Grid size for a grid-stride kernel over n items: enough CTAs to cover n, capped at
 // `waves` CTAs per SM so a launch never exceeds a few resident waves.
 inline int grid_for(long long n, int block, int waves = 8) {

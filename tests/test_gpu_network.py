@@ -206,3 +206,20 @@ def test_host_top_indices(scn, abi, oracle):
         for _ in range(20):
             v = np.round(rng.standard_normal(n) * 2).astype(np.float32)
             np.testing.assert_array_equal(scn.net.host_top_indices(v, k), oracle.top_indices(v, k))
+
+
+def test_alternating_batches_reuse_buffers(scn, abi, nets):
+    """Every layer's buffers are reused from one forward to the next, and with dependent launches a kernel's
+    set-up overlaps the end of the kernel in front of it: two different batches, alternated, must keep
+    giving the bits of their first forwards (no stale feature, rule or partial-sum reads)."""
+    gnet, _ = nets(2)
+    gnet.set_precision(abi.PREC_AUTO)
+    gnet.set_pool_fusion(True)
+    gen = scn.synth.CONFIGS[2]["gen"]
+    a, b = gen(24), gen(17, first=100)  # other inputs, other row counts
+    first = [np.array(gnet.forward_host(*x)[0], copy=True) for x in (a, b)]
+    assert not np.array_equal(first[0], first[1])
+    for it in range(12):
+        for x, want in zip((a, b), first):
+            got = gnet.forward_host(*x)[0]
+            assert np.array_equal(got, want), it
