@@ -33,6 +33,7 @@
 // records an error code in g_tc_error and carries on to its normal exit, so tensor memory is
 // always released and the context stays usable.
 #include "conv_nin_tc.cuh"
+#include <type_traits>
 #include <cuda_bf16.h>
 
 namespace scn {
@@ -211,27 +212,46 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint3
         if (ACT == SCN_PRELU) s4 = __ldg(reinterpret_cast<const float4 *>(P.prelu + col));
       }
       if (POOL) {
-        const int cells = P.poolCells, windows = BM / cells;
-        for (int pr = rsub; pr < windows; pr += 16) {
-          const long long w = (long long)tileM * windows + pr; // pooled row
-          if (!colOk || w * cells >= rows) continue;
-          float best[4] = {0.f, 0.f, 0.f, 0.f};
-          int idx[4] = {-1, -1, -1, -1};
-          bool none = true;
-          for (int cell = 0; cell < cells; ++cell) {
-            const int rl = pr * cells + cell, from = poolRow[rl];
-            if (from < 0) continue;
-            const float4 v = *reinterpret_cast<const float4 *>(epi + (size_t)rl * EPI_LD + c4 * 4);
-            const float o[4] = {activate_t<ACT>(P.p * v.x + P.p * b4.x, s4.x), activate_t<ACT>(P.p * v.y + P.p * b4.y, s4.y),
-                                activate_t<ACT>(P.p * v.z + P.p * b4.z, s4.z), activate_t<ACT>(P.p * v.w + P.p * b4.w, s4.w)};
-            const int base = from * P.N + col;
+        // the window's cells are read together (independent shared-memory loads), then compared in order
+        auto pool_windows = [&](auto cellsC, auto batchC) {
+          constexpr int CELLSC = decltype(cellsC)::value, CH = decltype(batchC)::value; // CELLSC == 0: any power of two
+          const int CELLS = CELLSC ? CELLSC : P.poolCells, WINDOWS = BM / CELLS;
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              if (none || best[k] < o[k]) { best[k] = o[k]; idx[k] = base + k; } // the first maximum wins
-            none = false;
+          for (int pr = rsub; pr < WINDOWS; pr += 16) { // (WINDOWS < 16: rows rsub >= WINDOWS have no window)
+            const long long w = (long long)tileM * WINDOWS + pr; // pooled row
+            if (!colOk || w * CELLS >= rows) continue;
+            float best[4] = {0.f, 0.f, 0.f, 0.f};
+            int idx[4] = {-1, -1, -1, -1};
+            bool none = true;
+#pragma unroll 1
+            for (int cell0 = 0; cell0 < CELLS; cell0 += CH) {
+              int from[CH];
+              float4 v[CH];
+#pragma unroll
+              for (int j = 0; j < CH; ++j) {
+                from[j] = poolRow[pr * CELLS + cell0 + j];
+                v[j] = *reinterpret_cast<const float4 *>(epi + (size_t)(pr * CELLS + cell0 + j) * EPI_LD + c4 * 4);
+              }
+#pragma unroll
+              for (int j = 0; j < CH; ++j) {
+                if (from[j] < 0) continue;
+                const float o[4] = {activate_t<ACT>(P.p * v[j].x + P.p * b4.x, s4.x), activate_t<ACT>(P.p * v[j].y + P.p * b4.y, s4.y),
+                                    activate_t<ACT>(P.p * v[j].z + P.p * b4.z, s4.z), activate_t<ACT>(P.p * v[j].w + P.p * b4.w, s4.w)};
+                const int base = from[j] * P.N + col;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                  if (none || best[k] < o[k]) { best[k] = o[k]; idx[k] = base + k; } // the first maximum wins
+                none = false;
+              }
+            }
+            *reinterpret_cast<float4 *>(P.out + w * P.N + col) = make_float4(best[0], best[1], best[2], best[3]);
+            *reinterpret_cast<int4 *>(P.choices + w * P.N + col) = make_int4(idx[0], idx[1], idx[2], idx[3]);
           }
-          *reinterpret_cast<float4 *>(P.out + w * P.N + col) = make_float4(best[0], best[1], best[2], best[3]);
-          *reinterpret_cast<int4 *>(P.choices + w * P.N + col) = make_int4(idx[0], idx[1], idx[2], idx[3]);
+        };
+        switch (P.poolCells) { // 2 x 2 and 2 x 2 x 2 windows unrolled; 2, 16 and 32 cells in batches of two
+        case 4: pool_windows(std::integral_constant<int, 4>(), std::integral_constant<int, 4>()); break;
+        case 8: pool_windows(std::integral_constant<int, 8>(), std::integral_constant<int, 8>()); break;
+        default: pool_windows(std::integral_constant<int, 0>(), std::integral_constant<int, 2>()); break;
         }
       } else
 #pragma unroll
@@ -391,43 +411,40 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
       }
       if (P.generic) {
         // nIn is not a multiple of 32 (e.g. 3 input channels): a slab spans several filter cells, so
-        // the tile is gathered word by word with 4-byte asynchronous copies.  Lane = position in the
-        // slab: its filter cell f and channel c are fixed per slab, and the 32 lanes of one copy
-        // instruction read neighbouring words of the few source rows that one output row names
-        // (9 sectors instead of 32 for a 3-channel 3x3 filter).  Each warp covers 32 rows; k >= K
-        // (padding up to a multiple of 32) and missing rows are zero-filled.  (Ordinary loads
-        // followed by shared stores were measured slower: they expose the load latency per slab.)
+        // the tile is gathered word by word.  Lane = position in the slab: its filter cell f and channel c
+        // are fixed per slab, and the 32 lanes of one load read neighbouring words of the few source rows
+        // that one output row names (9 sectors instead of 32 for a 3-channel 3x3 filter).  Each warp covers
+        // 32 rows with 32 independent loads held in registers, then stores them to the swizzled tile:
+        // one round trip to L2 per slab.  (4-byte asynchronous copies cost the load/store unit about a
+        // cycle per element, 4096 per slab, and starved the epilogue's loads and stores: the first
+        // convolution of the benchmark took 8700 cycles per tile in both roles.)  k >= K (padding up to a
+        // multiple of 32) and missing rows are zero.
         const int wq = warp - 4;
         for (int q = 0; q < nLoc; ++q, ring.next()) {
           const int s = slab0 + q, st = ring.idx;
           const int k = s * SLAB + lane;
           const bool kOk = k < P.K;
           const int f = kOk ? k / P.nIn : 0, c = k - f * P.nIn;
-          mbar_wait(emptyBar + 8 * st, ring.phase ^ 1, 1);
-          const uint32_t dst0 = smem_u32(smem + (size_t)st * stageBytes) + (uint32_t)wq * 4096 + (lane & 3) * 4;
-          // eight rows at a time: first all rule reads (independent of one another), then the copies,
-          // because the copy instructions keep their program order
-#pragma unroll 1
-          for (int i0 = 0; i0 < 32; i0 += 8) {
-            int src[8];
+          float v[32];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int rl = wq * 32 + i0 + j, r = row0 + rl;
-              src[j] = -1;
-              if (POOL) { if (kOk && fromT[rl] >= 0) src[j] = rulesT[rl * P.fs + f]; }
-              else if (kOk && r < rows) {
-                if (P.rulesBytes > 0) src[j] = rulesT[rl * P.fs + f];
-                else if (P.rules) src[j] = __ldg(P.rules + (long long)r * P.fs + f);
-                else src[j] = r;
-              }
+          for (int j = 0; j < 32; ++j) {
+            const int rl = wq * 32 + j, r = row0 + rl;
+            int src = -1;
+            if (POOL) { if (kOk && fromT[rl] >= 0) src = rulesT[rl * P.fs + f]; }
+            else if (kOk && r < rows) {
+              if (P.rulesBytes > 0) src = rulesT[rl * P.fs + f];
+              else if (P.rules) src = __ldg(P.rules + (long long)r * P.fs + f);
+              else src = r;
             }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const uint32_t dst = dst0 + (i0 >> 3) * 1024 + j * ROW_BYTES + (((lane >> 2) ^ j) << 4);
-              cp_async4(dst, src[j] >= 0 ? (const void *)(P.in + (long long)src[j] * P.nIn + c) : (const void *)P.in, src[j] >= 0 ? 4u : 0u);
-            }
+            v[j] = src >= 0 ? __ldg(P.in + (long long)src * P.nIn + c) : 0.f;
           }
-          cp_async_arrive(rawBar + 8 * st);
+          mbar_wait(emptyBar + 8 * st, ring.phase ^ 1, 1);
+          unsigned char *dst0 = smem + (size_t)st * stageBytes + wq * 4096 + (lane & 3) * 4;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            *reinterpret_cast<float *>(dst0 + (j >> 3) * 1024 + (j & 7) * ROW_BYTES + (((lane >> 2) ^ (j & 7)) << 4)) = v[j];
+          fence_async_smem(); // the tensor core reads the tile through the asynchronous proxy
+          mbar_arrive(rawBar + 8 * st);
         }
         continue;
       }
