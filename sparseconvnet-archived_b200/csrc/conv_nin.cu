@@ -217,7 +217,7 @@ k_nin_smalln_staged(const float *__restrict__ in, const int *__restrict__ rules,
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int i = base + u * 256 + threadIdx.x;
-      v[u] = i < nW4 ? __ldg(reinterpret_cast<const float4 *>(W) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[u] = __ldg(reinterpret_cast<const float4 *>(W) + (i < nW4 ? i : 0)); // unconditional: no select waits on the value
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -247,13 +247,12 @@ k_nin_smalln_staged(const float *__restrict__ in, const int *__restrict__ rules,
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int i = base + u * 256 + threadIdx.x, r = i / K4, k = 4 * (i - r * K4);
-        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (src[u] >= 0) v[u] = *reinterpret_cast<const float4 *>(in + (long long)src[u] * nIn + (k % nIn));
+        v[u] = *reinterpret_cast<const float4 *>(in + (long long)(src[u] >= 0 ? src[u] : 0) * nIn + (k % nIn));
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int i = base + u * 256 + threadIdx.x;
-        if (i < R * K4) reinterpret_cast<float4 *>(xS)[i] = v[u];
+        if (i < R * K4) reinterpret_cast<float4 *>(xS)[i] = src[u] >= 0 ? v[u] : make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
     __syncthreads();

@@ -44,6 +44,7 @@ __device__ int g_tc_error = 0;
 // from here instead of predicating each copy keeps the gather loop at three instructions per copy.
 constexpr int ZERO_ROW_FLOATS = 16384;
 __device__ __align__(128) float g_zero_row[ZERO_ROW_FLOATS];
+__device__ int g_no_row = -1; // what a load of a missing rule reads: loads stay unconditional, nothing selects on their values
 
 namespace {
 
@@ -367,13 +368,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
       int tileM, tileN, slab0, nLoc;
       itemTile(item, tileM, tileN, slab0, nLoc);
       const long long gr = (long long)tileM * BM + t;
-      return gr < rows ? __ldg(P.poolRules + gr) : -1;
+      return __ldg(gr < rows ? P.poolRules + gr : &g_no_row);
     };
     auto stage_rules_pool = [&](int buf, int from) {
       int *base = rulesS + buf * (P.rulesBytes >> 2);
       const uint32_t dst = smem_u32(base) + t * P.fs * 4;
-      for (int f = 0; f < P.fs; ++f)
-        cp_async4(dst + 4 * f, from >= 0 ? (const void *)(P.rules + (long long)from * P.fs + f) : (const void *)P.rules, from >= 0 ? 4u : 0u);
+      if (!P.generic) // (the word-by-word gather reads its rules from global memory, see there)
+        for (int f = 0; f < P.fs; ++f)
+          cp_async4(dst + 4 * f, from >= 0 ? (const void *)(P.rules + (long long)from * P.fs + f) : (const void *)P.rules, from >= 0 ? 4u : 0u);
       base[BM * P.fs + t] = from;
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -425,19 +427,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
           const int k = s * SLAB + lane;
           const bool kOk = k < P.K;
           const int f = kOk ? k / P.nIn : 0, c = k - f * P.nIn;
-          float v[32];
+          // every load is unconditional (a safe address for a missing row): a select on a loaded value would
+          // make the loads wait for one another
+          int src[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int rl = wq * 32 + j, r = row0 + rl;
-            int src = -1;
-            if (POOL) { if (kOk && fromT[rl] >= 0) src = rulesT[rl * P.fs + f]; }
-            else if (kOk && r < rows) {
-              if (P.rulesBytes > 0) src = rulesT[rl * P.fs + f];
-              else if (P.rules) src = __ldg(P.rules + (long long)r * P.fs + f);
-              else src = r;
+            if (POOL) { // the rules of the row that this tile row stands for, straight from global memory
+              const int from = fromT[rl];
+              src[j] = __ldg(kOk && from >= 0 ? P.rules + (long long)from * P.fs + f : &g_no_row);
+            } else {
+              src[j] = -1;
+              if (kOk && r < rows) {
+                if (P.rulesBytes > 0) src[j] = rulesT[rl * P.fs + f];
+                else if (P.rules) src[j] = __ldg(P.rules + (long long)r * P.fs + f);
+                else src[j] = r;
+              }
             }
-            v[j] = src >= 0 ? __ldg(P.in + (long long)src * P.nIn + c) : 0.f;
           }
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __ldg(src[j] >= 0 ? P.in + (long long)src[j] * P.nIn + c : g_zero_row);
           mbar_wait(emptyBar + 8 * st, ring.phase ^ 1, 1);
           unsigned char *dst0 = smem + (size_t)st * stageBytes + wq * 4096 + (lane & 3) * 4;
 #pragma unroll
