@@ -44,7 +44,7 @@ WORKLOAD = ("config 2: CIFAR-10-shaped dense 32x32x3 N(0,1) patch in a 96x96 gri
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of k_conv_nin_tc, averaged over the launches with K >= 128 of one
 # forward of config 2, batch 256 (profiles/conv_nin_tc_cfg2_batch256.md)
-TC_TRAFFIC = 18.7e6
+TC_TRAFFIC = 17.2e6
 
 
 def measured_peaks():
