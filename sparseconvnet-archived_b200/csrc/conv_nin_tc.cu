@@ -130,7 +130,7 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
-  int mTiles, accStride, K, generic, rulesDouble, rawEntries, nStages64, atmem, aBase; const int *rowsPtr; const int *poolRules; int *choices; int poolCells; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
+  int mTiles, accStride, K, generic, epi2, rulesDouble, rawEntries, nStages64, atmem, aBase; const int *rowsPtr; const int *poolRules; int *choices; int poolCells; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
@@ -164,17 +164,22 @@ constexpr int EPI_BYTES = BM * EPI_LD * 4;        // 18 KB
 // POOL: a non-overlapping max-pooling layer behind this layer is applied here (MaxPoolingLayer.cu:9-35).  The
 // tile's 128 rows are 128/cells pooling windows x cells; tile row i is the layer-output row poolRules[row0 + i]
 // (negative: skipped, as maxPool skips it).  Only the pooled rows and their choices are written.
+// Two groups (four warps each) may share the work: group g takes the work items n = g, g + 2, ... of this CTA,
+// i.e. always accumulator g; each has its own staging slice, pooling-row table and named barrier.
 template <bool SPLIT, int ACT, bool POOL = false>
-__device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint32_t tmem, uint32_t accFullBar, uint32_t accEmptyBar,
-                                              int nItems, int kSplit, int rows) {
-  __shared__ int poolRow[BM]; // POOL: this tile's layer-output row per tile row
-  const int warp = threadIdx.x >> 5;
-  const int t = threadIdx.x;
+__device__ __forceinline__ void epilogue_role(const Params &P, float *epiBase, uint32_t tmem, uint32_t accFullBar, uint32_t accEmptyBar,
+                                              int nItems, int kSplit, int rows, int group = 0, int nGroups = 1) {
+  __shared__ int poolRow0[BM]; // POOL: this tile's layer-output row per tile row (the second group's table follows its staging slice)
+  int *poolRow = group ? reinterpret_cast<int *>(epiBase + 2 * (EPI_BYTES / 4)) : poolRow0;
+  float *epi = epiBase + (size_t)group * (EPI_BYTES / 4);
+  const int barId = group ? 3 : 1;
+  const int t = threadIdx.x & 127; // thread of the group; its warp reads tensor-memory lanes 32 * (warp % 4)...
+  const int warp = t >> 5;
   const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
   float *myRow = epi + (size_t)t * EPI_LD;
   const int c4 = t & 7, rsub = t >> 3; // store phase: 8 threads per row, 16 rows per pass
-  int n = 0;
-  for (int item = blockIdx.x; item < nItems; item += gridDim.x, ++n) {
+  int n = group;
+  for (int item = blockIdx.x + group * gridDim.x; item < nItems; item += nGroups * gridDim.x, n += nGroups) {
     const int tileId = SPLIT ? item / kSplit : item, split = SPLIT ? item - tileId * kSplit : 0;
     const int tileN = tileId % P.nTiles, tileM = tileId / P.nTiles;
     const int ab = n & 1;
@@ -203,7 +208,7 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint3
       for (int q = 0; q < 32; q += 4)
         if (q < width)
           *reinterpret_cast<float4 *>(myRow + q) = make_float4(__uint_as_float(a[q]), __uint_as_float(a[q + 1]), __uint_as_float(a[q + 2]), __uint_as_float(a[q + 3]));
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync %0, 128;" ::"r"(barId) : "memory");
       // coalesced: 8 threads cover one row's 128 bytes, a warp covers 4 rows per instruction
       const int col = col0 + c + c4 * 4;
       const bool colOk = c4 * 4 < width && col < P.N; // N % 4 == 0: a float4 is in or out as a whole
@@ -270,7 +275,7 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epi, uint3
           *reinterpret_cast<float4 *>(P.out + (long long)r * P.N + col) = o;
         }
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory"); // the slice is free again
+      asm volatile("bar.sync %0, 128;" ::"r"(barId) : "memory"); // the slice is free again
     }
     tc_fence_before();
     mbar_arrive(accEmptyBar + 8 * ab); // this accumulator may be overwritten
@@ -339,8 +344,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
     return split;
   };
 
+  const bool epi2 = !SPLIT && !ATMEM && P.epi2;
   if (warp < 4) {
-    epilogue_role<SPLIT, ACT, POOL>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows);
+    epilogue_role<SPLIT, ACT, POOL>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows, 0, epi2 ? 2 : 1);
   } else if (warp < 8) {
     // ------------------------------------------------------------ gather: asynchronous 16-byte copies
     const int t = threadIdx.x - 128, chunk = t & 7, rbase = t >> 3;
@@ -410,6 +416,55 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
         const int nr = BM * P.fs;
         for (int e = t; e < nr; e += 128) rulesS[e] = __ldg(P.rules + min((long long)row0 * P.fs + e, (long long)rows * P.fs - 1));
         asm volatile("bar.sync 2, 128;" ::: "memory");
+      }
+      if (epi2) {
+        // Few input channels, one slab (a first layer): lane = tile row.  A lane reads its row's fs rules, then
+        // the fs x nIn words they name (every load unconditional: a missing rule reads a -1 word, a missing
+        // row the zero row), computes lo = x - tf32(x) and stores both images of its row as 16-byte chunks
+        // (rows r..r+7 fall on eight different chunk columns of the swizzled tile: no bank conflict).
+        // About 250 instructions per warp and tile where the lane-per-word form and the split warps need 700.
+        auto gather_rows = [&](auto ninC) {
+          constexpr int NIN = decltype(ninC)::value, FMAX = SLAB / NIN;
+          const int st = ring.idx;
+          int from;
+          if (POOL) from = fromT[t];
+          else from = row0 + t < rows ? row0 + t : -1;
+          int rule[FMAX];
+#pragma unroll
+          for (int f = 0; f < FMAX; ++f)
+            rule[f] = __ldg(f < P.fs && from >= 0 ? P.rules + (long long)from * P.fs + f : &g_no_row);
+          float v[SLAB];
+#pragma unroll
+          for (int k = 0; k < SLAB; ++k) v[k] = 0.f;
+#pragma unroll
+          for (int f = 0; f < FMAX; ++f)
+#pragma unroll
+            for (int c = 0; c < NIN; ++c)
+              v[f * NIN + c] = __ldg(rule[f] >= 0 ? P.in + (long long)rule[f] * NIN + c : g_zero_row);
+          mbar_wait(emptyBar + 8 * st, ring.phase ^ 1, 1);
+          unsigned char *rowp = smem + (size_t)st * stageBytes + (t >> 3) * 1024 + (t & 7) * ROW_BYTES;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            float4 hi = make_float4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]), lo;
+            lo.x = hi.x - __uint_as_float(__float_as_uint(hi.x) & 0xffffe000u);
+            lo.y = hi.y - __uint_as_float(__float_as_uint(hi.y) & 0xffffe000u);
+            lo.z = hi.z - __uint_as_float(__float_as_uint(hi.z) & 0xffffe000u);
+            lo.w = hi.w - __uint_as_float(__float_as_uint(hi.w) & 0xffffe000u);
+            const int off = (ch ^ (t & 7)) << 4;
+            *reinterpret_cast<float4 *>(rowp + off) = hi;
+            *reinterpret_cast<float4 *>(rowp + A_HALF + off) = lo;
+          }
+          fence_async_smem(); // the tensor core reads the tile through the asynchronous proxy
+          mbar_arrive(fullBar + 8 * st);
+          ring.next();
+        };
+        switch (P.nIn) { // (one slab: nLoc == 1)
+        case 1: gather_rows(std::integral_constant<int, 1>()); break;
+        case 2: gather_rows(std::integral_constant<int, 2>()); break;
+        case 3: gather_rows(std::integral_constant<int, 3>()); break;
+        default: gather_rows(std::integral_constant<int, 4>()); break;
+        }
+        continue;
       }
       if (P.generic) {
         // nIn is not a multiple of 32 (e.g. 3 input channels): a slab spans several filter cells, so
@@ -487,6 +542,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
         cp_async_arrive(rawBar + 8 * st);
       }
     }
+  } else if (warp < 12 && epi2) {
+    // the gather writes both images itself: these warps drain every second accumulator instead
+    if (!SPLIT && !ATMEM) epilogue_role<false, ACT, POOL>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows, 1, 2);
   } else if (warp < 12) {
     // ------------------------------------------------------------ split: lo = x - tf32(x)
     const int t = threadIdx.x - 256;
@@ -991,11 +1049,15 @@ int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) 
 
 struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, rulesDouble, accStride, atmem, aBase; size_t smemBytes; };
 
+// Word-wise gathers of at most this many input channels use the row-per-lane form with two epilogue groups
+constexpr int ROWWISE_MAX_NIN = 4;
+
 // oneItem: no CTA gets more than one work item, so the second accumulator is never used and its columns can
 // hold the A slots: the tensor-memory A path then reaches BN = 256.
-bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool oneItem = false, bool pool = false) {
+bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool oneItem = false, bool pool = false, bool epi2 = false) {
   if (K < 1 || N < 16) return false;
-  t->rulesBytes = (haveRules && fs <= 32) ? BM * fs * 4 : 0;
+  const int epiBytes = epi2 ? 2 * EPI_BYTES + BM * 4 : EPI_BYTES;
+  t->rulesBytes = (haveRules && fs <= 32 && !(epi2 && !pool)) ? BM * fs * 4 : 0; // (the row-per-lane gather reads rules from global memory)
   if (pool) { // fused max-pooling: staged rules are mandatory, two buffers, each followed by the tile's 128 row ids
     if (!t->rulesBytes) return false;
     t->rulesBytes += BM * 4;
@@ -1010,7 +1072,7 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool oneItem =
   t->atmem = (t->nSlabs >= 4 && t->aBase + 128 <= 512) ? 2 : 0;
   const int stageBytes = (t->atmem ? 1 : 2) * A_HALF + 2 * t->BN * ROW_BYTES;
   auto stagesWith = [&](int ruleBufs) {
-    const int n = (int)((226 * 1024 - 1024 - ruleBufs * t->rulesBytes - EPI_BYTES) / stageBytes);
+    const int n = (int)((226 * 1024 - 1024 - ruleBufs * t->rulesBytes - epiBytes) / stageBytes);
     return n > MAX_STAGES ? MAX_STAGES : n;
   };
   const int stages = stagesWith(pool ? 2 : 1);
@@ -1020,7 +1082,7 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool oneItem =
   int cols = 32;
   while (cols < (t->atmem ? t->aBase + 128 : 2 * t->accStride)) cols *= 2; // the accumulators [+ the A slots], at most 512 columns
   t->tmemCols = cols;
-  t->smemBytes = (size_t)stages * stageBytes + 1024 + (size_t)(1 + t->rulesDouble) * t->rulesBytes + EPI_BYTES;
+  t->smemBytes = (size_t)stages * stageBytes + 1024 + (size_t)(1 + t->rulesDouble) * t->rulesBytes + epiBytes;
   return true;
 }
 
@@ -1144,7 +1206,12 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
         (mTiles * t.nTiles + sms - 1) / sms > (plainTiles + sms - 1) / sms)
       return fail(SCN_ERR_UNSUPPORTED, "fused max-pooling would not pay for this shape");
   }
-  if (!passes && !t.atmem && mTiles * t.nTiles * kSplit <= sm_count()) make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, true, pool);
+  const bool oneItem = !passes && !t.atmem && mTiles * t.nTiles * kSplit <= sm_count();
+  // few input channels and one slab (a first layer): row-per-lane gather that also writes the lo image, and the
+  // four warps that would split become a second epilogue group
+  const bool epi2 = !passes && d_rules && nIn % SLAB != 0 && nIn <= ROWWISE_MAX_NIN && t.nSlabs == 1 && kSplit == 1 && !t.atmem;
+  if (oneItem || epi2) make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, oneItem, pool, epi2);
+  P.epi2 = epi2 ? 1 : 0;
   P.rawEntries = rawEntries; P.nStages64 = nStages64; P.atmem = passes ? 0 : t.atmem; P.aBase = t.aBase;
   if (d_rows && (passes || kSplit > 1)) return fail(SCN_ERR_UNSUPPORTED, "a device-side row count needs the 3xTF32 kernel without K split");
   P.rowsPtr = d_rows; P.poolRules = d_pool_rules; P.poolCells = pool_cells; P.choices = d_choices;
