@@ -675,9 +675,11 @@ __device__ __forceinline__ unsigned long long chain_ns() {
 template <int DIM>
 __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   extern __shared__ __align__(16) unsigned char chain_smem[];
-  __shared__ Regions R;
   __shared__ int sTicket, sTotal, sBase, sSitesBase;
-  uint2 *dir = reinterpret_cast<uint2 *>(chain_smem);
+  // every layer's descriptor is fetched once, at the start (a fetch per layer would put a round trip to global
+  // memory in front of each of the layers, most of which are a few microseconds long)
+  ChainLayer *sLayers = reinterpret_cast<ChainLayer *>(chain_smem);
+  uint2 *dir = reinterpret_cast<uint2 *>(chain_smem + (((size_t)P.nLayers * sizeof(ChainLayer) + 15) & ~(size_t)15));
   int *keysA = reinterpret_cast<int *>(dir + P.wMax);
   int *keysB = keysA + P.rowsMax;
   int *sorted = keysB + P.rowsMax;
@@ -686,7 +688,8 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   const int tid = threadIdx.x;
   const int NT = blockDim.x;
 
-  if (tid == 0) sTicket = atomicAdd(P.ticket, 1);
+  if (tid == 0) sTicket = atomicAdd(P.ticket, 1) + 1; // the ticket starts at -1
+  for (int i = tid; i < P.nLayers * (int)(sizeof(ChainLayer) / 4); i += NT) reinterpret_cast<int *>(sLayers)[i] = reinterpret_cast<const int *>(P.layers)[i];
   __syncthreads();
   const int b = sTicket;
   if (b >= P.batch) return;
@@ -702,10 +705,10 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   for (int j = tid; j < nRows; j += NT) inKeys[j] = P.inKeys[inBase + j];
 
   for (int l = 0; l < P.nLayers; ++l) {
-    const ChainLayer &L = P.layers[l];
+    const ChainLayer &L = sLayers[l];
+    const Regions &R = L.R;
     __syncthreads();
-    for (int i = tid; i < (int)(sizeof(Regions) / 4); i += NT) reinterpret_cast<int *>(&R)[i] = reinterpret_cast<const int *>(&L.R)[i];
-    for (int w = tid; w < P.wMax; w += NT) dir[w] = make_uint2(0u, 0u);
+    for (int w = tid; w < R.W; w += NT) dir[w] = make_uint2(0u, 0u);
     __syncthreads();
     // 1. occupancy bits
     for (int j = tid; j < nRows; j += NT) {
@@ -772,8 +775,7 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
     const int needBg = sitesOut < R.fullSize;
     const int rowsOut = sitesOut + needBg;
     // 6. publish this sample's count, sum the earlier samples' counts
-    if (tid == 0) {
-      __threadfence();
+    if (tid == 0) { // (no fence: the other samples read nothing of this one but the count itself)
       atomicExch(P.counts + l * P.batch + b, rowsOut | (needBg << 30));
       atomicMax(L.result + 3, sitesOut);
       sBase = 0; sSitesBase = 0;
@@ -881,7 +883,7 @@ ChainPlan plan_chain(const Regions *Rs, int n, int rowsIn, int rowsHint) {
     flagBytes = (size_t)p.rowsMax * p.tMax;
   }
   p.flagBytes = flagBytes;
-  p.smemBytes = (size_t)p.wMax * 8 + (size_t)p.rowsMax * 12 + ((size_t)p.rowsMax + 1) * 4 + flagBytes + 64;
+  p.smemBytes = (size_t)n * sizeof(ChainLayer) + 16 + (size_t)p.wMax * 8 + (size_t)p.rowsMax * 12 + ((size_t)p.rowsMax + 1) * 4 + flagBytes + 64;
   p.ok = p.smemBytes <= 200 * 1024;
   return p;
 }
@@ -1148,9 +1150,13 @@ extern "C" int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_laye
   int *ticket = counts + (size_t)n_layers * batch;
   // the descriptors travel through a pinned-free path: a small synchronous-to-stream copy from pageable memory
   SCN_CUDA_TRY(cudaMemcpyAsync(dLayers, h.data(), sizeof(ChainLayer) * n_layers, cudaMemcpyHostToDevice, s));
-  SCN_CUDA_TRY(cudaMemsetAsync(counts, 0xff, sizeof(int) * (size_t)n_layers * batch, s));
-  SCN_CUDA_TRY(cudaMemsetAsync(ticket, 0, sizeof(int), s));
-  for (int l = 0; l < n_layers; ++l) SCN_CUDA_TRY(cudaMemsetAsync(layers[l].d_result, 0, 4 * sizeof(int), s));
+  // few stream operations in front of the kernel (each costs a couple of microseconds of an idle GPU): counts and
+  // ticket are set by one fill (the ticket counts up from -1), the result records by one when they are contiguous
+  SCN_CUDA_TRY(cudaMemsetAsync(counts, 0xff, sizeof(int) * ((size_t)n_layers * batch + 1), s));
+  bool contiguous = true;
+  for (int l = 1; l < n_layers; ++l) contiguous = contiguous && layers[l].d_result == layers[0].d_result + 4 * l;
+  if (contiguous) SCN_CUDA_TRY(cudaMemsetAsync(layers[0].d_result, 0, 4 * sizeof(int) * (size_t)n_layers, s));
+  else for (int l = 0; l < n_layers; ++l) SCN_CUDA_TRY(cudaMemsetAsync(layers[l].d_result, 0, 4 * sizeof(int), s));
   static bool attrSet[64] = {false};
   int dev = 0;
   SCN_CUDA_TRY(cudaGetDevice(&dev));
