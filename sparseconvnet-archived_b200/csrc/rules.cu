@@ -675,11 +675,9 @@ __device__ __forceinline__ unsigned long long chain_ns() {
 template <int DIM>
 __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   extern __shared__ __align__(16) unsigned char chain_smem[];
+  __shared__ Regions R;
   __shared__ int sTicket, sTotal, sBase, sSitesBase;
-  // every layer's descriptor is fetched once, at the start (a fetch per layer would put a round trip to global
-  // memory in front of each of the layers, most of which are a few microseconds long)
-  ChainLayer *sLayers = reinterpret_cast<ChainLayer *>(chain_smem);
-  uint2 *dir = reinterpret_cast<uint2 *>(chain_smem + (((size_t)P.nLayers * sizeof(ChainLayer) + 15) & ~(size_t)15));
+  uint2 *dir = reinterpret_cast<uint2 *>(chain_smem);
   int *keysA = reinterpret_cast<int *>(dir + P.wMax);
   int *keysB = keysA + P.rowsMax;
   int *sorted = keysB + P.rowsMax;
@@ -689,7 +687,6 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   const int NT = blockDim.x;
 
   if (tid == 0) sTicket = atomicAdd(P.ticket, 1) + 1; // the ticket starts at -1
-  for (int i = tid; i < P.nLayers * (int)(sizeof(ChainLayer) / 4); i += NT) reinterpret_cast<int *>(sLayers)[i] = reinterpret_cast<const int *>(P.layers)[i];
   __syncthreads();
   const int b = sTicket;
   if (b >= P.batch) return;
@@ -705,10 +702,10 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   for (int j = tid; j < nRows; j += NT) inKeys[j] = P.inKeys[inBase + j];
 
   for (int l = 0; l < P.nLayers; ++l) {
-    const ChainLayer &L = sLayers[l];
-    const Regions &R = L.R;
+    const ChainLayer &L = P.layers[l];
     __syncthreads();
-    for (int w = tid; w < R.W; w += NT) dir[w] = make_uint2(0u, 0u);
+    for (int i = tid; i < (int)(sizeof(Regions) / 4); i += NT) reinterpret_cast<int *>(&R)[i] = reinterpret_cast<const int *>(&L.R)[i];
+    for (int w = tid; w < P.wMax; w += NT) dir[w] = make_uint2(0u, 0u);
     __syncthreads();
     // 1. occupancy bits
     for (int j = tid; j < nRows; j += NT) {
@@ -883,7 +880,7 @@ ChainPlan plan_chain(const Regions *Rs, int n, int rowsIn, int rowsHint) {
     flagBytes = (size_t)p.rowsMax * p.tMax;
   }
   p.flagBytes = flagBytes;
-  p.smemBytes = (size_t)n * sizeof(ChainLayer) + 16 + (size_t)p.wMax * 8 + (size_t)p.rowsMax * 12 + ((size_t)p.rowsMax + 1) * 4 + flagBytes + 64;
+  p.smemBytes = (size_t)p.wMax * 8 + (size_t)p.rowsMax * 12 + ((size_t)p.rowsMax + 1) * 4 + flagBytes + 64;
   p.ok = p.smemBytes <= 200 * 1024;
   return p;
 }
