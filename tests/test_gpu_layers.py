@@ -132,6 +132,8 @@ CONV_TC = [
     (1000, 1357, 9, 3, 96, "VLEAKYRELU", 0.9),    # the benchmark's first convolution, K = 27
     (200, 300, 4, 24, 64, "RELU", 1.0),
     (64, 150, 27, 1, 32, "LEAKYRELU", 1.0),
+    (400, 500, 8, 4, 64, "VLEAKYRELU", 1.0),      # row-per-lane gather: four channels, K = 32 exactly
+    (300, 350, 9, 2, 32, "RELU", 0.8),            # two channels, K = 18
     (100, 100, 1, 40, 48, "PRELU", 1.0),
     (300, 200, 8, 20, 288, "VLEAKYRELU", 1.0),
 ]
@@ -271,6 +273,8 @@ def test_conv_nin_with_row_count_on_the_device(abi, oracle):
     (500, 150, 4, 96, 192, 4, "RELU"),
     (300, 90, 8, 32, 288, 8, "LEAKYRELU"),      # 2^3 windows, two column tiles
     (200, 70, 4, 64, 32, 2, "PRELU"),
+    (800, 260, 27, 1, 32, 8, "VLEAKYRELU"),     # a 3-D first layer (one channel, 3^3 filter) + 2^3 pooling: row-per-lane gather, two epilogue groups
+    (500, 200, 8, 4, 48, 2, "RELU"),
 ])
 def test_conv_nin_maxpool_fused(abi, oracle, rows_in, windows, fs, nIn, N, cells, act):
     """Gather + NiN + non-overlapping max pooling in one kernel against the oracle's three steps: pooled values
@@ -288,7 +292,7 @@ def test_conv_nin_maxpool_fused(abi, oracle, rows_in, windows, fs, nIn, N, cells
     pool = rng.permutation(rows_mid)[: windows * cells].astype(np.int32).reshape(windows, cells)
     pool[rng.random(pool.shape) < 0.15] = -1      # cells without an input
     pool[3] = -1                                   # a window with none at all
-    pool[5, 1:] = pool[5, 0]                       # the same row several times: the first wins
+    pool[5, :] = 7                                 # the same row several times: the first wins
     X = oracle.gather(feat, rules, nIn).reshape(rows_mid, K)
     mid = oracle.nin_forward(X, W, B, prelu, 0.9, actc, accum64=True)
     ref_v, ref_c = oracle.maxpool(mid.astype(np.float32), pool, cells)
