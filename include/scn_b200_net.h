@@ -73,8 +73,9 @@ int scn_net_set_precision(scn_net_t *net, int precision);
  *   h_probs[batch x nClasses], h_predictions[batch x nTop] (either may be NULL) */
 int scn_net_forward_host(scn_net_t *net, int batch, const int *h_keys, const int *h_off, const float *h_features,
                          float *h_probs, int *h_predictions);
-/* The same with inputs already resident in device memory (they are copied device-to-device
- * into the batch's interface).  d_bg[batch] is each sample's background row or -1;
+/* The same with inputs already resident in device memory: the batch's interface reads the caller's
+ * arrays in place (no copy), so they must stay unchanged until the forward has run on the stream and
+ * must not be freed before the network's next forward call.  d_bg[batch] is each sample's background row or -1;
  * maxSitesPerSample the largest site count of a sample.  Results are left on the device:
  * d_probs[batch x nClasses], d_top[batch x nTop] (either may be NULL).  Does not wait for
  * the stream beyond the rule chain's one read-back. */

@@ -26,6 +26,7 @@ void SpatiallySparseBatchInterface::reset() {
   featuresPresent.resize(0);
   featuresPresent.copyToCPU();
   nSpatialSites = 0;
+  siteKeys.dropBorrowed(); sampleOffsets.dropBorrowed(); backgroundRows.dropBorrowed(); // a device-input call's arrays
   grids.resize(0);
   rules.resize(0);
   backpropErrors = false;

@@ -85,16 +85,12 @@ void adoptDeviceInput(SparseConvNetCUDA &cnn, SpatiallySparseBatch &b, int batch
   in.maxSitesPerSample = maxSites;
   in.gridOwner = &in;
   cudaStream_t s = cnn.memStream.stream;
-  in.siteKeys.copyToGPU(); in.sampleOffsets.copyToGPU(); in.backgroundRows.copyToGPU();
-  in.siteKeys.resize(rows); in.sampleOffsets.resize(batch + 1); in.backgroundRows.resize(batch);
-  in.sub->features.copyToGPU();
-  in.sub->features.resize(rows * cnn.nInputFeatures);
-  if (rows) {
-    cudaSafeCall(cudaMemcpyAsync(in.siteKeys.dPtr(), d_keys, sizeof(int) * rows, cudaMemcpyDeviceToDevice, s));
-    cudaSafeCall(cudaMemcpyAsync(in.sub->features.dPtr(), d_features, sizeof(float) * (size_t)rows * cnn.nInputFeatures, cudaMemcpyDeviceToDevice, s));
-  }
-  cudaSafeCall(cudaMemcpyAsync(in.sampleOffsets.dPtr(), d_off, sizeof(int) * (batch + 1), cudaMemcpyDeviceToDevice, s));
-  cudaSafeCall(cudaMemcpyAsync(in.backgroundRows.dPtr(), d_bg, sizeof(int) * batch, cudaMemcpyDeviceToDevice, s));
+  // no copies: the interface reads the caller's arrays (which must stay as they are until the forward has run)
+  (void)s;
+  in.siteKeys.borrowDevice(const_cast<int *>(d_keys), rows);
+  in.sampleOffsets.borrowDevice(const_cast<int *>(d_off), batch + 1);
+  in.backgroundRows.borrowDevice(const_cast<int *>(d_bg), batch);
+  in.sub->features.borrowDevice(const_cast<float *>(d_features), rows * cnn.nInputFeatures);
 }
 } // namespace
 

@@ -11,16 +11,28 @@ std::mt19937 &fillRng() { // deterministic fills (the reference seeds from the c
 }
 } // namespace
 
-template <typename t> vectorCUDA<t>::vectorCUDA(bool onGPU, unsigned int dsize) : d_vec(nullptr), dsize(dsize), dAllocated(0), onGPU(onGPU) {
+template <typename t> vectorCUDA<t>::vectorCUDA(bool onGPU, unsigned int dsize)
+    : d_vec(nullptr), dsize(dsize), dAllocated(0), ownVec(nullptr), ownAllocated(0), borrowed(false), onGPU(onGPU) {
   if (onGPU && dsize > 0) { dAllocated = dsize; cudaSafeCall(cudaMalloc((void **)&d_vec, sizeof(t) * dAllocated)); }
   else if (!onGPU) vec.resize(dsize);
 }
-template <typename t> vectorCUDA<t>::~vectorCUDA() { if (dAllocated > 0) cudaFree(d_vec); }
+template <typename t> vectorCUDA<t>::~vectorCUDA() { giveBack(); if (dAllocated > 0) cudaFree(d_vec); }
+template <typename t> void vectorCUDA<t>::giveBack() {
+  if (!borrowed) return;
+  d_vec = ownVec; dAllocated = ownAllocated; ownVec = nullptr; ownAllocated = 0; borrowed = false; dsize = 0;
+}
+template <typename t> void vectorCUDA<t>::borrowDevice(t *p, unsigned int n) {
+  if (!onGPU) { vec.clear(); onGPU = true; }
+  if (!borrowed) { ownVec = d_vec; ownAllocated = dAllocated; borrowed = true; }
+  d_vec = p; dsize = n; dAllocated = 0; // (nothing here may be freed)
+}
 template <typename t> vectorCUDA<t>::vectorCUDA(vectorCUDA &&o) noexcept
-    : d_vec(o.d_vec), dsize(o.dsize), dAllocated(o.dAllocated), vec(std::move(o.vec)), onGPU(o.onGPU) {
-  o.d_vec = nullptr; o.dAllocated = 0; o.dsize = 0;
+    : d_vec(o.d_vec), dsize(o.dsize), dAllocated(o.dAllocated), vec(std::move(o.vec)), ownVec(o.ownVec), ownAllocated(o.ownAllocated),
+      borrowed(o.borrowed), onGPU(o.onGPU) {
+  o.d_vec = nullptr; o.dAllocated = 0; o.dsize = 0; o.ownVec = nullptr; o.ownAllocated = 0; o.borrowed = false;
 }
 template <typename t> void vectorCUDA<t>::reserveDevice(size_t n) {
+  giveBack();
   if (n > dAllocated) {
     if (dAllocated > 0) cudaSafeCall(cudaFree(d_vec));
     d_vec = nullptr; dAllocated = 0;
@@ -33,6 +45,7 @@ template <typename t> void vectorCUDA<t>::copyToCPU() {
   onGPU = false;
   vec.resize(dsize);
   if (dsize > 0) cudaSafeCall(cudaMemcpy(vec.data(), d_vec, sizeof(t) * dsize, cudaMemcpyDeviceToHost));
+  giveBack(); // a later upload goes to this vector's own memory
 }
 template <typename t> void vectorCUDA<t>::copyToGPU() {
   if (onGPU) return;
@@ -70,12 +83,13 @@ template <typename t> void vectorCUDA<t>::copyToCPUAsync(cudaMemStream &ms) {
     cudaSafeCall(cudaStreamSynchronize(ms.stream));
     std::memcpy(vec.data(), stage, sizeof(t) * dsize);
   }
+  giveBack();
 }
 template <typename t> t *&vectorCUDA<t>::dPtr() { copyToGPU(); return d_vec; }
 template <typename t> std::vector<t> &vectorCUDA<t>::hVector() { copyToCPU(); return vec; }
 template <typename t> unsigned int vectorCUDA<t>::size() { return onGPU ? dsize : (unsigned int)vec.size(); }
 template <typename t> void vectorCUDA<t>::resize(int n) {
-  if (onGPU) { dsize = n; reserveDevice(n); }
+  if (onGPU) { reserveDevice(n); dsize = n; }
   else vec.resize(n);
 }
 template <typename t> float vectorCUDA<t>::meanAbs() {

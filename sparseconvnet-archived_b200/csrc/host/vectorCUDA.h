@@ -12,6 +12,10 @@ private:
   unsigned int dsize; // size while on the device
   size_t dAllocated;  // elements allocated on the device (>= dsize)
   std::vector<t> vec;
+  t *ownVec;          // while borrowing: this vector's own allocation, kept for later
+  size_t ownAllocated;
+  bool borrowed;
+  void giveBack();
 
 public:
   vectorCUDA(bool onGPU = true, unsigned int dsize = 0);
@@ -37,6 +41,10 @@ public:
   void setNormal(float mean = 0, float sd = 1);
   void resize(int n);
   void reserveDevice(size_t n); // grow the device allocation without changing size()
+  // Stand for n elements of device memory that the caller owns (no copy; not in the reference).  The vector
+  // reads them until its next resize(), host access or borrowDevice(); it never writes or frees them.
+  void borrowDevice(t *p, unsigned int n);
+  void dropBorrowed() { giveBack(); } // forget the caller's memory (size becomes 0); no-op otherwise
   void printSubset(const char *name, int nCol, int maxPrint = 10);
   void check(const char *file = 0, int linenumber = 0);
   void summary(const char *file = 0, int linenumber = 0);
