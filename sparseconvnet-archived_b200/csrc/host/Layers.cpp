@@ -603,9 +603,13 @@ void SoftmaxClassifier(SpatiallySparseBatchInterface &input, SpatiallySparseBatc
   cudaSafeCall(cudaStreamSynchronize(memStream.stream));
   const float *probs = (const float *)stage;
   const int *pred = (const int *)(stage + pb);
-  for (int i = 0; i < n; ++i) {
-    batch.probabilities.emplace_back(probs + (size_t)i * C, probs + (size_t)(i + 1) * C);
-    batch.predictions.emplace_back(pred + (size_t)i * nTop, pred + (size_t)(i + 1) * nTop);
+  for (int i = 0; i < n; ++i) { // refill the vectors that reset() set aside, where there are any
+    if (!batch.spareProbabilities.empty()) { batch.probabilities.emplace_back(std::move(batch.spareProbabilities.back())); batch.spareProbabilities.pop_back(); }
+    else batch.probabilities.emplace_back();
+    batch.probabilities.back().assign(probs + (size_t)i * C, probs + (size_t)(i + 1) * C);
+    if (!batch.sparePredictions.empty()) { batch.predictions.emplace_back(std::move(batch.sparePredictions.back())); batch.sparePredictions.pop_back(); }
+    else batch.predictions.emplace_back();
+    batch.predictions.back().assign(pred + (size_t)i * nTop, pred + (size_t)(i + 1) * nTop);
   }
   if (batch.type != UNLABELEDBATCH && batch.labels.size() == (unsigned)n) {
     std::vector<int> &labels = batch.labels.hVector();

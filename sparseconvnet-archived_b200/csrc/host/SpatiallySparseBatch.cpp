@@ -11,6 +11,8 @@ void SpatiallySparseBatch::reset() {
   for (auto &i : interfaces) i.reset();
   interfaces[0].sub->reset();
   labels.resize(0);
+  for (auto &v : predictions) sparePredictions.emplace_back(std::move(v));
+  for (auto &v : probabilities) spareProbabilities.emplace_back(std::move(v));
   predictions.clear();
   probabilities.clear();
   negativeLogLikelihood = 0;

@@ -16,6 +16,10 @@ public:
   vectorCUDA<int> labels;
   std::vector<std::vector<int>> predictions;
   std::vector<std::vector<float>> probabilities;
+  // the per-sample vectors of the previous batch, kept by reset() so that the classifier refills them
+  // instead of allocating two vectors per sample for every batch
+  std::vector<std::vector<int>> sparePredictions;
+  std::vector<std::vector<float>> spareProbabilities;
   float negativeLogLikelihood;
   int mistakes;
   void reset();
