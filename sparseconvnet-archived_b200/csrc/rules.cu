@@ -243,8 +243,40 @@ template <int DIM> __device__ __forceinline__ bool touched_output_f(const Region
   if (R.lattice == SCN_LATTICE_TRIANGULAR && sum >= R.nOut) return false;
   return ok;
 }
+// Any active cell among the keys k0 .. k0 + n - 1 (1 <= n <= 32): they are neighbouring bits of the bitmap.
+__device__ __forceinline__ bool range_any(const uint2 *d, int k0, int n) {
+  const int w = k0 >> 5, sh = k0 & 31;
+  unsigned bits = d[w].x >> sh;
+  if (sh + n > 32) bits |= d[w + 1].x << (32 - sh);
+  return (bits & (n == 32 ? 0xffffffffu : (1u << n) - 1u)) != 0u;
+}
 template <int DIM> __device__ bool creates_f(const Regions &R, const uint2 *d, const int *i, const int *j) {
   if (R.minActive == -1) return true;
+  if (R.minActive <= 1 && R.size <= 32) {
+    // Site i creates output j iff no cell of j's field with a smaller key is active.  Along the last axis the
+    // field's cells are neighbouring keys, so each line of the field in front of i is one masked look at the
+    // bitmap (a 3 x 3 field: at most 3 looks instead of 8 cell probes).
+    int co[DIM > 1 ? DIM - 1 : 1];
+#pragma unroll
+    for (int a = 0; a < DIM - 1; ++a) co[a] = 0;
+    const int x0 = j[DIM - 1] * R.stride, selfIn = i[DIM - 1] - x0;
+    for (int line = 0; line < R.cube; ++line) {
+      int key0 = 0;
+      bool same = true;
+#pragma unroll
+      for (int a = 0; a < DIM - 1; ++a) {
+        const int ia = j[a] * R.stride + co[a];
+        key0 = key0 * R.nIn + ia;
+        same = same && ia == i[a];
+      }
+      key0 = key0 * R.nIn + x0;
+      if (same) return selfIn == 0 || !range_any(d, key0, selfIn);
+      if (range_any(d, key0, R.size)) return false;
+#pragma unroll
+      for (int a = DIM - 2; a >= 0; --a) { if (++co[a] < R.size) break; co[a] = 0; }
+    }
+    return false;
+  }
   int cc[DIM], ii[DIM];
 #pragma unroll
   for (int a = 0; a < DIM; ++a) cc[a] = 0;
@@ -682,7 +714,8 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   int *keysB = keysA + P.rowsMax;
   int *sorted = keysB + P.rowsMax;
   int *cnt = sorted + P.rowsMax; // rowsMax + 1
-  unsigned char *flags = reinterpret_cast<unsigned char *>(cnt + P.rowsMax + 1);
+  int *pairs = cnt + P.rowsMax + 1; // rowsMax: which (site, output) pair made each output row
+  unsigned char *flags = reinterpret_cast<unsigned char *>(pairs + P.rowsMax);
   const int tid = threadIdx.x;
   const int NT = blockDim.x;
 
@@ -779,17 +812,24 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
     }
     // 7a. output keys into the shared copy (the next layer's input): needs no other sample, so it runs
     // while the published count travels and the earlier samples' counts arrive
+    // First the (site, output) pair behind every output row (a cheap pass over the flags), then one thread
+    // per output row: the coordinate arithmetic runs once per output instead of once per warp and flag.
     if (rowsOut <= P.rowsMax) {
-      for (int p = tid; p < nSites * R.T; p += NT) {
-        if (!flags[p]) continue;
+      for (int slot = tid; slot < nSites; slot += NT) {
+        int r = cnt[slot];
+        for (int t = 0; t < R.T; ++t)
+          if (flags[slot * R.T + t]) pairs[r++] = slot * R.T + t;
+      }
+    }
+    __syncthreads();
+    if (rowsOut <= P.rowsMax) {
+      for (int r = tid; r < sitesOut; r += NT) {
         int t;
-        const int slot = fdiv(p, R.T, R.rT, &t);
-        int rank = 0;
-        for (int q = 0; q < t; ++q) rank += flags[slot * R.T + q];
+        const int slot = fdiv(pairs[r], R.T, R.rT, &t);
         int i[DIM], j[DIM];
         decode_f<DIM>(inKeys[sorted[slot]], R.nIn, R.rNIn, i);
         touched_output_f<DIM>(R, i, t, j);
-        outKeysS[cnt[slot] + rank] = encode_f<DIM>(j, R.nOut);
+        outKeysS[r] = encode_f<DIM>(j, R.nOut);
       }
       if (needBg && tid == 0) outKeysS[sitesOut] = -1;
     }
@@ -831,22 +871,31 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
     // 7b. the interface's copy of the output keys (coalesced)
     for (int r = tid; r < rowsOut; r += NT) L.outKeys[base + r] = outKeysS[r];
     // 8. rule cells, coalesced over this sample's block of rows
-    for (int q = tid; q < rowsOut * R.sd; q += NT) {
-      int col;
-      const int r = fdiv(q, R.sd, R.rSd, &col);
+    // (a thread per output row: its coordinates are decoded once and the field's cells are walked with
+    // counters; a lane's sd words are neighbours in memory, a warp's rows one contiguous block)
+    for (int r = tid; r < rowsOut; r += NT) {
       const int key = outKeysS[r];
-      int v = inBgGlobal;
-      if (key >= 0) {
-        int j[DIM], cc[DIM], ii[DIM];
-        decode_f<DIM>(key, R.nOut, R.rNOut, j);
-        decode_f<DIM>(R.cellOfCol[col], R.size, R.rSize, cc);
-#pragma unroll
-        for (int a = 0; a < DIM; ++a) ii[a] = j[a] * R.stride + cc[a];
-        const int ck = encode_f<DIM>(ii, R.nIn);
-        const uint2 e = dir[ck >> 5];
-        if ((e.x >> (ck & 31)) & 1u) v = inBase + sorted[e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
+      int *out = L.rules + ((long long)base + r) * R.sd;
+      if (key < 0) {
+        for (int col = 0; col < R.sd; ++col) out[col] = inBgGlobal;
+        continue;
       }
-      L.rules[(long long)base * R.sd + q] = v;
+      int j[DIM], cc[DIM];
+      decode_f<DIM>(key, R.nOut, R.rNOut, j);
+#pragma unroll
+      for (int a = 0; a < DIM; ++a) { j[a] *= R.stride; cc[a] = 0; }
+      for (int cell = 0; cell < R.cube; ++cell) {
+        const int col = R.ord[cell];
+        if (col >= 0) {
+          int ck = j[0] + cc[0];
+#pragma unroll
+          for (int a = 1; a < DIM; ++a) ck = ck * R.nIn + j[a] + cc[a];
+          const uint2 e = dir[ck >> 5];
+          out[col] = ((e.x >> (ck & 31)) & 1u) ? inBase + sorted[e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))] : inBgGlobal;
+        }
+#pragma unroll
+        for (int a = DIM - 1; a >= 0; --a) { if (++cc[a] < R.size) break; cc[a] = 0; }
+      }
     }
     // the output is the next layer's input
     int *tmp = inKeys; inKeys = outKeysS; outKeysS = tmp;
@@ -880,7 +929,7 @@ ChainPlan plan_chain(const Regions *Rs, int n, int rowsIn, int rowsHint) {
     flagBytes = (size_t)p.rowsMax * p.tMax;
   }
   p.flagBytes = flagBytes;
-  p.smemBytes = (size_t)p.wMax * 8 + (size_t)p.rowsMax * 12 + ((size_t)p.rowsMax + 1) * 4 + flagBytes + 64;
+  p.smemBytes = (size_t)p.wMax * 8 + (size_t)p.rowsMax * 16 + ((size_t)p.rowsMax + 1) * 4 + flagBytes + 64;
   p.ok = p.smemBytes <= 200 * 1024;
   return p;
 }
