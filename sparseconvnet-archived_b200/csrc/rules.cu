@@ -871,31 +871,22 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
     // 7b. the interface's copy of the output keys (coalesced)
     for (int r = tid; r < rowsOut; r += NT) L.outKeys[base + r] = outKeysS[r];
     // 8. rule cells, coalesced over this sample's block of rows
-    // (a thread per output row: its coordinates are decoded once and the field's cells are walked with
-    // counters; a lane's sd words are neighbours in memory, a warp's rows one contiguous block)
-    for (int r = tid; r < rowsOut; r += NT) {
+    for (int q = tid; q < rowsOut * R.sd; q += NT) {
+      int col;
+      const int r = fdiv(q, R.sd, R.rSd, &col);
       const int key = outKeysS[r];
-      int *out = L.rules + ((long long)base + r) * R.sd;
-      if (key < 0) {
-        for (int col = 0; col < R.sd; ++col) out[col] = inBgGlobal;
-        continue;
+      int v = inBgGlobal;
+      if (key >= 0) {
+        int j[DIM], cc[DIM], ii[DIM];
+        decode_f<DIM>(key, R.nOut, R.rNOut, j);
+        decode_f<DIM>(R.cellOfCol[col], R.size, R.rSize, cc);
+#pragma unroll
+        for (int a = 0; a < DIM; ++a) ii[a] = j[a] * R.stride + cc[a];
+        const int ck = encode_f<DIM>(ii, R.nIn);
+        const uint2 e = dir[ck >> 5];
+        if ((e.x >> (ck & 31)) & 1u) v = inBase + sorted[e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
       }
-      int j[DIM], cc[DIM];
-      decode_f<DIM>(key, R.nOut, R.rNOut, j);
-#pragma unroll
-      for (int a = 0; a < DIM; ++a) { j[a] *= R.stride; cc[a] = 0; }
-      for (int cell = 0; cell < R.cube; ++cell) {
-        const int col = R.ord[cell];
-        if (col >= 0) {
-          int ck = j[0] + cc[0];
-#pragma unroll
-          for (int a = 1; a < DIM; ++a) ck = ck * R.nIn + j[a] + cc[a];
-          const uint2 e = dir[ck >> 5];
-          out[col] = ((e.x >> (ck & 31)) & 1u) ? inBase + sorted[e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))] : inBgGlobal;
-        }
-#pragma unroll
-        for (int a = DIM - 1; a >= 0; --a) { if (++cc[a] < R.size) break; cc[a] = 0; }
-      }
+      L.rules[(long long)base * R.sd + q] = v;
     }
     // the output is the next layer's input
     int *tmp = inKeys; inKeys = outKeysS; outKeysS = tmp;
