@@ -708,14 +708,14 @@ template <int DIM>
 __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   extern __shared__ __align__(16) unsigned char chain_smem[];
   __shared__ Regions R;
-  __shared__ int sTicket, sTotal, sBase, sSitesBase;
+  __shared__ int sTicket, sTotal, sBase, sSitesBase, colOff[MAX_CUBE];
   uint2 *dir = reinterpret_cast<uint2 *>(chain_smem);
   int *keysA = reinterpret_cast<int *>(dir + P.wMax);
   int *keysB = keysA + P.rowsMax;
   int *sorted = keysB + P.rowsMax;
   int *cnt = sorted + P.rowsMax; // rowsMax + 1
-  int *pairs = cnt + P.rowsMax + 1; // rowsMax: which (site, output) pair made each output row
-  unsigned char *flags = reinterpret_cast<unsigned char *>(pairs + P.rowsMax);
+  int *pairs = cnt + P.rowsMax + 1; // rowsMax + 1: which (site, output) pair made each output row
+  unsigned char *flags = reinterpret_cast<unsigned char *>(pairs + P.rowsMax + 1);
   const int tid = threadIdx.x;
   const int NT = blockDim.x;
 
@@ -830,8 +830,17 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
         decode_f<DIM>(inKeys[sorted[slot]], R.nIn, R.rNIn, i);
         touched_output_f<DIM>(R, i, t, j);
         outKeysS[r] = encode_f<DIM>(j, R.nOut);
+#pragma unroll
+        for (int a = 0; a < DIM; ++a) j[a] *= R.stride;
+        pairs[r] = encode_f<DIM>(j, R.nIn); // from here on: the key of the first cell of the row's field
       }
-      if (needBg && tid == 0) outKeysS[sitesOut] = -1;
+      if (needBg && tid == 0) { outKeysS[sitesOut] = -1; pairs[sitesOut] = -1; }
+      // key offset of every rule column's cell within a field
+      for (int col = tid; col < R.sd; col += NT) {
+        int cc[DIM];
+        decode_f<DIM>(R.cellOfCol[col], R.size, R.rSize, cc);
+        colOff[col] = encode_f<DIM>(cc, R.nIn);
+      }
     }
     __syncthreads();
     {
@@ -874,15 +883,10 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
     for (int q = tid; q < rowsOut * R.sd; q += NT) {
       int col;
       const int r = fdiv(q, R.sd, R.rSd, &col);
-      const int key = outKeysS[r];
+      const int first = pairs[r]; // key of the field's first cell, -1 on the background row
       int v = inBgGlobal;
-      if (key >= 0) {
-        int j[DIM], cc[DIM], ii[DIM];
-        decode_f<DIM>(key, R.nOut, R.rNOut, j);
-        decode_f<DIM>(R.cellOfCol[col], R.size, R.rSize, cc);
-#pragma unroll
-        for (int a = 0; a < DIM; ++a) ii[a] = j[a] * R.stride + cc[a];
-        const int ck = encode_f<DIM>(ii, R.nIn);
+      if (first >= 0) {
+        const int ck = first + colOff[col];
         const uint2 e = dir[ck >> 5];
         if ((e.x >> (ck & 31)) & 1u) v = inBase + sorted[e.y + __popc(e.x & ((1u << (ck & 31)) - 1u))];
       }
@@ -920,7 +924,7 @@ ChainPlan plan_chain(const Regions *Rs, int n, int rowsIn, int rowsHint) {
     flagBytes = (size_t)p.rowsMax * p.tMax;
   }
   p.flagBytes = flagBytes;
-  p.smemBytes = (size_t)p.wMax * 8 + (size_t)p.rowsMax * 16 + ((size_t)p.rowsMax + 1) * 4 + flagBytes + 64;
+  p.smemBytes = (size_t)p.wMax * 8 + (size_t)p.rowsMax * 12 + ((size_t)p.rowsMax + 1) * 8 + flagBytes + 64;
   p.ok = p.smemBytes <= 200 * 1024;
   return p;
 }
