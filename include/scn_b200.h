@@ -227,12 +227,16 @@ int scn_conv_nin_forward_dyn(const float *d_in, const int *d_rules, int rows_out
  * reaches memory.  d_rules are the convolution's rules (fs cells per row).  d_rows_pool: NULL, or the
  * device-side row count (then rows_pool_bound is an upper bound).  rows_unpooled: rows of the learnt
  * layer's own output if known, else 0; with it the call also answers SCN_ERR_UNSUPPORTED where fusing would
- * cost an extra wave of tiles (windows repeat background rows) or where the layer alone would split K.
+ * cost an extra wave of tiles (windows repeat background rows) or where the layer alone would split K
+ * and no workspace is given.  d_workspace (may be NULL): scn_conv_nin_workspace_bytes(rows_unpooled, ...)
+ * bytes; with it (and rows_unpooled, and no d_rows_pool) a layer that splits K keeps doing so and the pooling
+ * happens in the kernel that adds the partial sums.
  * 3xTF32 tensor-core kernel only; SCN_ERR_UNSUPPORTED for shapes it does not take. */
 int scn_conv_nin_maxpool_forward(const float *d_in, const int *d_rules, int fs, int nIn, const void *d_W_packed,
                                  const float *d_B, const float *d_prelu, int N, float p, int activation,
                                  const int *d_pool_rules, int pool_cells, int rows_pool_bound, const int *d_rows_pool,
-                                 int rows_unpooled, float *d_out, int *d_choices, scn_stream_t stream);
+                                 int rows_unpooled, float *d_out, int *d_choices, void *d_workspace, size_t workspace_bytes,
+                                 scn_stream_t stream);
 
 /* One-time repack of W[K x N] (K = fs*nIn) for a tensor-core precision: bytes needed, then
  * the packing kernel.  No reference counterpart (the reference hands W to cuBLAS as is). */

@@ -73,7 +73,7 @@ def lib():
         L.scn_terminal_rules_build.argtypes = [c_int, c_int, c_int, c_p, c_p, c_p, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]
         L.scn_conv_nin_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_int, c_f, c_int, c_int, c_p, c_p]
         L.scn_conv_nin_forward_dyn.argtypes = [c_p, c_p, c_int, c_p, c_int, c_int, c_p, c_p, c_p, c_int, c_f, c_int, c_p, c_p]
-        L.scn_conv_nin_maxpool_forward.argtypes = [c_p, c_p, c_int, c_int, c_p, c_p, c_p, c_int, c_f, c_int, c_p, c_int, c_int, c_p, c_int, c_p, c_p, c_p]
+        L.scn_conv_nin_maxpool_forward.argtypes = [c_p, c_p, c_int, c_int, c_p, c_p, c_p, c_int, c_f, c_int, c_p, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_sz, c_p]
         L.scn_conv_nin_forward_ws.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_int, c_f, c_int, c_int, c_p, c_p, c_sz, c_p]
         L.scn_conv_nin_workspace_bytes.restype = c_sz
         L.scn_conv_nin_workspace_bytes.argtypes = [c_int] * 5
@@ -318,16 +318,21 @@ def conv_nin_forward_dyn(feat, rules, fs, W, B, d_rows, rows_bound, prelu=None, 
     return out
 
 
-def conv_nin_maxpool_forward(feat, rules, fs, W, B, pool_rules, cells, prelu=None, p=1.0, act=NOSIGMOID, packed=None, d_rows=None):
-    """scn_conv_nin_maxpool_forward -> (pooled [rows_pool x N], choices)."""
+def conv_nin_maxpool_forward(feat, rules, fs, W, B, pool_rules, cells, prelu=None, p=1.0, act=NOSIGMOID, packed=None, d_rows=None,
+                             rows_unpooled=0, split_k=False):
+    """scn_conv_nin_maxpool_forward -> (pooled [rows_pool x N], choices).  split_k: hand over the workspace with which a
+    layer of few tiles splits K (the pooling then happens where the partial sums are added); needs rows_unpooled."""
     L = lib()
     K, N = W.shape
     rows_pool = pool_rules.numel() // cells
+    ws_bytes = L.scn_conv_nin_workspace_bytes(rows_unpooled, fs, K // fs, N, PREC_3XTF32) if (split_k and rows_unpooled) else 0
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=feat.device) if ws_bytes else None
     out = torch.zeros((rows_pool, N), dtype=torch.float32, device=feat.device)
     choices = torch.full((rows_pool, N), -7, dtype=torch.int32, device=feat.device)
     check(L.scn_conv_nin_maxpool_forward(_ptr(_f32(feat)), _ptr(_i32(rules)), fs, K // fs, _ptr(packed), _ptr(_f32(B)),
                                          None if prelu is None else _ptr(_f32(prelu)), N, p, act, _ptr(_i32(pool_rules)), cells, rows_pool,
-                                         None if d_rows is None else _ptr(_i32(d_rows)), 0, _ptr(out), _ptr(choices), _stream()))
+                                         None if d_rows is None else _ptr(_i32(d_rows)), rows_unpooled, _ptr(out), _ptr(choices),
+                                         _ptr(ws), ws_bytes, _stream()))
     return out, choices
 
 

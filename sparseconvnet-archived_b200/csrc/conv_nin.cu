@@ -461,7 +461,7 @@ extern "C" int scn_conv_nin_forward_dyn(const float *d_in, const int *d_rules, i
 extern "C" int scn_conv_nin_maxpool_forward(const float *d_in, const int *d_rules, int fs, int nIn, const void *d_W_packed, const float *d_B,
                                             const float *d_prelu, int N, float p, int act, const int *d_pool_rules, int pool_cells,
                                             int rows_pool_bound, const int *d_rows_pool, int rows_unpooled, float *d_out, int *d_choices,
-                                            scn_stream_t stream) {
+                                            void *d_workspace, size_t workspace_bytes, scn_stream_t stream) {
   clear_error();
   if (rows_pool_bound < 0 || fs < 1 || nIn < 1 || N < 1) return fail(SCN_ERR_INVALID, "bad conv/NiN sizes");
   if (act < SCN_NOSIGMOID || act > SCN_SIGMOID || act == SCN_SOFTMAX) return fail(SCN_ERR_INVALID, "activation not supported here");
@@ -469,8 +469,8 @@ extern "C" int scn_conv_nin_maxpool_forward(const float *d_in, const int *d_rule
   if (rows_pool_bound == 0) return SCN_OK;
   if (!d_in || !d_rules || !d_W_packed || !d_B || !d_pool_rules || !d_out || !d_choices) return fail(SCN_ERR_INVALID, "null pointer");
   if (!tc_shape_ok(fs, nIn, N, SCN_PREC_3XTF32)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
-  return tc_launch(d_in, d_rules, rows_pool_bound, fs, nIn, d_W_packed, d_B, d_prelu, N, p, act, SCN_PREC_3XTF32, d_out, nullptr, 0,
-                   (cudaStream_t)stream, d_rows_pool, d_pool_rules, pool_cells, d_choices, rows_unpooled);
+  return tc_launch(d_in, d_rules, rows_pool_bound, fs, nIn, d_W_packed, d_B, d_prelu, N, p, act, SCN_PREC_3XTF32, d_out, d_workspace,
+                   workspace_bytes, (cudaStream_t)stream, d_rows_pool, d_pool_rules, pool_cells, d_choices, rows_unpooled);
 }
 
 extern "C" size_t scn_conv_packed_weight_bytes(int K, int N, int precision) { return tc_packed_bytes(K, N, precision); }

@@ -1036,6 +1036,47 @@ __global__ void k_splitk_finish(const float *__restrict__ partial, int kSplit, l
   }
 }
 
+// The same with a non-overlapping max pooling applied on the way (MaxPoolingLayer.cu:9-35): one thread per pooled
+// row and four columns; every cell's partial sums are added in split order and finished exactly as above, the
+// first maximum wins, the choice is the flat index row * N + column of the learnt layer's (unwritten) output.
+template <int ACT>
+__global__ void k_splitk_finish_pool(const float *__restrict__ partial, int kSplit, long long rows, int N, const float *__restrict__ bias,
+                                     const float *__restrict__ prelu, float p, const int *__restrict__ poolRules, int cells, int rowsPool,
+                                     float *__restrict__ out, int *__restrict__ choices) {
+  dependents_may_launch();
+  wait_for_prior_grids(); // the partial sums come from the kernel in front
+  const int nv = N >> 2;
+  const long long n4 = rows * nv, total = (long long)rowsPool * nv;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < total; q += (long long)gridDim.x * blockDim.x) {
+    const int w = (int)(q / nv), v = (int)(q - (long long)w * nv);
+    const float4 b4 = __ldg(reinterpret_cast<const float4 *>(bias) + v);
+    float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (prelu) s4 = __ldg(reinterpret_cast<const float4 *>(prelu) + v);
+    float best[4] = {0.f, 0.f, 0.f, 0.f};
+    int idx[4] = {-1, -1, -1, -1};
+    bool none = true;
+    for (int c = 0; c < cells; ++c) {
+      const int from = __ldg(poolRules + (long long)w * cells + c);
+      if (from < 0) continue;
+      const long long src = (long long)from * nv + v;
+      float4 a = reinterpret_cast<const float4 *>(partial)[src];
+      for (int sp = 1; sp < kSplit; ++sp) {
+        const float4 b = reinterpret_cast<const float4 *>(partial)[(long long)sp * n4 + src];
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      }
+      const float o[4] = {activate_t<ACT>(p * a.x + p * b4.x, s4.x), activate_t<ACT>(p * a.y + p * b4.y, s4.y),
+                          activate_t<ACT>(p * a.z + p * b4.z, s4.z), activate_t<ACT>(p * a.w + p * b4.w, s4.w)};
+      const int base = from * N + 4 * v;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (none || best[k] < o[k]) { best[k] = o[k]; idx[k] = base + k; }
+      none = false;
+    }
+    reinterpret_cast<float4 *>(out)[q] = make_float4(best[0], best[1], best[2], best[3]);
+    reinterpret_cast<int4 *>(choices)[q] = make_int4(idx[0], idx[1], idx[2], idx[3]);
+  }
+}
+
 // How many CTAs share one output tile's K range: only when the tiles alone leave most SMs idle.
 int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) {
   const int sms = sm_count();
@@ -1181,7 +1222,8 @@ size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision) {
 
 int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed, const float *d_B,
               const float *d_prelu, int N, float p, int act, int precision, float *d_out, void *d_ws, size_t wsBytes,
-              cudaStream_t s, const int *d_rows, const int *d_pool_rules, int pool_cells, int *d_choices, int rows_unpooled) {
+              cudaStream_t s, const int *d_rows, const int *d_pool_rules, int pool_cells, int *d_choices, int rows_unpooled,
+              const FinishPool *finish_pool) {
   Tiling t;
   const int passes = passes_of(precision);
   int rawEntries = 0, nStages64 = 0;
@@ -1189,6 +1231,17 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   // pooled: `rows` counts pooled rows; the kernel's row space is pooled rows x cells (a tile = 128 / cells windows)
   if (pool && (passes || !d_rules || !d_choices || pool_cells < 2 || pool_cells > 32 || (pool_cells & (pool_cells - 1)) || (long long)rows * pool_cells > INT_MAX))
     return fail(SCN_ERR_UNSUPPORTED, "fused max-pooling needs the 3xTF32 kernel, rules, and 2, 4, 8, 16 or 32 cells per window");
+  // Where the layer alone would split K (few tiles) the fused row space is not used: the plain kernel writes its
+  // partial sums over the layer's own rows and the pooling happens in the finishing kernel.
+  if (pool && !passes && rows_unpooled > 0 && d_ws && !d_rows && N % 4 == 0 && ((uintptr_t)d_ws & 15) == 0 &&
+      precision == SCN_PREC_3XTF32 && make_tiling(fs * nIn, N, fs, true, &t)) {
+    const int plainTiles = ((rows_unpooled + BM - 1) / BM) * t.nTiles;
+    if (choose_ksplit(plainTiles, t.nSlabs, rows_unpooled, N, wsBytes) > 1) {
+      FinishPool fp = {d_pool_rules, pool_cells, rows, d_choices};
+      return tc_launch(d_in, d_rules, rows_unpooled, fs, nIn, d_packed, d_B, d_prelu, N, p, act, precision, d_out, d_ws, wsBytes, s,
+                       nullptr, nullptr, 0, nullptr, 0, &fp);
+    }
+  }
   if (pool) rows *= pool_cells;
   const bool ok = N % 4 == 0 && (passes ? make_tiling16(fs * nIn, N, fs, d_rules != nullptr, passes, &t, &rawEntries, &nStages64)
                                         : precision == SCN_PREC_3XTF32 && make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, false, pool));
@@ -1262,7 +1315,13 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   }
 #undef SCN_TC16_LAUNCH
   SCN_LAUNCH_CHECK("k_conv_nin_tc");
-  if (P.kSplit > 1) {
+  if (P.kSplit > 1 && finish_pool) {
+    const FinishPool &fp = *finish_pool;
+    SCN_DISPATCH_ACT(act, (void)launch_dependent(k_splitk_finish_pool<ACT>, dim3(grid_for((long long)fp.rowsPool * N / 4, 256)), dim3(256), (size_t)0, s,
+                                                 (const float *)P.partial, P.kSplit, (long long)rows, N, d_B, d_prelu, p, fp.poolRules, fp.cells, fp.rowsPool,
+                                                 d_out, fp.choices));
+    SCN_LAUNCH_CHECK("k_splitk_finish_pool");
+  } else if (P.kSplit > 1) {
     SCN_DISPATCH_ACT(act, (void)launch_dependent(k_splitk_finish<ACT>, dim3(grid_for((long long)rows * N / 4, 256)), dim3(256), (size_t)0, s, (const float *)P.partial, P.kSplit, rows, N, d_B, d_prelu, p, d_out));
     SCN_LAUNCH_CHECK("k_splitk_finish");
   }

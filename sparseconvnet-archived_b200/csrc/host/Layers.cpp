@@ -481,9 +481,16 @@ bool NetworkInNetworkLayer::forwardsPooled(SpatiallySparseBatch &batch, Spatiall
   poolOutput.sub->features.resize(n);
   poolOutput.sub->poolingChoices.resize(n);
   const float p = 1.0f - (batch.type != RESCALEBATCH ? dropout : 0.0f);
+  // a layer of few tiles keeps its K split: the pooling then runs where the partial sums are added
+  void *ws = nullptr;
+  const size_t wsBytes = (rowsUnpooled > 0 && !d_rowsPool) ? scn_conv_nin_workspace_bytes(rowsUnpooled, convCells, nIn, nFeaturesOut, SCN_PREC_3XTF32) : 0;
+  if (wsBytes) {
+    splitScratch.resize((int)((wsBytes + sizeof(float) - 1) / sizeof(float)));
+    ws = splitScratch.dPtr();
+  }
   const int rc = scn_conv_nin_maxpool_forward(source.sub->features.dPtr(), input.rules.dPtr(), convCells, nIn, pk, B.dPtr(), slopes(), nFeaturesOut, p,
                                               (int)fn, poolOutput.rules.dPtr(), poolCells, (int)rowsPoolBound, d_rowsPool, rowsUnpooled,
-                                              poolOutput.sub->features.dPtr(), poolOutput.sub->poolingChoices.dPtr(), memStream.stream);
+                                              poolOutput.sub->features.dPtr(), poolOutput.sub->poolingChoices.dPtr(), ws, wsBytes, memStream.stream);
   if (rc == SCN_ERR_UNSUPPORTED) return false; // e.g. so few rows that K would be split
   scnSafeCall(rc);
   return true;

@@ -277,6 +277,19 @@ def test_conv_nin_with_row_count_on_the_device(abi, oracle):
     (500, 200, 8, 4, 48, 2, "RELU"),
 ])
 def test_conv_nin_maxpool_fused(abi, oracle, rows_in, windows, fs, nIn, N, cells, act):
+    _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, False)
+
+
+@pytest.mark.parametrize("rows_in,windows,fs,nIn,N,cells,act", [
+    (300, 60, 4, 256, 128, 4, "VLEAKYRELU"),    # two tiles, 32 slabs: K is split and the pooling runs in the finishing kernel
+    (200, 30, 8, 128, 608, 8, "RELU"),
+])
+def test_conv_nin_maxpool_with_k_split(abi, oracle, rows_in, windows, fs, nIn, N, cells, act):
+    assert abi.lib().scn_conv_nin_workspace_bytes(windows * cells + 5, fs, nIn, N, abi.PREC_3XTF32) > 0
+    _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, True)
+
+
+def _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, split):
     """Gather + NiN + non-overlapping max pooling in one kernel against the oracle's three steps: pooled values
     within the fp32 tolerance, every choice names an input whose value is the window's maximum."""
     from oracle import orc
@@ -300,7 +313,8 @@ def test_conv_nin_maxpool_fused(abi, oracle, rows_in, windows, fs, nIn, N, cells
     packed = abi.pack_weights(dW, abi.PREC_3XTF32)
     out, ch = abi.conv_nin_maxpool_forward(torch.from_numpy(feat).cuda(), torch.from_numpy(rules).cuda().flatten(), fs, dW,
                                            torch.from_numpy(B).cuda(), torch.from_numpy(pool).cuda().flatten(), cells,
-                                           None if prelu is None else torch.from_numpy(prelu).cuda(), 0.9, actc, packed)
+                                           None if prelu is None else torch.from_numpy(prelu).cuda(), 0.9, actc, packed,
+                                           rows_unpooled=rows_mid if split else 0, split_k=split)
     torch.cuda.synchronize()
     assert abi.conv_tc_take_error() == 0
     out, ch = out.cpu().numpy(), ch.cpu().numpy()
