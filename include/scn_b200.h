@@ -238,6 +238,18 @@ int scn_conv_nin_maxpool_forward(const float *d_in, const int *d_rules, int fs, 
                                  int rows_unpooled, float *d_out, int *d_choices, void *d_workspace, size_t workspace_bytes,
                                  scn_stream_t stream);
 
+/* Two learnt layers in a row where the first has few rows and a long K (the top of a network: ConvolutionalLayer
+ * gather + NetworkInNetworkLayer, NetworkInNetworkLayer.cu:187-201, then the classifier's NetworkInNetworkLayer with
+ * its softmax, SigmoidLayer.cu:160-177): the first runs on the 3xTF32 kernel with K split over several CTAs
+ * (d_workspace: scn_conv_nin_workspace_bytes(rows_out, ...) bytes, must be > 0) and the kernel that adds the partial
+ * sums also applies the second layer W2[N x N2] (fp32, N2 <= 16, softmax allowed).  d_mid[rows_out x N] receives the
+ * first layer's output as scn_conv_nin_forward_ws would write it, d_out[rows_out x N2] the second's.
+ * SCN_ERR_UNSUPPORTED where the first layer would not split K or the shapes do not fit: run the two layers. */
+int scn_conv_nin_nin_forward(const float *d_in, const int *d_rules, int rows_out, int fs, int nIn, const void *d_W_packed,
+                             const float *d_B, const float *d_prelu, int N, float p, int activation, const float *d_W2,
+                             const float *d_B2, const float *d_prelu2, int N2, float p2, int activation2, float *d_mid,
+                             float *d_out, void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
+
 /* One-time repack of W[K x N] (K = fs*nIn) for a tensor-core precision: bytes needed, then
  * the packing kernel.  No reference counterpart (the reference hands W to cuBLAS as is). */
 size_t scn_conv_packed_weight_bytes(int K, int N, int precision);

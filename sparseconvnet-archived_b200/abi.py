@@ -20,7 +20,7 @@ DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
 EXPORTS = [
     "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
     "scn_rules_workspace_bytes", "scn_rules_build", "scn_fmp_rules_workspace_bytes", "scn_fmp_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_terminal_rules_workspace_bytes",
-    "scn_terminal_rules_build", "scn_conv_auto_precision", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_forward_dyn", "scn_conv_nin_maxpool_forward", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
+    "scn_terminal_rules_build", "scn_conv_auto_precision", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_forward_dyn", "scn_conv_nin_maxpool_forward", "scn_conv_nin_nin_forward", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
 ]
@@ -74,6 +74,7 @@ def lib():
         L.scn_conv_nin_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_int, c_f, c_int, c_int, c_p, c_p]
         L.scn_conv_nin_forward_dyn.argtypes = [c_p, c_p, c_int, c_p, c_int, c_int, c_p, c_p, c_p, c_int, c_f, c_int, c_p, c_p]
         L.scn_conv_nin_maxpool_forward.argtypes = [c_p, c_p, c_int, c_int, c_p, c_p, c_p, c_int, c_f, c_int, c_p, c_int, c_int, c_p, c_int, c_p, c_p, c_p, c_sz, c_p]
+        L.scn_conv_nin_nin_forward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_int, c_f, c_int, c_p, c_p, c_p, c_int, c_f, c_int, c_p, c_p, c_p, c_sz, c_p]
         L.scn_conv_nin_forward_ws.argtypes = [c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_int, c_f, c_int, c_int, c_p, c_p, c_sz, c_p]
         L.scn_conv_nin_workspace_bytes.restype = c_sz
         L.scn_conv_nin_workspace_bytes.argtypes = [c_int] * 5
@@ -334,6 +335,22 @@ def conv_nin_maxpool_forward(feat, rules, fs, W, B, pool_rules, cells, prelu=Non
                                          None if d_rows is None else _ptr(_i32(d_rows)), rows_unpooled, _ptr(out), _ptr(choices),
                                          _ptr(ws), ws_bytes, _stream()))
     return out, choices
+
+
+def conv_nin_nin_forward(feat, rules, fs, W, B, W2, B2, prelu=None, p=1.0, act=NOSIGMOID, p2=1.0, act2=SOFTMAX, packed=None):
+    """scn_conv_nin_nin_forward -> (first layer's output [rows x N], second's [rows x N2])."""
+    L = lib()
+    K, N = W.shape
+    N2 = W2.shape[1]
+    rows = feat.shape[0] if rules is None else rules.numel() // fs
+    mid = torch.empty((rows, N), dtype=torch.float32, device=feat.device)
+    out = torch.empty((rows, N2), dtype=torch.float32, device=feat.device)
+    ws_bytes = L.scn_conv_nin_workspace_bytes(rows, fs, K // fs, N, PREC_3XTF32)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=feat.device)
+    check(L.scn_conv_nin_nin_forward(_ptr(_f32(feat)), None if rules is None else _ptr(_i32(rules)), rows, fs, K // fs, _ptr(packed), _ptr(_f32(B)),
+                                     None if prelu is None else _ptr(_f32(prelu)), N, p, act, _ptr(_f32(W2)), _ptr(_f32(B2)), None, N2, p2, act2,
+                                     _ptr(mid), _ptr(out), _ptr(ws), ws_bytes, _stream()))
+    return mid, out
 
 
 def background_rows(keys, off):

@@ -473,6 +473,25 @@ extern "C" int scn_conv_nin_maxpool_forward(const float *d_in, const int *d_rule
                    workspace_bytes, (cudaStream_t)stream, d_rows_pool, d_pool_rules, pool_cells, d_choices, rows_unpooled);
 }
 
+extern "C" int scn_conv_nin_nin_forward(const float *d_in, const int *d_rules, int rows_out, int fs, int nIn, const void *d_W_packed,
+                                        const float *d_B, const float *d_prelu, int N, float p, int act, const float *d_W2, const float *d_B2,
+                                        const float *d_prelu2, int N2, float p2, int act2, float *d_mid, float *d_out, void *d_workspace,
+                                        size_t workspace_bytes, scn_stream_t stream) {
+  clear_error();
+  if (rows_out < 0 || fs < 1 || nIn < 1 || N < 1 || N2 < 1) return fail(SCN_ERR_INVALID, "bad conv/NiN sizes");
+  if (!d_rules && fs != 1) return fail(SCN_ERR_INVALID, "fs must be 1 without rules");
+  if (act < SCN_NOSIGMOID || act > SCN_SIGMOID || act == SCN_SOFTMAX) return fail(SCN_ERR_INVALID, "activation not supported for the first layer");
+  if (act2 < SCN_NOSIGMOID || act2 > SCN_SIGMOID) return fail(SCN_ERR_INVALID, "unknown activation");
+  if ((act == SCN_PRELU && !d_prelu) || (act2 == SCN_PRELU && !d_prelu2)) return fail(SCN_ERR_INVALID, "PReLU slopes missing");
+  if (rows_out == 0) return SCN_OK;
+  if (!d_in || !d_W_packed || !d_B || !d_W2 || !d_B2 || !d_mid || !d_out) return fail(SCN_ERR_INVALID, "null pointer");
+  if (N2 > 16 || N % 4 != 0 || !d_workspace || !tc_shape_ok(fs, nIn, N, SCN_PREC_3XTF32))
+    return fail(SCN_ERR_UNSUPPORTED, "needs the 3xTF32 kernel with a K split and at most 16 outputs of the second layer");
+  FinishNin f2 = {d_W2, d_B2, d_prelu2, N2, p2, act2, d_out};
+  return tc_launch(d_in, d_rules, rows_out, fs, nIn, d_W_packed, d_B, d_prelu, N, p, act, SCN_PREC_3XTF32, d_mid, d_workspace, workspace_bytes,
+                   (cudaStream_t)stream, nullptr, nullptr, 0, nullptr, 0, nullptr, &f2);
+}
+
 extern "C" size_t scn_conv_packed_weight_bytes(int K, int N, int precision) { return tc_packed_bytes(K, N, precision); }
 
 extern "C" int scn_conv_pack_weights(const float *d_W, int K, int N, int precision, void *d_W_packed,

@@ -1077,6 +1077,95 @@ __global__ void k_splitk_finish_pool(const float *__restrict__ partial, int kSpl
   }
 }
 
+// The K-split finish of a layer of few rows with the small learnt layer behind it (the classifier of a network:
+// NetworkInNetworkLayer.cu:187-201 twice, SigmoidLayer.cu:160-177 for its softmax) applied on the way: one CTA per
+// row adds the partial sums in split order, finishes the row exactly as k_splitk_finish does (and writes it), keeps
+// it in shared memory and multiplies it with W2[N x N2], N2 <= 16, in fp32 on the CUDA cores.
+template <int ACT>
+__global__ void __launch_bounds__(256)
+k_splitk_finish_nin(const float *__restrict__ partial, int kSplit, long long rows, int N, const float *__restrict__ bias,
+                    const float *__restrict__ prelu, float p, float *__restrict__ mid, const float *__restrict__ W2,
+                    const float *__restrict__ B2, const float *__restrict__ prelu2, int N2, float p2, int act2, float *__restrict__ out2) {
+  extern __shared__ float xS[]; // the finished row, then 8 x 16 partial dot products
+  float *red = xS + N;
+  dependents_may_launch();
+  wait_for_prior_grids(); // the partial sums come from the kernel in front
+  const int nv = N >> 2, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long n4 = rows * nv;
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    __syncthreads();
+    for (int v = threadIdx.x; v < nv; v += 256) {
+      const long long q = row * nv + v;
+      // eight partial sums are requested at a time (independent loads), then added in split order
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int sp0 = 0; sp0 < kSplit; sp0 += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) t[u] = reinterpret_cast<const float4 *>(partial)[(long long)min(sp0 + u, kSplit - 1) * n4 + q];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (sp0 + u == 0) a = t[u];
+          else if (sp0 + u < kSplit) { a.x += t[u].x; a.y += t[u].y; a.z += t[u].z; a.w += t[u].w; }
+        }
+      }
+      const float4 b4 = __ldg(reinterpret_cast<const float4 *>(bias) + v);
+      float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (prelu) s4 = __ldg(reinterpret_cast<const float4 *>(prelu) + v);
+      float4 o;
+      o.x = activate_t<ACT>(p * a.x + p * b4.x, s4.x); o.y = activate_t<ACT>(p * a.y + p * b4.y, s4.y);
+      o.z = activate_t<ACT>(p * a.z + p * b4.z, s4.z); o.w = activate_t<ACT>(p * a.w + p * b4.w, s4.w);
+      if (mid) reinterpret_cast<float4 *>(mid)[q] = o;
+      reinterpret_cast<float4 *>(xS)[v] = o;
+    }
+    __syncthreads();
+    float acc[16];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) acc[n] = 0.f;
+    for (int k0 = threadIdx.x; k0 < N; k0 += 256 * 3) { // three rows of W2 requested at a time
+      float w[3][16];
+#pragma unroll
+      for (int u = 0; u < 3; ++u) {
+        const float *wr = W2 + (long long)min(k0 + 256 * u, N - 1) * N2;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) w[u][n] = __ldg(wr + (n < N2 ? n : 0));
+      }
+#pragma unroll
+      for (int u = 0; u < 3; ++u) {
+        const float x = k0 + 256 * u < N ? xS[k0 + 256 * u] : 0.f;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) acc[n] = fmaf(x, w[u][n], acc[n]);
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      float v = acc[n];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) red[warp * 16 + n] = v;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      const bool valid = lane < N2;
+      float s = 0.f;
+      if (valid)
+        for (int w = 0; w < 8; ++w) s += red[w * 16 + lane];
+      float v = valid ? p2 * s + p2 * __ldg(B2 + lane) : -10000.0f;
+      if (act2 == SCN_SOFTMAX) { // SigmoidLayer.cu:160-177: running maximum from -10000
+        float mx = fmaxf(v, -10000.0f);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float e = valid ? expf(v - mx) : 0.f, sum = e;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        v = e / sum;
+      } else if (valid) {
+        v = activate(v, act2, prelu2 ? __ldg(prelu2 + lane) : 0.f);
+      }
+      if (valid) out2[row * N2 + lane] = v;
+    }
+  }
+}
+
 // How many CTAs share one output tile's K range: only when the tiles alone leave most SMs idle.
 int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) {
   const int sms = sm_count();
@@ -1223,7 +1312,7 @@ size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision) {
 int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const void *d_packed, const float *d_B,
               const float *d_prelu, int N, float p, int act, int precision, float *d_out, void *d_ws, size_t wsBytes,
               cudaStream_t s, const int *d_rows, const int *d_pool_rules, int pool_cells, int *d_choices, int rows_unpooled,
-              const FinishPool *finish_pool) {
+              const FinishPool *finish_pool, const FinishNin *finish_nin) {
   Tiling t;
   const int passes = passes_of(precision);
   int rawEntries = 0, nStages64 = 0;
@@ -1251,6 +1340,7 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   const int mTiles = (rows + BM - 1) / BM;
   int kSplit = (d_ws && ((uintptr_t)d_ws & 15) == 0) ? choose_ksplit(mTiles * t.nTiles, passes ? 2 * nStages64 : t.nSlabs, rows, N, wsBytes) : 1;
   if (pool && kSplit > 1) return fail(SCN_ERR_UNSUPPORTED, "fused max-pooling is not combined with a K split");
+  if (finish_nin && (kSplit <= 1 || passes || pool)) return fail(SCN_ERR_UNSUPPORTED, "the second learnt layer rides on the K-split finish only");
   if (pool && rows_unpooled > 0) {
     // The window-major row space repeats rows that several windows name (background rows) and pads ragged
     // windows: do not fuse where that costs a wave of tiles, or where the layer alone would split K.
@@ -1315,7 +1405,14 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   }
 #undef SCN_TC16_LAUNCH
   SCN_LAUNCH_CHECK("k_conv_nin_tc");
-  if (P.kSplit > 1 && finish_pool) {
+  if (P.kSplit > 1 && finish_nin) {
+    const FinishNin &fn2 = *finish_nin;
+    const int blocks = rows < 8 * sm_count() ? rows : 8 * sm_count();
+    SCN_DISPATCH_ACT(act, (void)launch_dependent(k_splitk_finish_nin<ACT>, dim3(blocks), dim3(256), (size_t)(N + 128) * sizeof(float), s, (const float *)P.partial,
+                                                 P.kSplit, (long long)rows, N, d_B, d_prelu, p, d_out, fn2.W2, fn2.B2, fn2.prelu2, fn2.N2, fn2.p2, fn2.act2,
+                                                 fn2.out2));
+    SCN_LAUNCH_CHECK("k_splitk_finish_nin");
+  } else if (P.kSplit > 1 && finish_pool) {
     const FinishPool &fp = *finish_pool;
     SCN_DISPATCH_ACT(act, (void)launch_dependent(k_splitk_finish_pool<ACT>, dim3(grid_for((long long)fp.rowsPool * N / 4, 256)), dim3(256), (size_t)0, s,
                                                  (const float *)P.partial, P.kSplit, (long long)rows, N, d_B, d_prelu, p, fp.poolRules, fp.cells, fp.rowsPool,

@@ -495,6 +495,42 @@ bool NetworkInNetworkLayer::forwardsPooled(SpatiallySparseBatch &batch, Spatiall
   scnSafeCall(rc);
   return true;
 }
+bool NetworkInNetworkLayer::forwardsWithNext(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                                             NetworkInNetworkLayer &next, SpatiallySparseBatchInterface &nextOutput) {
+  if (batch.type == TRAINBATCH || fusePoolNext || next.fusePoolNext) return false;
+  if ((precision != SCN_PREC_AUTO && precision != SCN_PREC_3XTF32) || scn_conv_auto_precision() != SCN_PREC_3XTF32) return false;
+  if (next.precision != SCN_PREC_AUTO && next.precision != SCN_PREC_FP32) return false;
+  if (fn == SOFTMAX || nFeaturesOut % 4 != 0 || next.nFeaturesOut > 16 || next.nFeaturesIn != nFeaturesOut) return false;
+  const float *src;
+  const int *rules = nullptr;
+  int fs = 1, nIn = nFeaturesIn;
+  if (input.deferredFrom) { // fused gather
+    src = input.deferredFrom->sub->features.dPtr();
+    rules = input.rules.dPtr();
+    fs = input.deferredCells;
+    nIn = nFeaturesIn / fs;
+  } else {
+    src = input.sub->features.dPtr();
+  }
+  const int rows = output.nSpatialSites;
+  const size_t wsBytes = rows > 0 ? scn_conv_nin_workspace_bytes(rows, fs, nIn, nFeaturesOut, SCN_PREC_3XTF32) : 0;
+  if (!wsBytes) return false; // the layer would not split K
+  const void *pk = packedWeights(fs, nIn, SCN_PREC_3XTF32);
+  if (!pk) return false;
+  splitScratch.resize((int)((wsBytes + sizeof(float) - 1) / sizeof(float)));
+  output.sub->features.resize(rows * output.featuresPresent.size());
+  nextOutput.sub->features.resize(rows * nextOutput.featuresPresent.size());
+  const bool rescale = batch.type == RESCALEBATCH;
+  const float p = 1.0f - (!rescale ? dropout : 0.0f), p2 = 1.0f - (!rescale ? next.dropout : 0.0f);
+  const int rc = scn_conv_nin_nin_forward(src, rules, rows, fs, nIn, pk, B.dPtr(), slopes(), nFeaturesOut, p, (int)fn, next.W.dPtr(), next.B.dPtr(),
+                                          next.slopes(), next.nFeaturesOut, p2, (int)next.fn, output.sub->features.dPtr(),
+                                          nextOutput.sub->features.dPtr(), splitScratch.dPtr(), wsBytes, memStream.stream);
+  if (rc == SCN_ERR_UNSUPPORTED) return false;
+  scnSafeCall(rc);
+  countMultiplyAdds(input, output);
+  next.countMultiplyAdds(output, nextOutput);
+  return true;
+}
 void NetworkInNetworkLayer::forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
   if (fusePoolNext && input.deferredFrom && batch.type != TRAINBATCH) { // the pooling layer behind this one runs all three steps
     output.deferredLearnt = this;

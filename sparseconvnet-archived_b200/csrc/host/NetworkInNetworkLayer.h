@@ -42,6 +42,11 @@ public:
   // Convolution + this layer + the max pooling behind it in one kernel: the pooled features and choices go to
   // poolOutput, this layer's own output is never written.  d_rowsPool: device-side pooled row count (then
   // rowsPoolBound is an upper bound) or nullptr.  False (nothing launched) if the kernel does not take the case.
+  // This layer and the small learnt layer behind it (the classifier) in one call, where this layer splits K (few
+  // rows): the kernel that adds the partial sums applies `next` as well.  Both outputs are written.  false: not
+  // taken, run the two layers.
+  bool forwardsWithNext(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                        NetworkInNetworkLayer &next, SpatiallySparseBatchInterface &nextOutput);
   bool forwardsPooled(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &source, SpatiallySparseBatchInterface &input,
                       SpatiallySparseBatchInterface &poolOutput, int convCells, int poolCells, long long rowsPoolBound, const int *d_rowsPool,
                       int rowsUnpooled = 0);

@@ -20,6 +20,7 @@ void SparseConvNetCUDA::init(int nInputFeatures_, int nClasses_) {
   // off by default: with BatchProducer threads the next batch is preprocessed while the current one is
   // still in its layers, and the features buffers behind the first layers are shared by the batch pool
   fusePooling = true;
+  fuseClassifier = true;
   earlyFirstLayer = false; earlyLayers = 0; inputReady = nullptr; countStream = nullptr; chainDone = nullptr;
   chainRowsHint = 0;
   inputSpatialSize = 0;
@@ -269,6 +270,20 @@ void SparseConvNetCUDA::forwardLayers(SpatiallySparseBatch &batch) {
     batch.interfaces[i + 1].sub->reset();
     batch.interfaces[i + 1].deferredFrom = nullptr;
     batch.interfaces[i + 1].deferredLearnt = nullptr;
+    if (fuseClassifier && i + 1 < layers.size()) { // a learnt layer of few rows and the small learnt layer behind it (the classifier) as one call
+      auto a = dynamic_cast<NetworkInNetworkLayer *>(layers[i]);
+      auto b = dynamic_cast<NetworkInNetworkLayer *>(layers[i + 1]);
+      if (a && b) {
+        batch.interfaces[i + 2].sub->reset();
+        batch.interfaces[i + 2].deferredFrom = nullptr;
+        batch.interfaces[i + 2].deferredLearnt = nullptr;
+        if (a->forwardsWithNext(batch, batch.interfaces[i], batch.interfaces[i + 1], *b, batch.interfaces[i + 2])) {
+          if (timing) cudaSafeCall(cudaEventRecord(events[i + 1], memStream.stream));
+          ++i;
+          continue;
+        }
+      }
+    }
     layers[i]->forwards(batch, batch.interfaces[i], batch.interfaces[i + 1]);
   }
   if (timing) cudaSafeCall(cudaEventRecord(events[layers.size()], memStream.stream));

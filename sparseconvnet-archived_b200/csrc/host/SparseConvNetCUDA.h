@@ -15,6 +15,7 @@ class SparseConvNetCUDA {
 public:
   // The first convolution + NiN pair is launched right behind the rule chain, before the row counts are
   // read back (its kernel takes its count from device memory), so the GPU works while the host waits.
+  bool fuseClassifier;      // forwardLayers() runs a learnt layer that splits K and the small learnt layer behind it (N <= 16) as one call
   bool fusePooling;         // builders mark learnt layers that a non-overlapping max pooling follows (see NetworkInNetworkLayer::fusePoolNext)
   bool earlyFirstLayer;
   int earlyLayers;          // layers of the current batch already launched by preprocessBatchOnDevice (0 or 2)

@@ -328,3 +328,39 @@ def _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, split):
     assert (ch[ok] % N == np.broadcast_to(np.arange(N), ch.shape)[ok]).all()
     assert np.isin(rows_of, pool[pool >= 0]).all()
     assert (ch[5] == pool[5, 0] * N + np.arange(N)).all()
+
+
+@pytest.mark.parametrize("rows_in,rows,fs,nIn,N,N2,act,act2", [
+    (1024, 256, 4, 512, 608, 10, "VLEAKYRELU", "SOFTMAX"),   # the top of the benchmark network: last convolution + classifier
+    (300, 100, 1, 1024, 96, 16, "RELU", "NOSIGMOID"),        # plain learnt layers, no rules
+    (200, 40, 8, 128, 288, 3, "LEAKYRELU", "SOFTMAX"),
+])
+def test_conv_nin_then_small_nin(abi, oracle, rows_in, rows, fs, nIn, N, N2, act, act2):
+    """A learnt layer that splits K and the small learnt layer behind it in one call (the second applied by the kernel
+    that adds the partial sums) against the oracle's two layers: both outputs within the fp32 tolerance."""
+    from oracle import orc
+    rng = np.random.default_rng(rows + N2)
+    K = fs * nIn
+    feat = rng.standard_normal((rows_in, nIn)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * np.sqrt(2.0 / K)).astype(np.float32)
+    B = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    W2 = (rng.standard_normal((N, N2)) * np.sqrt(2.0 / N)).astype(np.float32)
+    B2 = (rng.standard_normal(N2) * 0.1).astype(np.float32)
+    if fs > 1:
+        rules = random_rules(rng, rows, fs, rows_in)
+        X = oracle.gather(feat, rules, nIn).reshape(rows, K)
+        d_rules = torch.from_numpy(rules).cuda().flatten()
+    else:
+        feat = feat[:rows]
+        X, d_rules = feat, None
+    mid_ref = oracle.nin_forward(X, W, B, None, 0.9, getattr(orc, act), accum64=True)
+    out_ref = oracle.nin_forward(mid_ref.astype(np.float32), W2, B2, None, 1.0, getattr(orc, act2), accum64=True)
+    dW = torch.from_numpy(W).cuda()
+    packed = abi.pack_weights(dW, abi.PREC_3XTF32)
+    assert abi.lib().scn_conv_nin_workspace_bytes(rows, fs, nIn, N, abi.PREC_3XTF32) > 0
+    mid, out = abi.conv_nin_nin_forward(torch.from_numpy(feat).cuda(), d_rules, fs, dW, torch.from_numpy(B).cuda(), torch.from_numpy(W2).cuda(),
+                                        torch.from_numpy(B2).cuda(), None, 0.9, getattr(abi, act), 1.0, getattr(abi, act2), packed)
+    torch.cuda.synchronize()
+    assert abi.conv_tc_take_error() == 0
+    assert relerr(mid.cpu().numpy(), mid_ref) < RTOL_FP32
+    assert relerr(out.cpu().numpy(), out_ref) < RTOL_FP32
