@@ -708,7 +708,7 @@ template <int DIM>
 __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   extern __shared__ __align__(16) unsigned char chain_smem[];
   __shared__ Regions R;
-  __shared__ int sTicket, sTotal, sBase, sSitesBase, colOff[MAX_CUBE];
+  __shared__ int sTicket, sBase, sSitesBase, colOff[MAX_CUBE], sScan[2][32];
   uint2 *dir = reinterpret_cast<uint2 *>(chain_smem);
   int *keysA = reinterpret_cast<int *>(dir + P.wMax);
   int *keysB = keysA + P.rowsMax;
@@ -719,6 +719,24 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
   const int tid = threadIdx.x;
   const int NT = blockDim.x;
 
+  // Exclusive scan over the block with one barrier: every warp publishes its total, then every warp scans the
+  // totals for itself.  Two buffers alternate, so a call's reads are over (the next call's barrier) before
+  // the buffer is written again.
+  int scanFlip = 0;
+  auto scan = [&](int v, int *total) -> int {
+    const int lane = tid & 31, warp = tid >> 5, nWarps = NT >> 5;
+    int incl = v;
+    for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+    int *buf = sScan[scanFlip];
+    scanFlip ^= 1;
+    if (lane == 31) buf[warp] = incl;
+    __syncthreads();
+    const int t = lane < nWarps ? buf[lane] : 0;
+    int tincl = t;
+    for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, tincl, o); if (lane >= o) tincl += u; }
+    *total = __shfl_sync(0xffffffffu, tincl, nWarps - 1);
+    return __shfl_sync(0xffffffffu, tincl - t, warp) + incl - v;
+  };
   if (tid == 0) sTicket = atomicAdd(P.ticket, 1) + 1; // the ticket starts at -1
   __syncthreads();
   const int b = sTicket;
@@ -757,7 +775,7 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
         const int w = w0 + tid;
         const int c = (w < R.W) ? __popc(dir[w].x) : 0;
         int total;
-        const int ex = block_exclusive_scan(c, &total);
+        const int ex = scan(c, &total);
         if (w < R.W) dir[w].y = carry + ex;
         carry += total;
       }
@@ -787,21 +805,19 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
     }
     __syncthreads();
     // 5. prefix sums of the counts
+    int sitesOut = 0;
     {
       int carry = 0;
       for (int s0 = 0; s0 < nSites; s0 += NT) {
         const int s = s0 + tid;
         const int c = (s < nSites) ? cnt[s] : 0;
         int total;
-        const int ex = block_exclusive_scan(c, &total);
-        __syncthreads();
-        if (s < nSites) cnt[s] = carry + ex;
+        const int ex = scan(c, &total);
+        if (s < nSites) cnt[s] = carry + ex; // (read back by this thread only until the next barrier)
         carry += total;
       }
-      if (tid == 0) sTotal = carry;
+      sitesOut = carry; // every thread holds the total
     }
-    __syncthreads();
-    const int sitesOut = sTotal;
     const int needBg = sitesOut < R.fullSize;
     const int rowsOut = sitesOut + needBg;
     // 6. publish this sample's count, sum the earlier samples' counts
