@@ -2,6 +2,7 @@
 // HBM-bound: each input element is read once per rule that names it, every output element
 // is written once, accesses are coalesced along the channel axis (float4 where C % 4 == 0).
 #include "scn_common.cuh"
+#include <type_traits>
 
 namespace scn {
 namespace {
@@ -22,6 +23,32 @@ __global__ void k_maxpool(const float *__restrict__ in, const int *__restrict__ 
     bool none = true;
 #pragma unroll
     for (int v = 0; v < VEC; ++v) { best[v] = 0.f; idx[v] = -1; }
+    if (VEC == 4 && sd <= 8) {
+      // small windows: all rules, then all cells, are requested before the first comparison (two round trips to
+      // memory instead of two per cell); a missing cell reads the row of a cell that is there and is skipped
+      auto window = [&](auto widthC) {
+        constexpr int WIDTH = decltype(widthC)::value;
+        int rp[WIDTH], safe = -1;
+#pragma unroll
+        for (int p = 0; p < WIDTH; ++p) { rp[p] = p < sd ? __ldg(rules + (long long)r * sd + p) : -1; safe = max(safe, rp[p]); }
+        if (safe < 0) return;
+        float4 t[WIDTH];
+#pragma unroll
+        for (int p = 0; p < WIDTH; ++p) t[p] = *reinterpret_cast<const float4 *>(in + (long long)(rp[p] >= 0 ? rp[p] : safe) * C + j);
+#pragma unroll
+        for (int p = 0; p < WIDTH; ++p) {
+          if (rp[p] < 0) continue;
+          const float s[4] = {t[p].x, t[p].y, t[p].z, t[p].w};
+          const long long base = (long long)rp[p] * C + j;
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            if (none || best[v % VEC] < s[v]) { best[v % VEC] = s[v]; idx[v % VEC] = (int)(base + v); }
+          none = false;
+        }
+      };
+      if (sd <= 4) window(std::integral_constant<int, 4>());
+      else window(std::integral_constant<int, 8>());
+    } else
     for (int p = 0; p < sd; ++p) {
       const int rp = __ldg(rules + (long long)r * sd + p);
       if (rp < 0) continue;
