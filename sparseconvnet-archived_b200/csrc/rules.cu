@@ -250,6 +250,13 @@ __device__ __forceinline__ bool range_any(const uint2 *d, int k0, int n) {
   if (sh + n > 32) bits |= d[w + 1].x << (32 - sh);
   return (bits & (n == 32 ? 0xffffffffu : (1u << n) - 1u)) != 0u;
 }
+// The cells k0 .. k0 + n - 1 (1 <= n <= 32) as the low n bits of a word.
+__device__ __forceinline__ unsigned range_bits(const uint2 *d, int k0, int n) {
+  const int w = k0 >> 5, sh = k0 & 31;
+  unsigned bits = d[w].x >> sh;
+  if (sh + n > 32) bits |= d[w + 1].x << (32 - sh);
+  return bits & (n == 32 ? 0xffffffffu : (1u << n) - 1u);
+}
 template <int DIM> __device__ bool creates_f(const Regions &R, const uint2 *d, const int *i, const int *j) {
   if (R.minActive == -1) return true;
   if (R.minActive <= 1 && R.size <= 32) {
@@ -796,10 +803,44 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
       int i[DIM], j[DIM];
       decode_f<DIM>(inKeys[sorted[slot]], R.nIn, R.rNIn, i);
       int c = 0;
-      for (int t = 0; t < R.T; ++t) {
-        const bool f = touched_output_f<DIM>(R, i, t, j) && creates_f<DIM>(R, dir, i, j);
-        flags[slot * R.T + t] = f;
-        c += f;
+      if (DIM == 2 && R.stride == 1 && R.minActive >= 0 && R.minActive <= 1 && R.size <= 8 && R.lattice != SCN_LATTICE_TRIANGULAR && !R.fmp) {
+        // Square filters of stride 1 in two dimensions: the `size` grid lines that can hold a smaller key than
+        // this site's within any field it lies in are read once, as windows of 2 * size - 1 cells around the
+        // site's column (cells off the grid read 0); each output's test is then two masks.
+        const int y = i[0], x = i[DIM - 1], sz = R.size, left = x - sz + 1;
+        const int c0 = max(left, 0), c1 = min(x + sz - 1, R.nIn - 1);
+        unsigned win[7]; // the lines above the site's, nearest last
+#pragma unroll
+        for (int k = 0; k < 7; ++k) {
+          const int yy = y - sz + 1 + k;
+          win[k] = (k < sz - 1 && yy >= 0) ? range_bits(dir, yy * R.nIn + c0, c1 - c0 + 1) << (c0 - left) : 0u;
+        }
+        const unsigned own = range_bits(dir, y * R.nIn + c0, c1 - c0 + 1) << (c0 - left); // the site's own line
+        const int loY = max(y - sz + 1, 0), hiY = min(y + 1, R.nOut), loX = max(left, 0), hiX = min(x + 1, R.nOut);
+        const unsigned full = (1u << sz) - 1u;
+        int t = 0;
+        for (int ty = 0; ty < R.Tax; ++ty) {
+          const int jy = loY + ty;
+          unsigned above = 0u; // the field's lines in front of the site's
+#pragma unroll
+          for (int k = 0; k < 7; ++k)
+            if (k < sz - 1 && y - sz + 1 + k >= jy) above |= win[k];
+          for (int tx = 0; tx < R.Tax; ++tx, ++t) {
+            const int jx = loX + tx, sh = jx - left;
+            const bool ok = jy < hiY && jx < hiX;
+            // cells of the field in front of the site: its lines above, and the site's own line left of it
+            const unsigned blocked = ok ? (((above >> sh) & full) | ((own >> sh) & ((1u << (x - jx)) - 1u))) : 1u;
+            const bool f = blocked == 0u;
+            flags[slot * R.T + t] = f;
+            c += f;
+          }
+        }
+      } else {
+        for (int t = 0; t < R.T; ++t) {
+          const bool f = touched_output_f<DIM>(R, i, t, j) && creates_f<DIM>(R, dir, i, j);
+          flags[slot * R.T + t] = f;
+          c += f;
+        }
       }
       cnt[slot] = c;
     }
