@@ -23,6 +23,9 @@ struct scn_net {
   // quarters of the input bytes) runs while the rule chain, which needs only keys and offsets, is built
   cudaStream_t copyStream = nullptr;
   cudaEvent_t copyDone = nullptr;
+  // host buffers already seen to be page-locked (a driver query per buffer and call costs microseconds; should one
+  // of them have become pageable since, its copy is still correct, only less asynchronous)
+  std::vector<const void *> knownPinned;
   ~scn_net() {
     if (copyDone) cudaEventDestroy(copyDone);
     if (copyStream) cudaStreamDestroy(copyStream);
@@ -228,10 +231,14 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *
     // Buffers in pinned (page-locked) host memory are copied straight from where they lie; pageable
     // ones go through the stream's pinned staging block first.  Background rows are found on the device.
     const size_t kb = sizeof(int) * rows, ob = sizeof(int) * (batch + 1), fb = sizeof(float) * (size_t)rows * nF;
-    auto pinned = [](const void *p) {
+    auto pinned = [&](const void *p) {
+      for (const void *k : net->knownPinned) if (k == p) return true;
       cudaPointerAttributes a;
       if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
-      return a.type == cudaMemoryTypeHost;
+      if (a.type != cudaMemoryTypeHost) return false;
+      if (net->knownPinned.size() >= 64) net->knownPinned.clear();
+      net->knownPinned.push_back(p);
+      return true;
     };
     const void *sk = keys, *so = off, *sf = features;
     if (!(pinned(keys) && pinned(off) && pinned(features))) {
