@@ -16,6 +16,13 @@ of the class probabilities.  Rank r of N processes its own 256 samples (weak sca
   roofline  the kernel with the largest share of the step, CUDA-event timed in the same run
   cpu_baseline  the CPU oracle (port of the reference's host rule construction and layer
             semantics) on a bounded sample of the same workload, all host cores
+  parity    the last timed step of both legs checked, outside the timed regions, against the
+            oracle's forward of the same batch: every rulebook equal, largest error of the
+            probabilities relative to the largest probability, top-1 agreement; at N > 1 also
+            every rank's shard against the oracle's forward of that rank's samples
+
+Every leg is run LEGS times (each --steps long); `value` and `e2e` are the median leg, the
+fastest and slowest legs are printed beside them.
 
 --impl reference times that CPU path alone (the reference has no CPU-only executable and
 its CUDA kernels are what this library replaces), rank 0 only.
@@ -42,17 +49,29 @@ WORKLOAD = ("config 2: CIFAR-10-shaped dense 32x32x3 N(0,1) patch in a 96x96 gri
             "VLeakyReLU, test-time dropout scaling p=0.5 ramp, softmax 10), batch 256 per GPU")
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of k_conv_nin_tc, averaged over the launches with K >= 128 of one
-# forward of config 2, batch 256 (profiles/conv_nin_tc_cfg2_batch256.md)
-TC_TRAFFIC = 17.2e6
+LEGS = 5
+
+
+def measured_traffic(kernel):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) that a profiler capture of this workload
+    recorded for `kernel`: a line "<kernel> <bytes>" of profiles/dram_traffic.txt, None when no capture is on file."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.txt")
+    if not os.path.exists(path):
+        return None
+    for line in open(path):
+        f = line.split()
+        if len(f) >= 2 and f[0] == kernel:
+            return float(f[1])
+    return None
 
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return dict(hbm_gbs=p["hbm_gbs"], tflops=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
-    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
+        return dict(hbm_gbs=p["hbm_gbs"], tflops=p["bf16_tflops"], tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
 
 
 class ClockSampler:
@@ -191,6 +210,44 @@ def build_pair_cpu_only(scn):
     return None, onet
 
 
+def relerr(a, b):
+    return float(np.abs(a - b).max() / max(float(np.abs(b).max()), 1e-30))
+
+
+def parity_check(scn, gnet, last, world, rank_rows, gathered_host, n_rot, steps, threads):
+    """Outside every timed region: the oracle's forward of the batch the last timed step processed, against what both
+    legs produced for it.  `last` = dict(batch index, device-leg probabilities and top-1, host-leg probabilities and
+    top-1) of this rank.  At N > 1 rank 0 also forwards every other rank's last batch through the oracle and compares
+    the all-gathered probabilities and each rank's per-interface row counts with it."""
+    _, onet = build_pair_cpu_only(scn)
+    gen = scn.synth.CONFIGS[CFG]["gen"]
+    j = last["batch_index"]
+    keys, off, feats = gen(BATCH_PER_GPU, first=j * BATCH_PER_GPU)
+    oprobs, opred = onet.forward(keys.astype(np.int64), off, feats, threads=threads, accum64=True, keep=True)
+    layers = gnet.layers()
+    rules_equal = True
+    for i in range(len(layers) + 1):
+        g, o = gnet.iface(i, features=False), onet.iface(i)
+        rules_equal = rules_equal and g["nSpatialSites"] == o["nSpatialSites"] and np.array_equal(g["rules"], o["rules"]) \
+            and np.array_equal(g["row_keys"], o["row_keys"])
+    out = dict(rules_equal=bool(rules_equal),
+               max_rel_err=max(relerr(last["dev_probs"], oprobs), relerr(last["host_probs"], oprobs)),
+               top1_agree=float(min((last["dev_top"] == opred).mean(), (last["host_top"] == opred).mean())),
+               samples=int(len(opred)), checked="last timed step of the device-resident leg and of the host-buffer leg vs the oracle "
+               "(fp64 accumulation); rulebooks and grids of every interface")
+    if world > 1:
+        ok, worst = True, 0.0
+        for r in range(world):
+            k2, o2, f2 = gen(BATCH_PER_GPU, first=(r * n_rot + (steps - 1) % n_rot) * BATCH_PER_GPU)
+            p2, _ = onet.forward(k2.astype(np.int64), o2, f2, threads=threads, accum64=True, keep=True)
+            rows = [onet.iface(i)["nSpatialSites"] for i in range(len(layers) + 1)]
+            ok = ok and rows == [int(v) for v in rank_rows[r]]
+            worst = max(worst, relerr(gathered_host[r * BATCH_PER_GPU:(r + 1) * BATCH_PER_GPU], p2))
+        out["shards_equal_whole"] = bool(ok and worst < 1e-4)
+        out["shards_max_rel_err"] = worst
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -198,10 +255,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--precision", default="auto", choices=["auto", "fp32", "3xtf32", "bf16", "3xbf16"])
-    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="wall time of the cpu_baseline leg (0 = skip)")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="wall time of the cpu_baseline leg (0 = skip it and the parity check)")
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="synthetic configuration (2 = the headline workload; the others are side measurements)")
     ap.add_argument("--batch", type=int, default=0, help="samples per GPU (0 = the configuration's own batch size, at most 256)")
+    ap.add_argument("--legs", type=int, default=LEGS, help="how often each timed leg is repeated (the median leg is reported)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
 
@@ -231,6 +289,7 @@ def main():
     c = scn.synth.CONFIGS[CFG]
     nC = c["nClasses"]
     peaks = measured_peaks()
+    steps = args.steps
 
     with torch.cuda.stream(stream):
         gnet, _ = build_pair(scn, False)
@@ -246,42 +305,43 @@ def main():
             bg = off[:-1].copy()  # the background row is each sample's first row
             dev_batches.append(tuple(torch.from_numpy(x).to(dev) for x in (keys, off, bg, feats)) + (int(np.diff(off).max() - 1),))
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
-        d_probs = torch.empty((BATCH_PER_GPU, nC), dtype=torch.float32, device=dev)
         d_top = torch.empty((BATCH_PER_GPU, 1), dtype=torch.int32, device=dev)
-        gathered = torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32, device=dev)
-        # device leg at N > 1: the all-gather of step j overlaps the forward of step j + 1 (two buffer
-        # sets); step j + 1 ends only after the gather of step j has completed on its stream
-        d_probs2 = [torch.empty_like(d_probs) for _ in range(2)]
-        gathered2 = [torch.empty_like(gathered) for _ in range(2)]
+        # at N > 1 the all-gather of step j overlaps the forward of step j + 1 in both legs (two buffer sets); step
+        # j + 1 ends only after the gather of step j has completed, and the last gather is timed behind the last step
+        d_probs2 = [torch.empty((BATCH_PER_GPU, nC), dtype=torch.float32, device=dev) for _ in range(2)]
+        gathered2 = [torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32, device=dev) for _ in range(2)]
+        h_gathered2 = [torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32).pin_memory() for _ in range(2)]
         pending = []
-        h_gathered = torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32).pin_memory()
+        last_host = {}
 
         def step_device(j):
             dk, do, db, df, ms = dev_batches[j % n_rot]
-            if world == 1:
-                gnet.forward_device(dk, do, db, df, ms, d_probs, d_top)
-                return
             gnet.forward_device(dk, do, db, df, ms, d_probs2[j & 1], d_top)
+            if world == 1:
+                return
             work = dist.all_gather_into_tensor(gathered2[j & 1], d_probs2[j & 1], async_op=True)
-            while pending:
-                pending.pop().wait()  # the launching stream waits for the previous step's gather
-            pending.append(work)
+            drain()  # the launching stream waits for the previous step's gather
+            pending.append((work, j & 1, False))
 
         def drain():
             while pending:
-                pending.pop().wait()
+                work, k, to_host = pending.pop()
+                work.wait()
+                if to_host:  # the gathered block goes back to the host: part of what a step of this leg delivers
+                    h_gathered2[k].copy_(gathered2[k], non_blocking=True)
+                    stream.synchronize()
 
         def step_host(j):
             keys, off, feats = host_batches[j % n_rot]
             probs, pred = gnet.forward_host(keys, off, feats)
+            last_host["probs"], last_host["top"] = probs, pred
             if world > 1:
-                gnet.copy_probs_device(d_probs)
-                dist.all_gather_into_tensor(gathered, d_probs)
-                h_gathered.copy_(gathered, non_blocking=True)
-                stream.synchronize()
-            return probs
+                gnet.copy_probs_device(d_probs2[j & 1])
+                work = dist.all_gather_into_tensor(gathered2[j & 1], d_probs2[j & 1], async_op=True)
+                drain()
+                pending.append((work, j & 1, True))
 
-        def timed(step, steps, with_layer_times):
+        def timed(step, with_layer_times):
             ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
             layer_ms = None
             for j in range(steps):
@@ -310,6 +370,20 @@ def main():
                 dist.barrier()
             torch.cuda.synchronize()
 
+        def check_tc(leg):
+            code = abi.conv_tc_take_error()
+            if code:
+                raise RuntimeError("a tensor-core kernel gave up a time-limited wait (code %d) during the %s leg: its numbers are void" % (code, leg))
+
+        def legs(step):
+            out = []
+            for _ in range(max(1, args.legs)):
+                barrier()
+                ms, _ = timed(step, False)
+                barrier()
+                out.append(ms)
+            return out
+
         # ---- device-resident leg
         sampler = ClockSampler(local)
         sampler.wait_first()
@@ -320,23 +394,26 @@ def main():
         t_load0 = time.time()
         launches0 = abi.kernel_launch_count()
         t_wall = time.time()
-        ms_dev, _ = timed(step_device, args.steps, False)
-        barrier()
+        ms_dev_legs = legs(step_device)
         t_wall = time.time() - t_wall
-        launches = abi.kernel_launch_count() - launches0
+        launches = (abi.kernel_launch_count() - launches0) // max(1, args.legs)
+        check_tc("device-resident")
+        last = dict(batch_index=rank * n_rot + (steps - 1) % n_rot, dev_probs=d_probs2[(steps - 1) & 1].cpu().numpy(), dev_top=d_top.cpu().numpy())
+        gathered_host = gathered2[(steps - 1) & 1].cpu().numpy() if world > 1 else None
         # Per-kernel durations for the roofline and the breakdown: the same steps once more with a CUDA
         # event between the layers.  (Those events cost about 0.06 ms of GPU idle per step, which is why
         # they are kept out of the steps that `value` is computed from.)
         gnet.enable_timing(True)
-        _, layer_ms = timed(step_device, args.steps, True)
+        _, layer_ms = timed(step_device, True)
         barrier()
         gnet.enable_timing(False)
         # ---- host-buffer leg
         for j in range(args.warmup):
             step_host(j)
-        barrier()
-        ms_e2e, _ = timed(step_host, args.steps, False)
-        barrier()
+        drain()
+        ms_e2e_legs = legs(step_host)
+        check_tc("host-buffer")
+        last["host_probs"], last["host_top"] = last_host["probs"].copy(), last_host["top"].copy()
         # A short run (few steps) can end between two nvidia-smi samples: keep the same steps going,
         # untimed, until a handful of samples have been taken under this load.
         tail_ms, j = 0.0, 0
@@ -344,23 +421,32 @@ def main():
         # (no collective in here: every rank runs its own number of extra steps)
         while sampler.proc is not None and sampler.count_in(t_load0, time.time()) < 5 and time.time() - t_tail < 2.0:
             dk, do, db, df, ms = dev_batches[j % n_rot]
-            gnet.forward_device(dk, do, db, df, ms, d_probs, d_top)
+            gnet.forward_device(dk, do, db, df, ms, d_probs2[0], d_top)
             j += 1
         if j:
             stream.synchronize()
             tail_ms = (time.time() - t_tail) * 1e3
         clocks = sampler.stop(t_load0, time.time())
-        clocks["window"] = "both timed legs" + (" + %.0f ms of the same steps, untimed" % tail_ms if j else "")
+        clocks["window"] = "all timed legs" + (" + %.0f ms of the same steps, untimed" % tail_ms if j else "")
+        # leave the network holding the last timed batch of the host leg (the parity check reads its rulebooks)
+        gnet.forward_host(*host_batches[(steps - 1) % n_rot])
 
         # shapes of the last forward for the roofline arithmetic
         layers = gnet.layers()
         sizes = [gnet.iface(i, features=False) for i in range(len(layers) + 1)]
 
-    t = torch.tensor([ms_dev, ms_e2e], dtype=torch.float64, device=dev)
+    # every leg: max over ranks, then the median leg
+    t = torch.tensor([ms_dev_legs, ms_e2e_legs], dtype=torch.float64, device=dev)
+    rows_t = torch.tensor([sz["nSpatialSites"] for sz in sizes], dtype=torch.int64, device=dev)
+    rank_rows = [rows_t.cpu().numpy()]
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_dev, ms_e2e = (float(x) for x in t.cpu())
-    total = world * BATCH_PER_GPU * args.steps
+        allrows = torch.empty((world, rows_t.numel()), dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(allrows, rows_t)
+        rank_rows = allrows.cpu().numpy()
+    dev_legs, e2e_legs = (sorted(float(x) for x in row) for row in t.cpu())
+    ms_dev, ms_e2e = dev_legs[len(dev_legs) // 2], e2e_legs[len(e2e_legs) // 2]
+    total = world * BATCH_PER_GPU * steps
 
     # ---- roofline of the kernel with the largest share of the step
     per_layer = []
@@ -397,56 +483,71 @@ def main():
     rules_ms = float(layer_ms[len(layers)])
     # The dominant kernel of the step is the tensor-core fused conv/NiN kernel (k_conv_nin_tc): its
     # launches with K >= 128 are tensor-bound, so the roofline entry is their algorithmic flops per
-    # launch over their average launch time.  `traffic` is the DRAM bytes per launch that ncu measured
-    # for the same launches (profiles/conv_nin_tc_cfg2_batch256.md).
+    # launch over their average launch time, against the measured bf16 figure of a kernel timed alone
+    # (these launches last 25-70 us).  kind::tf32 runs at half the bf16 rate and 3xTF32 issues three MMAs
+    # per product: `pipe_frac` is the same time against that ceiling (peak / 6).
     tc = [d for d in per_layer if d["kernel"] != "maxpool_rules" and d.get("K", 0) >= 128 and d["N"] >= 16]
-    step_ms = ms_dev / args.steps
+    step_ms = ms_dev / steps
+    passes = {"auto": 6.0, "3xtf32": 6.0, "3xbf16": 3.0, "bf16": 1.0}.get(args.precision, 6.0)
     if tc and args.precision != "fp32":
         ach = sum(d["flops"] for d in tc) / (sum(d["ms"] for d in tc) * 1e-3) / 1e12
         roof = dict(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"],
-                    traffic=TC_TRAFFIC if (world == 1 and CFG == 2 and BATCH_PER_GPU == 256) else None, kernel="k_conv_nin_tc (%d launches per step with K >= 128, %d of them with the max pooling fused in)" % (len(tc), sum(d["kernel"] == "conv_nin_maxpool_fused" for d in tc)),
+                    traffic=measured_traffic("k_conv_nin_tc") if (world == 1 and CFG == 2 and BATCH_PER_GPU == 256) else None,
+                    kernel="k_conv_nin_tc (%d launches per step with K >= 128, %d of them with the max pooling fused in)" % (len(tc), sum(d["kernel"] == "conv_nin_maxpool_fused" for d in tc)),
                     ms_per_launch=sum(d["ms"] for d in tc) / len(tc), share_of_step=sum(d["ms"] for d in tc) / step_ms,
-                    issued_tf32_tflops=3 * ach,
-                    note="peak is the measured bf16 cuBLAS figure; kind::tf32 runs at half that rate and 3xTF32 issues 3 MMAs "
-                         "per product, so 1/6 of this peak is the ceiling of a perfect 3xTF32 kernel")
+                    frac_of_sustained_peak=ach / peaks["tflops_sustained"], pipe_frac=ach * passes / peaks["tflops"],
+                    note="peak is the measured bf16 cuBLAS burst figure; kind::tf32 runs at half that rate and 3xTF32 issues 3 MMAs "
+                         "per product, so 1/6 of this peak is the ceiling of a perfect 3xTF32 kernel (pipe_frac is against that ceiling)")
     else:
         top = max(per_layer, key=lambda d: d["ms"])
         ach = top["bytes"] / (top["ms"] * 1e-3) / 1e9
         roof = dict(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"], traffic=None,
                     kernel="layer %d %s" % (top["layer"], top["kernel"]), ms_per_launch=top["ms"], share_of_step=top["ms"] / step_ms)
     roof["peak_source"] = peaks["source"]
+    # the HBM side: pooling as a kernel of its own, and the fused convolution + pooling kernels against the same 70 % bar
+    hbm_side = []
+    for d in per_layer:
+        if d["kernel"] in ("maxpool_rules", "conv_nin_maxpool_fused") or d.get("K", 1 << 30) < 128:
+            gbs = d["bytes"] / (d["ms"] * 1e-3) / 1e9
+            hbm_side.append(dict(layer=d["layer"], kernel=d["kernel"], gbs=gbs, frac=gbs / peaks["hbm_gbs"]))
     pool = [d for d in per_layer if d["kernel"] == "maxpool_rules"]
     pool_top = max(pool, key=lambda d: d["ms"]) if pool else None
     all_flops = sum(d["flops"] for d in per_layer)
     conv_ms = sum(d["ms"] for d in per_layer if d["kernel"] != "maxpool_rules")
 
     if rank == 0:
-        cpu = None
+        cpu, parity = None, None
         if args.cpu_seconds > 0:
             try:
                 _, onet = build_pair_cpu_only(scn)
                 cpu = cpu_leg(scn, onet, args.cpu_seconds, os.cpu_count() or 1)
+                parity = parity_check(scn, gnet, last, world, rank_rows, gathered_host, n_rot, steps, os.cpu_count() or 1)
             except Exception as e:  # the oracle is a checker, its absence must not hide the GPU numbers
-                cpu = dict(value=None, unit="samples/s", cores=0, kind="port", sample="unavailable: %s" % e)
-        h2d = int(sum(x.nbytes for x in host_batches[0]) + host_batches[0][1][:-1].nbytes)
-        d2h = int(BATCH_PER_GPU * nC * 4 + BATCH_PER_GPU * 4 + (world * BATCH_PER_GPU * nC * 4 if world > 1 else 0))
+                cpu = cpu or dict(value=None, unit="samples/s", cores=0, kind="port", sample="unavailable: %s" % e)
+                parity = parity or dict(unavailable=str(e))
+        h2d = int(sum(x.nbytes for x in host_batches[0]))
+        d2h = int(BATCH_PER_GPU * nC * 4 + BATCH_PER_GPU * 4 + 4 + (world * BATCH_PER_GPU * nC * 4 if world > 1 else 0))
         line = dict(
-            metric=METRIC, value=total / (ms_dev * 1e-3), unit="samples/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
-            ms_per_step=ms_dev / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
+            metric=METRIC, value=total / (ms_dev * 1e-3), unit="samples/s", n_gpus=world, steps=steps, warmup=args.warmup,
+            ms_per_step=ms_dev / steps, higher_is_better=True, scaling="weak", vs_baseline=None,
             dtype="f32" if args.precision == "fp32" else ("bf16" if args.precision == "bf16" else "tf32x3/f32"), data="synthetic",
-            config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample, all-gather of probabilities%s" % (world, " (step j's gather overlaps step j+1 in the device leg)" if world > 1 else ""),
+            config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample, all-gather of probabilities%s" % (world, " (step j's gather overlaps step j+1 in both legs)" if world > 1 else ""),
                         l2="256 MiB written between timed steps; 2 distinct batches rotated", precision=args.precision,
-                        timing="CUDA events per step on the launching stream, max over ranks; wall %.3f s for the device leg; per-kernel durations from a second pass of the same steps with events between the layers" % t_wall),
+                        timing="CUDA events per step on the launching stream, max over ranks; each leg %d times, median leg reported; wall %.3f s for the device legs; per-kernel durations from one more pass of the same steps with events between the layers" % (max(1, args.legs), t_wall)),
+            legs=dict(n=max(1, args.legs), ms_per_step_device=[round(x / steps, 5) for x in dev_legs], ms_per_step_e2e=[round(x / steps, 5) for x in e2e_legs]),
             e2e=dict(value=total / (ms_e2e * 1e-3), unit="samples/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
-                     ms_per_step=ms_e2e / args.steps),
-            gpu_launches=int(launches), roofline=roof, cpu_baseline=cpu, clocks=clocks,
+                     ms_per_step=ms_e2e / steps),
+            gpu_launches=int(launches), roofline=roof, cpu_baseline=cpu, parity=parity, clocks=clocks,
             pooling_roofline=(dict(bound="hbm", kernel="k_maxpool layer %d" % pool_top["layer"], achieved=pool_top["bytes"] / (pool_top["ms"] * 1e-3) / 1e9,
                                    peak=peaks["hbm_gbs"], unit="GB/s", frac=pool_top["bytes"] / (pool_top["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"])
                               if pool_top else None),
+            hbm_side=hbm_side,
             breakdown=dict(rule_chain_ms=rules_ms, conv_nin_ms=conv_ms, conv_algorithmic_tflops=all_flops / (conv_ms * 1e-3) / 1e12,
                            multiply_adds_per_sample=all_flops / 2 / BATCH_PER_GPU,
                            layers=[dict(layer=d["layer"], kernel=d["kernel"], ms=round(d["ms"], 4), rows=d["rows"],
-                                        gflop=round(d["flops"] / 1e9, 3), mbytes=round(d["bytes"] / 1e6, 2)) for d in per_layer]),
+                                        gflop=round(d["flops"] / 1e9, 3), mbytes=round(d["bytes"] / 1e6, 2),
+                                        **({"pipe_frac": round(d["flops"] / (d["ms"] * 1e-3) / 1e12 * passes / peaks["tflops"], 3)} if d.get("K", 0) >= 128 and d.get("N", 0) >= 16 else {}))
+                                   for d in per_layer]),
         )
         print(json.dumps(line))
     if world > 1:

@@ -262,6 +262,12 @@ int scn_conv_pack_weights(const float *d_W, int K, int N, int precision, void *d
  * counterpart. */
 int scn_conv_tc_take_error(void);
 
+/* Device address of that code word on the current device (NULL if it cannot be resolved), for
+ * callers that would rather copy it with results they fetch anyway than wait in
+ * scn_conv_tc_take_error.  A non-zero word read this way stays set until
+ * scn_conv_tc_take_error or scn_classifier_result clears it.  No reference counterpart. */
+const int *scn_conv_tc_error_word(void);
+
 /* Replaces propForwardToMatrixMultiply alone (ConvolutionalLayer.cu:12-41): the
  * materialised gather, for callers that read ConvolutionalLayer's output themselves.
  * out[c*nIn + j] = in[rules[c]*nIn + j], zero where rules[c] < 0; count = rows_out*fs. */
@@ -297,6 +303,17 @@ int scn_terminal_pool_forward(const float *d_in, const int *d_rules, int batch, 
  * d_top[rows x nTop]. */
 int scn_top_indices(const float *d_probs, int rows, int nClasses, int nTop, int *d_top,
                     scn_stream_t stream);
+
+/* The same device half of SoftmaxClassifier (SoftmaxClassifier.cu:31-41: the copy of the
+ * probabilities to the host and vectorTopIndices per row) with everything the host reads back
+ * laid out as ONE block, so that one device-to-host copy fetches it:
+ *   float probs[rows * nClasses]; int top[rows * nTop]; int tc_error;
+ * tc_error is the code word of scn_conv_tc_take_error, taken (read and cleared) by this
+ * kernel: non-zero means a tensor-core kernel before it gave up a wait and the probabilities
+ * are not to be trusted.  scn_classifier_result_bytes gives the block's size. */
+size_t scn_classifier_result_bytes(int rows, int nClasses, int nTop);
+int scn_classifier_result(const float *d_probs, int rows, int nClasses, int nTop, void *d_block,
+                          scn_stream_t stream);
 
 #ifdef __cplusplus
 }

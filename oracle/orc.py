@@ -2,7 +2,9 @@
 
 `Oracle` wraps oracle/_build/libscn_oracle.so (the CPU restatement, scn_oracle.cpp) and
 `Reference` wraps oracle/_ref/libscn_ref.so (the reference's own Regions.cu compiled
-unchanged, see the Makefile).  Only tests/, the smoke check and the benchmark's CPU-baseline
+unchanged, see the Makefile) and `ReferenceGPU` wraps oracle/_ref_gpu/libscn_ref_gpu.so (the
+reference's own network classes and CUDA kernels compiled unchanged for the GPU; it needs a
+CUDA device and is used by GPU tests only).  Only tests/, the smoke check and the benchmark's CPU-baseline
 legs import this module; the product package never does.
 """
 import ctypes
@@ -14,6 +16,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "_build", "libscn_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libscn_ref.so")
+REF_GPU_SO = os.path.join(HERE, "_ref_gpu", "libscn_ref_gpu.so")
 
 c_int, c_ll, c_f, c_p, c_d = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p, ctypes.c_double
 
@@ -25,8 +28,9 @@ L_CONV, L_CONV_TRI, L_NIN, L_MAXPOOL, L_MAXPOOL_TRI, L_TERMINAL = range(6)
 FMP_PO, FMP_PD, FMP_RO, FMP_RD = range(4)
 
 
-# where the reference checkout lies on the machine that builds oracle/_ref (the Makefile's REF default)
-REF_DIR = os.environ.get("SCN_REFERENCE_DIR", "/root/reference/SparseConvNet")
+# where the reference checkout lies on the machine that builds oracle/_ref and oracle/_ref_gpu: named by
+# SCN_REFERENCE_DIR, else looked for beside this repository
+REF_DIR = os.environ.get("SCN_REFERENCE_DIR") or os.path.normpath(os.path.join(HERE, "..", "..", "reference", "SparseConvNet"))
 
 
 def build(force=False):
@@ -37,6 +41,9 @@ def build(force=False):
     if os.path.isdir(REF_DIR) and (force or not os.path.exists(REF_SO) or os.path.getmtime(REF_SO) < os.path.getmtime(
             os.path.join(HERE, "ref_wrap.cpp"))):
         subprocess.check_call(["make", "-C", HERE, "_ref", "REF=" + REF_DIR], stdout=subprocess.DEVNULL)
+    if os.path.isdir(REF_DIR) and (force or not os.path.exists(REF_GPU_SO) or os.path.getmtime(REF_GPU_SO) < os.path.getmtime(
+            os.path.join(HERE, "ref_gpu_wrap.cu"))):
+        subprocess.check_call(["make", "-C", HERE, "_ref_gpu", "REF=" + REF_DIR], stdout=subprocess.DEVNULL)
 
 
 def _p(a):
@@ -116,6 +123,119 @@ class Reference(_RulesLib):
         f.restype, f.argtypes = c_p, [c_int] * 5 + [ctypes.c_uint, c_int] + [c_p] * 5
         h = f(kind, dim, nIn, nOut, poolSize, seed, B, _p(keys), _p(rows), _p(off), _p(bg), _p(ticks))
         return self._fetch(h, B), ticks
+
+
+class ReferenceGPU:
+    """The reference's own SparseConvNetCUDA (builders, BatchProducer, layer classes, CUDA kernels, cuBLAS
+    SGEMM) on the current CUDA device, one batch at a time.  Mirrors OracleNet's builder calls."""
+
+    def __init__(self, dim, nInputFeatures, nClasses, nTop=1, lattice=0):
+        self.L = L = ctypes.CDLL(REF_GPU_SO)
+        L.refgpu_create.restype, L.refgpu_create.argtypes = c_p, [c_int] * 5
+        L.refgpu_destroy.argtypes = [c_p]
+        L.refgpu_addLeNetLayerMP.argtypes = [c_p] + [c_int] * 6 + [c_f, c_int]
+        L.refgpu_addTerminalPoolingLayer.argtypes = [c_p, c_int, c_int]
+        L.refgpu_addSoftmaxLayer.argtypes = [c_p]
+        L.refgpu_n_layers.restype, L.refgpu_n_layers.argtypes = c_int, [c_p]
+        L.refgpu_input_spatial_size.restype, L.refgpu_input_spatial_size.argtypes = c_int, [c_p]
+        L.refgpu_layer_info.argtypes = [c_p, c_int, c_p, c_p]
+        L.refgpu_load_weights.argtypes = [c_p, ctypes.c_char_p, c_int]
+        L.refgpu_save_weights.argtypes = [c_p, ctypes.c_char_p, c_int]
+        L.refgpu_forward.restype, L.refgpu_forward.argtypes = c_int, [c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_f, c_f]
+        L.refgpu_multiply_adds.restype = c_d
+        L.refgpu_last_cuda_error.restype = c_int
+        L.refgpu_iface_sizes.argtypes = [c_p, c_int, c_p]
+        L.refgpu_iface_fetch.argtypes = [c_p, c_int] + [c_p] * 6
+        L.refgpu_results.argtypes = [c_p] * 4
+        L.refgpu_layer_weights.argtypes = [c_p, c_int, c_p, c_p, c_p]
+        self.dim, self.nIn, self.nClasses, self.nTop, self.lattice = dim, nInputFeatures, nClasses, nTop, lattice
+        self.h = L.refgpu_create(dim, nInputFeatures, nClasses, nTop, lattice)
+
+    @staticmethod
+    def available():
+        return os.path.exists(REF_GPU_SO)
+
+    def __del__(self):
+        try:
+            self.L.refgpu_destroy(self.h)
+        except Exception:
+            pass
+
+    def addLeNetLayerMP(self, nFeatures, fs, fstride, ps, pstride, act=RELU, dropout=0.0, minActive=1):
+        self.L.refgpu_addLeNetLayerMP(self.h, nFeatures, fs, fstride, ps, pstride, act, dropout, minActive)
+
+    def addTerminalPoolingLayer(self, poolSize, S=None):
+        if S is None:  # the facades pass ipow / triangleSize (SparseConvNet.cu:56-58, 123-126)
+            S = poolSize ** self.dim
+            if self.lattice == 1:
+                S = 1
+                for k in range(self.dim):  # binomial(poolSize + dim - 1, dim)
+                    S = S * (poolSize + k) // (k + 1)
+        self.L.refgpu_addTerminalPoolingLayer(self.h, poolSize, S)
+
+    def addSoftmaxLayer(self):
+        self.L.refgpu_addSoftmaxLayer(self.h)
+
+    @property
+    def inputSpatialSize(self):
+        return self.L.refgpu_input_spatial_size(self.h)
+
+    def layers(self):
+        """Learnt-layer facts only: dict(learnt, nIn, nOut, act, dropout) per layer."""
+        out = []
+        for i in range(self.L.refgpu_n_layers(self.h)):
+            info = np.zeros(5, np.int32)
+            d = c_f()
+            self.L.refgpu_layer_info(self.h, i, _p(info), ctypes.byref(d))
+            out.append(dict(learnt=bool(info[0]), nIn=int(info[1]), nOut=int(info[2]), act=int(info[3]), dropout=float(d.value)))
+        return out
+
+    def load_weights(self, base, epoch):
+        self.L.refgpu_load_weights(self.h, base.encode(), epoch)
+
+    def save_weights(self, base, epoch):
+        self.L.refgpu_save_weights(self.h, base.encode(), epoch)
+
+    def forward(self, keys, off, features, labels=None, batch_type=2, learning_rate=0.0, momentum=0.0):
+        """One batch through BatchProducer + processBatch.  batch_type 0 TRAINBATCH (also runs backwards and the SGD
+        update), 1 TESTBATCH, 2 UNLABELEDBATCH.  -> (probabilities, predictions, dict(nll, mistakes, multiply_adds))."""
+        keys = np.ascontiguousarray(keys, np.int64)
+        off = np.ascontiguousarray(off, np.int32)
+        features = np.ascontiguousarray(features, np.float32)
+        labels = None if labels is None else np.ascontiguousarray(labels, np.int32)
+        B = len(off) - 1
+        n = self.L.refgpu_forward(self.h, B, _p(keys), _p(off), _p(features), _p(labels), batch_type, learning_rate, momentum)
+        err = self.L.refgpu_last_cuda_error()
+        if n != B or err != 0:
+            raise RuntimeError("reference forward failed (processed %d of %d samples, CUDA error %d)" % (n, B, err))
+        probs = np.zeros((B, self.nClasses), np.float32)
+        pred = np.zeros((B, self.nTop), np.int32)
+        stats = np.zeros(2, np.float64)
+        self.L.refgpu_results(self.h, _p(probs), _p(pred), _p(stats))
+        return probs, pred, dict(nll=float(stats[0]), mistakes=int(stats[1]), multiply_adds=float(self.L.refgpu_multiply_adds()))
+
+    def iface(self, i):
+        """Interface i of the last forward: 0 is the input, i+1 layer i's output."""
+        s = np.zeros(8, np.int64)
+        self.L.refgpu_iface_sizes(self.h, i, _p(s))
+        rows, nF, sp, nr, nfp, nfeat, ndf, nch = (int(v) for v in s)
+        feat, dfeat = np.zeros(nfeat, np.float32), np.zeros(ndf, np.float32)
+        ch, rules = np.zeros(nch, np.int32), np.zeros(nr, np.int32)
+        rk = np.zeros(rows, np.int64)
+        self.L.refgpu_iface_fetch(self.h, i, _p(feat), _p(dfeat), _p(ch), _p(rules), _p(rk), None)
+        w = nfp if nfp else nF
+        return dict(nSpatialSites=rows, nFeatures=nF, spatialSize=sp, featuresPresent=nfp,
+                    features=feat.reshape(-1, w) if nfeat == rows * w else feat,
+                    dfeatures=dfeat.reshape(-1, w) if ndf == rows * w else dfeat,
+                    choices=ch, rules=rules, row_keys=rk)
+
+    def layer_weights(self, i):
+        info = self.layers()[i]
+        W = np.zeros((info["nIn"], info["nOut"]), np.float32)
+        B = np.zeros(info["nOut"], np.float32)
+        pr = np.zeros(info["nOut"], np.float32)
+        self.L.refgpu_layer_weights(self.h, i, _p(W), _p(B), _p(pr))
+        return W, B, (pr if info["act"] == PRELU else None)
 
 
 class Oracle(_RulesLib):
@@ -281,7 +401,8 @@ class OracleNet:
             raise IOError("cannot read %s (%d)" % (path, rc))
 
     def forward(self, keys, off, features, threads=1, accum64=False, keep=False):
-        """keys[row] (int64, -1 = background row), off[batch+1], features [rows x nIn]."""
+        """keys[row] (int64, -1 = background row), off[batch+1], features [rows x nIn].  keep retains every
+        interface for iface(); with threads > 1 the batch is processed in that many sample chunks."""
         keys = np.ascontiguousarray(keys, np.int64)
         off = np.ascontiguousarray(off, np.int32)
         features = np.ascontiguousarray(features, np.float32)

@@ -547,6 +547,52 @@ static void forwardChunk(const Net &net, int batch, const int64_t *keys, const i
   }
 }
 
+// Join the interfaces of consecutive sample chunks (each numbered from row 0) into those of the whole
+// batch.  Rule cells name rows of the interface in front, choices flat indices row*C + channel into its
+// features; terminal-pooling rule rows are re-padded to the widest chunk's width, which is the whole
+// batch's (the maximum of the per-sample site counts).
+static std::vector<Iface> joinChunks(const Net &net, std::vector<std::vector<Iface>> &chunks) {
+  const size_t nI = net.layers.size() + 1;
+  std::vector<Iface> all(nI);
+  std::vector<std::vector<long long>> rowsOf(chunks.size(), std::vector<long long>(nI, 0));
+  for (size_t t = 0; t < chunks.size(); ++t)
+    for (size_t i = 0; i < nI && !chunks[t].empty(); ++i) rowsOf[t][i] = chunks[t][i].nSpatialSites;
+  for (size_t i = 0; i < nI; ++i) {
+    const int type = i ? net.layers[i - 1].type : -1;
+    int width = 0; // terminal pooling: cells per rule row of the whole batch
+    if (type == L_TERMINAL)
+      for (auto &c : chunks) if (!c.empty() && c[i].nSpatialSites) width = std::max(width, (int)(c[i].rules.size() / c[i].nSpatialSites));
+    Iface &A = all[i];
+    std::vector<long long> inBase(chunks.size(), 0);
+    long long rowsIn = 0, rowsOut = 0;
+    for (size_t t = 0; t < chunks.size(); ++t) { // rows in front of chunk t in the interface that feeds this one
+      inBase[t] = rowsIn;
+      if (i) rowsIn += rowsOf[t][i - 1];
+    }
+    for (size_t t = 0; t < chunks.size(); ++t) {
+      if (chunks[t].empty()) continue;
+      Iface &C = chunks[t][i];
+      A.nFeatures = C.nFeatures; A.spatialSize = C.spatialSize;
+      for (Grid g : C.grids) {
+        for (auto &sr : g.sites) sr.second += (int)rowsOut;
+        if (g.bg >= 0) g.bg += (int)rowsOut;
+        A.grids.push_back(std::move(g));
+      }
+      const int w = (type == L_TERMINAL && C.nSpatialSites) ? (int)(C.rules.size() / C.nSpatialSites) : 0;
+      for (size_t k = 0; k < C.rules.size(); ++k) {
+        A.rules.push_back(C.rules[k] >= 0 ? C.rules[k] + (int)inBase[t] : C.rules[k]);
+        if (w && (int)(k % w) == w - 1) A.rules.insert(A.rules.end(), width - w, -1);
+      }
+      for (int c : C.choices) A.choices.push_back(c >= 0 ? c + (int)(inBase[t] * C.nFeatures) : c);
+      A.features.insert(A.features.end(), C.features.begin(), C.features.end());
+      rowsOut += C.nSpatialSites;
+      C = Iface();
+    }
+    A.nSpatialSites = (int)rowsOut;
+  }
+  return all;
+}
+
 } // namespace orc
 
 using namespace orc;
@@ -700,13 +746,14 @@ int orc_net_load_weights(void *h, const char *path) {
 
 // Full forward.  probs [batch x nClasses], predictions [batch x nTop] (SoftmaxClassifier.cu:36-41).
 // nThreads > 1 splits the batch into contiguous chunks (samples are independent); keep=1
-// (single chunk) retains every interface for layer-by-layer comparison.
+// retains every interface for layer-by-layer comparison (chunks are joined into the whole
+// batch's numbering: row ids, rule cells and pooling choices shifted by the rows in front).
 // times[0] = rule construction seconds (summed over chunks / nThreads), times[1] = wall seconds.
 void orc_net_forward(void *h, int batch, const int64_t *keys, const int *off, const float *features,
                      int nThreads, int accum64, int keep, float *probs, int *predictions, double *times) {
   Net *net = (Net *)h;
   auto t0 = std::chrono::steady_clock::now();
-  if (keep || nThreads < 1) nThreads = 1;
+  if (nThreads < 1) nThreads = 1;
   nThreads = std::min(nThreads, std::max(1, batch));
   std::vector<double> tr(nThreads, 0.0);
   std::vector<std::vector<Iface>> ifs(nThreads);
@@ -733,7 +780,9 @@ void orc_net_forward(void *h, int batch, const int64_t *keys, const int *off, co
   };
   if (nThreads == 1) work(0);
   else { std::vector<std::thread> th; for (int t = 0; t < nThreads; ++t) th.emplace_back(work, t); for (auto &x : th) x.join(); }
-  if (keep) net->kept = std::move(ifs[0]); else net->kept.clear();
+  if (keep && nThreads == 1) net->kept = std::move(ifs[0]);
+  else if (keep) net->kept = joinChunks(*net, ifs);
+  else net->kept.clear();
   if (times) {
     double s = 0; for (double v : tr) s += v;
     times[0] = s / nThreads;

@@ -21,7 +21,7 @@ EXPORTS = [
     "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
     "scn_rules_workspace_bytes", "scn_rules_build", "scn_fmp_rules_workspace_bytes", "scn_fmp_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_terminal_rules_workspace_bytes",
     "scn_terminal_rules_build", "scn_conv_auto_precision", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_forward_dyn", "scn_conv_nin_maxpool_forward", "scn_conv_nin_nin_forward", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
-    "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_gather_forward", "scn_maxpool_forward",
+    "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_conv_tc_error_word", "scn_classifier_result_bytes", "scn_classifier_result", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
 ]
 
@@ -55,6 +55,8 @@ def lib():
         L.scn_last_error.restype = ctypes.c_char_p
         L.scn_device_supported.restype = c_int
         L.scn_kernel_launch_count.restype = c_ll
+        L.scn_conv_tc_error_word.restype = c_p
+        L.scn_classifier_result_bytes.restype = c_sz
         L.scn_regions_cells.restype, L.scn_regions_cells.argtypes = c_int, [c_p]
         L.scn_rules_workspace_bytes.restype = c_sz
         L.scn_rules_workspace_bytes.argtypes = [c_p, c_int, c_int]
@@ -242,6 +244,20 @@ def activation_forward(x, act, prelu=None):
     out = torch.empty_like(x)
     check(lib().scn_activation_forward(_ptr(_f32(x)), _ptr(out), rows, N, act, _ptr(prelu), _stream()))
     return out
+
+
+def classifier_result(probs, nTop):
+    """scn_classifier_result -> (probabilities, top, tc_error) unpacked from the one block the kernel writes."""
+    L = lib()
+    rows, nClasses = probs.shape
+    L.scn_classifier_result_bytes.restype = c_sz
+    nbytes = L.scn_classifier_result_bytes(rows, nClasses, nTop)
+    block = torch.empty(nbytes // 4, dtype=torch.int32, device=probs.device)
+    check(L.scn_classifier_result(_ptr(_f32(probs)), rows, nClasses, nTop, _ptr(block), _stream()))
+    host = block.cpu()
+    p = host[: rows * nClasses].view(torch.float32).reshape(rows, nClasses)
+    t = host[rows * nClasses: rows * nClasses + rows * nTop].reshape(rows, nTop)
+    return p, t, int(host[-1])
 
 
 def kernel_launch_count():

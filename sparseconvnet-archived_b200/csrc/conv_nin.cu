@@ -502,3 +502,4 @@ extern "C" int scn_conv_pack_weights(const float *d_W, int K, int N, int precisi
 }
 
 extern "C" int scn_conv_tc_take_error(void) { return tc_take_error(); }
+extern "C" const int *scn_conv_tc_error_word(void) { return tc_error_word(); }

@@ -1425,6 +1425,18 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   return SCN_OK;
 }
 
+int *tc_error_word() {
+  static int *cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cached[dev]) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_tc_error) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    cached[dev] = (int *)p;
+  }
+  return cached[dev];
+}
+
 int tc_take_error() {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;

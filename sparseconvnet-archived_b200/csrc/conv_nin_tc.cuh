@@ -29,4 +29,7 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
 // Error code a bounded wait of the kernel recorded since the last call (0 = none); waits for
 // the device and clears it.  1 gather/empty, 2 epilogue/accumulator, 3 weight copy/empty, 4 MMA/full.
 int tc_take_error();
+// Device address of that error word on the current device (nullptr if it cannot be resolved): kernels that
+// hand results to the host read and clear it there, so that the host sees it in a copy it makes anyway.
+int *tc_error_word();
 } // namespace scn

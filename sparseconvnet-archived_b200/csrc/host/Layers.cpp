@@ -232,7 +232,7 @@ long long FractionalMaxPoolingLayerBase::enqueueRules(SpatiallySparseBatch &batc
   scnSafeCall(scn_fmp_rules_build(dimension, inSpatialSize, outSpatialSize, poolSize, overlapping() ? 1 : 0, batch.batchSize, ticks.dPtr(),
                                   g->siteKeys.dPtr(), g->sampleOffsets.dPtr(), g->backgroundRows.dPtr(), (int)rowsInBound,
                                   output.siteKeys.dPtr(), output.sampleOffsets.dPtr(), output.backgroundRows.dPtr(), output.rules.dPtr(),
-                                  (int)bound, d_result, rulechain::workspace(wsBytes), wsBytes, memStream.stream));
+                                  (int)bound, d_result, memStream.deviceScratch(wsBytes), wsBytes, memStream.stream));
   return bound;
 }
 void FractionalMaxPoolingLayerBase::finishRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
@@ -339,7 +339,7 @@ long long TerminalPoolingLayer::enqueueRules(SpatiallySparseBatch &batch, Spatia
   output.backgroundRows.resize(batch.batchSize);
   output.rules.resize((int)(width * batch.batchSize));
   size_t wsBytes = scn_terminal_rules_workspace_bytes(dimension, inSpatialSize, batch.batchSize, (int)rowsInBound);
-  void *ws = rulechain::workspace(wsBytes);
+  void *ws = memStream.deviceScratch(wsBytes);
   scnSafeCall(scn_terminal_rules_build(dimension, inSpatialSize, batch.batchSize, g->siteKeys.dPtr(), g->sampleOffsets.dPtr(),
                                        g->backgroundRows.dPtr(), (int)rowsInBound, (int)width, output.siteKeys.dPtr(),
                                        output.sampleOffsets.dPtr(), output.backgroundRows.dPtr(), output.rules.dPtr(), d_result, ws,
@@ -361,11 +361,11 @@ void TerminalPoolingLayer::finishRules(SpatiallySparseBatch &batch, SpatiallySpa
     SpatiallySparseBatchInterface *g = input.gridOwner;
     output.rules.resize(exact * batch.batchSize);
     size_t wsBytes = scn_terminal_rules_workspace_bytes(dimension, inSpatialSize, batch.batchSize, input.nSpatialSites);
-    void *ws = rulechain::workspace(wsBytes);
+    void *ws = memStream.deviceScratch(wsBytes);
     scnSafeCall(scn_terminal_rules_build(dimension, inSpatialSize, batch.batchSize, g->siteKeys.dPtr(), g->sampleOffsets.dPtr(),
                                          g->backgroundRows.dPtr(), input.nSpatialSites, exact, output.siteKeys.dPtr(),
                                          output.sampleOffsets.dPtr(), output.backgroundRows.dPtr(), output.rules.dPtr(),
-                                         rulechain::scratchResult(), ws, wsBytes, memStream.stream));
+                                         memStream.deviceResult(), ws, wsBytes, memStream.stream));
     widthBuilt = exact;
   }
 }
@@ -630,20 +630,32 @@ void applySigmoid(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInte
                                      output.featuresPresent.size(), (int)fn, nullptr, memStream.stream));
 }
 
+// The classifier's device half and the one copy that brings its results to the host: probabilities, the nTop classes
+// per row and the error word of the tensor-core kernels travel as one block (scn_classifier_result).  Returns the
+// block in the stream's page-locked staging memory; throws if a tensor-core kernel gave up a wait.
+const char *fetchClassifierResult(SpatiallySparseBatchInterface &input, int n, int nTop, cudaMemStream &memStream) {
+  const int C = input.nFeatures;
+  static thread_local vectorCUDA<int> block;
+  const size_t bytes = scn_classifier_result_bytes(n, C, nTop);
+  block.resize((int)(bytes / sizeof(int)));
+  scnSafeCall(scn_classifier_result(input.sub->features.dPtr(), n, C, nTop, block.dPtr(), memStream.stream));
+  char *stage = (char *)memStream.staging(bytes);
+  cudaSafeCall(cudaMemcpyAsync(stage, block.dPtr(), bytes, cudaMemcpyDeviceToHost, memStream.stream));
+  cudaSafeCall(cudaStreamSynchronize(memStream.stream));
+  const int tcError = *(const int *)(stage + bytes - sizeof(int));
+  if (tcError) throw ScnException("a tensor-core kernel gave up a time-limited wait (code " + std::to_string(tcError) +
+                                  ": 1 gather, 2 epilogue, 3 weight copy, 4 MMA); this batch's features are not valid");
+  return stage;
+}
+
 // SoftmaxClassifier.cu:16-58 without the training branch: probabilities and the nTop
 // predictions come back in one staged copy; NLL and mistakes are scored on the host.
 void SoftmaxClassifier(SpatiallySparseBatchInterface &input, SpatiallySparseBatch &batch, int nTop, cudaMemStream &memStream) {
   requireInference(batch);
   if (batch.batchSize != input.nSpatialSites) throw ScnException("SoftmaxClassifier: the top layer must hold one row per sample");
   const int n = batch.batchSize, C = input.nFeatures;
-  static thread_local vectorCUDA<int> top;
-  top.resize(n * nTop);
-  scnSafeCall(scn_top_indices(input.sub->features.dPtr(), n, C, nTop, top.dPtr(), memStream.stream));
-  const size_t pb = sizeof(float) * (size_t)n * C, tb = sizeof(int) * (size_t)n * nTop;
-  char *stage = (char *)memStream.staging(pb + tb);
-  cudaSafeCall(cudaMemcpyAsync(stage, input.sub->features.dPtr(), pb, cudaMemcpyDeviceToHost, memStream.stream));
-  cudaSafeCall(cudaMemcpyAsync(stage + pb, top.dPtr(), tb, cudaMemcpyDeviceToHost, memStream.stream));
-  cudaSafeCall(cudaStreamSynchronize(memStream.stream));
+  const size_t pb = sizeof(float) * (size_t)n * C;
+  const char *stage = fetchClassifierResult(input, n, nTop, memStream);
   const float *probs = (const float *)stage;
   const int *pred = (const int *)(stage + pb);
   for (int i = 0; i < n; ++i) { // refill the vectors that reset() set aside, where there are any

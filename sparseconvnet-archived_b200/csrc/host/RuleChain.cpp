@@ -1,37 +1,7 @@
 #include "RuleChain.h"
 #include <climits>
-#include <mutex>
 
 namespace rulechain {
-namespace {
-struct PerDevice { void *ws = nullptr; size_t bytes = 0; int *res = nullptr; };
-PerDevice g_dev[64];
-std::mutex g_mu;
-PerDevice &cur() {
-  int d = 0;
-  cudaSafeCall(cudaGetDevice(&d));
-  return g_dev[d & 63];
-}
-} // namespace
-
-void *workspace(size_t bytes) {
-  std::lock_guard<std::mutex> lk(g_mu);
-  PerDevice &p = cur();
-  if (bytes > p.bytes) {
-    if (p.ws) { cudaSafeCall(cudaDeviceSynchronize()); cudaSafeCall(cudaFree(p.ws)); p.ws = nullptr; p.bytes = 0; }
-    size_t want = bytes + bytes / 4;
-    cudaSafeCall(cudaMalloc(&p.ws, want));
-    p.bytes = want;
-  }
-  return p.ws;
-}
-int *scratchResult() {
-  std::lock_guard<std::mutex> lk(g_mu);
-  PerDevice &p = cur();
-  if (!p.res) cudaSafeCall(cudaMalloc((void **)&p.res, 4 * sizeof(int)));
-  return p.res;
-}
-
 namespace { thread_local std::vector<DeferredBuild> *g_deferred = nullptr; }
 void beginDeferred(std::vector<DeferredBuild> *list) { g_deferred = list; }
 void endDeferred() { g_deferred = nullptr; }
@@ -44,14 +14,14 @@ bool runDeferred(std::vector<DeferredBuild> &list, int batch, int maxRowsPerSamp
   if (rowsHint > 0 && !scn_rules_chain_supported(layers.data(), n, batch, maxRowsPerSample, rowsHint)) rowsHint = 0;
   if (scn_rules_chain_supported(layers.data(), n, batch, maxRowsPerSample, rowsHint)) {
     size_t bytes = scn_rules_chain_workspace_bytes(n, batch);
-    void *ws = workspace(bytes);
+    void *ws = ms.deviceScratch(bytes);
     scnSafeCall(scn_rules_chain_build(layers.data(), n, batch, list[0].inKeys, list[0].inOff, list[0].inBg, maxRowsPerSample,
                                       rowsHint, ws, bytes, ms.stream));
     return rowsHint > 0;
   }
   for (auto &d : list) {
     size_t bytes = scn_rules_workspace_bytes(&d.R, batch, d.rowsInBound);
-    void *ws = workspace(bytes);
+    void *ws = ms.deviceScratch(bytes);
     scnSafeCall(scn_rules_build(&d.R, batch, d.inKeys, d.inOff, d.inBg, d.rowsInBound, d.out.d_out_keys, d.out.d_out_off,
                                 d.out.d_out_bg, d.out.d_rules, d.out.rows_out_capacity, d.out.d_result, ws, bytes, ms.stream));
   }
@@ -87,7 +57,7 @@ long long enqueueRegions(const scn_regions_t &R, SpatiallySparseBatch &batch, Sp
     return bound;
   }
   size_t wsBytes = scn_rules_workspace_bytes(&R, batch.batchSize, (int)rowsInBound);
-  void *ws = workspace(wsBytes);
+  void *ws = ms.deviceScratch(wsBytes);
   scnSafeCall(scn_rules_build(&R, batch.batchSize, g->siteKeys.dPtr(), g->sampleOffsets.dPtr(), g->backgroundRows.dPtr(),
                               (int)rowsInBound, output.siteKeys.dPtr(), output.sampleOffsets.dPtr(), output.backgroundRows.dPtr(),
                               output.rules.dPtr(), (int)bound, d_result, ws, wsBytes, ms.stream));
@@ -106,7 +76,7 @@ void finishRegions(const scn_regions_t &R, SpatiallySparseBatchInterface &output
 
 void preprocessNow(SpatiallySparseLayer &layer, SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
                    SpatiallySparseBatchInterface &output) {
-  int *d_res = scratchResult();
+  int *d_res = layer.memStream.deviceResult();
   layer.enqueueRules(batch, input, output, input.nSpatialSites, d_res);
   int h[4] = {0, 0, 0, 0};
   if (layer.changesGeometry) {

@@ -4,11 +4,7 @@
 #include "SpatiallySparseLayer.h"
 
 namespace rulechain {
-// Device scratch shared by all rule builds of a stream (grown on demand, never shrunk).
-void *workspace(size_t bytes);
-// A small device record array for callers that build one layer at a time.
-int *scratchResult();
-
+// (The device scratch of the rule builds belongs to the network's cudaMemStream: cudaMemStream::deviceScratch.)
 // While a list is installed (this thread), enqueueRegions() sizes the output buffers but records
 // the build instead of launching it, so that the caller can hand the whole chain to one kernel.
 struct DeferredBuild {

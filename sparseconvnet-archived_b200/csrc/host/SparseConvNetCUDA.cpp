@@ -194,7 +194,11 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
     cudaSafeCall(cudaStreamWaitEvent(memStream.stream, inputReady, 0));
     inputReady = nullptr;
   }
-  int *h = (int *)memStream.staging(sizeof(int) * 4 * nL);
+  int *h = (int *)memStream.staging(sizeof(int) * (4 * nL + 1));
+  // The error word of the tensor-core kernels rides along with the counts: set by an earlier batch's kernels whose
+  // results were never read through SoftmaxClassifier (the device-resident entry point), it is reported here.
+  const int *tcWord = scn_conv_tc_error_word();
+  h[4 * nL] = 0;
   bool countsRead = false;
   if (earlyFirstLayer && !timing && defer && nL >= 2) {
     ConvolutionalLayer *conv = dynamic_cast<ConvolutionalLayer *>(layers[0]);
@@ -216,6 +220,7 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
         // the counts come back on their own stream, behind the rule chain only, while the first layer runs
         cudaSafeCall(cudaStreamWaitEvent(countStream, chainDone, 0));
         cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, countStream));
+        if (tcWord) cudaSafeCall(cudaMemcpyAsync(h + 4 * nL, tcWord, sizeof(int), cudaMemcpyDeviceToHost, countStream));
         cudaSafeCall(cudaStreamSynchronize(countStream));
         countsRead = true;
       }
@@ -223,7 +228,14 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
   }
   if (!countsRead) {
     cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, memStream.stream));
+    if (tcWord) cudaSafeCall(cudaMemcpyAsync(h + 4 * nL, tcWord, sizeof(int), cudaMemcpyDeviceToHost, memStream.stream));
     cudaSafeCall(cudaStreamSynchronize(memStream.stream)); // the one host wait of the rule chain
+  }
+  if (h[4 * nL]) {
+    const int code = h[4 * nL];
+    scn_conv_tc_take_error(); // clear it: the kernels launched from here on wait with their full time limit again
+    throw ScnException("a tensor-core kernel of an earlier batch gave up a time-limited wait (code " + std::to_string(code) +
+                       "): that batch's results are not valid");
   }
   std::vector<int> counts(h, h + 4 * nL); // staging is reused below
   if (hinted) { // a sample outgrew the shared-memory hint learnt from earlier batches: rebuild for the worst case

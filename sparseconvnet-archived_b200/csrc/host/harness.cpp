@@ -277,13 +277,15 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *
     cnn.earlyFirstLayer = true; // one batch in flight here: the first layer may start behind the rule chain
     cnn.preprocessBatchOnDevice(b); // waits once, after the key upload and the rule chain
     cnn.earlyFirstLayer = false;
-    std::ofstream nof, nog;
-    cnn.processBatch(b, 0, 0, nof, nog);
+    // processBatch without the per-sample vectors of SpatiallySparseBatch: the results go straight to the caller's arrays
+    cnn.forwardLayers(b);
     net->last = &b;
-    for (int i = 0; i < batch; ++i) {
-      if (probs) std::memcpy(probs + (size_t)i * cnn.nClasses, b.probabilities[i].data(), sizeof(float) * cnn.nClasses);
-      if (predictions) std::memcpy(predictions + (size_t)i * cnn.nTop, b.predictions[i].data(), sizeof(int) * cnn.nTop);
-    }
+    SpatiallySparseBatchInterface &topI = b.interfaces.back();
+    if (batch != topI.nSpatialSites) throw ScnException("the top layer must hold one row per sample");
+    const char *block = fetchClassifierResult(topI, batch, cnn.nTop, cnn.memStream);
+    const size_t pb = sizeof(float) * (size_t)batch * cnn.nClasses;
+    if (probs) std::memcpy(probs, block, pb);
+    if (predictions) std::memcpy(predictions, block + pb, sizeof(int) * (size_t)batch * cnn.nTop);
   });
 }
 

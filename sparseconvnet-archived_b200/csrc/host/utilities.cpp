@@ -78,8 +78,24 @@ cudaMemStream::cudaMemStream(cudaStream_t external)
   cudaSafeCall(cudaMallocHost(&pinnedMemory, pinnedMemorySize));
 }
 cudaMemStream::~cudaMemStream() {
+  if (scratch || resultWords) cudaStreamSynchronize(stream);
+  if (scratch) cudaFree(scratch);
+  if (resultWords) cudaFree(resultWords);
   if (ownsStream && stream) cudaStreamDestroy(stream);
   if (pinnedMemory) cudaFreeHost(pinnedMemory);
+}
+void *cudaMemStream::deviceScratch(size_t bytes) {
+  if (bytes > scratchBytes) {
+    if (scratch) { cudaSafeCall(cudaStreamSynchronize(stream)); cudaSafeCall(cudaFree(scratch)); scratch = nullptr; scratchBytes = 0; }
+    const size_t want = bytes + bytes / 4;
+    cudaSafeCall(cudaMalloc(&scratch, want));
+    scratchBytes = want;
+  }
+  return scratch;
+}
+int *cudaMemStream::deviceResult() {
+  if (!resultWords) cudaSafeCall(cudaMalloc((void **)&resultWords, 4 * sizeof(int)));
+  return resultWords;
 }
 void *cudaMemStream::staging(size_t bytes) {
   if (bytes > (size_t)pinnedMemorySize) {

@@ -39,7 +39,9 @@ int initializeGPU(int pciBusID);
 
 // A stream plus a pinned staging buffer (utilities.h:105-112).  The buffer grows on demand.
 // With an external stream (the benchmark passes torch's current stream) the object does
-// not own it.
+// not own it.  It also owns the device scratch of this stream's rule builds (layer descriptors,
+// per-sample counts, bitmaps, prefix sums): one per network, like every other buffer of a
+// network, so that two networks on one device never share mutable state.
 class cudaMemStream {
 public:
   int pinnedMemorySize;
@@ -49,9 +51,14 @@ public:
   explicit cudaMemStream(cudaStream_t external);
   ~cudaMemStream();
   void *staging(size_t bytes); // pinned buffer of at least `bytes`
+  void *deviceScratch(size_t bytes); // device buffer of at least `bytes`; only work on `stream` may use it
+  int *deviceResult();               // four device ints for a rule build whose counts nobody reads
   cudaMemStream(const cudaMemStream &) = delete;
   cudaMemStream &operator=(const cudaMemStream &) = delete;
 
 private:
   bool ownsStream;
+  void *scratch = nullptr;
+  size_t scratchBytes = 0;
+  int *resultWords = nullptr;
 };

@@ -2,6 +2,7 @@
 // HBM-bound: each input element is read once per rule that names it, every output element
 // is written once, accesses are coalesced along the channel axis (float4 where C % 4 == 0).
 #include "scn_common.cuh"
+#include "conv_nin_tc.cuh"
 #include <type_traits>
 
 namespace scn {
@@ -127,6 +128,37 @@ __global__ void k_top_indices(const float *__restrict__ probs, int rows, int nCl
   }
 }
 
+// What the classifier's caller reads back, as one block: the probabilities, the nTop classes of every row and the
+// error word of the tensor-core kernels (taken: the word is cleared).  Same selection as k_top_indices.
+__global__ void k_classifier_result(const float *__restrict__ probs, int rows, int nClasses, int nTop, float *__restrict__ blockProbs,
+                                    int *__restrict__ blockTop, int *__restrict__ blockFlag, int *tcError) {
+  const int lane = threadIdx.x & 31;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *blockFlag = tcError ? atomicExch(tcError, 0) : 0;
+  for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += gridDim.x * (blockDim.x >> 5)) {
+    const float *v = probs + (long long)r * nClasses;
+    for (int i = lane; i < nClasses; i += 32) blockProbs[(long long)r * nClasses + i] = v[i];
+    float lastVal = 0.f;
+    int lastIdx = -1;
+    for (int t = 0; t < nTop; ++t) {
+      int best = -1;
+      float bv = 0.f;
+      for (int i = lane; i < nClasses; i += 32) {
+        const float x = v[i];
+        const bool eligible = (lastIdx < 0) || x < lastVal || (x == lastVal && i > lastIdx);
+        if (eligible && (best < 0 || x > bv)) { best = i; bv = x; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best, o);
+        if (oi >= 0 && (best < 0 || ov > bv || (ov == bv && oi < best))) { best = oi; bv = ov; }
+      }
+      if (lane == 0) blockTop[(long long)r * nTop + t] = best < 0 ? 0 : best;
+      lastVal = bv; lastIdx = best;
+    }
+  }
+}
+
 // Background row of each sample: the row whose key is negative (at most one per sample), -1 if
 // none.  One warp per sample.
 __global__ void k_background_rows(const int *__restrict__ keys, const int *__restrict__ off, int batch, int *__restrict__ bg) {
@@ -219,6 +251,23 @@ extern "C" int scn_gather_forward(const float *d_in, const int *d_rules, long lo
   if (!d_in || !d_rules || !d_out) return fail(SCN_ERR_INVALID, "null pointer");
   k_gather<<<grid_for(count * nIn, 256), 256, 0, (cudaStream_t)stream>>>(d_in, d_rules, count, nIn, d_out);
   SCN_LAUNCH_CHECK("k_gather");
+  return SCN_OK;
+}
+
+extern "C" size_t scn_classifier_result_bytes(int rows, int nClasses, int nTop) {
+  if (rows < 0 || nClasses < 1 || nTop < 1) return 0;
+  return sizeof(float) * (size_t)rows * nClasses + sizeof(int) * (size_t)rows * nTop + sizeof(int);
+}
+
+extern "C" int scn_classifier_result(const float *d_probs, int rows, int nClasses, int nTop, void *d_block, scn_stream_t stream) {
+  clear_error();
+  if (rows < 1 || nClasses < 1 || nTop < 1 || nTop > nClasses) return fail(SCN_ERR_INVALID, "need rows >= 1 and 1 <= nTop <= nClasses");
+  if (!d_probs || !d_block) return fail(SCN_ERR_INVALID, "null pointer");
+  float *bp = (float *)d_block;
+  int *bt = (int *)(bp + (size_t)rows * nClasses);
+  k_classifier_result<<<grid_for((long long)rows * 32, 128), 128, 0, (cudaStream_t)stream>>>(d_probs, rows, nClasses, nTop, bp, bt, bt + (size_t)rows * nTop,
+                                                                                             tc_error_word());
+  SCN_LAUNCH_CHECK("k_classifier_result");
   return SCN_OK;
 }
 

@@ -364,3 +364,17 @@ def test_conv_nin_then_small_nin(abi, oracle, rows_in, rows, fs, nIn, N, N2, act
     assert abi.conv_tc_take_error() == 0
     assert relerr(mid.cpu().numpy(), mid_ref) < RTOL_FP32
     assert relerr(out.cpu().numpy(), out_ref) < RTOL_FP32
+
+
+def test_classifier_result_block(abi, oracle):
+    """scn_classifier_result: the probabilities, the nTop classes of every row (vectorTopIndices order) and the
+    tensor-core error word as one block; the word is zero as long as no kernel gave up a wait."""
+    rng = np.random.default_rng(31)
+    for rows, n, k in ((256, 10, 1), (64, 101, 5), (3, 20, 3), (1, 2, 2)):
+        v = rng.random((rows, n)).astype(np.float32)
+        v[::3] = np.round(v[::3], 1)  # ties
+        p, t, flag = abi.classifier_result(torch.from_numpy(v).cuda(), k)
+        np.testing.assert_array_equal(p.numpy(), v)
+        np.testing.assert_array_equal(t.numpy(), np.stack([oracle.top_indices(row, k) for row in v]))
+        assert flag == 0
+    assert abi.lib().scn_conv_tc_error_word() != 0

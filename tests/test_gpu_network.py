@@ -103,12 +103,11 @@ def test_forward_layer_by_layer(scn, abi, nets, cfg, precision, fusion):
     gnet.set_pool_fusion(True)
 
 
-@pytest.mark.parametrize("cfg", [1, 3, 4])
-def test_pooling_choices_bit_exact_with_fp32_oracle(scn, abi, nets, cfg):
-    """poolingChoices equal the oracle's when both sides run the same fp32 arithmetic up to
-    ties: compare choices through the values they select (a tie between equal floats may pick
-    either index only if the features differ in the last bit, so check value equality at
-    the chosen index and exact index equality where the oracle's margin is clear)."""
+@pytest.mark.parametrize("cfg", [1, 2, 3, 4, 5])
+def test_pooling_choices_fp32_equal_up_to_near_ties(scn, abi, nets, cfg):
+    """Real-valued features: the fp32 kernels and the fp32 oracle add in different orders, so a choice may differ
+    where two candidates lie within rounding of each other, and only there (the bit-exact comparison, on data that
+    make the arithmetic exact, is test_gpu_benchmark_size.py::test_pooling_choices_bit_exact_on_integer_networks)."""
     gnet, onet = nets(cfg)
     gnet.set_precision(abi.PREC_FP32)
     keys, off, feats = scn.synth.CONFIGS[cfg]["gen"](BATCH[cfg])
