@@ -147,6 +147,32 @@ int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_layers, int bat
                           const int *d_in_off, const int *d_in_bg, int max_rows_per_sample, int rows_hint,
                           void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
 
+/* The same build for a caller that keeps the workspace to itself from one call to the next (a
+ * network that processes batch after batch).  In steady state the kernel is the only stream
+ * operation: layer descriptors stay on the device while they do not change, and every launch
+ * prepares the per-sample counters, the ticket and the result records of the launch AFTER
+ * it, which stream order puts behind it.  No reference counterpart.
+ *   st              host-side bookkeeping from scn_rules_chain_resident_create (no device memory);
+ *                   scn_rules_chain_resident_invalidate after anything else wrote the workspace
+ *   d_workspace     scn_rules_chain_resident_workspace_bytes(n_layers, batch) bytes that nothing
+ *                   else writes between calls
+ *   phase           0 or 1, alternating from call to call; the layers' d_result records belong
+ *                   to this phase
+ *   d_result_next   a block of n_result_next ints that holds every d_result record the NEXT
+ *                   call (other phase) will name, cleared by this launch; NULL if the next
+ *                   call is not known to be a resident one
+ *   d_in_bg         may be NULL: every sample's background row (the row with a negative key,
+ *                   -1 if none) is then found by the kernel and written to d_in_bg_out[batch]. */
+typedef struct scn_chain_resident scn_chain_resident_t;
+scn_chain_resident_t *scn_rules_chain_resident_create(void);
+void scn_rules_chain_resident_destroy(scn_chain_resident_t *st);
+void scn_rules_chain_resident_invalidate(scn_chain_resident_t *st);
+size_t scn_rules_chain_resident_workspace_bytes(int n_layers, int batch);
+int scn_rules_chain_build_resident(scn_chain_resident_t *st, const scn_chain_layer_t *layers, int n_layers, int batch,
+                                   const int *d_in_keys, const int *d_in_off, const int *d_in_bg, int *d_in_bg_out,
+                                   int max_rows_per_sample, int rows_hint, void *d_workspace, size_t workspace_bytes,
+                                   int phase, int *d_result_next, int n_result_next, scn_stream_t stream);
+
 /* scn_rules_build for callers that cannot allocate device memory (no counterpart in the
  * reference, whose rule construction runs on the host).  Hosts embedded in a framework that
  * owns the GPU's memory, code on a latency-critical path that must stay clear of cudaMalloc

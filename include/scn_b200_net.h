@@ -111,7 +111,7 @@ int scn_net_layer_times(scn_net_t *net, float *h_ms);
 int scn_net_process_dataset(scn_net_t *net, int nSamples, const int *h_keys, const int *h_off, const float *h_features,
                             const int *h_labels, int batchSize, float *errorRate, float *h_probs);
 
-/* utilities.cu:35-56, host version, for pinning against the oracle. */
+/* vectorTopIndices (utilities.cu:35-56), the host version SoftmaxClassifier-style callers use. */
 int scn_host_vectorTopIndices(const float *h_v, int n, int k, int *h_out);
 
 #ifdef __cplusplus

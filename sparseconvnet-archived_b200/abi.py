@@ -19,7 +19,7 @@ DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
 
 EXPORTS = [
     "scn_status_string", "scn_last_error", "scn_kernel_launch_count", "scn_device_supported", "scn_regions_cells",
-    "scn_rules_workspace_bytes", "scn_rules_build", "scn_fmp_rules_workspace_bytes", "scn_fmp_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_terminal_rules_workspace_bytes",
+    "scn_rules_workspace_bytes", "scn_rules_build", "scn_fmp_rules_workspace_bytes", "scn_fmp_rules_build", "scn_rules_static_scratch_bytes", "scn_rules_build_static", "scn_rules_chain_workspace_bytes", "scn_rules_chain_supported", "scn_rules_chain_build", "scn_rules_chain_resident_create", "scn_rules_chain_resident_destroy", "scn_rules_chain_resident_invalidate", "scn_rules_chain_resident_workspace_bytes", "scn_rules_chain_build_resident", "scn_terminal_rules_workspace_bytes",
     "scn_terminal_rules_build", "scn_conv_auto_precision", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_forward_dyn", "scn_conv_nin_maxpool_forward", "scn_conv_nin_nin_forward", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_conv_tc_error_word", "scn_classifier_result_bytes", "scn_classifier_result", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
@@ -321,6 +321,56 @@ def rules_chain_build(regions_list, keys, off, bg, max_rows_per_sample, capaciti
     for o in outs:
         o["workspace"] = ws
     return outs
+
+
+class ResidentChain:
+    """scn_rules_chain_build_resident: a chain of geometry layers whose device state stays with this object from call to
+    call, so that in steady state the kernel is the only stream operation.  Two sets of result records alternate; each
+    build() returns the per-layer output dicts of the set it used (valid until the call after next)."""
+
+    def __init__(self, regions_list, batch, capacities, device):
+        L = lib()
+        L.scn_rules_chain_resident_create.restype = c_p
+        L.scn_rules_chain_resident_workspace_bytes.restype = c_sz
+        self.L, self.n, self.batch = L, len(regions_list), batch
+        self.state = c_p(L.scn_rules_chain_resident_create())
+        self.results = torch.zeros((2, 4 * self.n), dtype=torch.int32, device=device)
+        self.arr, self.outs = [], []
+        for phase in range(2):
+            arr = (ChainLayer * self.n)()
+            outs = []
+            for i, (R, cap) in enumerate(zip(regions_list, capacities)):
+                sd = L.scn_regions_cells(ctypes.byref(R))
+                o = dict(out_keys=torch.empty(max(cap, 1), dtype=torch.int32, device=device),
+                         out_off=torch.empty(batch + 1, dtype=torch.int32, device=device),
+                         out_bg=torch.empty(batch, dtype=torch.int32, device=device),
+                         rules=torch.empty(max(cap, 1) * sd, dtype=torch.int32, device=device),
+                         result=self.results[phase, 4 * i: 4 * i + 4], sd=sd)
+                outs.append(o)
+                arr[i].regions = R
+                arr[i].d_out_keys, arr[i].d_out_off, arr[i].d_out_bg = o["out_keys"].data_ptr(), o["out_off"].data_ptr(), o["out_bg"].data_ptr()
+                arr[i].d_rules, arr[i].rows_out_capacity, arr[i].d_result = o["rules"].data_ptr(), cap, o["result"].data_ptr()
+            self.arr.append(arr)
+            self.outs.append(outs)
+        self.nbytes = L.scn_rules_chain_resident_workspace_bytes(self.n, batch)
+        self.ws = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.phase = 0
+        self.bg = torch.empty(batch, dtype=torch.int32, device=device)
+
+    def __del__(self):
+        try:
+            self.L.scn_rules_chain_resident_destroy(self.state)
+        except Exception:
+            pass
+
+    def build(self, keys, off, bg, max_rows_per_sample, rows_hint=0):
+        """bg None: the kernel finds the background rows (returned as self.bg)."""
+        p = self.phase
+        self.phase ^= 1
+        check(self.L.scn_rules_chain_build_resident(self.state, self.arr[p], self.n, self.batch, _ptr(_i32(keys)), _ptr(_i32(off)),
+                                                    None if bg is None else _ptr(_i32(bg)), _ptr(self.bg), max_rows_per_sample, rows_hint,
+                                                    _ptr(self.ws), self.nbytes, p, _ptr(self.results[1 - p]), 4 * self.n, _stream()))
+        return self.outs[p]
 
 
 def conv_nin_forward_dyn(feat, rules, fs, W, B, d_rows, rows_bound, prelu=None, p=1.0, act=NOSIGMOID, packed=None):

@@ -305,7 +305,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
                  accFullBar = smem_u32(&bars[3 * MAX_STAGES]), accEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 2]),
                  aFullBar = smem_u32(&bars[3 * MAX_STAGES + 4]), aEmptyBar = smem_u32(&bars[3 * MAX_STAGES + 6]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  scn::dependents_may_launch(); // the next kernel's CTAs may take over SMs as this grid's CTAs leave them
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P.stages; ++s) {
@@ -327,6 +326,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmemBase;
+  // The next kernel's CTAs may take over SMs as this grid's CTAs leave them.  Said only now that this CTA holds its
+  // tensor-memory columns: a dependent CTA that shared the SM could otherwise allocate first and then sit in its own
+  // wait for this grid while this CTA waits for columns (tcgen05.alloc has no time limit).
+  scn::dependents_may_launch();
   scn::wait_for_prior_grids(); // everything above overlapped the kernel in front; its results are read from here on
   // the row count may still be on its way to the host when this kernel is launched: read it from device memory
   // (POOL: rows counts tile rows = pooled rows x cells, and the device-side count is in pooled rows)

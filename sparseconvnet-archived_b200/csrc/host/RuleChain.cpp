@@ -6,13 +6,25 @@ namespace { thread_local std::vector<DeferredBuild> *g_deferred = nullptr; }
 void beginDeferred(std::vector<DeferredBuild> *list) { g_deferred = list; }
 void endDeferred() { g_deferred = nullptr; }
 
-bool runDeferred(std::vector<DeferredBuild> &list, int batch, int maxRowsPerSample, int rowsHint, cudaMemStream &ms) {
+bool runDeferred(std::vector<DeferredBuild> &list, int batch, int maxRowsPerSample, int rowsHint, cudaMemStream &ms,
+                 const ResidentChain *resident) {
   if (list.empty()) return false;
   std::vector<scn_chain_layer_t> layers;
   for (auto &d : list) layers.push_back(d.out);
   const int n = (int)layers.size();
   if (rowsHint > 0 && !scn_rules_chain_supported(layers.data(), n, batch, maxRowsPerSample, rowsHint)) rowsHint = 0;
-  if (scn_rules_chain_supported(layers.data(), n, batch, maxRowsPerSample, rowsHint)) {
+  const bool chain = scn_rules_chain_supported(layers.data(), n, batch, maxRowsPerSample, rowsHint) != 0;
+  if (chain && resident) {
+    const size_t bytes = scn_rules_chain_resident_workspace_bytes(n, batch);
+    void *ws = ms.chainWorkspace(bytes);
+    scnSafeCall(scn_rules_chain_build_resident(ms.chainState(), layers.data(), n, batch, list[0].inKeys, list[0].inOff,
+                                               resident->findBackground ? nullptr : list[0].inBg, const_cast<int *>(list[0].inBg),
+                                               maxRowsPerSample, rowsHint, ws, bytes, resident->phase, resident->resultNext, resident->nResultNext, ms.stream));
+    return rowsHint > 0;
+  }
+  if (resident && resident->findBackground)
+    scnSafeCall(scn_background_rows(list[0].inKeys, list[0].inOff, batch, const_cast<int *>(list[0].inBg), ms.stream));
+  if (chain) {
     size_t bytes = scn_rules_chain_workspace_bytes(n, batch);
     void *ws = ms.deviceScratch(bytes);
     scnSafeCall(scn_rules_chain_build(layers.data(), n, batch, list[0].inKeys, list[0].inOff, list[0].inBg, maxRowsPerSample,

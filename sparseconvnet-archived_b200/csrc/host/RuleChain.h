@@ -18,7 +18,13 @@ void endDeferred();
 // Run recorded builds: one fused kernel when the samples are small enough, else one
 // scn_rules_build per layer.  rowsHint as in scn_rules_chain_build; returns true if the fused
 // kernel ran with a hint (so a capacity error means "retry with rowsHint = 0").
-bool runDeferred(std::vector<DeferredBuild> &list, int batch, int maxRowsPerSample, int rowsHint, cudaMemStream &ms);
+// resident: how a network that owns its chain state runs the fused kernel without stream operations in front of it
+// (scn_rules_chain_build_resident): the phase of this batch's result records, the records of the next batch, and
+// whether the input's background rows are still to be found (then they are written to list[0].inBg by the kernel,
+// or by scn_background_rows where the fused kernel does not apply).
+struct ResidentChain { int phase; int *resultNext; int nResultNext; bool findBackground; };
+bool runDeferred(std::vector<DeferredBuild> &list, int batch, int maxRowsPerSample, int rowsHint, cudaMemStream &ms,
+                 const ResidentChain *resident = nullptr);
 
 long long enqueueRegions(const scn_regions_t &R, SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
                          SpatiallySparseBatchInterface &output, long long rowsInBound, int *d_result, cudaMemStream &ms);

@@ -1,7 +1,7 @@
 // The public facade (SparseConvNet.h:20-99): thin forwarding classes over SparseConvNetCUDA
 // for square/cubic lattices (SparseConvNet) and triangular/tetrahedral ones
-// (SparseConvTriangLeNet).  Fractional max-pooling builders and the index-learner head are
-// not built (training-only / random regions).
+// (SparseConvTriangLeNet), fractional max-pooling builders included.  The index-learner head
+// (training only) is not built.
 #pragma once
 #include <memory>
 #include <string>

@@ -23,6 +23,8 @@ void SparseConvNetCUDA::init(int nInputFeatures_, int nClasses_) {
   fuseClassifier = true;
   earlyFirstLayer = false; earlyLayers = 0; inputReady = nullptr; countStream = nullptr; chainDone = nullptr;
   chainRowsHint = 0;
+  chainPhase = 0;
+  inputBackgroundPending = false;
   inputSpatialSize = 0;
   cublasHandle = nullptr;
   batchPool.reserve(nBatchProducerThreads); // interfaces hold pointers into each other: no reallocation later
@@ -163,8 +165,13 @@ void SparseConvNetCUDA::prepareBatch(SpatiallySparseBatch &batch) {
 void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
   prepareBatch(batch);
   const int nL = (int)layers.size();
-  chainResults.resize(4 * nL + 4);
-  int *d_res = chainResults.dPtr();
+  // two sets of result records, used in turn: the fused rule chain of one batch clears the records of the next
+  chainResults.resize(8 * nL + 4);
+  const int phase = chainPhase;
+  chainPhase ^= 1;
+  int *d_res = chainResults.dPtr() + phase * 4 * nL;
+  rulechain::ResidentChain resident = {phase, chainResults.dPtr() + (1 - phase) * 4 * nL, 4 * nL, inputBackgroundPending};
+  inputBackgroundPending = false;
   long long bound = batch.interfaces[0].nSpatialSites, bound0 = 0, bound2 = 0;
   earlyLayers = 0;
   if (timing) cudaSafeCall(cudaEventRecord(events[nL + 1], memStream.stream));
@@ -172,6 +179,11 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
   // only recorded here and then run together: one fused kernel when the samples are small.
   bool defer = true;
   for (auto L : layers) defer = defer && dynamic_cast<TerminalPoolingLayer *>(L) == nullptr && dynamic_cast<FractionalMaxPoolingLayerBase *>(L) == nullptr;
+  if (resident.findBackground && (!defer || nL == 0 || !layers[0]->changesGeometry)) { // no fused chain will look for them
+    SpatiallySparseBatchInterface &in = batch.interfaces[0];
+    scnSafeCall(scn_background_rows(in.siteKeys.dPtr(), in.sampleOffsets.dPtr(), batch.batchSize, in.backgroundRows.dPtr(), memStream.stream));
+    resident.findBackground = false;
+  }
   std::vector<rulechain::DeferredBuild> builds;
   if (defer) rulechain::beginDeferred(&builds);
   try {
@@ -187,7 +199,7 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
   bool hinted = false;
   if (defer) {
     rulechain::endDeferred();
-    hinted = rulechain::runDeferred(builds, batch.batchSize, batch.interfaces[0].maxSitesPerSample + 1, chainRowsHint, memStream);
+    hinted = rulechain::runDeferred(builds, batch.batchSize, batch.interfaces[0].maxSitesPerSample + 1, chainRowsHint, memStream, &resident);
   }
   if (timing) cudaSafeCall(cudaEventRecord(events[nL + 2], memStream.stream));
   if (inputReady) { // the features were uploaded on another stream while the rules were built
@@ -244,7 +256,8 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
     if (overflow) {
       earlyLayers = 0; // the early kernel ran on truncated rules: the layers run again from the first
       chainRowsHint = 0;
-      rulechain::runDeferred(builds, batch.batchSize, batch.interfaces[0].maxSitesPerSample + 1, 0, memStream);
+      const rulechain::ResidentChain again = {phase, resident.resultNext, resident.nResultNext, false}; // (the background rows are known by now)
+      rulechain::runDeferred(builds, batch.batchSize, batch.interfaces[0].maxSitesPerSample + 1, 0, memStream, &again);
       cudaSafeCall(cudaMemcpyAsync(h, d_res, sizeof(int) * 4 * nL, cudaMemcpyDeviceToHost, memStream.stream));
       cudaSafeCall(cudaStreamSynchronize(memStream.stream));
       counts.assign(h, h + 4 * nL);

@@ -75,11 +75,15 @@ public:
   // returns layers.size()+1 values in ms: each layer's forwards(), then the rule chain.
   void enableTiming(bool on);
   std::vector<float> layerTimes();
+  // Set before preprocessBatchOnDevice when interface 0's backgroundRows have not been filled in: the rule chain's
+  // kernel finds them on its way (a kernel of their own where the fused chain does not apply).
+  bool inputBackgroundPending;
 
 private:
   void init(int nInputFeatures, int nClasses);
-  vectorCUDA<int> chainResults; // 4 ints per layer
+  vectorCUDA<int> chainResults; // two sets of 4 ints per layer, used by alternate batches
   bool timing;
   int chainRowsHint; // rows per sample seen so far (+25 %): sizes the fused rule chain's shared memory
+  int chainPhase;    // which of the two sets of rule-chain result records the next batch uses
   std::vector<cudaEvent_t> events; // layers.size()+1 layer boundaries, then rule chain begin/end
 };

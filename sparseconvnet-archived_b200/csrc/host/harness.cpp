@@ -272,7 +272,7 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *
       cudaSafeCall(cudaMemcpyAsync(dst, sf, fb, cudaMemcpyHostToDevice, net->copyStream));
       cudaSafeCall(cudaEventRecord(net->copyDone, net->copyStream));
     }
-    scnSafeCall(scn_background_rows(in.siteKeys.dPtr(), in.sampleOffsets.dPtr(), batch, in.backgroundRows.dPtr(), s));
+    cnn.inputBackgroundPending = true; // found by the rule chain's kernel (or by a kernel of its own where that one does not apply)
     if (rows) cnn.inputReady = net->copyDone; // the layers (not the rule chain) wait for the features
     cnn.earlyFirstLayer = true; // one batch in flight here: the first layer may start behind the rule chain
     cnn.preprocessBatchOnDevice(b); // waits once, after the key upload and the rule chain

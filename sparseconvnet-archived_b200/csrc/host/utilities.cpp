@@ -78,7 +78,9 @@ cudaMemStream::cudaMemStream(cudaStream_t external)
   cudaSafeCall(cudaMallocHost(&pinnedMemory, pinnedMemorySize));
 }
 cudaMemStream::~cudaMemStream() {
-  if (scratch || resultWords) cudaStreamSynchronize(stream);
+  if (scratch || resultWords || chainBlock) cudaStreamSynchronize(stream);
+  if (chainBlock) cudaFree(chainBlock);
+  if (chainResident) scn_rules_chain_resident_destroy(chainResident);
   if (scratch) cudaFree(scratch);
   if (resultWords) cudaFree(resultWords);
   if (ownsStream && stream) cudaStreamDestroy(stream);
@@ -92,6 +94,21 @@ void *cudaMemStream::deviceScratch(size_t bytes) {
     scratchBytes = want;
   }
   return scratch;
+}
+void *cudaMemStream::chainWorkspace(size_t bytes) {
+  if (bytes > chainBytes) {
+    if (chainBlock) { cudaSafeCall(cudaStreamSynchronize(stream)); cudaSafeCall(cudaFree(chainBlock)); chainBlock = nullptr; chainBytes = 0; }
+    const size_t want = bytes + bytes / 4;
+    cudaSafeCall(cudaMalloc(&chainBlock, want));
+    chainBytes = want;
+    if (chainResident) scn_rules_chain_resident_invalidate(chainResident);
+  }
+  return chainBlock;
+}
+scn_chain_resident_t *cudaMemStream::chainState() {
+  if (!chainResident) chainResident = scn_rules_chain_resident_create();
+  if (!chainResident) throw ScnException("out of host memory");
+  return chainResident;
 }
 int *cudaMemStream::deviceResult() {
   if (!resultWords) cudaSafeCall(cudaMalloc((void **)&resultWords, 4 * sizeof(int)));

@@ -53,6 +53,9 @@ public:
   void *staging(size_t bytes); // pinned buffer of at least `bytes`
   void *deviceScratch(size_t bytes); // device buffer of at least `bytes`; only work on `stream` may use it
   int *deviceResult();               // four device ints for a rule build whose counts nobody reads
+  // Device block of the fused rule chain's resident build (scn_rules_chain_build_resident): nothing else writes it.
+  void *chainWorkspace(size_t bytes);
+  scn_chain_resident_t *chainState();
   cudaMemStream(const cudaMemStream &) = delete;
   cudaMemStream &operator=(const cudaMemStream &) = delete;
 
@@ -61,4 +64,7 @@ private:
   void *scratch = nullptr;
   size_t scratchBytes = 0;
   int *resultWords = nullptr;
+  void *chainBlock = nullptr;
+  size_t chainBytes = 0;
+  scn_chain_resident_t *chainResident = nullptr;
 };

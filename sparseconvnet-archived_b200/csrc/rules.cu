@@ -20,6 +20,8 @@
 // synchronisation: every size the kernels need is read from device memory.
 #include "scn_common.cuh"
 #include <algorithm>
+#include <cstring>
+#include <new>
 #include <mutex>
 #include <vector>
 
@@ -700,6 +702,12 @@ struct ChainParams {
   int *counts;  // [nLayers x batch], -1 until published; value = rows | needBg << 30
   int *ticket;
   int rowsMax, wMax, tMax, flagBytes;
+  // Resident use (scn_rules_chain_build_resident): this launch leaves the state the NEXT launch will use ready
+  // (its counters at -1, its ticket at -1, its result records at 0), so no stream operation has to run in front
+  // of that launch.  All three are null otherwise.
+  int *nextCounts, *nextTicket, *nextResults;
+  int nNextResults; // ints to clear at nextResults
+  int *bgOut; // not null: inBg is null, every sample's background row is found here and written to bgOut
 };
 
 constexpr int CHAIN_THREADS = 512;
@@ -744,20 +752,36 @@ __global__ void __launch_bounds__(1024) k_rule_chain(const ChainParams P) {
     *total = __shfl_sync(0xffffffffu, tincl, nWarps - 1);
     return __shfl_sync(0xffffffffu, tincl - t, warp) + incl - v;
   };
-  if (tid == 0) sTicket = atomicAdd(P.ticket, 1) + 1; // the ticket starts at -1
+  if (tid == 0) { sTicket = atomicAdd(P.ticket, 1) + 1; sBase = -1; } // the ticket starts at -1
   __syncthreads();
   const int b = sTicket;
   if (b >= P.batch) return;
+  if (P.nextCounts) { // nothing reads these before the next launch, which stream order puts behind this one
+    for (int l = tid; l < P.nLayers; l += NT) P.nextCounts[l * P.batch + b] = -1;
+    if (b == 0) {
+      if (tid == 0) *P.nextTicket = -1;
+      for (int i = tid; i < P.nNextResults; i += NT) P.nextResults[i] = 0;
+    }
+  }
 
   int *inKeys = keysA, *outKeysS = keysB;
   int inBase = P.inOff[b];
   int nRows = P.inOff[b + 1] - inBase;
-  int inBgGlobal = P.inBg[b];
+  int inBgGlobal = P.inBg ? P.inBg[b] : -1;
   if (nRows > P.rowsMax) { // the caller's bound was wrong: report on every layer and stop
     if (tid == 0) for (int l = 0; l < P.nLayers; ++l) { atomicOr(P.layers[l].result + 2, SCN_DEV_ERR_CAPACITY); P.counts[l * P.batch + b] = 0; }
     return;
   }
-  for (int j = tid; j < nRows; j += NT) inKeys[j] = P.inKeys[inBase + j];
+  for (int j = tid; j < nRows; j += NT) {
+    const int k = P.inKeys[inBase + j];
+    inKeys[j] = k;
+    if (P.bgOut && k < 0) sBase = inBase + j; // at most one background row per sample
+  }
+  if (P.bgOut) {
+    __syncthreads();
+    inBgGlobal = sBase;
+    if (tid == 0) P.bgOut[b] = inBgGlobal;
+  }
 
   for (int l = 0; l < P.nLayers; ++l) {
     const ChainLayer &L = P.layers[l];
@@ -1221,13 +1245,12 @@ extern "C" int scn_rules_chain_supported(const scn_chain_layer_t *layers, int n_
   return plan_chain(Rs.data(), n_layers, max_rows_per_sample, rows_hint).ok ? 1 : 0;
 }
 
-extern "C" int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_layers, int batch, const int *d_in_keys,
-                                     const int *d_in_off, const int *d_in_bg, int max_rows_per_sample, int rows_hint,
-                                     void *d_workspace, size_t workspace_bytes, scn_stream_t stream_) {
-  clear_error();
+namespace {
+// Checks the caller's layers and turns them into kernel descriptors and a shared-memory plan.
+int chain_prepare(const scn_chain_layer_t *layers, int n_layers, int batch, int max_rows_per_sample, int rows_hint,
+                  std::vector<ChainLayer> &h, ChainPlan &plan, int *dim) {
   if (!layers || n_layers < 1 || n_layers > 64 || batch < 1 || max_rows_per_sample < 0) return fail(SCN_ERR_INVALID, "bad chain arguments");
-  if (!d_in_off || !d_in_bg || !d_workspace) return fail(SCN_ERR_INVALID, "null pointer");
-  std::vector<ChainLayer> h(n_layers);
+  h.resize(n_layers);
   std::vector<Regions> Rs(n_layers);
   for (int l = 0; l < n_layers; ++l) {
     int st = make_regions(&layers[l].regions, &Rs[l]);
@@ -1235,12 +1258,52 @@ extern "C" int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_laye
     if (!layers[l].d_out_keys || !layers[l].d_out_off || !layers[l].d_out_bg || !layers[l].d_rules || !layers[l].d_result)
       return fail(SCN_ERR_INVALID, "null pointer in a chain layer");
     if (l > 0 && (Rs[l].nIn != Rs[l - 1].nOut || Rs[l].dim != Rs[l - 1].dim)) return fail(SCN_ERR_INVALID, "chain layers do not fit together");
+    std::memset(&h[l], 0, sizeof(ChainLayer)); // descriptors are compared bytewise by the resident build: no stray padding
     h[l].R = Rs[l];
     h[l].outKeys = layers[l].d_out_keys; h[l].outOff = layers[l].d_out_off; h[l].outBg = layers[l].d_out_bg;
     h[l].rules = layers[l].d_rules; h[l].result = layers[l].d_result; h[l].capacity = layers[l].rows_out_capacity;
   }
-  ChainPlan plan = plan_chain(Rs.data(), n_layers, max_rows_per_sample, rows_hint);
+  plan = plan_chain(Rs.data(), n_layers, max_rows_per_sample, rows_hint);
   if (!plan.ok) return fail(SCN_ERR_UNSUPPORTED, "samples too large for the fused rule chain: build layer by layer with scn_rules_build");
+  *dim = Rs[0].dim;
+  return SCN_OK;
+}
+
+int chain_launch(ChainParams &P, const ChainPlan &plan, int dim, int batch, cudaStream_t s) {
+  static bool attrSet[64] = {false};
+  int dev = 0;
+  SCN_CUDA_TRY(cudaGetDevice(&dev));
+  if (!attrSet[dev & 63]) {
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attrSet[dev & 63] = true;
+  }
+  P.batch = batch;
+  P.rowsMax = plan.rowsMax; P.wMax = plan.wMax; P.tMax = plan.tMax; P.flagBytes = (int)std::min<size_t>(plan.flagBytes, 0x7fffffff);
+  const int chainThreads = CHAIN_THREADS;
+  switch (dim) {
+  case 1: k_rule_chain<1><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
+  case 2: k_rule_chain<2><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
+  case 3: k_rule_chain<3><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
+  default: k_rule_chain<4><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
+  }
+  SCN_LAUNCH_CHECK("k_rule_chain");
+  return SCN_OK;
+}
+} // namespace
+
+extern "C" int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_layers, int batch, const int *d_in_keys,
+                                     const int *d_in_off, const int *d_in_bg, int max_rows_per_sample, int rows_hint,
+                                     void *d_workspace, size_t workspace_bytes, scn_stream_t stream_) {
+  clear_error();
+  if (!d_in_off || !d_in_bg || !d_workspace) return fail(SCN_ERR_INVALID, "null pointer");
+  std::vector<ChainLayer> h;
+  ChainPlan plan;
+  int dim = 0;
+  int st = chain_prepare(layers, n_layers, batch, max_rows_per_sample, rows_hint, h, plan, &dim);
+  if (st != SCN_OK) return st;
   if (scn_rules_chain_workspace_bytes(n_layers, batch) > workspace_bytes) return fail(SCN_ERR_WORKSPACE, "workspace smaller than scn_rules_chain_workspace_bytes()");
   cudaStream_t s = (cudaStream_t)stream_;
   ChainLayer *dLayers = (ChainLayer *)d_workspace;
@@ -1255,28 +1318,77 @@ extern "C" int scn_rules_chain_build(const scn_chain_layer_t *layers, int n_laye
   for (int l = 1; l < n_layers; ++l) contiguous = contiguous && layers[l].d_result == layers[0].d_result + 4 * l;
   if (contiguous) SCN_CUDA_TRY(cudaMemsetAsync(layers[0].d_result, 0, 4 * sizeof(int) * (size_t)n_layers, s));
   else for (int l = 0; l < n_layers; ++l) SCN_CUDA_TRY(cudaMemsetAsync(layers[l].d_result, 0, 4 * sizeof(int), s));
-  static bool attrSet[64] = {false};
-  int dev = 0;
-  SCN_CUDA_TRY(cudaGetDevice(&dev));
-  if (!attrSet[dev & 63]) {
-    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    SCN_CUDA_TRY(cudaFuncSetAttribute(k_rule_chain<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attrSet[dev & 63] = true;
-  }
   ChainParams P;
-  P.layers = dLayers; P.nLayers = n_layers; P.batch = batch;
+  P.layers = dLayers; P.nLayers = n_layers;
   P.inKeys = d_in_keys; P.inOff = d_in_off; P.inBg = d_in_bg;
   P.counts = counts; P.ticket = ticket;
-  P.rowsMax = plan.rowsMax; P.wMax = plan.wMax; P.tMax = plan.tMax; P.flagBytes = (int)std::min<size_t>(plan.flagBytes, 0x7fffffff);
-  const int chainThreads = CHAIN_THREADS;
-  switch (Rs[0].dim) {
-  case 1: k_rule_chain<1><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
-  case 2: k_rule_chain<2><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
-  case 3: k_rule_chain<3><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
-  default: k_rule_chain<4><<<batch, chainThreads, plan.smemBytes, s>>>(P); break;
+  P.nextCounts = nullptr; P.nextTicket = nullptr; P.nextResults = nullptr; P.nNextResults = 0; P.bgOut = nullptr;
+  return chain_launch(P, plan, dim, batch, s);
+}
+
+// ---- resident form: the caller keeps the workspace to itself, so the state of one launch is prepared by the launch before it
+struct scn_chain_resident {
+  void *workspace = nullptr;            // the device block the shadows below describe
+  int nLayers = 0, batch = 0;
+  std::vector<ChainLayer> shadow[2];    // descriptors resident on the device, per phase
+  bool ready[2] = {false, false};       // phase state (counters, ticket, result records) prepared by the launch before
+  int *preparedResults = nullptr;       // the result records that launch cleared
+  int lastPhase = -1;
+};
+
+extern "C" scn_chain_resident_t *scn_rules_chain_resident_create(void) { return new (std::nothrow) scn_chain_resident(); }
+extern "C" void scn_rules_chain_resident_destroy(scn_chain_resident_t *st) { delete st; }
+extern "C" void scn_rules_chain_resident_invalidate(scn_chain_resident_t *st) {
+  if (st) { st->workspace = nullptr; st->ready[0] = st->ready[1] = false; st->shadow[0].clear(); st->shadow[1].clear(); st->lastPhase = -1; }
+}
+extern "C" size_t scn_rules_chain_resident_workspace_bytes(int n_layers, int batch) {
+  return 2 * scn_rules_chain_workspace_bytes(n_layers, batch);
+}
+
+extern "C" int scn_rules_chain_build_resident(scn_chain_resident_t *st, const scn_chain_layer_t *layers, int n_layers, int batch,
+                                              const int *d_in_keys, const int *d_in_off, const int *d_in_bg, int *d_in_bg_out,
+                                              int max_rows_per_sample, int rows_hint, void *d_workspace, size_t workspace_bytes,
+                                              int phase, int *d_result_next, int n_result_next, scn_stream_t stream_) {
+  clear_error();
+  if (!st || !d_in_off || !d_workspace || (phase != 0 && phase != 1)) return fail(SCN_ERR_INVALID, "bad resident chain arguments");
+  if (!d_in_bg && !d_in_bg_out) return fail(SCN_ERR_INVALID, "need the background rows or a place to write them");
+  std::vector<ChainLayer> h;
+  ChainPlan plan;
+  int dim = 0;
+  int rc = chain_prepare(layers, n_layers, batch, max_rows_per_sample, rows_hint, h, plan, &dim);
+  if (rc != SCN_OK) return rc;
+  if (d_result_next && n_result_next < 1) return fail(SCN_ERR_INVALID, "resident chain: n_result_next must be positive");
+  const size_t half = scn_rules_chain_workspace_bytes(n_layers, batch);
+  if (2 * half > workspace_bytes) return fail(SCN_ERR_WORKSPACE, "workspace smaller than scn_rules_chain_resident_workspace_bytes()");
+  cudaStream_t s = (cudaStream_t)stream_;
+  if (st->workspace != d_workspace || st->nLayers != n_layers || st->batch != batch) {
+    scn_rules_chain_resident_invalidate(st);
+    st->workspace = d_workspace; st->nLayers = n_layers; st->batch = batch;
   }
-  SCN_LAUNCH_CHECK("k_rule_chain");
-  return SCN_OK;
+  char *base = (char *)d_workspace + (size_t)phase * half, *other = (char *)d_workspace + (size_t)(1 - phase) * half;
+  const size_t descBytes = align_up(sizeof(ChainLayer) * (size_t)n_layers, 256);
+  ChainLayer *dLayers = (ChainLayer *)base;
+  int *counts = (int *)(base + descBytes), *ticket = counts + (size_t)n_layers * batch;
+  int *nextCounts = (int *)(other + descBytes), *nextTicket = nextCounts + (size_t)n_layers * batch;
+  if (st->shadow[phase].size() != (size_t)n_layers || std::memcmp(st->shadow[phase].data(), h.data(), sizeof(ChainLayer) * n_layers) != 0) {
+    SCN_CUDA_TRY(cudaMemcpyAsync(dLayers, h.data(), sizeof(ChainLayer) * n_layers, cudaMemcpyHostToDevice, s));
+    st->shadow[phase] = h;
+  }
+  if (!st->ready[phase] || st->lastPhase == phase || st->preparedResults != layers[0].d_result) { // first use of this phase, the same phase twice, other result records: prepare it here
+    SCN_CUDA_TRY(cudaMemsetAsync(counts, 0xff, sizeof(int) * ((size_t)n_layers * batch + 1), s));
+    for (int l = 0; l < n_layers; ++l) SCN_CUDA_TRY(cudaMemsetAsync(layers[l].d_result, 0, 4 * sizeof(int), s));
+  }
+  ChainParams P;
+  P.layers = dLayers; P.nLayers = n_layers;
+  P.inKeys = d_in_keys; P.inOff = d_in_off; P.inBg = d_in_bg;
+  P.counts = counts; P.ticket = ticket;
+  P.nNextResults = d_result_next ? n_result_next : 0;
+  P.nextCounts = d_result_next ? nextCounts : nullptr; P.nextTicket = d_result_next ? nextTicket : nullptr; P.nextResults = d_result_next;
+  P.bgOut = d_in_bg ? nullptr : d_in_bg_out;
+  rc = chain_launch(P, plan, dim, batch, s);
+  st->ready[phase] = false;
+  st->ready[1 - phase] = (rc == SCN_OK && d_result_next != nullptr);
+  st->preparedResults = d_result_next;
+  st->lastPhase = phase;
+  return rc;
 }

@@ -234,6 +234,37 @@ def test_fused_chain_matches_oracle(abi, oracle, lattice, dim, S, steps):
             n = nOut
 
 
+def test_resident_chain_matches_one_shot_build(abi, oracle):
+    """scn_rules_chain_build_resident over a run of different batches (the device state of call n + 1 is prepared by the
+    kernel of call n, the background rows are found by the kernel) against scn_rules_chain_build on the same grids: every
+    output and every result record equal, call after call."""
+    rng = np.random.default_rng(404)
+    dim, S, batch = 2, 24, 37
+    steps = [(3, 1, 1), (2, 2, 1), (2, 1, 2), (2, 2, 1)]
+    regs, caps, n, bound = [], [], S, batch * (S * S + 1)
+    for size, stride, mn in steps:
+        nOut = (n - size) // stride + 1
+        regs.append(abi.regions(0, dim, n, nOut, size, stride, mn))
+        caps.append(batch * (nOut ** dim + 1))
+        n = nOut
+    chain = abi.ResidentChain(regs, batch, caps, torch.device("cuda"))
+    for it, dens in enumerate(([0.3], [0.05, 0.9], [0.0, 1.0], [0.5], [0.2], [0.7, 0.1])):
+        g = random_grids(rng, batch, dim, S, dens)
+        dk, doff, dbg, _ = to_dev_grid(*g)
+        max_rows = int(np.diff(g[2]).max() + 1)
+        want = abi.rules_chain_build(regs, dk, doff, dbg, max_rows, caps)
+        got = chain.build(dk, doff, None if it % 2 == 0 else dbg, max_rows)
+        torch.cuda.synchronize()
+        if it % 2 == 0:
+            assert torch.equal(chain.bg, dbg)
+        for a, b in zip(got, want):
+            rows = int(b["result"][0])
+            assert torch.equal(a["result"].cpu(), b["result"].cpu()), it
+            assert torch.equal(a["out_off"], b["out_off"]) and torch.equal(a["out_bg"], b["out_bg"])
+            assert torch.equal(a["out_keys"][:rows], b["out_keys"][:rows])
+            assert torch.equal(a["rules"][: rows * a["sd"]], b["rules"][: rows * b["sd"]])
+
+
 def test_fused_chain_declines_large_samples(abi):
     regs = [abi.regions(0, 3, 48, 46, 3, 1, 1)]
     z = torch.zeros(4, dtype=torch.int32, device="cuda")
