@@ -341,6 +341,62 @@ size_t scn_classifier_result_bytes(int rows, int nClasses, int nTop);
 int scn_classifier_result(const float *d_probs, int rows, int nClasses, int nTop, void *d_block,
                           scn_stream_t stream);
 
+/* ------------------------------------------------------------------ backward pass (training step)
+ * The reference runs every layer's backwards() in reverse order behind SoftmaxClassifier
+ * (SparseConvNetCUDA.cu:247-251).  Training-time dropout (random feature subsets and the
+ * shrunk weight matrices, NetworkInNetworkLayer.cu:162-186) is not built: these entry points
+ * serve layers whose dropout is 0. */
+
+/* Replaces dDerivativeOfCostWRTpreSoftmaxTopLevelWeights (SoftmaxClassifier.cu:7-14, 27-33):
+ * d_dfeatures[r][c] = d_probs[r][c] - (c == d_labels[r]), not averaged over the batch. */
+int scn_softmax_nll_backward(const float *d_probs, const int *d_labels, int rows, int nClasses,
+                             float *d_dfeatures, scn_stream_t stream);
+
+/* Replaces applySigmoidBackProp (SigmoidLayer.cu:224-268) and PReLUBackprop
+ * (NetworkInNetworkPReLULayer.cu:25-47), in place on the output's gradient: d *= f'(.),
+ * the derivative taken from the ACTIVATED features as the reference takes it.  PReLU also
+ * gets the slope gradient d_dprelu[N] = sum over rows of d * (b > 0 ? 0 : b / slope).
+ * Softmax and NOSIGMOID pass through. */
+int scn_activation_backward(const float *d_out_features, float *d_dfeatures, int rows, int N, int act,
+                            const float *d_prelu, float *d_dprelu, scn_stream_t stream);
+
+/* Replaces the weight half of NetworkInNetworkLayer::backwards (NetworkInNetworkLayer.cu:226-239:
+ * cuBLAS SGEMM X^T d, columnSum) with the convolution's gather read through the rulebook
+ * inside the kernel (the gathered matrix is never written): d_dW[(fs*nIn) x N] = X^T d_dout,
+ * d_dB[N] = column sums of d_dout; X as in scn_conv_nin_forward (d_rules NULL and fs 1: plain). */
+int scn_conv_nin_backward_weights(const float *d_in, const int *d_rules, int rows, int fs, int nIn,
+                                  const float *d_dout, int N, float *d_dW, float *d_dB, scn_stream_t stream);
+
+/* d_Wt[N x K] = transpose of d_W[K x N].  The input half of NetworkInNetworkLayer::backwards
+ * (NetworkInNetworkLayer.cu:266-277: dX = d W^T) is scn_conv_nin_forward_ws on d_dout with
+ * these transposed weights (zero bias, no activation), so it runs on the tensor cores
+ * wherever the forward pass does. */
+int scn_transpose_weights(const float *d_W, int K, int N, float *d_Wt, scn_stream_t stream);
+
+/* Replaces propBackwardFromMatrixMultiply (ConvolutionalLayer.cu:42-72): zeroes
+ * d_din[rows_in x nIn], then d_din[rules[c]] += d_dconv[c] for the count = rows_out*fs rule
+ * cells with a non-negative rule. */
+int scn_gather_backward(const float *d_dconv, const int *d_rules, long long count, int nIn, float *d_din,
+                        long long rows_in, scn_stream_t stream);
+
+/* Replaces maxPoolBackProp (MaxPoolingLayer.cu:74-93, 134-146): zeroes d_din[n_in], then
+ * d_din[d_choices[i]] += d_dout[i] for the n pooled values. */
+int scn_maxpool_backward(const float *d_dout, const int *d_choices, long long n, float *d_din, long long n_in,
+                         scn_stream_t stream);
+
+/* Replaces terminalPoolBackProp (TerminalPoolingLayer.cu:48-73, 112-125): zeroes
+ * d_din[rows_in x C]; every input row a sample pooled receives that sample's gradient
+ * divided by the number of rows pooled. */
+int scn_terminal_pool_backward(const float *d_dout, const int *d_rules, int batch, int S, int C, float *d_din,
+                               long long rows_in, scn_stream_t stream);
+
+/* Replaces dGradientDescent (NetworkInNetworkLayer.cu:26-40): w -= m*momentum;
+ * m = momentum*m - learningRate*(1-momentum)*delta; w += m*(1+momentum); with keep_positive
+ * also dGradientDescentKeepPositive (NetworkInNetworkPReLULayer.cu:67-84), the PReLU slopes'
+ * update, which then holds w at 0.001 or above. */
+int scn_sgd_update(float *d_w, float *d_momentum, const float *d_delta, long long n, float learningRate,
+                   float momentum, int keep_positive, scn_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -73,6 +73,20 @@ int scn_net_set_precision(scn_net_t *net, int precision);
  *   h_probs[batch x nClasses], h_predictions[batch x nTop] (either may be NULL) */
 int scn_net_forward_host(scn_net_t *net, int batch, const int *h_keys, const int *h_off, const float *h_features,
                          float *h_probs, int *h_predictions);
+/* One training step on one batch given like scn_net_forward_host plus one label per sample:
+ * the TRAINBATCH branch of SparseConvNetCUDA::processBatch (SparseConvNetCUDA.cu:227-251):
+ * forward, SoftmaxClassifier (negative log-likelihood and mistakes into stats[0..1], the
+ * probabilities into h_probs), every layer's backwards() in reverse order with the SGD update
+ * of its weights (learningRate, momentum as in NetworkInNetworkLayer.cu:26-40).  The samples
+ * stay in the order given.  Networks with dropout are refused. */
+int scn_net_train_batch(scn_net_t *net, int batch, const int *h_keys, const int *h_off, const float *h_features, const int *h_labels,
+                        float learningRate, float momentum, float *h_probs, double *stats);
+/* A learnt layer's weights as they are now (W [nIn x nOut], B [nOut], PReLU slopes [nOut] or NULL). */
+int scn_net_get_weights(scn_net_t *net, int layer, float *h_W, float *h_B, float *h_prelu);
+/* d cost / d features of interface i after scn_net_train_batch: returns their count (-1 on
+ * error, 0 where no gradient reaches) and copies them when h_dfeatures is not NULL. */
+long long scn_net_iface_dfeatures(scn_net_t *net, int i, float *h_dfeatures);
+
 /* The same with inputs already resident in device memory: the batch's interface reads the caller's
  * arrays in place (no copy), so they must stay unchanged until the forward has run on the stream and
  * must not be freed before the network's next forward call.  d_bg[batch] is each sample's background row or -1;

@@ -148,6 +148,7 @@ class ReferenceGPU:
         L.refgpu_iface_fetch.argtypes = [c_p, c_int] + [c_p] * 6
         L.refgpu_results.argtypes = [c_p] * 4
         L.refgpu_layer_weights.argtypes = [c_p, c_int, c_p, c_p, c_p]
+        L.refgpu_sample_numbers.argtypes = [c_p, c_p]
         self.dim, self.nIn, self.nClasses, self.nTop, self.lattice = dim, nInputFeatures, nClasses, nTop, lattice
         self.h = L.refgpu_create(dim, nInputFeatures, nClasses, nTop, lattice)
 
@@ -229,6 +230,12 @@ class ReferenceGPU:
                     dfeatures=dfeat.reshape(-1, w) if ndf == rows * w else dfeat,
                     choices=ch, rules=rules, row_keys=rk)
 
+    def sample_numbers(self, batch):
+        """Position -> caller's sample index within the last batch (a TRAINBATCH is shuffled by the reference)."""
+        out = np.zeros(batch, np.int32)
+        self.L.refgpu_sample_numbers(self.h, _p(out))
+        return out
+
     def layer_weights(self, i):
         info = self.layers()[i]
         W = np.zeros((info["nIn"], info["nOut"]), np.float32)
@@ -268,6 +275,16 @@ class Oracle(_RulesLib):
         L.orc_net_forward.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_int, c_int, c_p, c_p, c_p]
         L.orc_net_iface_sizes.argtypes = [c_p, c_int, c_p]
         L.orc_net_iface_fetch.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p]
+        L.orc_net_train_step.restype = c_int
+        L.orc_net_train_step.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_int, c_p, c_p]
+        L.orc_net_iface_dfeatures.restype, L.orc_net_iface_dfeatures.argtypes = c_ll, [c_p, c_int, c_p]
+        L.orc_net_get_weights.argtypes = [c_p, c_int, c_p, c_p, c_p]
+        L.orc_activation_backward.argtypes = [c_p, c_p, c_ll, c_int, c_int, c_p, c_p]
+        L.orc_nin_backward.argtypes = [c_p, c_p, c_ll, c_int, c_int, c_p, c_p, c_p, c_p]
+        L.orc_gather_backward.argtypes = [c_p, c_p, c_ll, c_int, c_ll, c_p]
+        L.orc_maxpool_backward.argtypes = [c_p, c_p, c_ll, c_ll, c_p]
+        L.orc_terminal_pool_backward.argtypes = [c_p, c_p, c_int, c_int, c_int, c_ll, c_p]
+        L.orc_sgd_update.argtypes = [c_p, c_p, c_p, c_ll, c_f, c_f, c_int]
 
     # ---- fractional max-pooling
     def fmp_ticks(self, kind, dim, nIn, nOut, poolSize, seed, count):
@@ -329,6 +346,56 @@ class Oracle(_RulesLib):
         out = np.zeros(k, np.int32)
         self.lib.orc_top_indices(_p(v), len(v), k, _p(out))
         return out
+
+    # ---- backward operations (fp64 accumulation)
+    def activation_backward(self, out_features, d, act, prelu=None):
+        """-> (d * f'(.) as a new array, slope gradient or None)."""
+        b = np.ascontiguousarray(out_features, np.float32)
+        d = np.array(d, np.float32, copy=True, order="C")
+        rows, N = b.shape
+        prelu = None if prelu is None else np.ascontiguousarray(prelu, np.float32)
+        dpr = np.zeros(N, np.float32)
+        self.lib.orc_activation_backward(_p(b), _p(d), rows, N, act, _p(prelu), _p(dpr))
+        return d, (dpr if act == PRELU else None)
+
+    def nin_backward(self, X, d, W, want_dx=True):
+        """-> (dW [K x N], dB [N], dX [rows x K] or None)."""
+        X, d, W = (np.ascontiguousarray(a, np.float32) for a in (X, d, W))
+        rows, K = X.shape
+        N = W.shape[1]
+        dW, dB = np.zeros((K, N), np.float32), np.zeros(N, np.float32)
+        dX = np.zeros((rows, K), np.float32) if want_dx else None
+        self.lib.orc_nin_backward(_p(X), _p(d), rows, K, N, _p(W), _p(dW), _p(dB), _p(dX))
+        return dW, dB, dX
+
+    def gather_backward(self, d_conv, rules, nIn, rows_in):
+        d_conv = np.ascontiguousarray(d_conv, np.float32)
+        rules = np.ascontiguousarray(rules, np.int32).ravel()
+        out = np.zeros((rows_in, nIn), np.float32)
+        self.lib.orc_gather_backward(_p(d_conv), _p(rules), rules.size, nIn, rows_in, _p(out))
+        return out
+
+    def maxpool_backward(self, d_out, choices, n_in):
+        d_out = np.ascontiguousarray(d_out, np.float32)
+        choices = np.ascontiguousarray(choices, np.int32)
+        out = np.zeros(n_in, np.float32)
+        self.lib.orc_maxpool_backward(_p(d_out), _p(choices), d_out.size, n_in, _p(out))
+        return out
+
+    def terminal_pool_backward(self, d_out, rules, S, rows_in):
+        d_out = np.ascontiguousarray(d_out, np.float32)
+        rules = np.ascontiguousarray(rules, np.int32).reshape(-1, S)
+        C = d_out.shape[1]
+        out = np.zeros((rows_in, C), np.float32)
+        self.lib.orc_terminal_pool_backward(_p(d_out), _p(rules), rules.shape[0], S, C, rows_in, _p(out))
+        return out
+
+    def sgd_update(self, w, m, d, lr, momentum, keep_positive=False):
+        """NAG-light update in place on copies -> (w, m)."""
+        w, m = np.array(w, np.float32, copy=True, order="C"), np.array(m, np.float32, copy=True, order="C")
+        d = np.ascontiguousarray(d, np.float32)
+        self.lib.orc_sgd_update(_p(w), _p(m), _p(d), w.size, lr, momentum, int(keep_positive))
+        return w, m
 
 
 class OracleNet:
@@ -414,6 +481,35 @@ class OracleNet:
                                _p(probs), _p(pred), _p(times))
         self.times = times
         return probs, pred
+
+    def train_step(self, keys, off, features, labels, learning_rate, momentum, accum64=True):
+        """One TRAINBATCH step (forward, SoftmaxClassifier, every layer's backwards with its SGD update) on a network
+        without dropout -> (probabilities, dict(nll, mistakes)); interfaces and their dfeatures are kept."""
+        keys = np.ascontiguousarray(keys, np.int64)
+        off = np.ascontiguousarray(off, np.int32)
+        features = np.ascontiguousarray(features, np.float32)
+        labels = np.ascontiguousarray(labels, np.int32)
+        B = len(off) - 1
+        probs = np.zeros((B, self.nClasses), np.float32)
+        stats = np.zeros(2, np.float64)
+        rc = self.L.orc_net_train_step(self.h, B, _p(keys), _p(off), _p(features), _p(labels), learning_rate, momentum, int(accum64),
+                                       _p(probs), _p(stats))
+        if rc:
+            raise ValueError("the oracle's training step needs a network without dropout")
+        return probs, dict(nll=float(stats[0]), mistakes=int(stats[1]))
+
+    def dfeatures(self, i):
+        n = self.L.orc_net_iface_dfeatures(self.h, i, None)
+        d = np.zeros(n, np.float32)
+        self.L.orc_net_iface_dfeatures(self.h, i, _p(d))
+        return d
+
+    def get_weights(self, i):
+        L = self.layers()[i]
+        W, B = np.zeros((L["nIn"], L["nOut"]), np.float32), np.zeros(L["nOut"], np.float32)
+        pr = np.zeros(L["nOut"], np.float32)
+        self.L.orc_net_get_weights(self.h, i, _p(W), _p(B), _p(pr))
+        return W, B, (pr if L["act"] == PRELU else None)
 
     def iface(self, i):
         """Interface i of the last forward(keep=True): 0 is the input, i+1 layer i's output."""

@@ -210,6 +210,12 @@ void refgpu_results(void *p, float *probs, int *pred, double *stats) {
   }
   if (stats) { stats[0] = b.negativeLogLikelihood; stats[1] = b.mistakes; }
 }
+// The order in which the batch holds the caller's samples: BatchProducer shuffles a TRAINBATCH dataset
+// (BatchProducer.cu:24-27), so row blocks of a training batch follow this permutation.
+void refgpu_sample_numbers(void *p, int *out) {
+  Handle *h = (Handle *)p;
+  for (size_t i = 0; i < h->batch->sampleNumbers.size(); ++i) out[i] = h->batch->sampleNumbers[i];
+}
 // A learnt layer's weights as they are now (after a TRAINBATCH step: updated by the reference's SGD).
 void refgpu_layer_weights(void *p, int layer, float *W, float *B, float *prelu) {
   Quiet q;

@@ -381,6 +381,7 @@ struct Layer {
   int fmpKind = 0; float fmpShrink = 1;     // fractional max-pooling: tick kind (see makeTicks), shrink factor
   int inSpatial = 0, outSpatial = 0;
   std::vector<float> W, B, prelu;
+  std::vector<float> MW, MB, Mprelu; // momentum of the training step (zero until the first one)
 };
 
 struct Iface { // SpatiallySparseBatchInterface.h:19-46, host side only
@@ -389,6 +390,7 @@ struct Iface { // SpatiallySparseBatchInterface.h:19-46, host side only
   std::vector<int> rules;
   std::vector<float> features;
   std::vector<int> choices;
+  std::vector<float> dfeatures; // training step only: d cost / d features
 };
 
 struct Net {
@@ -473,6 +475,109 @@ struct Net {
     inputSpatialSize = s;
   }
 };
+
+// ------------------------------------------------------------------------------------------ backward pass
+// The reference's training step for one batch (SparseConvNetCUDA.cu:247-251: every layer's backwards() in
+// reverse order behind SoftmaxClassifier), restated for layers without training-time dropout.
+
+// SoftmaxClassifier.cu:7-14: d cost / d (softmax input) = probabilities - one_hot(label), not averaged over the batch.
+static void softmaxNllBackward(const float *probs, const int *labels, int rows, int N, float *d) {
+  for (int r = 0; r < rows; ++r)
+    for (int n = 0; n < N; ++n) d[(size_t)r * N + n] = probs[(size_t)r * N + n] - (n == labels[r] ? 1.0f : 0.0f);
+}
+// applySigmoidBackProp in place on the output's dfeatures, from the output's (activated) features
+// (SigmoidLayer.cu:224-268 and the kernels it dispatches to; softmax and NOSIGMOID pass through).  PReLU:
+// NetworkInNetworkPReLULayer.cu:25-38, which also accumulates the slope gradient sum_rows d * (b > 0 ? 0 : b / slope).
+template <class Acc>
+static void activationBackward(const float *b, float *d, long long rows, int N, int act, const float *prelu, float *dprelu) {
+  std::vector<Acc> ds(act == PRELU ? N : 0, (Acc)0);
+  for (long long r = 0; r < rows; ++r)
+    for (int n = 0; n < N; ++n) {
+      const size_t i = (size_t)r * N + n;
+      switch (act) {
+      case RELU: d[i] = b[i] > 0 ? d[i] : 0; break;
+      case VLEAKYRELU: d[i] = b[i] > 0 ? d[i] : d[i] * 0.333f; break;
+      case LEAKYRELU: d[i] = b[i] > 0 ? d[i] : d[i] * 0.01f; break;
+      case TANH: d[i] = d[i] * (1 + b[i]) * (1 - b[i]); break;
+      case SIGMOID: d[i] = d[i] * b[i] * (1 - b[i]); break;
+      case PRELU:
+        ds[n] += (Acc)d[i] * (b[i] > 0 ? (Acc)0 : (Acc)(b[i] / prelu[n]));
+        d[i] = b[i] > 0 ? d[i] : d[i] * prelu[n];
+        break;
+      default: break;
+      }
+    }
+  if (act == PRELU) for (int n = 0; n < N; ++n) dprelu[n] = (float)ds[n];
+}
+// NetworkInNetworkLayer.cu:226-239, 266-277 (no dropout): dW = X^T d, dB = column sums of d, dX = d W^T.
+template <class Acc>
+static void ninBackward(const float *X, const float *d, long long rows, int K, int N, const float *W, float *dW, float *dB, float *dX) {
+  std::vector<Acc> aw((size_t)K * N, (Acc)0), ab(N, (Acc)0);
+  for (long long r = 0; r < rows; ++r) {
+    const float *x = X + r * K, *dr = d + r * N;
+    for (int n = 0; n < N; ++n) ab[n] += dr[n];
+    for (int k = 0; k < K; ++k) {
+      const Acc xv = x[k];
+      if (xv == 0) continue;
+      Acc *a = aw.data() + (size_t)k * N;
+      for (int n = 0; n < N; ++n) a[n] += xv * (Acc)dr[n];
+    }
+  }
+  for (size_t i = 0; i < aw.size(); ++i) dW[i] = (float)aw[i];
+  for (int n = 0; n < N; ++n) dB[n] = (float)ab[n];
+  if (dX) {
+    std::vector<Acc> ax(K);
+    for (long long r = 0; r < rows; ++r) {
+      const float *dr = d + r * N;
+      for (int k = 0; k < K; ++k) {
+        const float *w = W + (size_t)k * N;
+        Acc t = 0;
+        for (int n = 0; n < N; ++n) t += (Acc)dr[n] * (Acc)w[n];
+        dX[r * K + k] = (float)t;
+      }
+    }
+  }
+}
+// NetworkInNetworkLayer.cu:26-40 ("NAG light"), one parameter array; keepPositive: the PReLU slopes' variant
+// (NetworkInNetworkPReLULayer.cu:67-84).
+static void sgdUpdate(float *w, float *m, const float *d, size_t n, float lr, float momentum, bool keepPositive = false) {
+  for (size_t i = 0; i < n; ++i) {
+    float wi = w[i], mi = m[i];
+    wi -= mi * momentum;
+    mi = momentum * mi - lr * (1 - momentum) * d[i];
+    wi += mi * (1 + momentum);
+    if (keepPositive) wi = (wi > 0.001) ? wi : 0.001f;
+    w[i] = wi; m[i] = mi;
+  }
+}
+// ConvolutionalLayer.cu:42-59: the gathered matrix's gradient added back onto the rows it was gathered from.
+template <class Acc>
+static void gatherBackward(const float *dConv, const int *rules, long long count, int nIn, long long rowsIn, float *dIn) {
+  std::vector<Acc> acc((size_t)rowsIn * nIn, (Acc)0);
+  for (long long c = 0; c < count; ++c)
+    if (rules[c] >= 0)
+      for (int j = 0; j < nIn; ++j) acc[(size_t)rules[c] * nIn + j] += dConv[c * nIn + j];
+  for (size_t i = 0; i < acc.size(); ++i) dIn[i] = (float)acc[i];
+}
+// MaxPoolingLayer.cu:74-80: the pooled gradient added onto the inputs the forward pass chose.
+template <class Acc>
+static void maxPoolBackward(const float *dOut, const int *choice, long long n, long long nIn, float *dIn) {
+  std::vector<Acc> acc((size_t)nIn, (Acc)0);
+  for (long long i = 0; i < n; ++i) if (choice[i] >= 0) acc[choice[i]] += dOut[i];
+  for (long long i = 0; i < nIn; ++i) dIn[i] = (float)acc[i];
+}
+// TerminalPoolingLayer.cu:48-62: every pooled input row receives the gradient divided by the number of rows pooled (stored, not added).
+static void terminalPoolBackward(const float *dOut, const int *rules, int count, int S, int C, long long rowsIn, float *dIn) {
+  std::fill(dIn, dIn + rowsIn * C, 0.0f);
+  for (int b = 0; b < count; ++b) {
+    int maxP = 0;
+    while (maxP < S && rules[b * S + maxP] >= 0) ++maxP;
+    for (int j = 0; j < C; ++j) {
+      const float t = dOut[b * C + j] / maxP;
+      for (int p = 0; p < maxP; ++p) dIn[(long long)rules[b * S + p] * C + j] = t;
+    }
+  }
+}
 
 // Every layer's preprocess() then forwards(), in the order BatchProducer.cu:72-75 and
 // SparseConvNetCUDA.cu:242-246 run them.  Input rows of sample b are [off[b], off[b+1]);
@@ -789,6 +894,86 @@ void orc_net_forward(void *h, int batch, const int64_t *keys, const int *off, co
     times[1] = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
   }
 }
+// One training step on one batch (TRAINBATCH without dropout): forward (fp32 or fp64 accumulation), SoftmaxClassifier,
+// then every layer's backwards() in reverse order with the SGD update of its weights.  Keeps every interface
+// (features and dfeatures) for orc_net_iface_fetch / orc_net_iface_dfeatures.  stats = {negativeLogLikelihood, mistakes}.
+// backpropErrors is false for the input and true from the first learnt layer's output on (NetworkInNetworkLayer.cu:155).
+int orc_net_train_step(void *h, int batch, const int64_t *keys, const int *off, const float *features, const int *labels,
+                       float learningRate, float momentum, int accum64, float *probs, double *stats) {
+  Net *net = (Net *)h;
+  for (const Layer &L : net->layers) if (L.type == L_NIN && L.dropout > 0) return 1; // training-time dropout draws random feature subsets: not restated
+  std::vector<std::vector<Ticks>> noTicks(net->layers.size());
+  std::vector<Iface> ifs;
+  forwardChunk(*net, batch, keys, off, features, accum64 != 0, ifs, nullptr, noTicks, 0);
+  const int nL = (int)net->layers.size();
+  Iface &top = ifs.back();
+  const int C = net->nClasses;
+  std::memcpy(probs, top.features.data(), sizeof(float) * (size_t)batch * C);
+  double nll = 0; int mistakes = batch;
+  for (int b = 0; b < batch; ++b) { // SoftmaxClassifier.cu:43-53
+    nll -= std::log(std::max(probs[(size_t)b * C + labels[b]], 1.0e-15f));
+    int best; topIndices(probs + (size_t)b * C, C, 1, &best);
+    if (best == labels[b]) --mistakes;
+  }
+  if (stats) { stats[0] = nll; stats[1] = mistakes; }
+  top.dfeatures.resize(top.features.size());
+  softmaxNllBackward(top.features.data(), labels, batch, C, top.dfeatures.data());
+  std::vector<char> backprop(nL + 1, 0);
+  for (int l = 0; l < nL; ++l) backprop[l + 1] = net->layers[l].type == L_NIN ? 1 : backprop[l];
+  for (int l = nL - 1; l >= 0; --l) {
+    Layer &L = net->layers[l];
+    Iface &in = ifs[l], &out = ifs[l + 1];
+    const long long rowsOut = out.nSpatialSites, rowsIn = in.nSpatialSites;
+    if (L.type == L_NIN) {
+      std::vector<float> dprelu(L.nOut, 0.f);
+      if (accum64) activationBackward<double>(out.features.data(), out.dfeatures.data(), rowsOut, L.nOut, L.act, L.prelu.empty() ? nullptr : L.prelu.data(), dprelu.data());
+      else activationBackward<float>(out.features.data(), out.dfeatures.data(), rowsOut, L.nOut, L.act, L.prelu.empty() ? nullptr : L.prelu.data(), dprelu.data());
+      std::vector<float> dW((size_t)L.nIn * L.nOut), dB(L.nOut);
+      if (backprop[l]) in.dfeatures.assign((size_t)rowsIn * L.nIn, 0.f);
+      float *dX = backprop[l] ? in.dfeatures.data() : nullptr;
+      if (accum64) ninBackward<double>(in.features.data(), out.dfeatures.data(), rowsOut, L.nIn, L.nOut, L.W.data(), dW.data(), dB.data(), dX);
+      else ninBackward<float>(in.features.data(), out.dfeatures.data(), rowsOut, L.nIn, L.nOut, L.W.data(), dW.data(), dB.data(), dX);
+      if (L.MW.empty()) { L.MW.assign(L.W.size(), 0.f); L.MB.assign(L.B.size(), 0.f); L.Mprelu.assign(L.prelu.size(), 0.f); }
+      sgdUpdate(L.W.data(), L.MW.data(), dW.data(), L.W.size(), learningRate, momentum);
+      sgdUpdate(L.B.data(), L.MB.data(), dB.data(), L.B.size(), learningRate, momentum);
+      if (L.act == PRELU) sgdUpdate(L.prelu.data(), L.Mprelu.data(), dprelu.data(), L.prelu.size(), learningRate, momentum, true);
+    } else if (!backprop[l]) {
+      continue;
+    } else if (L.type == L_CONV || L.type == L_CONV_TRI) {
+      in.dfeatures.resize((size_t)rowsIn * L.nIn);
+      if (accum64) gatherBackward<double>(out.dfeatures.data(), out.rules.data(), rowsOut * L.fs, L.nIn, rowsIn, in.dfeatures.data());
+      else gatherBackward<float>(out.dfeatures.data(), out.rules.data(), rowsOut * L.fs, L.nIn, rowsIn, in.dfeatures.data());
+    } else if (L.type == L_MAXPOOL || L.type == L_MAXPOOL_TRI || L.type == L_FMP) {
+      in.dfeatures.resize(in.features.size());
+      if (accum64) maxPoolBackward<double>(out.dfeatures.data(), out.choices.data(), (long long)out.dfeatures.size(), (long long)in.features.size(), in.dfeatures.data());
+      else maxPoolBackward<float>(out.dfeatures.data(), out.choices.data(), (long long)out.dfeatures.size(), (long long)in.features.size(), in.dfeatures.data());
+    } else if (L.type == L_TERMINAL) {
+      in.dfeatures.resize(in.features.size());
+      terminalPoolBackward(out.dfeatures.data(), out.rules.data(), (int)rowsOut, (int)(out.rules.size() / batch), L.nOut, rowsIn, in.dfeatures.data());
+    }
+  }
+  net->kept = std::move(ifs);
+  return 0;
+}
+// dfeatures of kept interface i after orc_net_train_step: returns their count, copies them if d is not null.
+long long orc_net_iface_dfeatures(void *h, int i, float *d) {
+  const Iface &I = ((Net *)h)->kept[i];
+  if (d && !I.dfeatures.empty()) std::memcpy(d, I.dfeatures.data(), I.dfeatures.size() * sizeof(float));
+  return (long long)I.dfeatures.size();
+}
+void orc_net_get_weights(void *h, int i, float *W, float *B, float *prelu) {
+  const Layer &L = ((Net *)h)->layers[i];
+  std::memcpy(W, L.W.data(), L.W.size() * sizeof(float));
+  std::memcpy(B, L.B.data(), L.B.size() * sizeof(float));
+  if (prelu && !L.prelu.empty()) std::memcpy(prelu, L.prelu.data(), L.prelu.size() * sizeof(float));
+}
+// Single backward operations, for layer-level tests.
+void orc_activation_backward(const float *b, float *d, long long rows, int N, int act, const float *prelu, float *dprelu) { activationBackward<double>(b, d, rows, N, act, prelu, dprelu); }
+void orc_nin_backward(const float *X, const float *d, long long rows, int K, int N, const float *W, float *dW, float *dB, float *dX) { ninBackward<double>(X, d, rows, K, N, W, dW, dB, dX); }
+void orc_gather_backward(const float *dConv, const int *rules, long long count, int nIn, long long rowsIn, float *dIn) { gatherBackward<double>(dConv, rules, count, nIn, rowsIn, dIn); }
+void orc_maxpool_backward(const float *dOut, const int *choice, long long n, long long nIn, float *dIn) { maxPoolBackward<double>(dOut, choice, n, nIn, dIn); }
+void orc_terminal_pool_backward(const float *dOut, const int *rules, int count, int S, int C, long long rowsIn, float *dIn) { terminalPoolBackward(dOut, rules, count, S, C, rowsIn, dIn); }
+void orc_sgd_update(float *w, float *m, const float *d, long long n, float lr, float momentum, int keepPositive) { sgdUpdate(w, m, d, (size_t)n, lr, momentum, keepPositive != 0); }
 // Kept interface i (0 = input): sizes[0..4] = nSpatialSites, nFeatures, spatialSize, rules.size(), choices.size()
 void orc_net_iface_sizes(void *h, int i, long long *sizes) {
   const Iface &I = ((Net *)h)->kept[i];

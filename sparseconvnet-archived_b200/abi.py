@@ -23,6 +23,8 @@ EXPORTS = [
     "scn_terminal_rules_build", "scn_conv_auto_precision", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_forward_dyn", "scn_conv_nin_maxpool_forward", "scn_conv_nin_nin_forward", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_conv_tc_error_word", "scn_classifier_result_bytes", "scn_classifier_result", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
+    "scn_softmax_nll_backward", "scn_activation_backward", "scn_conv_nin_backward_weights", "scn_transpose_weights", "scn_gather_backward",
+    "scn_maxpool_backward", "scn_terminal_pool_backward", "scn_sgd_update",
 ]
 
 
@@ -424,3 +426,63 @@ def background_rows(keys, off):
     bg = torch.empty(batch, dtype=torch.int32, device=keys.device)
     check(lib().scn_background_rows(_ptr(_i32(keys)), _ptr(_i32(off)), batch, _ptr(bg), _stream()))
     return bg
+
+
+# ---------------------------------------------------------------------------------------------- backward pass
+def softmax_nll_backward(probs, labels):
+    rows, C = probs.shape
+    d = torch.empty_like(probs)
+    check(lib().scn_softmax_nll_backward(_ptr(_f32(probs)), _ptr(_i32(labels)), rows, C, _ptr(d), _stream()))
+    return d
+
+
+def activation_backward(out_features, d, act, prelu=None):
+    """-> (d * f'(.) as a new tensor, slope gradient or None)."""
+    rows, N = out_features.shape
+    d = d.clone()
+    dpr = torch.zeros(N, dtype=torch.float32, device=d.device) if act == PRELU else None
+    check(lib().scn_activation_backward(_ptr(_f32(out_features)), _ptr(d), rows, N, act, _ptr(prelu), _ptr(dpr), _stream()))
+    return d, dpr
+
+
+def conv_nin_backward_weights(feat, rules, fs, dout):
+    """-> (dW [(fs*nIn) x N], dB [N])."""
+    nIn = feat.shape[1]
+    rows, N = dout.shape
+    K = fs * nIn if rules is not None else nIn
+    dW = torch.empty((K, N), dtype=torch.float32, device=dout.device)
+    dB = torch.empty(N, dtype=torch.float32, device=dout.device)
+    check(lib().scn_conv_nin_backward_weights(_ptr(_f32(feat)), None if rules is None else _ptr(_i32(rules)), rows, fs if rules is not None else 1,
+                                              nIn, _ptr(_f32(dout)), N, _ptr(dW), _ptr(dB), _stream()))
+    return dW, dB
+
+
+def transpose_weights(W):
+    K, N = W.shape
+    Wt = torch.empty((N, K), dtype=torch.float32, device=W.device)
+    check(lib().scn_transpose_weights(_ptr(_f32(W)), K, N, _ptr(Wt), _stream()))
+    return Wt
+
+
+def gather_backward(dconv, rules, nIn, rows_in):
+    din = torch.empty((rows_in, nIn), dtype=torch.float32, device=dconv.device)
+    check(lib().scn_gather_backward(_ptr(_f32(dconv)), _ptr(_i32(rules)), c_ll(rules.numel()), nIn, _ptr(din), c_ll(rows_in), _stream()))
+    return din
+
+
+def maxpool_backward(dout, choices, n_in):
+    din = torch.empty(n_in, dtype=torch.float32, device=dout.device)
+    check(lib().scn_maxpool_backward(_ptr(_f32(dout)), _ptr(_i32(choices)), c_ll(dout.numel()), _ptr(din), c_ll(n_in), _stream()))
+    return din
+
+
+def terminal_pool_backward(dout, rules, S, rows_in):
+    batch, C = dout.shape
+    din = torch.empty((rows_in, C), dtype=torch.float32, device=dout.device)
+    check(lib().scn_terminal_pool_backward(_ptr(_f32(dout)), _ptr(_i32(rules)), batch, S, C, _ptr(din), c_ll(rows_in), _stream()))
+    return din
+
+
+def sgd_update(w, m, d, lr, momentum, keep_positive=False):
+    """In place on w and m."""
+    check(lib().scn_sgd_update(_ptr(w), _ptr(m), _ptr(_f32(d)), c_ll(w.numel()), c_f(lr), c_f(momentum), int(keep_positive), _stream()))

@@ -1,0 +1,339 @@
+// Backward pass of the layers of the forward path (training step): the error at the softmax, the activation
+// derivatives, the learnt layers' weight / bias gradients with the convolution's gather read through the
+// rulebook inside the kernel, the scatter of the gathered matrix's gradient back onto the rows it came from,
+// the max-pooling and terminal-pooling gradients and the reference's SGD update.  The gradient with respect
+// to a learnt layer's input is its forward kernel run on the transposed weights (scn_conv_nin_forward_ws),
+// so it takes the tensor-core path wherever the forward does.
+#include "scn_common.cuh"
+#include <algorithm>
+
+namespace scn {
+namespace {
+
+// SoftmaxClassifier.cu:7-14: d cost / d (softmax input) = probabilities - one_hot(label).
+__global__ void k_softmax_nll_backward(const float *__restrict__ probs, const int *__restrict__ labels, long long n, int N, float *__restrict__ d) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / N;
+    const int c = (int)(i - r * N);
+    d[i] = probs[i] - (c == labels[r] ? 1.0f : 0.0f);
+  }
+}
+
+// applySigmoidBackProp in place (SigmoidLayer.cu:24-30, 62-68, 97-103, 137-143, 178-185): the derivative is
+// taken from the ACTIVATED features b, as the reference does.
+template <int ACT> __device__ __forceinline__ float act_backward(float b, float d, float slope) {
+  if (ACT == SCN_RELU) return b > 0.f ? d : 0.f;
+  if (ACT == SCN_VLEAKYRELU) return b > 0.f ? d : d * 0.333f;
+  if (ACT == SCN_LEAKYRELU) return b > 0.f ? d : d * 0.01f;
+  if (ACT == SCN_TANH) return d * (1.f + b) * (1.f - b);
+  if (ACT == SCN_SIGMOID) return d * b * (1.f - b);
+  if (ACT == SCN_PRELU) return b > 0.f ? d : d * slope;
+  return d;
+}
+template <int ACT>
+__global__ void k_activation_backward(const float *__restrict__ b, float *__restrict__ d, long long n4, const float *__restrict__ prelu, int N) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 bv = reinterpret_cast<const float4 *>(b)[i];
+    float4 dv = reinterpret_cast<float4 *>(d)[i];
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ACT == SCN_PRELU) s = *reinterpret_cast<const float4 *>(prelu + (int)((i * 4) % N));
+    dv.x = act_backward<ACT>(bv.x, dv.x, s.x); dv.y = act_backward<ACT>(bv.y, dv.y, s.y);
+    dv.z = act_backward<ACT>(bv.z, dv.z, s.z); dv.w = act_backward<ACT>(bv.w, dv.w, s.w);
+    reinterpret_cast<float4 *>(d)[i] = dv;
+  }
+}
+template <int ACT>
+__global__ void k_activation_backward_scalar(const float *__restrict__ b, float *__restrict__ d, long long n, const float *__restrict__ prelu, int N) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    d[i] = act_backward<ACT>(b[i], d[i], ACT == SCN_PRELU ? prelu[(int)(i % N)] : 0.f);
+}
+// PReLU slope gradient (NetworkInNetworkPReLULayer.cu:25-38): dprelu[c] = sum over rows of d * (b > 0 ? 0 : b / slope), taken
+// BEFORE d is scaled.  One warp per 32 columns and chunk of rows; partial sums meet in dprelu by atomic adds.
+__global__ void k_prelu_slope_gradient(const float *__restrict__ b, const float *__restrict__ d, int rows, int N, const float *__restrict__ prelu,
+                                       float *__restrict__ dprelu, int rowsPerChunk) {
+  const int c = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int r0 = blockIdx.y * rowsPerChunk + (threadIdx.x >> 5), r1 = min(rows, (blockIdx.y + 1) * rowsPerChunk);
+  if (c >= N) return;
+  const float slope = prelu[c];
+  float t = 0.f;
+  for (int r = r0; r < r1; r += blockDim.x >> 5) {
+    const float bv = b[(long long)r * N + c];
+    t += d[(long long)r * N + c] * (bv > 0.f ? 0.f : bv / slope);
+  }
+  atomicAdd(dprelu + c, t);
+}
+
+// dW[K x N] = X^T d and dB[N] = column sums of d (NetworkInNetworkLayer.cu:226-239), X being the layer's input: either a
+// plain [rows x K] matrix or (GATHER) the convolution's gathered matrix, read through the rulebook as the forward kernel
+// reads it (column k = f * nIn + c of row r is input row rules[r * fs + f], channel c; a negative rule is a zero row).
+// 64 x 64 output tile per CTA, 4 x 4 per thread, rows split into chunks over gridDim.z whose partial sums meet by atomic adds.
+constexpr int BW_T = 64, BW_R = 16;
+template <bool GATHER>
+__global__ void __launch_bounds__(256) k_backward_weights(const float *__restrict__ in, const int *__restrict__ rules, int rows, int fs, int nIn,
+                                                          const float *__restrict__ dout, int N, float *__restrict__ dW, float *__restrict__ dB,
+                                                          int rowsPerChunk) {
+  __shared__ __align__(16) float As[BW_R][BW_T];
+  __shared__ __align__(16) float Ds[BW_R][BW_T];
+  const int K = fs * nIn;
+  const int k0 = blockIdx.x * BW_T, n0 = blockIdx.y * BW_T;
+  const int r0 = blockIdx.z * rowsPerChunk, r1 = min(rows, r0 + rowsPerChunk);
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  float acc[4][4] = {};
+  float colsum[4] = {0.f, 0.f, 0.f, 0.f};
+  // each thread stages 4 elements of each tile per step: element e = tid + 256 * i -> (row e / 64, column e % 64)
+  int kk[4], ff[4], cc[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int e = tid + 256 * i;
+    kk[i] = k0 + (e & 63);
+    ff[i] = GATHER ? kk[i] / nIn : 0;
+    cc[i] = GATHER ? kk[i] - ff[i] * nIn : kk[i];
+  }
+  for (int rb = r0; rb < r1; rb += BW_R) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = tid + 256 * i, rr = e >> 6, r = rb + rr;
+      float a = 0.f, dv = 0.f;
+      if (r < r1) {
+        if (kk[i] < K) {
+          if (GATHER) {
+            const int rule = rules[(long long)r * fs + ff[i]];
+            if (rule >= 0) a = in[(long long)rule * nIn + cc[i]];
+          } else {
+            a = in[(long long)r * K + kk[i]];
+          }
+        }
+        const int n = n0 + (e & 63);
+        if (n < N) dv = dout[(long long)r * N + n];
+      }
+      As[rr][e & 63] = a;
+      Ds[rr][e & 63] = dv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int rr = 0; rr < BW_R; ++rr) {
+      const float4 a = *reinterpret_cast<const float4 *>(&As[rr][ty * 4]);
+      const float4 dv = *reinterpret_cast<const float4 *>(&Ds[rr][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, dd[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], dd[j], acc[i][j]);
+      if (ty == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) colsum[j] += dd[j];
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int k = k0 + ty * 4 + i;
+    if (k >= K) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) atomicAdd(dW + (long long)k * N + n, acc[i][j]);
+    }
+  }
+  if (blockIdx.x == 0 && ty == 0 && dB) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) atomicAdd(dB + n, colsum[j]);
+    }
+  }
+}
+
+// out[n * K + k] = in[k * N + n]  (32 x 32 tiles through shared memory)
+__global__ void k_transpose(const float *__restrict__ in, int K, int N, float *__restrict__ out) {
+  __shared__ float tile[32][33];
+  const int kb = blockIdx.x * 32, nb = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int k = kb + i, n = nb + threadIdx.x;
+    tile[i][threadIdx.x] = (k < K && n < N) ? in[(long long)k * N + n] : 0.f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int n = nb + i, k = kb + threadIdx.x;
+    if (n < N && k < K) out[(long long)n * K + k] = tile[threadIdx.x][i];
+  }
+}
+
+// ConvolutionalLayer.cu:42-59: dIn[rules[c]] += dConv[c] for every rule cell c with a non-negative rule; a warp takes
+// a cell's nIn channels, consecutive lanes consecutive channels.
+__global__ void k_gather_backward(const float *__restrict__ dconv, const int *__restrict__ rules, long long count, int nIn, float *__restrict__ din) {
+  const long long total = count * nIn;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long c = i / nIn;
+    const int j = (int)(i - c * nIn);
+    const int rule = rules[c];
+    if (rule >= 0) atomicAdd(din + (long long)rule * nIn + j, dconv[i]);
+  }
+}
+
+// MaxPoolingLayer.cu:74-80: the pooled gradient goes to the input the forward pass chose (windows may overlap: atomic adds).
+__global__ void k_maxpool_backward(const float *__restrict__ dout, const int *__restrict__ choice, long long n, float *__restrict__ din) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int c = choice[i];
+    if (c >= 0) atomicAdd(din + c, dout[i]);
+  }
+}
+
+// TerminalPoolingLayer.cu:48-62: every row a sample pooled receives the sample's gradient divided by their number.
+__global__ void k_terminal_pool_backward(const float *__restrict__ dout, const int *__restrict__ rules, int S, int C, float *__restrict__ din) {
+  const int b = blockIdx.x;
+  int maxP = 0;
+  while (maxP < S && rules[(long long)b * S + maxP] >= 0) ++maxP;
+  for (int j = threadIdx.x; j < C; j += blockDim.x) {
+    const float t = dout[(long long)b * C + j] / maxP;
+    for (int p = 0; p < maxP; ++p) din[(long long)rules[(long long)b * S + p] * C + j] = t;
+  }
+}
+
+// NetworkInNetworkLayer.cu:26-40 ("NAG light"); keepPositive: the PReLU slopes' variant, which holds the result at 0.001 or
+// above (NetworkInNetworkPReLULayer.cu:67-84).
+__global__ void k_sgd_update(float *__restrict__ w, float *__restrict__ m, const float *__restrict__ d, long long n, float lr, float momentum,
+                             int keepPositive) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float wi = w[i], mi = m[i];
+    wi -= mi * momentum;
+    mi = momentum * mi - lr * (1 - momentum) * d[i];
+    wi += mi * (1 + momentum);
+    if (keepPositive) wi = wi > 0.001f ? wi : 0.001f;
+    w[i] = wi;
+    m[i] = mi;
+  }
+}
+
+} // namespace
+} // namespace scn
+
+using namespace scn;
+
+extern "C" int scn_softmax_nll_backward(const float *d_probs, const int *d_labels, int rows, int nClasses, float *d_dfeatures, scn_stream_t stream) {
+  clear_error();
+  if (rows < 0 || nClasses < 1) return fail(SCN_ERR_INVALID, "bad softmax sizes");
+  if (rows == 0) return SCN_OK;
+  if (!d_probs || !d_labels || !d_dfeatures) return fail(SCN_ERR_INVALID, "null pointer");
+  const long long n = (long long)rows * nClasses;
+  k_softmax_nll_backward<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(d_probs, d_labels, n, nClasses, d_dfeatures);
+  SCN_LAUNCH_CHECK("k_softmax_nll_backward");
+  return SCN_OK;
+}
+
+extern "C" int scn_activation_backward(const float *d_out_features, float *d_dfeatures, int rows, int N, int act, const float *d_prelu,
+                                       float *d_dprelu, scn_stream_t stream) {
+  clear_error();
+  if (rows < 0 || N < 1) return fail(SCN_ERR_INVALID, "bad activation sizes");
+  if (act < SCN_NOSIGMOID || act > SCN_SIGMOID) return fail(SCN_ERR_INVALID, "unknown activation");
+  if (act == SCN_PRELU && (!d_prelu || !d_dprelu)) return fail(SCN_ERR_INVALID, "PReLU needs its slopes and a place for their gradient");
+  if (rows == 0 || act == SCN_NOSIGMOID || act == SCN_SOFTMAX) return SCN_OK; // softmax: the classifier's gradient is already taken at its input
+  if (!d_out_features || !d_dfeatures) return fail(SCN_ERR_INVALID, "null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (act == SCN_PRELU) {
+    SCN_CUDA_TRY(cudaMemsetAsync(d_dprelu, 0, sizeof(float) * N, s));
+    const int chunks = std::max(1, std::min((rows + 63) / 64, 4 * sm_count() / ((N + 31) / 32) + 1));
+    const int rowsPerChunk = (rows + chunks - 1) / chunks;
+    k_prelu_slope_gradient<<<dim3((N + 31) / 32, chunks), 256, 0, s>>>(d_out_features, d_dfeatures, rows, N, d_prelu, d_dprelu, rowsPerChunk);
+    SCN_LAUNCH_CHECK("k_prelu_slope_gradient");
+  }
+  const long long n = (long long)rows * N;
+  const bool vec = N % 4 == 0 && (((uintptr_t)d_out_features | (uintptr_t)d_dfeatures | (uintptr_t)d_prelu) & 15) == 0;
+  if (vec) { SCN_DISPATCH_ACT(act, (k_activation_backward<ACT><<<grid_for(n / 4, 256), 256, 0, s>>>(d_out_features, d_dfeatures, n / 4, d_prelu, N))); }
+  else { SCN_DISPATCH_ACT(act, (k_activation_backward_scalar<ACT><<<grid_for(n, 256), 256, 0, s>>>(d_out_features, d_dfeatures, n, d_prelu, N))); }
+  SCN_LAUNCH_CHECK("k_activation_backward");
+  return SCN_OK;
+}
+
+extern "C" int scn_conv_nin_backward_weights(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const float *d_dout, int N,
+                                             float *d_dW, float *d_dB, scn_stream_t stream) {
+  clear_error();
+  if (rows < 0 || fs < 1 || nIn < 1 || N < 1) return fail(SCN_ERR_INVALID, "bad conv/NiN sizes");
+  if (!d_rules && fs != 1) return fail(SCN_ERR_INVALID, "fs must be 1 without rules");
+  if (!d_dW) return fail(SCN_ERR_INVALID, "null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int K = fs * nIn;
+  SCN_CUDA_TRY(cudaMemsetAsync(d_dW, 0, sizeof(float) * (size_t)K * N, s));
+  if (d_dB) SCN_CUDA_TRY(cudaMemsetAsync(d_dB, 0, sizeof(float) * N, s));
+  if (rows == 0) return SCN_OK;
+  if (!d_in || !d_dout) return fail(SCN_ERR_INVALID, "null pointer");
+  const int tk = (K + BW_T - 1) / BW_T, tn = (N + BW_T - 1) / BW_T;
+  int chunks = std::max(1, 6 * sm_count() / (tk * tn));
+  chunks = std::min(chunks, (rows + 4 * BW_R - 1) / (4 * BW_R));
+  chunks = std::max(1, std::min(chunks, 65535));
+  int rowsPerChunk = (rows + chunks - 1) / chunks;
+  rowsPerChunk = (rowsPerChunk + BW_R - 1) / BW_R * BW_R;
+  chunks = (rows + rowsPerChunk - 1) / rowsPerChunk;
+  const dim3 grid(tk, tn, chunks);
+  if (d_rules) k_backward_weights<true><<<grid, 256, 0, s>>>(d_in, d_rules, rows, fs, nIn, d_dout, N, d_dW, d_dB, rowsPerChunk);
+  else k_backward_weights<false><<<grid, 256, 0, s>>>(d_in, nullptr, rows, 1, nIn, d_dout, N, d_dW, d_dB, rowsPerChunk);
+  SCN_LAUNCH_CHECK("k_backward_weights");
+  return SCN_OK;
+}
+
+extern "C" int scn_transpose_weights(const float *d_W, int K, int N, float *d_Wt, scn_stream_t stream) {
+  clear_error();
+  if (K < 1 || N < 1 || !d_W || !d_Wt) return fail(SCN_ERR_INVALID, "bad transpose arguments");
+  k_transpose<<<dim3((K + 31) / 32, (N + 31) / 32), dim3(32, 8), 0, (cudaStream_t)stream>>>(d_W, K, N, d_Wt);
+  SCN_LAUNCH_CHECK("k_transpose");
+  return SCN_OK;
+}
+
+extern "C" int scn_gather_backward(const float *d_dconv, const int *d_rules, long long count, int nIn, float *d_din, long long rows_in,
+                                   scn_stream_t stream) {
+  clear_error();
+  if (count < 0 || nIn < 1 || rows_in < 0) return fail(SCN_ERR_INVALID, "bad gather sizes");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (rows_in > 0) {
+    if (!d_din) return fail(SCN_ERR_INVALID, "null pointer");
+    SCN_CUDA_TRY(cudaMemsetAsync(d_din, 0, sizeof(float) * (size_t)rows_in * nIn, s));
+  }
+  if (count == 0) return SCN_OK;
+  if (!d_dconv || !d_rules || !d_din) return fail(SCN_ERR_INVALID, "null pointer");
+  k_gather_backward<<<grid_for(count * nIn, 256), 256, 0, s>>>(d_dconv, d_rules, count, nIn, d_din);
+  SCN_LAUNCH_CHECK("k_gather_backward");
+  return SCN_OK;
+}
+
+extern "C" int scn_maxpool_backward(const float *d_dout, const int *d_choices, long long n, float *d_din, long long n_in, scn_stream_t stream) {
+  clear_error();
+  if (n < 0 || n_in < 0) return fail(SCN_ERR_INVALID, "bad pooling sizes");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (n_in > 0) {
+    if (!d_din) return fail(SCN_ERR_INVALID, "null pointer");
+    SCN_CUDA_TRY(cudaMemsetAsync(d_din, 0, sizeof(float) * (size_t)n_in, s));
+  }
+  if (n == 0) return SCN_OK;
+  if (!d_dout || !d_choices || !d_din) return fail(SCN_ERR_INVALID, "null pointer");
+  k_maxpool_backward<<<grid_for(n, 256), 256, 0, s>>>(d_dout, d_choices, n, d_din);
+  SCN_LAUNCH_CHECK("k_maxpool_backward");
+  return SCN_OK;
+}
+
+extern "C" int scn_terminal_pool_backward(const float *d_dout, const int *d_rules, int batch, int S, int C, float *d_din, long long rows_in,
+                                          scn_stream_t stream) {
+  clear_error();
+  if (batch < 0 || S < 1 || C < 1 || rows_in < 0) return fail(SCN_ERR_INVALID, "bad terminal pooling sizes");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (rows_in > 0) {
+    if (!d_din) return fail(SCN_ERR_INVALID, "null pointer");
+    SCN_CUDA_TRY(cudaMemsetAsync(d_din, 0, sizeof(float) * (size_t)rows_in * C, s));
+  }
+  if (batch == 0) return SCN_OK;
+  if (!d_dout || !d_rules || !d_din) return fail(SCN_ERR_INVALID, "null pointer");
+  k_terminal_pool_backward<<<batch, 128, 0, s>>>(d_dout, d_rules, S, C, d_din);
+  SCN_LAUNCH_CHECK("k_terminal_pool_backward");
+  return SCN_OK;
+}
+
+extern "C" int scn_sgd_update(float *d_w, float *d_momentum, const float *d_delta, long long n, float learningRate, float momentum,
+                              int keep_positive, scn_stream_t stream) {
+  clear_error();
+  if (n < 0) return fail(SCN_ERR_INVALID, "bad size");
+  if (n == 0) return SCN_OK;
+  if (!d_w || !d_momentum || !d_delta) return fail(SCN_ERR_INVALID, "null pointer");
+  k_sgd_update<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(d_w, d_momentum, d_delta, n, learningRate, momentum, keep_positive);
+  SCN_LAUNCH_CHECK("k_sgd_update");
+  return SCN_OK;
+}

@@ -22,6 +22,11 @@ BatchProducer::BatchProducer(SparseConvNetCUDA &cnn, SpatiallySparseDataset &dat
     : cnn(cnn), dataset(dataset), spatialSize(spatialSize), batchSize(batchSize), nextToServe(0), lastServedSlot(-1), stop(false) {
   if (batchSize < 1) throw ScnException("BatchProducer: batchSize must be positive");
   nBatches = ((int)dataset.pictures.size() + batchSize - 1) / batchSize;
+  permutation = range((int)dataset.pictures.size());
+  if (dataset.type == TRAINBATCH) { // BatchProducer.cu:23-27
+    RNG rng;
+    rng.vectorShuffle(permutation);
+  }
   slotState.assign(cnn.nBatchProducerThreads, -1);
   for (auto &b : cnn.batchPool) cnn.prepareBatch(b);
   for (int t = 0; t < cnn.nBatchProducerThreads; ++t) workers.emplace_back(&BatchProducer::worker, this, t);
@@ -47,13 +52,13 @@ void BatchProducer::preprocessBatch(int c, int cc) {
   b.labels.copyToCPU();
   const int lo = c * batchSize, hi = std::min((c + 1) * batchSize, (int)dataset.pictures.size());
   for (int i = lo; i < hi; ++i) {
-    Picture *pic = dataset.pictures[i]->distort(0, dataset.type);
-    b.sampleNumbers.push_back(i);
+    Picture *pic = dataset.pictures[permutation[i]]->distort(0, dataset.type);
+    b.sampleNumbers.push_back(permutation[i]);
     b.batchSize++;
     in.grids.push_back(SparseGrid());
     b.labels.hVector().push_back(pic->label);
     pic->codifyInputData(in.grids.back(), feat, in.nSpatialSites, spatialSize);
-    if (pic != dataset.pictures[i]) delete pic;
+    if (pic != dataset.pictures[permutation[i]]) delete pic;
   }
   if ((int)feat.size() != in.nFeatures * in.nSpatialSites) throw ScnException("codifyInputData wrote a wrong number of features");
   if (!cnn.inputNormalizingConstants.empty())

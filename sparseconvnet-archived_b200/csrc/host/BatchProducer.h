@@ -8,6 +8,7 @@
 #include <mutex>
 #include <thread>
 #include <vector>
+#include "Rng.h"
 #include "SparseConvNetCUDA.h"
 #include "SpatiallySparseDataset.h"
 
@@ -18,6 +19,7 @@ public:
   int spatialSize;
   int batchSize;
   int nBatches;
+  std::vector<int> permutation; // picture order: shuffled for a TRAINBATCH dataset (BatchProducer.cu:23-27)
   BatchProducer(SparseConvNetCUDA &cnn, SpatiallySparseDataset &dataset, int spatialSize, int batchSize);
   ~BatchProducer();
   // Next batch, uploaded and preprocessed, or nullptr after the last one.

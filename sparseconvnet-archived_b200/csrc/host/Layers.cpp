@@ -18,8 +18,14 @@
 using rulechain::preprocessNow;
 
 namespace {
-void requireInference(const SpatiallySparseBatch &batch) {
-  if (batch.type == TRAINBATCH) throw ScnException("TRAINBATCH: this is an inference library (TESTBATCH, UNLABELEDBATCH, RESCALEBATCH only)");
+// Every batch type runs the same forward kernels; a TRAINBATCH is refused only by learnt layers that would have to draw a
+// dropout subset (see NetworkInNetworkLayer::enqueueRules).
+void requireInference(const SpatiallySparseBatch &) {}
+// Zeroed device vector of n elements.
+void zeroed(vectorCUDA<float> &v, int n, cudaMemStream &ms) {
+  v.copyToGPU();
+  v.resize(n);
+  if (n) cudaSafeCall(cudaMemsetAsync(v.dPtr(), 0, sizeof(float) * (size_t)n, ms.stream));
 }
 // Shared body of the four region layers' finishRules().
 void finishGeometry(const scn_regions_t &R, SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
@@ -390,8 +396,8 @@ int TerminalPoolingLayer::calculateInputSpatialSize(int outputSpatialSize) {
 NetworkInNetworkLayer::NetworkInNetworkLayer(cudaMemStream &memStream, cublasHandle_t &, int nFeaturesIn, int nFeaturesOut, float dropout,
                                              ActivationFunction fn, float alpha)
     : SpatiallySparseLayer(memStream), W(false, nFeaturesIn * nFeaturesOut), MW(false, 0), B(false, nFeaturesOut), MB(false, 0), fn(fn),
-      nFeaturesIn(nFeaturesIn), nFeaturesOut(nFeaturesOut), dropout(dropout), precision(SCN_PREC_AUTO), fusePoolNext(false), precisionFallback(false), packed(nullptr), packedBytes(0),
-      packedPrecision(-100), packedFs(0) {
+      nFeaturesIn(nFeaturesIn), nFeaturesOut(nFeaturesOut), dropout(dropout), precision(SCN_PREC_AUTO), fusePoolNext(false), precisionFallback(false), packedT(nullptr), packedTBytes(0), packed(nullptr),
+      packedBytes(0), packedPrecision(-100), packedFs(0) {
   // uniform(+-sqrt(6/(nIn + nOut*alpha))) as NetworkInNetworkLayer.cu:135-137, from a fixed
   // seed (the reference seeds from the clock); real runs load weights.
   const float scale = std::pow(6.0f / (nFeaturesIn + nFeaturesOut * alpha), 0.5f);
@@ -401,8 +407,13 @@ NetworkInNetworkLayer::NetworkInNetworkLayer(cudaMemStream &memStream, cublasHan
   B.setZero();
   std::cout << "Learn " << nFeaturesIn << "->" << nFeaturesOut << " dropout=" << dropout << " " << sigmoidNames[fn] << std::endl;
 }
-NetworkInNetworkLayer::~NetworkInNetworkLayer() { if (packed) cudaFree(packed); }
+NetworkInNetworkLayer::~NetworkInNetworkLayer() {
+  if (packed) cudaFree(packed);
+  if (packedT) cudaFree(packedT);
+}
 float *NetworkInNetworkLayer::slopes() { return nullptr; }
+float *NetworkInNetworkLayer::slopeGradient() { return nullptr; }
+void NetworkInNetworkLayer::updateSlopes(float, float) {}
 void NetworkInNetworkLayer::weightsChanged() { packedPrecision = -100; }
 const void *NetworkInNetworkLayer::packedWeights(int fs, int nIn, int prec) {
   if (prec == SCN_PREC_FP32) return nullptr;
@@ -422,7 +433,9 @@ const void *NetworkInNetworkLayer::packedWeights(int fs, int nIn, int prec) {
 }
 long long NetworkInNetworkLayer::enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
                                               SpatiallySparseBatchInterface &output, long long rowsInBound, int *) {
-  requireInference(batch);
+  if (batch.type == TRAINBATCH && dropout > 0)
+    throw ScnException("NetworkInNetworkLayer: training with dropout (random feature subsets, NetworkInNetworkLayer.cu:152-154) is not built; "
+                       "build the network with dropout 0 to train it");
   if (input.nFeatures != nFeaturesIn) throw ScnException("NetworkInNetworkLayer: wrong number of input features");
   output.nFeatures = nFeaturesOut;
   output.spatialSize = input.spatialSize;
@@ -655,6 +668,11 @@ void SoftmaxClassifier(SpatiallySparseBatchInterface &input, SpatiallySparseBatc
   if (batch.batchSize != input.nSpatialSites) throw ScnException("SoftmaxClassifier: the top layer must hold one row per sample");
   const int n = batch.batchSize, C = input.nFeatures;
   const size_t pb = sizeof(float) * (size_t)n * C;
+  if (batch.type == TRAINBATCH) { // the backward pass starts here: d cost / d (softmax input), SoftmaxClassifier.cu:24-33
+    if (batch.labels.size() != (unsigned)n) throw ScnException("SoftmaxClassifier: a TRAINBATCH needs one label per sample");
+    input.sub->dfeatures.resize(n * C);
+    scnSafeCall(scn_softmax_nll_backward(input.sub->features.dPtr(), batch.labels.dPtr(), n, C, input.sub->dfeatures.dPtr(), memStream.stream));
+  }
   const char *stage = fetchClassifierResult(input, n, nTop, memStream);
   const float *probs = (const float *)stage;
   const int *pred = (const int *)(stage + pb);
@@ -675,4 +693,143 @@ void SoftmaxClassifier(SpatiallySparseBatchInterface &input, SpatiallySparseBatc
         if (batch.predictions[i][j] == labels[i]) batch.mistakes--;
     }
   }
+}
+
+// ------------------------------------------------------------------ backward pass (training step)
+// ConvolutionalLayer.cu:134-146.  Behind a fused gather the learnt layer's backwards() has already scattered its input
+// gradient through the rulebook onto this layer's input, so nothing is left to do here.
+void ConvolutionalLayer::backwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float, float) {
+  if (!input.backpropErrors || output.deferredFrom) return;
+  const int nIn = input.featuresPresent.size();
+  input.sub->dfeatures.resize(input.nSpatialSites * nIn);
+  scnSafeCall(scn_gather_backward(output.sub->dfeatures.dPtr(), output.rules.dPtr(), (long long)output.nSpatialSites * fs, nIn,
+                                  input.sub->dfeatures.dPtr(), input.nSpatialSites, memStream.stream));
+}
+void ConvolutionalTriangularLayer::backwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float,
+                                             float) {
+  if (!input.backpropErrors || output.deferredFrom) return;
+  const int nIn = input.featuresPresent.size();
+  input.sub->dfeatures.resize(input.nSpatialSites * nIn);
+  scnSafeCall(scn_gather_backward(output.sub->dfeatures.dPtr(), output.rules.dPtr(), (long long)output.nSpatialSites * fs, nIn,
+                                  input.sub->dfeatures.dPtr(), input.nSpatialSites, memStream.stream));
+}
+// MaxPoolingLayer.cu:134-146 (and MaxPoolingTriangularLayer.cu:49-61).
+static void poolBackwards(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, cudaMemStream &ms) {
+  if (!input.backpropErrors) return;
+  const long long nIn = (long long)input.nSpatialSites * input.featuresPresent.size();
+  const long long n = (long long)output.nSpatialSites * output.featuresPresent.size();
+  if (output.sub->poolingChoices.size() != (unsigned)n) throw ScnException("max pooling backwards: no pooling choices (run forwards first)");
+  input.sub->dfeatures.resize((int)nIn);
+  scnSafeCall(scn_maxpool_backward(output.sub->dfeatures.dPtr(), output.sub->poolingChoices.dPtr(), n, input.sub->dfeatures.dPtr(), nIn, ms.stream));
+}
+void MaxPoolingLayer::backwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float, float) {
+  poolBackwards(input, output, memStream);
+}
+void MaxPoolingTriangularLayer::backwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float,
+                                          float) {
+  poolBackwards(input, output, memStream);
+}
+// MaxPoolingLayer.cu:187-199 and its three siblings: the same gradient routing through the pooling choices.
+void FractionalMaxPoolingLayerBase::backwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float,
+                                              float) {
+  poolBackwards(input, output, memStream);
+}
+// TerminalPoolingLayer.cu:112-125.
+void TerminalPoolingLayer::backwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float,
+                                     float) {
+  if (!input.backpropErrors) return;
+  const int C = output.featuresPresent.size();
+  input.sub->dfeatures.resize(input.nSpatialSites * C);
+  scnSafeCall(scn_terminal_pool_backward(output.sub->dfeatures.dPtr(), output.rules.dPtr(), output.nSpatialSites, output.rules.size() / batch.batchSize,
+                                         C, input.sub->dfeatures.dPtr(), input.nSpatialSites, memStream.stream));
+}
+// NetworkInNetworkLayer.cu:221-289 for a layer without dropout: activation derivative in place on the output's gradient;
+// dW = X^T d and dB = column sums (X read through the rulebook where the convolution in front is fused); the input's
+// gradient d W^T with the weights as they were in the forward pass, scattered through the rulebook onto the
+// convolution's input where fused; then the SGD update of W, B (and the PReLU slopes).
+void NetworkInNetworkLayer::backwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                                      float learningRate, float momentum) {
+  if (dropout > 0) throw ScnException("NetworkInNetworkLayer::backwards: training with dropout is not built");
+  (void)batch;
+  const int rows = output.nSpatialSites, N = nFeaturesOut, K = nFeaturesIn;
+  cudaStream_t s = memStream.stream;
+  if ((int)output.sub->dfeatures.size() != rows * N) throw ScnException("NetworkInNetworkLayer::backwards: the output's gradient is missing");
+  if ((int)output.sub->features.size() != rows * N) throw ScnException("NetworkInNetworkLayer::backwards: the output's features are missing (run forwards on a TRAINBATCH)");
+  float *d = output.sub->dfeatures.dPtr();
+  scnSafeCall(scn_activation_backward(output.sub->features.dPtr(), d, rows, N, (int)fn, slopes(), slopeGradient(), s));
+  const float *src;
+  const int *rules = nullptr;
+  int fs = 1, nIn = K;
+  SpatiallySparseBatchInterface *target = &input; // whose dfeatures receive the input gradient
+  if (input.deferredFrom) {
+    target = input.deferredFrom;
+    src = target->sub->features.dPtr();
+    rules = input.rules.dPtr();
+    fs = input.deferredCells;
+    nIn = K / fs;
+  } else {
+    src = input.sub->features.dPtr();
+  }
+  dw.copyToGPU(); db.copyToGPU();
+  dw.resize(K * N); db.resize(N);
+  scnSafeCall(scn_conv_nin_backward_weights(src, rules, rows, fs, nIn, d, N, dw.dPtr(), db.dPtr(), s));
+  if (input.backpropErrors && rows > 0) {
+    Wt.copyToGPU();
+    Wt.resize(K * N);
+    scnSafeCall(scn_transpose_weights(W.dPtr(), K, N, Wt.dPtr(), s));
+    if ((int)zeroBias.size() != K) zeroed(zeroBias, K, memStream);
+    // the forward kernel on the transposed weights: [rows x N] times [N x K]
+    int prec = precision == SCN_PREC_AUTO ? scn_conv_auto_precision() : precision;
+    const void *pk = nullptr;
+    if (prec != SCN_PREC_FP32 && K % 4 == 0) {
+      const size_t need = scn_conv_packed_weight_bytes(N, K, prec);
+      if (need) {
+        if (need > packedTBytes) {
+          if (packedT) cudaSafeCall(cudaFree(packedT));
+          packedT = nullptr;
+          cudaSafeCall(cudaMalloc(&packedT, need));
+          packedTBytes = need;
+        }
+        scnSafeCall(scn_conv_pack_weights(Wt.dPtr(), N, K, prec, packedT, s));
+        pk = packedT;
+      }
+    }
+    if (!pk) prec = SCN_PREC_FP32;
+    float *dX;
+    if (rules) {
+      dGathered.copyToGPU();
+      dGathered.resize(rows * K);
+      dX = dGathered.dPtr();
+    } else {
+      input.sub->dfeatures.resize(rows * K);
+      dX = input.sub->dfeatures.dPtr();
+    }
+    void *ws = nullptr;
+    const size_t wsBytes = pk ? scn_conv_nin_workspace_bytes(rows, 1, N, K, prec) : 0;
+    if (wsBytes) {
+      splitScratch.resize((int)((wsBytes + sizeof(float) - 1) / sizeof(float)));
+      ws = splitScratch.dPtr();
+    }
+    scnSafeCall(scn_conv_nin_forward_ws(d, nullptr, rows, 1, N, Wt.dPtr(), pk, zeroBias.dPtr(), nullptr, K, 1.0f, SCN_NOSIGMOID, prec, dX, ws, wsBytes, s));
+    multiplyAddCount += (__int128_t)rows * K * N;
+    if (rules) {
+      target->sub->dfeatures.resize(target->nSpatialSites * nIn);
+      scnSafeCall(scn_gather_backward(dX, rules, (long long)rows * fs, nIn, target->sub->dfeatures.dPtr(), target->nSpatialSites, s));
+    }
+  }
+  multiplyAddCount += (__int128_t)rows * K * N;
+  if ((int)MW.size() != K * N) { zeroed(MW, K * N, memStream); zeroed(MB, N, memStream); }
+  scnSafeCall(scn_sgd_update(W.dPtr(), MW.dPtr(), dw.dPtr(), (long long)K * N, learningRate, momentum, 0, s));
+  scnSafeCall(scn_sgd_update(B.dPtr(), MB.dPtr(), db.dPtr(), N, learningRate, momentum, 0, s));
+  updateSlopes(learningRate, momentum);
+  weightsChanged();
+}
+float *NetworkInNetworkPReLULayer::slopeGradient() {
+  dprelu.copyToGPU();
+  dprelu.resize(nFeaturesOut);
+  return dprelu.dPtr();
+}
+void NetworkInNetworkPReLULayer::updateSlopes(float learningRate, float momentum) {
+  if ((int)MPReLU.size() != nFeaturesOut) zeroed(MPReLU, nFeaturesOut, memStream);
+  scnSafeCall(scn_sgd_update(PReLU.dPtr(), MPReLU.dPtr(), dprelu.dPtr(), nFeaturesOut, learningRate, momentum, 1, memStream.stream));
 }

@@ -16,6 +16,8 @@ public:
   MaxPoolingLayer(cudaMemStream &memStream, int poolSize, int poolStride, int dimension);
   void preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
   void forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
+  void backwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float learningRate,
+                 float momentum);
   int calculateInputSpatialSize(int outputSpatialSize);
   long long enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
                          long long rowsInBound, int *d_result);
@@ -35,6 +37,8 @@ public:
   FractionalMaxPoolingLayerBase(cudaMemStream &memStream, int poolSize, float fmpShrink, int dimension, const char *label, const char *tag);
   void preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
   void forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
+  void backwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float learningRate,
+                 float momentum);
   int calculateInputSpatialSize(int outputSpatialSize);
   long long enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
                          long long rowsInBound, int *d_result);

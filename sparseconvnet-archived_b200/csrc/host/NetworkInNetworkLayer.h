@@ -8,10 +8,12 @@
 class NetworkInNetworkLayer : public SpatiallySparseLayer {
 public:
   vectorCUDA<float> W;  // [nFeaturesIn x nFeaturesOut], row-major
-  vectorCUDA<float> MW; // momentum (kept for weight-file compatibility; unused)
+  vectorCUDA<float> MW; // momentum of the SGD update (zero until the first training step)
   vectorCUDA<float> B;  // [nFeaturesOut]
   vectorCUDA<float> MB;
   vectorCUDA<float> splitScratch; // partial sums when the kernel splits K (layers with few rows)
+  vectorCUDA<float> dw, db;       // gradients of the last training step
+  vectorCUDA<float> Wt, zeroBias, dGathered; // backward pass: transposed weights, a zero bias for them, the gathered matrix's gradient
   ActivationFunction fn;
   int nFeaturesIn, nFeaturesOut;
   float dropout;
@@ -24,6 +26,8 @@ public:
   ~NetworkInNetworkLayer();
   void preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
   void forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
+  void backwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float learningRate,
+                 float momentum);
   void loadWeightsFromStream(std::ifstream &f, bool momentum);
   void putWeightsToStream(std::ofstream &f, bool momentum);
   int calculateInputSpatialSize(int outputSpatialSize);
@@ -58,6 +62,10 @@ public:
 
 protected:
   virtual float *slopes(); // per-channel PReLU slopes, or nullptr
+  virtual float *slopeGradient();                               // where backwards() leaves the slopes' gradient, or nullptr
+  virtual void updateSlopes(float learningRate, float momentum); // SGD step on the slopes (PReLU layers)
+  void *packedT;           // Wt repacked for the tensor-core kernel (input gradient)
+  size_t packedTBytes;
   void *packed;            // W repacked for `packedPrecision`
   size_t packedBytes;
   int packedPrecision;

@@ -6,7 +6,8 @@
 class NetworkInNetworkPReLULayer : public NetworkInNetworkLayer {
 public:
   vectorCUDA<float> PReLU;  // [nFeaturesOut]
-  vectorCUDA<float> MPReLU; // momentum (unused)
+  vectorCUDA<float> MPReLU; // momentum of the SGD update
+  vectorCUDA<float> dprelu; // slope gradient of the last training step
   NetworkInNetworkPReLULayer(cudaMemStream &memStream, cublasHandle_t &cublasHandle, int nFeaturesIn, int nFeaturesOut,
                              float dropout = 0, float alpha = 1);
   void loadWeightsFromStream(std::ifstream &f, bool momentum);
@@ -14,4 +15,6 @@ public:
 
 protected:
   float *slopes();
+  float *slopeGradient();
+  void updateSlopes(float learningRate, float momentum);
 };

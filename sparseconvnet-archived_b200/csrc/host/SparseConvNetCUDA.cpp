@@ -344,11 +344,14 @@ std::vector<float> SparseConvNetCUDA::layerTimes() {
   return ms;
 }
 
-// SparseConvNetCUDA.cu:227-271 without the training and rescaling branches.
-void SparseConvNetCUDA::processBatch(SpatiallySparseBatch &batch, float, float, std::ofstream &f, std::ofstream &g) {
-  if (batch.type == TRAINBATCH) throw ScnException("processBatch: TRAINBATCH is not supported by this inference library");
+// SparseConvNetCUDA.cu:227-271 without the rescaling branch: every layer's forwards, SoftmaxClassifier and, for a
+// TRAINBATCH, every layer's backwards in reverse order (each learnt layer updates its weights on the way).
+void SparseConvNetCUDA::processBatch(SpatiallySparseBatch &batch, float learningRate, float momentum, std::ofstream &f, std::ofstream &g) {
+  if (batch.type == RESCALEBATCH) throw ScnException("processBatch: the weight rescaling pass (RESCALEBATCH) is not built");
   forwardLayers(batch);
   SoftmaxClassifier(batch.interfaces.back(), batch, nTop, memStream);
+  if (batch.type == TRAINBATCH)
+    for (int i = (int)layers.size() - 1; i >= 0; --i) layers[i]->backwards(batch, batch.interfaces[i], batch.interfaces[i + 1], learningRate, momentum);
   if (f)
     for (auto &p : batch.predictions) {
       for (size_t k = 0; k < p.size(); ++k) f << (k ? " " : "") << p[k];
@@ -365,7 +368,6 @@ void SparseConvNetCUDA::processBatch(SpatiallySparseBatch &batch, float, float, 
 // the reference's summary line.
 float SparseConvNetCUDA::processDataset(SpatiallySparseDataset &dataset, int batchSize, float learningRate, float momentum) {
   if (dataset.pictures.empty()) throw ScnException("processDataset: empty dataset");
-  if (dataset.type == TRAINBATCH) throw ScnException("processDataset: TRAINBATCH is not supported by this inference library");
   float errorRate = 0, nll = 0;
   multiplyAddCount = 0;
   auto start = std::chrono::system_clock::now();

@@ -9,7 +9,7 @@
 class SpatiallySparseBatchSubInterface {
 public:
   vectorCUDA<float> features;     // [nSpatialSites x featuresPresent.size()]
-  vectorCUDA<float> dfeatures;    // backward pass only (unused: inference library)
+  vectorCUDA<float> dfeatures;    // backward pass: d cost / d features, same shape
   vectorCUDA<int> poolingChoices; // argmax of max pooling, flat input index
   SpatiallySparseBatchSubInterface();
   void reset();

@@ -3,10 +3,10 @@
 SpatiallySparseLayer::SpatiallySparseLayer(cudaMemStream &memStream) : memStream(memStream), changesGeometry(false) {}
 SpatiallySparseLayer::~SpatiallySparseLayer() {}
 void SpatiallySparseLayer::scaleWeights(SpatiallySparseBatchInterface &, SpatiallySparseBatchInterface &, float &, bool) {
-  throw ScnException("scaleWeights: weight rescaling belongs to training and is not part of this inference library");
+  throw ScnException("scaleWeights: the weight rescaling pass (RESCALEBATCH) is not built");
 }
 void SpatiallySparseLayer::backwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &, SpatiallySparseBatchInterface &, float, float) {
-  throw ScnException("backwards: this is an inference library");
+  throw ScnException("backwards: this layer type has no backward pass");
 }
 void SpatiallySparseLayer::loadWeightsFromStream(std::ifstream &, bool) {}
 void SpatiallySparseLayer::putWeightsToStream(std::ofstream &, bool) {}

@@ -12,6 +12,8 @@ public:
   TerminalPoolingLayer(cudaMemStream &memStream, int poolSize, int S);
   void preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
   void forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
+  void backwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float learningRate,
+                 float momentum);
   int calculateInputSpatialSize(int outputSpatialSize);
   long long enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
                          long long rowsInBound, int *d_result);

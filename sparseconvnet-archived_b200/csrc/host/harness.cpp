@@ -95,6 +95,71 @@ void adoptDeviceInput(SparseConvNetCUDA &cnn, SpatiallySparseBatch &b, int batch
   in.backgroundRows.borrowDevice(const_cast<int *>(d_bg), batch);
   in.sub->features.borrowDevice(const_cast<float *>(d_features), rows * cnn.nInputFeatures);
 }
+// Interface 0 of the network's first pool slot filled from host arrays (pinned ones are copied from where they lie,
+// pageable ones through the stream's staging block); the features travel on a stream of their own.
+SpatiallySparseBatch &uploadHostInput(scn_net *net, int batch, const int *keys, const int *off, const float *features, batchType type) {
+  SparseConvNetCUDA &cnn = *net->cnn;
+  if (batch < 1) throw ScnException("batch must be positive");
+  SpatiallySparseBatch &b = cnn.batchPool[0];
+  cnn.prepareBatch(b);
+  b.reset();
+  b.type = type;
+  b.batchSize = batch;
+  SpatiallySparseBatchInterface &in = b.interfaces[0];
+  const int rows = off[batch];
+  const int nF = cnn.nInputFeatures;
+  in.nFeatures = nF;
+  in.spatialSize = cnn.inputSpatialSize;
+  in.featuresPresent.hVector() = range(nF);
+  in.nSpatialSites = rows;
+  in.gridOwner = &in;
+  in.backpropErrors = false;
+  const size_t kb = sizeof(int) * rows, ob = sizeof(int) * (batch + 1), fb = sizeof(float) * (size_t)rows * nF;
+  auto pinned = [&](const void *p) {
+    for (const void *k : net->knownPinned) if (k == p) return true;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (a.type != cudaMemoryTypeHost) return false;
+    if (net->knownPinned.size() >= 64) net->knownPinned.clear();
+    net->knownPinned.push_back(p);
+    return true;
+  };
+  const void *sk = keys, *so = off, *sf = features;
+  if (!(pinned(keys) && pinned(off) && pinned(features))) {
+    char *stage = (char *)cnn.memStream.staging(kb + ob + fb);
+    std::memcpy(stage, keys, kb);
+    std::memcpy(stage + kb, off, ob);
+    std::memcpy(stage + kb + ob, features, fb);
+    sk = stage; so = stage + kb; sf = stage + kb + ob;
+  }
+  int maxRows = 0;
+  for (int s = 0; s < batch; ++s) maxRows = std::max(maxRows, off[s + 1] - off[s]);
+  in.maxSitesPerSample = maxRows; // an upper bound (exact when a sample has no background row)
+  if (!cnn.layers.empty() && dynamic_cast<TerminalPoolingLayer *>(cnn.layers[0])) { // its rule width needs the exact count
+    int most = 0;
+    for (int s = 0; s < batch; ++s) { int n = 0; for (int r = off[s]; r < off[s + 1]; ++r) n += keys[r] >= 0; most = std::max(most, n); }
+    in.maxSitesPerSample = most;
+  }
+  in.siteKeys.copyToGPU(); in.sampleOffsets.copyToGPU(); in.backgroundRows.copyToGPU(); in.sub->features.copyToGPU();
+  in.siteKeys.resize(rows); in.sampleOffsets.resize(batch + 1); in.backgroundRows.resize(batch); in.sub->features.resize(rows * nF);
+  cudaStream_t s = cnn.memStream.stream;
+  if (rows) cudaSafeCall(cudaMemcpyAsync(in.siteKeys.dPtr(), sk, kb, cudaMemcpyHostToDevice, s));
+  cudaSafeCall(cudaMemcpyAsync(in.sampleOffsets.dPtr(), so, ob, cudaMemcpyHostToDevice, s));
+  if (!net->copyStream) {
+    cudaSafeCall(cudaStreamCreateWithFlags(&net->copyStream, cudaStreamNonBlocking));
+    cudaSafeCall(cudaEventCreateWithFlags(&net->copyDone, cudaEventDisableTiming));
+  }
+  if (rows) { // nothing is in flight on the features buffer: the previous batch ended with a host wait
+    float *dst = in.sub->features.dPtr();
+    cudaSafeCall(cudaEventRecord(net->copyDone, s)); // ... but the resize above may have enqueued work on s
+    cudaSafeCall(cudaStreamWaitEvent(net->copyStream, net->copyDone, 0));
+    cudaSafeCall(cudaMemcpyAsync(dst, sf, fb, cudaMemcpyHostToDevice, net->copyStream));
+    cudaSafeCall(cudaEventRecord(net->copyDone, net->copyStream));
+  }
+  cnn.inputBackgroundPending = true; // found by the rule chain's kernel (or by a kernel of its own where that one does not apply)
+  if (rows) cnn.inputReady = net->copyDone; // the layers (not the rule chain) wait for the features
+  return b;
+}
 } // namespace
 
 extern "C" {
@@ -214,66 +279,7 @@ int scn_net_set_precision(scn_net_t *net, int precision) {
 int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *off, const float *features, float *probs, int *predictions) {
   return guarded([&] {
     SparseConvNetCUDA &cnn = *net->cnn;
-    if (batch < 1) throw ScnException("batch must be positive");
-    SpatiallySparseBatch &b = cnn.batchPool[0];
-    cnn.prepareBatch(b);
-    b.reset();
-    b.type = UNLABELEDBATCH;
-    b.batchSize = batch;
-    SpatiallySparseBatchInterface &in = b.interfaces[0];
-    const int rows = off[batch];
-    const int nF = cnn.nInputFeatures;
-    in.nFeatures = nF;
-    in.spatialSize = cnn.inputSpatialSize;
-    in.featuresPresent.hVector() = range(nF);
-    in.nSpatialSites = rows;
-    in.gridOwner = &in;
-    // Buffers in pinned (page-locked) host memory are copied straight from where they lie; pageable
-    // ones go through the stream's pinned staging block first.  Background rows are found on the device.
-    const size_t kb = sizeof(int) * rows, ob = sizeof(int) * (batch + 1), fb = sizeof(float) * (size_t)rows * nF;
-    auto pinned = [&](const void *p) {
-      for (const void *k : net->knownPinned) if (k == p) return true;
-      cudaPointerAttributes a;
-      if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
-      if (a.type != cudaMemoryTypeHost) return false;
-      if (net->knownPinned.size() >= 64) net->knownPinned.clear();
-      net->knownPinned.push_back(p);
-      return true;
-    };
-    const void *sk = keys, *so = off, *sf = features;
-    if (!(pinned(keys) && pinned(off) && pinned(features))) {
-      char *stage = (char *)cnn.memStream.staging(kb + ob + fb);
-      std::memcpy(stage, keys, kb);
-      std::memcpy(stage + kb, off, ob);
-      std::memcpy(stage + kb + ob, features, fb);
-      sk = stage; so = stage + kb; sf = stage + kb + ob;
-    }
-    int maxRows = 0;
-    for (int s = 0; s < batch; ++s) maxRows = std::max(maxRows, off[s + 1] - off[s]);
-    in.maxSitesPerSample = maxRows; // an upper bound (exact when a sample has no background row)
-    if (!cnn.layers.empty() && dynamic_cast<TerminalPoolingLayer *>(cnn.layers[0])) { // its rule width needs the exact count
-      int most = 0;
-      for (int s = 0; s < batch; ++s) { int n = 0; for (int r = off[s]; r < off[s + 1]; ++r) n += keys[r] >= 0; most = std::max(most, n); }
-      in.maxSitesPerSample = most;
-    }
-    in.siteKeys.copyToGPU(); in.sampleOffsets.copyToGPU(); in.backgroundRows.copyToGPU(); in.sub->features.copyToGPU();
-    in.siteKeys.resize(rows); in.sampleOffsets.resize(batch + 1); in.backgroundRows.resize(batch); in.sub->features.resize(rows * nF);
-    cudaStream_t s = cnn.memStream.stream;
-    if (rows) cudaSafeCall(cudaMemcpyAsync(in.siteKeys.dPtr(), sk, kb, cudaMemcpyHostToDevice, s));
-    cudaSafeCall(cudaMemcpyAsync(in.sampleOffsets.dPtr(), so, ob, cudaMemcpyHostToDevice, s));
-    if (!net->copyStream) {
-      cudaSafeCall(cudaStreamCreateWithFlags(&net->copyStream, cudaStreamNonBlocking));
-      cudaSafeCall(cudaEventCreateWithFlags(&net->copyDone, cudaEventDisableTiming));
-    }
-    if (rows) { // nothing is in flight on the features buffer: the previous forward ended with a host wait
-      float *dst = in.sub->features.dPtr();
-      cudaSafeCall(cudaEventRecord(net->copyDone, s)); // ... but the resize above may have enqueued work on s
-      cudaSafeCall(cudaStreamWaitEvent(net->copyStream, net->copyDone, 0));
-      cudaSafeCall(cudaMemcpyAsync(dst, sf, fb, cudaMemcpyHostToDevice, net->copyStream));
-      cudaSafeCall(cudaEventRecord(net->copyDone, net->copyStream));
-    }
-    cnn.inputBackgroundPending = true; // found by the rule chain's kernel (or by a kernel of its own where that one does not apply)
-    if (rows) cnn.inputReady = net->copyDone; // the layers (not the rule chain) wait for the features
+    SpatiallySparseBatch &b = uploadHostInput(net, batch, keys, off, features, UNLABELEDBATCH);
     cnn.earlyFirstLayer = true; // one batch in flight here: the first layer may start behind the rule chain
     cnn.preprocessBatchOnDevice(b); // waits once, after the key upload and the rule chain
     cnn.earlyFirstLayer = false;
@@ -287,6 +293,52 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *
     if (probs) std::memcpy(probs, block, pb);
     if (predictions) std::memcpy(predictions, block + pb, sizeof(int) * (size_t)batch * cnn.nTop);
   });
+}
+
+int scn_net_train_batch(scn_net_t *net, int batch, const int *keys, const int *off, const float *features, const int *labels, float learningRate,
+                        float momentum, float *probs, double *stats) {
+  return guarded([&] {
+    SparseConvNetCUDA &cnn = *net->cnn;
+    if (!labels) throw ScnException("a training step needs labels");
+    SpatiallySparseBatch &b = uploadHostInput(net, batch, keys, off, features, TRAINBATCH);
+    b.labels.copyToCPU();
+    b.labels.hVector().assign(labels, labels + batch);
+    cnn.preprocessBatchOnDevice(b);
+    std::ofstream nof, nog;
+    cnn.processBatch(b, learningRate, momentum, nof, nog);
+    net->last = &b;
+    cudaSafeCall(cudaStreamSynchronize(cnn.memStream.stream));
+    for (int i = 0; i < batch && probs; ++i) std::memcpy(probs + (size_t)i * cnn.nClasses, b.probabilities[i].data(), sizeof(float) * cnn.nClasses);
+    if (stats) { stats[0] = b.negativeLogLikelihood; stats[1] = b.mistakes; }
+  });
+}
+
+int scn_net_get_weights(scn_net_t *net, int layer, float *W, float *B, float *prelu) {
+  return guarded([&] {
+    auto n = dynamic_cast<NetworkInNetworkLayer *>(net->cnn->layers.at(layer));
+    if (!n) throw ScnException("layer has no weights");
+    cudaSafeCall(cudaStreamSynchronize(net->cnn->memStream.stream));
+    auto fetch = [&](vectorCUDA<float> &v, float *dst) {
+      if (!dst || !v.size()) return;
+      if (v.onGPU) cudaSafeCall(cudaMemcpy(dst, v.dPtr(), sizeof(float) * v.size(), cudaMemcpyDeviceToHost));
+      else std::memcpy(dst, v.hVector().data(), sizeof(float) * v.size());
+    };
+    fetch(n->W, W);
+    fetch(n->B, B);
+    if (auto pr = dynamic_cast<NetworkInNetworkPReLULayer *>(n)) fetch(pr->PReLU, prelu);
+  });
+}
+
+long long scn_net_iface_dfeatures(scn_net_t *net, int i, float *dfeatures) {
+  long long n = -1;
+  guarded([&] {
+    if (!net->last) throw ScnException("no batch has run");
+    SpatiallySparseBatchInterface &I = net->last->interfaces.at(i);
+    cudaSafeCall(cudaStreamSynchronize(net->cnn->memStream.stream));
+    n = I.sub->dfeatures.size();
+    if (dfeatures && n) cudaSafeCall(cudaMemcpy(dfeatures, I.sub->dfeatures.dPtr(), sizeof(float) * n, cudaMemcpyDeviceToHost));
+  });
+  return n;
 }
 
 int scn_net_forward_device(scn_net_t *net, int batch, int rows, int maxSites, const int *d_keys, const int *d_off, const int *d_bg,

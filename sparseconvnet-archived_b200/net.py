@@ -17,7 +17,7 @@ EXPORTS = [
     "scn_net_addTerminalPoolingLayer", "scn_net_addSoftmaxLayer", "scn_net_DeepCNet", "scn_net_n_layers",
     "scn_net_input_spatial_size", "scn_net_layer_info", "scn_net_set_weights", "scn_net_load_weights",
     "scn_net_save_weights", "scn_net_set_precision", "scn_net_forward_host", "scn_net_forward_device",
-    "scn_net_copy_probs_device", "scn_net_iface_sizes", "scn_net_iface_fetch", "scn_net_take_multiply_adds", "scn_net_enable_timing",
+    "scn_net_copy_probs_device", "scn_net_train_batch", "scn_net_get_weights", "scn_net_iface_dfeatures", "scn_net_iface_sizes", "scn_net_iface_fetch", "scn_net_take_multiply_adds", "scn_net_enable_timing",
     "scn_net_layer_times", "scn_net_process_dataset", "scn_host_vectorTopIndices",
 ]
 
@@ -63,6 +63,9 @@ def lib():
         L.scn_net_forward_host.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p, c_p]
         L.scn_net_forward_device.argtypes = [c_p, c_int, c_int, c_int, c_p, c_p, c_p, c_p, c_p, c_p]
         L.scn_net_copy_probs_device.argtypes = [c_p, c_p]
+        L.scn_net_train_batch.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p, c_p]
+        L.scn_net_get_weights.argtypes = [c_p, c_int, c_p, c_p, c_p]
+        L.scn_net_iface_dfeatures.restype, L.scn_net_iface_dfeatures.argtypes = c_ll, [c_p, c_int, c_p]
         L.scn_net_iface_sizes.argtypes = [c_p, c_int, c_p]
         L.scn_net_iface_fetch.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p]
         L.scn_net_take_multiply_adds.restype = c_d
@@ -191,6 +194,34 @@ class Net:
                                              c_p(d_bg.data_ptr()), c_p(d_features.data_ptr()), c_p(d_probs.data_ptr()),
                                              c_p(d_top.data_ptr())))
         return d_probs, d_top
+
+    def train_batch(self, keys, off, features, labels, learning_rate, momentum):
+        """One training step (forward, classifier, backward with SGD updates) -> (probabilities, dict(nll, mistakes))."""
+        keys = np.ascontiguousarray(keys, np.int32)
+        off = np.ascontiguousarray(off, np.int32)
+        features = np.ascontiguousarray(features, np.float32)
+        labels = np.ascontiguousarray(labels, np.int32)
+        B = len(off) - 1
+        probs = np.empty((B, self.nClasses), np.float32)
+        stats = np.zeros(2, np.float64)
+        _check(self.L.scn_net_train_batch(self.h, B, _np(keys), _np(off), _np(features), _np(labels), learning_rate, momentum, _np(probs), _np(stats)))
+        return probs, dict(nll=float(stats[0]), mistakes=int(stats[1]))
+
+    def get_weights(self, i):
+        L = self.layers()[i]
+        W, B = np.zeros((L["nIn"], L["nOut"]), np.float32), np.zeros(L["nOut"], np.float32)
+        pr = np.zeros(L["nOut"], np.float32)
+        _check(self.L.scn_net_get_weights(self.h, i, _np(W), _np(B), _np(pr)))
+        return W, B, (pr if L["act"] == abi.PRELU else None)
+
+    def dfeatures(self, i):
+        n = self.L.scn_net_iface_dfeatures(self.h, i, None)
+        if n < 0:
+            raise abi.ScnError(self.L.scn_net_last_error().decode())
+        d = np.zeros(n, np.float32)
+        if n:
+            self.L.scn_net_iface_dfeatures(self.h, i, _np(d))
+        return d
 
     def copy_probs_device(self, d_probs):
         _check(self.L.scn_net_copy_probs_device(self.h, c_p(d_probs.data_ptr())))

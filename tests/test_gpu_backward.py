@@ -1,0 +1,292 @@
+"""GPU parity of the backward pass (the training step behind the forward path): every backward operation through
+the C ABI against the oracle's restatement, one whole training step of the configurations' networks (without
+dropout) against the oracle, and the oracle's training step pinned to the reference's own TRAINBATCH branch
+(its layer classes' backwards(), cuBLAS SGEMMs and SGD kernels compiled unchanged, oracle/_ref_gpu)."""
+import numpy as np
+import pytest
+import torch
+
+from netutil import build_with, relerr, rules_safe_for_reference_kernels, write_cnn
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-4  # largest deviation relative to the largest value of a tensor
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("act", ["NOSIGMOID", "RELU", "VLEAKYRELU", "LEAKYRELU", "TANH", "SIGMOID", "PRELU", "SOFTMAX"])
+@pytest.mark.parametrize("rows,N", [(300, 96), (77, 10)])
+def test_activation_backward(abi, oracle, act, rows, N):
+    from oracle import orc
+    rng = np.random.default_rng(N + len(act))
+    a = getattr(orc, act)
+    b = rng.standard_normal((rows, N)).astype(np.float32)
+    if act in ("SIGMOID", "SOFTMAX"):
+        b = (1 / (1 + np.exp(-b))).astype(np.float32)
+    if act == "TANH":
+        b = np.tanh(b).astype(np.float32)
+    d = rng.standard_normal((rows, N)).astype(np.float32)
+    pr = rng.uniform(0.1, 0.4, N).astype(np.float32) if act == "PRELU" else None
+    want, wpr = oracle.activation_backward(b, d, a, pr)
+    got, gpr = abi.activation_backward(dev(b), dev(d), a, None if pr is None else dev(pr))
+    assert relerr(got.cpu().numpy(), want) < 1e-6
+    if act == "PRELU":
+        assert relerr(gpr.cpu().numpy(), wpr) < 1e-5
+
+
+@pytest.mark.parametrize("rows_in,rows,fs,nIn,N", [
+    (300, 257, 9, 3, 32), (500, 1000, 4, 96, 192), (64, 64, 1, 160, 10), (200, 513, 27, 1, 32), (90, 77, 4, 50, 101),
+    (3000, 5000, 8, 32, 64), (256, 256, 1, 608, 10), (2000, 3000, 1, 70, 33),
+])
+def test_conv_nin_backward_weights(abi, oracle, rows_in, rows, fs, nIn, N):
+    """dW = X^T d, dB = column sums, the gathered matrix read through the rulebook inside the kernel."""
+    rng = np.random.default_rng(rows + N)
+    feat = rng.standard_normal((rows_in, nIn)).astype(np.float32)
+    d = rng.standard_normal((rows if fs > 1 else rows_in, N)).astype(np.float32)
+    if fs > 1:
+        rules = rng.integers(0, rows_in, size=(rows, fs)).astype(np.int32)
+        rules[rng.random(rules.shape) < 0.1] = -1
+        X = oracle.gather(feat, rules, nIn).reshape(rows, fs * nIn)
+        drules = dev(rules).flatten()
+    else:
+        X, drules = feat, None
+    W = np.zeros((X.shape[1], N), np.float32)
+    wdW, wdB, _ = oracle.nin_backward(X, d, W, want_dx=False)
+    gdW, gdB = abi.conv_nin_backward_weights(dev(feat), drules, fs, dev(d))
+    assert relerr(gdW.cpu().numpy(), wdW) < TOL
+    assert relerr(gdB.cpu().numpy(), wdB) < TOL
+
+
+@pytest.mark.parametrize("precision", ["FP32", "3XTF32"])
+@pytest.mark.parametrize("rows,K,N", [(1000, 384, 192), (300, 96, 32), (256, 608, 10), (5000, 1152, 416)])
+def test_input_gradient_is_the_forward_kernel_on_transposed_weights(abi, oracle, rows, K, N, precision):
+    """dX = d W^T through scn_transpose_weights + scn_conv_nin_forward_ws (tensor cores where the shape allows)."""
+    rng = np.random.default_rng(K + N)
+    d = rng.standard_normal((rows, N)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) / np.sqrt(K)).astype(np.float32)
+    _, _, want = oracle.nin_backward(np.zeros((rows, K), np.float32), d, W)
+    Wt = abi.transpose_weights(dev(W))
+    np.testing.assert_array_equal(Wt.cpu().numpy(), W.T)
+    prec = getattr(abi, "PREC_" + precision)
+    packed = None
+    if precision != "FP32":
+        if abi.lib().scn_conv_packed_weight_bytes(N, K, prec) == 0:
+            pytest.skip("no tensor-core layout for this shape")
+        packed = abi.pack_weights(Wt, prec)
+    got = abi.conv_nin_forward(dev(d), None, 1, Wt, torch.zeros(K, device="cuda"), None, 1.0, abi.NOSIGMOID, prec, packed=packed)
+    torch.cuda.synchronize()
+    assert abi.conv_tc_take_error() == 0
+    assert relerr(got.cpu().numpy(), want) < TOL
+
+
+def test_gather_backward(abi, oracle):
+    rng = np.random.default_rng(5)
+    rows_in, rows, fs, nIn = 400, 700, 9, 24
+    rules = rng.integers(0, rows_in, size=(rows, fs)).astype(np.int32)
+    rules[rng.random(rules.shape) < 0.2] = -1
+    dconv = rng.standard_normal((rows * fs, nIn)).astype(np.float32)
+    want = oracle.gather_backward(dconv, rules, nIn, rows_in)
+    got = abi.gather_backward(dev(dconv), dev(rules).flatten(), nIn, rows_in)
+    assert relerr(got.cpu().numpy(), want) < 1e-5
+
+
+def test_maxpool_backward(abi, oracle):
+    """Overlapping windows: several pooled values may choose the same input, their gradients add up."""
+    rng = np.random.default_rng(6)
+    n_in, n = 5000, 3000
+    choices = rng.integers(0, n_in // 4, n).astype(np.int32)  # many duplicates
+    choices[rng.random(n) < 0.05] = -1
+    dout = rng.standard_normal(n).astype(np.float32)
+    want = oracle.maxpool_backward(dout, choices, n_in)
+    got = abi.maxpool_backward(dev(dout), dev(choices), n_in)
+    assert relerr(got.cpu().numpy(), want) < 1e-5
+
+
+def test_terminal_pool_backward(abi, oracle):
+    rng = np.random.default_rng(7)
+    C, S, batch, rows_in = 96, 9, 17, 200
+    rules = np.full((batch, S), -1, np.int32)
+    perm = rng.permutation(rows_in)
+    at = 0
+    for b in range(batch):
+        n = int(rng.integers(1, S + 1))
+        rules[b, :n] = perm[at:at + n]
+        at += n
+    dout = rng.standard_normal((batch, C)).astype(np.float32)
+    want = oracle.terminal_pool_backward(dout, rules, S, rows_in)
+    got = abi.terminal_pool_backward(dev(dout), dev(rules).flatten(), S, rows_in)
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-6, atol=1e-7)
+
+
+def test_softmax_nll_backward_and_sgd_update(abi, oracle):
+    rng = np.random.default_rng(8)
+    p = rng.random((64, 10)).astype(np.float32)
+    p /= p.sum(1, keepdims=True)
+    labels = rng.integers(0, 10, 64).astype(np.int32)
+    got = abi.softmax_nll_backward(dev(p), dev(labels)).cpu().numpy()
+    want = p.copy()
+    want[np.arange(64), labels] -= 1
+    np.testing.assert_array_equal(got, want)
+    w, m, d = (rng.standard_normal(5000).astype(np.float32) for _ in range(3))
+    ww, wm = oracle.sgd_update(w, m, d, 0.003, 0.99)
+    gw, gm = dev(w), dev(m)
+    abi.sgd_update(gw, gm, dev(d), 0.003, 0.99)
+    np.testing.assert_allclose(gw.cpu().numpy(), ww, rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(gm.cpu().numpy(), wm, rtol=1e-6, atol=1e-7)
+    ww, wm = oracle.sgd_update(w, m, d, 0.5, 0.9, keep_positive=True)  # the PReLU slopes' update: held at 0.001 or above
+    gw, gm = dev(w), dev(m)
+    abi.sgd_update(gw, gm, dev(d), 0.5, 0.9, keep_positive=True)
+    np.testing.assert_allclose(gw.cpu().numpy(), ww, rtol=1e-6, atol=1e-7)
+    assert gw.min().item() >= 0.001 and (gw == 0.001).any().item()
+
+
+# ---------------------------------------------------------------------------------------------- whole training steps
+def _levels(scn, cfg, act):
+    c = scn.synth.CONFIGS[cfg]
+    w = c["widths"]
+    out = []
+    for i, nf in enumerate(w):
+        pool = not (c["tail"] == "conv" and i == len(w) - 1)
+        out.append((nf, c.get("first_filter", 3) if i == 0 else 2, 1, 2 if pool else 1, 2 if pool else 1, act, 0.0, 1))
+    return out, (c.get("terminal") if c["tail"] == "terminal" else None)
+
+
+def _compare_step(gnet, onet, layers, old):
+    """dfeatures of every interface a gradient reaches and every learnt layer's update, product against oracle."""
+    checked = 0
+    for i in range(len(layers) + 1):
+        o = onet.dfeatures(i)
+        if i and layers[i - 1]["type"] in (0, 1):
+            continue  # the gathered matrix's gradient is never materialised by the fused kernels
+        g = gnet.dfeatures(i)
+        if o.size == 0:
+            continue
+        assert g.size == o.size, "gradient of interface %d" % i
+        assert relerr(g, o) < TOL, "gradient of interface %d" % i
+        checked += 1
+    for i, L in enumerate(layers):
+        if L["type"] != 2:
+            continue
+        gW, gB, gpr = gnet.get_weights(i)
+        oW, oB, opr = onet.get_weights(i)
+        W0, B0, pr0 = old[i]
+        assert relerr(gW - W0, oW - W0) < TOL, "weight update of layer %d" % i
+        assert relerr(gB - B0, oB - B0) < TOL, "bias update of layer %d" % i
+        if opr is not None:
+            assert relerr(gpr - pr0, opr - pr0) < TOL, "slope update of layer %d" % i
+    return checked
+
+
+@pytest.mark.parametrize("cfg,batch,act", [(1, 16, "VLEAKYRELU"), (2, 32, "VLEAKYRELU"), (3, 6, "RELU"), (4, 6, "PRELU"), (5, 2, "VLEAKYRELU"), (1, 8, "TANH")])
+def test_training_step_matches_oracle(scn, abi, oracle, cfg, batch, act):
+    """Two consecutive training steps (the second runs on updated weights and non-zero momentum) of each configuration's
+    network built without dropout: probabilities, negative log-likelihood, the gradient at every interface and every
+    weight update within 1e-4 of the fp64-accumulating oracle."""
+    from oracle import orc
+    c = scn.synth.CONFIGS[cfg]
+    levels, terminal = _levels(scn, cfg, getattr(orc, act))
+    onet = orc.OracleNet(oracle, c["dim"], c["nIn"], c["nClasses"], 1, lattice=c["lattice"])
+    build_with(onet, levels, terminal)
+    gnet = scn.net.Net(c["dim"], c["nIn"], c["nClasses"], 1, c["lattice"])
+    build_with(gnet, levels, terminal)
+    layers = gnet.layers()
+    weights = scn.synth.init_weights(layers, 11)
+    for i, (W, B, _) in weights.items():
+        pr = np.random.default_rng(i).uniform(0.1, 0.4, len(B)).astype(np.float32) if layers[i]["act"] == orc.PRELU else None
+        weights[i] = (W, B, pr)
+        onet.set_weights(i, W, B, pr)
+        gnet.set_weights(i, W, B, pr)
+    for step in range(2):
+        keys, off, feats = c["gen"](batch, first=100 * step)
+        labels = ((np.arange(batch) * 7 + step) % c["nClasses"]).astype(np.int32)
+        old = {i: onet.get_weights(i) for i in weights}
+        oprobs, ostats = onet.train_step(keys, off, feats, labels, 0.01, 0.9)
+        gprobs, gstats = gnet.train_batch(keys, off, feats, labels, 0.01, 0.9)
+        assert abi.conv_tc_take_error() == 0
+        assert relerr(gprobs, oprobs) < TOL
+        assert gstats["nll"] == pytest.approx(ostats["nll"], rel=1e-4)
+        assert gstats["mistakes"] == ostats["mistakes"]
+        assert _compare_step(gnet, onet, layers, old) >= 3
+    # the updated network still forwards like the oracle's
+    keys, off, feats = c["gen"](batch, first=500)
+    op, ot = onet.forward(keys, off, feats, accum64=True)
+    gp, gt = gnet.forward_host(keys, off, feats)
+    assert relerr(gp, op) < TOL
+
+
+def test_training_with_dropout_is_refused(scn, abi):
+    gnet = scn.net.Net(2, 3, 10, 1, 0)
+    scn.synth.build_network(gnet, 2)  # dropout ramp 0 .. 0.5
+    keys, off, feats = scn.synth.CONFIGS[2]["gen"](2)
+    with pytest.raises(abi.ScnError):
+        gnet.train_batch(keys, off, feats, np.zeros(2, np.int32), 0.01, 0.9)
+    gnet.forward_host(keys, off, feats)  # inference still works
+
+
+@pytest.mark.parametrize("cfg,batch,act", [(1, 8, "VLEAKYRELU"), (2, 4, "RELU"), (4, 3, "PRELU"), (5, 1, "TANH"), (1, 6, "SIGMOID")])
+def test_oracle_training_step_matches_reference(scn, abi, oracle, tmp_path, cfg, batch, act):
+    """The oracle's backward pass pinned to the reference: one TRAINBATCH through the reference's own processBatch (forward,
+    SoftmaxClassifier, every layer's backwards with its SGD kernels) against orc_net_train_step on the same samples in the
+    order the reference's BatchProducer shuffled them into: gradients at every interface, updated weights, NLL, mistakes.
+    The product's training step is compared with the reference's directly as well."""
+    from oracle import orc
+    if not orc.ReferenceGPU.available():
+        pytest.skip("oracle/_ref_gpu/libscn_ref_gpu.so not built")
+    c = scn.synth.CONFIGS[cfg]
+    levels, terminal = _levels(scn, cfg, getattr(orc, act))
+    onet = orc.OracleNet(oracle, c["dim"], c["nIn"], c["nClasses"], 1, lattice=c["lattice"])
+    build_with(onet, levels, terminal)
+    ref = orc.ReferenceGPU(c["dim"], c["nIn"], c["nClasses"], 1, c["lattice"])
+    build_with(ref, levels, terminal)
+    gnet = scn.net.Net(c["dim"], c["nIn"], c["nClasses"], 1, c["lattice"])
+    build_with(gnet, levels, terminal)
+    layers = onet.layers()
+    weights = scn.synth.init_weights(layers, 13)
+    for i, (W, B, _) in weights.items():
+        pr = np.random.default_rng(i).uniform(0.1, 0.4, len(B)).astype(np.float32) if layers[i]["act"] == orc.PRELU else None
+        weights[i] = (W, B, pr)
+        onet.set_weights(i, W, B, pr)
+        gnet.set_weights(i, W, B, pr)
+    base = str(tmp_path / "t")
+    write_cnn(base, 0, layers, weights)
+    ref.load_weights(base, 0)
+    keys, off, feats = c["gen"](batch)
+    labels = ((np.arange(batch) * 3) % c["nClasses"]).astype(np.int32)
+    onet.forward(keys, off, feats, keep=True)
+    assert rules_safe_for_reference_kernels(onet)
+    lr, mom = 0.01, 0.9
+    rprobs, _, rstats = ref.forward(keys, off, feats, labels=labels, batch_type=0, learning_rate=lr, momentum=mom)
+    order = ref.sample_numbers(batch)
+    # the same samples in the reference's order
+    k2 = np.concatenate([keys[off[s]:off[s + 1]] for s in order])
+    f2 = np.concatenate([feats[off[s]:off[s + 1]] for s in order])
+    o2 = np.concatenate([[0], np.cumsum([off[s + 1] - off[s] for s in order])]).astype(np.int32)
+    l2 = labels[order]
+    oprobs, ostats = onet.train_step(k2, o2, f2, l2, lr, mom)
+    gprobs, gstats = gnet.train_batch(k2, o2, f2, l2, lr, mom)
+    assert relerr(oprobs, rprobs) < TOL and relerr(gprobs, rprobs) < TOL
+    assert rstats["nll"] == pytest.approx(ostats["nll"], rel=1e-4)
+    assert rstats["mistakes"] == ostats["mistakes"] == gstats["mistakes"]
+    checked = 0
+    for i in range(len(layers) + 1):
+        r = ref.iface(i)["dfeatures"].ravel()
+        o = onet.dfeatures(i)
+        if o.size == 0:
+            continue
+        assert r.size == o.size, "gradient of interface %d" % i
+        assert relerr(o, r) < TOL, "oracle gradient of interface %d" % i
+        if not (i and layers[i - 1]["type"] in (0, 1)):
+            assert relerr(gnet.dfeatures(i), r) < TOL, "product gradient of interface %d" % i
+        checked += 1
+    assert checked >= 3
+    for i, (W0, B0, pr0) in weights.items():
+        rW, rB, rpr = ref.layer_weights(i)
+        oW, oB, opr = onet.get_weights(i)
+        gW, gB, gpr = gnet.get_weights(i)
+        assert relerr(oW - W0, rW - W0) < TOL and relerr(gW - W0, rW - W0) < TOL, "weight update of layer %d" % i
+        assert relerr(oB - B0, rB - B0) < TOL and relerr(gB - B0, rB - B0) < TOL, "bias update of layer %d" % i
+        if pr0 is not None:
+            assert relerr(opr - pr0, rpr - pr0) < TOL and relerr(gpr - pr0, rpr - pr0) < TOL, "slope update of layer %d" % i
