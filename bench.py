@@ -254,7 +254,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--precision", default="auto", choices=["auto", "fp32", "3xtf32", "bf16", "3xbf16"])
+    ap.add_argument("--precision", default="auto", choices=["auto", "split", "fp32", "3xtf32", "bf16", "3xbf16"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="wall time of the cpu_baseline leg (0 = skip it and the parity check)")
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="synthetic configuration (2 = the headline workload; the others are side measurements)")
@@ -293,7 +293,7 @@ def main():
 
     with torch.cuda.stream(stream):
         gnet, _ = build_pair(scn, False)
-        gnet.set_precision(dict(auto=abi.PREC_AUTO, fp32=abi.PREC_FP32, **{"3xtf32": abi.PREC_3XTF32, "3xbf16": abi.PREC_3XBF16}, bf16=abi.PREC_BF16)[args.precision])
+        gnet.set_precision(dict(auto=abi.PREC_AUTO, split=abi.PREC_SPLIT, fp32=abi.PREC_FP32, **{"3xtf32": abi.PREC_3XTF32, "3xbf16": abi.PREC_3XBF16}, bf16=abi.PREC_BF16)[args.precision])
         # this rank's shard of the global batch, several distinct batches rotated between steps
         n_rot = 2
         host_batches = [c["gen"](BATCH_PER_GPU, first=(rank * n_rot + j) * BATCH_PER_GPU) for j in range(n_rot)]
@@ -488,7 +488,9 @@ def main():
     # per product: `pipe_frac` is the same time against that ceiling (peak / 6).
     tc = [d for d in per_layer if d["kernel"] != "maxpool_rules" and d.get("K", 0) >= 128 and d["N"] >= 16]
     step_ms = ms_dev / steps
-    passes = {"auto": 6.0, "3xtf32": 6.0, "3xbf16": 3.0, "bf16": 1.0}.get(args.precision, 6.0)
+    # tensor-pipe passes per product against the bf16 rate: three bf16 products for the layers with K >= 128 (auto / split),
+    # three tf32 products at half the bf16 rate for 3xtf32
+    passes = {"auto": 3.0, "split": 3.0, "3xtf32": 6.0, "3xbf16": 3.0, "bf16": 1.0}.get(args.precision, 3.0)
     if tc and args.precision != "fp32":
         ach = sum(d["flops"] for d in tc) / (sum(d["ms"] for d in tc) * 1e-3) / 1e12
         roof = dict(bound="tensor", achieved=ach, peak=peaks["tflops"], unit="TFLOP/s", frac=ach / peaks["tflops"],
@@ -496,8 +498,9 @@ def main():
                     kernel="k_conv_nin_tc (%d launches per step with K >= 128, %d of them with the max pooling fused in)" % (len(tc), sum(d["kernel"] == "conv_nin_maxpool_fused" for d in tc)),
                     ms_per_launch=sum(d["ms"] for d in tc) / len(tc), share_of_step=sum(d["ms"] for d in tc) / step_ms,
                     frac_of_sustained_peak=ach / peaks["tflops_sustained"], pipe_frac=ach * passes / peaks["tflops"],
-                    note="peak is the measured bf16 cuBLAS burst figure; kind::tf32 runs at half that rate and 3xTF32 issues 3 MMAs "
-                         "per product, so 1/6 of this peak is the ceiling of a perfect 3xTF32 kernel (pipe_frac is against that ceiling)")
+                    note="peak is the measured bf16 cuBLAS burst figure; these layers (K >= 128) run the three-product split on bf16 operands "
+                         "(auto / split; three tf32 products at half the rate for 3xtf32), so 1/3 (1/6) of this peak is the ceiling of a perfect "
+                         "kernel: pipe_frac is against that ceiling")
     else:
         top = max(per_layer, key=lambda d: d["ms"])
         ach = top["bytes"] / (top["ms"] * 1e-3) / 1e9
@@ -530,7 +533,7 @@ def main():
         line = dict(
             metric=METRIC, value=total / (ms_dev * 1e-3), unit="samples/s", n_gpus=world, steps=steps, warmup=args.warmup,
             ms_per_step=ms_dev / steps, higher_is_better=True, scaling="weak", vs_baseline=None,
-            dtype="f32" if args.precision == "fp32" else ("bf16" if args.precision == "bf16" else "tf32x3/f32"), data="synthetic",
+            dtype={"fp32": "f32", "bf16": "bf16", "3xtf32": "tf32x3/f32", "3xbf16": "bf16x3/f32"}.get(args.precision, "bf16x3|tf32x3/f32"), data="synthetic",
             config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample, all-gather of probabilities%s" % (world, " (step j's gather overlaps step j+1 in both legs)" if world > 1 else ""),
                         l2="256 MiB written between timed steps; 2 distinct batches rotated", precision=args.precision,
                         timing="CUDA events per step on the launching stream, max over ranks; each leg %d times, median leg reported; wall %.3f s for the device legs; per-kernel durations from one more pass of the same steps with events between the layers" % (max(1, args.legs), t_wall)),

@@ -56,7 +56,11 @@ enum scn_precision {
   SCN_PREC_FP32 = 0,   /* fp32 FMA on CUDA cores                                           */
   SCN_PREC_3XTF32 = 1, /* tcgen05 kind::tf32, hi/lo split of both operands (fp32-grade)    */
   SCN_PREC_BF16 = 2,   /* tcgen05 kind::f16 with bf16 operands, fp32 accumulation          */
-  SCN_PREC_3XBF16 = 3  /* kind::f16, bf16 hi/lo split of both operands, three products     */
+  SCN_PREC_3XBF16 = 3, /* kind::f16, bf16 hi/lo split of both operands, three products     */
+  SCN_PREC_SPLIT = 4   /* the three-product hi/lo split with the operand format chosen per
+                          layer: bf16 (16 mantissa bits per product, half the tensor time)
+                          where the kernel feeds A from tensor memory (fs*nIn >= 128), tf32
+                          (21 bits) elsewhere; what SCN_PREC_AUTO resolves to by default    */
 };
 /* The tensor-core precision SCN_PREC_AUTO resolves to when the shape has a tensor-core path
  * (the host classes pack their weights for it).  No reference counterpart. */
@@ -236,13 +240,13 @@ int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, int rows_out,
 
 /* The same fused layer launched before the host knows the row count: rows_out_bound is an upper
  * bound (d_out and d_rules are sized for it), the kernel reads the count itself from *d_rows_out,
- * where an earlier call on the same stream (scn_rules_build's d_result[0], say) leaves it.  3xTF32
- * tensor-core kernel only (weights packed for SCN_PREC_3XTF32; SCN_ERR_UNSUPPORTED for other shapes),
- * no softmax.  It lets the first layer of a network start while the rulebooks' counts travel to the host.
+ * where an earlier call on the same stream (scn_rules_build's d_result[0], say) leaves it.  Split
+ * tensor-core kernel only (precision SCN_PREC_3XTF32 or SCN_PREC_SPLIT, weights packed for it;
+ * SCN_ERR_UNSUPPORTED for other shapes), no softmax.  It lets the first layer of a network start while the rulebooks' counts travel to the host.
  * No reference counterpart. */
 int scn_conv_nin_forward_dyn(const float *d_in, const int *d_rules, int rows_out_bound, const int *d_rows_out,
                              int fs, int nIn, const void *d_W_packed, const float *d_B, const float *d_prelu,
-                             int N, float p, int activation, float *d_out, scn_stream_t stream);
+                             int N, float p, int activation, float *d_out, int precision, scn_stream_t stream);
 
 /* ConvolutionalLayer gather + NetworkInNetworkLayer + MaxPoolingLayer in one kernel (ConvolutionalLayer.cu:124-133,
  * NetworkInNetworkLayer.cu:187-201, MaxPoolingLayer.cu:9-35) for pooling windows that do not overlap
@@ -257,12 +261,13 @@ int scn_conv_nin_forward_dyn(const float *d_in, const int *d_rules, int rows_out
  * and no workspace is given.  d_workspace (may be NULL): scn_conv_nin_workspace_bytes(rows_unpooled, ...)
  * bytes; with it (and rows_unpooled, and no d_rows_pool) a layer that splits K keeps doing so and the pooling
  * happens in the kernel that adds the partial sums.
- * 3xTF32 tensor-core kernel only; SCN_ERR_UNSUPPORTED for shapes it does not take. */
+ * Split tensor-core kernel only (precision SCN_PREC_3XTF32 or SCN_PREC_SPLIT, weights packed for it);
+ * SCN_ERR_UNSUPPORTED for shapes it does not take. */
 int scn_conv_nin_maxpool_forward(const float *d_in, const int *d_rules, int fs, int nIn, const void *d_W_packed,
                                  const float *d_B, const float *d_prelu, int N, float p, int activation,
                                  const int *d_pool_rules, int pool_cells, int rows_pool_bound, const int *d_rows_pool,
                                  int rows_unpooled, float *d_out, int *d_choices, void *d_workspace, size_t workspace_bytes,
-                                 scn_stream_t stream);
+                                 int precision, scn_stream_t stream);
 
 /* Two learnt layers in a row where the first has few rows and a long K (the top of a network: ConvolutionalLayer
  * gather + NetworkInNetworkLayer, NetworkInNetworkLayer.cu:187-201, then the classifier's NetworkInNetworkLayer with
@@ -270,11 +275,12 @@ int scn_conv_nin_maxpool_forward(const float *d_in, const int *d_rules, int fs, 
  * (d_workspace: scn_conv_nin_workspace_bytes(rows_out, ...) bytes, must be > 0) and the kernel that adds the partial
  * sums also applies the second layer W2[N x N2] (fp32, N2 <= 16, softmax allowed).  d_mid[rows_out x N] receives the
  * first layer's output as scn_conv_nin_forward_ws would write it, d_out[rows_out x N2] the second's.
+ * precision: SCN_PREC_3XTF32 or SCN_PREC_SPLIT (the first layer's packed weights are for it).
  * SCN_ERR_UNSUPPORTED where the first layer would not split K or the shapes do not fit: run the two layers. */
 int scn_conv_nin_nin_forward(const float *d_in, const int *d_rules, int rows_out, int fs, int nIn, const void *d_W_packed,
                              const float *d_B, const float *d_prelu, int N, float p, int activation, const float *d_W2,
                              const float *d_B2, const float *d_prelu2, int N2, float p2, int activation2, float *d_mid,
-                             float *d_out, void *d_workspace, size_t workspace_bytes, scn_stream_t stream);
+                             float *d_out, void *d_workspace, size_t workspace_bytes, int precision, scn_stream_t stream);
 
 /* One-time repack of W[K x N] (K = fs*nIn) for a tensor-core precision: bytes needed, then
  * the packing kernel.  No reference counterpart (the reference hands W to cuBLAS as is). */

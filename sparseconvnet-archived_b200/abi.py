@@ -14,7 +14,7 @@ c_int, c_ll, c_f, c_p, c_sz = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, c
 SCN_OK = 0
 LATTICE_SQUARE, LATTICE_TRIANGULAR = 0, 1
 NOSIGMOID, RELU, VLEAKYRELU, LEAKYRELU, TANH, SOFTMAX, PRELU, SIGMOID = range(8)
-PREC_AUTO, PREC_FP32, PREC_3XTF32, PREC_BF16, PREC_3XBF16 = -1, 0, 1, 2, 3
+PREC_AUTO, PREC_FP32, PREC_3XTF32, PREC_BF16, PREC_3XBF16, PREC_SPLIT = -1, 0, 1, 2, 3, 4
 DEV_ERR_CAPACITY, DEV_ERR_KEY, DEV_ERR_DUPLICATE = 1, 2, 4
 
 EXPORTS = [
@@ -375,37 +375,39 @@ class ResidentChain:
         return self.outs[p]
 
 
-def conv_nin_forward_dyn(feat, rules, fs, W, B, d_rows, rows_bound, prelu=None, p=1.0, act=NOSIGMOID, packed=None):
-    """scn_conv_nin_forward_dyn: the 3xTF32 kernel with its row count read from the int32 CUDA tensor
-    d_rows (clamped to rows_bound).  Returns [rows_bound x N]; rows past the count are left untouched."""
+def conv_nin_forward_dyn(feat, rules, fs, W, B, d_rows, rows_bound, prelu=None, p=1.0, act=NOSIGMOID, packed=None, precision=PREC_3XTF32):
+    """scn_conv_nin_forward_dyn: the split tensor-core kernel (weights packed for `precision`: PREC_3XTF32 or PREC_SPLIT) with
+    its row count read from the int32 CUDA tensor d_rows (clamped to rows_bound).  Returns [rows_bound x N]; rows past the
+    count are left untouched."""
     L = lib()
     K, N = W.shape
     nIn = K // fs
     out = torch.zeros((rows_bound, N), dtype=torch.float32, device=feat.device)
     check(L.scn_conv_nin_forward_dyn(_ptr(_f32(feat)), None if rules is None else _ptr(_i32(rules)), rows_bound, _ptr(_i32(d_rows)), fs, nIn,
-                                     _ptr(packed), _ptr(_f32(B)), None if prelu is None else _ptr(_f32(prelu)), N, p, act, _ptr(out), _stream()))
+                                     _ptr(packed), _ptr(_f32(B)), None if prelu is None else _ptr(_f32(prelu)), N, p, act, _ptr(out), precision, _stream()))
     return out
 
 
 def conv_nin_maxpool_forward(feat, rules, fs, W, B, pool_rules, cells, prelu=None, p=1.0, act=NOSIGMOID, packed=None, d_rows=None,
-                             rows_unpooled=0, split_k=False):
+                             rows_unpooled=0, split_k=False, precision=PREC_3XTF32):
     """scn_conv_nin_maxpool_forward -> (pooled [rows_pool x N], choices).  split_k: hand over the workspace with which a
     layer of few tiles splits K (the pooling then happens where the partial sums are added); needs rows_unpooled."""
     L = lib()
     K, N = W.shape
     rows_pool = pool_rules.numel() // cells
-    ws_bytes = L.scn_conv_nin_workspace_bytes(rows_unpooled, fs, K // fs, N, PREC_3XTF32) if (split_k and rows_unpooled) else 0
+    ws_bytes = L.scn_conv_nin_workspace_bytes(rows_unpooled, fs, K // fs, N, precision) if (split_k and rows_unpooled) else 0
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=feat.device) if ws_bytes else None
     out = torch.zeros((rows_pool, N), dtype=torch.float32, device=feat.device)
     choices = torch.full((rows_pool, N), -7, dtype=torch.int32, device=feat.device)
     check(L.scn_conv_nin_maxpool_forward(_ptr(_f32(feat)), _ptr(_i32(rules)), fs, K // fs, _ptr(packed), _ptr(_f32(B)),
                                          None if prelu is None else _ptr(_f32(prelu)), N, p, act, _ptr(_i32(pool_rules)), cells, rows_pool,
                                          None if d_rows is None else _ptr(_i32(d_rows)), rows_unpooled, _ptr(out), _ptr(choices),
-                                         _ptr(ws), ws_bytes, _stream()))
+                                         _ptr(ws), ws_bytes, precision, _stream()))
     return out, choices
 
 
-def conv_nin_nin_forward(feat, rules, fs, W, B, W2, B2, prelu=None, p=1.0, act=NOSIGMOID, p2=1.0, act2=SOFTMAX, packed=None):
+def conv_nin_nin_forward(feat, rules, fs, W, B, W2, B2, prelu=None, p=1.0, act=NOSIGMOID, p2=1.0, act2=SOFTMAX, packed=None,
+                         precision=PREC_3XTF32):
     """scn_conv_nin_nin_forward -> (first layer's output [rows x N], second's [rows x N2])."""
     L = lib()
     K, N = W.shape
@@ -413,11 +415,11 @@ def conv_nin_nin_forward(feat, rules, fs, W, B, W2, B2, prelu=None, p=1.0, act=N
     rows = feat.shape[0] if rules is None else rules.numel() // fs
     mid = torch.empty((rows, N), dtype=torch.float32, device=feat.device)
     out = torch.empty((rows, N2), dtype=torch.float32, device=feat.device)
-    ws_bytes = L.scn_conv_nin_workspace_bytes(rows, fs, K // fs, N, PREC_3XTF32)
+    ws_bytes = L.scn_conv_nin_workspace_bytes(rows, fs, K // fs, N, precision)
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=feat.device)
     check(L.scn_conv_nin_nin_forward(_ptr(_f32(feat)), None if rules is None else _ptr(_i32(rules)), rows, fs, K // fs, _ptr(packed), _ptr(_f32(B)),
                                      None if prelu is None else _ptr(_f32(prelu)), N, p, act, _ptr(_f32(W2)), _ptr(_f32(B2)), None, N2, p2, act2,
-                                     _ptr(mid), _ptr(out), _ptr(ws), ws_bytes, _stream()))
+                                     _ptr(mid), _ptr(out), _ptr(ws), ws_bytes, precision, _stream()))
     return mid, out
 
 

@@ -348,13 +348,13 @@ __global__ void k_softmax_rows(float *x, int rows, int N) {
 using namespace scn;
 
 extern "C" int scn_conv_auto_precision(void) {
-  // SCN_AUTO_PRECISION=3xtf32|3xbf16|bf16 overrides the default for a process (read once)
+  // SCN_AUTO_PRECISION=split|3xtf32|3xbf16|bf16 overrides the default for a process (read once)
   static const int chosen = [] {
     const char *e = getenv("SCN_AUTO_PRECISION");
     if (e && !strcmp(e, "3xbf16")) return (int)SCN_PREC_3XBF16;
     if (e && !strcmp(e, "bf16")) return (int)SCN_PREC_BF16;
     if (e && !strcmp(e, "3xtf32")) return (int)SCN_PREC_3XTF32;
-    return (int)SCN_PREC_3XTF32;
+    return (int)SCN_PREC_SPLIT;
   }();
   return chosen;
 }
@@ -382,7 +382,7 @@ extern "C" int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, in
   if (act < SCN_NOSIGMOID || act > SCN_SIGMOID) return fail(SCN_ERR_INVALID, "unknown activation");
   if (act == SCN_PRELU && !d_prelu) return fail(SCN_ERR_INVALID, "PReLU slopes missing");
   if (act == SCN_SOFTMAX && N > 1024) return fail(SCN_ERR_INVALID, "softmax over more than 1024 classes");
-  if (precision < SCN_PREC_AUTO || precision > SCN_PREC_3XBF16) return fail(SCN_ERR_INVALID, "unknown precision");
+  if (precision < SCN_PREC_AUTO || precision > SCN_PREC_SPLIT) return fail(SCN_ERR_INVALID, "unknown precision");
   if (rows_out == 0) return SCN_OK;
   if (!d_in || !d_W || !d_B || !d_out) return fail(SCN_ERR_INVALID, "null pointer");
   cudaStream_t s = (cudaStream_t)stream;
@@ -446,38 +446,41 @@ extern "C" int scn_conv_nin_forward_ws(const float *d_in, const int *d_rules, in
 
 extern "C" int scn_conv_nin_forward_dyn(const float *d_in, const int *d_rules, int rows_out_bound, const int *d_rows_out, int fs, int nIn,
                                         const void *d_W_packed, const float *d_B, const float *d_prelu, int N, float p, int act,
-                                        float *d_out, scn_stream_t stream) {
+                                        float *d_out, int precision, scn_stream_t stream) {
   clear_error();
+  if (precision != SCN_PREC_3XTF32 && precision != SCN_PREC_SPLIT) return fail(SCN_ERR_UNSUPPORTED, "precision must be SCN_PREC_3XTF32 or SCN_PREC_SPLIT here");
   if (rows_out_bound < 1 || fs < 1 || nIn < 1 || N < 1) return fail(SCN_ERR_INVALID, "bad conv/NiN sizes");
   if (!d_rules && fs != 1) return fail(SCN_ERR_INVALID, "fs must be 1 without rules");
   if (act < SCN_NOSIGMOID || act > SCN_SIGMOID || act == SCN_SOFTMAX) return fail(SCN_ERR_INVALID, "activation not supported here");
   if (act == SCN_PRELU && !d_prelu) return fail(SCN_ERR_INVALID, "PReLU slopes missing");
   if (!d_in || !d_rows_out || !d_W_packed || !d_B || !d_out) return fail(SCN_ERR_INVALID, "null pointer");
-  if (!tc_shape_ok(fs, nIn, N, SCN_PREC_3XTF32)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
-  return tc_launch(d_in, d_rules, rows_out_bound, fs, nIn, d_W_packed, d_B, d_prelu, N, p, act, SCN_PREC_3XTF32, d_out, nullptr, 0,
+  if (!tc_shape_ok(fs, nIn, N, precision)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
+  return tc_launch(d_in, d_rules, rows_out_bound, fs, nIn, d_W_packed, d_B, d_prelu, N, p, act, precision, d_out, nullptr, 0,
                    (cudaStream_t)stream, d_rows_out);
 }
 
 extern "C" int scn_conv_nin_maxpool_forward(const float *d_in, const int *d_rules, int fs, int nIn, const void *d_W_packed, const float *d_B,
                                             const float *d_prelu, int N, float p, int act, const int *d_pool_rules, int pool_cells,
                                             int rows_pool_bound, const int *d_rows_pool, int rows_unpooled, float *d_out, int *d_choices,
-                                            void *d_workspace, size_t workspace_bytes, scn_stream_t stream) {
+                                            void *d_workspace, size_t workspace_bytes, int precision, scn_stream_t stream) {
   clear_error();
+  if (precision != SCN_PREC_3XTF32 && precision != SCN_PREC_SPLIT) return fail(SCN_ERR_UNSUPPORTED, "precision must be SCN_PREC_3XTF32 or SCN_PREC_SPLIT here");
   if (rows_pool_bound < 0 || fs < 1 || nIn < 1 || N < 1) return fail(SCN_ERR_INVALID, "bad conv/NiN sizes");
   if (act < SCN_NOSIGMOID || act > SCN_SIGMOID || act == SCN_SOFTMAX) return fail(SCN_ERR_INVALID, "activation not supported here");
   if (act == SCN_PRELU && !d_prelu) return fail(SCN_ERR_INVALID, "PReLU slopes missing");
   if (rows_pool_bound == 0) return SCN_OK;
   if (!d_in || !d_rules || !d_W_packed || !d_B || !d_pool_rules || !d_out || !d_choices) return fail(SCN_ERR_INVALID, "null pointer");
-  if (!tc_shape_ok(fs, nIn, N, SCN_PREC_3XTF32)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
-  return tc_launch(d_in, d_rules, rows_pool_bound, fs, nIn, d_W_packed, d_B, d_prelu, N, p, act, SCN_PREC_3XTF32, d_out, d_workspace,
+  if (!tc_shape_ok(fs, nIn, N, precision)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
+  return tc_launch(d_in, d_rules, rows_pool_bound, fs, nIn, d_W_packed, d_B, d_prelu, N, p, act, precision, d_out, d_workspace,
                    workspace_bytes, (cudaStream_t)stream, d_rows_pool, d_pool_rules, pool_cells, d_choices, rows_unpooled);
 }
 
 extern "C" int scn_conv_nin_nin_forward(const float *d_in, const int *d_rules, int rows_out, int fs, int nIn, const void *d_W_packed,
                                         const float *d_B, const float *d_prelu, int N, float p, int act, const float *d_W2, const float *d_B2,
                                         const float *d_prelu2, int N2, float p2, int act2, float *d_mid, float *d_out, void *d_workspace,
-                                        size_t workspace_bytes, scn_stream_t stream) {
+                                        size_t workspace_bytes, int precision, scn_stream_t stream) {
   clear_error();
+  if (precision != SCN_PREC_3XTF32 && precision != SCN_PREC_SPLIT) return fail(SCN_ERR_UNSUPPORTED, "precision must be SCN_PREC_3XTF32 or SCN_PREC_SPLIT here");
   if (rows_out < 0 || fs < 1 || nIn < 1 || N < 1 || N2 < 1) return fail(SCN_ERR_INVALID, "bad conv/NiN sizes");
   if (!d_rules && fs != 1) return fail(SCN_ERR_INVALID, "fs must be 1 without rules");
   if (act < SCN_NOSIGMOID || act > SCN_SIGMOID || act == SCN_SOFTMAX) return fail(SCN_ERR_INVALID, "activation not supported for the first layer");
@@ -485,10 +488,10 @@ extern "C" int scn_conv_nin_nin_forward(const float *d_in, const int *d_rules, i
   if ((act == SCN_PRELU && !d_prelu) || (act2 == SCN_PRELU && !d_prelu2)) return fail(SCN_ERR_INVALID, "PReLU slopes missing");
   if (rows_out == 0) return SCN_OK;
   if (!d_in || !d_W_packed || !d_B || !d_W2 || !d_B2 || !d_mid || !d_out) return fail(SCN_ERR_INVALID, "null pointer");
-  if (N2 > 16 || N % 4 != 0 || !d_workspace || !tc_shape_ok(fs, nIn, N, SCN_PREC_3XTF32))
-    return fail(SCN_ERR_UNSUPPORTED, "needs the 3xTF32 kernel with a K split and at most 16 outputs of the second layer");
+  if (N2 > 16 || N % 4 != 0 || !d_workspace || !tc_shape_ok(fs, nIn, N, precision))
+    return fail(SCN_ERR_UNSUPPORTED, "needs the split tensor-core kernel with a K split and at most 16 outputs of the second layer");
   FinishNin f2 = {d_W2, d_B2, d_prelu2, N2, p2, act2, d_out};
-  return tc_launch(d_in, d_rules, rows_out, fs, nIn, d_W_packed, d_B, d_prelu, N, p, act, SCN_PREC_3XTF32, d_mid, d_workspace, workspace_bytes,
+  return tc_launch(d_in, d_rules, rows_out, fs, nIn, d_W_packed, d_B, d_prelu, N, p, act, precision, d_mid, d_workspace, workspace_bytes,
                    (cudaStream_t)stream, nullptr, nullptr, 0, nullptr, 0, nullptr, &f2);
 }
 

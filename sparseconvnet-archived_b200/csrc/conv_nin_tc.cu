@@ -33,6 +33,7 @@
 // records an error code in g_tc_error and carries on to its normal exit, so tensor memory is
 // always released and the context stays usable.
 #include "conv_nin_tc.cuh"
+#include <cstdlib>
 #include <type_traits>
 #include <cuda_bf16.h>
 
@@ -108,6 +109,21 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
   d |= (uint64_t)2 << 61;             // SWIZZLE_128B
   return d;
 }
+// The same for a tile whose rows are 64 bytes long (32 bf16 values of K), SWIZZLE_64B: 8-row groups 512 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc64(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3fff);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;             // SWIZZLE_64B
+  return d;
+}
+// bf16 operands (kind::f16), A in tensor memory: lane = row, each 32-bit column holds two consecutive values of K
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
                ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
@@ -130,7 +146,7 @@ struct Params {
   const float *in; const int *rules; int rows, fs, nIn;
   const unsigned char *packed; const float *bias; const float *prelu;
   int N, BN, nTiles, nSlabs, stages, tmemCols, rulesBytes; float p; int act; float *out; uint32_t idesc;
-  int mTiles, accStride, K, generic, epi2, rulesDouble, rawEntries, nStages64, atmem, aBase; const int *rowsPtr; const int *poolRules; int *choices; int poolCells; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
+  int mTiles, accStride, K, generic, epi2, rulesDouble, rawEntries, nStages64, atmem, aBase, bf16; const int *rowsPtr; const int *poolRules; int *choices; int poolCells; int kSplit; float *partial; // K split over kSplit CTAs per tile: raw partial sums go to partial[split][row][col]
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t srcBytes) {
@@ -295,7 +311,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   int *rulesS = reinterpret_cast<int *>(smem_raw); // [128 x fs] rule tile of the current item (when it fits)
   // 1024-byte alignment: the swizzle pattern is a function of absolute shared-memory address bits
   unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + (P.rulesDouble ? 2 : 1) * P.rulesBytes + 1023) & ~(uintptr_t)1023);
-  const int bHalf = P.BN * ROW_BYTES;            // one of B_hi / B_lo
+  const int bHalf = P.BN * ((ATMEM && P.bf16) ? ROW_BYTES / 2 : ROW_BYTES); // one of B_hi / B_lo: 32 values of K per row, tf32 or bf16
   const int aBytes = ATMEM ? A_HALF : 2 * A_HALF;  // A raw (= hi) [, A_lo]
   const int stageBytes = aBytes + 2 * bHalf;       // then B_hi, B_lo
   float *epi = reinterpret_cast<float *>(smem + (size_t)P.stages * stageBytes);
@@ -569,8 +585,38 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
             const uint4 x = *reinterpret_cast<const uint4 *>(rowp + ((c ^ (t & 7)) << 4));
             v[4 * c] = x.x; v[4 * c + 1] = x.y; v[4 * c + 2] = x.z; v[4 * c + 3] = x.w;
           }
+          // bf16 operands: x = hi + lo with hi = bf16(x), lo = bf16(x - hi); two consecutive values of K share a 32-bit
+          // column (the lower one in the lower half).  Converted BEFORE the wait for the slot, so that only the stores
+          // to tensor memory stand between the MMAs that free the slot and the MMAs that read it next.
+          uint32_t w16[32];
+          if (P.bf16) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float a = __uint_as_float(v[2 * j]), b = __uint_as_float(v[2 * j + 1]);
+              const __nv_bfloat162 hi2 = __floats2bfloat162_rn(a, b);
+              const __nv_bfloat162 lo2 = __floats2bfloat162_rn(a - __low2float(hi2), b - __high2float(hi2));
+              w16[j] = *reinterpret_cast<const uint32_t *>(&hi2);
+              w16[16 + j] = *reinterpret_cast<const uint32_t *>(&lo2);
+            }
+          }
           mbar_wait(aEmptyBar + 8 * slot.idx, slot.phase ^ 1, 8); // the MMAs that read this slot have finished
           tc_fence_after();
+          if (P.bf16) {
+            // hi image at columns +0..15 of the slot, lo at +16..31
+            const uint32_t taddr16 = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(P.aBase + slot.idx * 32);
+#pragma unroll
+            for (int g16 = 0; g16 < 2; ++g16)
+              asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                           ::"r"(taddr16 + g16 * 16), "r"(w16[16 * g16]), "r"(w16[16 * g16 + 1]), "r"(w16[16 * g16 + 2]), "r"(w16[16 * g16 + 3]),
+                             "r"(w16[16 * g16 + 4]), "r"(w16[16 * g16 + 5]), "r"(w16[16 * g16 + 6]), "r"(w16[16 * g16 + 7]), "r"(w16[16 * g16 + 8]),
+                             "r"(w16[16 * g16 + 9]), "r"(w16[16 * g16 + 10]), "r"(w16[16 * g16 + 11]), "r"(w16[16 * g16 + 12]), "r"(w16[16 * g16 + 13]),
+                             "r"(w16[16 * g16 + 14]), "r"(w16[16 * g16 + 15]) : "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(aFullBar + 8 * slot.idx);
+            slot.next();
+            continue;
+          }
           // lanes 32*(warp % 4)..+31 belong to this warp; hi image at columns +0..31, lo at +32..63
           const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(P.aBase + slot.idx * 64);
 #pragma unroll
@@ -650,6 +696,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
           if (ATMEM) {
             mbar_wait(aFullBar + 8 * slot.idx, slot.phase, 9);
             tc_fence_after();
+            if (P.bf16) { // two K = 16 steps per slab and product; A advances 8 columns, B 32 bytes per step
+              const uint32_t t16Hi = tmem + (uint32_t)(P.aBase + slot.idx * 32), t16Lo = t16Hi + 16;
+              const uint64_t eBhi = smem_desc64(bHi), eBlo = smem_desc64(bLo);
+#pragma unroll
+              for (int k = 0; k < 2; ++k) mma_bf16_ts(acc, t16Lo + 8 * k, eBhi + 2 * k, P.idesc, (q | k) != 0);
+#pragma unroll
+              for (int k = 0; k < 2; ++k) mma_bf16_ts(acc, t16Hi + 8 * k, eBlo + 2 * k, P.idesc, 1);
+#pragma unroll
+              for (int k = 0; k < 2; ++k) mma_bf16_ts(acc, t16Hi + 8 * k, eBhi + 2 * k, P.idesc, 1);
+              mma_commit(emptyBar + 8 * st);
+              mma_commit(aEmptyBar + 8 * slot.idx);
+              slot.next();
+              continue;
+            }
             const uint32_t tHi = tmem + (uint32_t)(P.aBase + slot.idx * 64), tLo = tHi + 32;
 #pragma unroll
             for (int k = 0; k < 4; ++k) mma_tf32_ts(acc, tLo + 8 * k, dBhi + 2 * k, P.idesc, (q | k) != 0);
@@ -995,6 +1055,25 @@ __global__ void k_pack_bf16(const float *__restrict__ W, int K, int N, int BN, i
   }
 }
 
+// W[K x N] row-major -> per (column tile, 32-wide K slab) one contiguous block: the bf16 hi image [BN x 32] (K-major rows of
+// 64 bytes in SWIZZLE_64B order: 16-byte chunk c of row n sits at chunk c ^ ((n >> 1) & 3)), then the lo image.
+__global__ void k_pack_bf16_slab(const float *__restrict__ W, int K, int N, int BN, int nTiles, int nSlabs, unsigned short *__restrict__ packed) {
+  const long long total = (long long)nTiles * nSlabs * BN * SLAB;
+  for (long long q = (long long)blockIdx.x * blockDim.x + threadIdx.x; q < total; q += (long long)gridDim.x * blockDim.x) {
+    const int kl = (int)(q % SLAB);
+    const int nl = (int)((q / SLAB) % BN);
+    const long long blk = q / ((long long)SLAB * BN);
+    const int slab = (int)(blk % nSlabs), tile = (int)(blk / nSlabs);
+    const int k = slab * SLAB + kl, n = tile * BN + nl;
+    const float w = (k < K && n < N) ? W[(long long)k * N + n] : 0.f;
+    const __nv_bfloat16 hi = __float2bfloat16_rn(w), lo = __float2bfloat16_rn(w - __bfloat162float(hi));
+    const int off = (nl >> 3) * 512 + (nl & 7) * 64 + ((((kl >> 3) ^ ((nl >> 1) & 3))) << 4) + (kl & 7) * 2;
+    unsigned short *base = packed + blk * (2LL * BN * SLAB);
+    base[off >> 1] = *reinterpret_cast<const unsigned short *>(&hi);
+    base[BN * SLAB + (off >> 1)] = *reinterpret_cast<const unsigned short *>(&lo);
+  }
+}
+
 // W[K x N] row-major -> per (column tile, K slab) one contiguous block: the hi image then the lo
 // image of the [BN x 32] K-major tile, already in the SWIZZLE_128B shared-memory order.
 __global__ void k_pack_tf32(const float *__restrict__ W, int K, int N, int BN, int nTiles, int nSlabs, float *__restrict__ packed) {
@@ -1180,30 +1259,41 @@ int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) 
   return k < 2 ? 1 : k;
 }
 
-struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, rulesDouble, accStride, atmem, aBase; size_t smemBytes; };
+struct Tiling { int BN, nTiles, nSlabs, stages, tmemCols, rulesBytes, rulesDouble, accStride, atmem, aBase, bf16; size_t smemBytes; };
 
 // Word-wise gathers of at most this many input channels use the row-per-lane form with two epilogue groups
 constexpr int ROWWISE_MAX_NIN = 4;
 
+// Operand format of the three-product split (x = hi + lo for both operands, lo*lo dropped).  tf32 (SCN_PREC_3XTF32): 21
+// mantissa bits per product.  SCN_PREC_SPLIT chooses per layer: bf16 operands (16 bits per product: measured 1.0-2.4e-5
+// against fp64 on the benchmark networks, bound 1e-4; half the tensor-pipe time and half the weight bytes in shared
+// memory) where the A operand is fed from tensor memory (K >= 128: four slabs or more), tf32 elsewhere.  The choice
+// depends on K and N only, because the weights are packed for it before any batch is seen.
+bool is_split(int precision) { return precision == SCN_PREC_3XTF32 || precision == SCN_PREC_SPLIT; }
+
 // oneItem: no CTA gets more than one work item, so the second accumulator is never used and its columns can
 // hold the A slots: the tensor-memory A path then reaches BN = 256.
-bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool oneItem = false, bool pool = false, bool epi2 = false) {
+bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool allowBf16, bool oneItem = false, bool pool = false, bool epi2 = false) {
   if (K < 1 || N < 16) return false;
+  t->nSlabs = (K + SLAB - 1) / SLAB; // the last slab is zero-padded
+  t->bf16 = (allowBf16 && t->nSlabs >= 4 && !epi2) ? 1 : 0;
   const int epiBytes = epi2 ? 2 * EPI_BYTES + BM * 4 : EPI_BYTES;
   t->rulesBytes = (haveRules && fs <= 32 && !(epi2 && !pool)) ? BM * fs * 4 : 0; // (the row-per-lane gather reads rules from global memory)
   if (pool) { // fused max-pooling: staged rules are mandatory, two buffers, each followed by the tile's 128 row ids
     if (!t->rulesBytes) return false;
     t->rulesBytes += BM * 4;
   }
-  t->nTiles = (N + 255) / 256; // narrower tiles (so that every layer could use the tensor-memory A path) were measured slower: A is gathered once per column tile
+  // tf32: narrower tiles (so that every layer could use the tensor-memory A path) were measured slower: A is gathered once
+  // per column tile.  bf16: two accumulators and two 32-column A slots must fit in 512 columns: tiles of at most 224.
+  t->nTiles = t->bf16 ? (N + 223) / 224 : (N + 255) / 256;
   t->BN = ((N + t->nTiles - 1) / t->nTiles + 15) / 16 * 16;
-  t->nSlabs = (K + SLAB - 1) / SLAB; // the last slab is zero-padded
   t->accStride = (t->BN + 31) / 32 * 32;
   // 64-column A slots in tensor memory beside the two accumulators: two (BN <= 192) or none, A then stays in
   // shared memory (a single slot serialises split and MMA and was measured slower); short K gains nothing
   t->aBase = (oneItem ? 1 : 2) * t->accStride;
-  t->atmem = (t->nSlabs >= 4 && t->aBase + 128 <= 512) ? 2 : 0;
-  const int stageBytes = (t->atmem ? 1 : 2) * A_HALF + 2 * t->BN * ROW_BYTES;
+  t->atmem = (t->nSlabs >= 4 && t->aBase + (t->bf16 ? 64 : 128) <= 512) ? 2 : 0;
+  if (t->bf16 && !t->atmem) return false; // (cannot happen: BN <= 224)
+  const int stageBytes = (t->atmem ? 1 : 2) * A_HALF + 2 * t->BN * (t->bf16 ? ROW_BYTES / 2 : ROW_BYTES);
   auto stagesWith = [&](int ruleBufs) {
     const int n = (int)((226 * 1024 - 1024 - ruleBufs * t->rulesBytes - epiBytes) / stageBytes);
     return n > MAX_STAGES ? MAX_STAGES : n;
@@ -1213,7 +1303,7 @@ bool make_tiling(int K, int N, int fs, bool haveRules, Tiling *t, bool oneItem =
   t->stages = stages;
   t->rulesDouble = (pool || (t->rulesBytes > 0 && stagesWith(2) == stages)) ? 1 : 0; // prefetch the next tile's rules if that costs no stage
   int cols = 32;
-  while (cols < (t->atmem ? t->aBase + 128 : 2 * t->accStride)) cols *= 2; // the accumulators [+ the A slots], at most 512 columns
+  while (cols < (t->atmem ? t->aBase + (t->bf16 ? 64 : 128) : 2 * t->accStride)) cols *= 2; // the accumulators [+ the A slots], at most 512 columns
   t->tmemCols = cols;
   t->smemBytes = (size_t)stages * stageBytes + 1024 + (size_t)(1 + t->rulesDouble) * t->rulesBytes + epiBytes;
   return true;
@@ -1265,8 +1355,8 @@ bool tc_shape_ok(int fs, int nIn, int N, int precision) {
   if (nIn % SLAB == 0 && nIn > ZERO_ROW_FLOATS) return false; // the 16-byte gather reads missing rows from g_zero_row
   int raw, st64;
   if (passes_of(precision)) return N % 4 == 0 && make_tiling16(fs * nIn, N, fs, true, passes_of(precision), &t, &raw, &st64);
-  if (precision != SCN_PREC_3XTF32) return false;
-  return N % 4 == 0 && make_tiling(fs * nIn, N, fs, true, &t);
+  if (!is_split(precision)) return false;
+  return N % 4 == 0 && make_tiling(fs * nIn, N, fs, true, &t, precision == SCN_PREC_SPLIT);
 }
 
 size_t tc_packed_bytes(int K, int N, int precision) {
@@ -1276,9 +1366,9 @@ size_t tc_packed_bytes(int K, int N, int precision) {
     if (!make_tiling16(K, N, 1, false, passes, &t, &raw, &st64)) return 0;
     return (size_t)t.nTiles * st64 * (passes == 3 ? 2 : 1) * t.BN * ROW_BYTES;
   }
-  if (precision != SCN_PREC_3XTF32) return 0;
-  if (!make_tiling(K, N, 1, false, &t)) return 0;
-  return (size_t)t.nTiles * t.nSlabs * 2 * t.BN * ROW_BYTES;
+  if (!is_split(precision)) return 0;
+  if (!make_tiling(K, N, 1, false, &t, precision == SCN_PREC_SPLIT)) return 0;
+  return (size_t)t.nTiles * t.nSlabs * 2 * t.BN * (t.bf16 ? ROW_BYTES / 2 : ROW_BYTES);
 }
 
 int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaStream_t s) {
@@ -1291,8 +1381,13 @@ int tc_pack(const float *d_W, int K, int N, int precision, void *d_packed, cudaS
     SCN_LAUNCH_CHECK("k_pack_bf16");
     return SCN_OK;
   }
-  if (precision != SCN_PREC_3XTF32 || !make_tiling(K, N, 1, false, &t)) return fail(SCN_ERR_UNSUPPORTED, "no tensor-core layout for this shape/precision");
+  if (!is_split(precision) || !make_tiling(K, N, 1, false, &t, precision == SCN_PREC_SPLIT)) return fail(SCN_ERR_UNSUPPORTED, "no tensor-core layout for this shape/precision");
   const long long total = (long long)t.nTiles * t.nSlabs * t.BN * SLAB;
+  if (t.bf16) {
+    k_pack_bf16_slab<<<grid_for(total, 256), 256, 0, s>>>(d_W, K, N, t.BN, t.nTiles, t.nSlabs, (unsigned short *)d_packed);
+    SCN_LAUNCH_CHECK("k_pack_bf16_slab");
+    return SCN_OK;
+  }
   k_pack_tf32<<<grid_for(total, 256), 256, 0, s>>>(d_W, K, N, t.BN, t.nTiles, t.nSlabs, (float *)d_packed);
   SCN_LAUNCH_CHECK("k_pack_tf32");
   return SCN_OK;
@@ -1306,7 +1401,7 @@ size_t tc_workspace_bytes(int rows, int fs, int nIn, int N, int precision) {
     const int k = choose_ksplit(((rows + BM - 1) / BM) * t.nTiles, st64 * 2, rows, N, (size_t)-1);
     return k > 1 ? (size_t)k * rows * N * sizeof(float) : 0;
   }
-  if (precision != SCN_PREC_3XTF32 || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, true, &t)) return 0;
+  if (!is_split(precision) || N % 4 != 0 || !make_tiling(fs * nIn, N, fs, true, &t, precision == SCN_PREC_SPLIT)) return 0;
   const int tiles = ((rows + BM - 1) / BM) * t.nTiles;
   const int k = choose_ksplit(tiles, t.nSlabs, rows, N, (size_t)-1);
   return k > 1 ? (size_t)k * rows * N * sizeof(float) : 0;
@@ -1322,11 +1417,11 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   const bool pool = d_pool_rules != nullptr;
   // pooled: `rows` counts pooled rows; the kernel's row space is pooled rows x cells (a tile = 128 / cells windows)
   if (pool && (passes || !d_rules || !d_choices || pool_cells < 2 || pool_cells > 32 || (pool_cells & (pool_cells - 1)) || (long long)rows * pool_cells > INT_MAX))
-    return fail(SCN_ERR_UNSUPPORTED, "fused max-pooling needs the 3xTF32 kernel, rules, and 2, 4, 8, 16 or 32 cells per window");
+    return fail(SCN_ERR_UNSUPPORTED, "fused max-pooling needs the split (tf32 / bf16 operand) kernel, rules, and 2, 4, 8, 16 or 32 cells per window");
   // Where the layer alone would split K (few tiles) the fused row space is not used: the plain kernel writes its
   // partial sums over the layer's own rows and the pooling happens in the finishing kernel.
   if (pool && !passes && rows_unpooled > 0 && d_ws && !d_rows && N % 4 == 0 && ((uintptr_t)d_ws & 15) == 0 &&
-      precision == SCN_PREC_3XTF32 && make_tiling(fs * nIn, N, fs, true, &t)) {
+      is_split(precision) && make_tiling(fs * nIn, N, fs, true, &t, precision == SCN_PREC_SPLIT)) {
     const int plainTiles = ((rows_unpooled + BM - 1) / BM) * t.nTiles;
     if (choose_ksplit(plainTiles, t.nSlabs, rows_unpooled, N, wsBytes) > 1) {
       FinishPool fp = {d_pool_rules, pool_cells, rows, d_choices};
@@ -1336,7 +1431,7 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   }
   if (pool) rows *= pool_cells;
   const bool ok = N % 4 == 0 && (passes ? make_tiling16(fs * nIn, N, fs, d_rules != nullptr, passes, &t, &rawEntries, &nStages64)
-                                        : precision == SCN_PREC_3XTF32 && make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, false, pool));
+                                        : is_split(precision) && make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, precision == SCN_PREC_SPLIT, false, pool));
   if (!ok || (nIn % SLAB == 0 && nIn > ZERO_ROW_FLOATS)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
   if (((uintptr_t)d_in | (uintptr_t)d_out | (uintptr_t)d_packed) & 15) return fail(SCN_ERR_INVALID, "tensor-core path needs 16-byte aligned buffers");
   Params P;
@@ -1356,17 +1451,18 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   // few input channels and one slab (a first layer): row-per-lane gather that also writes the lo image, and the
   // four warps that would split become a second epilogue group
   const bool epi2 = !passes && d_rules && nIn % SLAB != 0 && nIn <= ROWWISE_MAX_NIN && t.nSlabs == 1 && kSplit == 1 && !t.atmem;
-  if (oneItem || epi2) make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, oneItem, pool, epi2);
+  if (oneItem || epi2) make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, precision == SCN_PREC_SPLIT, oneItem, pool, epi2);
   P.epi2 = epi2 ? 1 : 0;
   P.rawEntries = rawEntries; P.nStages64 = nStages64; P.atmem = passes ? 0 : t.atmem; P.aBase = t.aBase;
-  if (d_rows && (passes || kSplit > 1)) return fail(SCN_ERR_UNSUPPORTED, "a device-side row count needs the 3xTF32 kernel without K split");
+  P.bf16 = (!passes && t.bf16 && t.atmem) ? 1 : 0;
+  if (d_rows && (passes || kSplit > 1)) return fail(SCN_ERR_UNSUPPORTED, "a device-side row count needs the split (tf32 / bf16 operand) kernel without K split");
   P.rowsPtr = d_rows; P.poolRules = d_pool_rules; P.poolCells = pool_cells; P.choices = d_choices;
   P.in = d_in; P.rules = d_rules; P.rows = rows; P.fs = fs; P.nIn = nIn;
   P.packed = (const unsigned char *)d_packed; P.bias = d_B; P.prelu = d_prelu;
   P.N = N; P.BN = t.BN; P.nTiles = t.nTiles; P.nSlabs = t.nSlabs; P.stages = t.stages; P.tmemCols = t.tmemCols; P.rulesBytes = t.rulesBytes;
   P.p = p; P.act = act; P.out = d_out;
   // instruction descriptor: D = fp32, A = B = tf32 (2) or bf16 (1), both K-major, N = BN, M = 128
-  const uint32_t fmt = passes ? 1u : 2u;
+  const uint32_t fmt = (passes || P.bf16) ? 1u : 2u;
   P.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(t.BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   P.kSplit = kSplit;
   P.partial = (float *)d_ws;

@@ -21,6 +21,15 @@ namespace {
 // Every batch type runs the same forward kernels; a TRAINBATCH is refused only by learnt layers that would have to draw a
 // dropout subset (see NetworkInNetworkLayer::enqueueRules).
 void requireInference(const SpatiallySparseBatch &) {}
+// The split tensor-core precision (SCN_PREC_3XTF32 or SCN_PREC_SPLIT) a layer set to `precision` runs a batch of this type
+// in, or -1 if it runs in another one.  Training steps use tf32 operands throughout: the bf16 operands that SCN_PREC_SPLIT
+// gives layers with long K carry 16 mantissa bits per product, and a gradient that has gone through a whole forward and
+// backward pass amplifies that about 250 times.
+int splitPrecision(int precision, const SpatiallySparseBatch &batch) {
+  int p = precision == SCN_PREC_AUTO ? scn_conv_auto_precision() : precision;
+  if (p == SCN_PREC_SPLIT && batch.type == TRAINBATCH) p = SCN_PREC_3XTF32;
+  return (p == SCN_PREC_3XTF32 || p == SCN_PREC_SPLIT) ? p : -1;
+}
 // Zeroed device vector of n elements.
 void zeroed(vectorCUDA<float> &v, int n, cudaMemStream &ms) {
   v.copyToGPU();
@@ -461,15 +470,16 @@ void NetworkInNetworkLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySpa
 bool NetworkInNetworkLayer::forwardsEarly(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &source, SpatiallySparseBatchInterface &input,
                                           SpatiallySparseBatchInterface &output, int cells, long long rowsBound, const int *d_rows) {
   if (batch.type == TRAINBATCH || rowsBound < 1 || rowsBound * (long long)nFeaturesOut > INT_MAX) return false;
-  if ((precision != SCN_PREC_AUTO && precision != SCN_PREC_3XTF32) || scn_conv_auto_precision() != SCN_PREC_3XTF32) return false;
+  const int sp = splitPrecision(precision, batch);
+  if (sp < 0) return false;
   if (fn == SOFTMAX || nFeaturesOut % 4 != 0 || nFeaturesIn % cells != 0) return false;
   const int nIn = nFeaturesIn / cells;
-  const void *pk = packedWeights(cells, nIn, SCN_PREC_3XTF32);
+  const void *pk = packedWeights(cells, nIn, sp);
   if (!pk) return false;
   output.sub->features.resize((int)(rowsBound * nFeaturesOut));
   const float p = 1.0f - (batch.type != RESCALEBATCH ? dropout : 0.0f);
   const int rc = scn_conv_nin_forward_dyn(source.sub->features.dPtr(), input.rules.dPtr(), (int)rowsBound, d_rows, cells, nIn, pk, B.dPtr(), slopes(),
-                                          nFeaturesOut, p, (int)fn, output.sub->features.dPtr(), memStream.stream);
+                                          nFeaturesOut, p, (int)fn, output.sub->features.dPtr(), sp, memStream.stream);
   if (rc == SCN_ERR_UNSUPPORTED) return false; // e.g. so few rows that K would be split
   scnSafeCall(rc);
   return true;
@@ -485,10 +495,11 @@ bool NetworkInNetworkLayer::forwardsPooled(SpatiallySparseBatch &batch, Spatiall
                                            SpatiallySparseBatchInterface &poolOutput, int convCells, int poolCells, long long rowsPoolBound,
                                            const int *d_rowsPool, int rowsUnpooled) {
   if (batch.type == TRAINBATCH || rowsPoolBound < 1 || rowsPoolBound * (long long)nFeaturesOut > INT_MAX) return false;
-  if ((precision != SCN_PREC_AUTO && precision != SCN_PREC_3XTF32) || scn_conv_auto_precision() != SCN_PREC_3XTF32) return false;
+  const int sp = splitPrecision(precision, batch);
+  if (sp < 0) return false;
   if (fn == SOFTMAX || nFeaturesOut % 4 != 0 || nFeaturesIn % convCells != 0) return false;
   const int nIn = nFeaturesIn / convCells;
-  const void *pk = packedWeights(convCells, nIn, SCN_PREC_3XTF32);
+  const void *pk = packedWeights(convCells, nIn, sp);
   if (!pk) return false;
   const int n = (int)(rowsPoolBound * nFeaturesOut);
   poolOutput.sub->features.resize(n);
@@ -496,14 +507,14 @@ bool NetworkInNetworkLayer::forwardsPooled(SpatiallySparseBatch &batch, Spatiall
   const float p = 1.0f - (batch.type != RESCALEBATCH ? dropout : 0.0f);
   // a layer of few tiles keeps its K split: the pooling then runs where the partial sums are added
   void *ws = nullptr;
-  const size_t wsBytes = (rowsUnpooled > 0 && !d_rowsPool) ? scn_conv_nin_workspace_bytes(rowsUnpooled, convCells, nIn, nFeaturesOut, SCN_PREC_3XTF32) : 0;
+  const size_t wsBytes = (rowsUnpooled > 0 && !d_rowsPool) ? scn_conv_nin_workspace_bytes(rowsUnpooled, convCells, nIn, nFeaturesOut, sp) : 0;
   if (wsBytes) {
     splitScratch.resize((int)((wsBytes + sizeof(float) - 1) / sizeof(float)));
     ws = splitScratch.dPtr();
   }
   const int rc = scn_conv_nin_maxpool_forward(source.sub->features.dPtr(), input.rules.dPtr(), convCells, nIn, pk, B.dPtr(), slopes(), nFeaturesOut, p,
                                               (int)fn, poolOutput.rules.dPtr(), poolCells, (int)rowsPoolBound, d_rowsPool, rowsUnpooled,
-                                              poolOutput.sub->features.dPtr(), poolOutput.sub->poolingChoices.dPtr(), ws, wsBytes, memStream.stream);
+                                              poolOutput.sub->features.dPtr(), poolOutput.sub->poolingChoices.dPtr(), ws, wsBytes, sp, memStream.stream);
   if (rc == SCN_ERR_UNSUPPORTED) return false; // e.g. so few rows that K would be split
   scnSafeCall(rc);
   return true;
@@ -511,7 +522,8 @@ bool NetworkInNetworkLayer::forwardsPooled(SpatiallySparseBatch &batch, Spatiall
 bool NetworkInNetworkLayer::forwardsWithNext(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
                                              NetworkInNetworkLayer &next, SpatiallySparseBatchInterface &nextOutput) {
   if (batch.type == TRAINBATCH || fusePoolNext || next.fusePoolNext) return false;
-  if ((precision != SCN_PREC_AUTO && precision != SCN_PREC_3XTF32) || scn_conv_auto_precision() != SCN_PREC_3XTF32) return false;
+  const int sp = splitPrecision(precision, batch);
+  if (sp < 0) return false;
   if (next.precision != SCN_PREC_AUTO && next.precision != SCN_PREC_FP32) return false;
   if (fn == SOFTMAX || nFeaturesOut % 4 != 0 || next.nFeaturesOut > 16 || next.nFeaturesIn != nFeaturesOut) return false;
   const float *src;
@@ -526,9 +538,9 @@ bool NetworkInNetworkLayer::forwardsWithNext(SpatiallySparseBatch &batch, Spatia
     src = input.sub->features.dPtr();
   }
   const int rows = output.nSpatialSites;
-  const size_t wsBytes = rows > 0 ? scn_conv_nin_workspace_bytes(rows, fs, nIn, nFeaturesOut, SCN_PREC_3XTF32) : 0;
+  const size_t wsBytes = rows > 0 ? scn_conv_nin_workspace_bytes(rows, fs, nIn, nFeaturesOut, sp) : 0;
   if (!wsBytes) return false; // the layer would not split K
-  const void *pk = packedWeights(fs, nIn, SCN_PREC_3XTF32);
+  const void *pk = packedWeights(fs, nIn, sp);
   if (!pk) return false;
   splitScratch.resize((int)((wsBytes + sizeof(float) - 1) / sizeof(float)));
   output.sub->features.resize(rows * output.featuresPresent.size());
@@ -537,7 +549,7 @@ bool NetworkInNetworkLayer::forwardsWithNext(SpatiallySparseBatch &batch, Spatia
   const float p = 1.0f - (!rescale ? dropout : 0.0f), p2 = 1.0f - (!rescale ? next.dropout : 0.0f);
   const int rc = scn_conv_nin_nin_forward(src, rules, rows, fs, nIn, pk, B.dPtr(), slopes(), nFeaturesOut, p, (int)fn, next.W.dPtr(), next.B.dPtr(),
                                           next.slopes(), next.nFeaturesOut, p2, (int)next.fn, output.sub->features.dPtr(),
-                                          nextOutput.sub->features.dPtr(), splitScratch.dPtr(), wsBytes, memStream.stream);
+                                          nextOutput.sub->features.dPtr(), splitScratch.dPtr(), wsBytes, sp, memStream.stream);
   if (rc == SCN_ERR_UNSUPPORTED) return false;
   scnSafeCall(rc);
   countMultiplyAdds(input, output);
@@ -569,13 +581,15 @@ void NetworkInNetworkLayer::forwardsNow(SpatiallySparseBatch &batch, SpatiallySp
   } else {
     src = input.sub->features.dPtr();
   }
-  int prec = precision;
+  const bool wasAuto = precision == SCN_PREC_AUTO;
+  int prec = wasAuto ? scn_conv_auto_precision() : precision;
+  if (splitPrecision(precision, batch) >= 0) prec = splitPrecision(precision, batch); // (tf32 operands for training steps)
   const void *pk = nullptr;
   if (prec != SCN_PREC_FP32) {
-    pk = packedWeights(fs, nIn, prec == SCN_PREC_AUTO ? scn_conv_auto_precision() : prec);
+    pk = packedWeights(fs, nIn, prec);
     if (nFeaturesOut % 4 != 0) pk = nullptr; // the tensor-core kernels store whole float4 columns
-    if (!pk && prec != SCN_PREC_AUTO) {
-      if (!precisionFallback) throw ScnException("NetworkInNetworkLayer: layer shape has no tensor-core path; use SCN_PREC_AUTO or SCN_PREC_FP32");
+    if (!pk) {
+      if (!wasAuto && !precisionFallback) throw ScnException("NetworkInNetworkLayer: layer shape has no tensor-core path; use SCN_PREC_AUTO or SCN_PREC_FP32");
       prec = SCN_PREC_FP32;
     }
   }
@@ -780,6 +794,7 @@ void NetworkInNetworkLayer::backwards(SpatiallySparseBatch &batch, SpatiallySpar
     if ((int)zeroBias.size() != K) zeroed(zeroBias, K, memStream);
     // the forward kernel on the transposed weights: [rows x N] times [N x K]
     int prec = precision == SCN_PREC_AUTO ? scn_conv_auto_precision() : precision;
+    if (prec == SCN_PREC_SPLIT) prec = SCN_PREC_3XTF32; // gradients keep tf32 operands (see splitPrecision)
     const void *pk = nullptr;
     if (prec != SCN_PREC_FP32 && K % 4 == 0) {
       const size_t need = scn_conv_packed_weight_bytes(N, K, prec);

@@ -364,8 +364,8 @@ void SparseConvNetCUDA::processBatch(SpatiallySparseBatch &batch, float learning
     }
 }
 
-// One pass over a dataset (SparseConvNetCUDA.cu:272-326): returns the error rate and prints
-// the reference's summary line.
+// One pass over a dataset (SparseConvNetCUDA.cu:272-326): prints the reference's summary line and returns the mean
+// negative log-likelihood.  A TRAINBATCH dataset is shuffled by the batch producer and every batch updates the weights.
 float SparseConvNetCUDA::processDataset(SpatiallySparseDataset &dataset, int batchSize, float learningRate, float momentum) {
   if (dataset.pictures.empty()) throw ScnException("processDataset: empty dataset");
   float errorRate = 0, nll = 0;
@@ -384,12 +384,14 @@ float SparseConvNetCUDA::processDataset(SpatiallySparseDataset &dataset, int bat
   }
   auto end = std::chrono::system_clock::now();
   double diff = std::chrono::duration_cast<std::chrono::nanoseconds>(end - start).count();
-  if (dataset.type != UNLABELEDBATCH)
-    std::cout << dataset.name << " Mistakes:" << 100.0 * errorRate << "% NLL:" << nll
-              << " MegaMultiplyAdds/sample:" << std::round((double)multiplyAddCount / dataset.pictures.size() / 1000000)
+  if (dataset.type != RESCALEBATCH) { // the summary line of SparseConvNetCUDA.cu:310-324
+    std::cout << dataset.name;
+    if (dataset.type != UNLABELEDBATCH) std::cout << " Mistakes:" << 100.0 * errorRate << "% NLL:" << nll;
+    std::cout << " MegaMultiplyAdds/sample:" << std::round((double)multiplyAddCount / dataset.pictures.size() / 1000000)
               << " time:" << diff / 1000000000L << "s GigaMultiplyAdds/s:" << std::round((double)multiplyAddCount / diff)
               << " rate:" << std::round(dataset.pictures.size() * 1000000000.0f / diff) << "/s" << std::endl;
-  return errorRate;
+  }
+  return nll; // (the mean negative log-likelihood, as SparseConvNetCUDA.cu:325 returns it; the error rate is in the printed line)
 }
 
 // Repeated test passes with averaged probabilities (SparseConvNetCUDA.cu:327-405): prints the

@@ -270,7 +270,7 @@ int scn_net_load_weights(scn_net_t *net, const char *base, int epoch) { return g
 int scn_net_save_weights(scn_net_t *net, const char *base, int epoch) { return guarded([&] { net->cnn->saveWeights(base, epoch, false); }); }
 int scn_net_set_precision(scn_net_t *net, int precision) {
   return guarded([&] {
-    if (precision < SCN_PREC_AUTO || precision > SCN_PREC_3XBF16) throw ScnException("unknown precision");
+    if (precision < SCN_PREC_AUTO || precision > SCN_PREC_SPLIT) throw ScnException("unknown precision");
     for (auto L : net->cnn->layers)
       if (auto n = dynamic_cast<NetworkInNetworkLayer *>(L)) { n->precision = precision; n->precisionFallback = true; }
   });

@@ -142,6 +142,7 @@ CONV_TC = [
 # precision -> (bound against the fp64-accumulating oracle, bound that shows the split is at work)
 TC_PRECISIONS = {
     "3XTF32": (RTOL_FP32, 2e-5),   # a single tf32 product would be about 1e-3
+    "SPLIT": (RTOL_FP32, 5e-5),    # bf16 operands where K >= 128 (16 bits per product), tf32 operands elsewhere
     "3XBF16": (RTOL_FP32, 5e-5),   # products carry 16 mantissa bits: about 2^-16 per product; plain bf16 is about 5e-3
     "BF16": (2e-2, 2e-2),          # the optional reduced-precision path
 }
@@ -211,7 +212,7 @@ def test_background_rows(abi):
     assert bg.cpu().tolist() == [1, -1, -1, 5]
 
 
-@pytest.mark.parametrize("precision", ["3XTF32", "3XBF16"])
+@pytest.mark.parametrize("precision", ["3XTF32", "3XBF16", "SPLIT"])
 def test_split_k_matches_single_pass(abi, oracle, precision):
     """Layers with few output tiles split K over several CTAs; the partial sums are added in a
     fixed order, so repeated runs are bit-identical; split and unsplit kernels differ only by
@@ -276,20 +277,23 @@ def test_conv_nin_with_row_count_on_the_device(abi, oracle):
     (800, 260, 27, 1, 32, 8, "VLEAKYRELU"),     # a 3-D first layer (one channel, 3^3 filter) + 2^3 pooling: row-per-lane gather, two epilogue groups
     (500, 200, 8, 4, 48, 2, "RELU"),
 ])
-def test_conv_nin_maxpool_fused(abi, oracle, rows_in, windows, fs, nIn, N, cells, act):
-    _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, False)
+@pytest.mark.parametrize("precision", ["3XTF32", "SPLIT"])
+def test_conv_nin_maxpool_fused(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, precision):
+    _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, False, getattr(abi, "PREC_" + precision))
 
 
 @pytest.mark.parametrize("rows_in,windows,fs,nIn,N,cells,act", [
     (300, 60, 4, 256, 128, 4, "VLEAKYRELU"),    # two tiles, 32 slabs: K is split and the pooling runs in the finishing kernel
     (200, 30, 8, 128, 608, 8, "RELU"),
 ])
-def test_conv_nin_maxpool_with_k_split(abi, oracle, rows_in, windows, fs, nIn, N, cells, act):
-    assert abi.lib().scn_conv_nin_workspace_bytes(windows * cells + 5, fs, nIn, N, abi.PREC_3XTF32) > 0
-    _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, True)
+@pytest.mark.parametrize("precision", ["3XTF32", "SPLIT"])
+def test_conv_nin_maxpool_with_k_split(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, precision):
+    prec = getattr(abi, "PREC_" + precision)
+    assert abi.lib().scn_conv_nin_workspace_bytes(windows * cells + 5, fs, nIn, N, prec) > 0
+    _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, True, prec)
 
 
-def _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, split):
+def _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, split, prec):
     """Gather + NiN + non-overlapping max pooling in one kernel against the oracle's three steps: pooled values
     within the fp32 tolerance, every choice names an input whose value is the window's maximum."""
     from oracle import orc
@@ -310,11 +314,11 @@ def _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, split):
     mid = oracle.nin_forward(X, W, B, prelu, 0.9, actc, accum64=True)
     ref_v, ref_c = oracle.maxpool(mid.astype(np.float32), pool, cells)
     dW = torch.from_numpy(W).cuda()
-    packed = abi.pack_weights(dW, abi.PREC_3XTF32)
+    packed = abi.pack_weights(dW, prec)
     out, ch = abi.conv_nin_maxpool_forward(torch.from_numpy(feat).cuda(), torch.from_numpy(rules).cuda().flatten(), fs, dW,
                                            torch.from_numpy(B).cuda(), torch.from_numpy(pool).cuda().flatten(), cells,
                                            None if prelu is None else torch.from_numpy(prelu).cuda(), 0.9, actc, packed,
-                                           rows_unpooled=rows_mid if split else 0, split_k=split)
+                                           rows_unpooled=rows_mid if split else 0, split_k=split, precision=prec)
     torch.cuda.synchronize()
     assert abi.conv_tc_take_error() == 0
     out, ch = out.cpu().numpy(), ch.cpu().numpy()
@@ -335,7 +339,8 @@ def _fused_case(abi, oracle, rows_in, windows, fs, nIn, N, cells, act, split):
     (300, 100, 1, 1024, 96, 16, "RELU", "NOSIGMOID"),        # plain learnt layers, no rules
     (200, 40, 8, 128, 288, 3, "LEAKYRELU", "SOFTMAX"),
 ])
-def test_conv_nin_then_small_nin(abi, oracle, rows_in, rows, fs, nIn, N, N2, act, act2):
+@pytest.mark.parametrize("precision", ["3XTF32", "SPLIT"])
+def test_conv_nin_then_small_nin(abi, oracle, rows_in, rows, fs, nIn, N, N2, act, act2, precision):
     """A learnt layer that splits K and the small learnt layer behind it in one call (the second applied by the kernel
     that adds the partial sums) against the oracle's two layers: both outputs within the fp32 tolerance."""
     from oracle import orc
@@ -356,10 +361,11 @@ def test_conv_nin_then_small_nin(abi, oracle, rows_in, rows, fs, nIn, N, N2, act
     mid_ref = oracle.nin_forward(X, W, B, None, 0.9, getattr(orc, act), accum64=True)
     out_ref = oracle.nin_forward(mid_ref.astype(np.float32), W2, B2, None, 1.0, getattr(orc, act2), accum64=True)
     dW = torch.from_numpy(W).cuda()
-    packed = abi.pack_weights(dW, abi.PREC_3XTF32)
-    assert abi.lib().scn_conv_nin_workspace_bytes(rows, fs, nIn, N, abi.PREC_3XTF32) > 0
+    prec = getattr(abi, "PREC_" + precision)
+    packed = abi.pack_weights(dW, prec)
+    assert abi.lib().scn_conv_nin_workspace_bytes(rows, fs, nIn, N, prec) > 0
     mid, out = abi.conv_nin_nin_forward(torch.from_numpy(feat).cuda(), d_rules, fs, dW, torch.from_numpy(B).cuda(), torch.from_numpy(W2).cuda(),
-                                        torch.from_numpy(B2).cuda(), None, 0.9, getattr(abi, act), 1.0, getattr(abi, act2), packed)
+                                        torch.from_numpy(B2).cuda(), None, 0.9, getattr(abi, act), 1.0, getattr(abi, act2), packed, precision=prec)
     torch.cuda.synchronize()
     assert abi.conv_tc_take_error() == 0
     assert relerr(mid.cpu().numpy(), mid_ref) < RTOL_FP32

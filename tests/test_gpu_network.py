@@ -58,13 +58,13 @@ def test_deepcnet_builder_rounds_widths(scn, abi, oracle):
 
 @pytest.mark.parametrize("cfg", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("fusion", [False, True])
-@pytest.mark.parametrize("precision", ["fp32", "auto", "3xtf32", "3xbf16", "bf16"])
+@pytest.mark.parametrize("precision", ["fp32", "auto", "3xtf32", "split", "3xbf16", "bf16"])
 def test_forward_layer_by_layer(scn, abi, nets, cfg, precision, fusion):
     """Rulebooks and grids bit-exact; features of every interface and the probabilities within 1e-4 of
     the fp64-accumulating oracle for fp32 and the two split tensor-core precisions, within 2e-2 for the
     optional plain-bf16 precision; top-1 agrees (bf16: at least 99.9 % over the batch)."""
     gnet, onet = nets(cfg)
-    gnet.set_precision(dict(fp32=abi.PREC_FP32, auto=abi.PREC_AUTO, **{"3xtf32": abi.PREC_3XTF32, "3xbf16": abi.PREC_3XBF16},
+    gnet.set_precision(dict(fp32=abi.PREC_FP32, auto=abi.PREC_AUTO, split=abi.PREC_SPLIT, **{"3xtf32": abi.PREC_3XTF32, "3xbf16": abi.PREC_3XBF16},
                             bf16=abi.PREC_BF16)[precision])
     RTOL = 2e-2 if precision == "bf16" else 1e-4
     # fusion: convolution + learnt layer + non-overlapping pooling as one kernel (the default); the learnt layer's
