@@ -46,6 +46,12 @@ int scn_net_addTerminalPoolingLayer(scn_net_t *net, int poolSize);
 int scn_net_addSoftmaxLayer(scn_net_t *net);
 /* DeepCNet::DeepCNet (NetworkArchitectures.cpp:3-11), on the given stream. */
 scn_net_t *scn_net_DeepCNet(int dimension, int l, int k, int fn, int nInputFeatures, int nClasses, float p, int nTop, void *stream);
+/* Any of the named architectures (NetworkArchitectures.h:4-69), built by constructing the class of that name
+ * on the default device: DeepCNet DeepC2 DeepCNiN DeepC2C2 DeepC3C3Valid DeepC3C3 POFMPSparseConvNet
+ * ROFMPSparseConvNet PDFMPSparseConvNet RDFMPSparseConvNet.  fmpShrink is read by the last four only.
+ * NULL (and scn_net_last_error) for an unknown name or a builder that refuses its arguments. */
+scn_net_t *scn_net_named(const char *name, int dimension, int l, int k, float fmpShrink, int fn, int nInputFeatures, int nClasses, float p,
+                         int nTop);
 
 int scn_net_n_layers(scn_net_t *net);
 int scn_net_input_spatial_size(scn_net_t *net);

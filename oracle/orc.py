@@ -129,9 +129,15 @@ class ReferenceGPU:
     """The reference's own SparseConvNetCUDA (builders, BatchProducer, layer classes, CUDA kernels, cuBLAS
     SGEMM) on the current CUDA device, one batch at a time.  Mirrors OracleNet's builder calls."""
 
-    def __init__(self, dim, nInputFeatures, nClasses, nTop=1, lattice=0):
+    def __init__(self, dim, nInputFeatures, nClasses, nTop=1, lattice=0, named=None):
+        """named = (name, l, k, fn, p, fmpShrink): construct the reference's class of that name
+        (NetworkArchitectures.cpp) instead of an empty network."""
         self.L = L = ctypes.CDLL(REF_GPU_SO)
         L.refgpu_create.restype, L.refgpu_create.argtypes = c_p, [c_int] * 5
+        L.refgpu_named.restype = c_p
+        L.refgpu_named.argtypes = [ctypes.c_char_p, c_int, c_int, c_int, c_f, c_int, c_int, c_int, c_f, c_int]
+        L.refgpu_seed_fmp.argtypes = [c_p, ctypes.c_uint]
+        L.refgpu_layer_describe.argtypes = [c_p, c_int, c_p]
         L.refgpu_destroy.argtypes = [c_p]
         L.refgpu_addLeNetLayerMP.argtypes = [c_p] + [c_int] * 6 + [c_f, c_int]
         L.refgpu_addTerminalPoolingLayer.argtypes = [c_p, c_int, c_int]
@@ -150,7 +156,24 @@ class ReferenceGPU:
         L.refgpu_layer_weights.argtypes = [c_p, c_int, c_p, c_p, c_p]
         L.refgpu_sample_numbers.argtypes = [c_p, c_p]
         self.dim, self.nIn, self.nClasses, self.nTop, self.lattice = dim, nInputFeatures, nClasses, nTop, lattice
-        self.h = L.refgpu_create(dim, nInputFeatures, nClasses, nTop, lattice)
+        if named is None:
+            self.h = L.refgpu_create(dim, nInputFeatures, nClasses, nTop, lattice)
+        else:
+            name, l, k, fn, p, fmpShrink = named
+            self.h = L.refgpu_named(name.encode(), dim, l, k, fmpShrink, fn, nInputFeatures, nClasses, p, nTop)
+            if not self.h:
+                raise ValueError("unknown architecture " + name)
+
+    def seed_fmp(self, seed):
+        """Fractional max-pooling layer l draws from a generator seeded with seed + l from now on."""
+        self.L.refgpu_seed_fmp(self.h, seed)
+
+    def describe(self):
+        """Per layer the ten ints {type, size, stride, minActive, nIn, nOut, multiplier, fn, inSize, outSize}."""
+        out = np.zeros((self.L.refgpu_n_layers(self.h), 10), np.int32)
+        for i in range(out.shape[0]):
+            self.L.refgpu_layer_describe(self.h, i, out[i].ctypes.data)
+        return out
 
     @staticmethod
     def available():

@@ -25,6 +25,12 @@
 #include <string>
 #include <vector>
 #include "BatchProducer.h"
+#include "ConvolutionalLayer.h"
+#include "ConvolutionalTriangularLayer.h"
+#include "MaxPoolingLayer.h"
+#include "MaxPoolingTriangularLayer.h"
+#include "TerminalPoolingLayer.h"
+#include "NetworkArchitectures.h"
 #include "NetworkInNetworkLayer.h"
 #include "NetworkInNetworkPReLULayer.h"
 #include "SparseConvNetCUDA.h"
@@ -77,6 +83,19 @@ template <class T> void fetch(vectorCUDA<T> &v, T *dst) {
 }
 } // namespace
 
+namespace {
+template <class F> bool describeFmp(SpatiallySparseLayer *L, int *v) {
+  if (auto f = dynamic_cast<F *>(L)) {
+    int sd = 1; // poolSize^dimension, the width of a rule row
+    for (int i = 0; i < f->dimension; ++i) sd *= f->poolSize;
+    int w[10] = {6, f->poolSize, 1, 1, 0, 0, sd, 0, f->inSpatialSize, f->outSpatialSize};
+    std::memcpy(v, w, sizeof(w));
+    return true;
+  }
+  return false;
+}
+} // namespace
+
 extern "C" {
 
 void *refgpu_create(int dimension, int nInputFeatures, int nClasses, int nTop, int lattice) {
@@ -108,6 +127,45 @@ void refgpu_addSoftmaxLayer(void *p) {
   Quiet q;
   ((Handle *)p)->cnn->addSoftmaxLayer();
 }
+// One of the reference's named architectures (NetworkArchitectures.cpp): the class is constructed as a
+// caller of the reference would, then its runtime (`cnn`, a public member, SparseConvNet.h:20-23) is
+// taken over by the handle.  Names: DeepCNet DeepC2 DeepCNiN DeepC2C2 DeepC3C3Valid DeepC3C3
+// POFMPSparseConvNet ROFMPSparseConvNet PDFMPSparseConvNet RDFMPSparseConvNet; fmpShrink is read by
+// the last four only.  Returns NULL for an unknown name.
+void *refgpu_named(const char *name, int dimension, int l, int k, float fmpShrink, int fn, int nInputFeatures, int nClasses, float p, int nTop) {
+  Quiet q;
+  const std::string n(name);
+  const ActivationFunction a = (ActivationFunction)fn;
+  std::unique_ptr<SparseConvNet> net;
+  if (n == "DeepCNet") net.reset(new DeepCNet(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+  else if (n == "DeepC2") net.reset(new DeepC2(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+  else if (n == "DeepCNiN") net.reset(new DeepCNiN(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+  else if (n == "DeepC2C2") net.reset(new DeepC2C2(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+  else if (n == "DeepC3C3Valid") net.reset(new DeepC3C3Valid(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+  else if (n == "DeepC3C3") net.reset(new DeepC3C3(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+  else if (n == "POFMPSparseConvNet") net.reset(new POFMPSparseConvNet(dimension, l, k, fmpShrink, a, nInputFeatures, nClasses, p, -1, nTop));
+  else if (n == "ROFMPSparseConvNet") net.reset(new ROFMPSparseConvNet(dimension, l, k, fmpShrink, a, nInputFeatures, nClasses, p, -1, nTop));
+  else if (n == "PDFMPSparseConvNet") net.reset(new PDFMPSparseConvNet(dimension, l, k, fmpShrink, a, nInputFeatures, nClasses, p, -1, nTop));
+  else if (n == "RDFMPSparseConvNet") net.reset(new RDFMPSparseConvNet(dimension, l, k, fmpShrink, a, nInputFeatures, nClasses, p, -1, nTop));
+  else return nullptr;
+  Handle *h = new Handle();
+  h->lattice = 0;
+  h->cnn = std::move(net->cnn);
+  h->cnn->nBatchProducerThreads = 1; // samples reach the fractional pooling layers' generators in batch order
+  return h;
+}
+// Seed the generator of fractional max-pooling layer l (MaxPoolingLayer.h:44,72,99,126: a public RNG
+// member per layer) with seed + l, so that a test can give two implementations the same stream.
+void refgpu_seed_fmp(void *p, unsigned seed) {
+  Handle *h = (Handle *)p;
+  for (size_t l = 0; l < h->cnn->layers.size(); ++l) {
+    SpatiallySparseLayer *L = h->cnn->layers[l];
+    if (auto f = dynamic_cast<PseudorandomOverlappingFractionalMaxPoolingLayer *>(L)) f->rng.gen.seed(seed + (unsigned)l);
+    else if (auto f = dynamic_cast<PseudorandomNonOverlappingFractionalMaxPoolingLayer *>(L)) f->rng.gen.seed(seed + (unsigned)l);
+    else if (auto f = dynamic_cast<RandomOverlappingFractionalMaxPoolingLayer *>(L)) f->rng.gen.seed(seed + (unsigned)l);
+    else if (auto f = dynamic_cast<RandomNonOverlappingFractionalMaxPoolingLayer *>(L)) f->rng.gen.seed(seed + (unsigned)l);
+  }
+}
 int refgpu_n_layers(void *p) { return (int)((Handle *)p)->cnn->layers.size(); }
 int refgpu_input_spatial_size(void *p) { return ((Handle *)p)->cnn->inputSpatialSize; }
 // info: {isLearnt, nFeaturesIn, nFeaturesOut, fn, isPReLU}; dropout as the builder re-quantised it
@@ -123,6 +181,42 @@ void refgpu_layer_info(void *p, int layer, int *info, float *dropout) {
     info[0] = 1; info[1] = n->nFeaturesIn; info[2] = n->nFeaturesOut; info[3] = (int)PRELU; info[4] = 1;
     *dropout = n->dropout;
   }
+}
+// The layer as the builder made it, ten ints: {type, size, stride, minActiveInputs, nFeaturesIn,
+// nFeaturesOut, multiplier, fn, inSpatialSize, outSpatialSize} with type 0 convolution, 1 triangular
+// convolution, 2 learnt layer, 3 max pooling, 4 triangular max pooling, 5 terminal pooling,
+// 6 fractional max pooling (size = poolSize, multiplier = sd), -1 anything else.
+void refgpu_layer_describe(void *p, int layer, int *info) {
+  Handle *h = (Handle *)p;
+  SpatiallySparseLayer *L = h->cnn->layers.at(layer);
+  int v[10] = {-1, 1, 1, 1, 0, 0, 1, 0, 0, 0};
+  if (auto c = dynamic_cast<ConvolutionalLayer *>(L)) {
+    int w[10] = {0, c->filterSize, c->filterStride, c->minActiveInputs, c->nFeaturesIn, c->nFeaturesOut, c->nFeaturesOut / c->nFeaturesIn, 0, c->inSpatialSize, c->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto c = dynamic_cast<ConvolutionalTriangularLayer *>(L)) {
+    int w[10] = {1, c->filterSize, c->filterStride, c->minActiveInputs, c->nFeaturesIn, c->nFeaturesOut, c->nFeaturesOut / c->nFeaturesIn, 0, c->inSpatialSize, c->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto n = dynamic_cast<NetworkInNetworkLayer *>(L)) {
+    int w[10] = {2, 1, 1, 1, n->nFeaturesIn, n->nFeaturesOut, 1, (int)n->fn, 0, 0};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto n = dynamic_cast<NetworkInNetworkPReLULayer *>(L)) {
+    int w[10] = {2, 1, 1, 1, n->nFeaturesIn, n->nFeaturesOut, 1, (int)PRELU, 0, 0};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto m = dynamic_cast<MaxPoolingLayer *>(L)) {
+    int w[10] = {3, m->poolSize, m->poolStride, 1, 0, 0, m->sd, 0, m->inSpatialSize, m->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto m = dynamic_cast<MaxPoolingTriangularLayer *>(L)) {
+    int w[10] = {4, m->poolSize, m->poolStride, 1, 0, 0, m->S, 0, m->inSpatialSize, m->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto t = dynamic_cast<TerminalPoolingLayer *>(L)) {
+    int w[10] = {5, t->poolSize, 1, 1, 0, 0, 1, 0, t->inSpatialSize, t->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  } else if (describeFmp<PseudorandomOverlappingFractionalMaxPoolingLayer>(L, v) ||
+             describeFmp<PseudorandomNonOverlappingFractionalMaxPoolingLayer>(L, v) ||
+             describeFmp<RandomOverlappingFractionalMaxPoolingLayer>(L, v) ||
+             describeFmp<RandomNonOverlappingFractionalMaxPoolingLayer>(L, v)) {
+  }
+  std::memcpy(info, v, sizeof(v));
 }
 // SparseConvNetCUDA::loadWeights (SparseConvNetCUDA.cu:406-424) on <base>_epoch-<epoch>.cnn
 void refgpu_load_weights(void *p, const char *base, int epoch) {

@@ -7,6 +7,7 @@
 #include "ConvolutionalTriangularLayer.h"
 #include "MaxPoolingLayer.h"
 #include "MaxPoolingTriangularLayer.h"
+#include "NetworkArchitectures.h"
 #include "NetworkInNetworkLayer.h"
 #include "NetworkInNetworkPReLULayer.h"
 #include "SoftmaxClassifier.h"
@@ -242,6 +243,34 @@ scn_net_t *scn_net_DeepCNet(int dimension, int l, int k, int fn, int nInputFeatu
     n->cnn->addSoftmaxLayer();
   });
   if (rc) { scn_net_destroy(n); return nullptr; }
+  return n;
+}
+
+scn_net_t *scn_net_named(const char *name, int dimension, int l, int k, float fmpShrink, int fn, int nInputFeatures, int nClasses, float p,
+                         int nTop) {
+  scn_net *n = nullptr;
+  int rc = guarded([&] {
+    Quiet q;
+    const std::string s(name ? name : "");
+    const ActivationFunction a = (ActivationFunction)fn;
+    std::unique_ptr<SparseConvNet> net; // constructed as a caller of the class would; its runtime then moves into the handle
+    if (s == "DeepCNet") net.reset(new DeepCNet(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+    else if (s == "DeepC2") net.reset(new DeepC2(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+    else if (s == "DeepCNiN") net.reset(new DeepCNiN(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+    else if (s == "DeepC2C2") net.reset(new DeepC2C2(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+    else if (s == "DeepC3C3Valid") net.reset(new DeepC3C3Valid(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+    else if (s == "DeepC3C3") net.reset(new DeepC3C3(dimension, l, k, a, nInputFeatures, nClasses, p, -1, nTop));
+    else if (s == "POFMPSparseConvNet") net.reset(new POFMPSparseConvNet(dimension, l, k, fmpShrink, a, nInputFeatures, nClasses, p, -1, nTop));
+    else if (s == "ROFMPSparseConvNet") net.reset(new ROFMPSparseConvNet(dimension, l, k, fmpShrink, a, nInputFeatures, nClasses, p, -1, nTop));
+    else if (s == "PDFMPSparseConvNet") net.reset(new PDFMPSparseConvNet(dimension, l, k, fmpShrink, a, nInputFeatures, nClasses, p, -1, nTop));
+    else if (s == "RDFMPSparseConvNet") net.reset(new RDFMPSparseConvNet(dimension, l, k, fmpShrink, a, nInputFeatures, nClasses, p, -1, nTop));
+    else throw ScnException("unknown architecture name '" + s + "'");
+    n = new scn_net();
+    n->lattice = 0;
+    n->last = nullptr;
+    n->cnn = std::move(net->cnn);
+  });
+  if (rc) { delete n; return nullptr; }
   return n;
 }
 

@@ -14,7 +14,7 @@ c_int, c_ll, c_f, c_p, c_d = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ct
 
 EXPORTS = [
     "scn_net_last_error", "scn_net_create", "scn_net_destroy", "scn_net_addLeNetLayerMP", "scn_net_addLeNetLayerFMP", "scn_net_seed_fmp", "scn_net_set_pool_fusion",
-    "scn_net_addTerminalPoolingLayer", "scn_net_addSoftmaxLayer", "scn_net_DeepCNet", "scn_net_n_layers",
+    "scn_net_addTerminalPoolingLayer", "scn_net_addSoftmaxLayer", "scn_net_DeepCNet", "scn_net_named", "scn_net_n_layers",
     "scn_net_input_spatial_size", "scn_net_layer_info", "scn_net_set_weights", "scn_net_load_weights",
     "scn_net_save_weights", "scn_net_set_precision", "scn_net_forward_host", "scn_net_forward_device",
     "scn_net_copy_probs_device", "scn_net_train_batch", "scn_net_get_weights", "scn_net_iface_dfeatures", "scn_net_iface_sizes", "scn_net_iface_fetch", "scn_net_take_multiply_adds", "scn_net_enable_timing",
@@ -53,6 +53,8 @@ def lib():
         L.scn_net_addSoftmaxLayer.argtypes = [c_p]
         L.scn_net_DeepCNet.restype = c_p
         L.scn_net_DeepCNet.argtypes = [c_int] * 6 + [c_f, c_int, c_p]
+        L.scn_net_named.restype = c_p
+        L.scn_net_named.argtypes = [ctypes.c_char_p, c_int, c_int, c_int, c_f, c_int, c_int, c_int, c_f, c_int]
         L.scn_net_n_layers.argtypes = [c_p]
         L.scn_net_input_spatial_size.argtypes = [c_p]
         L.scn_net_layer_info.argtypes = [c_p, c_int, c_p, c_p]
@@ -104,6 +106,16 @@ class Net:
     def DeepCNet(cls, dim, l, k, fn, nInputFeatures, nClasses, p=0.0, nTop=1):
         L = lib()
         h = L.scn_net_DeepCNet(dim, l, k, fn, nInputFeatures, nClasses, p, nTop, _current_stream())
+        if not h:
+            raise abi.ScnError(L.scn_net_last_error().decode())
+        return cls(dim, nInputFeatures, nClasses, nTop, 0, handle=h)
+
+    @classmethod
+    def named(cls, name, dim, l, k, fn, nInputFeatures, nClasses, p=0.0, nTop=1, fmpShrink=0.0):
+        """One of the named architectures of NetworkArchitectures.h, constructed through its class; the
+        network runs on a stream of its own, as the reference's does."""
+        L = lib()
+        h = L.scn_net_named(name.encode(), dim, l, k, fmpShrink, fn, nInputFeatures, nClasses, p, nTop)
         if not h:
             raise abi.ScnError(L.scn_net_last_error().decode())
         return cls(dim, nInputFeatures, nClasses, nTop, 0, handle=h)

@@ -53,6 +53,40 @@ def rules_safe_for_reference_kernels(onet):
         r = onet.iface(i + 1)["rules"]
         if L["type"] in (0, 1) and r.size and r.min() < 0:
             return False
-        if L["type"] in (3, 4) and r.size and (r.reshape(-1, L["fs"]).max(axis=1) < 0).any():
+        if L["type"] in (3, 4, 6) and r.size and (r.reshape(-1, L["fs"]).max(axis=1) < 0).any():
             return False
     return True
+
+
+NAMED_ARCHITECTURES = ("DeepCNet", "DeepC2", "DeepCNiN", "DeepC2C2", "DeepC3C3Valid", "DeepC3C3", "POFMPSparseConvNet",
+                       "ROFMPSparseConvNet", "PDFMPSparseConvNet", "RDFMPSparseConvNet")
+
+
+def build_named(net, name, l, k, fn, p=0.0, fmpShrink=0.0):
+    """The builder calls the constructor of the named class makes (NetworkArchitectures.cpp:3-122), on any
+    object that offers addLeNetLayerMP / addLeNetLayerFMP / addSoftmaxLayer.  Dropout arguments are float32
+    products as in the C++ expressions."""
+    f = np.float32
+    ramp = lambda i, d: float(f(f(f(p) * f(i)) * f(1.0)) / f(d))
+    mp = net.addLeNetLayerMP
+    if name in ("DeepCNet", "DeepC2", "DeepCNiN"):
+        for i in range(l + 1):
+            last = i == l
+            mp((i + 1) * k, 3 if (name == "DeepCNet" and i == 0) else 2, 1, 1 if last else 3, 1 if last else 2, fn, ramp(i, l), 1)
+            if name == "DeepCNiN":
+                mp((i + 1) * k, 1, 1, 1, 1, fn, ramp(i, l), 1)
+    elif name in ("DeepC2C2", "DeepC3C3Valid", "DeepC3C3"):
+        fs = 2 if name == "DeepC2C2" else 3
+        ma = -1 if name == "DeepC3C3Valid" else 1
+        for i in range(l):
+            mp((i + 1) * k, fs, 1, 1, 1, fn, ramp(i, l), ma)
+            mp((i + 1) * k, fs, 1, 3, 2, fn, ramp(i, l), ma)
+        mp((l + 1) * k, fs, 1, 1, 1, fn, float(f(p)), 1)
+        mp((l + 1) * k, 1, 1, 1, 1, fn, float(f(p)), 1)
+    else:
+        kind = {"PO": 0, "PD": 1, "RO": 2, "RD": 3}[name[:2]]
+        for i in range(l):
+            net.addLeNetLayerFMP(kind, k * (i + 1), 2, 1, 2, fmpShrink, fn, float(f(f(p) * f(i)) / f(l + 1)), 1)
+        mp(k * (l + 1), 2, 1, 1, 1, fn, float(f(f(p) * f(l)) / f(l + 1)), 1)
+        mp(k * (l + 2), 1, 1, 1, 1, fn, float(f(p)), 1)
+    net.addSoftmaxLayer()
