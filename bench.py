@@ -306,40 +306,43 @@ def main():
             dev_batches.append(tuple(torch.from_numpy(x).to(dev) for x in (keys, off, bg, feats)) + (int(np.diff(off).max() - 1),))
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
         d_top = torch.empty((BATCH_PER_GPU, 1), dtype=torch.int32, device=dev)
-        # at N > 1 the all-gather of step j overlaps the forward of step j + 1 in both legs (two buffer sets); step
-        # j + 1 ends only after the gather of step j has completed, and the last gather is timed behind the last step
+        # At N > 1 every rank's probabilities go to every rank over peer memory (ResultExchange: the forward call stores
+        # its block into the peers' buffers and collects the step before in front of its one copy-and-wait; no collective
+        # call per step).  The blocks of step j are therefore delivered by step j + 1, in both legs; the last step's
+        # blocks are collected, and timed, behind the last step.
         d_probs2 = [torch.empty((BATCH_PER_GPU, nC), dtype=torch.float32, device=dev) for _ in range(2)]
-        gathered2 = [torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32, device=dev) for _ in range(2)]
-        h_gathered2 = [torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32).pin_memory() for _ in range(2)]
+        gathered2 = [torch.zeros((world * BATCH_PER_GPU, nC), dtype=torch.float32, device=dev) for _ in range(2)]
+        d_rows_status = torch.zeros(world + 1, dtype=torch.int32, device=dev)
+        h_gathered = np.zeros((world, BATCH_PER_GPU, nC), np.float32)
+        h_rows = np.zeros(world, np.int32)
         pending = []
         last_host = {}
+        if world > 1:
+            scn.shard.connect_exchange(gnet, BATCH_PER_GPU)
 
         def step_device(j):
             dk, do, db, df, ms = dev_batches[j % n_rot]
             gnet.forward_device(dk, do, db, df, ms, d_probs2[j & 1], d_top)
-            if world == 1:
-                return
-            work = dist.all_gather_into_tensor(gathered2[j & 1], d_probs2[j & 1], async_op=True)
-            drain()  # the launching stream waits for the previous step's gather
-            pending.append((work, j & 1, False))
+            if world > 1:  # collects step j - 1 into gathered2[(j - 1) & 1], publishes step j
+                gnet.exchange_step_device(d_probs2[j & 1], BATCH_PER_GPU, gathered2[(j - 1) & 1], d_rows_status)
+                pending[:] = [("device", j & 1)]
 
         def drain():
             while pending:
-                work, k, to_host = pending.pop()
-                work.wait()
-                if to_host:  # the gathered block goes back to the host: part of what a step of this leg delivers
-                    h_gathered2[k].copy_(gathered2[k], non_blocking=True)
-                    stream.synchronize()
+                kind, k = pending.pop()
+                if kind == "device":
+                    gnet.exchange_step_device(None, 0, gathered2[k], d_rows_status)
+                else:  # the host leg's last step: its blocks come back to the host
+                    gnet.exchange_flush(h_gathered, h_rows)
 
         def step_host(j):
             keys, off, feats = host_batches[j % n_rot]
-            probs, pred = gnet.forward_host(keys, off, feats)
+            if world == 1:
+                probs, pred = gnet.forward_host(keys, off, feats)
+            else:
+                probs, pred, _, _ = gnet.forward_host_exchange(keys, off, feats, h_gathered, h_rows)
+                pending[:] = [("host", 0)]
             last_host["probs"], last_host["top"] = probs, pred
-            if world > 1:
-                gnet.copy_probs_device(d_probs2[j & 1])
-                work = dist.all_gather_into_tensor(gathered2[j & 1], d_probs2[j & 1], async_op=True)
-                drain()
-                pending.append((work, j & 1, True))
 
         def timed(step, with_layer_times):
             ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
@@ -400,6 +403,8 @@ def main():
         check_tc("device-resident")
         last = dict(batch_index=rank * n_rot + (steps - 1) % n_rot, dev_probs=d_probs2[(steps - 1) & 1].cpu().numpy(), dev_top=d_top.cpu().numpy())
         gathered_host = gathered2[(steps - 1) & 1].cpu().numpy() if world > 1 else None
+        if world > 1 and int(d_rows_status[world].item()):
+            raise RuntimeError("the result exchange gave up waiting for ranks (bits %d): this leg's numbers are void" % int(d_rows_status[world].item()))
         # Per-kernel durations for the roofline and the breakdown: the same steps once more with a CUDA
         # event between the layers.  (Those events cost about 0.06 ms of GPU idle per step, which is why
         # they are kept out of the steps that `value` is computed from.)
@@ -529,12 +534,12 @@ def main():
                 cpu = cpu or dict(value=None, unit="samples/s", cores=0, kind="port", sample="unavailable: %s" % e)
                 parity = parity or dict(unavailable=str(e))
         h2d = int(sum(x.nbytes for x in host_batches[0]))
-        d2h = int(BATCH_PER_GPU * nC * 4 + BATCH_PER_GPU * 4 + 4 + (world * BATCH_PER_GPU * nC * 4 if world > 1 else 0))
+        d2h = int(BATCH_PER_GPU * nC * 4 + BATCH_PER_GPU * 4 + 4 + (world * BATCH_PER_GPU * nC * 4 + (world + 1) * 4 if world > 1 else 0))
         line = dict(
             metric=METRIC, value=total / (ms_dev * 1e-3), unit="samples/s", n_gpus=world, steps=steps, warmup=args.warmup,
             ms_per_step=ms_dev / steps, higher_is_better=True, scaling="weak", vs_baseline=None,
             dtype={"fp32": "f32", "bf16": "bf16", "3xtf32": "tf32x3/f32", "3xbf16": "bf16x3/f32"}.get(args.precision, "bf16x3|tf32x3/f32"), data="synthetic",
-            config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample, all-gather of probabilities%s" % (world, " (step j's gather overlaps step j+1 in both legs)" if world > 1 else ""),
+            config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample%s" % (world, ", every rank's probabilities stored into every rank's buffer over peer memory by the forward call (no collective call per step); step j's blocks are delivered by step j+1 in both legs, the last step's behind it" if world > 1 else ""),
                         l2="256 MiB written between timed steps; 2 distinct batches rotated", precision=args.precision,
                         timing="CUDA events per step on the launching stream, max over ranks; each leg %d times, median leg reported; wall %.3f s for the device legs; per-kernel durations from one more pass of the same steps with events between the layers" % (max(1, args.legs), t_wall)),
             legs=dict(n=max(1, args.legs), ms_per_step_device=[round(x / steps, 5) for x in dev_legs], ms_per_step_e2e=[round(x / steps, 5) for x in e2e_legs]),
@@ -554,6 +559,7 @@ def main():
         )
         print(json.dumps(line))
     if world > 1:
+        scn.shard.disconnect_exchange(gnet)
         dist.destroy_process_group()
 
 

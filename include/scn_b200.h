@@ -403,6 +403,40 @@ int scn_terminal_pool_backward(const float *d_dout, const int *d_rules, int batc
 int scn_sgd_update(float *d_w, float *d_momentum, const float *d_delta, long long n, float learningRate,
                    float momentum, int keep_positive, scn_stream_t stream);
 
+/* ------------------------------------------------------------------ result exchange between the GPUs of one node
+ * The reference runs on one GPU (SparseConvNetCUDA.cu:43-71 picks a single device).  Sharded by sample over several
+ * GPUs, the path has one exchange step: every rank's [rows x nClasses] block of probabilities (what
+ * SoftmaxClassifier.cu:36-41 copies to the host) goes to every other rank.  These calls do that over peer memory, on
+ * the rank's own stream, without a host-side collective:
+ *   scn_exchange_buffer_bytes   size of a rank's buffer for `world` ranks (at most 16) and blocks of at most
+ *                               cap_floats floats (0 = bad arguments);
+ *   scn_exchange_alloc          cudaMalloc + clear such a buffer and, where ipc_handle is not NULL, write the 64 bytes
+ *                               another process of this node passes to scn_exchange_open to map it;
+ *   scn_exchange_publish        store d_block[floats] (rows = its row count, carried along) into the buffer of every rank
+ *                               named in peers[world] (host array of device pointers, own buffer included) and
+ *                               announce it as `step` (1, 2, 3, ... on every rank alike);
+ *   scn_exchange_collect        wait until every rank's block of `step` has arrived in d_local, then
+ *                               d_out[r * cap_floats ...] = rank r's block and d_rows[r] = its row count (d_rows may be
+ *                               NULL).  A rank whose block does not arrive within the time limit
+ *                               (scn_exchange_set_timeout_ms, 2000 by default) gets bit r of *d_status set and its part
+ *                               of d_out left as it was; the kernel always returns.
+ *   scn_exchange_step           both in ONE launch: collect `collect_step` (0 = nothing to collect), publish
+ *                               `publish_step` (0 = nothing to publish), collect_step < publish_step.
+ * A rank must collect step s before it publishes step s + 1; with that order four slots per source are enough for
+ * a slot never to be overwritten before its owner has read it. */
+size_t scn_exchange_buffer_bytes(int world, int cap_floats);
+void scn_exchange_set_timeout_ms(int ms);
+int scn_exchange_alloc(size_t bytes, void **d_buffer, unsigned char *ipc_handle);
+int scn_exchange_free(void *d_buffer);
+int scn_exchange_open(const unsigned char *ipc_handle, void **d_peer);
+int scn_exchange_close(void *d_peer);
+int scn_exchange_publish(const float *d_block, int floats, int rows, void *const *peers, int world, int rank, int cap_floats,
+                         unsigned step, scn_stream_t stream);
+int scn_exchange_collect(void *d_local, int world, int cap_floats, unsigned step, float *d_out, int *d_rows, int *d_status,
+                         scn_stream_t stream);
+int scn_exchange_step(void *d_local, unsigned collect_step, float *d_out, int *d_rows, int *d_status, const float *d_block, int floats,
+                      int rows, void *const *peers, int world, int rank, int cap_floats, unsigned publish_step, scn_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

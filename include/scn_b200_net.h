@@ -134,6 +134,33 @@ int scn_net_process_dataset(scn_net_t *net, int nSamples, const int *h_keys, con
 /* vectorTopIndices (utilities.cu:35-56), the host version SoftmaxClassifier-style callers use. */
 int scn_host_vectorTopIndices(const float *h_v, int n, int k, int *h_out);
 
+/* ---- results of a batch sharded by sample over the GPUs of one node (ResultExchange: peer stores + bounded waits,
+ * no host-side collective; the reference itself runs on one device, SparseConvNetCUDA.cu:43-71).
+ * scn_net_exchange_create allocates this rank's buffer for blocks of at most cap_rows x nClasses probabilities and
+ * writes the 64 bytes (handle_out) that the other ranks' processes need; scn_net_exchange_connect takes all ranks'
+ * 64-byte entries in rank order (world x 64 bytes; how they travel is the caller's business: one all-gather at
+ * start-up).  Ranks that live in ONE process (tests) pass each other's scn_net_exchange_buffer pointers to
+ * scn_net_exchange_connect_local instead.  Every rank must run the same sequence of exchange steps.  Before
+ * scn_net_exchange_destroy / scn_net_destroy the ranks synchronise (no peer may still be storing into the buffer). */
+int scn_net_exchange_create(scn_net_t *net, int world, int rank, int cap_rows, unsigned char *handle_out);
+void *scn_net_exchange_buffer(scn_net_t *net);
+int scn_net_exchange_connect(scn_net_t *net, const unsigned char *handles);
+int scn_net_exchange_connect_local(scn_net_t *net, void *const *buffers);
+int scn_net_exchange_destroy(scn_net_t *net);
+/* scn_net_forward_host that also publishes this step's probabilities to every rank and returns what every rank
+ * published in the step BEFORE: gathered_prev[world x cap_rows x nClasses] (rank r's block at r * cap_rows * nClasses)
+ * and rows_prev[world] (-1 everywhere on the first step).  One copy-and-wait ends the step, as in scn_net_forward_host.
+ * A rank whose block has not arrived within the time limit (scn_exchange_set_timeout_ms) makes the call fail. */
+int scn_net_forward_host_exchange(scn_net_t *net, int batch, const int *keys, const int *off, const float *features, float *probs,
+                                  int *predictions, float *gathered_prev, int *rows_prev);
+/* The blocks of the last published step (ends a run of scn_net_forward_host_exchange calls; waits for the stream). */
+int scn_net_exchange_flush(scn_net_t *net, float *gathered, int *rows);
+/* Device-resident form, enqueued on the network's stream without waiting: collects the step before into
+ * d_gathered_prev[world x cap_rows x nClasses] and d_rows_status_prev[world + 1] (row counts, then a word with bit r
+ * set if rank r's block did not arrive in time), then publishes d_probs[rows x nClasses] as the next step
+ * (d_probs NULL: collect only). */
+int scn_net_exchange_step_device(scn_net_t *net, const float *d_probs, int rows, float *d_gathered_prev, int *d_rows_status_prev);
+
 #ifdef __cplusplus
 }
 #endif

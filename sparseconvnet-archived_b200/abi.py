@@ -23,6 +23,7 @@ EXPORTS = [
     "scn_terminal_rules_build", "scn_conv_auto_precision", "scn_conv_nin_forward", "scn_conv_nin_forward_ws", "scn_conv_nin_forward_dyn", "scn_conv_nin_maxpool_forward", "scn_conv_nin_nin_forward", "scn_conv_nin_workspace_bytes", "scn_conv_packed_weight_bytes",
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_conv_tc_error_word", "scn_classifier_result_bytes", "scn_classifier_result", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
+    "scn_exchange_buffer_bytes", "scn_exchange_set_timeout_ms", "scn_exchange_alloc", "scn_exchange_free", "scn_exchange_open", "scn_exchange_close", "scn_exchange_publish", "scn_exchange_collect", "scn_exchange_step",
     "scn_softmax_nll_backward", "scn_activation_backward", "scn_conv_nin_backward_weights", "scn_transpose_weights", "scn_gather_backward",
     "scn_maxpool_backward", "scn_terminal_pool_backward", "scn_sgd_update",
 ]
@@ -60,6 +61,15 @@ def lib():
         L.scn_conv_tc_error_word.restype = c_p
         L.scn_classifier_result_bytes.restype = c_sz
         L.scn_regions_cells.restype, L.scn_regions_cells.argtypes = c_int, [c_p]
+        L.scn_exchange_buffer_bytes.restype, L.scn_exchange_buffer_bytes.argtypes = c_sz, [c_int, c_int]
+        L.scn_exchange_set_timeout_ms.restype, L.scn_exchange_set_timeout_ms.argtypes = None, [c_int]
+        L.scn_exchange_alloc.argtypes = [c_sz, c_p, c_p]
+        L.scn_exchange_free.argtypes = [c_p]
+        L.scn_exchange_open.argtypes = [c_p, c_p]
+        L.scn_exchange_close.argtypes = [c_p]
+        L.scn_exchange_publish.argtypes = [c_p, c_int, c_int, c_p, c_int, c_int, c_int, ctypes.c_uint, c_p]
+        L.scn_exchange_collect.argtypes = [c_p, c_int, c_int, ctypes.c_uint, c_p, c_p, c_p, c_p]
+        L.scn_exchange_step.argtypes = [c_p, ctypes.c_uint, c_p, c_p, c_p, c_p, c_int, c_int, c_p, c_int, c_int, c_int, ctypes.c_uint, c_p]
         L.scn_rules_workspace_bytes.restype = c_sz
         L.scn_rules_workspace_bytes.argtypes = [c_p, c_int, c_int]
         L.scn_rules_build.argtypes = [c_p, c_int, c_p, c_p, c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_p, c_p, c_sz, c_p]
@@ -488,3 +498,52 @@ def terminal_pool_backward(dout, rules, S, rows_in):
 def sgd_update(w, m, d, lr, momentum, keep_positive=False):
     """In place on w and m."""
     check(lib().scn_sgd_update(_ptr(w), _ptr(m), _ptr(_f32(d)), c_ll(w.numel()), c_f(lr), c_f(momentum), int(keep_positive), _stream()))
+
+
+class ExchangeBuffer:
+    """One rank's buffer of the result exchange (scn_exchange_alloc): blocks of at most cap_floats floats from each
+    of `world` ranks.  `handle` is what another process of the node passes to ExchangeBuffer.open()."""
+
+    def __init__(self, world, cap_floats):
+        self.world, self.cap_floats = world, cap_floats
+        nbytes = lib().scn_exchange_buffer_bytes(world, cap_floats)
+        if not nbytes:
+            raise ScnError("bad exchange sizes")
+        p, h = c_p(), (ctypes.c_ubyte * 64)()
+        check(lib().scn_exchange_alloc(c_sz(nbytes), ctypes.byref(p), h))
+        self.ptr, self.handle = p.value, bytes(h)
+
+    def free(self):
+        if self.ptr:
+            check(lib().scn_exchange_free(c_p(self.ptr)))
+            self.ptr = None
+
+    @staticmethod
+    def open(handle):
+        p = c_p()
+        check(lib().scn_exchange_open((ctypes.c_ubyte * 64).from_buffer_copy(handle), ctypes.byref(p)))
+        return p.value
+
+    @staticmethod
+    def close(ptr):
+        check(lib().scn_exchange_close(c_p(ptr)))
+
+
+def exchange_set_timeout_ms(ms):
+    lib().scn_exchange_set_timeout_ms(int(ms))
+
+
+def exchange_publish(block, rows, peers, rank, cap_floats, step):
+    """block: float32 CUDA tensor (this rank's results of `step`); peers: every rank's buffer pointer."""
+    arr = (c_p * len(peers))(*peers)
+    check(lib().scn_exchange_publish(_ptr(_f32(block)), block.numel(), rows, arr, len(peers), rank, cap_floats, step, _stream()))
+
+
+def exchange_collect(local_ptr, world, cap_floats, step, out=None, rows=None, status=None):
+    """-> (out[world, cap_floats], rows[world], status[1]) once every rank's block of `step` has arrived or timed out."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = torch.zeros((world, cap_floats), dtype=torch.float32, device=dev) if out is None else out
+    rows = torch.full((world,), -1, dtype=torch.int32, device=dev) if rows is None else rows
+    status = torch.zeros(1, dtype=torch.int32, device=dev) if status is None else status
+    check(lib().scn_exchange_collect(c_p(local_ptr), world, cap_floats, step, _ptr(out), _ptr(rows), _ptr(status), _stream()))
+    return out, rows, status

@@ -10,6 +10,7 @@
 #include "NetworkArchitectures.h"
 #include "NetworkInNetworkLayer.h"
 #include "NetworkInNetworkPReLULayer.h"
+#include "ResultExchange.h"
 #include "SoftmaxClassifier.h"
 #include "SparseConvNetCUDA.h"
 #include "TerminalPoolingLayer.h"
@@ -27,7 +28,9 @@ struct scn_net {
   // host buffers already seen to be page-locked (a driver query per buffer and call costs microseconds; should one
   // of them have become pageable since, its copy is still correct, only less asynchronous)
   std::vector<const void *> knownPinned;
+  std::unique_ptr<ResultExchange> exchange; // results to and from the other ranks of a sharded batch
   ~scn_net() {
+    exchange.reset();
     if (copyDone) cudaEventDestroy(copyDone);
     if (copyStream) cudaStreamDestroy(copyStream);
   }
@@ -321,6 +324,86 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *
     const size_t pb = sizeof(float) * (size_t)batch * cnn.nClasses;
     if (probs) std::memcpy(probs, block, pb);
     if (predictions) std::memcpy(predictions, block + pb, sizeof(int) * (size_t)batch * cnn.nTop);
+  });
+}
+
+int scn_net_exchange_create(scn_net_t *net, int world, int rank, int cap_rows, unsigned char *handle_out) {
+  return guarded([&] {
+    net->exchange.reset(new ResultExchange(world, rank, cap_rows, net->cnn->nClasses));
+    if (handle_out) std::memcpy(handle_out, net->exchange->handle(), 64);
+  });
+}
+void *scn_net_exchange_buffer(scn_net_t *net) { return net->exchange ? net->exchange->localBuffer() : nullptr; }
+int scn_net_exchange_connect(scn_net_t *net, const unsigned char *handles) {
+  return guarded([&] {
+    if (!net->exchange) throw ScnException("no exchange (scn_net_exchange_create)");
+    net->exchange->connect(handles);
+  });
+}
+int scn_net_exchange_connect_local(scn_net_t *net, void *const *buffers) {
+  return guarded([&] {
+    if (!net->exchange) throw ScnException("no exchange (scn_net_exchange_create)");
+    net->exchange->connectLocal(buffers);
+  });
+}
+int scn_net_exchange_destroy(scn_net_t *net) { return guarded([&] { net->exchange.reset(); }); }
+
+namespace {
+void deliverExchange(ResultExchange &ex, bool any, float *gathered, int *rows) {
+  if (any) { ex.deliver(gathered, rows); return; }
+  for (int r = 0; r < ex.world && rows; ++r) rows[r] = -1; // nothing had been published before this step
+}
+} // namespace
+
+int scn_net_forward_host_exchange(scn_net_t *net, int batch, const int *keys, const int *off, const float *features, float *probs, int *predictions,
+                                  float *gathered_prev, int *rows_prev) {
+  return guarded([&] {
+    SparseConvNetCUDA &cnn = *net->cnn;
+    if (!net->exchange || !net->exchange->connected()) throw ScnException("no connected exchange (scn_net_exchange_create / _connect)");
+    ResultExchange &ex = *net->exchange;
+    SpatiallySparseBatch &b = uploadHostInput(net, batch, keys, off, features, UNLABELEDBATCH);
+    cnn.earlyFirstLayer = true;
+    cnn.preprocessBatchOnDevice(b);
+    cnn.earlyFirstLayer = false;
+    cnn.forwardLayers(b);
+    net->last = &b;
+    SpatiallySparseBatchInterface &topI = b.interfaces.back();
+    if (batch != topI.nSpatialSites) throw ScnException("the top layer must hold one row per sample");
+    // the step before: every rank published it at the end of its previous call, so this wait is over at once unless a
+    // rank has fallen a whole step behind; then this step's block goes out.  Both ride in front of the one copy + wait
+    // that ends the step.
+    const bool any = ex.published > 0;
+    cudaStream_t s = cnn.memStream.stream;
+    ex.step(topI.sub->features.dPtr(), batch, s);
+    if (any) ex.copyBlockToHost(s);
+    const char *block = fetchClassifierResult(topI, batch, cnn.nTop, cnn.memStream);
+    const size_t pb = sizeof(float) * (size_t)batch * cnn.nClasses;
+    if (probs) std::memcpy(probs, block, pb);
+    if (predictions) std::memcpy(predictions, block + pb, sizeof(int) * (size_t)batch * cnn.nTop);
+    deliverExchange(ex, any, gathered_prev, rows_prev);
+  });
+}
+
+int scn_net_exchange_flush(scn_net_t *net, float *gathered, int *rows) {
+  return guarded([&] {
+    if (!net->exchange || !net->exchange->connected()) throw ScnException("no connected exchange");
+    ResultExchange &ex = *net->exchange;
+    cudaStream_t s = net->cnn->memStream.stream;
+    const bool any = ex.published > 0;
+    ex.step(nullptr, 0, s);
+    if (any) ex.copyBlockToHost(s);
+    cudaSafeCall(cudaStreamSynchronize(s));
+    deliverExchange(ex, any, gathered, rows);
+  });
+}
+
+int scn_net_exchange_step_device(scn_net_t *net, const float *d_probs, int rows, float *d_gathered_prev, int *d_rows_status_prev) {
+  return guarded([&] {
+    if (!net->exchange || !net->exchange->connected()) throw ScnException("no connected exchange");
+    ResultExchange &ex = *net->exchange;
+    cudaStream_t s = net->cnn->memStream.stream;
+    if ((d_gathered_prev == nullptr) != (d_rows_status_prev == nullptr)) throw ScnException("pass both result arrays or neither");
+    ex.step(d_probs, rows, s, d_gathered_prev, d_rows_status_prev);
   });
 }
 

@@ -19,6 +19,8 @@ EXPORTS = [
     "scn_net_save_weights", "scn_net_set_precision", "scn_net_forward_host", "scn_net_forward_device",
     "scn_net_copy_probs_device", "scn_net_train_batch", "scn_net_get_weights", "scn_net_iface_dfeatures", "scn_net_iface_sizes", "scn_net_iface_fetch", "scn_net_take_multiply_adds", "scn_net_enable_timing",
     "scn_net_layer_times", "scn_net_process_dataset", "scn_host_vectorTopIndices",
+    "scn_net_exchange_create", "scn_net_exchange_buffer", "scn_net_exchange_connect", "scn_net_exchange_connect_local", "scn_net_exchange_destroy",
+    "scn_net_forward_host_exchange", "scn_net_exchange_flush", "scn_net_exchange_step_device",
 ]
 
 LAYER_KEYS = ("type", "size", "stride", "minActive", "nIn", "nOut", "fs", "act", "inSpatial", "outSpatial")
@@ -75,6 +77,14 @@ def lib():
         L.scn_net_layer_times.argtypes = [c_p, c_p]
         L.scn_net_process_dataset.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p, c_int, c_p, c_p]
         L.scn_host_vectorTopIndices.argtypes = [c_p, c_int, c_int, c_p]
+        L.scn_net_exchange_create.argtypes = [c_p, c_int, c_int, c_int, c_p]
+        L.scn_net_exchange_buffer.restype, L.scn_net_exchange_buffer.argtypes = c_p, [c_p]
+        L.scn_net_exchange_connect.argtypes = [c_p, c_p]
+        L.scn_net_exchange_connect_local.argtypes = [c_p, c_p]
+        L.scn_net_exchange_destroy.argtypes = [c_p]
+        L.scn_net_forward_host_exchange.argtypes = [c_p, c_int] + [c_p] * 7
+        L.scn_net_exchange_flush.argtypes = [c_p, c_p, c_p]
+        L.scn_net_exchange_step_device.argtypes = [c_p, c_p, c_int, c_p, c_p]
         _lib = L
     return _lib
 
@@ -193,6 +203,64 @@ class Net:
         pred = np.empty((B, self.nTop), np.int32)
         _check(self.L.scn_net_forward_host(self.h, B, _np(keys), _np(off), _np(features), _np(probs), _np(pred)))
         return probs, pred
+
+    # ---- results of a batch sharded over the GPUs of one node (peer stores, no host-side collective)
+    def exchange_create(self, world, rank, cap_rows):
+        """Allocates this rank's exchange buffer; returns the 64 bytes the other ranks need (bytes)."""
+        h = (ctypes.c_ubyte * 64)()
+        _check(self.L.scn_net_exchange_create(self.h, world, rank, cap_rows, h))
+        self._exchange = (world, cap_rows)
+        return bytes(h)
+
+    def exchange_buffer(self):
+        return self.L.scn_net_exchange_buffer(self.h)
+
+    def exchange_connect(self, handles):
+        """handles: the ranks' 64-byte entries in rank order (bytes of length world * 64)."""
+        buf = (ctypes.c_ubyte * len(handles)).from_buffer_copy(handles)
+        _check(self.L.scn_net_exchange_connect(self.h, buf))
+
+    def exchange_connect_local(self, buffers):
+        """buffers: every rank's exchange_buffer() pointer, for ranks that live in this process."""
+        arr = (c_p * len(buffers))(*buffers)
+        _check(self.L.scn_net_exchange_connect_local(self.h, arr))
+
+    def exchange_destroy(self):
+        _check(self.L.scn_net_exchange_destroy(self.h))
+
+    def forward_host_exchange(self, keys, off, features, gathered_prev=None, rows_prev=None):
+        """forward_host that also publishes this step's probabilities to every rank; returns (probs, pred,
+        gathered_prev[world, cap_rows, nClasses], rows_prev[world]): what every rank published in the step before
+        (rows_prev all -1 on the first step)."""
+        world, cap = self._exchange
+        keys = np.ascontiguousarray(keys, np.int32)
+        off = np.ascontiguousarray(off, np.int32)
+        features = np.ascontiguousarray(features, np.float32)
+        B = len(off) - 1
+        probs = np.empty((B, self.nClasses), np.float32)
+        pred = np.empty((B, self.nTop), np.int32)
+        if gathered_prev is None:
+            gathered_prev = np.empty((world, cap, self.nClasses), np.float32)
+        if rows_prev is None:
+            rows_prev = np.empty(world, np.int32)
+        _check(self.L.scn_net_forward_host_exchange(self.h, B, _np(keys), _np(off), _np(features), _np(probs), _np(pred),
+                                                    _np(gathered_prev), _np(rows_prev)))
+        return probs, pred, gathered_prev, rows_prev
+
+    def exchange_flush(self, gathered=None, rows=None):
+        """The blocks of the last published step (waits for the stream)."""
+        world, cap = self._exchange
+        if gathered is None:
+            gathered = np.empty((world, cap, self.nClasses), np.float32)
+        if rows is None:
+            rows = np.empty(world, np.int32)
+        _check(self.L.scn_net_exchange_flush(self.h, _np(gathered), _np(rows)))
+        return gathered, rows
+
+    def exchange_step_device(self, d_probs, rows, d_gathered_prev, d_rows_status_prev):
+        """Enqueue: collect the step before into the two device tensors, then publish d_probs (None: collect only)."""
+        _check(self.L.scn_net_exchange_step_device(self.h, None if d_probs is None else c_p(d_probs.data_ptr()), rows,
+                                                   c_p(d_gathered_prev.data_ptr()), c_p(d_rows_status_prev.data_ptr())))
 
     def forward_device(self, d_keys, d_off, d_bg, d_features, max_sites, d_probs=None, d_top=None):
         """torch CUDA tensors in and out; returns (d_probs, d_top) without synchronising."""

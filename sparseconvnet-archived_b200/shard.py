@@ -1,8 +1,10 @@
 """Sharding of a batch over ranks: samples are independent through every layer (rules, gather
 and pooling are per sample, the GEMM is row-wise), so rank r simply takes a contiguous block
 of samples, builds its own rulebooks and runs its own forward; the single exchange step is an
-all-gather of the final class probabilities.  Works with any torch.distributed backend (NCCL
-on GPUs, gloo in the CPU tests)."""
+all-gather of the final class probabilities.  On the GPUs of one node that step runs over peer
+memory inside the forward call (connect_exchange, then Net.forward_host_exchange /
+Net.exchange_step_device: no collective call per step); gather_probabilities / gather_ragged do
+the same through torch.distributed for any backend (NCCL on GPUs, gloo in the CPU tests)."""
 import numpy as np
 import torch
 import torch.distributed as dist
@@ -58,3 +60,25 @@ def gather_ragged(local, counts, group=None):
     pad[: local.shape[0]] = local
     g = gather_probabilities(pad, group)
     return torch.cat([g[r * m: r * m + int(counts[r])] for r in range(len(counts))])
+
+
+def connect_exchange(net, cap_rows, group=None):
+    """Sets up the peer-memory result exchange of `net` among the ranks of `group` (one process per GPU, one node):
+    every rank allocates its buffer, the 64-byte handles travel once through torch.distributed, every rank maps the
+    others' buffers.  cap_rows = the largest number of samples a rank will publish in one step."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    handle = net.exchange_create(world, rank, cap_rows)
+    dev = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+    mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev)
+    everyone = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine, group=group)
+    net.exchange_connect(b"".join(bytes(t.cpu().tolist()) for t in everyone))
+    dist.barrier(group)  # nobody publishes before everybody has mapped everybody
+
+
+def disconnect_exchange(net, group=None):
+    """Every rank has stopped publishing (its stream is idle) before any rank frees its buffer."""
+    torch.cuda.synchronize()
+    dist.barrier(group)
+    net.exchange_destroy()
+    dist.barrier(group)
