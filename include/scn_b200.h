@@ -192,7 +192,9 @@ int scn_rules_chain_build_resident(scn_chain_resident_t *st, const scn_chain_lay
  *   - All calls on a device share the one array.  It keeps the last call's contents and the
  *     kernels clear what they need cleared, so back-to-back calls on one stream are fine;
  *     calls that can overlap on the GPU (different streams, different threads) race and
- *     corrupt each other's rules. */
+ *     corrupt each other's rules.
+ *   - The array's device address is looked up once per device ordinal and kept for the life of
+ *     the process: it does not survive cudaDeviceReset() or a second context on that ordinal. */
 #define SCN_RULES_STATIC_SCRATCH_BYTES (16u << 20)
 size_t scn_rules_static_scratch_bytes(void);
 int scn_rules_build_static(const scn_regions_t *r, int batch, const int *d_in_keys, const int *d_in_off,
