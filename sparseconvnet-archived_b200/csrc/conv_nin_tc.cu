@@ -182,20 +182,33 @@ constexpr int EPI_BYTES = BM * EPI_LD * 4;        // 18 KB
 // (negative: skipped, as maxPool skips it).  Only the pooled rows and their choices are written.
 // Two groups (four warps each) may share the work: group g takes the work items n = g, g + 2, ... of this CTA,
 // i.e. always accumulator g; each has its own staging slice, pooling-row table and named barrier.
+// The CTA's LAST work item has no main loop behind it to hide under, so the producer warps, idle by then, help:
+// with tailShare = 3 the owner (tailRank 0) takes every third 32-column slice of that item and the gather and split
+// warps (tailRank 1, 2: they run this function for that one item, staging through tailEpi, a pipeline stage that is
+// free once the item's MMAs have completed) take the others.
 template <bool SPLIT, int ACT, bool POOL = false>
 __device__ __forceinline__ void epilogue_role(const Params &P, float *epiBase, uint32_t tmem, uint32_t accFullBar, uint32_t accEmptyBar,
-                                              int nItems, int kSplit, int rows, int group = 0, int nGroups = 1) {
+                                              int nItems, int kSplit, int rows, int group = 0, int nGroups = 1, int tailShare = 0,
+                                              int tailRank = 0, float *tailEpi = nullptr) {
   __shared__ int poolRow0[BM]; // POOL: this tile's layer-output row per tile row (the second group's table follows its staging slice)
-  int *poolRow = group ? reinterpret_cast<int *>(epiBase + 2 * (EPI_BYTES / 4)) : poolRow0;
-  float *epi = epiBase + (size_t)group * (EPI_BYTES / 4);
-  const int barId = group ? 3 : 1;
+  int *poolRow = tailRank ? reinterpret_cast<int *>(tailEpi + EPI_BYTES / 4) : group ? reinterpret_cast<int *>(epiBase + 2 * (EPI_BYTES / 4)) : poolRow0;
+  float *epi = tailRank ? tailEpi : epiBase + (size_t)group * (EPI_BYTES / 4);
+  const int barId = tailRank ? 3 + tailRank : group ? 3 : 1;
   const int t = threadIdx.x & 127; // thread of the group; its warp reads tensor-memory lanes 32 * (warp % 4)...
   const int warp = t >> 5;
   const uint32_t laneAddr = tmem + ((uint32_t)(warp * 32) << 16);
   float *myRow = epi + (size_t)t * EPI_LD;
   const int c4 = t & 7, rsub = t >> 3; // store phase: 8 threads per row, 16 rows per pass
-  int n = group;
-  for (int item = blockIdx.x + group * gridDim.x; item < nItems; item += nGroups * gridDim.x, n += nGroups) {
+  int n = group, firstItem = blockIdx.x + group * gridDim.x;
+  if (tailRank) { // a helper: this CTA's last item only
+    const int count = (nItems - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    if (nItems <= (int)blockIdx.x || count <= 0) return;
+    n = count - 1;
+    firstItem = blockIdx.x + n * gridDim.x;
+  }
+  for (int item = firstItem; item < nItems; item += nGroups * gridDim.x, n += nGroups) {
+    const bool shared = tailShare > 1 && item + nGroups * (int)gridDim.x >= nItems;
+    const int sliceFirst = shared ? tailRank * EPI_COLS : 0, sliceStep = shared ? tailShare * EPI_COLS : EPI_COLS;
     const int tileId = SPLIT ? item / kSplit : item, split = SPLIT ? item - tileId * kSplit : 0;
     const int tileN = tileId % P.nTiles, tileM = tileId / P.nTiles;
     const int ab = n & 1;
@@ -206,7 +219,7 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epiBase, u
       const long long gr = (long long)row0 + t;
       poolRow[t] = gr < rows ? __ldg(P.poolRules + gr) : -1;
     }
-    for (int c = 0; c < P.BN; c += EPI_COLS) {
+    for (int c = sliceFirst; c < P.BN; c += sliceStep) {
       const int width = min(EPI_COLS, P.BN - c); // 32, or 16 for the last slice when BN % 32 == 16
       uint32_t a[32];
       const uint32_t addr = laneAddr + (uint32_t)(ab * P.accStride + c);
@@ -293,6 +306,7 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epiBase, u
       }
       asm volatile("bar.sync %0, 128;" ::"r"(barId) : "memory"); // the slice is free again
     }
+    if (tailRank) break; // (nothing waits for the last item's accumulator)
     tc_fence_before();
     mbar_arrive(accEmptyBar + 8 * ab); // this accumulator may be overwritten
   }
@@ -364,8 +378,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
   };
 
   const bool epi2 = !SPLIT && !ATMEM && P.epi2;
+  // the producer warps share the epilogue of the CTA's last item (two free pipeline stages serve as their staging slices)
+  const int tailShare = (!epi2 && P.stages >= 2 && stageBytes >= EPI_BYTES + BM * 4) ? 3 : 0;
   if (warp < 4) {
-    epilogue_role<SPLIT, ACT, POOL>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows, 0, epi2 ? 2 : 1);
+    epilogue_role<SPLIT, ACT, POOL>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows, 0, epi2 ? 2 : 1, tailShare);
   } else if (warp < 8) {
     // ------------------------------------------------------------ gather: asynchronous 16-byte copies
     const int t = threadIdx.x - 128, chunk = t & 7, rbase = t >> 3;
@@ -561,6 +577,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
         cp_async_arrive(rawBar + 8 * st);
       }
     }
+    if (tailShare)
+      epilogue_role<SPLIT, ACT, POOL>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows, 0, 1, tailShare, 1, reinterpret_cast<float *>(smem));
   } else if (warp < 12 && epi2) {
     // the gather writes both images itself: these warps drain every second accumulator instead
     if (!SPLIT && !ATMEM) epilogue_role<false, ACT, POOL>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows, 1, 2);
@@ -657,6 +675,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) k_conv_nin_tc(const Params P) 
         mbar_arrive(fullBar + 8 * st);
       }
     }
+    if (tailShare)
+      epilogue_role<SPLIT, ACT, POOL>(P, epi, tmem, accFullBar, accEmptyBar, nItems, kSplit, rows, 0, 1, tailShare, 2,
+                                      reinterpret_cast<float *>(smem + stageBytes));
   } else if (warp == 12) {
     // ------------------------------------------------------------ weight tiles by bulk copy
     if (lane == 0) {
