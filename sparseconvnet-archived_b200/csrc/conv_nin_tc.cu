@@ -250,6 +250,7 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epiBase, u
         // the window's cells are read together (independent shared-memory loads), then compared in order
         auto pool_windows = [&](auto cellsC, auto batchC) {
           constexpr int CELLSC = decltype(cellsC)::value, CH = decltype(batchC)::value; // CELLSC == 0: any power of two
+          constexpr bool ACT_LAST = ACT == SCN_NOSIGMOID || ACT == SCN_VLEAKYRELU || ACT == SCN_LEAKYRELU; // strictly increasing
           const int CELLS = CELLSC ? CELLSC : P.poolCells, WINDOWS = BM / CELLS;
 #pragma unroll
           for (int pr = rsub; pr < WINDOWS; pr += 16) { // (WINDOWS < 16: rows rsub >= WINDOWS have no window)
@@ -270,14 +271,23 @@ __device__ __forceinline__ void epilogue_role(const Params &P, float *epiBase, u
 #pragma unroll
               for (int j = 0; j < CH; ++j) {
                 if (from[j] < 0) continue;
-                const float o[4] = {activate_t<ACT>(P.p * v[j].x + P.p * b4.x, s4.x), activate_t<ACT>(P.p * v[j].y + P.p * b4.y, s4.y),
-                                    activate_t<ACT>(P.p * v[j].z + P.p * b4.z, s4.z), activate_t<ACT>(P.p * v[j].w + P.p * b4.w, s4.w)};
+                // ACT_LAST: p * v + p * b and the activation do not decrease in v, so the cells are compared on the raw
+                // sums and only the winner is finished (where two different sums round to one output, this picks the
+                // larger sum and the reference the earlier cell: the pooled value is the same)
+                const float o[4] = {ACT_LAST ? v[j].x : activate_t<ACT>(P.p * v[j].x + P.p * b4.x, s4.x),
+                                    ACT_LAST ? v[j].y : activate_t<ACT>(P.p * v[j].y + P.p * b4.y, s4.y),
+                                    ACT_LAST ? v[j].z : activate_t<ACT>(P.p * v[j].z + P.p * b4.z, s4.z),
+                                    ACT_LAST ? v[j].w : activate_t<ACT>(P.p * v[j].w + P.p * b4.w, s4.w)};
                 const int base = from[j] * P.N + col;
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
                   if (none || best[k] < o[k]) { best[k] = o[k]; idx[k] = base + k; } // the first maximum wins
                 none = false;
               }
+            }
+            if (ACT_LAST && !none) {
+              best[0] = activate_t<ACT>(P.p * best[0] + P.p * b4.x, s4.x); best[1] = activate_t<ACT>(P.p * best[1] + P.p * b4.y, s4.y);
+              best[2] = activate_t<ACT>(P.p * best[2] + P.p * b4.z, s4.z); best[3] = activate_t<ACT>(P.p * best[3] + P.p * b4.w, s4.w);
             }
             *reinterpret_cast<float4 *>(P.out + w * P.N + col) = make_float4(best[0], best[1], best[2], best[3]);
             *reinterpret_cast<int4 *>(P.choices + w * P.N + col) = make_int4(idx[0], idx[1], idx[2], idx[3]);
