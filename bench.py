@@ -317,32 +317,51 @@ def main():
         h_rows = np.zeros(world, np.int32)
         pending = []
         last_host = {}
-        if world > 1:
-            scn.shard.connect_exchange(gnet, BATCH_PER_GPU)
+        # (should the buffers not map on this machine, every rank falls back to an NCCL all-gather per step, gather of
+        # step j on NCCL's stream while step j + 1 computes: the line's config says which one ran)
+        exchange = world > 1 and os.environ.get("SCN_EXCHANGE", "1") != "0" and scn.shard.connect_exchange(gnet, BATCH_PER_GPU)
+        h_gathered_pinned = torch.empty((world * BATCH_PER_GPU, nC), dtype=torch.float32).pin_memory() if world > 1 and not exchange else None
 
         def step_device(j):
             dk, do, db, df, ms = dev_batches[j % n_rot]
             gnet.forward_device(dk, do, db, df, ms, d_probs2[j & 1], d_top)
-            if world > 1:  # collects step j - 1 into gathered2[(j - 1) & 1], publishes step j
+            if world == 1:
+                return
+            if exchange:  # collects step j - 1 into gathered2[(j - 1) & 1], publishes step j
                 gnet.exchange_step_device(d_probs2[j & 1], BATCH_PER_GPU, gathered2[(j - 1) & 1], d_rows_status)
                 pending[:] = [("device", j & 1)]
+            else:
+                work = dist.all_gather_into_tensor(gathered2[j & 1], d_probs2[j & 1], async_op=True)
+                drain()  # the launching stream waits for the previous step's gather
+                pending.append(("nccl", work, j & 1, False))
 
         def drain():
             while pending:
-                kind, k = pending.pop()
-                if kind == "device":
-                    gnet.exchange_step_device(None, 0, gathered2[k], d_rows_status)
-                else:  # the host leg's last step: its blocks come back to the host
+                entry = pending.pop()
+                if entry[0] == "device":
+                    gnet.exchange_step_device(None, 0, gathered2[entry[1]], d_rows_status)
+                elif entry[0] == "host":  # the host leg's last step: its blocks come back to the host
                     gnet.exchange_flush(h_gathered, h_rows)
+                else:
+                    _, work, k, to_host = entry
+                    work.wait()
+                    if to_host:
+                        h_gathered_pinned.copy_(gathered2[k], non_blocking=True)
+                        stream.synchronize()
 
         def step_host(j):
             keys, off, feats = host_batches[j % n_rot]
-            if world == 1:
+            if world == 1 or not exchange:
                 probs, pred = gnet.forward_host(keys, off, feats)
             else:
                 probs, pred, _, _ = gnet.forward_host_exchange(keys, off, feats, h_gathered, h_rows)
                 pending[:] = [("host", 0)]
             last_host["probs"], last_host["top"] = probs, pred
+            if world > 1 and not exchange:
+                gnet.copy_probs_device(d_probs2[j & 1])
+                work = dist.all_gather_into_tensor(gathered2[j & 1], d_probs2[j & 1], async_op=True)
+                drain()
+                pending.append(("nccl", work, j & 1, True))
 
         def timed(step, with_layer_times):
             ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
@@ -403,7 +422,7 @@ def main():
         check_tc("device-resident")
         last = dict(batch_index=rank * n_rot + (steps - 1) % n_rot, dev_probs=d_probs2[(steps - 1) & 1].cpu().numpy(), dev_top=d_top.cpu().numpy())
         gathered_host = gathered2[(steps - 1) & 1].cpu().numpy() if world > 1 else None
-        if world > 1 and int(d_rows_status[world].item()):
+        if world > 1 and exchange and int(d_rows_status[world].item()):
             raise RuntimeError("the result exchange gave up waiting for ranks (bits %d): this leg's numbers are void" % int(d_rows_status[world].item()))
         # Per-kernel durations for the roofline and the breakdown: the same steps once more with a CUDA
         # event between the layers.  (Those events cost about 0.06 ms of GPU idle per step, which is why
@@ -539,7 +558,7 @@ def main():
             metric=METRIC, value=total / (ms_dev * 1e-3), unit="samples/s", n_gpus=world, steps=steps, warmup=args.warmup,
             ms_per_step=ms_dev / steps, higher_is_better=True, scaling="weak", vs_baseline=None,
             dtype={"fp32": "f32", "bf16": "bf16", "3xtf32": "tf32x3/f32", "3xbf16": "bf16x3/f32"}.get(args.precision, "bf16x3|tf32x3/f32"), data="synthetic",
-            config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample%s" % (world, ", every rank's probabilities stored into every rank's buffer over peer memory by the forward call (no collective call per step); step j's blocks are delivered by step j+1 in both legs, the last step's behind it" if world > 1 else ""),
+            config=dict(workload=WORKLOAD, global_batch=world * BATCH_PER_GPU, parallelism="dp%d by sample%s" % (world, "" if world == 1 else ", every rank's probabilities stored into every rank's buffer over peer memory by the forward call (no collective call per step); step j's blocks are delivered by step j+1 in both legs, the last step's behind it" if exchange else ", NCCL all-gather of the probabilities per step (the peer-memory exchange could not be set up here), overlapped with the next step"),
                         l2="256 MiB written between timed steps; 2 distinct batches rotated", precision=args.precision,
                         timing="CUDA events per step on the launching stream, max over ranks; each leg %d times, median leg reported; wall %.3f s for the device legs; per-kernel durations from one more pass of the same steps with events between the layers" % (max(1, args.legs), t_wall)),
             legs=dict(n=max(1, args.legs), ms_per_step_device=[round(x / steps, 5) for x in dev_legs], ms_per_step_e2e=[round(x / steps, 5) for x in e2e_legs]),
@@ -559,7 +578,8 @@ def main():
         )
         print(json.dumps(line))
     if world > 1:
-        scn.shard.disconnect_exchange(gnet)
+        if exchange:
+            scn.shard.disconnect_exchange(gnet)
         dist.destroy_process_group()
 
 

@@ -155,10 +155,14 @@ int scn_net_forward_host_exchange(scn_net_t *net, int batch, const int *keys, co
                                   int *predictions, float *gathered_prev, int *rows_prev);
 /* The blocks of the last published step (ends a run of scn_net_forward_host_exchange calls; waits for the stream). */
 int scn_net_exchange_flush(scn_net_t *net, float *gathered, int *rows);
-/* Device-resident form, enqueued on the network's stream without waiting: collects the step before into
+/* Device-resident form, enqueued without waiting: collects the step before into
  * d_gathered_prev[world x cap_rows x nClasses] and d_rows_status_prev[world + 1] (row counts, then a word with bit r
  * set if rank r's block did not arrive in time), then publishes d_probs[rows x nClasses] as the next step
- * (d_probs NULL: collect only). */
+ * (d_probs NULL: collect only).  The kernel runs on a stream of the exchange's own, ordered behind what the network's
+ * stream holds at the call, so the next forward does not queue behind it: d_probs must stay as it is, and what was
+ * collected is complete, for work enqueued on the network's stream after the NEXT call (after this one when d_probs
+ * is NULL, which is how a run of steps ends).  A host-buffer step (scn_net_forward_host_exchange) must not follow
+ * before such a collect-only call. */
 int scn_net_exchange_step_device(scn_net_t *net, const float *d_probs, int rows, float *d_gathered_prev, int *d_rows_status_prev);
 
 #ifdef __cplusplus

@@ -17,6 +17,9 @@ ResultExchange::~ResultExchange() {
   cudaDeviceSynchronize(); // no kernel of this rank may still store into a peer's buffer
   for (int r = 0; r < world; ++r)
     if (opened[r]) scn_exchange_close(peers[r]);
+  if (sideDone) cudaEventDestroy(sideDone);
+  if (mainReady) cudaEventDestroy(mainReady);
+  if (side) cudaStreamDestroy(side);
   if (hOut) cudaFreeHost(hOut);
   if (dOut) cudaFree(dOut);
   scn_exchange_free(local);
@@ -53,6 +56,24 @@ void ResultExchange::step(const float *dProbs, int rows, cudaStream_t stream, fl
                                 stream));
   collected = published;
   if (publishStep) ++published;
+}
+
+void ResultExchange::stepBeside(const float *dProbs, int rows, cudaStream_t main, float *dGathered, int *dRowsStatus) {
+  if (!side) {
+    cudaSafeCall(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
+    cudaSafeCall(cudaEventCreateWithFlags(&mainReady, cudaEventDisableTiming));
+    cudaSafeCall(cudaEventCreateWithFlags(&sideDone, cudaEventDisableTiming));
+  }
+  if (sidePending) cudaSafeCall(cudaStreamWaitEvent(main, sideDone, 0)); // the step before: over long ago, but now ordered
+  cudaSafeCall(cudaEventRecord(mainReady, main));
+  cudaSafeCall(cudaStreamWaitEvent(side, mainReady, 0));
+  step(dProbs, rows, side, dGathered, dRowsStatus);
+  cudaSafeCall(cudaEventRecord(sideDone, side));
+  sidePending = true;
+  if (!dProbs) {
+    cudaSafeCall(cudaStreamWaitEvent(main, sideDone, 0));
+    sidePending = false;
+  }
 }
 
 void ResultExchange::copyBlockToHost(cudaStream_t stream) {

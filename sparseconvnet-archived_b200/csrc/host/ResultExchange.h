@@ -35,6 +35,10 @@ public:
   // it out (gathered may be NULL) and throws if a rank's block did not arrive within the time limit.
   void copyBlockToHost(cudaStream_t stream);
   void deliver(float *gathered, int *rows);
+  // The same step on a stream of this object's own, ordered behind what `main` holds now: the device-resident caller's
+  // next forward does not queue behind the exchange kernel.  What the step collected is complete for work enqueued on
+  // `main` after the NEXT call of stepBeside (or after this one, when dProbs is NULL: a collect-only call ends a run).
+  void stepBeside(const float *dProbs, int rows, cudaStream_t main, float *dGathered, int *dRowsStatus);
 
 private:
   void *local = nullptr;
@@ -44,4 +48,7 @@ private:
   bool isConnected = false;
   float *dOut = nullptr; // device block
   char *hOut = nullptr;  // page-locked copy
+  cudaStream_t side = nullptr;
+  cudaEvent_t mainReady = nullptr, sideDone = nullptr;
+  bool sidePending = false;
 };

@@ -403,7 +403,7 @@ int scn_net_exchange_step_device(scn_net_t *net, const float *d_probs, int rows,
     ResultExchange &ex = *net->exchange;
     cudaStream_t s = net->cnn->memStream.stream;
     if ((d_gathered_prev == nullptr) != (d_rows_status_prev == nullptr)) throw ScnException("pass both result arrays or neither");
-    ex.step(d_probs, rows, s, d_gathered_prev, d_rows_status_prev);
+    ex.stepBeside(d_probs, rows, s, d_gathered_prev, d_rows_status_prev);
   });
 }
 

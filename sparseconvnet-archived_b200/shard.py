@@ -62,18 +62,41 @@ def gather_ragged(local, counts, group=None):
     return torch.cat([g[r * m: r * m + int(counts[r])] for r in range(len(counts))])
 
 
+def _all_ok(ok, dev, group):
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return bool(int(flag.item()))
+
+
 def connect_exchange(net, cap_rows, group=None):
     """Sets up the peer-memory result exchange of `net` among the ranks of `group` (one process per GPU, one node):
     every rank allocates its buffer, the 64-byte handles travel once through torch.distributed, every rank maps the
-    others' buffers.  cap_rows = the largest number of samples a rank will publish in one step."""
+    others' buffers.  cap_rows = the largest number of samples a rank will publish in one step.  Returns True when
+    EVERY rank succeeded; otherwise every rank has dropped its half-built exchange and gets False (the caller falls
+    back to gather_probabilities).  Ranks agree after each local step, so no rank is left alone in a collective."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
-    handle = net.exchange_create(world, rank, cap_rows)
     dev = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl" else torch.device("cpu")
+    handle, ok = bytes(64), True
+    try:
+        handle = net.exchange_create(world, rank, cap_rows)
+    except Exception:
+        ok = False
+    if not _all_ok(ok, dev, group):
+        net.exchange_destroy()
+        return False
     mine = torch.tensor(list(handle), dtype=torch.uint8, device=dev)
     everyone = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather(everyone, mine, group=group)
-    net.exchange_connect(b"".join(bytes(t.cpu().tolist()) for t in everyone))
-    dist.barrier(group)  # nobody publishes before everybody has mapped everybody
+    try:
+        net.exchange_connect(b"".join(bytes(t.cpu().tolist()) for t in everyone))
+    except Exception:
+        ok = False
+    if not _all_ok(ok, dev, group):  # (also the point behind which everybody has mapped everybody: publishing may start)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        net.exchange_destroy()
+        return False
+    return True
 
 
 def disconnect_exchange(net, group=None):

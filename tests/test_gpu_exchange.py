@@ -127,6 +127,50 @@ def test_sharded_forward_delivers_every_ranks_results_one_step_later(scn, abi, o
         n.exchange_destroy()
 
 
+def test_device_resident_steps_deliver_one_step_later(scn, abi, oracle):
+    """The device-resident form (exchange kernel beside the network's stream): two emulated ranks, three steps and the
+    collect-only call that ends the run."""
+    cfg, world, per = 2, 2, 6
+    c = scn.synth.CONFIGS[cfg]
+    nC = c["nClasses"]
+    nets = [make_pair(scn, oracle, cfg)[0] for _ in range(world)]
+    for r, n in enumerate(nets):
+        n.exchange_create(world, r, per)
+    bufs = [n.exchange_buffer() for n in nets]
+    for n in nets:
+        n.exchange_connect_local(bufs)
+    dev = torch.device("cuda")
+    gathered = [[torch.zeros((world, per, nC), device=dev) for _ in range(2)] for _ in range(world)]
+    status = [torch.zeros(world + 1, dtype=torch.int32, device=dev) for _ in range(world)]
+    d_top = torch.empty((per, 1), dtype=torch.int32, device=dev)
+    history = []
+    for step in range(3):
+        own = []
+        for r, n in enumerate(nets):
+            keys, off, feats = c["gen"](per, first=(step * world + r) * per)
+            want, _ = n.forward_host(keys, off, feats)
+            dk, do, df = (torch.from_numpy(x).to(dev) for x in (keys, off, feats))
+            db = do[:-1].clone()
+            d_probs = torch.empty((per, nC), device=dev)
+            n.forward_device(dk, do, db, df, int(np.diff(off).max() - 1), d_probs, d_top)
+            n.exchange_step_device(d_probs, per, gathered[r][(step - 1) & 1], status[r])
+            torch.cuda.synchronize()  # (the emulated ranks share one GPU: a step is published before the next rank collects)
+            np.testing.assert_array_equal(d_probs.cpu().numpy(), want)
+            own.append(want)
+        history.append(own)
+    for r, n in enumerate(nets):
+        n.exchange_step_device(None, 0, gathered[r][2 & 1], status[r])
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert int(status[r][world].item()) == 0
+        assert status[r][:world].tolist() == [per] * world
+        for s_ in range(world):
+            np.testing.assert_array_equal(gathered[r][0][s_].cpu().numpy(), history[2][s_])  # step 2, collected last
+            np.testing.assert_array_equal(gathered[r][1][s_].cpu().numpy(), history[1][s_])  # step 1, collected in step 2
+    for n in nets:
+        n.exchange_destroy()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -151,7 +195,7 @@ def _rank_process(rank, world, port, out_dir):
         scn.synth.build_network(net, cfg)
         for i, (W, B, pr) in scn.synth.init_weights(net.layers()).items():
             net.set_weights(i, W, B, pr)
-        scn.shard.connect_exchange(net, per)
+        assert scn.shard.connect_exchange(net, per)
         record = []
         for step in range(6):
             keys, off, feats = c["gen"](per - (step + rank) % 2, first=(step * world + rank) * per)
