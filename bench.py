@@ -7,12 +7,15 @@ CIFAR-10-shaped dense-in-sparse 2-D workload, batch 256 per GPU.
 
 One "step" = one full forward of one batch: rule construction for every layer on the
 device, all fused conv/NiN, pooling and softmax kernels, top-1, and (N > 1) the all-gather
-of the class probabilities.  Rank r of N processes its own 256 samples (weak scaling).
+of the class probabilities (over peer memory, inside the forward call).  Rank r of N processes
+its own 256 samples (weak scaling).
 
   value     device-timed throughput with the inputs already resident in HBM
-  e2e       the same through the host-buffer entry point (scn_net_forward_host): pinned
-            staging + H2D of keys/offsets/features inside the timed region, D2H of
-            probabilities and predictions at the end of every step
+  e2e       the same through the host-buffer entry points (scn_net_forward_host_begin / _end:
+            the upload of batch j + 1 runs while batch j is computed, as the reference's
+            producer threads do): every step issues the H2D copies of one batch's keys, offsets
+            and features from pinned memory and ends with the D2H copy of one batch's
+            probabilities and predictions and a host wait, all inside the timed region
   roofline  the kernel with the largest share of the step, CUDA-event timed in the same run
   cpu_baseline  the CPU oracle (port of the reference's host rule construction and layer
             semantics) on a bounded sample of the same workload, all host cores
@@ -349,12 +352,20 @@ def main():
                         h_gathered_pinned.copy_(gathered2[k], non_blocking=True)
                         stream.synchronize()
 
+        run = {"n": steps}  # length of the run of steps under way (the host leg begins batch j + 1 before it ends batch j)
+
         def step_host(j):
-            keys, off, feats = host_batches[j % n_rot]
+            # forward_host in two halves: the inputs of batch j + 1 start their way to the device, then batch j (begun by
+            # the previous step) is computed and its results are waited for.  Every step issues one batch's copies and
+            # returns one batch's results; the first step of a run issues two batches' copies, the last one none.
+            if j == 0:
+                gnet.forward_host_begin(*host_batches[0])
+            if j + 1 < run["n"]:
+                gnet.forward_host_begin(*host_batches[(j + 1) % n_rot])
             if world == 1 or not exchange:
-                probs, pred = gnet.forward_host(keys, off, feats)
+                probs, pred = gnet.forward_host_end()
             else:
-                probs, pred, _, _ = gnet.forward_host_exchange(keys, off, feats, h_gathered, h_rows)
+                probs, pred, _, _ = gnet.forward_host_end(True, h_gathered, h_rows)
                 pending[:] = [("host", 0)]
             last_host["probs"], last_host["top"] = probs, pred
             if world > 1 and not exchange:
@@ -432,9 +443,11 @@ def main():
         barrier()
         gnet.enable_timing(False)
         # ---- host-buffer leg
+        run["n"] = args.warmup
         for j in range(args.warmup):
             step_host(j)
         drain()
+        run["n"] = steps
         ms_e2e_legs = legs(step_host)
         check_tc("host-buffer")
         last["host_probs"], last["host_top"] = last_host["probs"].copy(), last_host["top"].copy()
@@ -563,6 +576,7 @@ def main():
                         timing="CUDA events per step on the launching stream, max over ranks; each leg %d times, median leg reported; wall %.3f s for the device legs; per-kernel durations from one more pass of the same steps with events between the layers" % (max(1, args.legs), t_wall)),
             legs=dict(n=max(1, args.legs), ms_per_step_device=[round(x / steps, 5) for x in dev_legs], ms_per_step_e2e=[round(x / steps, 5) for x in e2e_legs]),
             e2e=dict(value=total / (ms_e2e * 1e-3), unit="samples/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                     call="scn_net_forward_host_begin / _end: each step starts the copies of the next batch, then computes and returns the current one",
                      ms_per_step=ms_e2e / steps),
             gpu_launches=int(launches), roofline=roof, cpu_baseline=cpu, parity=parity, clocks=clocks,
             pooling_roofline=(dict(bound="hbm", kernel="k_maxpool layer %d" % pool_top["layer"], achieved=pool_top["bytes"] / (pool_top["ms"] * 1e-3) / 1e9,

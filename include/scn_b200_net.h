@@ -134,6 +134,15 @@ int scn_net_process_dataset(scn_net_t *net, int nSamples, const int *h_keys, con
 /* vectorTopIndices (utilities.cu:35-56), the host version SoftmaxClassifier-style callers use. */
 int scn_host_vectorTopIndices(const float *h_v, int n, int k, int *h_out);
 
+/* scn_net_forward_host in two halves, so that a caller with a stream of batches overlaps the upload of the next
+ * batch with the computation of the current one, as the reference's producer threads do for its consumer thread
+ * (BatchProducer.cu:90-142, SparseConvNetCUDA.cu:272-326): _begin starts the copies of a batch's host arrays (which
+ * must stay as they are until the matching _end returns; page-locked memory makes the copies asynchronous) and
+ * returns; _end computes the oldest batch begun and not yet ended and returns its results.  At most two batches may be
+ * on their way.  With gathered_prev / rows_prev not NULL, _end also does what scn_net_forward_host_exchange does. */
+int scn_net_forward_host_begin(scn_net_t *net, int batch, const int *keys, const int *off, const float *features);
+int scn_net_forward_host_end(scn_net_t *net, float *probs, int *predictions, float *gathered_prev, int *rows_prev);
+
 /* ---- results of a batch sharded by sample over the GPUs of one node (ResultExchange: peer stores + bounded waits,
  * no host-side collective; the reference itself runs on one device, SparseConvNetCUDA.cu:43-71).
  * scn_net_exchange_create allocates this rank's buffer for blocks of at most cap_rows x nClasses probabilities and

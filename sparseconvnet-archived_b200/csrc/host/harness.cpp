@@ -29,8 +29,21 @@ struct scn_net {
   // of them have become pageable since, its copy is still correct, only less asynchronous)
   std::vector<const void *> knownPinned;
   std::unique_ptr<ResultExchange> exchange; // results to and from the other ranks of a sharded batch
+  // scn_net_forward_host_begin / _end: the inputs of the batch after the one being computed travel to one of two
+  // device-side slots on the copy stream meanwhile (what the reference's producer threads do for its consumer)
+  struct HostUpload {
+    vectorCUDA<int> keys, off;
+    vectorCUDA<float> feats;
+    int batch = 0, rows = 0, maxSites = 0;
+    cudaEvent_t keysDone = nullptr, featsDone = nullptr;
+  } up[2];
+  int upHead = 0, upTail = 0, upCount = 0;
   ~scn_net() {
     exchange.reset();
+    for (HostUpload &u : up) {
+      if (u.keysDone) cudaEventDestroy(u.keysDone);
+      if (u.featsDone) cudaEventDestroy(u.featsDone);
+    }
     if (copyDone) cudaEventDestroy(copyDone);
     if (copyStream) cudaStreamDestroy(copyStream);
   }
@@ -308,22 +321,120 @@ int scn_net_set_precision(scn_net_t *net, int precision) {
   });
 }
 
+namespace {
+void deliverExchange(ResultExchange &ex, bool any, float *gathered, int *rows) {
+  if (any) { ex.deliver(gathered, rows); return; }
+  for (int r = 0; r < ex.world && rows; ++r) rows[r] = -1; // nothing had been published before this step
+}
+// Rule chain, layers and the one copy-and-wait that ends a step, for a batch whose input interface is filled (its
+// copies may still be on their way: the stream and the layers wait for them where they need them).  processBatch
+// without the per-sample vectors of SpatiallySparseBatch: the results go straight to the caller's arrays.  With
+// `exchange` the step's probabilities also go to the other ranks and theirs of the step before come back.
+void runHostBatch(scn_net *net, SpatiallySparseBatch &b, int batch, float *probs, int *predictions, bool exchange, float *gathered_prev,
+                  int *rows_prev) {
+  SparseConvNetCUDA &cnn = *net->cnn;
+  if (exchange && (!net->exchange || !net->exchange->connected())) throw ScnException("no connected exchange (scn_net_exchange_create / _connect)");
+  cnn.earlyFirstLayer = true; // one batch in flight here: the first layer may start behind the rule chain
+  cnn.preprocessBatchOnDevice(b); // waits once, after the key upload and the rule chain
+  cnn.earlyFirstLayer = false;
+  cnn.forwardLayers(b);
+  net->last = &b;
+  SpatiallySparseBatchInterface &topI = b.interfaces.back();
+  if (batch != topI.nSpatialSites) throw ScnException("the top layer must hold one row per sample");
+  bool any = false;
+  if (exchange) {
+    // the step before: every rank published it at the end of its previous call, so this wait is over at once unless a
+    // rank has fallen a whole step behind; then this step's block goes out.  Both ride in front of the one copy + wait
+    // that ends the step.
+    ResultExchange &ex = *net->exchange;
+    any = ex.published > 0;
+    cudaStream_t s = cnn.memStream.stream;
+    ex.step(topI.sub->features.dPtr(), batch, s);
+    if (any) ex.copyBlockToHost(s);
+  }
+  const char *block = fetchClassifierResult(topI, batch, cnn.nTop, cnn.memStream);
+  const size_t pb = sizeof(float) * (size_t)batch * cnn.nClasses;
+  if (probs) std::memcpy(probs, block, pb);
+  if (predictions) std::memcpy(predictions, block + pb, sizeof(int) * (size_t)batch * cnn.nTop);
+  if (exchange) deliverExchange(*net->exchange, any, gathered_prev, rows_prev);
+}
+} // namespace
+
 int scn_net_forward_host(scn_net_t *net, int batch, const int *keys, const int *off, const float *features, float *probs, int *predictions) {
   return guarded([&] {
-    SparseConvNetCUDA &cnn = *net->cnn;
     SpatiallySparseBatch &b = uploadHostInput(net, batch, keys, off, features, UNLABELEDBATCH);
-    cnn.earlyFirstLayer = true; // one batch in flight here: the first layer may start behind the rule chain
-    cnn.preprocessBatchOnDevice(b); // waits once, after the key upload and the rule chain
-    cnn.earlyFirstLayer = false;
-    // processBatch without the per-sample vectors of SpatiallySparseBatch: the results go straight to the caller's arrays
-    cnn.forwardLayers(b);
-    net->last = &b;
-    SpatiallySparseBatchInterface &topI = b.interfaces.back();
-    if (batch != topI.nSpatialSites) throw ScnException("the top layer must hold one row per sample");
-    const char *block = fetchClassifierResult(topI, batch, cnn.nTop, cnn.memStream);
-    const size_t pb = sizeof(float) * (size_t)batch * cnn.nClasses;
-    if (probs) std::memcpy(probs, block, pb);
-    if (predictions) std::memcpy(predictions, block + pb, sizeof(int) * (size_t)batch * cnn.nTop);
+    runHostBatch(net, b, batch, probs, predictions, false, nullptr, nullptr);
+  });
+}
+
+int scn_net_forward_host_begin(scn_net_t *net, int batch, const int *keys, const int *off, const float *features) {
+  return guarded([&] {
+    SparseConvNetCUDA &cnn = *net->cnn;
+    if (batch < 1) throw ScnException("batch must be positive");
+    if (net->upCount == 2) throw ScnException("two batches are on their way already: take one with scn_net_forward_host_end first");
+    scn_net::HostUpload &u = net->up[net->upHead];
+    const int rows = off[batch], nF = cnn.nInputFeatures;
+    int maxRows = 0;
+    for (int s = 0; s < batch; ++s) maxRows = std::max(maxRows, off[s + 1] - off[s]);
+    if (!cnn.layers.empty() && dynamic_cast<TerminalPoolingLayer *>(cnn.layers[0])) { // its rule width needs the exact count
+      int most = 0;
+      for (int s = 0; s < batch; ++s) { int n = 0; for (int r = off[s]; r < off[s + 1]; ++r) n += keys[r] >= 0; most = std::max(most, n); }
+      maxRows = most;
+    }
+    u.batch = batch; u.rows = rows; u.maxSites = maxRows;
+    u.keys.resize(rows); u.off.resize(batch + 1); u.feats.resize(rows * nF);
+    if (!net->copyStream) {
+      cudaSafeCall(cudaStreamCreateWithFlags(&net->copyStream, cudaStreamNonBlocking));
+      cudaSafeCall(cudaEventCreateWithFlags(&net->copyDone, cudaEventDisableTiming));
+    }
+    if (!u.keysDone) {
+      cudaSafeCall(cudaEventCreateWithFlags(&u.keysDone, cudaEventDisableTiming));
+      cudaSafeCall(cudaEventCreateWithFlags(&u.featsDone, cudaEventDisableTiming));
+    }
+    // (the slot's buffers are idle: the batch that used them last ended with a host wait two calls ago; a resize may have
+    // enqueued work on the network's stream, so the copies are ordered behind it)
+    cudaStream_t cs = net->copyStream;
+    cudaSafeCall(cudaEventRecord(net->copyDone, cnn.memStream.stream));
+    cudaSafeCall(cudaStreamWaitEvent(cs, net->copyDone, 0));
+    if (rows) cudaSafeCall(cudaMemcpyAsync(u.keys.dPtr(), keys, sizeof(int) * (size_t)rows, cudaMemcpyHostToDevice, cs));
+    cudaSafeCall(cudaMemcpyAsync(u.off.dPtr(), off, sizeof(int) * (size_t)(batch + 1), cudaMemcpyHostToDevice, cs));
+    cudaSafeCall(cudaEventRecord(u.keysDone, cs));
+    if (rows) cudaSafeCall(cudaMemcpyAsync(u.feats.dPtr(), features, sizeof(float) * (size_t)rows * nF, cudaMemcpyHostToDevice, cs));
+    cudaSafeCall(cudaEventRecord(u.featsDone, cs));
+    net->upHead ^= 1;
+    ++net->upCount;
+  });
+}
+
+int scn_net_forward_host_end(scn_net_t *net, float *probs, int *predictions, float *gathered_prev, int *rows_prev) {
+  return guarded([&] {
+    SparseConvNetCUDA &cnn = *net->cnn;
+    if (net->upCount == 0) throw ScnException("no batch is on its way (scn_net_forward_host_begin)");
+    scn_net::HostUpload &u = net->up[net->upTail];
+    net->upTail ^= 1;
+    --net->upCount;
+    SpatiallySparseBatch &b = cnn.batchPool[0];
+    cnn.prepareBatch(b);
+    b.reset();
+    b.type = UNLABELEDBATCH;
+    b.batchSize = u.batch;
+    SpatiallySparseBatchInterface &in = b.interfaces[0];
+    in.nFeatures = cnn.nInputFeatures;
+    in.spatialSize = cnn.inputSpatialSize;
+    in.featuresPresent.hVector() = range(cnn.nInputFeatures);
+    in.nSpatialSites = u.rows;
+    in.maxSitesPerSample = u.maxSites;
+    in.gridOwner = &in;
+    in.backpropErrors = false;
+    in.backgroundRows.copyToGPU();
+    in.backgroundRows.resize(u.batch);
+    in.siteKeys.borrowDevice(u.keys.dPtr(), u.rows);
+    in.sampleOffsets.borrowDevice(u.off.dPtr(), u.batch + 1);
+    in.sub->features.borrowDevice(u.feats.dPtr(), u.rows * cnn.nInputFeatures);
+    cudaSafeCall(cudaStreamWaitEvent(cnn.memStream.stream, u.keysDone, 0)); // the rule chain reads keys and offsets
+    cnn.inputBackgroundPending = true;
+    if (u.rows) cnn.inputReady = u.featsDone; // the layers wait for the features
+    runHostBatch(net, b, u.batch, probs, predictions, gathered_prev != nullptr || rows_prev != nullptr, gathered_prev, rows_prev);
   });
 }
 
@@ -348,39 +459,12 @@ int scn_net_exchange_connect_local(scn_net_t *net, void *const *buffers) {
 }
 int scn_net_exchange_destroy(scn_net_t *net) { return guarded([&] { net->exchange.reset(); }); }
 
-namespace {
-void deliverExchange(ResultExchange &ex, bool any, float *gathered, int *rows) {
-  if (any) { ex.deliver(gathered, rows); return; }
-  for (int r = 0; r < ex.world && rows; ++r) rows[r] = -1; // nothing had been published before this step
-}
-} // namespace
-
 int scn_net_forward_host_exchange(scn_net_t *net, int batch, const int *keys, const int *off, const float *features, float *probs, int *predictions,
                                   float *gathered_prev, int *rows_prev) {
   return guarded([&] {
-    SparseConvNetCUDA &cnn = *net->cnn;
     if (!net->exchange || !net->exchange->connected()) throw ScnException("no connected exchange (scn_net_exchange_create / _connect)");
-    ResultExchange &ex = *net->exchange;
     SpatiallySparseBatch &b = uploadHostInput(net, batch, keys, off, features, UNLABELEDBATCH);
-    cnn.earlyFirstLayer = true;
-    cnn.preprocessBatchOnDevice(b);
-    cnn.earlyFirstLayer = false;
-    cnn.forwardLayers(b);
-    net->last = &b;
-    SpatiallySparseBatchInterface &topI = b.interfaces.back();
-    if (batch != topI.nSpatialSites) throw ScnException("the top layer must hold one row per sample");
-    // the step before: every rank published it at the end of its previous call, so this wait is over at once unless a
-    // rank has fallen a whole step behind; then this step's block goes out.  Both ride in front of the one copy + wait
-    // that ends the step.
-    const bool any = ex.published > 0;
-    cudaStream_t s = cnn.memStream.stream;
-    ex.step(topI.sub->features.dPtr(), batch, s);
-    if (any) ex.copyBlockToHost(s);
-    const char *block = fetchClassifierResult(topI, batch, cnn.nTop, cnn.memStream);
-    const size_t pb = sizeof(float) * (size_t)batch * cnn.nClasses;
-    if (probs) std::memcpy(probs, block, pb);
-    if (predictions) std::memcpy(predictions, block + pb, sizeof(int) * (size_t)batch * cnn.nTop);
-    deliverExchange(ex, any, gathered_prev, rows_prev);
+    runHostBatch(net, b, batch, probs, predictions, true, gathered_prev, rows_prev);
   });
 }
 

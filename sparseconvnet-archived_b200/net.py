@@ -21,6 +21,7 @@ EXPORTS = [
     "scn_net_layer_times", "scn_net_process_dataset", "scn_host_vectorTopIndices",
     "scn_net_exchange_create", "scn_net_exchange_buffer", "scn_net_exchange_connect", "scn_net_exchange_connect_local", "scn_net_exchange_destroy",
     "scn_net_forward_host_exchange", "scn_net_exchange_flush", "scn_net_exchange_step_device",
+    "scn_net_forward_host_begin", "scn_net_forward_host_end",
 ]
 
 LAYER_KEYS = ("type", "size", "stride", "minActive", "nIn", "nOut", "fs", "act", "inSpatial", "outSpatial")
@@ -85,6 +86,8 @@ def lib():
         L.scn_net_forward_host_exchange.argtypes = [c_p, c_int] + [c_p] * 7
         L.scn_net_exchange_flush.argtypes = [c_p, c_p, c_p]
         L.scn_net_exchange_step_device.argtypes = [c_p, c_p, c_int, c_p, c_p]
+        L.scn_net_forward_host_begin.argtypes = [c_p, c_int, c_p, c_p, c_p]
+        L.scn_net_forward_host_end.argtypes = [c_p, c_p, c_p, c_p, c_p]
         _lib = L
     return _lib
 
@@ -203,6 +206,33 @@ class Net:
         pred = np.empty((B, self.nTop), np.int32)
         _check(self.L.scn_net_forward_host(self.h, B, _np(keys), _np(off), _np(features), _np(probs), _np(pred)))
         return probs, pred
+
+    def forward_host_begin(self, keys, off, features):
+        """Starts the upload of a batch (int32 keys, int32 offsets, float32 features: contiguous arrays that the caller
+        keeps alive and unchanged until the matching forward_host_end); at most two batches may be on their way."""
+        for a, t in ((keys, np.int32), (off, np.int32), (features, np.float32)):
+            if a.dtype != t or not a.flags["C_CONTIGUOUS"]:
+                raise abi.ScnError("forward_host_begin takes contiguous int32 / int32 / float32 arrays (no copies are made)")
+        B = len(off) - 1
+        _check(self.L.scn_net_forward_host_begin(self.h, B, _np(keys), _np(off), _np(features)))
+        self._begun = getattr(self, "_begun", []) + [(B, keys, off, features)]
+
+    def forward_host_end(self, exchange=False, gathered_prev=None, rows_prev=None):
+        """Computes the oldest batch begun; returns (probs, pred) or, with exchange, (probs, pred, gathered_prev, rows_prev)."""
+        if not getattr(self, "_begun", None):
+            raise abi.ScnError("no batch is on its way (forward_host_begin)")
+        B = self._begun.pop(0)[0]
+        probs = np.empty((B, self.nClasses), np.float32)
+        pred = np.empty((B, self.nTop), np.int32)
+        if exchange:
+            world, cap = self._exchange
+            if gathered_prev is None:
+                gathered_prev = np.empty((world, cap, self.nClasses), np.float32)
+            if rows_prev is None:
+                rows_prev = np.empty(world, np.int32)
+        _check(self.L.scn_net_forward_host_end(self.h, _np(probs), _np(pred), _np(gathered_prev) if exchange else None,
+                                               _np(rows_prev) if exchange else None))
+        return (probs, pred, gathered_prev, rows_prev) if exchange else (probs, pred)
 
     # ---- results of a batch sharded over the GPUs of one node (peer stores, no host-side collective)
     def exchange_create(self, world, rank, cap_rows):

@@ -222,3 +222,27 @@ def test_alternating_batches_reuse_buffers(scn, abi, nets):
         for x, want in zip((a, b), first):
             got = gnet.forward_host(*x)[0]
             assert np.array_equal(got, want), it
+
+
+def test_begin_end_pipeline_equals_plain_calls(scn, abi, oracle):
+    """forward_host in two halves: uploads run one batch ahead; results, order and the limit of two batches on their way."""
+    c = scn.synth.CONFIGS[2]
+    gnet, _ = make_pair(scn, oracle, 2)
+    batches = [c["gen"](5 + (i % 3), first=10 * i) for i in range(6)]
+    want = [gnet.forward_host(*b) for b in batches]
+    with pytest.raises(scn.abi.ScnError):
+        gnet.forward_host_end()  # nothing begun
+    gnet.forward_host_begin(*batches[0])
+    for i in range(len(batches)):
+        if i + 1 < len(batches):
+            gnet.forward_host_begin(*batches[i + 1])
+            if i == 0:
+                with pytest.raises(scn.abi.ScnError):
+                    gnet.forward_host_begin(*batches[2])  # a third one
+        probs, pred = gnet.forward_host_end()
+        np.testing.assert_array_equal(probs, want[i][0])
+        np.testing.assert_array_equal(pred, want[i][1])
+    # the plain call still works behind the pipelined ones (and after a device-resident one)
+    probs, pred = gnet.forward_host(*batches[1])
+    np.testing.assert_array_equal(probs, want[1][0])
+    assert abi.conv_tc_take_error() == 0
