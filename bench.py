@@ -194,7 +194,7 @@ def run_reference(args, scn):
     line = dict(impl="reference", metric=METRIC, value=v, unit="samples/s", n_gpus=args.gpus, steps=args.steps,
                 warmup=args.warmup, ms_per_step=1000.0 * wall / args.steps, higher_is_better=True, scaling="weak",
                 vs_baseline=None, dtype="f32", data="synthetic",
-                config=dict(workload=WORKLOAD, step="one CPU forward of a bounded sample of %d samples" % n),
+                config=dict(workload=WORKLOAD), step="one CPU forward of a bounded sample of %d samples (one batch)" % n,
                 cpu_baseline=dict(value=v, unit="samples/s", cores=threads, kind="port",
                                   sample="%d samples per step, %d steps; the reference's host rule construction and "
                                          "layer semantics restated in C++ (oracle), std::thread over samples" % (n, args.steps)),
