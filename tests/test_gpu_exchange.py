@@ -127,6 +127,43 @@ def test_sharded_forward_delivers_every_ranks_results_one_step_later(scn, abi, o
         n.exchange_destroy()
 
 
+def test_two_halves_entry_point_with_exchange(scn, abi, oracle):
+    """forward_host_begin / forward_host_end(exchange=True) on two emulated ranks: uploads one batch ahead, results of the
+    other rank one step later."""
+    cfg, world, per = 2, 2, 5
+    c = scn.synth.CONFIGS[cfg]
+    nets = [make_pair(scn, oracle, cfg)[0] for _ in range(world)]
+    for r, n in enumerate(nets):
+        n.exchange_create(world, r, per)
+    bufs = [n.exchange_buffer() for n in nets]
+    for n in nets:
+        n.exchange_connect_local(bufs)
+    steps = 4
+    data = [[c["gen"](per - (s + r) % 2, first=(s * world + r) * per) for s in range(steps)] for r in range(world)]
+    want = [[nets[r].forward_host(*data[r][s])[0] for s in range(steps)] for r in range(world)]
+    for r in range(world):
+        nets[r].forward_host_begin(*data[r][0])
+    for s in range(steps):
+        for r in range(world):
+            if s + 1 < steps:
+                nets[r].forward_host_begin(*data[r][s + 1])
+            probs, _, gathered, rows = nets[r].forward_host_end(True)
+            np.testing.assert_array_equal(probs, want[r][s])
+            if s == 0:
+                assert rows.tolist() == [-1] * world
+            else:
+                assert rows.tolist() == [len(want[q][s - 1]) for q in range(world)]
+                for q in range(world):
+                    np.testing.assert_array_equal(gathered[q, : rows[q]], want[q][s - 1])
+    for r in range(world):
+        gathered, rows = nets[r].exchange_flush()
+        for q in range(world):
+            np.testing.assert_array_equal(gathered[q, : rows[q]], want[q][steps - 1])
+    torch.cuda.synchronize()
+    for n in nets:
+        n.exchange_destroy()
+
+
 def test_device_resident_steps_deliver_one_step_later(scn, abi, oracle):
     """The device-resident form (exchange kernel beside the network's stream): two emulated ranks, three steps and the
     collect-only call that ends the run."""
