@@ -213,6 +213,36 @@ def build_pair_cpu_only(scn):
     return None, onet
 
 
+def training_side_measurement(scn, n_steps):
+    """Outside every timed leg: a few training steps (forward, softmax gradient, every layer's backwards, momentum update;
+    host buffers in, probabilities out) of the same layer sequence without dropout (dropout masks while training are not
+    built), timed by wall clock around the synchronous call."""
+    c = scn.synth.CONFIGS[CFG]
+    net = scn.net.Net(c["dim"], c["nIn"], c["nClasses"], 1, c["lattice"])
+    w, L = c["widths"], len(c["widths"]) - 1
+    for i, nf in enumerate(w):
+        fs = c.get("first_filter", 3) if i == 0 else 2
+        pool = not (c["tail"] == "conv" and i == L)
+        net.addLeNetLayerMP(nf, fs, 1, 2 if pool else 1, 2 if pool else 1, scn.synth.VLEAKYRELU, 0.0, 1)
+    if c["tail"] == "terminal":
+        net.addTerminalPoolingLayer(c["terminal"])
+    net.addSoftmaxLayer()
+    for i, (W, B, pr) in scn.synth.init_weights(net.layers()).items():
+        net.set_weights(i, W, B, pr)
+    keys, off, feats = c["gen"](BATCH_PER_GPU)
+    labels = (np.arange(BATCH_PER_GPU) % c["nClasses"]).astype(np.int32)
+    nll, ms = [], []
+    for j in range(n_steps + 1):  # the first step allocates the gradient buffers
+        t0 = time.time()
+        _, stats = net.train_batch(keys, off, feats, labels, 1e-8, 0.9)  # (a rate small enough for the summed, unnormalised gradients of 256 samples)
+        ms.append((time.time() - t0) * 1e3)
+        nll.append(stats["nll"] / BATCH_PER_GPU)
+    best = min(ms[1:])
+    return dict(ms_per_step=best, samples_per_s=BATCH_PER_GPU / (best * 1e-3), steps=n_steps, nll_per_sample=[round(v, 4) for v in nll],
+                what="forward + backward + update of the same layers without dropout on one batch repeated, tf32 operands (three products), "
+                     "host buffers, wall clock; the weight-gradient kernels are fp32 CUDA-core kernels that no performance work has touched")
+
+
 def relerr(a, b):
     return float(np.abs(a - b).max() / max(float(np.abs(b).max()), 1e-30))
 
@@ -262,6 +292,7 @@ def main():
     ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 4, 5],
                     help="synthetic configuration (2 = the headline workload; the others are side measurements)")
     ap.add_argument("--batch", type=int, default=0, help="samples per GPU (0 = the configuration's own batch size, at most 256)")
+    ap.add_argument("--train-steps", type=int, default=3, help="training steps of the side measurement (0 = skip it)")
     ap.add_argument("--legs", type=int, default=LEGS, help="how often each timed leg is repeated (the median leg is reported)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
@@ -555,6 +586,13 @@ def main():
     all_flops = sum(d["flops"] for d in per_layer)
     conv_ms = sum(d["ms"] for d in per_layer if d["kernel"] != "maxpool_rules")
 
+    training = None
+    if rank == 0 and args.train_steps > 0:
+        try:
+            with torch.cuda.stream(stream):
+                training = training_side_measurement(scn, args.train_steps)
+        except Exception as e:  # a side measurement must not take the benchmark line with it
+            training = dict(unavailable=str(e))
     if rank == 0:
         cpu, parity = None, None
         if args.cpu_seconds > 0:
@@ -578,7 +616,7 @@ def main():
             e2e=dict(value=total / (ms_e2e * 1e-3), unit="samples/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                      call="scn_net_forward_host_begin / _end: each step starts the copies of the next batch, then computes and returns the current one",
                      ms_per_step=ms_e2e / steps),
-            gpu_launches=int(launches), roofline=roof, cpu_baseline=cpu, parity=parity, clocks=clocks,
+            gpu_launches=int(launches), roofline=roof, cpu_baseline=cpu, parity=parity, clocks=clocks, training_step=training,
             pooling_roofline=(dict(bound="hbm", kernel="k_maxpool layer %d" % pool_top["layer"], achieved=pool_top["bytes"] / (pool_top["ms"] * 1e-3) / 1e9,
                                    peak=peaks["hbm_gbs"], unit="GB/s", frac=pool_top["bytes"] / (pool_top["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"])
                               if pool_top else None),
