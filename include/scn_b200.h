@@ -375,6 +375,16 @@ int scn_activation_backward(const float *d_out_features, float *d_dfeatures, int
 int scn_conv_nin_backward_weights(const float *d_in, const int *d_rules, int rows, int fs, int nIn,
                                   const float *d_dout, int N, float *d_dW, float *d_dB, scn_stream_t stream);
 
+/* The same weight gradient on the tensor cores (three tf32 products): the gathered input is written once, transposed,
+ * the output gradient is packed like a weight matrix, and the fused forward kernel multiplies them with the roles
+ * turned (its rows = the fs*nIn input channels, its contraction = the layer's rows), K split over the CTAs.
+ * Workspace: scn_conv_nin_backward_weights_tc_bytes (0: shape not taken -- fewer than 128 rows, N below 16 or not a
+ * multiple of 4 --, for which the call answers SCN_ERR_UNSUPPORTED: use scn_conv_nin_backward_weights). */
+size_t scn_conv_nin_backward_weights_tc_bytes(int rows, int fs, int nIn, int N);
+int scn_conv_nin_backward_weights_tc(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const float *d_dout,
+                                     int N, float *d_dW, float *d_dB, void *d_workspace, size_t workspace_bytes,
+                                     scn_stream_t stream);
+
 /* d_Wt[N x K] = transpose of d_W[K x N].  The input half of NetworkInNetworkLayer::backwards
  * (NetworkInNetworkLayer.cu:266-277: dX = d W^T) is scn_conv_nin_forward_ws on d_dout with
  * these transposed weights (zero bias, no activation), so it runs on the tensor cores

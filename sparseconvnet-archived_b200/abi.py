@@ -24,7 +24,7 @@ EXPORTS = [
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_conv_tc_error_word", "scn_classifier_result_bytes", "scn_classifier_result", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
     "scn_exchange_buffer_bytes", "scn_exchange_set_timeout_ms", "scn_exchange_alloc", "scn_exchange_free", "scn_exchange_open", "scn_exchange_close", "scn_exchange_publish", "scn_exchange_collect", "scn_exchange_step",
-    "scn_softmax_nll_backward", "scn_activation_backward", "scn_conv_nin_backward_weights", "scn_transpose_weights", "scn_gather_backward",
+    "scn_softmax_nll_backward", "scn_activation_backward", "scn_conv_nin_backward_weights", "scn_conv_nin_backward_weights_tc_bytes", "scn_conv_nin_backward_weights_tc", "scn_transpose_weights", "scn_gather_backward",
     "scn_maxpool_backward", "scn_terminal_pool_backward", "scn_sgd_update",
 ]
 
@@ -466,6 +466,25 @@ def conv_nin_backward_weights(feat, rules, fs, dout):
     dB = torch.empty(N, dtype=torch.float32, device=dout.device)
     check(lib().scn_conv_nin_backward_weights(_ptr(_f32(feat)), None if rules is None else _ptr(_i32(rules)), rows, fs if rules is not None else 1,
                                               nIn, _ptr(_f32(dout)), N, _ptr(dW), _ptr(dB), _stream()))
+    return dW, dB
+
+
+def conv_nin_backward_weights_tc(feat, rules, fs, dout):
+    """The same on the tensor cores -> (dW, dB); raises ScnError (unsupported configuration) for shapes it does not take."""
+    nIn = feat.shape[1]
+    rows, N = dout.shape
+    f = fs if rules is not None else 1
+    K = f * nIn
+    L = lib()
+    L.scn_conv_nin_backward_weights_tc_bytes.restype = c_sz
+    nbytes = L.scn_conv_nin_backward_weights_tc_bytes(rows, f, nIn, N)
+    if not nbytes:
+        raise ScnError("unsupported configuration: the tensor-core weight gradient does not take rows=%d N=%d" % (rows, N))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dout.device)
+    dW = torch.empty((K, N), dtype=torch.float32, device=dout.device)
+    dB = torch.empty(N, dtype=torch.float32, device=dout.device)
+    check(L.scn_conv_nin_backward_weights_tc(_ptr(_f32(feat)), None if rules is None else _ptr(_i32(rules)), rows, f, nIn, _ptr(_f32(dout)), N,
+                                             _ptr(dW), _ptr(dB), _ptr(ws), c_sz(nbytes), _stream()))
     return dW, dB
 
 

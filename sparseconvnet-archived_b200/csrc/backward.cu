@@ -5,6 +5,7 @@
 // to a learnt layer's input is its forward kernel run on the transposed weights (scn_conv_nin_forward_ws),
 // so it takes the tensor-core path wherever the forward does.
 #include "scn_common.cuh"
+#include "conv_nin_tc.cuh"
 #include <algorithm>
 
 namespace scn {
@@ -206,6 +207,74 @@ __global__ void k_sgd_update(float *__restrict__ w, float *__restrict__ m, const
   }
 }
 
+// ---- the weight gradient on the tensor cores: dW[K x N] = Xg^T[K x rows] * d[rows x N] is the forward kernel's product with
+// the roles turned: its "rows" are the K gathered input channels, its contraction runs over the layer's rows, its
+// "weights" are the output gradient.  The gathered input is written once, transposed ([Kp x rowsP], Kp and rowsP padded
+// with zeros to whole tiles and whole slabs), the gradient is packed like a weight matrix, and the fused kernel
+// (three tf32 products, K split over the CTAs, partial sums added in a fixed order) does the rest.
+constexpr int GT_TILE = 32;
+// out[k][r] = X[r][k] for the gathered input X (row r of a convolution's input matrix: cell f = k / nIn of the rule row,
+// channel k % nIn), zero where the rule is negative and in the padding.  32 x 32 tiles through shared memory: reads run
+// along the channels, writes along the rows.
+__global__ void __launch_bounds__(256) k_gather_transpose(const float *__restrict__ in, const int *__restrict__ rules, int rows, int fs, int nIn,
+                                                          int K, int rowsP, float *__restrict__ out) {
+  __shared__ float tile[GT_TILE][GT_TILE + 1];
+  const int tx = threadIdx.x, ty = threadIdx.y; // 32 x 8
+  const long long r0 = (long long)blockIdx.x * GT_TILE;
+  const int k0 = blockIdx.y * GT_TILE;
+  const int k = k0 + tx;
+  const int f = k < K ? k / nIn : 0, c = k - f * nIn;
+#pragma unroll
+  for (int j = 0; j < GT_TILE; j += 8) {
+    const long long r = r0 + ty + j;
+    float v = 0.f;
+    if (r < rows && k < K) {
+      const int src = rules ? __ldg(rules + r * fs + f) : (int)r;
+      if (src >= 0) v = __ldg(in + (long long)src * nIn + c);
+    }
+    tile[ty + j][tx] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < GT_TILE; j += 8) {
+    const int kk = k0 + ty + j;
+    out[(long long)kk * rowsP + r0 + tx] = tile[tx][ty + j]; // (the grid covers exactly Kp x rowsP)
+  }
+}
+// db[n] += sum over a chunk of rows of d[r][n]
+__global__ void __launch_bounds__(256) k_column_sums(const float *__restrict__ d, int rows, int N, int rowsPerChunk, float *__restrict__ db) {
+  __shared__ float part[8][33];
+  const int tx = threadIdx.x, ty = threadIdx.y, n = blockIdx.x * 32 + tx;
+  const long long rBegin = (long long)blockIdx.y * rowsPerChunk, rEnd = min((long long)rows, rBegin + rowsPerChunk);
+  float acc = 0.f;
+  if (n < N)
+    for (long long r = rBegin + ty; r < rEnd; r += 8) acc += __ldg(d + r * N + n);
+  part[ty][tx] = acc;
+  __syncthreads();
+  if (ty == 0 && n < N) {
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sum += part[j][tx];
+    atomicAdd(db + n, sum);
+  }
+}
+struct WeightGradPlan { int K, Kp, rowsP; size_t gatheredBytes, packedBytes, splitBytes, biasBytes, outBytes, total; bool ok; };
+WeightGradPlan plan_weight_grad(int rows, int fs, int nIn, int N) {
+  WeightGradPlan p = {};
+  p.K = fs * nIn;
+  p.Kp = (p.K + 127) / 128 * 128;
+  p.rowsP = (rows + 31) / 32 * 32;
+  p.ok = rows >= 128 && N >= 16 && N % 4 == 0 && (long long)p.Kp * p.rowsP < (1ll << 40);
+  if (!p.ok) return p;
+  p.gatheredBytes = align_up(sizeof(float) * (size_t)p.Kp * p.rowsP, 256);
+  p.packedBytes = align_up(tc_packed_bytes(rows, N, SCN_PREC_3XTF32), 256);
+  p.splitBytes = align_up(tc_workspace_bytes(p.Kp, 1, p.rowsP, N, SCN_PREC_3XTF32), 256);
+  p.biasBytes = align_up(sizeof(float) * (size_t)N, 256);
+  p.outBytes = p.Kp == p.K ? 0 : align_up(sizeof(float) * (size_t)p.Kp * N, 256); // the product's rows for the padded channels need a place
+  p.ok = p.packedBytes > 0;
+  p.total = p.gatheredBytes + p.packedBytes + p.splitBytes + p.biasBytes + p.outBytes;
+  return p;
+}
 } // namespace
 } // namespace scn
 
@@ -269,6 +338,50 @@ extern "C" int scn_conv_nin_backward_weights(const float *d_in, const int *d_rul
   if (d_rules) k_backward_weights<true><<<grid, 256, 0, s>>>(d_in, d_rules, rows, fs, nIn, d_dout, N, d_dW, d_dB, rowsPerChunk);
   else k_backward_weights<false><<<grid, 256, 0, s>>>(d_in, nullptr, rows, 1, nIn, d_dout, N, d_dW, d_dB, rowsPerChunk);
   SCN_LAUNCH_CHECK("k_backward_weights");
+  return SCN_OK;
+}
+
+
+extern "C" size_t scn_conv_nin_backward_weights_tc_bytes(int rows, int fs, int nIn, int N) {
+  if (rows < 1 || fs < 1 || nIn < 1 || N < 1) return 0;
+  const WeightGradPlan p = plan_weight_grad(rows, fs, nIn, N);
+  return p.ok ? p.total : 0;
+}
+
+extern "C" int scn_conv_nin_backward_weights_tc(const float *d_in, const int *d_rules, int rows, int fs, int nIn, const float *d_dout, int N,
+                                                float *d_dW, float *d_dB, void *d_workspace, size_t workspace_bytes, scn_stream_t stream) {
+  clear_error();
+  if (rows < 1 || fs < 1 || nIn < 1 || N < 1) return fail(SCN_ERR_INVALID, "bad conv/NiN sizes");
+  if (!d_rules && fs != 1) return fail(SCN_ERR_INVALID, "fs must be 1 without rules");
+  if (!d_in || !d_dout || !d_dW || !d_workspace) return fail(SCN_ERR_INVALID, "null pointer");
+  const WeightGradPlan p = plan_weight_grad(rows, fs, nIn, N);
+  if (!p.ok) return fail(SCN_ERR_UNSUPPORTED, "weight gradient: shape not taken by the tensor-core form (few rows, or N not a multiple of 4 or below 16)");
+  if (workspace_bytes < p.total) return fail(SCN_ERR_WORKSPACE, "workspace smaller than scn_conv_nin_backward_weights_tc_bytes()");
+  if (((uintptr_t)d_workspace | (uintptr_t)d_dout | (uintptr_t)d_dW) & 15) return fail(SCN_ERR_INVALID, "weight gradient: buffers must be 16-byte aligned");
+  cudaStream_t s = (cudaStream_t)stream;
+  char *w = (char *)d_workspace;
+  float *gatheredT = (float *)w;
+  void *packed = w + p.gatheredBytes;
+  void *split = p.splitBytes ? w + p.gatheredBytes + p.packedBytes : nullptr;
+  float *zeroBias = (float *)(w + p.gatheredBytes + p.packedBytes + p.splitBytes);
+  SCN_CUDA_TRY(cudaMemsetAsync(zeroBias, 0, sizeof(float) * N, s));
+  k_gather_transpose<<<dim3(p.rowsP / GT_TILE, p.Kp / GT_TILE), dim3(32, 8), 0, s>>>(d_in, d_rules, rows, fs, nIn, p.K, p.rowsP, gatheredT);
+  SCN_LAUNCH_CHECK("k_gather_transpose");
+  int rc = tc_pack(d_dout, rows, N, SCN_PREC_3XTF32, packed, s);
+  if (rc != SCN_OK) return rc;
+  // "rows" = Kp input channels (whole tiles: no tile row is missing), one "input row" per channel of length rowsP
+  float *product = p.outBytes ? (float *)(w + p.gatheredBytes + p.packedBytes + p.splitBytes + p.biasBytes) : d_dW;
+  rc = tc_launch(gatheredT, nullptr, p.Kp, 1, p.rowsP, packed, zeroBias, nullptr, N, 1.0f, SCN_NOSIGMOID, SCN_PREC_3XTF32, product, split, p.splitBytes, s);
+  if (rc == SCN_OK && p.outBytes) SCN_CUDA_TRY(cudaMemcpyAsync(d_dW, product, sizeof(float) * (size_t)p.K * N, cudaMemcpyDeviceToDevice, s));
+  if (rc != SCN_OK) return rc;
+  if (d_dB) {
+    SCN_CUDA_TRY(cudaMemsetAsync(d_dB, 0, sizeof(float) * N, s));
+    int chunks = std::max(1, std::min(4 * sm_count() / std::max(1, (N + 31) / 32), (rows + 255) / 256));
+    const int rowsPerChunk = (rows + chunks - 1) / chunks;
+    chunks = (rows + rowsPerChunk - 1) / rowsPerChunk;
+    k_column_sums<<<dim3((N + 31) / 32, chunks), dim3(32, 8), 0, s>>>(d_dout, rows, N, rowsPerChunk, d_dB);
+    SCN_LAUNCH_CHECK("k_column_sums");
+  }
   return SCN_OK;
 }
 

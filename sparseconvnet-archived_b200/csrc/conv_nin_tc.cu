@@ -1463,7 +1463,9 @@ int tc_launch(const float *d_in, const int *d_rules, int rows, int fs, int nIn, 
   if (pool) rows *= pool_cells;
   const bool ok = N % 4 == 0 && (passes ? make_tiling16(fs * nIn, N, fs, d_rules != nullptr, passes, &t, &rawEntries, &nStages64)
                                         : is_split(precision) && make_tiling(fs * nIn, N, fs, d_rules != nullptr, &t, precision == SCN_PREC_SPLIT, false, pool));
-  if (!ok || (nIn % SLAB == 0 && nIn > ZERO_ROW_FLOATS)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
+  // (a row longer than the zero row is fine where no tile row can be missing: no rules and whole tiles of real rows)
+  const bool noMissingRows = !d_rules && !pool && !d_rows && rows % BM == 0;
+  if (!ok || (nIn % SLAB == 0 && nIn > ZERO_ROW_FLOATS && !noMissingRows)) return fail(SCN_ERR_UNSUPPORTED, "shape not supported by the tensor-core kernel");
   if (((uintptr_t)d_in | (uintptr_t)d_out | (uintptr_t)d_packed) & 15) return fail(SCN_ERR_INVALID, "tensor-core path needs 16-byte aligned buffers");
   Params P;
   const int mTiles = (rows + BM - 1) / BM;

@@ -786,7 +786,18 @@ void NetworkInNetworkLayer::backwards(SpatiallySparseBatch &batch, SpatiallySpar
   }
   dw.copyToGPU(); db.copyToGPU();
   dw.resize(K * N); db.resize(N);
-  scnSafeCall(scn_conv_nin_backward_weights(src, rules, rows, fs, nIn, d, N, dw.dPtr(), db.dPtr(), s));
+  // the weight gradient: on the tensor cores (three tf32 products, the forward kernel with the roles turned) where the
+  // shape has a form for it and the layer does not ask for plain fp32, else the CUDA-core kernel
+  bool onTensorCores = false;
+  if (precision != SCN_PREC_FP32 && rows > 0) {
+    const size_t need = scn_conv_nin_backward_weights_tc_bytes(rows, fs, nIn, N);
+    if (need) {
+      const int st = scn_conv_nin_backward_weights_tc(src, rules, rows, fs, nIn, d, N, dw.dPtr(), db.dPtr(), memStream.deviceScratch(need), need, s);
+      if (st == SCN_OK) onTensorCores = true;
+      else if (st != SCN_ERR_UNSUPPORTED) scnSafeCall(st);
+    }
+  }
+  if (!onTensorCores) scnSafeCall(scn_conv_nin_backward_weights(src, rules, rows, fs, nIn, d, N, dw.dPtr(), db.dPtr(), s));
   if (input.backpropErrors && rows > 0) {
     Wt.copyToGPU();
     Wt.resize(K * N);

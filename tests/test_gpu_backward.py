@@ -73,6 +73,39 @@ def test_conv_nin_backward_weights(abi, oracle, rows_in, rows, fs, nIn, N):
     assert relerr(gdB.cpu().numpy(), wdB) < TOL
 
 
+@pytest.mark.parametrize("rows_in,rows,fs,nIn,N", [
+    (300, 257, 9, 3, 32), (500, 1000, 4, 96, 192), (200, 513, 27, 1, 32), (90, 177, 4, 50, 100), (3000, 5000, 8, 32, 64),
+    (2000, 3000, 1, 70, 36), (256, 256, 1, 2048, 608), (20000, 40000, 4, 96, 192), (9000, 70001, 9, 3, 96),
+])
+def test_conv_nin_backward_weights_on_tensor_cores(abi, oracle, rows_in, rows, fs, nIn, N):
+    """The same gradient as the forward kernel's product with the roles turned (gathered input transposed, gradient packed
+    as the weight operand, contraction over the rows split over the CTAs): within 1e-4 of the largest entry."""
+    rng = np.random.default_rng(rows + N)
+    feat = rng.standard_normal((rows_in, nIn)).astype(np.float32)
+    d = rng.standard_normal((rows if fs > 1 else rows_in, N)).astype(np.float32)
+    if fs > 1:
+        rules = rng.integers(0, rows_in, size=(rows, fs)).astype(np.int32)
+        rules[rng.random(rules.shape) < 0.1] = -1
+        X = oracle.gather(feat, rules, nIn).reshape(rows, fs * nIn)
+        drules = dev(rules).flatten()
+    else:
+        X, drules = feat, None
+    wdW = (X.astype(np.float64).T @ d.astype(np.float64)).astype(np.float32)
+    wdB = d.astype(np.float64).sum(axis=0).astype(np.float32)
+    gdW, gdB = abi.conv_nin_backward_weights_tc(dev(feat), drules, fs, dev(d))
+    assert abi.conv_tc_take_error() == 0
+    assert relerr(gdW.cpu().numpy(), wdW) < TOL
+    assert relerr(gdB.cpu().numpy(), wdB) < TOL
+    sdW, sdB = abi.conv_nin_backward_weights(dev(feat), drules, fs, dev(d))  # the CUDA-core form agrees
+    assert relerr(gdW.cpu().numpy(), sdW.cpu().numpy()) < TOL
+
+
+def test_tensor_core_weight_gradient_refuses_small_shapes(abi):
+    feat, d = torch.zeros((64, 32), device="cuda"), torch.zeros((64, 10), device="cuda")
+    with pytest.raises(abi.ScnError):
+        abi.conv_nin_backward_weights_tc(feat, None, 1, d)
+
+
 @pytest.mark.parametrize("precision", ["FP32", "3XTF32"])
 @pytest.mark.parametrize("rows,K,N", [(1000, 384, 192), (300, 96, 32), (256, 608, 10), (5000, 1152, 416)])
 def test_input_gradient_is_the_forward_kernel_on_transposed_weights(abi, oracle, rows, K, N, precision):
