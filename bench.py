@@ -240,7 +240,8 @@ def training_side_measurement(scn, n_steps):
     best = min(ms[1:])
     return dict(ms_per_step=best, samples_per_s=BATCH_PER_GPU / (best * 1e-3), steps=n_steps, nll_per_sample=[round(v, 4) for v in nll],
                 what="forward + backward + update of the same layers without dropout on one batch repeated, tf32 operands (three products), "
-                     "host buffers, wall clock; the weight-gradient kernels are fp32 CUDA-core kernels that no performance work has touched")
+                     "host buffers, wall clock; weight gradients through the fused tensor-core kernel with the roles turned (gathered input transposed, "
+                     "gradient packed as the weight operand), input gradients through the same kernel on the transposed weights")
 
 
 def relerr(a, b):
