@@ -1285,7 +1285,7 @@ int choose_ksplit(int tiles, int nSlabs, long long rows, int N, size_t wsBytes) 
   if (tiles * 2 > sms || nSlabs < 8) return 1;
   int k = sms / tiles;
   if (k > nSlabs / 4) k = nSlabs / 4;
-  if (k > 32) k = 32;
+  if (k > 128) k = 128;
   while (k > 1 && (size_t)k * rows * N * sizeof(float) > wsBytes) --k;
   return k < 2 ? 1 : k;
 }
