@@ -87,6 +87,10 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *h_keys, const int
  * stay in the order given.  Networks with dropout are refused. */
 int scn_net_train_batch(scn_net_t *net, int batch, const int *h_keys, const int *h_off, const float *h_features, const int *h_labels,
                         float learningRate, float momentum, float *h_probs, double *stats);
+/* One RESCALEBATCH through processBatch (SparseConvNetCUDA.cu:230-240): every layer's forwards followed by its
+ * scaleWeights (NetworkInNetworkLayer.cu:203-220: weights and biases scaled by the -0.1th power of the layer's mean
+ * absolute output, the scale applied underneath divided out again, the top layer left alone). */
+int scn_net_rescale_batch(scn_net_t *net, int batch, const int *keys, const int *off, const float *features);
 /* A learnt layer's weights as they are now (W [nIn x nOut], B [nOut], PReLU slopes [nOut] or NULL). */
 int scn_net_get_weights(scn_net_t *net, int layer, float *h_W, float *h_B, float *h_prelu);
 /* d cost / d features of interface i after scn_net_train_batch: returns their count (-1 on

@@ -424,6 +424,23 @@ float *NetworkInNetworkLayer::slopes() { return nullptr; }
 float *NetworkInNetworkLayer::slopeGradient() { return nullptr; }
 void NetworkInNetworkLayer::updateSlopes(float, float) {}
 void NetworkInNetworkLayer::weightsChanged() { packedPrecision = -100; }
+// NetworkInNetworkLayer.cu:203-220 (and NetworkInNetworkPReLULayer.cu:175-191, the same): after this layer's forwards on
+// a RESCALEBATCH, weights and biases are scaled so that the mean absolute output moves towards 1 (by its -0.1th power)
+// and the scale applied underneath is taken out of the weights again; the top layer is left at scale 1.
+void NetworkInNetworkLayer::scaleWeights(SpatiallySparseBatchInterface &, SpatiallySparseBatchInterface &output, float &scalingUnderneath, bool topLayer) {
+  if (output.sub->features.size() == 0) throw ScnException("scaleWeights: call after forwards() on a RESCALEBATCH");
+  cudaSafeCall(cudaStreamSynchronize(memStream.stream));
+  float scale = output.sub->features.meanAbs();
+  if (scale != scale) throw ScnException("scaleWeights: the layer's output holds a NaN");
+  std::cout << "featureScale:" << scale << std::endl;
+  scale = topLayer ? 1.0f : std::pow(scale, -0.1f);
+  W.multiplicativeRescale(scale / scalingUnderneath);
+  B.multiplicativeRescale(scale);
+  MW.multiplicativeRescale(scale / scalingUnderneath);
+  MB.multiplicativeRescale(scale);
+  scalingUnderneath = scale;
+  weightsChanged();
+}
 const void *NetworkInNetworkLayer::packedWeights(int fs, int nIn, int prec) {
   if (prec == SCN_PREC_FP32) return nullptr;
   size_t need = scn_conv_packed_weight_bytes(nFeaturesIn, nFeaturesOut, prec);
@@ -469,7 +486,7 @@ void NetworkInNetworkLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySpa
 }
 bool NetworkInNetworkLayer::forwardsEarly(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &source, SpatiallySparseBatchInterface &input,
                                           SpatiallySparseBatchInterface &output, int cells, long long rowsBound, const int *d_rows) {
-  if (batch.type == TRAINBATCH || rowsBound < 1 || rowsBound * (long long)nFeaturesOut > INT_MAX) return false;
+  if (batch.type == TRAINBATCH || batch.type == RESCALEBATCH || rowsBound < 1 || rowsBound * (long long)nFeaturesOut > INT_MAX) return false;
   const int sp = splitPrecision(precision, batch);
   if (sp < 0) return false;
   if (fn == SOFTMAX || nFeaturesOut % 4 != 0 || nFeaturesIn % cells != 0) return false;
@@ -494,7 +511,7 @@ void NetworkInNetworkLayer::finishEarly(SpatiallySparseBatchInterface &input, Sp
 bool NetworkInNetworkLayer::forwardsPooled(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &source, SpatiallySparseBatchInterface &input,
                                            SpatiallySparseBatchInterface &poolOutput, int convCells, int poolCells, long long rowsPoolBound,
                                            const int *d_rowsPool, int rowsUnpooled) {
-  if (batch.type == TRAINBATCH || rowsPoolBound < 1 || rowsPoolBound * (long long)nFeaturesOut > INT_MAX) return false;
+  if (batch.type == TRAINBATCH || batch.type == RESCALEBATCH || rowsPoolBound < 1 || rowsPoolBound * (long long)nFeaturesOut > INT_MAX) return false;
   const int sp = splitPrecision(precision, batch);
   if (sp < 0) return false;
   if (fn == SOFTMAX || nFeaturesOut % 4 != 0 || nFeaturesIn % convCells != 0) return false;
@@ -521,7 +538,7 @@ bool NetworkInNetworkLayer::forwardsPooled(SpatiallySparseBatch &batch, Spatiall
 }
 bool NetworkInNetworkLayer::forwardsWithNext(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
                                              NetworkInNetworkLayer &next, SpatiallySparseBatchInterface &nextOutput) {
-  if (batch.type == TRAINBATCH || fusePoolNext || next.fusePoolNext) return false;
+  if (batch.type == TRAINBATCH || batch.type == RESCALEBATCH || fusePoolNext || next.fusePoolNext) return false;
   const int sp = splitPrecision(precision, batch);
   if (sp < 0) return false;
   if (next.precision != SCN_PREC_AUTO && next.precision != SCN_PREC_FP32) return false;
@@ -557,7 +574,7 @@ bool NetworkInNetworkLayer::forwardsWithNext(SpatiallySparseBatch &batch, Spatia
   return true;
 }
 void NetworkInNetworkLayer::forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
-  if (fusePoolNext && input.deferredFrom && batch.type != TRAINBATCH) { // the pooling layer behind this one runs all three steps
+  if (fusePoolNext && input.deferredFrom && batch.type != TRAINBATCH && batch.type != RESCALEBATCH) { // the pooling layer behind this one runs all three steps
     output.deferredLearnt = this;
     output.deferredLearntInput = &input;
     countMultiplyAdds(input, output);

@@ -26,6 +26,7 @@ public:
   ~NetworkInNetworkLayer();
   void preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
   void forwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output);
+  void scaleWeights(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float &scalingUnderneath, bool topLayer) override;
   void backwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float learningRate,
                  float momentum);
   void loadWeightsFromStream(std::ifstream &f, bool momentum);

@@ -344,11 +344,21 @@ std::vector<float> SparseConvNetCUDA::layerTimes() {
   return ms;
 }
 
-// SparseConvNetCUDA.cu:227-271 without the rescaling branch: every layer's forwards, SoftmaxClassifier and, for a
-// TRAINBATCH, every layer's backwards in reverse order (each learnt layer updates its weights on the way).
+// SparseConvNetCUDA.cu:227-271: every layer's forwards (on a RESCALEBATCH each followed by its scaleWeights),
+// SoftmaxClassifier and, for a TRAINBATCH, every layer's backwards in reverse order (each learnt layer updates its
+// weights on the way).
 void SparseConvNetCUDA::processBatch(SpatiallySparseBatch &batch, float learningRate, float momentum, std::ofstream &f, std::ofstream &g) {
-  if (batch.type == RESCALEBATCH) throw ScnException("processBatch: the weight rescaling pass (RESCALEBATCH) is not built");
-  forwardLayers(batch);
+  if (batch.type == RESCALEBATCH) {
+    float scalingUnderneath = 1;
+    for (size_t i = 0; i < layers.size(); ++i) {
+      batch.interfaces[i + 1].sub->reset();
+      batch.interfaces[i + 1].deferredFrom = nullptr;
+      batch.interfaces[i + 1].deferredLearnt = nullptr;
+      layers[i]->forwards(batch, batch.interfaces[i], batch.interfaces[i + 1]);
+      layers[i]->scaleWeights(batch.interfaces[i], batch.interfaces[i + 1], scalingUnderneath, i + 1 == layers.size());
+    }
+  } else
+    forwardLayers(batch);
   SoftmaxClassifier(batch.interfaces.back(), batch, nTop, memStream);
   if (batch.type == TRAINBATCH)
     for (int i = (int)layers.size() - 1; i >= 0; --i) layers[i]->backwards(batch, batch.interfaces[i], batch.interfaces[i + 1], learningRate, momentum);

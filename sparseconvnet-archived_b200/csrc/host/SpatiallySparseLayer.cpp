@@ -2,9 +2,7 @@
 
 SpatiallySparseLayer::SpatiallySparseLayer(cudaMemStream &memStream) : memStream(memStream), changesGeometry(false) {}
 SpatiallySparseLayer::~SpatiallySparseLayer() {}
-void SpatiallySparseLayer::scaleWeights(SpatiallySparseBatchInterface &, SpatiallySparseBatchInterface &, float &, bool) {
-  throw ScnException("scaleWeights: the weight rescaling pass (RESCALEBATCH) is not built");
-}
+void SpatiallySparseLayer::scaleWeights(SpatiallySparseBatchInterface &, SpatiallySparseBatchInterface &, float &, bool) {} // SpatiallySparseLayer.cu:3-6
 void SpatiallySparseLayer::backwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &, SpatiallySparseBatchInterface &, float, float) {
   throw ScnException("backwards: this layer type has no backward pass");
 }

@@ -509,6 +509,19 @@ int scn_net_train_batch(scn_net_t *net, int batch, const int *keys, const int *o
   });
 }
 
+int scn_net_rescale_batch(scn_net_t *net, int batch, const int *keys, const int *off, const float *features) {
+  return guarded([&] {
+    Quiet q; // (every learnt layer prints its featureScale line, as the reference does)
+    SparseConvNetCUDA &cnn = *net->cnn;
+    SpatiallySparseBatch &b = uploadHostInput(net, batch, keys, off, features, RESCALEBATCH);
+    cnn.preprocessBatchOnDevice(b);
+    std::ofstream nof, nog;
+    cnn.processBatch(b, 0.f, 0.f, nof, nog);
+    net->last = &b;
+    cudaSafeCall(cudaStreamSynchronize(cnn.memStream.stream));
+  });
+}
+
 int scn_net_get_weights(scn_net_t *net, int layer, float *W, float *B, float *prelu) {
   return guarded([&] {
     auto n = dynamic_cast<NetworkInNetworkLayer *>(net->cnn->layers.at(layer));

@@ -21,7 +21,7 @@ EXPORTS = [
     "scn_net_layer_times", "scn_net_process_dataset", "scn_host_vectorTopIndices",
     "scn_net_exchange_create", "scn_net_exchange_buffer", "scn_net_exchange_connect", "scn_net_exchange_connect_local", "scn_net_exchange_destroy",
     "scn_net_forward_host_exchange", "scn_net_exchange_flush", "scn_net_exchange_step_device",
-    "scn_net_forward_host_begin", "scn_net_forward_host_end",
+    "scn_net_forward_host_begin", "scn_net_forward_host_end", "scn_net_rescale_batch",
 ]
 
 LAYER_KEYS = ("type", "size", "stride", "minActive", "nIn", "nOut", "fs", "act", "inSpatial", "outSpatial")
@@ -87,6 +87,7 @@ def lib():
         L.scn_net_exchange_flush.argtypes = [c_p, c_p, c_p]
         L.scn_net_exchange_step_device.argtypes = [c_p, c_p, c_int, c_p, c_p]
         L.scn_net_forward_host_begin.argtypes = [c_p, c_int, c_p, c_p, c_p]
+        L.scn_net_rescale_batch.argtypes = [c_p, c_int, c_p, c_p, c_p]
         L.scn_net_forward_host_end.argtypes = [c_p, c_p, c_p, c_p, c_p]
         _lib = L
     return _lib
@@ -316,6 +317,13 @@ class Net:
         stats = np.zeros(2, np.float64)
         _check(self.L.scn_net_train_batch(self.h, B, _np(keys), _np(off), _np(features), _np(labels), learning_rate, momentum, _np(probs), _np(stats)))
         return probs, dict(nll=float(stats[0]), mistakes=int(stats[1]))
+
+    def rescale_batch(self, keys, off, features):
+        """One RESCALEBATCH: every learnt layer's weights are rescaled from the statistics of its output on this batch."""
+        keys = np.ascontiguousarray(keys, np.int32)
+        off = np.ascontiguousarray(off, np.int32)
+        features = np.ascontiguousarray(features, np.float32)
+        _check(self.L.scn_net_rescale_batch(self.h, len(off) - 1, _np(keys), _np(off), _np(features)))
 
     def get_weights(self, i):
         L = self.layers()[i]

@@ -170,11 +170,6 @@ int main() {
     // ---- 5. what the library refuses
     {
       bool threw = false;
-      float scale = 1.f;
-      try { SpatiallySparseBatch &b = cnn.batchPool[0]; cnn.layers[1]->scaleWeights(b.interfaces[1], b.interfaces[2], scale, false); }
-      catch (const ScnException &) { threw = true; }
-      CHECK(threw); // the weight rescaling pass is not built
-      threw = false;
       try { cnn.loadWeights("/nonexistent/w", 1, false); } catch (const ScnException &) { threw = true; }
       CHECK(threw);
       std::printf("OK refusals\n");

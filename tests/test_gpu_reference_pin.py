@@ -219,3 +219,32 @@ def test_product_matches_reference_at_benchmark_batch(scn, abi, oracle, refgpu, 
             assert relerr(gf, r["features"]) < 1e-4, "pooled features of interface %d" % i
     assert relerr(gprobs, rprobs) < 1e-4
     np.testing.assert_array_equal(gpred, rpred)
+
+
+@pytest.mark.parametrize("cfg,batch", [(1, 8), (2, 6), (4, 4)])
+def test_rescale_batch_matches_the_reference(scn, abi, oracle, refgpu, tmp_path, cfg, batch):
+    """RESCALEBATCH (SparseConvNetCUDA.cu:230-240, NetworkInNetworkLayer.cu:203-220): after one such batch every learnt
+    layer's weights and biases equal the reference's; a forward afterwards gives the same probabilities."""
+    c = scn.synth.CONFIGS[cfg]
+    onet, ref, gnet, layers, weights = _triple(scn, oracle, refgpu, tmp_path, c["dim"], c["nIn"], c["nClasses"], c["lattice"],
+                                               lambda n: scn.synth.build_network(n, cfg), product=True)
+    keys, off, feats = c["gen"](batch)
+    onet.forward(keys, off, feats, keep=True)
+    assert rules_safe_for_reference_kernels(onet)
+    ref.forward(keys, off, feats, batch_type=3)  # RESCALEBATCH
+    gnet.rescale_batch(keys, off, feats)
+    assert abi.conv_tc_take_error() == 0
+    changed = False
+    for i, L in enumerate(layers):
+        if L["type"] != 2:
+            continue
+        rW, rB, _ = ref.layer_weights(i)
+        gW, gB, _ = gnet.get_weights(i)
+        assert relerr(gW, rW) < 1e-5, "weights of layer %d" % i
+        assert relerr(gB, rB) < 1e-5, "biases of layer %d" % i
+        changed = changed or relerr(gW, weights[i][0]) > 1e-3
+    assert changed  # the pass did rescale something
+    rprobs, rpred, _ = ref.forward(keys, off, feats)
+    gprobs, gpred = gnet.forward_host(keys, off, feats)
+    assert relerr(gprobs, rprobs) < 1e-4
+    np.testing.assert_array_equal(gpred, rpred)
