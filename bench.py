@@ -215,8 +215,7 @@ def build_pair_cpu_only(scn):
 
 def training_side_measurement(scn, n_steps):
     """Outside every timed leg: a few training steps (forward, softmax gradient, every layer's backwards, momentum update;
-    host buffers in, probabilities out) of the same layer sequence without dropout (dropout masks while training are not
-    built), timed by wall clock around the synchronous call."""
+    host buffers in, probabilities out) of the same layer sequence without dropout, timed by wall clock around the synchronous call."""
     c = scn.synth.CONFIGS[CFG]
     net = scn.net.Net(c["dim"], c["nIn"], c["nClasses"], 1, c["lattice"])
     w, L = c["widths"], len(c["widths"]) - 1

@@ -415,6 +415,17 @@ int scn_terminal_pool_backward(const float *d_dout, const int *d_rules, int batc
 int scn_sgd_update(float *d_w, float *d_momentum, const float *d_delta, long long n, float learningRate,
                    float momentum, int keep_positive, scn_stream_t stream);
 
+/* Training-time dropout (NetworkInNetworkLayer.cu:152-186, 240-263) with full-width matrices: instead of shrinking W, the
+ * features and the gradients to the features a batch keeps, the dropped features' columns are zeroed
+ * (scn_mask_columns: d_x[r][n] = 0 where d_mask[n] == 0) and the update skips the weights of dropped input and output
+ * features (scn_sgd_update_masked: entry (row, col) of d_w[rows x N] is updated like scn_sgd_update unless
+ * d_row_mask[row % row_period] == 0 or d_col_mask[col] == 0; either mask may be NULL).  The values the reference's narrow
+ * matrices hold are the same. */
+int scn_mask_columns(float *d_x, long long rows, int N, const float *d_mask, scn_stream_t stream);
+int scn_sgd_update_masked(float *d_w, float *d_momentum, const float *d_delta, long long rows, int N,
+                          const float *d_row_mask, int row_period, const float *d_col_mask, float learningRate,
+                          float momentum, int keep_positive, scn_stream_t stream);
+
 /* ------------------------------------------------------------------ result exchange between the GPUs of one node
  * The reference runs on one GPU (SparseConvNetCUDA.cu:43-71 picks a single device).  Sharded by sample over several
  * GPUs, the path has one exchange step: every rank's [rows x nClasses] block of probabilities (what

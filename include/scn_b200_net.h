@@ -84,9 +84,16 @@ int scn_net_forward_host(scn_net_t *net, int batch, const int *h_keys, const int
  * forward, SoftmaxClassifier (negative log-likelihood and mistakes into stats[0..1], the
  * probabilities into h_probs), every layer's backwards() in reverse order with the SGD update
  * of its weights (learningRate, momentum as in NetworkInNetworkLayer.cu:26-40).  The samples
- * stay in the order given.  Networks with dropout are refused. */
+ * stay in the order given.  A learnt layer with dropout d keeps floor(nOut (1 - d)) randomly drawn output features per
+ * batch (NetworkInNetworkLayer.cu:152-154): the others are zero in the forward pass and untouched by the update. */
 int scn_net_train_batch(scn_net_t *net, int batch, const int *h_keys, const int *h_off, const float *h_features, const int *h_labels,
                         float learningRate, float momentum, float *h_probs, double *stats);
+/* The output features learnt layer `layer` keeps in the training batches that follow, instead of a random draw: n
+ * ascending indices below its nFeaturesOut (n = 0: back to random draws).  For repeating a run with known subsets. */
+int scn_net_set_dropout_features(scn_net_t *net, int layer, const int *present, int n);
+/* The features interface i kept in the last batch (see above): returns their count, which is the interface's nFeatures
+ * unless it is a learnt layer's output in a training batch with dropout, and copies the indices if `present` is not NULL. */
+int scn_net_iface_present(scn_net_t *net, int i, int *present);
 /* One RESCALEBATCH through processBatch (SparseConvNetCUDA.cu:230-240): every layer's forwards followed by its
  * scaleWeights (NetworkInNetworkLayer.cu:203-220: weights and biases scaled by the -0.1th power of the layer's mean
  * absolute output, the scale applied underneath divided out again, the top layer left alone). */

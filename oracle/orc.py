@@ -137,6 +137,7 @@ class ReferenceGPU:
         L.refgpu_named.restype = c_p
         L.refgpu_named.argtypes = [ctypes.c_char_p, c_int, c_int, c_int, c_f, c_int, c_int, c_int, c_f, c_int]
         L.refgpu_seed_fmp.argtypes = [c_p, ctypes.c_uint]
+        L.refgpu_seed_dropout.argtypes = [c_p, ctypes.c_uint]
         L.refgpu_layer_describe.argtypes = [c_p, c_int, c_p]
         L.refgpu_destroy.argtypes = [c_p]
         L.refgpu_addLeNetLayerMP.argtypes = [c_p] + [c_int] * 6 + [c_f, c_int]
@@ -152,6 +153,7 @@ class ReferenceGPU:
         L.refgpu_last_cuda_error.restype = c_int
         L.refgpu_iface_sizes.argtypes = [c_p, c_int, c_p]
         L.refgpu_iface_fetch.argtypes = [c_p, c_int] + [c_p] * 6
+        L.refgpu_iface_features_present.argtypes = [c_p, c_int, c_p]
         L.refgpu_results.argtypes = [c_p] * 4
         L.refgpu_layer_weights.argtypes = [c_p, c_int, c_p, c_p, c_p]
         L.refgpu_sample_numbers.argtypes = [c_p, c_p]
@@ -167,6 +169,10 @@ class ReferenceGPU:
     def seed_fmp(self, seed):
         """Fractional max-pooling layer l draws from a generator seeded with seed + l from now on."""
         self.L.refgpu_seed_fmp(self.h, seed)
+
+    def seed_dropout(self, seed):
+        """Seed every learnt layer's dropout generator (seed + layer index): the subsets TRAINBATCHes draw then repeat."""
+        self.L.refgpu_seed_dropout(self.h, seed)
 
     def describe(self):
         """Per layer the ten ints {type, size, stride, minActive, nIn, nOut, multiplier, fn, inSize, outSize}."""
@@ -248,7 +254,10 @@ class ReferenceGPU:
         rk = np.zeros(rows, np.int64)
         self.L.refgpu_iface_fetch(self.h, i, _p(feat), _p(dfeat), _p(ch), _p(rules), _p(rk), None)
         w = nfp if nfp else nF
-        return dict(nSpatialSites=rows, nFeatures=nF, spatialSize=sp, featuresPresent=nfp,
+        present = np.zeros(nfp, np.int32)
+        if nfp:
+            self.L.refgpu_iface_features_present(self.h, i, _p(present))
+        return dict(nSpatialSites=rows, nFeatures=nF, spatialSize=sp, featuresPresent=nfp, present=present,
                     features=feat.reshape(-1, w) if nfeat == rows * w else feat,
                     dfeatures=dfeat.reshape(-1, w) if ndf == rows * w else dfeat,
                     choices=ch, rules=rules, row_keys=rk)

@@ -24,6 +24,16 @@
 #include <sstream>
 #include <string>
 #include <vector>
+#include <fstream>
+#include "SpatiallySparseLayer.h"
+#include "Rng.h"
+// The learnt layers keep the generator that draws their dropout subsets private and seed it from the clock
+// (NetworkInNetworkLayer.h:7-8, Rng.cpp:7-15).  This translation unit alone reads their two headers with the member
+// reachable, so that refgpu_seed_dropout can make a dropout test repeat; the reference's own files are compiled as they are.
+#define private public
+#include "NetworkInNetworkLayer.h"
+#include "NetworkInNetworkPReLULayer.h"
+#undef private
 #include "BatchProducer.h"
 #include "ConvolutionalLayer.h"
 #include "ConvolutionalTriangularLayer.h"
@@ -166,6 +176,15 @@ void refgpu_seed_fmp(void *p, unsigned seed) {
     else if (auto f = dynamic_cast<RandomNonOverlappingFractionalMaxPoolingLayer *>(L)) f->rng.gen.seed(seed + (unsigned)l);
   }
 }
+// The same for the generators the learnt layers draw their dropout subsets from.
+void refgpu_seed_dropout(void *p, unsigned seed) {
+  Handle *h = (Handle *)p;
+  for (size_t l = 0; l < h->cnn->layers.size(); ++l) {
+    SpatiallySparseLayer *L = h->cnn->layers[l];
+    if (auto f = dynamic_cast<NetworkInNetworkLayer *>(L)) f->rng.gen.seed(seed + (unsigned)l);
+    else if (auto f = dynamic_cast<NetworkInNetworkPReLULayer *>(L)) f->rng.gen.seed(seed + (unsigned)l);
+  }
+}
 int refgpu_n_layers(void *p) { return (int)((Handle *)p)->cnn->layers.size(); }
 int refgpu_input_spatial_size(void *p) { return ((Handle *)p)->cnn->inputSpatialSize; }
 // info: {isLearnt, nFeaturesIn, nFeaturesOut, fn, isPReLU}; dropout as the builder re-quantised it
@@ -293,6 +312,11 @@ void refgpu_iface_fetch(void *p, int i, float *features, float *dfeatures, int *
   }
   if (backgroundCols)
     for (size_t s = 0; s < I.grids.size(); ++s) backgroundCols[s] = I.grids[s].backgroundCol;
+}
+// The features interface i holds (featuresPresent: all of them except behind a learnt layer with dropout in a TRAINBATCH).
+void refgpu_iface_features_present(void *p, int i, int *out) {
+  Quiet q;
+  fetch(((Handle *)p)->batch->interfaces.at(i).featuresPresent, out);
 }
 // probabilities [batch x nClasses], predictions [batch x nTop], stats = {negativeLogLikelihood, mistakes}
 void refgpu_results(void *p, float *probs, int *pred, double *stats) {

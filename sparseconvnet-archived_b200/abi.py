@@ -24,7 +24,7 @@ EXPORTS = [
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_conv_tc_error_word", "scn_classifier_result_bytes", "scn_classifier_result", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
     "scn_exchange_buffer_bytes", "scn_exchange_set_timeout_ms", "scn_exchange_alloc", "scn_exchange_free", "scn_exchange_open", "scn_exchange_close", "scn_exchange_publish", "scn_exchange_collect", "scn_exchange_step",
-    "scn_softmax_nll_backward", "scn_activation_backward", "scn_conv_nin_backward_weights", "scn_conv_nin_backward_weights_tc_bytes", "scn_conv_nin_backward_weights_tc", "scn_transpose_weights", "scn_gather_backward",
+    "scn_mask_columns", "scn_sgd_update_masked", "scn_softmax_nll_backward", "scn_activation_backward", "scn_conv_nin_backward_weights", "scn_conv_nin_backward_weights_tc_bytes", "scn_conv_nin_backward_weights_tc", "scn_transpose_weights", "scn_gather_backward",
     "scn_maxpool_backward", "scn_terminal_pool_backward", "scn_sgd_update",
 ]
 
@@ -517,6 +517,21 @@ def terminal_pool_backward(dout, rules, S, rows_in):
 def sgd_update(w, m, d, lr, momentum, keep_positive=False):
     """In place on w and m."""
     check(lib().scn_sgd_update(_ptr(w), _ptr(m), _ptr(_f32(d)), c_ll(w.numel()), c_f(lr), c_f(momentum), int(keep_positive), _stream()))
+
+
+def mask_columns(x, mask):
+    """In place: x[r, n] = 0 where mask[n] == 0 (the features a training batch drops)."""
+    rows, N = x.shape
+    check(lib().scn_mask_columns(_ptr(x), c_ll(rows), N, _ptr(_f32(mask)), _stream()))
+
+
+def sgd_update_masked(w, m, d, row_mask, row_period, col_mask, lr, momentum, keep_positive=False):
+    """scn_sgd_update on the entries of w [rows x N] whose row mask (index row % row_period) and column mask are non-zero;
+    either mask may be None.  In place on w and m."""
+    rows, N = w.shape
+    check(lib().scn_sgd_update_masked(_ptr(w), _ptr(m), _ptr(_f32(d)), c_ll(rows), N, _ptr(_f32(row_mask)) if row_mask is not None else None,
+                                      int(row_period), _ptr(_f32(col_mask)) if col_mask is not None else None, c_f(lr), c_f(momentum),
+                                      int(keep_positive), _stream()))
 
 
 class ExchangeBuffer:

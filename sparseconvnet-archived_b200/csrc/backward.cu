@@ -207,6 +207,36 @@ __global__ void k_sgd_update(float *__restrict__ w, float *__restrict__ m, const
   }
 }
 
+// Training-time dropout keeps every matrix at its full width and zeroes the dropped features instead of shrinking
+// the matrices to the present ones (NetworkInNetworkLayer.cu:162-186 shrinks): a zero input column contributes nothing
+// to a product and a zeroed gradient column gives zero weight gradients, so the numbers that exist in the reference's
+// narrow matrices are the same here, and the tensor-core kernels keep their shapes.
+// x[r][n] *= mask[n]
+__global__ void k_mask_columns(float *__restrict__ x, long long total, int N, const float *__restrict__ mask) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    if (mask[i % N] == 0.f) x[i] = 0.f;
+}
+// k_sgd_update on the entries whose input feature (row, mask index row % rowPeriod) and output feature (column) are
+// both present: dGradientDescentShrunkMatrix / ...ShrunkVector (NetworkInNetworkLayer.cu:43-81) leave the others, and
+// their momentum, untouched.
+__global__ void k_sgd_update_masked(float *__restrict__ w, float *__restrict__ m, const float *__restrict__ d, long long n, int N,
+                                    const float *__restrict__ rowMask, int rowPeriod, const float *__restrict__ colMask, float lr, float momentum,
+                                    int keepPositive) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / N;
+    const int col = (int)(i - row * N);
+    if (rowMask && rowMask[row % rowPeriod] == 0.f) continue;
+    if (colMask && colMask[col] == 0.f) continue;
+    float wi = w[i], mi = m[i];
+    wi -= mi * momentum;
+    mi = momentum * mi - lr * (1 - momentum) * d[i];
+    wi += mi * (1 + momentum);
+    if (keepPositive) wi = wi > 0.001f ? wi : 0.001f;
+    w[i] = wi;
+    m[i] = mi;
+  }
+}
+
 // ---- the weight gradient on the tensor cores: dW[K x N] = Xg^T[K x rows] * d[rows x N] is the forward kernel's product with
 // the roles turned: its "rows" are the K gathered input channels, its contraction runs over the layer's rows, its
 // "weights" are the output gradient.  The gathered input is written once, transposed ([Kp x rowsP], Kp and rowsP padded
@@ -448,5 +478,30 @@ extern "C" int scn_sgd_update(float *d_w, float *d_momentum, const float *d_delt
   if (!d_w || !d_momentum || !d_delta) return fail(SCN_ERR_INVALID, "null pointer");
   k_sgd_update<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(d_w, d_momentum, d_delta, n, learningRate, momentum, keep_positive);
   SCN_LAUNCH_CHECK("k_sgd_update");
+  return SCN_OK;
+}
+
+
+extern "C" int scn_mask_columns(float *d_x, long long rows, int N, const float *d_mask, scn_stream_t stream) {
+  clear_error();
+  if (rows < 0 || N < 1) return fail(SCN_ERR_INVALID, "bad mask sizes");
+  if (rows == 0) return SCN_OK;
+  if (!d_x || !d_mask) return fail(SCN_ERR_INVALID, "null pointer");
+  k_mask_columns<<<grid_for(rows * N, 256), 256, 0, (cudaStream_t)stream>>>(d_x, rows * N, N, d_mask);
+  SCN_LAUNCH_CHECK("k_mask_columns");
+  return SCN_OK;
+}
+
+extern "C" int scn_sgd_update_masked(float *d_w, float *d_momentum, const float *d_delta, long long rows, int N, const float *d_row_mask,
+                                     int row_period, const float *d_col_mask, float learningRate, float momentum, int keep_positive,
+                                     scn_stream_t stream) {
+  clear_error();
+  if (rows < 0 || N < 1 || (d_row_mask && row_period < 1)) return fail(SCN_ERR_INVALID, "bad update sizes");
+  if (rows == 0) return SCN_OK;
+  if (!d_w || !d_momentum || !d_delta) return fail(SCN_ERR_INVALID, "null pointer");
+  k_sgd_update_masked<<<grid_for(rows * N, 256), 256, 0, (cudaStream_t)stream>>>(d_w, d_momentum, d_delta, rows * N, N, d_row_mask,
+                                                                                 d_row_mask ? row_period : 1, d_col_mask, learningRate, momentum,
+                                                                                 keep_positive);
+  SCN_LAUNCH_CHECK("k_sgd_update_masked");
   return SCN_OK;
 }

@@ -18,9 +18,22 @@
 using rulechain::preprocessNow;
 
 namespace {
-// Every batch type runs the same forward kernels; a TRAINBATCH is refused only by learnt layers that would have to draw a
-// dropout subset (see NetworkInNetworkLayer::enqueueRules).
+// Every batch type runs the same forward kernels (a TRAINBATCH of a layer with dropout zeroes the dropped features behind them).
 void requireInference(const SpatiallySparseBatch &) {}
+// The 0/1 mask (one float per feature, on the device) of the features a training batch keeps at `iface`, or nullptr if it
+// keeps them all: the mask of the nearest learnt layer's output at or below it.  The layers in between copy features
+// through (a convolution: `copies` times, so masks apply with the period of their own length).
+const float *presentMaskAt(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &iface, int &period) {
+  SpatiallySparseBatchInterface *first = batch.interfaces.data();
+  for (SpatiallySparseBatchInterface *i = &iface; i >= first && i < first + batch.interfaces.size(); --i) {
+    if (i->learntOutput || i == first) {
+      period = (int)i->presentMask.size();
+      return period ? i->presentMask.dPtr() : nullptr;
+    }
+  }
+  period = 0;
+  return nullptr;
+}
 // The split tensor-core precision (SCN_PREC_3XTF32 or SCN_PREC_SPLIT) a layer set to `precision` runs a batch of this type
 // in, or -1 if it runs in another one.  Training steps use tf32 operands throughout: the bf16 operands that SCN_PREC_SPLIT
 // gives layers with long K carry 16 mantissa bits per product, and a gradient that has gone through a whole forward and
@@ -422,7 +435,7 @@ NetworkInNetworkLayer::~NetworkInNetworkLayer() {
 }
 float *NetworkInNetworkLayer::slopes() { return nullptr; }
 float *NetworkInNetworkLayer::slopeGradient() { return nullptr; }
-void NetworkInNetworkLayer::updateSlopes(float, float) {}
+void NetworkInNetworkLayer::updateSlopes(float, float, const float *) {}
 void NetworkInNetworkLayer::weightsChanged() { packedPrecision = -100; }
 // NetworkInNetworkLayer.cu:203-220 (and NetworkInNetworkPReLULayer.cu:175-191, the same): after this layer's forwards on
 // a RESCALEBATCH, weights and biases are scaled so that the mean absolute output moves towards 1 (by its -0.1th power)
@@ -459,9 +472,7 @@ const void *NetworkInNetworkLayer::packedWeights(int fs, int nIn, int prec) {
 }
 long long NetworkInNetworkLayer::enqueueRules(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input,
                                               SpatiallySparseBatchInterface &output, long long rowsInBound, int *) {
-  if (batch.type == TRAINBATCH && dropout > 0)
-    throw ScnException("NetworkInNetworkLayer: training with dropout (random feature subsets, NetworkInNetworkLayer.cu:152-154) is not built; "
-                       "build the network with dropout 0 to train it");
+  (void)batch;
   if (input.nFeatures != nFeaturesIn) throw ScnException("NetworkInNetworkLayer: wrong number of input features");
   output.nFeatures = nFeaturesOut;
   output.spatialSize = input.spatialSize;
@@ -477,8 +488,29 @@ void NetworkInNetworkLayer::finishRules(SpatiallySparseBatch &batch, SpatiallySp
   output.nSpatialSites = input.nSpatialSites;
   output.maxSitesPerSample = input.maxSitesPerSample;
   output.gridOwner = input.gridOwner; // same geometry: the grids are shared, not copied
-  output.featuresPresent.hVector() = range(nFeaturesOut); // all features at test time
+  output.featuresPresent.hVector() = range(nFeaturesOut); // the matrices keep their full width; see presentSubset
   output.backpropErrors = true;
+  output.learntOutput = true;
+  output.presentSubset.clear();
+  output.presentMask.resize(0);
+  if (batch.type == TRAINBATCH && dropout > 0) { // NetworkInNetworkLayer.cu:152-154
+    const int keep = nFeaturesOut * (1.0f - dropout);
+    if (!forcedPresent.empty()) {
+      for (size_t i = 0; i < forcedPresent.size(); ++i)
+        if (forcedPresent[i] < 0 || forcedPresent[i] >= nFeaturesOut || (i && forcedPresent[i] <= forcedPresent[i - 1]))
+          throw ScnException("NetworkInNetworkLayer: forcedPresent must hold ascending feature indices below nFeaturesOut");
+      output.presentSubset = forcedPresent;
+    } else {
+      output.presentSubset = rng.NchooseM(nFeaturesOut, keep);
+    }
+    if ((int)output.presentSubset.size() < nFeaturesOut) {
+      output.presentMask.copyToCPU();
+      std::vector<float> &m = output.presentMask.hVector();
+      m.assign(nFeaturesOut, 0.f);
+      for (int f : output.presentSubset) m[f] = 1.f;
+      output.presentMask.copyToGPU();
+    }
+  }
 }
 void NetworkInNetworkLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
   enqueueRules(batch, input, output, input.nSpatialSites, nullptr);
@@ -586,7 +618,10 @@ void NetworkInNetworkLayer::forwards(SpatiallySparseBatch &batch, SpatiallySpars
 void NetworkInNetworkLayer::forwardsNow(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
   requireInference(batch);
   output.sub->features.resize(output.nSpatialSites * output.featuresPresent.size());
-  const float p = 1.0f - (batch.type != RESCALEBATCH ? dropout : 0.0f); // NetworkInNetworkLayer.cu:188
+  float p = 1.0f - (batch.type != RESCALEBATCH ? dropout : 0.0f); // NetworkInNetworkLayer.cu:188
+  int inPeriod = 0;
+  // a training batch that drops features on either side of this layer runs on the kept ones unscaled (NetworkInNetworkLayer.cu:162-186)
+  if (batch.type == TRAINBATCH && (output.presentMask.size() || presentMaskAt(batch, input, inPeriod))) p = 1.0f;
   const float *src;
   const int *rules = nullptr;
   int fs = 1, nIn = nFeaturesIn;
@@ -618,6 +653,8 @@ void NetworkInNetworkLayer::forwardsNow(SpatiallySparseBatch &batch, SpatiallySp
   }
   scnSafeCall(scn_conv_nin_forward_ws(src, rules, output.nSpatialSites, fs, nIn, W.dPtr(), pk, B.dPtr(), slopes(), nFeaturesOut, p,
                                       (int)fn, prec, output.sub->features.dPtr(), ws, wsBytes, memStream.stream));
+  if (output.presentMask.size()) // the dropped features: zeros in place of the columns the reference's narrow matrix leaves out
+    scnSafeCall(scn_mask_columns(output.sub->features.dPtr(), output.nSpatialSites, nFeaturesOut, output.presentMask.dPtr(), memStream.stream));
 }
 // Weight files: raw fp32 W then B (then momentum copies) per layer (NetworkInNetworkLayer.cu:290-328).
 void NetworkInNetworkLayer::loadWeightsFromStream(std::ifstream &f, bool momentum) {
@@ -774,19 +811,24 @@ void TerminalPoolingLayer::backwards(SpatiallySparseBatch &batch, SpatiallySpars
   scnSafeCall(scn_terminal_pool_backward(output.sub->dfeatures.dPtr(), output.rules.dPtr(), output.nSpatialSites, output.rules.size() / batch.batchSize,
                                          C, input.sub->dfeatures.dPtr(), input.nSpatialSites, memStream.stream));
 }
-// NetworkInNetworkLayer.cu:221-289 for a layer without dropout: activation derivative in place on the output's gradient;
+// NetworkInNetworkLayer.cu:221-289: activation derivative in place on the output's gradient;
 // dW = X^T d and dB = column sums (X read through the rulebook where the convolution in front is fused); the input's
 // gradient d W^T with the weights as they were in the forward pass, scattered through the rulebook onto the
-// convolution's input where fused; then the SGD update of W, B (and the PReLU slopes).
+// convolution's input where fused; then the SGD update of W, B (and the PReLU slopes).  Where the batch drops features
+// (on this layer's output, or on the learnt layer's below) the gradients of the dropped columns are zeroed on both sides
+// and the update leaves the weights that touch a dropped feature, and their momentum, alone
+// (dGradientDescentShrunkMatrix, NetworkInNetworkLayer.cu:43-61).
 void NetworkInNetworkLayer::backwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
                                       float learningRate, float momentum) {
-  if (dropout > 0) throw ScnException("NetworkInNetworkLayer::backwards: training with dropout is not built");
-  (void)batch;
   const int rows = output.nSpatialSites, N = nFeaturesOut, K = nFeaturesIn;
   cudaStream_t s = memStream.stream;
   if ((int)output.sub->dfeatures.size() != rows * N) throw ScnException("NetworkInNetworkLayer::backwards: the output's gradient is missing");
   if ((int)output.sub->features.size() != rows * N) throw ScnException("NetworkInNetworkLayer::backwards: the output's features are missing (run forwards on a TRAINBATCH)");
   float *d = output.sub->dfeatures.dPtr();
+  int inPeriod = 0;
+  const float *inMask = presentMaskAt(batch, input, inPeriod);
+  const float *outMask = output.presentMask.size() ? output.presentMask.dPtr() : nullptr;
+  if (outMask) scnSafeCall(scn_mask_columns(d, rows, N, outMask, s));
   scnSafeCall(scn_activation_backward(output.sub->features.dPtr(), d, rows, N, (int)fn, slopes(), slopeGradient(), s));
   const float *src;
   const int *rules = nullptr;
@@ -855,6 +897,7 @@ void NetworkInNetworkLayer::backwards(SpatiallySparseBatch &batch, SpatiallySpar
     }
     scnSafeCall(scn_conv_nin_forward_ws(d, nullptr, rows, 1, N, Wt.dPtr(), pk, zeroBias.dPtr(), nullptr, K, 1.0f, SCN_NOSIGMOID, prec, dX, ws, wsBytes, s));
     multiplyAddCount += (__int128_t)rows * K * N;
+    if (inMask) scnSafeCall(scn_mask_columns(dX, (long long)rows * (K / inPeriod), inPeriod, inMask, s));
     if (rules) {
       target->sub->dfeatures.resize(target->nSpatialSites * nIn);
       scnSafeCall(scn_gather_backward(dX, rules, (long long)rows * fs, nIn, target->sub->dfeatures.dPtr(), target->nSpatialSites, s));
@@ -862,9 +905,14 @@ void NetworkInNetworkLayer::backwards(SpatiallySparseBatch &batch, SpatiallySpar
   }
   multiplyAddCount += (__int128_t)rows * K * N;
   if ((int)MW.size() != K * N) { zeroed(MW, K * N, memStream); zeroed(MB, N, memStream); }
-  scnSafeCall(scn_sgd_update(W.dPtr(), MW.dPtr(), dw.dPtr(), (long long)K * N, learningRate, momentum, 0, s));
-  scnSafeCall(scn_sgd_update(B.dPtr(), MB.dPtr(), db.dPtr(), N, learningRate, momentum, 0, s));
-  updateSlopes(learningRate, momentum);
+  if (inMask || outMask) {
+    scnSafeCall(scn_sgd_update_masked(W.dPtr(), MW.dPtr(), dw.dPtr(), K, N, inMask, inPeriod, outMask, learningRate, momentum, 0, s));
+    scnSafeCall(scn_sgd_update_masked(B.dPtr(), MB.dPtr(), db.dPtr(), 1, N, nullptr, 1, outMask, learningRate, momentum, 0, s));
+  } else {
+    scnSafeCall(scn_sgd_update(W.dPtr(), MW.dPtr(), dw.dPtr(), (long long)K * N, learningRate, momentum, 0, s));
+    scnSafeCall(scn_sgd_update(B.dPtr(), MB.dPtr(), db.dPtr(), N, learningRate, momentum, 0, s));
+  }
+  updateSlopes(learningRate, momentum, outMask);
   weightsChanged();
 }
 float *NetworkInNetworkPReLULayer::slopeGradient() {
@@ -872,7 +920,15 @@ float *NetworkInNetworkPReLULayer::slopeGradient() {
   dprelu.resize(nFeaturesOut);
   return dprelu.dPtr();
 }
-void NetworkInNetworkPReLULayer::updateSlopes(float learningRate, float momentum) {
+// A batch that drops features updates the slopes of the kept ones only.  (The reference means to,
+// NetworkInNetworkPReLULayer.cu:199-207, but its test `size() < size()` never holds, so it runs the full-width update on a
+// narrow gradient vector and reads past its end: training a PReLU layer with dropout has no defined reference result.)
+void NetworkInNetworkPReLULayer::updateSlopes(float learningRate, float momentum, const float *presentMask) {
   if ((int)MPReLU.size() != nFeaturesOut) zeroed(MPReLU, nFeaturesOut, memStream);
+  if (presentMask) {
+    scnSafeCall(scn_sgd_update_masked(PReLU.dPtr(), MPReLU.dPtr(), dprelu.dPtr(), 1, nFeaturesOut, nullptr, 1, presentMask, learningRate, momentum, 1,
+                                      memStream.stream));
+    return;
+  }
   scnSafeCall(scn_sgd_update(PReLU.dPtr(), MPReLU.dPtr(), dprelu.dPtr(), nFeaturesOut, learningRate, momentum, 1, memStream.stream));
 }

@@ -1,8 +1,10 @@
-// 1x1 convolution: out = act(p * X W + p * B) at test time (NetworkInNetworkLayer.h:6-45).
+// 1x1 convolution: out = act(p * X W + p * B) at test time (NetworkInNetworkLayer.h:6-45); in a training batch
+// with dropout, out = act(X W + B) on the features the batch keeps and zero on the others.
 // Behind a fused ConvolutionalLayer it is the whole convolution: one kernel gathers the rows
 // named by the rules, contracts them with W and applies bias, dropout scaling and activation.
 #pragma once
 #include <fstream>
+#include "Rng.h"
 #include "SpatiallySparseLayer.h"
 
 class NetworkInNetworkLayer : public SpatiallySparseLayer {
@@ -20,6 +22,10 @@ public:
   int precision; // scn_precision used by forwards(); SCN_PREC_AUTO by default
   bool fusePoolNext; // set by the builders when a non-overlapping max-pooling layer follows: forwards() then leaves the
                      // output unmaterialised and the pooling layer runs gather + this layer + pooling as one kernel
+  RNG rng; // draws the features each training batch keeps (NetworkInNetworkLayer.h:8)
+  // The features the next training batches keep instead of a random draw (ascending indices below nFeaturesOut), so that a
+  // run can be repeated with the subsets another run drew; an empty vector returns to random draws.
+  std::vector<int> forcedPresent;
   bool precisionFallback; // true: a tensor-core precision falls back to the CUDA-core kernel where the shape has no tensor-core path (false: throw)
   NetworkInNetworkLayer(cudaMemStream &memStream, cublasHandle_t &cublasHandle, int nFeaturesIn, int nFeaturesOut,
                         float dropout = 0, ActivationFunction fn = NOSIGMOID, float alpha = 1);
@@ -64,7 +70,7 @@ public:
 protected:
   virtual float *slopes(); // per-channel PReLU slopes, or nullptr
   virtual float *slopeGradient();                               // where backwards() leaves the slopes' gradient, or nullptr
-  virtual void updateSlopes(float learningRate, float momentum); // SGD step on the slopes (PReLU layers)
+  virtual void updateSlopes(float learningRate, float momentum, const float *presentMask); // SGD step on the slopes (PReLU layers); presentMask: 0/1 per output feature or nullptr
   void *packedT;           // Wt repacked for the tensor-core kernel (input gradient)
   size_t packedTBytes;
   void *packed;            // W repacked for `packedPrecision`

@@ -16,5 +16,5 @@ public:
 protected:
   float *slopes();
   float *slopeGradient();
-  void updateSlopes(float learningRate, float momentum);
+  void updateSlopes(float learningRate, float momentum, const float *presentMask);
 };

@@ -17,7 +17,8 @@ SpatiallySparseBatchInterface::SpatiallySparseBatchInterface(SpatiallySparseBatc
     : sub(o.sub), nFeatures(o.nFeatures), featuresPresent(std::move(o.featuresPresent)), nSpatialSites(o.nSpatialSites),
       spatialSize(o.spatialSize), backpropErrors(o.backpropErrors), grids(std::move(o.grids)), rules(std::move(o.rules)),
       siteKeys(std::move(o.siteKeys)), sampleOffsets(std::move(o.sampleOffsets)), backgroundRows(std::move(o.backgroundRows)),
-      maxSitesPerSample(o.maxSitesPerSample), gridOwner(this), deferredFrom(nullptr), deferredCells(0), deferredLearnt(nullptr), deferredLearntInput(nullptr) {}
+      maxSitesPerSample(o.maxSitesPerSample), gridOwner(this), deferredFrom(nullptr), deferredCells(0), deferredLearnt(nullptr), deferredLearntInput(nullptr),
+      presentSubset(std::move(o.presentSubset)), presentMask(std::move(o.presentMask)), learntOutput(o.learntOutput) {}
 void SpatiallySparseBatchInterface::summary() {
   std::cout << "nFeatures " << nFeatures << " featuresPresent " << featuresPresent.size() << " spatialSize " << spatialSize
             << " nSpatialSites " << nSpatialSites << " features " << sub->features.size() << " grids " << grids.size() << std::endl;
@@ -30,6 +31,9 @@ void SpatiallySparseBatchInterface::reset() {
   grids.resize(0);
   rules.resize(0);
   backpropErrors = false;
+  presentSubset.clear();
+  presentMask.resize(0);
+  learntOutput = false;
   maxSitesPerSample = 0;
   gridOwner = this;
   deferredFrom = nullptr;

@@ -45,6 +45,14 @@ public:
   class NetworkInNetworkLayer *deferredLearnt;
   SpatiallySparseBatchInterface *deferredLearntInput;
 
+  // Training-time dropout.  The reference narrows `features` to the features a training batch keeps and lists them in
+  // featuresPresent (NetworkInNetworkLayer.cu:152-154); here `features` keeps its full width, the dropped features'
+  // columns hold zeros, featuresPresent lists every feature, and the subset drawn for the batch is in `presentSubset`
+  // with `presentMask` its 0/1 form on the device (both empty: nothing dropped).  `learntOutput`: written by a learnt layer.
+  std::vector<int> presentSubset;
+  vectorCUDA<float> presentMask;
+  bool learntOutput;
+
   explicit SpatiallySparseBatchInterface(SpatiallySparseBatchSubInterface *s);
   SpatiallySparseBatchInterface(SpatiallySparseBatchInterface &&o) noexcept; // pointers into a moved-from interface are dropped
   void summary();

@@ -509,6 +509,31 @@ int scn_net_train_batch(scn_net_t *net, int batch, const int *keys, const int *o
   });
 }
 
+int scn_net_set_dropout_features(scn_net_t *net, int layer, const int *present, int n) {
+  return guarded([&] {
+    auto l = dynamic_cast<NetworkInNetworkLayer *>(net->cnn->layers.at(layer));
+    if (!l) throw ScnException("layer has no weights");
+    if (n < 0 || n > l->nFeaturesOut || (n && !present)) throw ScnException("bad feature subset");
+    l->forcedPresent.assign(present, present + n);
+  });
+}
+
+int scn_net_iface_present(scn_net_t *net, int i, int *present) {
+  int n = -1;
+  guarded([&] {
+    if (!net->last) throw ScnException("no batch has run");
+    SpatiallySparseBatchInterface &I = net->last->interfaces.at(i);
+    if (I.presentMask.size() == 0) {
+      n = I.nFeatures;
+      for (int f = 0; f < n && present; ++f) present[f] = f;
+    } else {
+      n = (int)I.presentSubset.size();
+      if (present) std::copy(I.presentSubset.begin(), I.presentSubset.end(), present);
+    }
+  });
+  return n;
+}
+
 int scn_net_rescale_batch(scn_net_t *net, int batch, const int *keys, const int *off, const float *features) {
   return guarded([&] {
     Quiet q; // (every learnt layer prints its featureScale line, as the reference does)

@@ -21,7 +21,7 @@ EXPORTS = [
     "scn_net_layer_times", "scn_net_process_dataset", "scn_host_vectorTopIndices",
     "scn_net_exchange_create", "scn_net_exchange_buffer", "scn_net_exchange_connect", "scn_net_exchange_connect_local", "scn_net_exchange_destroy",
     "scn_net_forward_host_exchange", "scn_net_exchange_flush", "scn_net_exchange_step_device",
-    "scn_net_forward_host_begin", "scn_net_forward_host_end", "scn_net_rescale_batch",
+    "scn_net_forward_host_begin", "scn_net_forward_host_end", "scn_net_rescale_batch", "scn_net_set_dropout_features", "scn_net_iface_present",
 ]
 
 LAYER_KEYS = ("type", "size", "stride", "minActive", "nIn", "nOut", "fs", "act", "inSpatial", "outSpatial")
@@ -88,6 +88,8 @@ def lib():
         L.scn_net_exchange_step_device.argtypes = [c_p, c_p, c_int, c_p, c_p]
         L.scn_net_forward_host_begin.argtypes = [c_p, c_int, c_p, c_p, c_p]
         L.scn_net_rescale_batch.argtypes = [c_p, c_int, c_p, c_p, c_p]
+        L.scn_net_set_dropout_features.argtypes = [c_p, c_int, c_p, c_int]
+        L.scn_net_iface_present.argtypes = [c_p, c_int, c_p]
         L.scn_net_forward_host_end.argtypes = [c_p, c_p, c_p, c_p, c_p]
         _lib = L
     return _lib
@@ -324,6 +326,22 @@ class Net:
         off = np.ascontiguousarray(off, np.int32)
         features = np.ascontiguousarray(features, np.float32)
         _check(self.L.scn_net_rescale_batch(self.h, len(off) - 1, _np(keys), _np(off), _np(features)))
+
+    def set_dropout_features(self, layer, present):
+        """The output features learnt layer `layer` keeps in the training batches that follow (ascending indices; an empty
+        list returns to random draws)."""
+        present = np.ascontiguousarray(present, np.int32)
+        _check(self.L.scn_net_set_dropout_features(self.h, layer, _np(present), len(present)))
+
+    def iface_present(self, i):
+        """The features interface i kept in the last batch (all of them outside training with dropout)."""
+        n = self.L.scn_net_iface_present(self.h, i, None)
+        if n < 0:
+            raise abi.ScnError(self.L.scn_net_last_error().decode())
+        out = np.zeros(n, np.int32)
+        if n:
+            self.L.scn_net_iface_present(self.h, i, _np(out))
+        return out
 
     def get_weights(self, i):
         L = self.layers()[i]
