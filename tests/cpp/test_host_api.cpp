@@ -186,6 +186,50 @@ int main() {
       ds.type = TESTBATCH;
       std::printf("OK training (NLL %.3f -> %.3f)\n", first, last);
     }
+    // ---- 5c. training with dropout: each TRAINBATCH keeps a drawn subset of a learnt layer's output features
+    //          (NetworkInNetworkLayer.cu:152-154), zeros stand in the dropped columns, test batches keep every feature
+    {
+      SparseConvNet dnet(2, 3, 5);
+      dnet.addLeNetLayerMP(32, 3, 1, 2, 2, VLEAKYRELU, 0.0f);
+      dnet.addLeNetLayerMP(128, 2, 1, 2, 2, VLEAKYRELU, 0.5f); // keeps 64 of 128
+      dnet.addLeNetLayerMP(96, 2, 1, 1, 1, VLEAKYRELU, 0.5f);  // 48 rounds to 64 of 96: dropout 1/3 (SparseConvNetCUDA.cu:56-60)
+      dnet.addSoftmaxLayer();
+      SparseConvNetCUDA &d = *dnet.cnn;
+      CHECK(d.inputSpatialSize == S);
+      fillWeights(d, 6);
+      ds.type = TRAINBATCH;
+      const float first = d.processDataset(ds, 4, 0.01f, 0.9f);
+      float last = first;
+      for (int epoch = 0; epoch < 12; ++epoch) last = d.processDataset(ds, 4, 0.01f, 0.9f);
+      CHECK(std::isfinite(first) && std::isfinite(last) && last < first);
+      {
+        BatchProducer bp(d, ds, S, 4);
+        std::ofstream nof, nog;
+        SpatiallySparseBatch *b = bp.nextBatch();
+        CHECK(b != nullptr);
+        d.processBatch(*b, 0.01f, 0.9f, nof, nog);
+        int withDropout = 0;
+        for (size_t l = 0; l < d.layers.size(); ++l) {
+          auto nin = dynamic_cast<NetworkInNetworkLayer *>(d.layers[l]);
+          if (!nin || nin->dropout == 0.f) continue;
+          SpatiallySparseBatchInterface &I = b->interfaces[l + 1];
+          CHECK((int)I.presentSubset.size() == 64 && (int)I.featuresPresent.size() == nin->nFeaturesOut);
+          std::vector<float> &f = I.sub->features.hVector();
+          std::vector<char> kept(nin->nFeaturesOut, 0);
+          for (int k : I.presentSubset) kept[k] = 1;
+          for (int r = 0; r < I.nSpatialSites; ++r)
+            for (int k = 0; k < nin->nFeaturesOut; ++k)
+              if (!kept[k]) CHECK(f[(size_t)r * nin->nFeaturesOut + k] == 0.f);
+          ++withDropout;
+        }
+        CHECK(withDropout == 2);
+        while (bp.nextBatch()) {}
+      }
+      ds.type = TESTBATCH;
+      const float test = d.processDataset(ds, 4);
+      CHECK(std::isfinite(test));
+      std::printf("OK training with dropout (NLL %.3f -> %.3f)\n", first, last);
+    }
     // ---- 6. fractional max-pooling: a named FMP network, and the host gridRules over FractionalPoolingRegions
     {
       POFMPSparseConvNet fmp(2, 3, 32, 1.414f, VLEAKYRELU, 2, 5);
