@@ -849,6 +849,21 @@ int orc_net_load_weights(void *h, const char *path) {
   return f ? 0 : -2;
 }
 
+// Fractional max-pooling: every sample's tick tables, drawn in batch order from each layer's generator, which is seeded
+// anew (seed + layer index) for every batch.
+static std::vector<std::vector<Ticks>> drawFmpTicks(const Net &net, int batch) {
+  std::vector<std::vector<Ticks>> fmpTicks(net.layers.size());
+  for (size_t l = 0; l < net.layers.size(); ++l) {
+    const Layer &L = net.layers[l];
+    if (L.type != L_FMP) continue;
+    FmpRng rng;
+    rng.gen.seed(net.fmpSeed + (unsigned)l);
+    for (int b = 0; b < batch; ++b)
+      for (int a = 0; a < net.dim; ++a) fmpTicks[l].push_back(makeTicks(L.fmpKind, L.inSpatial, L.outSpatial, L.size, rng));
+  }
+  return fmpTicks;
+}
+
 // Full forward.  probs [batch x nClasses], predictions [batch x nTop] (SoftmaxClassifier.cu:36-41).
 // nThreads > 1 splits the batch into contiguous chunks (samples are independent); keep=1
 // retains every interface for layer-by-layer comparison (chunks are joined into the whole
@@ -862,16 +877,7 @@ void orc_net_forward(void *h, int batch, const int64_t *keys, const int *off, co
   nThreads = std::min(nThreads, std::max(1, batch));
   std::vector<double> tr(nThreads, 0.0);
   std::vector<std::vector<Iface>> ifs(nThreads);
-  // fractional max-pooling: every sample's tick tables, drawn in batch order from each layer's RNG
-  std::vector<std::vector<Ticks>> fmpTicks(net->layers.size());
-  for (size_t l = 0; l < net->layers.size(); ++l) {
-    const Layer &L = net->layers[l];
-    if (L.type != L_FMP) continue;
-    FmpRng rng;
-    rng.gen.seed(net->fmpSeed + (unsigned)l);
-    for (int b = 0; b < batch; ++b)
-      for (int a = 0; a < net->dim; ++a) fmpTicks[l].push_back(makeTicks(L.fmpKind, L.inSpatial, L.outSpatial, L.size, rng));
-  }
+  std::vector<std::vector<Ticks>> fmpTicks = drawFmpTicks(*net, batch);
   auto work = [&](int t) {
     int b0 = (int)((long long)batch * t / nThreads), b1 = (int)((long long)batch * (t + 1) / nThreads);
     if (b1 <= b0) return;
@@ -902,9 +908,9 @@ int orc_net_train_step(void *h, int batch, const int64_t *keys, const int *off, 
                        float learningRate, float momentum, int accum64, float *probs, double *stats) {
   Net *net = (Net *)h;
   for (const Layer &L : net->layers) if (L.type == L_NIN && L.dropout > 0) return 1; // training-time dropout draws random feature subsets: not restated
-  std::vector<std::vector<Ticks>> noTicks(net->layers.size());
+  std::vector<std::vector<Ticks>> fmpTicks = drawFmpTicks(*net, batch);
   std::vector<Iface> ifs;
-  forwardChunk(*net, batch, keys, off, features, accum64 != 0, ifs, nullptr, noTicks, 0);
+  forwardChunk(*net, batch, keys, off, features, accum64 != 0, ifs, nullptr, fmpTicks, 0);
   const int nL = (int)net->layers.size();
   Iface &top = ifs.back();
   const int C = net->nClasses;

@@ -650,3 +650,45 @@ def test_named_architectures_train_with_dropout_like_the_reference(scn, abi, ora
         return np.concatenate(keys).astype(np.int32), np.array(off, np.int32), np.concatenate(feats).astype(np.float32)
 
     _reference_dropout_steps(abi, ref, gnet, onet, layers, weights, gen, batch, nClasses, min_dropped=1)
+
+
+@pytest.mark.parametrize("name", ["POFMPSparseConvNet", "ROFMPSparseConvNet", "PDFMPSparseConvNet", "RDFMPSparseConvNet"])
+def test_fractional_max_pooling_networks_train_like_the_oracle(scn, abi, oracle, name):
+    """Two training steps of the four fractional max-pooling classes (NetworkArchitectures.cpp:72-122, no dropout; both sides
+    draw their pooling regions from the same seeded generators): the backward pass routes gradients through the pooling
+    choices of overlapping and disjoint, pseudorandom and random regions (MaxPoolingLayer.cu:187-199 and its siblings)."""
+    from oracle import orc
+    from netutil import build_named
+    l, k, nIn, nClasses, batch, shrink = 3, 32, 3, 10, 5, 1.5
+    act = orc.VLEAKYRELU
+    gnet = scn.net.Net.named(name, 2, l, k, act, nIn, nClasses, p=0.0, fmpShrink=shrink)
+    onet = orc.OracleNet(oracle, 2, nIn, nClasses, 1)
+    build_named(onet, name, l, k, act, 0.0, shrink)
+    layers = gnet.layers()
+    weights = scn.synth.init_weights(layers, 23)
+    for i, (W, B, _) in weights.items():
+        weights[i] = (W, B, None)
+        onet.set_weights(i, W, B, None)
+        gnet.set_weights(i, W, B, None)
+    onet.seed_fmp(77)
+    S = gnet.inputSpatialSize
+    for step in range(2):
+        gnet.seed_fmp(77)  # (the oracle seeds its generators anew for every batch)
+        rng = np.random.default_rng(300 + step)
+        keys, feats, off = [], [], [0]
+        for _ in range(batch):
+            kk = np.unique(rng.integers(0, S * S, 4 * S))
+            keys.append(np.concatenate([[-1], kk]))
+            feats.append(np.concatenate([np.zeros((1, nIn)), rng.uniform(-1, 1, (len(kk), nIn))]))
+            off.append(off[-1] + len(kk) + 1)
+        keys, off, feats = np.concatenate(keys).astype(np.int32), np.array(off, np.int32), np.concatenate(feats).astype(np.float32)
+        labels = ((np.arange(batch) * 7 + step) % nClasses).astype(np.int32)
+        old = {i: onet.get_weights(i) for i in weights}
+        oprobs, ostats = onet.train_step(keys, off, feats, labels, 0.01, 0.9)
+        gprobs, gstats = gnet.train_batch(keys, off, feats, labels, 0.01, 0.9)
+        assert abi.conv_tc_take_error() == 0
+        assert relerr(gprobs, oprobs) < TOL
+        assert gstats["nll"] == pytest.approx(ostats["nll"], rel=1e-4)
+        for i in range(len(layers) + 1):
+            np.testing.assert_array_equal(gnet.iface(i, features=False)["rules"], onet.iface(i)["rules"], err_msg="rulebook of interface %d" % i)
+        assert _compare_step(gnet, onet, layers, old) >= 3
