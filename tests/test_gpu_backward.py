@@ -692,3 +692,52 @@ def test_fractional_max_pooling_networks_train_like_the_oracle(scn, abi, oracle,
         for i in range(len(layers) + 1):
             np.testing.assert_array_equal(gnet.iface(i, features=False)["rules"], onet.iface(i)["rules"], err_msg="rulebook of interface %d" % i)
         assert _compare_step(gnet, onet, layers, old) >= 3
+
+
+def test_training_step_at_benchmark_batch_on_both_kernel_families(scn, abi):
+    """Config 2 at its benchmark batch of 256 (dropout 0), one training step twice: with the default kernels (tensor cores:
+    forward, input gradients and weight gradients through the fused kernel) and with every learnt layer set to plain fp32
+    (CUDA-core kernels, the ones the small cases above compare with the oracle, which needs minutes at this size).  Two
+    independent implementations must agree on the probabilities, the gradient at every materialised interface and every
+    weight update."""
+    c = scn.synth.CONFIGS[2]
+    batch = 256
+    levels, terminal = _levels(scn, 2, abi.VLEAKYRELU)
+    nets = []
+    for prec in (abi.PREC_AUTO, abi.PREC_FP32):
+        net = scn.net.Net(c["dim"], c["nIn"], c["nClasses"], 1, c["lattice"])
+        build_with(net, levels, terminal)
+        net.set_precision(prec)
+        nets.append(net)
+    layers = nets[0].layers()
+    weights = scn.synth.init_weights(layers, 29)
+    for net in nets:
+        for i, (W, B, _) in weights.items():
+            net.set_weights(i, W, B, None)
+    keys, off, feats = c["gen"](batch)
+    labels = ((np.arange(batch) * 7) % c["nClasses"]).astype(np.int32)
+    out = [net.train_batch(keys, off, feats, labels, 1e-5, 0.9) for net in nets]  # (summed gradients of 256 samples: a small rate)
+    assert abi.conv_tc_take_error() == 0
+    assert relerr(out[0][0], out[1][0]) < TOL
+    assert out[0][1]["nll"] == pytest.approx(out[1][1]["nll"], rel=1e-4)
+    checked = 0
+    for i in range(len(layers) + 1):
+        if i and layers[i - 1]["type"] in (0, 1):
+            continue
+        a, b = nets[0].dfeatures(i), nets[1].dfeatures(i)
+        if b.size == 0:
+            continue
+        # millions of elements: a handful of near-ties fall differently in the two forwards, and each spreads over whole rows
+        # of every interface below it (measured: up to 0.16 % of an interface beyond 1e-3; the top interfaces agree to 2e-6)
+        assert a.size == b.size and grad_close(a, b, outliers=5e-3), "gradient of interface %d: %g" % (i, relerr(a, b))
+        if i >= len(layers) - 3:
+            assert relerr(a, b) < TOL, "gradient of interface %d" % i
+        checked += 1
+    assert checked >= 6
+    for i, (W0, B0, _) in weights.items():
+        (aW, aB, _), (bW, bB, _) = nets[0].get_weights(i), nets[1].get_weights(i)
+        # the update is read back as w_new - w_old: what can be seen of it is bounded by the rounding of the weights themselves
+        seen = lambda w0, dw: 4 * UPDATE_TOL + 2 * 6e-8 * float(np.abs(w0).max()) / max(float(np.abs(dw).max()), 1e-30)
+        assert np.abs(bW - W0).max() > 100 * 6e-8 * np.abs(W0).max()
+        assert relerr(aW - W0, bW - W0) < seen(W0, bW - W0), "weight update of layer %d" % i
+        assert relerr(aB - B0, bB - B0) < seen(B0, bB - B0), "bias update of layer %d" % i
