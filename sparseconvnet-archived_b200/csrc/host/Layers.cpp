@@ -495,6 +495,7 @@ void NetworkInNetworkLayer::finishRules(SpatiallySparseBatch &batch, SpatiallySp
   output.presentMask.resize(0);
   if (batch.type == TRAINBATCH && dropout > 0) { // NetworkInNetworkLayer.cu:152-154
     const int keep = nFeaturesOut * (1.0f - dropout);
+    std::lock_guard<std::mutex> lock(rngMutex);
     if (!forcedPresent.empty()) {
       for (size_t i = 0; i < forcedPresent.size(); ++i)
         if (forcedPresent[i] < 0 || forcedPresent[i] >= nFeaturesOut || (i && forcedPresent[i] <= forcedPresent[i - 1]))

@@ -4,6 +4,7 @@
 // named by the rules, contracts them with W and applies bias, dropout scaling and activation.
 #pragma once
 #include <fstream>
+#include <mutex>
 #include "Rng.h"
 #include "SpatiallySparseLayer.h"
 
@@ -23,6 +24,7 @@ public:
   bool fusePoolNext; // set by the builders when a non-overlapping max-pooling layer follows: forwards() then leaves the
                      // output unmaterialised and the pooling layer runs gather + this layer + pooling as one kernel
   RNG rng; // draws the features each training batch keeps (NetworkInNetworkLayer.h:8)
+  std::mutex rngMutex; // BatchProducer threads preprocess different batches through the same layer object
   // The features the next training batches keep instead of a random draw (ascending indices below nFeaturesOut), so that a
   // run can be repeated with the subsets another run drew; an empty vector returns to random draws.
   std::vector<int> forcedPresent;
