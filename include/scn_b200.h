@@ -426,6 +426,12 @@ int scn_sgd_update_masked(float *d_w, float *d_momentum, const float *d_delta, l
                           const float *d_row_mask, int row_period, const float *d_col_mask, float learningRate,
                           float momentum, int keep_positive, scn_stream_t stream);
 
+/* Index learning (IndexLearnerLayer.cu:8-20, 57-66): d_w[k][j] = d_W[k][d_idx[j]] for the n columns of d_W [K x N] a batch
+ * indexes, and d_W[k][d_idx[j]] += alpha * d_delta[k][j] (the update without momentum; the indices must be distinct). */
+int scn_gather_columns(const float *d_W, int K, int N, const int *d_idx, int n, float *d_w, scn_stream_t stream);
+int scn_scatter_columns_axpy(float *d_W, int K, int N, const int *d_idx, int n, const float *d_delta, float alpha,
+                             scn_stream_t stream);
+
 /* ------------------------------------------------------------------ result exchange between the GPUs of one node
  * The reference runs on one GPU (SparseConvNetCUDA.cu:43-71 picks a single device).  Sharded by sample over several
  * GPUs, the path has one exchange step: every rank's [rows x nClasses] block of probabilities (what

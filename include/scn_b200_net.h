@@ -94,6 +94,14 @@ int scn_net_set_dropout_features(scn_net_t *net, int layer, const int *present, 
 /* The features interface i kept in the last batch (see above): returns their count, which is the interface's nFeatures
  * unless it is a learnt layer's output in a training batch with dropout, and copies the indices if `present` is not NULL. */
 int scn_net_iface_present(scn_net_t *net, int i, int *present);
+/* Index learning (IndexLearnerLayer.h, SparseConvNetCUDA.cu:211-225, 443-474): addIndexLearnerLayer in place of
+ * addSoftmaxLayer makes nClasses the number of pictures of the training set; a step runs every layer, the index learner on
+ * the columns `sample_numbers` (each picture's number in the training set, distinct), IndexLearner (picture i's class is
+ * column i: h_probs [batch x batch], stats = {negative log-likelihood, mistakes}) and the backward pass (the index learner
+ * updates without momentum). */
+int scn_net_addIndexLearnerLayer(scn_net_t *net);
+int scn_net_index_learner_batch(scn_net_t *net, int batch, const int *h_keys, const int *h_off, const float *h_features,
+                                const int *sample_numbers, float learningRate, float momentum, float *h_probs, double *stats);
 /* One RESCALEBATCH through processBatch (SparseConvNetCUDA.cu:230-240): every layer's forwards followed by its
  * scaleWeights (NetworkInNetworkLayer.cu:203-220: weights and biases scaled by the -0.1th power of the layer's mean
  * absolute output, the scale applied underneath divided out again, the top layer left alone). */

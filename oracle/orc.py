@@ -138,6 +138,9 @@ class ReferenceGPU:
         L.refgpu_named.argtypes = [ctypes.c_char_p, c_int, c_int, c_int, c_f, c_int, c_int, c_int, c_f, c_int]
         L.refgpu_seed_fmp.argtypes = [c_p, ctypes.c_uint]
         L.refgpu_seed_dropout.argtypes = [c_p, ctypes.c_uint]
+        L.refgpu_addIndexLearnerLayer.argtypes = [c_p]
+        L.refgpu_index_learner_batch.restype, L.refgpu_index_learner_batch.argtypes = c_int, [c_p, c_int, c_p, c_p, c_p, c_int, c_f, c_f]
+        L.refgpu_results_wide.argtypes = [c_p, c_int, c_p, c_p]
         L.refgpu_layer_describe.argtypes = [c_p, c_int, c_p]
         L.refgpu_destroy.argtypes = [c_p]
         L.refgpu_addLeNetLayerMP.argtypes = [c_p] + [c_int] * 6 + [c_f, c_int]
@@ -205,6 +208,24 @@ class ReferenceGPU:
 
     def addSoftmaxLayer(self):
         self.L.refgpu_addSoftmaxLayer(self.h)
+
+    def addIndexLearnerLayer(self):
+        self.L.refgpu_addIndexLearnerLayer(self.h)
+
+    def index_learner_batch(self, keys, off, features, batch_size, learning_rate, momentum):
+        """One index-learning step of the reference on the first batch its BatchProducer draws from the pictures given.
+        -> (sample numbers of the batch, probabilities [batch x batch], dict(nll, mistakes))."""
+        keys = np.ascontiguousarray(keys, np.int64)
+        off = np.ascontiguousarray(off, np.int32)
+        features = np.ascontiguousarray(features, np.float32)
+        n = self.L.refgpu_index_learner_batch(self.h, len(off) - 1, _p(keys), _p(off), _p(features), batch_size, learning_rate, momentum)
+        err = self.L.refgpu_last_cuda_error()
+        if n < 1 or err != 0:
+            raise RuntimeError("reference index-learning step failed (%d pictures, CUDA error %d)" % (n, err))
+        probs = np.zeros((n, n), np.float32)
+        stats = np.zeros(2, np.float64)
+        self.L.refgpu_results_wide(self.h, n, _p(probs), _p(stats))
+        return self.sample_numbers(n), probs, dict(nll=float(stats[0]), mistakes=int(stats[1]))
 
     @property
     def inputSpatialSize(self):

@@ -33,6 +33,7 @@
 #define private public
 #include "NetworkInNetworkLayer.h"
 #include "NetworkInNetworkPReLULayer.h"
+#include "IndexLearnerLayer.h" // (its weights are private too: read back by refgpu_layer_weights)
 #undef private
 #include "BatchProducer.h"
 #include "ConvolutionalLayer.h"
@@ -199,6 +200,8 @@ void refgpu_layer_info(void *p, int layer, int *info, float *dropout) {
   } else if (auto n = dynamic_cast<NetworkInNetworkPReLULayer *>(L)) {
     info[0] = 1; info[1] = n->nFeaturesIn; info[2] = n->nFeaturesOut; info[3] = (int)PRELU; info[4] = 1;
     *dropout = n->dropout;
+  } else if (auto n = dynamic_cast<IndexLearnerLayer *>(L)) {
+    info[0] = 2; info[1] = n->nFeaturesIn; info[2] = n->nFeaturesOut; info[3] = (int)SOFTMAX;
   }
 }
 // The layer as the builder made it, ten ints: {type, size, stride, minActiveInputs, nFeaturesIn,
@@ -283,6 +286,53 @@ int refgpu_forward(void *p, int nSamples, const int64_t *keys, const int *off, c
   cudaDeviceSynchronize();
   return h->batch->batchSize;
 }
+void refgpu_addIndexLearnerLayer(void *p) {
+  Quiet q;
+  ((Handle *)p)->cnn->addIndexLearnerLayer();
+}
+// One index-learning step (SparseConvNetCUDA.cu:443-474) on the FIRST batch of `batchSize` pictures that the reference's
+// BatchProducer draws from the nSamples pictures given (a TRAINBATCH data set is shuffled: refgpu_sample_numbers tells
+// which pictures the batch holds, in order).  Returns the number of pictures processed.
+int refgpu_index_learner_batch(void *p, int nSamples, const int64_t *keys, const int *off, const float *features, int batchSize,
+                               float learningRate, float momentum) {
+  Quiet q;
+  Handle *h = (Handle *)p;
+  SparseConvNetCUDA &cnn = *h->cnn;
+  h->bp.reset();
+  h->batch = nullptr;
+  h->pics.clear();
+  h->ds = SpatiallySparseDataset();
+  h->ds.name = "flat";
+  h->ds.nFeatures = cnn.nInputFeatures;
+  h->ds.nClasses = cnn.nClasses;
+  h->ds.type = TRAINBATCH;
+  const int nF = cnn.nInputFeatures;
+  for (int s = 0; s < nSamples; ++s) {
+    bool bg = off[s + 1] > off[s] && keys[off[s]] < 0;
+    h->pics.emplace_back(new FlatPicture(nF, s, bg));
+    for (int r = off[s] + (bg ? 1 : 0); r < off[s + 1]; ++r) {
+      h->pics.back()->keys.push_back(keys[r]);
+      h->pics.back()->feats.insert(h->pics.back()->feats.end(), features + (size_t)r * nF, features + (size_t)(r + 1) * nF);
+    }
+    h->ds.pictures.push_back(h->pics.back().get());
+  }
+  multiplyAddCount = 0;
+  h->bp.reset(new BatchProducer(cnn, h->ds, cnn.inputSpatialSize, batchSize));
+  h->batch = h->bp->nextBatch();
+  if (!h->batch) return 0;
+  std::ofstream f;
+  cnn.processIndexLearnerBatch(*h->batch, learningRate, momentum, f);
+  cudaStreamSynchronize(cnn.memStream.stream);
+  cudaDeviceSynchronize();
+  return h->batch->batchSize;
+}
+// probabilities [batch x width] of the last batch (an index-learning batch has width = batch), stats as refgpu_results
+void refgpu_results_wide(void *p, int width, float *probs, double *stats) {
+  Handle *h = (Handle *)p;
+  SpatiallySparseBatch &b = *h->batch;
+  for (int s = 0; s < b.batchSize && probs; ++s) std::memcpy(probs + (size_t)s * width, b.probabilities[s].data(), sizeof(float) * width);
+  if (stats) { stats[0] = b.negativeLogLikelihood; stats[1] = b.mistakes; }
+}
 double refgpu_multiply_adds(void) { return (double)multiplyAddCount; }
 int refgpu_last_cuda_error(void) { return (int)cudaGetLastError(); }
 
@@ -342,5 +392,6 @@ void refgpu_layer_weights(void *p, int layer, float *W, float *B, float *prelu) 
   cudaStreamSynchronize(h->cnn->memStream.stream);
   if (auto n = dynamic_cast<NetworkInNetworkLayer *>(L)) { fetch(n->W, W); fetch(n->B, B); }
   else if (auto n = dynamic_cast<NetworkInNetworkPReLULayer *>(L)) { fetch(n->W, W); fetch(n->B, B); fetch(n->PReLU, prelu); }
+  else if (auto n = dynamic_cast<IndexLearnerLayer *>(L)) fetch(n->W, W);
 }
 }

@@ -24,7 +24,7 @@ EXPORTS = [
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_conv_tc_error_word", "scn_classifier_result_bytes", "scn_classifier_result", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
     "scn_exchange_buffer_bytes", "scn_exchange_set_timeout_ms", "scn_exchange_alloc", "scn_exchange_free", "scn_exchange_open", "scn_exchange_close", "scn_exchange_publish", "scn_exchange_collect", "scn_exchange_step",
-    "scn_mask_columns", "scn_sgd_update_masked", "scn_softmax_nll_backward", "scn_activation_backward", "scn_conv_nin_backward_weights", "scn_conv_nin_backward_weights_tc_bytes", "scn_conv_nin_backward_weights_tc", "scn_transpose_weights", "scn_gather_backward",
+    "scn_mask_columns", "scn_sgd_update_masked", "scn_gather_columns", "scn_scatter_columns_axpy", "scn_softmax_nll_backward", "scn_activation_backward", "scn_conv_nin_backward_weights", "scn_conv_nin_backward_weights_tc_bytes", "scn_conv_nin_backward_weights_tc", "scn_transpose_weights", "scn_gather_backward",
     "scn_maxpool_backward", "scn_terminal_pool_backward", "scn_sgd_update",
 ]
 

@@ -237,6 +237,21 @@ __global__ void k_sgd_update_masked(float *__restrict__ w, float *__restrict__ m
   }
 }
 
+// Index learning (IndexLearnerLayer.cu:57-66, 8-20): a batch uses only the columns of W [K x N] that its own samples
+// index.  w[k][j] = W[k][idx[j]] on the way in, W[k][idx[j]] += alpha * d[k][j] on the way out (no momentum).
+__global__ void k_gather_columns(const float *__restrict__ W, int K, int N, const int *__restrict__ idx, int n, float *__restrict__ w) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)K * n; i += (long long)gridDim.x * blockDim.x) {
+    const long long k = i / n;
+    w[i] = W[k * N + idx[i - k * n]];
+  }
+}
+__global__ void k_scatter_columns_axpy(float *__restrict__ W, int K, int N, const int *__restrict__ idx, int n, const float *__restrict__ d, float alpha) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < (long long)K * n; i += (long long)gridDim.x * blockDim.x) {
+    const long long k = i / n;
+    W[k * N + idx[i - k * n]] += alpha * d[i]; // (the indices of a batch are distinct: no two threads share an element)
+  }
+}
+
 // ---- the weight gradient on the tensor cores: dW[K x N] = Xg^T[K x rows] * d[rows x N] is the forward kernel's product with
 // the roles turned: its "rows" are the K gathered input channels, its contraction runs over the layer's rows, its
 // "weights" are the output gradient.  The gathered input is written once, transposed ([Kp x rowsP], Kp and rowsP padded
@@ -503,5 +518,26 @@ extern "C" int scn_sgd_update_masked(float *d_w, float *d_momentum, const float 
                                                                                  d_row_mask ? row_period : 1, d_col_mask, learningRate, momentum,
                                                                                  keep_positive);
   SCN_LAUNCH_CHECK("k_sgd_update_masked");
+  return SCN_OK;
+}
+
+
+extern "C" int scn_gather_columns(const float *d_W, int K, int N, const int *d_idx, int n, float *d_w, scn_stream_t stream) {
+  clear_error();
+  if (K < 1 || N < 1 || n < 0) return fail(SCN_ERR_INVALID, "bad column-gather sizes");
+  if (n == 0) return SCN_OK;
+  if (!d_W || !d_idx || !d_w) return fail(SCN_ERR_INVALID, "null pointer");
+  k_gather_columns<<<grid_for((long long)K * n, 256), 256, 0, (cudaStream_t)stream>>>(d_W, K, N, d_idx, n, d_w);
+  SCN_LAUNCH_CHECK("k_gather_columns");
+  return SCN_OK;
+}
+
+extern "C" int scn_scatter_columns_axpy(float *d_W, int K, int N, const int *d_idx, int n, const float *d_delta, float alpha, scn_stream_t stream) {
+  clear_error();
+  if (K < 1 || N < 1 || n < 0) return fail(SCN_ERR_INVALID, "bad column-scatter sizes");
+  if (n == 0) return SCN_OK;
+  if (!d_W || !d_idx || !d_delta) return fail(SCN_ERR_INVALID, "null pointer");
+  k_scatter_columns_axpy<<<grid_for((long long)K * n, 256), 256, 0, (cudaStream_t)stream>>>(d_W, K, N, d_idx, n, d_delta, alpha);
+  SCN_LAUNCH_CHECK("k_scatter_columns_axpy");
   return SCN_OK;
 }

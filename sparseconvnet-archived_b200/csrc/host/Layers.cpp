@@ -6,6 +6,7 @@
 #include <random>
 #include "ConvolutionalLayer.h"
 #include "ConvolutionalTriangularLayer.h"
+#include "IndexLearnerLayer.h"
 #include "MaxPoolingLayer.h"
 #include "MaxPoolingTriangularLayer.h"
 #include "NetworkInNetworkLayer.h"
@@ -932,4 +933,116 @@ void NetworkInNetworkPReLULayer::updateSlopes(float learningRate, float momentum
     return;
   }
   scnSafeCall(scn_sgd_update(PReLU.dPtr(), MPReLU.dPtr(), dprelu.dPtr(), nFeaturesOut, learningRate, momentum, 1, memStream.stream));
+}
+
+// ------------------------------------------------------------------ IndexLearnerLayer (index learning: every picture its own class)
+IndexLearnerLayer::IndexLearnerLayer(cudaMemStream &memStream, cublasHandle_t &, int nFeaturesIn, int nFeaturesOut)
+    : SpatiallySparseLayer(memStream), W(true, 0), nFeaturesIn(nFeaturesIn), nFeaturesOut(nFeaturesOut), indices(false, 0) {
+  std::cout << "IndexLearnerLayer" << std::endl;
+  zeroed(W, nFeaturesIn * nFeaturesOut, memStream); // IndexLearnerLayer.cu:29-31: the weights start at zero
+  changesGeometry = false;
+}
+// IndexLearnerLayer.cu:35-45: only a TRAINBATCH runs this layer (processIndexLearnerBatch stops one layer early otherwise).
+long long IndexLearnerLayer::enqueueRules(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                                          long long rowsInBound, int *) {
+  if (input.nFeatures != nFeaturesIn) throw ScnException("IndexLearnerLayer: wrong number of input features");
+  output.nFeatures = nFeaturesOut;
+  output.spatialSize = input.spatialSize;
+  output.gridOwner = input.gridOwner;
+  return rowsInBound;
+}
+void IndexLearnerLayer::finishRules(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, const int *) {
+  output.nFeatures = nFeaturesOut;
+  output.spatialSize = input.spatialSize;
+  output.nSpatialSites = input.nSpatialSites;
+  output.maxSitesPerSample = input.maxSitesPerSample;
+  output.gridOwner = input.gridOwner;
+  output.backpropErrors = true;
+  output.learntOutput = true;
+}
+void IndexLearnerLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  enqueueRules(batch, input, output, input.nSpatialSites, nullptr);
+  finishRules(batch, input, output, nullptr);
+}
+// IndexLearnerLayer.cu:47-70: softmax(X w) with w the batch's columns of W; no bias.
+void IndexLearnerLayer::forwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  const int n = (int)indexLearnerIndices.size(), rows = output.nSpatialSites;
+  if (n < 1 || n > 1024) throw ScnException("IndexLearnerLayer: a batch of 1..1024 pictures is needed (set indexLearnerIndices)");
+  for (int i : indexLearnerIndices)
+    if (i < 0 || i >= nFeaturesOut) throw ScnException("IndexLearnerLayer: a picture's index exceeds the layer's width (the size of the training set)");
+  output.featuresPresent.hVector() = indexLearnerIndices;
+  indices.copyToCPU();
+  indices.hVector() = indexLearnerIndices;
+  output.sub->features.resize(rows * n);
+  output.sub->dfeatures.resize(rows * n);
+  w.copyToGPU();
+  w.resize(nFeaturesIn * n);
+  cudaStream_t s = memStream.stream;
+  scnSafeCall(scn_gather_columns(W.dPtr(), nFeaturesIn, nFeaturesOut, indices.dPtr(), n, w.dPtr(), s));
+  if ((int)zeroBias.size() < std::max(n, nFeaturesIn)) zeroed(zeroBias, std::max(n, nFeaturesIn), memStream);
+  scnSafeCall(scn_conv_nin_forward_ws(input.sub->features.dPtr(), nullptr, rows, 1, nFeaturesIn, w.dPtr(), nullptr, zeroBias.dPtr(), nullptr, n, 1.0f,
+                                      SCN_SOFTMAX, SCN_PREC_FP32, output.sub->features.dPtr(), nullptr, 0, s));
+  multiplyAddCount += (__int128_t)rows * nFeaturesIn * n;
+}
+// IndexLearnerLayer.cu:71-100: dw = X^T d, the input's gradient d w^T, and the update of the batch's columns without momentum.
+void IndexLearnerLayer::backwards(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                                  float learningRate, float) {
+  const int n = (int)indexLearnerIndices.size(), rows = output.nSpatialSites, K = nFeaturesIn;
+  cudaStream_t s = memStream.stream;
+  if ((int)output.sub->dfeatures.size() != rows * n) throw ScnException("IndexLearnerLayer::backwards: the output's gradient is missing");
+  float *d = output.sub->dfeatures.dPtr();
+  dw.copyToGPU(); db.copyToGPU();
+  dw.resize(K * n); db.resize(n);
+  scnSafeCall(scn_conv_nin_backward_weights(input.sub->features.dPtr(), nullptr, rows, 1, K, d, n, dw.dPtr(), db.dPtr(), s));
+  if (input.backpropErrors && rows > 0) {
+    wt.copyToGPU();
+    wt.resize(K * n);
+    scnSafeCall(scn_transpose_weights(w.dPtr(), K, n, wt.dPtr(), s));
+    input.sub->dfeatures.resize(rows * K);
+    scnSafeCall(scn_conv_nin_forward_ws(d, nullptr, rows, 1, n, wt.dPtr(), nullptr, zeroBias.dPtr(), nullptr, K, 1.0f, SCN_NOSIGMOID, SCN_PREC_FP32,
+                                        input.sub->dfeatures.dPtr(), nullptr, 0, s));
+    int period = 0;
+    if (const float *mask = presentMaskAt(batch, input, period)) // features the batch dropped below this layer
+      scnSafeCall(scn_mask_columns(input.sub->dfeatures.dPtr(), (long long)rows * (K / period), period, mask, s));
+    multiplyAddCount += (__int128_t)rows * K * n;
+  }
+  multiplyAddCount += (__int128_t)rows * K * n;
+  // (a dropped input feature's column of X is zero, so its row of dw is zero and its weights stay as they are)
+  scnSafeCall(scn_scatter_columns_axpy(W.dPtr(), K, nFeaturesOut, indices.dPtr(), n, dw.dPtr(), -learningRate, s));
+}
+void IndexLearnerLayer::loadWeightsFromStream(std::ifstream &f, bool) { // IndexLearnerLayer.cu:101-103: the weights alone
+  std::vector<float> &h = W.hVector();
+  f.read((char *)h.data(), sizeof(float) * h.size());
+  if (!f) throw ScnException("weight file ends early");
+}
+void IndexLearnerLayer::putWeightsToStream(std::ofstream &f, bool) {
+  const bool on = W.onGPU;
+  std::vector<float> &h = W.hVector();
+  f.write((char *)h.data(), sizeof(float) * h.size());
+  if (on) W.copyToGPU();
+}
+int IndexLearnerLayer::calculateInputSpatialSize(int outputSpatialSize) { return outputSpatialSize; }
+
+void IndexLearner(SpatiallySparseBatchInterface &input, SpatiallySparseBatch &batch, int nTop, cudaMemStream &memStream) {
+  const int n = batch.batchSize;
+  if (n != input.nSpatialSites || (size_t)n * n != input.sub->features.size()) throw ScnException("IndexLearner: the top layer must hold one row per picture and one column per picture of the batch");
+  if (batch.type != TRAINBATCH) throw ScnException("IndexLearner: a TRAINBATCH is needed");
+  // the backward pass starts here: d cost / d (softmax input) with picture i's class = column i (IndexLearnerLayer.cu:129-141)
+  vectorCUDA<int> own(false, 0);
+  own.hVector() = range(n);
+  input.sub->dfeatures.resize(n * n);
+  scnSafeCall(scn_softmax_nll_backward(input.sub->features.dPtr(), own.dPtr(), n, n, input.sub->dfeatures.dPtr(), memStream.stream));
+  std::vector<float> probs((size_t)n * n);
+  cudaSafeCall(cudaMemcpyAsync(probs.data(), input.sub->features.dPtr(), sizeof(float) * probs.size(), cudaMemcpyDeviceToHost, memStream.stream));
+  cudaSafeCall(cudaStreamSynchronize(memStream.stream)); // (also: `own` is read before it goes out of scope)
+  for (int i = 0; i < n; ++i) {
+    batch.probabilities.emplace_back(probs.begin() + (size_t)i * n, probs.begin() + (size_t)(i + 1) * n);
+    batch.predictions.push_back(vectorTopIndices(batch.probabilities.back(), nTop));
+  }
+  batch.mistakes += n;
+  for (int i = 0; i < n; ++i) {
+    batch.negativeLogLikelihood -= std::log(std::max(batch.probabilities[i][i], 1.0e-15f));
+    for (int j = 0; j < nTop; ++j)
+      if (batch.predictions[i][j] == i) batch.mistakes--;
+  }
 }

@@ -28,6 +28,8 @@ public:
                           float dropout = 0.0f, int minActiveInputs = 1);
   void addTerminalPoolingLayer(int poolSize);
   void addSoftmaxLayer();
+  void addIndexLearnerLayer();
+  float processIndexLearnerDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0.0, float momentum = 0.99);
   float processDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0, float momentum = 0.99);
   void processDatasetRepeatTest(SpatiallySparseDataset &dataset, int batchSize = 100, int nReps = 12,
                                 std::string predictionsFilename = "", std::string confusionMatrixFilename = "");
@@ -44,6 +46,8 @@ public:
                        ActivationFunction activationFn = RELU, float dropout = 0.0f, int minActiveInputs = 1);
   void addTerminalPoolingLayer(int poolSize);
   void addSoftmaxLayer();
+  void addIndexLearnerLayer();
+  float processIndexLearnerDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0.0, float momentum = 0.99);
   float processDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0, float momentum = 0.99);
   void processDatasetRepeatTest(SpatiallySparseDataset &dataset, int batchSize = 100, int nReps = 12,
                                 std::string predictionsFilename = "", std::string confusionMatrixFilename = "");

@@ -1,4 +1,5 @@
 #include "SparseConvNetCUDA.h"
+#include "IndexLearnerLayer.h"
 #include <chrono>
 #include <cmath>
 #include "BatchProducer.h"
@@ -153,6 +154,19 @@ void SparseConvNetCUDA::addSoftmaxLayer() {
   std::cout << std::endl;
 }
 
+// SparseConvNetCUDA.cu:211-225: "nClasses" is the number of pictures of the training set.
+void SparseConvNetCUDA::addIndexLearnerLayer() {
+  std::cout << layers.size() << ":";
+  layers.push_back(new IndexLearnerLayer(memStream, cublasHandle, nOutputFeatures, nClasses));
+  std::cout << "Index Learner " << nOutputFeatures << "-> " << nClasses << std::endl;
+  nOutputFeatures = nClasses;
+  inputSpatialSize = 1;
+  for (int i = (int)layers.size() - 1; i >= 0; --i) inputSpatialSize = layers[i]->calculateInputSpatialSize(inputSpatialSize);
+  std::cout << "Spatially sparse CNN: input size " << inputSpatialSize;
+  for (int i = 1; i < dimension; ++i) std::cout << "x" << inputSpatialSize;
+  std::cout << std::endl;
+}
+
 void SparseConvNetCUDA::prepareBatch(SpatiallySparseBatch &batch) {
   if (batch.interfaces.size() == layers.size() + 1) return;
   batch.interfaces.reserve(layers.size() + 1); // before any pointer into the vector exists
@@ -271,8 +285,9 @@ void SparseConvNetCUDA::preprocessBatchOnDevice(SpatiallySparseBatch &batch) {
   for (int i = 0; i < nL; ++i) layers[i]->finishRules(batch, batch.interfaces[i], batch.interfaces[i + 1], counts.data() + 4 * i);
 }
 
-void SparseConvNetCUDA::forwardLayers(SpatiallySparseBatch &batch) {
-  for (size_t i = 0; i < layers.size(); ++i) {
+void SparseConvNetCUDA::forwardLayers(SpatiallySparseBatch &batch, size_t count) {
+  count = std::min(count, layers.size());
+  for (size_t i = 0; i < count; ++i) {
     if (timing) cudaSafeCall(cudaEventRecord(events[i], memStream.stream));
     if ((int)i == 1 && earlyLayers == 2) { // already running: launched behind the rule chain
       static_cast<NetworkInNetworkLayer *>(layers[1])->finishEarly(batch.interfaces[1], batch.interfaces[2]);
@@ -295,7 +310,7 @@ void SparseConvNetCUDA::forwardLayers(SpatiallySparseBatch &batch) {
     batch.interfaces[i + 1].sub->reset();
     batch.interfaces[i + 1].deferredFrom = nullptr;
     batch.interfaces[i + 1].deferredLearnt = nullptr;
-    if (fuseClassifier && i + 1 < layers.size()) { // a learnt layer of few rows and the small learnt layer behind it (the classifier) as one call
+    if (fuseClassifier && i + 1 < count) { // a learnt layer of few rows and the small learnt layer behind it (the classifier) as one call
       auto a = dynamic_cast<NetworkInNetworkLayer *>(layers[i]);
       auto b = dynamic_cast<NetworkInNetworkLayer *>(layers[i + 1]);
       if (a && b) {
@@ -311,7 +326,7 @@ void SparseConvNetCUDA::forwardLayers(SpatiallySparseBatch &batch) {
     }
     layers[i]->forwards(batch, batch.interfaces[i], batch.interfaces[i + 1]);
   }
-  if (timing) cudaSafeCall(cudaEventRecord(events[layers.size()], memStream.stream));
+  if (timing) cudaSafeCall(cudaEventRecord(events[count], memStream.stream));
 }
 void SparseConvNetCUDA::enableTiming(bool on) {
   timing = on;
@@ -372,6 +387,60 @@ void SparseConvNetCUDA::processBatch(SpatiallySparseBatch &batch, float learning
       for (size_t k = 0; k < p.size(); ++k) g << (k ? " " : "") << p[k];
       g << std::endl;
     }
+}
+
+// SparseConvNetCUDA.cu:443-474: every layer but the index learner runs forwards; `f`, if open, receives the features under
+// the index learner ("sample number, label, features" per picture); a TRAINBATCH then runs the index learner on the
+// columns of its own pictures, IndexLearner, and every layer's backwards.
+void SparseConvNetCUDA::processIndexLearnerBatch(SpatiallySparseBatch &batch, float learningRate, float momentum, std::ofstream &f) {
+  const int n = (int)layers.size();
+  auto top = n ? dynamic_cast<IndexLearnerLayer *>(layers[n - 1]) : nullptr;
+  if (!top) throw ScnException("processIndexLearnerBatch: the network's last layer must be an IndexLearnerLayer (addIndexLearnerLayer)");
+  forwardLayers(batch, n - 1);
+  SpatiallySparseBatchInterface &under = batch.interfaces[n - 1];
+  if (f.is_open()) {
+    cudaSafeCall(cudaStreamSynchronize(memStream.stream));
+    if (under.nSpatialSites != batch.batchSize) throw ScnException("processIndexLearnerBatch: the layer under the index learner must hold one row per picture");
+    std::vector<float> feat((size_t)batch.batchSize * under.nFeatures);
+    if (!feat.empty()) cudaSafeCall(cudaMemcpy(feat.data(), under.sub->features.dPtr(), sizeof(float) * feat.size(), cudaMemcpyDeviceToHost));
+    std::vector<int> &labels = batch.labels.hVector();
+    for (int i = 0; i < batch.batchSize; ++i) {
+      f << batch.sampleNumbers[i] << " " << (i < (int)labels.size() ? labels[i] : -1);
+      for (int j = 0; j < under.nFeatures; ++j) f << " " << feat[(size_t)i * under.nFeatures + j];
+      f << std::endl;
+    }
+  }
+  if (batch.type == TRAINBATCH) {
+    top->indexLearnerIndices = batch.sampleNumbers;
+    batch.interfaces[n].sub->reset();
+    top->forwards(batch, under, batch.interfaces[n]);
+    IndexLearner(batch.interfaces[n], batch, nTop, memStream);
+    for (int i = n - 1; i >= 0; --i) layers[i]->backwards(batch, batch.interfaces[i], batch.interfaces[i + 1], learningRate, momentum);
+  }
+}
+
+// SparseConvNetCUDA.cu:475-510: one pass; a data set that is not a training set writes "<name>.features" instead of learning.
+float SparseConvNetCUDA::processIndexLearnerDataset(SpatiallySparseDataset &dataset, int batchSize, float learningRate, float momentum) {
+  if (dataset.pictures.empty()) throw ScnException("processIndexLearnerDataset: empty dataset");
+  float errorRate = 0, nll = 0;
+  multiplyAddCount = 0;
+  auto start = std::chrono::system_clock::now();
+  std::ofstream f;
+  BatchProducer bp(*this, dataset, inputSpatialSize, batchSize);
+  if (dataset.type != TRAINBATCH) f.open((dataset.name + ".features").c_str());
+  while (SpatiallySparseBatch *batch = bp.nextBatch()) {
+    processIndexLearnerBatch(*batch, learningRate, momentum, f);
+    errorRate += batch->mistakes * 1.0 / dataset.pictures.size();
+    nll += batch->negativeLogLikelihood * 1.0 / dataset.pictures.size();
+  }
+  auto end = std::chrono::system_clock::now();
+  double diff = std::chrono::duration_cast<std::chrono::nanoseconds>(end - start).count();
+  if (dataset.type == TRAINBATCH)
+    std::cout << dataset.name << " Mistakes:" << 100.0 * errorRate << "% NLL:" << nll
+              << " MegaMultiplyAdds/sample:" << std::round((double)multiplyAddCount / dataset.pictures.size() / 1000000) << " time:" << diff / 1000000000L
+              << "s GigaMultiplyAdds/s:" << std::round((double)multiplyAddCount / diff) << " rate:" << std::round(dataset.pictures.size() * 1000000000.0f / diff)
+              << "/s" << std::endl;
+  return nll; // (SparseConvNetCUDA.cu:505)
 }
 
 // One pass over a dataset (SparseConvNetCUDA.cu:272-326): prints the reference's summary line and returns the mean

@@ -56,6 +56,9 @@ public:
   void addTriangularLeNetLayerMP(int nFeatures, int filterSize, int filterStride, int poolSize, int poolStride,
                                  ActivationFunction activationFn = RELU, float dropout = 0.0f, int minActiveInputs = 1);
   void addSoftmaxLayer();
+  void addIndexLearnerLayer();
+  void processIndexLearnerBatch(SpatiallySparseBatch &batch, float learningRate, float momentum, std::ofstream &f);
+  float processIndexLearnerDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0.0, float momentum = 0.99);
   void addTerminalPoolingLayer(int poolSize, int S);
   float processDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0, float momentum = 0.99);
   void processDatasetRepeatTest(SpatiallySparseDataset &dataset, int batchSize = 100, int nReps = 12,
@@ -70,7 +73,7 @@ public:
   // Grow batch.interfaces to layers.size()+1.
   void prepareBatch(SpatiallySparseBatch &batch);
   // Forward of all layers without the classifier read-back.
-  void forwardLayers(SpatiallySparseBatch &batch);
+  void forwardLayers(SpatiallySparseBatch &batch, size_t count = (size_t)-1); // the first `count` layers
   // CUDA-event timing per layer (off by default).  layerTimes() waits for the stream and
   // returns layers.size()+1 values in ms: each layer's forwards(), then the rule chain.
   void enableTiming(bool on);

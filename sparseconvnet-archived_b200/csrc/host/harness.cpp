@@ -8,6 +8,7 @@
 #include "MaxPoolingLayer.h"
 #include "MaxPoolingTriangularLayer.h"
 #include "NetworkArchitectures.h"
+#include "IndexLearnerLayer.h"
 #include "NetworkInNetworkLayer.h"
 #include "NetworkInNetworkPReLULayer.h"
 #include "ResultExchange.h"
@@ -86,6 +87,9 @@ void describe(SpatiallySparseLayer *L, int *info, float *dropout) {
     std::memcpy(v, w, sizeof(v));
   } else if (auto t = dynamic_cast<TerminalPoolingLayer *>(L)) {
     int w[10] = {5, t->poolSize, 1, 1, 0, 0, 1, 0, t->inSpatialSize, t->outSpatialSize};
+    std::memcpy(v, w, sizeof(v));
+  } else if (auto x = dynamic_cast<IndexLearnerLayer *>(L)) {
+    int w[10] = {7, 1, 1, 1, x->nFeaturesIn, x->nFeaturesOut, 1, (int)SOFTMAX, 0, 0};
     std::memcpy(v, w, sizeof(v));
   }
   std::memcpy(info, v, sizeof(v));
@@ -248,6 +252,7 @@ int scn_net_addTerminalPoolingLayer(scn_net_t *net, int poolSize) {
   });
 }
 int scn_net_addSoftmaxLayer(scn_net_t *net) { return guarded([&] { Quiet q; net->cnn->addSoftmaxLayer(); }); }
+int scn_net_addIndexLearnerLayer(scn_net_t *net) { return guarded([&] { Quiet q; net->cnn->addIndexLearnerLayer(); }); }
 
 scn_net_t *scn_net_DeepCNet(int dimension, int l, int k, int fn, int nInputFeatures, int nClasses, float p, int nTop, void *stream) {
   scn_net_t *n = scn_net_create(dimension, nInputFeatures, nClasses, nTop, 0, stream);
@@ -534,6 +539,23 @@ int scn_net_iface_present(scn_net_t *net, int i, int *present) {
   return n;
 }
 
+int scn_net_index_learner_batch(scn_net_t *net, int batch, const int *keys, const int *off, const float *features, const int *sample_numbers,
+                                float learningRate, float momentum, float *probs, double *stats) {
+  return guarded([&] {
+    SparseConvNetCUDA &cnn = *net->cnn;
+    if (!sample_numbers) throw ScnException("an index-learning step needs the pictures' numbers in the data set");
+    SpatiallySparseBatch &b = uploadHostInput(net, batch, keys, off, features, TRAINBATCH);
+    b.sampleNumbers.assign(sample_numbers, sample_numbers + batch);
+    cnn.preprocessBatchOnDevice(b);
+    std::ofstream nof;
+    cnn.processIndexLearnerBatch(b, learningRate, momentum, nof);
+    net->last = &b;
+    cudaSafeCall(cudaStreamSynchronize(cnn.memStream.stream));
+    for (int i = 0; i < batch && probs; ++i) std::memcpy(probs + (size_t)i * batch, b.probabilities[i].data(), sizeof(float) * batch);
+    if (stats) { stats[0] = b.negativeLogLikelihood; stats[1] = b.mistakes; }
+  });
+}
+
 int scn_net_rescale_batch(scn_net_t *net, int batch, const int *keys, const int *off, const float *features) {
   return guarded([&] {
     Quiet q; // (every learnt layer prints its featureScale line, as the reference does)
@@ -549,14 +571,15 @@ int scn_net_rescale_batch(scn_net_t *net, int batch, const int *keys, const int 
 
 int scn_net_get_weights(scn_net_t *net, int layer, float *W, float *B, float *prelu) {
   return guarded([&] {
-    auto n = dynamic_cast<NetworkInNetworkLayer *>(net->cnn->layers.at(layer));
-    if (!n) throw ScnException("layer has no weights");
-    cudaSafeCall(cudaStreamSynchronize(net->cnn->memStream.stream));
     auto fetch = [&](vectorCUDA<float> &v, float *dst) {
       if (!dst || !v.size()) return;
       if (v.onGPU) cudaSafeCall(cudaMemcpy(dst, v.dPtr(), sizeof(float) * v.size(), cudaMemcpyDeviceToHost));
       else std::memcpy(dst, v.hVector().data(), sizeof(float) * v.size());
     };
+    cudaSafeCall(cudaStreamSynchronize(net->cnn->memStream.stream));
+    if (auto x = dynamic_cast<IndexLearnerLayer *>(net->cnn->layers.at(layer))) { fetch(x->W, W); return; } // (no bias)
+    auto n = dynamic_cast<NetworkInNetworkLayer *>(net->cnn->layers.at(layer));
+    if (!n) throw ScnException("layer has no weights");
     fetch(n->W, W);
     fetch(n->B, B);
     if (auto pr = dynamic_cast<NetworkInNetworkPReLULayer *>(n)) fetch(pr->PReLU, prelu);

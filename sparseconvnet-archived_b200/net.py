@@ -21,7 +21,7 @@ EXPORTS = [
     "scn_net_layer_times", "scn_net_process_dataset", "scn_host_vectorTopIndices",
     "scn_net_exchange_create", "scn_net_exchange_buffer", "scn_net_exchange_connect", "scn_net_exchange_connect_local", "scn_net_exchange_destroy",
     "scn_net_forward_host_exchange", "scn_net_exchange_flush", "scn_net_exchange_step_device",
-    "scn_net_forward_host_begin", "scn_net_forward_host_end", "scn_net_rescale_batch", "scn_net_set_dropout_features", "scn_net_iface_present",
+    "scn_net_forward_host_begin", "scn_net_forward_host_end", "scn_net_rescale_batch", "scn_net_addIndexLearnerLayer", "scn_net_index_learner_batch", "scn_net_set_dropout_features", "scn_net_iface_present",
 ]
 
 LAYER_KEYS = ("type", "size", "stride", "minActive", "nIn", "nOut", "fs", "act", "inSpatial", "outSpatial")
@@ -89,6 +89,8 @@ def lib():
         L.scn_net_forward_host_begin.argtypes = [c_p, c_int, c_p, c_p, c_p]
         L.scn_net_rescale_batch.argtypes = [c_p, c_int, c_p, c_p, c_p]
         L.scn_net_set_dropout_features.argtypes = [c_p, c_int, c_p, c_int]
+        L.scn_net_addIndexLearnerLayer.argtypes = [c_p]
+        L.scn_net_index_learner_batch.argtypes = [c_p, c_int, c_p, c_p, c_p, c_p, c_f, c_f, c_p, c_p]
         L.scn_net_iface_present.argtypes = [c_p, c_int, c_p]
         L.scn_net_forward_host_end.argtypes = [c_p, c_p, c_p, c_p, c_p]
         _lib = L
@@ -318,6 +320,23 @@ class Net:
         probs = np.empty((B, self.nClasses), np.float32)
         stats = np.zeros(2, np.float64)
         _check(self.L.scn_net_train_batch(self.h, B, _np(keys), _np(off), _np(features), _np(labels), learning_rate, momentum, _np(probs), _np(stats)))
+        return probs, dict(nll=float(stats[0]), mistakes=int(stats[1]))
+
+    def addIndexLearnerLayer(self):
+        _check(self.L.scn_net_addIndexLearnerLayer(self.h))
+
+    def index_learner_batch(self, keys, off, features, sample_numbers, learning_rate, momentum):
+        """One index-learning step: every picture is its own class among the pictures of the batch.
+        -> (probabilities [batch x batch], dict(nll, mistakes))."""
+        keys = np.ascontiguousarray(keys, np.int32)
+        off = np.ascontiguousarray(off, np.int32)
+        features = np.ascontiguousarray(features, np.float32)
+        sample_numbers = np.ascontiguousarray(sample_numbers, np.int32)
+        B = len(off) - 1
+        probs = np.zeros((B, B), np.float32)
+        stats = np.zeros(2, np.float64)
+        _check(self.L.scn_net_index_learner_batch(self.h, B, _np(keys), _np(off), _np(features), _np(sample_numbers), learning_rate, momentum,
+                                                  _np(probs), _np(stats)))
         return probs, dict(nll=float(stats[0]), mistakes=int(stats[1]))
 
     def rescale_batch(self, keys, off, features):

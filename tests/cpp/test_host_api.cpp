@@ -4,6 +4,7 @@
 // Built and run by tests/test_gpu_cpp_api.py on a B200; prints "OK" lines and exits 0 on success.
 #include <cmath>
 #include <cstdio>
+#include <sstream>
 #include <cstdlib>
 #include <random>
 #include <vector>
@@ -229,6 +230,41 @@ int main() {
       const float test = d.processDataset(ds, 4);
       CHECK(std::isfinite(test));
       std::printf("OK training with dropout (NLL %.3f -> %.3f)\n", first, last);
+    }
+    // ---- 5d. index learning (SparseConvNet.h:50, 57-60): every picture its own class; a data set that is not a training
+    //          set writes "<name>.features" (sample number, label, the features under the index learner)
+    {
+      SparseConvNet inet(2, 3, (int)ds.pictures.size());
+      inet.addLeNetLayerMP(32, 3, 1, 2, 2, VLEAKYRELU, 0.0f);
+      inet.addLeNetLayerMP(64, 2, 1, 2, 2, VLEAKYRELU, 0.0f);
+      inet.addLeNetLayerMP(96, 2, 1, 1, 1, VLEAKYRELU, 0.0f);
+      inet.addIndexLearnerLayer();
+      CHECK(inet.cnn->inputSpatialSize == S);
+      fillWeights(*inet.cnn, 8); // (leaves the index learner's weights at zero: it is no NetworkInNetworkLayer)
+      ds.type = TRAINBATCH;
+      const float first = inet.processIndexLearnerDataset(ds, 4, 0.01f, 0.9f);
+      float last = first;
+      for (int epoch = 0; epoch < 15; ++epoch) last = inet.processIndexLearnerDataset(ds, 4, 0.01f, 0.9f);
+      CHECK(std::isfinite(first) && std::isfinite(last) && last < first);
+      ds.type = TESTBATCH;
+      ds.name = "cpp-test-index";
+      inet.processIndexLearnerDataset(ds, 4);
+      std::ifstream ff("cpp-test-index.features");
+      int lines = 0;
+      std::string line;
+      while (std::getline(ff, line)) {
+        std::istringstream is(line);
+        int number, label, count = 0;
+        float v;
+        is >> number >> label;
+        while (is >> v) ++count;
+        CHECK(count == 96 && number == lines);
+        ++lines;
+      }
+      CHECK(lines == (int)ds.pictures.size());
+      std::remove("cpp-test-index.features");
+      ds.name = "cpp-test";
+      std::printf("OK index learning (NLL %.3f -> %.3f)\n", first, last);
     }
     // ---- 6. fractional max-pooling: a named FMP network, and the host gridRules over FractionalPoolingRegions
     {
