@@ -352,8 +352,8 @@ int scn_classifier_result(const float *d_probs, int rows, int nClasses, int nTop
 /* ------------------------------------------------------------------ backward pass (training step)
  * The reference runs every layer's backwards() in reverse order behind SoftmaxClassifier
  * (SparseConvNetCUDA.cu:247-251).  Training-time dropout (random feature subsets and the
- * shrunk weight matrices, NetworkInNetworkLayer.cu:162-186) is not built: these entry points
- * serve layers whose dropout is 0. */
+ * shrunk weight matrices, NetworkInNetworkLayer.cu:162-186) keeps full-width matrices here:
+ * see scn_mask_columns and scn_sgd_update_masked below. */
 
 /* Replaces dDerivativeOfCostWRTpreSoftmaxTopLevelWeights (SoftmaxClassifier.cu:7-14, 27-33):
  * d_dfeatures[r][c] = d_probs[r][c] - (c == d_labels[r]), not averaged over the batch. */

@@ -1,7 +1,6 @@
 // The public facade (SparseConvNet.h:20-99): thin forwarding classes over SparseConvNetCUDA
 // for square/cubic lattices (SparseConvNet) and triangular/tetrahedral ones
-// (SparseConvTriangLeNet), fractional max-pooling builders included.  The index-learner head
-// (training only) is not built.
+// (SparseConvTriangLeNet), fractional max-pooling builders and the index-learner head included.
 #pragma once
 #include <memory>
 #include <string>

@@ -1,7 +1,7 @@
 // Layer interface (SpatiallySparseLayer.h:6-27).  preprocess() builds the output grids and
 // rules (on the device here), forwards() enqueues the layer's kernels on memStream.stream
-// and returns without synchronising; backwards() enqueues the layer's share of a training step
-// (for layers without training-time dropout); scaleWeights() is a learnt layer's share of a RESCALEBATCH pass.
+// and returns without synchronising; backwards() enqueues the layer's share of a training step;
+// scaleWeights() is a learnt layer's share of a RESCALEBATCH pass.
 #pragma once
 #include <fstream>
 #include <iostream>
