@@ -29,6 +29,8 @@ public:
   void addSoftmaxLayer();
   void addIndexLearnerLayer();
   float processIndexLearnerDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0.0, float momentum = 0.99);
+  void processDatasetDumpTopLevelFeatures(SpatiallySparseDataset &dataset, int batchSize, int reps = 1);
+  void calculateInputRegularizingConstants(SpatiallySparseDataset dataset);
   float processDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0, float momentum = 0.99);
   void processDatasetRepeatTest(SpatiallySparseDataset &dataset, int batchSize = 100, int nReps = 12,
                                 std::string predictionsFilename = "", std::string confusionMatrixFilename = "");
@@ -47,6 +49,8 @@ public:
   void addSoftmaxLayer();
   void addIndexLearnerLayer();
   float processIndexLearnerDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0.0, float momentum = 0.99);
+  void processDatasetDumpTopLevelFeatures(SpatiallySparseDataset &dataset, int batchSize, int reps = 1);
+  void calculateInputRegularizingConstants(SpatiallySparseDataset dataset);
   float processDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0, float momentum = 0.99);
   void processDatasetRepeatTest(SpatiallySparseDataset &dataset, int batchSize = 100, int nReps = 12,
                                 std::string predictionsFilename = "", std::string confusionMatrixFilename = "");

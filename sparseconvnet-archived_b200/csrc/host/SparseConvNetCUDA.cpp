@@ -443,6 +443,59 @@ float SparseConvNetCUDA::processIndexLearnerDataset(SpatiallySparseDataset &data
   return nll; // (SparseConvNetCUDA.cu:505)
 }
 
+// SparseConvNetCUDA.cu:507-535: every layer but the last runs forwards and the features under it go to "<name>.features"
+// ("sample number, label, features" per picture), `reps` passes over a data set that is not a training set.
+void SparseConvNetCUDA::processBatchDumpTopLevelFeaturess(SpatiallySparseBatch &batch, std::ofstream &f) {
+  const int n = (int)layers.size();
+  if (n < 1) throw ScnException("processBatchDumpTopLevelFeaturess: the network has no layers");
+  forwardLayers(batch, n - 1);
+  cudaSafeCall(cudaStreamSynchronize(memStream.stream));
+  SpatiallySparseBatchInterface &under = batch.interfaces[n - 1];
+  if (under.nSpatialSites != batch.batchSize) throw ScnException("processBatchDumpTopLevelFeaturess: the layer under the top one must hold one row per picture");
+  std::vector<float> feat((size_t)batch.batchSize * under.nFeatures);
+  if (!feat.empty()) cudaSafeCall(cudaMemcpy(feat.data(), under.sub->features.dPtr(), sizeof(float) * feat.size(), cudaMemcpyDeviceToHost));
+  std::vector<int> &labels = batch.labels.hVector();
+  for (int i = 0; i < batch.batchSize; ++i) {
+    f << batch.sampleNumbers[i] << " " << (i < (int)labels.size() ? labels[i] : -1);
+    for (int j = 0; j < under.nFeatures; ++j) f << " " << feat[(size_t)i * under.nFeatures + j];
+    f << std::endl;
+  }
+}
+void SparseConvNetCUDA::processDatasetDumpTopLevelFeatures(SpatiallySparseDataset &dataset, int batchSize, int reps) {
+  if (dataset.pictures.empty()) throw ScnException("processDatasetDumpTopLevelFeatures: empty dataset");
+  if (dataset.type == TRAINBATCH) throw ScnException("processDatasetDumpTopLevelFeatures: not for a training set");
+  std::ofstream f((dataset.name + ".features").c_str());
+  for (int i = 0; i < reps; ++i) {
+    BatchProducer bp(*this, dataset, inputSpatialSize, batchSize);
+    while (SpatiallySparseBatch *batch = bp.nextBatch()) processBatchDumpTopLevelFeaturess(*batch, f);
+  }
+}
+
+// SparseConvNetCUDA.cu:537-566: one over the largest absolute value of each input feature over (at most 10000 pictures of)
+// the data set, read as a test set (no augmentation); BatchProducer multiplies every batch's input by them from then on
+// and the weight files carry them.
+void SparseConvNetCUDA::calculateInputRegularizingConstants(SpatiallySparseDataset dataset) { // (a copy, as in the reference)
+  inputNormalizingConstants.resize(0); // no rescaling while the maxima are taken
+  std::cout << "Using " << std::min(10000, (int)dataset.pictures.size()) << " out of " << dataset.pictures.size()
+            << " training samples to calculate regularizing constants." << std::endl;
+  if (dataset.pictures.size() > 10000) dataset.pictures.resize(10000);
+  dataset.type = TESTBATCH;
+  std::vector<float> c(nInputFeatures, 0.f);
+  {
+    BatchProducer bp(*this, dataset, inputSpatialSize, 100);
+    while (SpatiallySparseBatch *batch = bp.nextBatch()) {
+      cudaSafeCall(cudaStreamSynchronize(memStream.stream));
+      std::vector<float> &features = batch->interfaces[0].sub->features.hVector();
+      for (size_t i = 0; i < features.size(); ++i) c[i % nInputFeatures] = std::max(c[i % nInputFeatures], std::fabs(features[i]));
+    }
+  }
+  for (int i = 0; i < nInputFeatures; ++i) {
+    inputNormalizingConstants.push_back(c[i] > 0 ? 1.0f / c[i] : 0);
+    std::cout << inputNormalizingConstants.back() << " ";
+  }
+  std::cout << std::endl;
+}
+
 // One pass over a dataset (SparseConvNetCUDA.cu:272-326): prints the reference's summary line and returns the mean
 // negative log-likelihood.  A TRAINBATCH dataset is shuffled by the batch producer and every batch updates the weights.
 float SparseConvNetCUDA::processDataset(SpatiallySparseDataset &dataset, int batchSize, float learningRate, float momentum) {

@@ -57,6 +57,9 @@ public:
                                  ActivationFunction activationFn = RELU, float dropout = 0.0f, int minActiveInputs = 1);
   void addSoftmaxLayer();
   void addIndexLearnerLayer();
+  void processBatchDumpTopLevelFeaturess(SpatiallySparseBatch &batch, std::ofstream &f);
+  void processDatasetDumpTopLevelFeatures(SpatiallySparseDataset &dataset, int batchSize, int reps = 1);
+  void calculateInputRegularizingConstants(SpatiallySparseDataset dataset);
   void processIndexLearnerBatch(SpatiallySparseBatch &batch, float learningRate, float momentum, std::ofstream &f);
   float processIndexLearnerDataset(SpatiallySparseDataset &dataset, int batchSize = 100, float learningRate = 0.0, float momentum = 0.99);
   void addTerminalPoolingLayer(int poolSize, int S);

@@ -231,6 +231,46 @@ int main() {
       CHECK(std::isfinite(test));
       std::printf("OK training with dropout (NLL %.3f -> %.3f)\n", first, last);
     }
+    // ---- 5e. input regularising constants (SparseConvNetCUDA.cu:537-566) and the dump of the features under the top layer
+    {
+      SparseConvNet rnet(2, 3, 5);
+      rnet.addLeNetLayerMP(32, 3, 1, 2, 2, VLEAKYRELU, 0.0f);
+      rnet.addLeNetLayerMP(64, 2, 1, 2, 2, VLEAKYRELU, 0.0f);
+      rnet.addLeNetLayerMP(96, 2, 1, 1, 1, VLEAKYRELU, 0.0f);
+      rnet.addSoftmaxLayer();
+      fillWeights(*rnet.cnn, 12);
+      ds.type = TESTBATCH;
+      float largest[3] = {0.f, 0.f, 0.f};
+      for (auto p : pics) {
+        SparseGrid g; std::vector<float> f; int rows = 0;
+        p->codifyInputData(g, f, rows, S);
+        for (size_t i = 0; i < f.size(); ++i) largest[i % 3] = std::max(largest[i % 3], std::fabs(f[i]));
+      }
+      const float before = rnet.processDataset(ds, 4);
+      rnet.calculateInputRegularizingConstants(ds);
+      CHECK(rnet.cnn->inputNormalizingConstants.size() == 3);
+      for (int c = 0; c < 3; ++c) CHECK(std::fabs(rnet.cnn->inputNormalizingConstants[c] * largest[c] - 1.f) < 1e-6f);
+      const float after = rnet.processDataset(ds, 4); // the same pictures, inputs now scaled into [-1, 1]
+      CHECK(std::isfinite(after) && after != before);
+      ds.name = "cpp-test-dump";
+      rnet.processDatasetDumpTopLevelFeatures(ds, 3, 2);
+      std::ifstream ff("cpp-test-dump.features");
+      int lines = 0;
+      std::string line;
+      while (std::getline(ff, line)) {
+        std::istringstream is(line);
+        int number, label, count = 0;
+        float v;
+        is >> number >> label;
+        while (is >> v) ++count;
+        CHECK(count == 96 && number == lines % (int)ds.pictures.size() && label == pics[number]->label);
+        ++lines;
+      }
+      CHECK(lines == 2 * (int)ds.pictures.size());
+      std::remove("cpp-test-dump.features");
+      ds.name = "cpp-test";
+      std::printf("OK regularising constants and feature dump\n");
+    }
     // ---- 5d. index learning (SparseConvNet.h:50, 57-60): every picture its own class; a data set that is not a training
     //          set writes "<name>.features" (sample number, label, the features under the index learner)
     {
