@@ -393,12 +393,13 @@ int scn_transpose_weights(const float *d_W, int K, int N, float *d_Wt, scn_strea
 
 /* Replaces propBackwardFromMatrixMultiply (ConvolutionalLayer.cu:42-72): zeroes
  * d_din[rows_in x nIn], then d_din[rules[c]] += d_dconv[c] for the count = rows_out*fs rule
- * cells with a non-negative rule. */
+ * cells with a non-negative rule.  rows_in = 0: nothing is zeroed (the reference's free function:
+ * the caller has zeroed d_din). */
 int scn_gather_backward(const float *d_dconv, const int *d_rules, long long count, int nIn, float *d_din,
                         long long rows_in, scn_stream_t stream);
 
 /* Replaces maxPoolBackProp (MaxPoolingLayer.cu:74-93, 134-146): zeroes d_din[n_in], then
- * d_din[d_choices[i]] += d_dout[i] for the n pooled values. */
+ * d_din[d_choices[i]] += d_dout[i] for the n pooled values.  n_in = 0: nothing is zeroed. */
 int scn_maxpool_backward(const float *d_dout, const int *d_choices, long long n, float *d_din, long long n_in,
                          scn_stream_t stream);
 

@@ -13,11 +13,6 @@ void SitesPicture::codifyInputData(SparseGrid &grid, std::vector<float> &out, in
     }
   }
 }
-void SpatiallySparseDataset::summary() {
-  std::cout << "Name:           " << name << "\nType:           " << batchTypeNames[type] << "\nnFeatures:      " << nFeatures
-            << "\nnPictures:      " << pictures.size() << "\nnClasses:       " << nClasses << std::endl;
-}
-
 BatchProducer::BatchProducer(SparseConvNetCUDA &cnn, SpatiallySparseDataset &dataset, int spatialSize, int batchSize)
     : cnn(cnn), dataset(dataset), spatialSize(spatialSize), batchSize(batchSize), nextToServe(0), lastServedSlot(-1), stop(false) {
   if (batchSize < 1) throw ScnException("BatchProducer: batchSize must be positive");

@@ -26,3 +26,6 @@ public:
 };
 
 void propForwardToMatrixMultiply(float *inFeatures, float *outFeatures, int *rules, int count, int nIn, cudaMemStream &memStream);
+// inDFeatures[rules[c]] += outDFeatures[c] for the count rule cells with a rule >= 0 (ConvolutionalLayer.cu:42-72): the
+// caller zeroes inDFeatures first.
+void propBackwardFromMatrixMultiply(float *inDFeatures, float *outDFeatures, int *rules, int count, int nIn, cudaMemStream &memStream);

@@ -713,6 +713,62 @@ void applySigmoid(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInte
                                      output.featuresPresent.size(), (int)fn, nullptr, memStream.stream));
 }
 
+// SigmoidLayer.cu:224-267.  (PReLU has its own layer class there too; SOFTMAX hands the gradient through unchanged: the
+// classifier's gradient is already taken with respect to the softmax input.)
+void applySigmoidBackProp(SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, ActivationFunction fn,
+                          cudaMemStream &memStream) {
+  if (fn == PRELU) throw ScnException("applySigmoidBackProp: PReLU needs its layer's slopes");
+  const int rows = output.nSpatialSites, N = output.featuresPresent.size();
+  if ((int)output.sub->dfeatures.size() != rows * N) throw ScnException("applySigmoidBackProp: the output's gradient is missing");
+  float *d = output.sub->dfeatures.dPtr();
+  if (input.sub != output.sub) {
+    input.sub->dfeatures.resize(rows * N);
+    cudaSafeCall(cudaMemcpyAsync(input.sub->dfeatures.dPtr(), d, sizeof(float) * (size_t)rows * N, cudaMemcpyDeviceToDevice, memStream.stream));
+    d = input.sub->dfeatures.dPtr();
+  }
+  scnSafeCall(scn_activation_backward(output.sub->features.dPtr(), d, rows, N, (int)fn, nullptr, nullptr, memStream.stream));
+}
+void maxPoolBackProp(float *d1, float *d2, int count, int nOut, int *d_choice, cudaMemStream &memStream) {
+  scnSafeCall(scn_maxpool_backward(d2, d_choice, (long long)count * nOut, d1, 0, memStream.stream)); // (0: nothing is zeroed)
+}
+void propBackwardFromMatrixMultiply(float *inDFeatures, float *outDFeatures, int *rules, int count, int nIn, cudaMemStream &memStream) {
+  scnSafeCall(scn_gather_backward(outDFeatures, rules, count, nIn, inDFeatures, 0, memStream.stream)); // (0: nothing is zeroed)
+}
+
+// SigmoidLayer.cu:269-310: a layer that only applies an activation.
+SigmoidLayer::SigmoidLayer(cudaMemStream &memStream, ActivationFunction fn) : SpatiallySparseLayer(memStream), fn(fn) {
+  std::cout << sigmoidNames[fn] << std::endl;
+  changesGeometry = false;
+}
+long long SigmoidLayer::enqueueRules(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output,
+                                     long long rowsInBound, int *) {
+  output.nFeatures = input.nFeatures;
+  output.spatialSize = input.spatialSize;
+  output.gridOwner = input.gridOwner;
+  return rowsInBound;
+}
+void SigmoidLayer::finishRules(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, const int *) {
+  output.nFeatures = input.nFeatures;
+  output.featuresPresent.hVector() = input.featuresPresent.hVector();
+  output.spatialSize = input.spatialSize;
+  output.nSpatialSites = input.nSpatialSites;
+  output.maxSitesPerSample = input.maxSitesPerSample;
+  output.gridOwner = input.gridOwner;
+  output.backpropErrors = input.backpropErrors;
+}
+void SigmoidLayer::preprocess(SpatiallySparseBatch &batch, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  enqueueRules(batch, input, output, input.nSpatialSites, nullptr);
+  finishRules(batch, input, output, nullptr);
+}
+void SigmoidLayer::forwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output) {
+  output.sub->features.resize(output.nSpatialSites * output.featuresPresent.size());
+  applySigmoid(input, output, fn, memStream);
+}
+void SigmoidLayer::backwards(SpatiallySparseBatch &, SpatiallySparseBatchInterface &input, SpatiallySparseBatchInterface &output, float, float) {
+  if (input.backpropErrors) applySigmoidBackProp(input, output, fn, memStream);
+}
+int SigmoidLayer::calculateInputSpatialSize(int outputSpatialSize) { return outputSpatialSize; }
+
 // The classifier's device half and the one copy that brings its results to the host: probabilities, the nTop classes
 // per row and the error word of the tensor-core kernels travel as one block (scn_classifier_result).  Returns the
 // block in the stream's page-locked staging memory; throws if a tensor-core kernel gave up a wait.

@@ -4,6 +4,8 @@
 #include "SpatiallySparseLayer.h"
 
 void maxPool(float *g1, float *g2, int *rules, int count, int sd, int nOut, int *d_choice, cudaMemStream &memStream);
+// d1[d_choice[i]] += d2[i] for the count x nOut pooled values (MaxPoolingLayer.cu:74-93): the caller zeroes d1 first.
+void maxPoolBackProp(float *d1, float *d2, int count, int nOut, int *d_choice, cudaMemStream &memStream);
 
 class MaxPoolingLayer : public SpatiallySparseLayer {
 public:

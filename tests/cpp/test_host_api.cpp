@@ -2,6 +2,7 @@
 // the reference would: builders, per-layer preprocess()/forwards(), processBatch(), the host
 // gridRules() entry point, vectorCUDA migration, fused against unfused convolution.
 // Built and run by tests/test_gpu_cpp_api.py on a B200; prints "OK" lines and exits 0 on success.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <sstream>
@@ -10,6 +11,7 @@
 #include <vector>
 #include "BatchProducer.h"
 #include "ConvolutionalLayer.h"
+#include "MaxPoolingLayer.h"
 #include "NetworkArchitectures.h"
 #include "NetworkInNetworkLayer.h"
 #include "Regions.h"
@@ -336,6 +338,78 @@ int main() {
       for (int v : rls) placed += v > 0;
       CHECK(placed == 17); // every input site appears exactly once: the regions do not overlap
       std::printf("OK fractional max-pooling\n");
+    }
+    // ---- 8. the data set helpers (SpatiallySparseDataset.h:18-30)
+    {
+      SpatiallySparseDataset all;
+      all.name = "helpers"; all.nFeatures = 3; all.nClasses = 4; all.type = TRAINBATCH;
+      for (int i = 0; i < 20; ++i) all.pictures.push_back(new SitesPicture(3, i % 4));
+      all.summary();
+      SpatiallySparseDataset val = all.extractValidationSet(0.25f);
+      CHECK(val.pictures.size() == 5 && all.pictures.size() == 15 && val.type == TESTBATCH && val.nClasses == 4);
+      CHECK(val.name == "helpers Validation set" && all.name == "helpers minus Validation set");
+      SpatiallySparseDataset six = all.subset(6);
+      CHECK(six.pictures.size() == 6 && six.type == TRAINBATCH);
+      for (size_t i = 0; i < 6; ++i)
+        for (size_t j = i + 1; j < 6; ++j) CHECK(six.pictures[i] != six.pictures[j]);
+      SpatiallySparseDataset two = all.balancedSample(2);
+      int perClass[4] = {0, 0, 0, 0};
+      for (auto p : two.pictures) ++perClass[p->label];
+      CHECK(two.pictures.size() == 8 && perClass[0] == 2 && perClass[1] == 2 && perClass[2] == 2 && perClass[3] == 2);
+      std::vector<Picture *> order = all.pictures;
+      all.shuffle();
+      std::vector<Picture *> a = order, b = all.pictures;
+      std::sort(a.begin(), a.end()); std::sort(b.begin(), b.end());
+      CHECK(a == b);
+      all.repeatSamples(3);
+      CHECK(all.pictures.size() == 45 && all.pictures[0] == all.pictures[15] && all.pictures[14] == all.pictures[44]);
+      all.pictures.resize(15);
+      int kept = 0;
+      for (auto p : all.pictures) kept += (p->label == 1 || p->label == 3);
+      all.subsetOfClasses({3, 1}); // keeps classes 3 and 1 as 0 and 1, deletes the other pictures
+      CHECK((int)all.pictures.size() == kept && all.nClasses == 2);
+      for (auto p : all.pictures) CHECK(p->label == 0 || p->label == 1);
+      for (auto p : all.pictures) delete p;
+      for (auto p : val.pictures) delete p;
+      CHECK(globVector("/nonexistent-dir-for-this-test/*").empty());
+      std::printf("OK data set helpers\n");
+    }
+    // ---- 9. the stand-alone backward passes (MaxPoolingLayer.h:8, ConvolutionalLayer.h:41, SigmoidLayer.h:7) and SigmoidLayer
+    {
+      vectorCUDA<float> d1(false, 0), d2(false, 0);
+      vectorCUDA<int> choice(false, 0), rules(false, 0);
+      d1.hVector() = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+      d2.hVector() = {1.f, 2.f, 3.f, 4.f};
+      choice.hVector() = {0, 5, 0, 2};
+      maxPoolBackProp(d1.dPtr(), d2.dPtr(), 2, 2, choice.dPtr(), cnn.memStream); // adds onto what d1 holds
+      cudaStreamSynchronize(cnn.memStream.stream);
+      CHECK((d1.hVector() == std::vector<float>{5.f, 1.f, 5.f, 1.f, 1.f, 3.f}));
+      vectorCUDA<float> in(false, 0), out(false, 0);
+      in.hVector() = {1.f, 1.f, 1.f, 1.f};
+      out.hVector() = {1.f, 2.f, 3.f, 4.f, 5.f, 6.f};
+      rules.hVector() = {1, -1, 0};
+      propBackwardFromMatrixMultiply(in.dPtr(), out.dPtr(), rules.dPtr(), 3, 2, cnn.memStream);
+      cudaStreamSynchronize(cnn.memStream.stream);
+      CHECK((in.hVector() == std::vector<float>{6.f, 7.f, 2.f, 3.f}));
+      SpatiallySparseBatchSubInterface subIn, subOut;
+      SpatiallySparseBatchInterface I(&subIn), O(&subOut);
+      I.nSpatialSites = O.nSpatialSites = 1; I.nFeatures = O.nFeatures = 4;
+      I.featuresPresent.hVector() = range(4); O.featuresPresent.hVector() = range(4);
+      I.backpropErrors = true;
+      subIn.features.hVector() = {-3.f, -1.f, 0.5f, 2.f};
+      SpatiallySparseBatch &none = cnn.batchPool[0]; // (the layer does not read it)
+      SigmoidLayer leaky(cnn.memStream, VLEAKYRELU);
+      leaky.forwards(none, I, O);
+      cudaStreamSynchronize(cnn.memStream.stream);
+      std::vector<float> f = subOut.features.hVector();
+      CHECK(std::fabs(f[0] + 0.999f) < 1e-6f && std::fabs(f[1] + 0.333f) < 1e-6f && f[2] == 0.5f && f[3] == 2.f);
+      subOut.dfeatures.hVector() = {10.f, 10.f, 10.f, 10.f};
+      leaky.backwards(none, I, O, 0.f, 0.f);
+      cudaStreamSynchronize(cnn.memStream.stream);
+      std::vector<float> g = subIn.dfeatures.hVector();
+      CHECK(std::fabs(g[0] - 3.33f) < 1e-5f && std::fabs(g[1] - 3.33f) < 1e-5f && g[2] == 10.f && g[3] == 10.f);
+      CHECK(leaky.calculateInputSpatialSize(7) == 7);
+      std::printf("OK stand-alone backward passes\n");
     }
     for (auto p : pics) delete p;
   } catch (const std::exception &e) {
