@@ -433,6 +433,12 @@ int scn_gather_columns(const float *d_W, int K, int N, const int *d_idx, int n, 
 int scn_scatter_columns_axpy(float *d_W, int K, int N, const int *d_idx, int n, const float *d_delta, float alpha,
                              scn_stream_t stream);
 
+/* The reference's four cuBLAS wrappers (utilities.cu:132-169) as one call: C[l x r] = alpha * op(A) * op(B) + beta * C on
+ * row-major fp32 matrices, op(A) l x m, op(B) m x r; transA / transB non-zero: that operand is stored transposed (m x l,
+ * r x m).  CUDA cores; not used by the forward path. */
+int scn_sgemm_rowmajor(int transA, int transB, const float *d_A, const float *d_B, float *d_C, int l, int m, int r,
+                       float alpha, float beta, scn_stream_t stream);
+
 /* ------------------------------------------------------------------ result exchange between the GPUs of one node
  * The reference runs on one GPU (SparseConvNetCUDA.cu:43-71 picks a single device).  Sharded by sample over several
  * GPUs, the path has one exchange step: every rank's [rows x nClasses] block of probabilities (what

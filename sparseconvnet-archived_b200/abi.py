@@ -24,7 +24,7 @@ EXPORTS = [
     "scn_conv_pack_weights", "scn_conv_tc_take_error", "scn_conv_tc_error_word", "scn_classifier_result_bytes", "scn_classifier_result", "scn_gather_forward", "scn_maxpool_forward",
     "scn_terminal_pool_forward", "scn_top_indices", "scn_activation_forward", "scn_background_rows",
     "scn_exchange_buffer_bytes", "scn_exchange_set_timeout_ms", "scn_exchange_alloc", "scn_exchange_free", "scn_exchange_open", "scn_exchange_close", "scn_exchange_publish", "scn_exchange_collect", "scn_exchange_step",
-    "scn_mask_columns", "scn_sgd_update_masked", "scn_gather_columns", "scn_scatter_columns_axpy", "scn_softmax_nll_backward", "scn_activation_backward", "scn_conv_nin_backward_weights", "scn_conv_nin_backward_weights_tc_bytes", "scn_conv_nin_backward_weights_tc", "scn_transpose_weights", "scn_gather_backward",
+    "scn_mask_columns", "scn_sgd_update_masked", "scn_gather_columns", "scn_scatter_columns_axpy", "scn_sgemm_rowmajor", "scn_softmax_nll_backward", "scn_activation_backward", "scn_conv_nin_backward_weights", "scn_conv_nin_backward_weights_tc_bytes", "scn_conv_nin_backward_weights_tc", "scn_transpose_weights", "scn_gather_backward",
     "scn_maxpool_backward", "scn_terminal_pool_backward", "scn_sgd_update",
 ]
 
@@ -532,6 +532,11 @@ def sgd_update_masked(w, m, d, row_mask, row_period, col_mask, lr, momentum, kee
     check(lib().scn_sgd_update_masked(_ptr(w), _ptr(m), _ptr(_f32(d)), c_ll(rows), N, _ptr(_f32(row_mask)) if row_mask is not None else None,
                                       int(row_period), _ptr(_f32(col_mask)) if col_mask is not None else None, c_f(lr), c_f(momentum),
                                       int(keep_positive), _stream()))
+
+
+def sgemm_rowmajor(A, B, C, l, m, r, alpha=1.0, beta=0.0, trans_a=False, trans_b=False):
+    """C[l x r] = alpha * op(A) op(B) + beta * C (in place on C)."""
+    check(lib().scn_sgemm_rowmajor(int(trans_a), int(trans_b), _ptr(_f32(A)), _ptr(_f32(B)), _ptr(_f32(C)), l, m, r, c_f(alpha), c_f(beta), _stream()))
 
 
 class ExchangeBuffer:

@@ -127,3 +127,20 @@ void *cudaMemStream::staging(size_t bytes) {
   }
   return pinnedMemory;
 }
+
+// utilities.cu:132-169.  file / linenumber name the caller in the error message.
+static void sgemmForm(bool ta, bool tb, float *A, float *B, float *C, int l, int m, int r, float alpha, float beta, const char *file, int line) {
+  scnCheckStatus(scn_sgemm_rowmajor(ta, tb, A, B, C, l, m, r, alpha, beta, nullptr), file ? file : __FILE__, file ? line : __LINE__);
+}
+void d_rowMajorSGEMM_alphaAB_betaC(cublasHandle_t, float *A, float *B, float *C, int l, int m, int r, float alpha, float beta, const char *file, int line) {
+  sgemmForm(false, false, A, B, C, l, m, r, alpha, beta, file, line);
+}
+void d_rowMajorSGEMM_alphaAtB_betaC(cublasHandle_t, float *A, float *B, float *C, int l, int m, int r, float alpha, float beta, const char *file, int line) {
+  sgemmForm(true, false, A, B, C, l, m, r, alpha, beta, file, line);
+}
+void d_rowMajorSGEMM_alphaABt_betaC(cublasHandle_t, float *A, float *B, float *C, int l, int m, int r, float alpha, float beta, const char *file, int line) {
+  sgemmForm(false, true, A, B, C, l, m, r, alpha, beta, file, line);
+}
+void d_rowMajorSGEMM_alphaAtBt_betaC(cublasHandle_t, float *A, float *B, float *C, int l, int m, int r, float alpha, float beta, const char *file, int line) {
+  sgemmForm(true, true, A, B, C, l, m, r, alpha, beta, file, line);
+}

@@ -13,6 +13,18 @@
 struct cublasContext;
 typedef struct cublasContext *cublasHandle_t;
 
+// The reference's cuBLAS wrappers (utilities.h:82-102): C[l x r] = alpha * op(A) * op(B) + beta * C, row-major, op(A) l x m
+// and op(B) m x r ("At": A is stored m x l, "Bt": B is stored r x m).  The handle is ignored; the product runs on the
+// legacy default stream, which is ordered against the blocking streams the networks create.
+void d_rowMajorSGEMM_alphaAB_betaC(cublasHandle_t handle, float *A, float *B, float *C, int l, int m, int r, float alpha, float beta,
+                                   const char *file = 0, int linenumber = 0);
+void d_rowMajorSGEMM_alphaAtB_betaC(cublasHandle_t handle, float *A, float *B, float *C, int l, int m, int r, float alpha, float beta,
+                                    const char *file = 0, int linenumber = 0);
+void d_rowMajorSGEMM_alphaABt_betaC(cublasHandle_t handle, float *A, float *B, float *C, int l, int m, int r, float alpha, float beta,
+                                    const char *file = 0, int linenumber = 0);
+void d_rowMajorSGEMM_alphaAtBt_betaC(cublasHandle_t handle, float *A, float *B, float *C, int l, int m, int r, float alpha, float beta,
+                                     const char *file = 0, int linenumber = 0);
+
 #define NTHREADS 512
 #define KERNELBLOCKSIZE 32
 

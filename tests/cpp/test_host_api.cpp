@@ -409,6 +409,14 @@ int main() {
       std::vector<float> g = subIn.dfeatures.hVector();
       CHECK(std::fabs(g[0] - 3.33f) < 1e-5f && std::fabs(g[1] - 3.33f) < 1e-5f && g[2] == 10.f && g[3] == 10.f);
       CHECK(leaky.calculateInputSpatialSize(7) == 7);
+      // the cuBLAS wrappers' signatures (utilities.h:82-102): C[2 x 2] = A^t B with A stored 3 x 2, B 3 x 2
+      vectorCUDA<float> mA(false, 0), mB(false, 0), mC(false, 0);
+      mA.hVector() = {1.f, 2.f, 3.f, 4.f, 5.f, 6.f};
+      mB.hVector() = {1.f, 0.f, 0.f, 1.f, 1.f, 1.f};
+      mC.hVector() = {100.f, 100.f, 100.f, 100.f};
+      d_rowMajorSGEMM_alphaAtB_betaC(cnn.cublasHandle, mA.dPtr(), mB.dPtr(), mC.dPtr(), 2, 3, 2, 1.0f, 0.5f, __FILE__, __LINE__);
+      cudaDeviceSynchronize();
+      CHECK((mC.hVector() == std::vector<float>{56.f, 58.f, 58.f, 60.f}));
       std::printf("OK stand-alone backward passes\n");
     }
     for (auto p : pics) delete p;

@@ -384,3 +384,24 @@ def test_classifier_result_block(abi, oracle):
         np.testing.assert_array_equal(t.numpy(), np.stack([oracle.top_indices(row, k) for row in v]))
         assert flag == 0
     assert abi.lib().scn_conv_tc_error_word() != 0
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("l,m,r", [(70, 45, 33), (128, 64, 64), (1, 300, 5), (257, 1, 130)])
+def test_sgemm_rowmajor_forms(abi, trans_a, trans_b, l, m, r):
+    """The four products of the reference's cuBLAS wrappers (utilities.cu:132-169: AB, AtB, ABt, AtBt on row-major
+    matrices with alpha and beta) against float64 numpy; with beta = 0 the old contents of C are not read."""
+    import torch
+    rng = np.random.default_rng(l * 1000 + m * 10 + r)
+    A = rng.standard_normal((l, m))
+    B = rng.standard_normal((m, r))
+    C0 = rng.standard_normal((l, r))
+    dA = torch.from_numpy(np.ascontiguousarray(A.T if trans_a else A, np.float32)).cuda()
+    dB = torch.from_numpy(np.ascontiguousarray(B.T if trans_b else B, np.float32)).cuda()
+    dC = torch.from_numpy(C0.astype(np.float32)).cuda()
+    abi.sgemm_rowmajor(dA, dB, dC, l, m, r, 0.7, 0.3, trans_a, trans_b)
+    want = 0.7 * (A.astype(np.float32).astype(np.float64) @ B.astype(np.float32).astype(np.float64)) + 0.3 * C0.astype(np.float32)
+    assert relerr(dC.cpu().numpy(), want) < 1e-5
+    dC = torch.full((l, r), float("nan"), dtype=torch.float32).cuda()
+    abi.sgemm_rowmajor(dA, dB, dC, l, m, r, 1.0, 0.0, trans_a, trans_b)
+    assert relerr(dC.cpu().numpy(), want / 0.7 - 0.3 / 0.7 * C0.astype(np.float32)) < 1e-5
