@@ -67,7 +67,7 @@ void SpatiallySparseDataset::subsetOfClasses(std::vector<int> activeClasses) {
   pictures.resize(kept);
 }
 
-// Up to n pictures of every class (SpatiallySparseDataset.cpp:58-88): passes over fresh permutations of the set; a
+// n pictures of every class that has any (SpatiallySparseDataset.cpp:58-88): passes over fresh permutations of the set; a
 // picture is taken while its class has been met fewer than n times, a class is complete in the pass in which it is met
 // for the n-th time, and the search ends when every class is complete or a whole pass took nothing.
 SpatiallySparseDataset SpatiallySparseDataset::balancedSample(int n) {

@@ -25,7 +25,7 @@ public:
   // Keeps the pictures whose label is listed, relabels them by position in the list and DELETES the others.
   void subsetOfClasses(std::vector<int> activeClasses);
   SpatiallySparseDataset subset(int n);         // n pictures drawn without replacement, in their order
-  SpatiallySparseDataset balancedSample(int n); // n pictures of every class where the set has them
+  SpatiallySparseDataset balancedSample(int n); // n pictures of every class (a class with fewer is sampled again and again)
   void repeatSamples(int reps);                 // the list repeated: small sets then give epochs of a useful length
 };
 
