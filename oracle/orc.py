@@ -316,6 +316,7 @@ class Oracle(_RulesLib):
             getattr(L, n).argtypes = [c_p] + [c_int] * 6 + [c_f, c_int]
         L.orc_net_addLeNetLayerFMP.argtypes = [c_p] + [c_int] * 5 + [c_f, c_int, c_f, c_int]
         L.orc_net_set_fmp_seed.argtypes = [c_p, ctypes.c_uint]
+        L.orc_net_set_dropout_features.restype, L.orc_net_set_dropout_features.argtypes = c_int, [c_p, c_int, c_p, c_int]
         L.orc_net_addTerminalPoolingLayer.argtypes = [c_p, c_int, c_int]
         L.orc_net_addSoftmaxLayer.argtypes = [c_p]
         L.orc_net_DeepCNet.restype = c_p
@@ -534,6 +535,12 @@ class OracleNet:
                                _p(probs), _p(pred), _p(times))
         self.times = times
         return probs, pred
+
+    def set_dropout_features(self, layer, present):
+        """The output features learnt layer `layer` keeps in the training steps that follow (ascending; empty: all)."""
+        present = np.ascontiguousarray(present, np.int32)
+        if self.L.orc_net_set_dropout_features(self.h, layer, _p(present), len(present)):
+            raise ValueError("not a learnt layer, or more features than it has")
 
     def train_step(self, keys, off, features, labels, learning_rate, momentum, accum64=True):
         """One TRAINBATCH step (forward, SoftmaxClassifier, every layer's backwards with its SGD update) on a network

@@ -382,7 +382,20 @@ struct Layer {
   int inSpatial = 0, outSpatial = 0;
   std::vector<float> W, B, prelu;
   std::vector<float> MW, MB, Mprelu; // momentum of the training step (zero until the first one)
+  // Training-time dropout (NetworkInNetworkLayer.cu:152-154): the output features the next training step keeps, ascending;
+  // empty = all of them.  The reference draws them at random per batch; here the caller names them (orc_net_set_dropout_features),
+  // so that two implementations can run the same step.
+  std::vector<int> present;
 };
+
+// 0/1 per output feature of learnt layer `l` for a training step, or empty when the step keeps them all.
+static std::vector<char> keptMask(const Layer &L) {
+  std::vector<char> m;
+  if (L.present.empty() || (int)L.present.size() >= L.nOut) return m;
+  m.assign(L.nOut, 0);
+  for (int f : L.present) m[f] = 1;
+  return m;
+}
 
 struct Iface { // SpatiallySparseBatchInterface.h:19-46, host side only
   int nFeatures = 0, spatialSize = 0, nSpatialSites = 0;
@@ -584,7 +597,7 @@ static void terminalPoolBackward(const float *dOut, const int *rules, int count,
 // keys[row] is the site key, or -1 for the sample's background ("null vector") row.
 static void forwardChunk(const Net &net, int batch, const int64_t *keys, const int *off, const float *features,
                          bool accum64, std::vector<Iface> &ifs, double *tRules,
-                         const std::vector<std::vector<Ticks>> &fmpTicks, int firstSample) {
+                         const std::vector<std::vector<Ticks>> &fmpTicks, int firstSample, bool training = false) {
   auto t0 = std::chrono::steady_clock::now();
   ifs.assign(net.layers.size() + 1, Iface());
   Iface &I0 = ifs[0];
@@ -637,10 +650,26 @@ static void forwardChunk(const Net &net, int batch, const int64_t *keys, const i
     case L_CONV: case L_CONV_TRI:
       gather(in.features.data(), out.rules.data(), (long long)out.nSpatialSites * L.fs, L.nIn, out.features.data());
       break;
-    case L_NIN:
-      if (accum64) ninForward<double>(in.features.data(), out.nSpatialSites, L.nIn, L.W.data(), L.B.data(), L.prelu.empty() ? nullptr : L.prelu.data(), L.nOut, 1.0f - L.dropout, L.act, out.features.data());
-      else ninForward<float>(in.features.data(), out.nSpatialSites, L.nIn, L.W.data(), L.B.data(), L.prelu.empty() ? nullptr : L.prelu.data(), L.nOut, 1.0f - L.dropout, L.act, out.features.data());
+    case L_NIN: {
+      // A training step that drops features on either side of the layer runs on the kept ones without the test-time
+      // scaling (NetworkInNetworkLayer.cu:162-186); the dropped inputs are zero columns here, the dropped outputs are zeroed.
+      float p = 1.0f - L.dropout;
+      std::vector<char> outMask;
+      if (training) {
+        outMask = keptMask(L);
+        bool inDropped = false;
+        for (int k = (int)l - 1; k >= 0; --k)
+          if (net.layers[k].type == L_NIN) { inDropped = !keptMask(net.layers[k]).empty(); break; }
+        if (!outMask.empty() || inDropped) p = 1.0f;
+      }
+      if (accum64) ninForward<double>(in.features.data(), out.nSpatialSites, L.nIn, L.W.data(), L.B.data(), L.prelu.empty() ? nullptr : L.prelu.data(), L.nOut, p, L.act, out.features.data());
+      else ninForward<float>(in.features.data(), out.nSpatialSites, L.nIn, L.W.data(), L.B.data(), L.prelu.empty() ? nullptr : L.prelu.data(), L.nOut, p, L.act, out.features.data());
+      if (!outMask.empty())
+        for (long long r = 0; r < out.nSpatialSites; ++r)
+          for (int n = 0; n < L.nOut; ++n)
+            if (!outMask[n]) out.features[(size_t)r * L.nOut + n] = 0.f;
       break;
+    }
     case L_MAXPOOL: case L_MAXPOOL_TRI: case L_FMP:
       out.choices.resize(out.features.size());
       maxPool(in.features.data(), out.rules.data(), out.nSpatialSites, L.fs, L.nOut, out.features.data(), out.choices.data());
@@ -812,6 +841,13 @@ void orc_net_addLeNetLayerMP(void *h, int nFeatures, int fs, int fstride, int ps
 void orc_net_addTriangularLeNetLayerMP(void *h, int nFeatures, int fs, int fstride, int ps, int pstride, int act, float dropout, int minActive) { ((Net *)h)->addTriangularLeNetLayerMP(nFeatures, fs, fstride, ps, pstride, act, dropout, minActive); }
 void orc_net_addLeNetLayerFMP(void *h, int kind, int nFeatures, int fs, int fstride, int ps, float shrink, int act, float dropout, int minActive) { ((Net *)h)->addLeNetLayerFMP(kind, nFeatures, fs, fstride, ps, shrink, act, dropout, minActive); }
 void orc_net_set_fmp_seed(void *h, unsigned seed) { ((Net *)h)->fmpSeed = seed; }
+// The output features learnt layer `layer` keeps in the training steps that follow (n ascending indices; n = 0: all).
+int orc_net_set_dropout_features(void *h, int layer, const int *present, int n) {
+  Net *net = (Net *)h;
+  if (layer < 0 || layer >= (int)net->layers.size() || net->layers[layer].type != L_NIN || n < 0 || n > net->layers[layer].nOut) return 1;
+  net->layers[layer].present.assign(present, present + n);
+  return 0;
+}
 void orc_net_addTerminalPoolingLayer(void *h, int poolSize, int S) { ((Net *)h)->addTerminalPoolingLayer(poolSize, S); }
 void orc_net_addSoftmaxLayer(void *h) { ((Net *)h)->addSoftmaxLayer(); }
 // NetworkArchitectures.cpp:3-11.
@@ -907,10 +943,11 @@ void orc_net_forward(void *h, int batch, const int64_t *keys, const int *off, co
 int orc_net_train_step(void *h, int batch, const int64_t *keys, const int *off, const float *features, const int *labels,
                        float learningRate, float momentum, int accum64, float *probs, double *stats) {
   Net *net = (Net *)h;
-  for (const Layer &L : net->layers) if (L.type == L_NIN && L.dropout > 0) return 1; // training-time dropout draws random feature subsets: not restated
+  // (a layer built with dropout must have been told its subset: the random draw itself is not restated)
+  for (const Layer &L : net->layers) if (L.type == L_NIN && L.dropout > 0 && L.present.empty()) return 1;
   std::vector<std::vector<Ticks>> fmpTicks = drawFmpTicks(*net, batch);
   std::vector<Iface> ifs;
-  forwardChunk(*net, batch, keys, off, features, accum64 != 0, ifs, nullptr, fmpTicks, 0);
+  forwardChunk(*net, batch, keys, off, features, accum64 != 0, ifs, nullptr, fmpTicks, 0, true);
   const int nL = (int)net->layers.size();
   Iface &top = ifs.back();
   const int C = net->nClasses;
@@ -931,6 +968,16 @@ int orc_net_train_step(void *h, int batch, const int64_t *keys, const int *off, 
     Iface &in = ifs[l], &out = ifs[l + 1];
     const long long rowsOut = out.nSpatialSites, rowsIn = in.nSpatialSites;
     if (L.type == L_NIN) {
+      // dropout: gradients of dropped features are zero on both sides, and the update leaves every weight that touches
+      // one (and its momentum) as it is (dGradientDescentShrunkMatrix / ...Vector, NetworkInNetworkLayer.cu:43-81)
+      const std::vector<char> outMask = keptMask(L);
+      std::vector<char> inMask;
+      for (int k = l - 1; k >= 0; --k)
+        if (net->layers[k].type == L_NIN) { inMask = keptMask(net->layers[k]); break; }
+      if (!outMask.empty())
+        for (long long r = 0; r < rowsOut; ++r)
+          for (int n = 0; n < L.nOut; ++n)
+            if (!outMask[n]) out.dfeatures[(size_t)r * L.nOut + n] = 0.f;
       std::vector<float> dprelu(L.nOut, 0.f);
       if (accum64) activationBackward<double>(out.features.data(), out.dfeatures.data(), rowsOut, L.nOut, L.act, L.prelu.empty() ? nullptr : L.prelu.data(), dprelu.data());
       else activationBackward<float>(out.features.data(), out.dfeatures.data(), rowsOut, L.nOut, L.act, L.prelu.empty() ? nullptr : L.prelu.data(), dprelu.data());
@@ -939,10 +986,29 @@ int orc_net_train_step(void *h, int batch, const int64_t *keys, const int *off, 
       float *dX = backprop[l] ? in.dfeatures.data() : nullptr;
       if (accum64) ninBackward<double>(in.features.data(), out.dfeatures.data(), rowsOut, L.nIn, L.nOut, L.W.data(), dW.data(), dB.data(), dX);
       else ninBackward<float>(in.features.data(), out.dfeatures.data(), rowsOut, L.nIn, L.nOut, L.W.data(), dW.data(), dB.data(), dX);
+      if (dX && !inMask.empty()) { // (the convolution in front repeats the features: the mask applies with its own period)
+        const size_t period = inMask.size();
+        for (size_t i = 0; i < (size_t)rowsIn * L.nIn; ++i)
+          if (!inMask[i % period]) dX[i] = 0.f;
+      }
       if (L.MW.empty()) { L.MW.assign(L.W.size(), 0.f); L.MB.assign(L.B.size(), 0.f); L.Mprelu.assign(L.prelu.size(), 0.f); }
+      const std::vector<float> W0 = L.W, MW0 = L.MW, B0 = L.B, MB0 = L.MB, P0 = L.prelu, MP0 = L.Mprelu;
       sgdUpdate(L.W.data(), L.MW.data(), dW.data(), L.W.size(), learningRate, momentum);
       sgdUpdate(L.B.data(), L.MB.data(), dB.data(), L.B.size(), learningRate, momentum);
       if (L.act == PRELU) sgdUpdate(L.prelu.data(), L.Mprelu.data(), dprelu.data(), L.prelu.size(), learningRate, momentum, true);
+      if (!outMask.empty() || !inMask.empty()) {
+        for (int k = 0; k < L.nIn; ++k)
+          for (int n = 0; n < L.nOut; ++n)
+            if ((!inMask.empty() && !inMask[k % inMask.size()]) || (!outMask.empty() && !outMask[n])) {
+              L.W[(size_t)k * L.nOut + n] = W0[(size_t)k * L.nOut + n];
+              L.MW[(size_t)k * L.nOut + n] = MW0[(size_t)k * L.nOut + n];
+            }
+        for (int n = 0; n < L.nOut && !outMask.empty(); ++n)
+          if (!outMask[n]) {
+            L.B[n] = B0[n]; L.MB[n] = MB0[n];
+            if (L.act == PRELU) { L.prelu[n] = P0[n]; L.Mprelu[n] = MP0[n]; } // (what NetworkInNetworkPReLULayer.cu:199-207 means to do)
+          }
+      }
     } else if (!backprop[l]) {
       continue;
     } else if (L.type == L_CONV || L.type == L_CONV_TRI) {

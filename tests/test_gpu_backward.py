@@ -362,6 +362,8 @@ def _reference_dropout_steps(abi, ref, gnet, onet, layers, weights, gen, batch, 
     `gen(step)` gives the samples of a step, `onet` (same layers) only checks that the rulebooks are safe for the reference's
     kernels.  See test_training_steps_with_dropout_match_reference for what is compared."""
     nL = len(layers)
+    for i, (W, B, pr) in weights.items():  # the oracle runs the same steps: its restatement of dropout is pinned here too
+        onet.set_weights(i, W, B, pr)
     ref.seed_dropout(1234)  # (the reference seeds these generators from the clock)
     lr, mom = 0.01, 0.9
     dropped_somewhere = 0
@@ -380,6 +382,7 @@ def _reference_dropout_steps(abi, ref, gnet, onet, layers, weights, gen, batch, 
         for i, L in enumerate(layers):
             if L["type"] == 2:
                 gnet.set_dropout_features(i, cols[i + 1] if len(cols[i + 1]) < L["nOut"] else [])
+                onet.set_dropout_features(i, cols[i + 1])
                 dropped_somewhere += len(cols[i + 1]) < L["nOut"]
         k2 = np.concatenate([keys[off[s]:off[s + 1]] for s in order])
         f2 = np.concatenate([feats[off[s]:off[s + 1]] for s in order])
@@ -390,6 +393,14 @@ def _reference_dropout_steps(abi, ref, gnet, onet, layers, weights, gen, batch, 
         assert relerr(gprobs, rprobs) < TOL
         assert gstats["nll"] == pytest.approx(rstats["nll"], rel=1e-4)
         assert gstats["mistakes"] == rstats["mistakes"]
+        obefore = {i: onet.get_weights(i) for i in weights}
+        oprobs, ostats = onet.train_step(k2, o2, f2, l2, lr, mom)
+        assert relerr(oprobs, rprobs) < TOL and ostats["nll"] == pytest.approx(rstats["nll"], rel=1e-4) and ostats["mistakes"] == rstats["mistakes"]
+        for i in weights:
+            oW, oB, _ = onet.get_weights(i)
+            rW, rB, _ = ref.layer_weights(i)
+            assert relerr(oW - obefore[i][0], rW - rbefore[i][0]) < 4 * UPDATE_TOL, "oracle's weight update of layer %d" % i
+            assert relerr(oB - obefore[i][1], rB - rbefore[i][1]) < 4 * UPDATE_TOL, "oracle's bias update of layer %d" % i
         checked = 0
         tie_above = nL + 2  # the highest interface at which a near-tie of the forward pass fell the other way (see grad_close)
         for i in range(nL, -1, -1):
@@ -741,3 +752,57 @@ def test_training_step_at_benchmark_batch_on_both_kernel_families(scn, abi):
         assert np.abs(bW - W0).max() > 100 * 6e-8 * np.abs(W0).max()
         assert relerr(aW - W0, bW - W0) < seen(W0, bW - W0), "weight update of layer %d" % i
         assert relerr(aB - B0, bB - B0) < seen(B0, bB - B0), "bias update of layer %d" % i
+
+
+@pytest.mark.parametrize("cfg,batch,act", [(1, 12, "VLEAKYRELU"), (2, 8, "PRELU"), (4, 4, "PRELU"), (5, 2, "RELU")])
+def test_training_steps_with_dropout_match_oracle(scn, abi, oracle, cfg, batch, act):
+    """Two training steps with dropout against the oracle's restatement of the same step (fp64 accumulation), both told the
+    same feature subsets, drawn here anew for each step.  Independent of the reference library: it also covers the PReLU
+    layers, for which the reference has no defined result (the slopes of dropped features must stay as they are)."""
+    from oracle import orc
+    c = scn.synth.CONFIGS[cfg]
+    levels, terminal = _levels(scn, cfg, getattr(orc, act))
+    levels = [lv[:6] + (0.0 if i == 0 else 0.5,) + lv[7:] for i, lv in enumerate(levels)]
+    onet = orc.OracleNet(oracle, c["dim"], c["nIn"], c["nClasses"], 1, lattice=c["lattice"])
+    build_with(onet, levels, terminal)
+    gnet = scn.net.Net(c["dim"], c["nIn"], c["nClasses"], 1, c["lattice"])
+    build_with(gnet, levels, terminal)
+    layers = gnet.layers()
+    weights = scn.synth.init_weights(layers, 37)
+    for i, (W, B, _) in weights.items():
+        pr = np.random.default_rng(i).uniform(0.1, 0.4, len(B)).astype(np.float32) if layers[i]["act"] == orc.PRELU else None
+        weights[i] = (W, B, pr)
+        onet.set_weights(i, W, B, pr)
+        gnet.set_weights(i, W, B, pr)
+    rng = np.random.default_rng(41)
+    with_dropout = [i for i, L in enumerate(layers) if L["type"] == 2 and L["dropout"] > 0]
+    assert len(with_dropout) >= 2
+    for step in range(2):
+        subsets = {}
+        for i in with_dropout:
+            L = layers[i]
+            keep = int(np.float32(L["nOut"]) * (np.float32(1.0) - np.float32(L["dropout"])))
+            subsets[i] = np.sort(rng.choice(L["nOut"], keep, replace=False)).astype(np.int32)
+            onet.set_dropout_features(i, subsets[i])
+            gnet.set_dropout_features(i, subsets[i])
+        keys, off, feats = c["gen"](batch, first=70 * step)
+        labels = ((np.arange(batch) * 5 + step) % c["nClasses"]).astype(np.int32)
+        old = {i: onet.get_weights(i) for i in weights}
+        mine = {i: gnet.get_weights(i) for i in weights}
+        oprobs, ostats = onet.train_step(keys, off, feats, labels, 0.01, 0.9)
+        gprobs, gstats = gnet.train_batch(keys, off, feats, labels, 0.01, 0.9)
+        assert abi.conv_tc_take_error() == 0
+        assert relerr(gprobs, oprobs) < TOL
+        assert gstats["nll"] == pytest.approx(ostats["nll"], rel=1e-4)
+        assert _compare_step(gnet, onet, layers, old) >= 3
+        for i in with_dropout:
+            dropped = np.setdiff1d(np.arange(layers[i]["nOut"]), subsets[i])
+            assert (gnet.iface_present(i + 1) == subsets[i]).all()
+            assert not gnet.iface(i + 1)["features"][:, dropped].any() and not onet.iface(i + 1)["features"][:, dropped].any()
+            gW, gB, gpr = gnet.get_weights(i)
+            oW, oB, opr = onet.get_weights(i)
+            assert (gW[:, dropped] == mine[i][0][:, dropped]).all() and (gB[dropped] == mine[i][1][dropped]).all()
+            assert (oW[:, dropped] == old[i][0][:, dropped]).all() and (oB[dropped] == old[i][1][dropped]).all()
+            if gpr is not None:
+                assert (gpr[dropped] == mine[i][2][dropped]).all() and (gpr[subsets[i]] != mine[i][2][subsets[i]]).any()
+                assert (opr[dropped] == old[i][2][dropped]).all()
