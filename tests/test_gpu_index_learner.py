@@ -59,6 +59,7 @@ def test_index_learning_steps_match_the_reference(scn, abi, tmp_path, dropout):
         rbefore = {i: ref.layer_weights(i) for i in learnt + [top]}
         nums, rprobs, rstats = ref.index_learner_batch(keys, off, feats, BATCH, lr, mom)
         assert len(nums) == BATCH and len(set(nums.tolist())) == BATCH
+        met_before = bool(seen & set(nums.tolist()))  # a picture whose column has been trained: only then is there a gradient below
         seen.update(nums.tolist())
         for i in learnt:  # the feature subsets the reference drew (layers with dropout)
             present = ref.iface(i + 1)["present"]
@@ -78,11 +79,13 @@ def test_index_learning_steps_match_the_reference(scn, abi, tmp_path, dropout):
         assert (gW[:, others] == W0[:, others]).all() and (rW[:, others] == rW0[:, others]).all()
         assert np.abs(rW - rW0).max() > 0
         assert relerr((gW - W0)[:, nums], (rW - rW0)[:, nums]) < UPDATE_TOL
-        if step > 0:  # (the first step's gradient below the index learner is zero: its weights start at zero)
-            for i in learnt:
-                gWi, rWi = gnet.get_weights(i)[0], ref.layer_weights(i)[0]
+        for i in learnt:
+            gWi, rWi = gnet.get_weights(i)[0], ref.layer_weights(i)[0]
+            if met_before:
                 assert np.abs(rWi - rbefore[i][0]).max() > 0
                 assert relerr(gWi - before[i][0], rWi - rbefore[i][0]) < 4 * UPDATE_TOL, "weight update of layer %d" % i
+            else:  # the batch's columns of the index learner are still zero: nothing flows back, nothing moves
+                assert (gWi == before[i][0]).all() and (rWi == rbefore[i][0]).all()
     assert len(seen) > BATCH
     # the weight file carries the index learner's weights: the reference reads the product's file back
     gnet.save_weights(base, 1)
